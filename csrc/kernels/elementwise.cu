@@ -1,0 +1,547 @@
+// HBM-bound fused elementwise / row kernels of the training step (sm_100a):
+// RMSNorm (+residual) fwd/bwd, RoPE, SwiGLU, L2-norm of q/k heads, and the
+// fused soft-cap + cross-entropy forward/backward over vocabulary rows.
+//
+// Math follows the reference model: rms_norm (model/__init__.py:305-310),
+// _apply_rope interleaved pairs (model/__init__.py:337-359), _swiglu
+// (model/__init__.py:547-549), _l2_normalize (model/__init__.py:201-203),
+// soft_cap + cross_entropy (train/__init__.py:561-604).
+#include "common.cuh"
+
+namespace pb {
+
+// ---------------------------------------------------------------------------
+// RMSNorm forward. One warp per row. Optional residual add:
+//   h = x (+ res);  y = h * rsqrt(mean(h^2) + eps) * w
+// h_out (may alias x) receives h when res != nullptr.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) rmsnorm_fwd_kernel(const bf16* __restrict__ x,
+                                                          const bf16* __restrict__ res,
+                                                          const float* __restrict__ w,
+                                                          bf16* __restrict__ y, bf16* h_out,
+                                                          float* __restrict__ rstd_out, int rows,
+                                                          int d, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const size_t base = static_cast<size_t>(row) * d;
+  const int nvec = d >> 3;
+  float ss = 0.f;
+  for (int v = lane; v < nvec; v += 32) {
+    float f[8];
+    bf16x8 p = *reinterpret_cast<const bf16x8*>(x + base + v * 8);
+    unpack8(p, f);
+    if (res != nullptr) {
+      float g[8];
+      bf16x8 q = *reinterpret_cast<const bf16x8*>(res + base + v * 8);
+      unpack8(q, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] += g[i];
+      p = pack8(f);
+      unpack8(p, f);  // the norm sees the rounded residual stream
+      *reinterpret_cast<bf16x8*>(h_out + base + v * 8) = p;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / static_cast<float>(d) + eps);
+  if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+  const bf16* src = (res != nullptr) ? h_out : x;
+  for (int v = lane; v < nvec; v += 32) {
+    float f[8];
+    bf16x8 p = *reinterpret_cast<const bf16x8*>(src + base + v * 8);
+    unpack8(p, f);
+    const float4 w0 = *reinterpret_cast<const float4*>(w + v * 8);
+    const float4 w1 = *reinterpret_cast<const float4*>(w + v * 8 + 4);
+    f[0] *= rstd * w0.x; f[1] *= rstd * w0.y; f[2] *= rstd * w0.z; f[3] *= rstd * w0.w;
+    f[4] *= rstd * w1.x; f[5] *= rstd * w1.y; f[6] *= rstd * w1.z; f[7] *= rstd * w1.w;
+    *reinterpret_cast<bf16x8*>(y + base + v * 8) = pack8(f);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm backward. Persistent: each warp walks rows with a grid stride and
+// keeps its share of dw in registers (NV vectors of 8 columns per lane), then
+// the CTA writes one fp32 partial row to `dw_partial[blockIdx.x]`.
+//   xh = h * rstd;  g = dy * w;  dx = rstd * (g - xh * mean(g * xh)) (+ dres)
+// A second kernel folds the partial rows in a fixed order (deterministic).
+// ---------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(128) rmsnorm_bwd_kernel(
+    const bf16* __restrict__ dy, const bf16* __restrict__ h, const float* __restrict__ w,
+    const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+    float* __restrict__ dw_partial, int rows, int d) {
+  extern __shared__ float sdw[];  // [4 warps][d]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int wpb = blockDim.x >> 5;
+  float acc[NV * 8];
+#pragma unroll
+  for (int i = 0; i < NV * 8; ++i) acc[i] = 0.f;
+  const float inv_d = 1.f / static_cast<float>(d);
+  for (int row = blockIdx.x * wpb + warp; row < rows; row += gridDim.x * wpb) {
+    const size_t base = static_cast<size_t>(row) * d;
+    const float rstd = rstd_in[row];
+    bf16x8 pdy[NV], ph[NV];
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int col = (v * 32 + lane) * 8;
+      float a[8], b[8];
+      pdy[v] = *reinterpret_cast<const bf16x8*>(dy + base + col);
+      ph[v] = *reinterpret_cast<const bf16x8*>(h + base + col);
+      unpack8(pdy[v], a);
+      unpack8(ph[v], b);
+      const float4 w0 = *reinterpret_cast<const float4*>(w + col);
+      const float4 w1 = *reinterpret_cast<const float4*>(w + col + 4);
+      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xhat = b[i] * rstd;
+        dot += a[i] * ww[i] * xhat;
+        acc[v * 8 + i] += a[i] * xhat;
+      }
+    }
+    dot = warp_sum(dot) * inv_d;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int col = (v * 32 + lane) * 8;
+      float a[8], b[8], o[8];
+      unpack8(pdy[v], a);
+      unpack8(ph[v], b);
+      const float4 w0 = *reinterpret_cast<const float4*>(w + col);
+      const float4 w1 = *reinterpret_cast<const float4*>(w + col + 4);
+      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = rstd * (a[i] * ww[i] - b[i] * rstd * dot);
+      if (dres != nullptr) {
+        float r[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(dres + base + col), r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += r[i];
+      }
+      *reinterpret_cast<bf16x8*>(dx + base + col) = pack8(o);
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int col = (v * 32 + lane) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sdw[warp * d + col + i] = acc[v * 8 + i];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float s = 0.f;
+    for (int ww = 0; ww < wpb; ++ww) s += sdw[ww * d + c];
+    dw_partial[static_cast<size_t>(blockIdx.x) * d + c] = s;
+  }
+}
+
+// Generic-width fallback (any d % 8 == 0): one CTA per row at a time, smem dw.
+__global__ void __launch_bounds__(256) rmsnorm_bwd_generic_kernel(
+    const bf16* __restrict__ dy, const bf16* __restrict__ h, const float* __restrict__ w,
+    const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+    float* __restrict__ dw_partial, int rows, int d) {
+  extern __shared__ float sm[];  // [d] dw + 33 scratch
+  float* sdw = sm;
+  float* scratch = sm + d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) sdw[c] = 0.f;
+  __syncthreads();
+  const float inv_d = 1.f / static_cast<float>(d);
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t base = static_cast<size_t>(row) * d;
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+      const float xhat = bf16_to_f32(h[base + c]) * rstd;
+      const float a = bf16_to_f32(dy[base + c]);
+      dot += a * w[c] * xhat;
+      sdw[c] += a * xhat;
+    }
+    dot = block_sum(dot, scratch) * inv_d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+      const float xhat = bf16_to_f32(h[base + c]) * rstd;
+      float o = rstd * (bf16_to_f32(dy[base + c]) * w[c] - xhat * dot);
+      if (dres != nullptr) o += bf16_to_f32(dres[base + c]);
+      dx[base + c] = f32_to_bf16(o);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += blockDim.x)
+    dw_partial[static_cast<size_t>(blockIdx.x) * d + c] = sdw[c];
+}
+
+// dw[c] (+)= sum_p partial[p][c], p in increasing order.
+__global__ void fold_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                     int nparts, int d, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partial[static_cast<size_t>(p) * d + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+// ---------------------------------------------------------------------------
+// RoPE, interleaved (even, odd) pairs, in place. x: [tokens, heads, D].
+// pos[t] is the position of token t (nullptr: t % seq_len). rot_pairs pairs
+// are rotated, the rest pass through. inverse != 0 applies the transpose.
+// ---------------------------------------------------------------------------
+__global__ void rope_kernel(bf16* __restrict__ x, const int* __restrict__ pos, long tokens,
+                            int heads, int D, int rot_pairs, int seq_len, float base,
+                            int inverse) {
+  const int vec_per_head = D >> 3;
+  const long total = tokens * heads * vec_per_head;
+  const float rot_dim = static_cast<float>(rot_pairs * 2);
+  const float log2_base = log2f(base);
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i % vec_per_head);
+    const long th = i / vec_per_head;
+    const long t = th / heads;
+    const int pair0 = v * 4;
+    if (pair0 >= rot_pairs) continue;
+    const float p = pos != nullptr ? static_cast<float>(pos[t])
+                                   : static_cast<float>(t % seq_len);
+    bf16x8* ptr = reinterpret_cast<bf16x8*>(x) + i;
+    float f[8];
+    unpack8(*ptr, f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int pr = pair0 + j;
+      if (pr < rot_pairs) {
+        const float inv_freq = exp2f(-2.f * static_cast<float>(pr) / rot_dim * log2_base);
+        float s, c;
+        sincosf(p * inv_freq, &s, &c);
+        if (inverse) s = -s;
+        const float e = f[2 * j], o = f[2 * j + 1];
+        f[2 * j] = e * c - o * s;
+        f[2 * j + 1] = e * s + o * c;
+      }
+    }
+    *ptr = pack8(f);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU on a fused [rows, 2H] projection: out = silu(gu[:, :H]) * gu[:, H:]
+// ---------------------------------------------------------------------------
+__global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long rows,
+                                  int H) {
+  const int vph = H >> 3;
+  const long total = rows * vph;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = i / vph;
+    const int c = static_cast<int>(i % vph) * 8;
+    float g[8], u[8], o[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(gu + r * 2 * H + c), g);
+    unpack8(*reinterpret_cast<const bf16x8*>(gu + r * 2 * H + H + c), u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] * sigmoidf_(g[j]) * u[j];
+    *reinterpret_cast<bf16x8*>(out + r * H + c) = pack8(o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ gu,
+                                  bf16* __restrict__ dgu, long rows, int H) {
+  const int vph = H >> 3;
+  const long total = rows * vph;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = i / vph;
+    const int c = static_cast<int>(i % vph) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(gu + r * 2 * H + c), g);
+    unpack8(*reinterpret_cast<const bf16x8*>(gu + r * 2 * H + H + c), u);
+    unpack8(*reinterpret_cast<const bf16x8*>(dout + r * H + c), d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = sigmoidf_(g[j]);
+      const float silu = g[j] * s;
+      du[j] = d[j] * silu;
+      dg[j] = d[j] * u[j] * (s + silu * (1.f - s));
+    }
+    *reinterpret_cast<bf16x8*>(dgu + r * 2 * H + c) = pack8(dg);
+    *reinterpret_cast<bf16x8*>(dgu + r * 2 * H + H + c) = pack8(du);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// L2 normalisation of head vectors, in place. x: [nvec, D], one warp each.
+//   xn = x / max(|x|, eps);   inv_norm[nvec] saved for the backward.
+// Backward (in place on dxn): dx = inv * (dxn - xn * <xn, dxn>)
+// (exact when |x| > eps; when clamped the projection term is dropped.)
+// ---------------------------------------------------------------------------
+__global__ void l2norm_fwd_kernel(bf16* __restrict__ x, float* __restrict__ inv_norm, long nvec,
+                                  int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long vec = blockIdx.x * static_cast<long>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (vec >= nvec) return;
+  bf16* p = x + vec * D;
+  float ss = 0.f;
+  for (int c = lane * 4; c < D; c += 128) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(p + c));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(p + c + 2));
+    ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+  }
+  ss = warp_sum(ss);
+  const float n = sqrtf(ss);
+  const float inv = 1.f / fmaxf(n, eps);
+  if (lane == 0) inv_norm[vec] = n > eps ? inv : -inv;  // sign marks the clamped case
+  for (int c = lane * 4; c < D; c += 128) {
+    float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(p + c));
+    float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(p + c + 2));
+    *reinterpret_cast<bf162*>(p + c) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
+    *reinterpret_cast<bf162*>(p + c + 2) = __floats2bfloat162_rn(b.x * inv, b.y * inv);
+  }
+}
+__global__ void l2norm_bwd_kernel(bf16* __restrict__ dxn, const bf16* __restrict__ xn,
+                                  const float* __restrict__ inv_norm, long nvec, int D) {
+  const int lane = threadIdx.x & 31;
+  const long vec = blockIdx.x * static_cast<long>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (vec >= nvec) return;
+  bf16* g = dxn + vec * D;
+  const bf16* y = xn + vec * D;
+  float dot = 0.f;
+  for (int c = lane * 4; c < D; c += 128) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(g + c));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(g + c + 2));
+    const float2 ya = __bfloat1622float2(*reinterpret_cast<const bf162*>(y + c));
+    const float2 yb = __bfloat1622float2(*reinterpret_cast<const bf162*>(y + c + 2));
+    dot += a.x * ya.x + a.y * ya.y + b.x * yb.x + b.y * yb.y;
+  }
+  dot = warp_sum(dot);
+  float inv = inv_norm[vec];
+  if (inv < 0.f) { inv = -inv; dot = 0.f; }
+  for (int c = lane * 4; c < D; c += 128) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(g + c));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(g + c + 2));
+    const float2 ya = __bfloat1622float2(*reinterpret_cast<const bf162*>(y + c));
+    const float2 yb = __bfloat1622float2(*reinterpret_cast<const bf162*>(y + c + 2));
+    *reinterpret_cast<bf162*>(g + c) =
+        __floats2bfloat162_rn(inv * (a.x - ya.x * dot), inv * (a.y - ya.y * dot));
+    *reinterpret_cast<bf162*>(g + c + 2) =
+        __floats2bfloat162_rn(inv * (b.x - yb.x * dot), inv * (b.y - yb.y * dot));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Fused soft-cap + cross-entropy, forward and backward in one launch.
+// logits: [rows, V] bf16, overwritten with d(loss)/d(logits).
+//   c = cap * tanh(x / cap)   (cap <= 0: c = x)
+//   loss_row = wt[row] * (logsumexp(c) - c[target]);  wt carries mask / denom
+//   dx = wt * (softmax(c) - onehot) * (1 - (c/cap)^2)
+// One CTA per row; the row is read from HBM once and re-read from L2.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(512) softcap_ce_kernel(bf16* __restrict__ logits,
+                                                         const int* __restrict__ targets,
+                                                         const float* __restrict__ wt,
+                                                         float* __restrict__ loss_rows,
+                                                         float* __restrict__ lse_rows, int V,
+                                                         float cap, int write_grad) {
+  __shared__ float scratch[33];
+  const long row = blockIdx.x;
+  bf16* p = logits + row * V;
+  const float w = wt[row];
+  const int tgt = targets[row];
+  const int nvec = V >> 3;
+  const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+  if (w == 0.f) {
+    // masked row: zero gradient, zero loss, nothing to reduce
+    if (write_grad) {
+      bf16x8 z;
+      for (int i = 0; i < 4; ++i) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) reinterpret_cast<bf16x8*>(p)[v] = z;
+    }
+    if (threadIdx.x == 0) {
+      loss_rows[row] = 0.f;
+      if (lse_rows != nullptr) lse_rows[row] = 0.f;
+    }
+    return;
+  }
+  float shift;
+  if (cap > 0.f) {
+    shift = cap;  // capped logits are bounded by cap: no max pass needed
+  } else {
+    float m = -INFINITY;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float f[8];
+      unpack8(reinterpret_cast<const bf16x8*>(p)[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, f[i]);
+    }
+    shift = block_max(m, scratch);
+  }
+  float s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(p)[v], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float c = cap > 0.f ? cap * tanh_fast(f[i] * inv_cap) : f[i];
+      s += __expf(c - shift);
+    }
+  }
+  s = block_sum(s, scratch);
+  const float xt = bf16_to_f32(p[tgt]);
+  const float ct = cap > 0.f ? cap * tanh_fast(xt * inv_cap) : xt;
+  const float lse = __logf(s) + shift;
+  if (threadIdx.x == 0) {
+    loss_rows[row] = w * (lse - ct);
+    if (lse_rows != nullptr) lse_rows[row] = lse;
+  }
+  if (!write_grad) return;
+  const float inv_s = 1.f / s;
+  __syncthreads();  // the target element is read above before anyone overwrites it
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(p)[v], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float t = cap > 0.f ? tanh_fast(f[i] * inv_cap) : 0.f;
+      const float c = cap > 0.f ? cap * t : f[i];
+      float g = __expf(c - shift) * inv_s;
+      if (v * 8 + i == tgt) g -= 1.f;
+      g *= w;
+      if (cap > 0.f) g *= (1.f - t * t);
+      f[i] = g;
+    }
+    reinterpret_cast<bf16x8*>(p)[v] = pack8(f);
+  }
+}
+
+// out[i] = sigmoid(x[i]) (bf16 -> bf16), dx = dy * s * (1 - s)
+__global__ void sigmoid_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long n) {
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x)
+    y[i] = f32_to_bf16(sigmoidf_(bf16_to_f32(x[i])));
+}
+
+static inline int grid_for(long total, int block, int cap = 148 * 16) {
+  long g = (total + block - 1) / block;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+
+}  // namespace pb
+
+using namespace pb;
+
+PB_API int pb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out,
+                          void* rstd, int rows, int d, float eps, cudaStream_t st) {
+  if (d % 8 != 0 || rows <= 0) return PB_BAD_ARG;
+  const int wpb = 4;
+  rmsnorm_fwd_kernel<<<(rows + wpb - 1) / wpb, wpb * 32, 0, st>>>(
+      static_cast<const bf16*>(x), static_cast<const bf16*>(res), static_cast<const float*>(w),
+      static_cast<bf16*>(y), static_cast<bf16*>(h_out), static_cast<float*>(rstd), rows, d, eps);
+  return cudaGetLastError();
+}
+
+// Number of partial rows rmsnorm_bwd writes (scratch must hold that many x d floats).
+PB_API int pb_rmsnorm_bwd_nparts(int rows, int d) {
+  int g = 148 * 4;
+  const int per = (d % 256 == 0 && d <= 2048) ? 4 : 1;
+  const int need = (rows + per - 1) / per;
+  return need < g ? (need < 1 ? 1 : need) : g;
+}
+
+PB_API int pb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const void* rstd,
+                          const void* dres, void* dx, void* dw, void* scratch, int accumulate,
+                          int rows, int d, cudaStream_t st) {
+  if (d % 8 != 0 || rows <= 0) return PB_BAD_ARG;
+  const int grid = pb_rmsnorm_bwd_nparts(rows, d);
+  const bf16* dy_ = static_cast<const bf16*>(dy);
+  const bf16* h_ = static_cast<const bf16*>(h);
+  const float* w_ = static_cast<const float*>(w);
+  const float* r_ = static_cast<const float*>(rstd);
+  const bf16* dr_ = static_cast<const bf16*>(dres);
+  bf16* dx_ = static_cast<bf16*>(dx);
+  float* part = static_cast<float*>(scratch);
+  if (d % 256 == 0 && d <= 2048) {
+    const size_t smem = 4 * d * sizeof(float);
+    switch (d / 256) {
+#define PB_CASE(NV)                                                                          \
+  case NV:                                                                                   \
+    rmsnorm_bwd_kernel<NV><<<grid, 128, smem, st>>>(dy_, h_, w_, r_, dr_, dx_, part, rows, d); \
+    break;
+      PB_CASE(1) PB_CASE(2) PB_CASE(3) PB_CASE(4) PB_CASE(5) PB_CASE(6) PB_CASE(7) PB_CASE(8)
+#undef PB_CASE
+      default:
+        return PB_BAD_ARG;
+    }
+  } else {
+    const size_t smem = (d + 33) * sizeof(float);
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(rmsnorm_bwd_generic_kernel,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    rmsnorm_bwd_generic_kernel<<<grid, 256, smem, st>>>(dy_, h_, w_, r_, dr_, dx_, part, rows, d);
+  }
+  fold_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(part, static_cast<float*>(dw), grid, d,
+                                                        accumulate);
+  return cudaGetLastError();
+}
+
+PB_API int pb_rope(void* x, const void* pos, long tokens, int heads, int D, int rot_pairs,
+                   int seq_len, float base, int inverse, cudaStream_t st) {
+  if (D % 8 != 0) return PB_BAD_ARG;
+  const long total = tokens * heads * (D / 8);
+  rope_kernel<<<grid_for(total, 256), 256, 0, st>>>(static_cast<bf16*>(x),
+                                                    static_cast<const int*>(pos), tokens, heads,
+                                                    D, rot_pairs, seq_len, base, inverse);
+  return cudaGetLastError();
+}
+
+PB_API int pb_swiglu_fwd(const void* gu, void* out, long rows, int H, cudaStream_t st) {
+  if (H % 8 != 0) return PB_BAD_ARG;
+  swiglu_fwd_kernel<<<grid_for(rows * (H / 8), 256), 256, 0, st>>>(
+      static_cast<const bf16*>(gu), static_cast<bf16*>(out), rows, H);
+  return cudaGetLastError();
+}
+PB_API int pb_swiglu_bwd(const void* dout, const void* gu, void* dgu, long rows, int H,
+                         cudaStream_t st) {
+  if (H % 8 != 0) return PB_BAD_ARG;
+  swiglu_bwd_kernel<<<grid_for(rows * (H / 8), 256), 256, 0, st>>>(
+      static_cast<const bf16*>(dout), static_cast<const bf16*>(gu), static_cast<bf16*>(dgu), rows,
+      H);
+  return cudaGetLastError();
+}
+
+PB_API int pb_l2norm_fwd(void* x, void* inv_norm, long nvec, int D, float eps, cudaStream_t st) {
+  if (D % 4 != 0) return PB_BAD_ARG;
+  const int wpb = 8;
+  l2norm_fwd_kernel<<<static_cast<unsigned>((nvec + wpb - 1) / wpb), wpb * 32, 0, st>>>(
+      static_cast<bf16*>(x), static_cast<float*>(inv_norm), nvec, D, eps);
+  return cudaGetLastError();
+}
+PB_API int pb_l2norm_bwd(void* dxn, const void* xn, const void* inv_norm, long nvec, int D,
+                         cudaStream_t st) {
+  if (D % 4 != 0) return PB_BAD_ARG;
+  const int wpb = 8;
+  l2norm_bwd_kernel<<<static_cast<unsigned>((nvec + wpb - 1) / wpb), wpb * 32, 0, st>>>(
+      static_cast<bf16*>(dxn), static_cast<const bf16*>(xn),
+      static_cast<const float*>(inv_norm), nvec, D);
+  return cudaGetLastError();
+}
+
+PB_API int pb_softcap_ce(void* logits, const void* targets, const void* wt, void* loss_rows,
+                         void* lse_rows, long rows, int V, float cap, int write_grad,
+                         cudaStream_t st) {
+  if (V % 8 != 0 || rows <= 0) return PB_BAD_ARG;
+  softcap_ce_kernel<<<static_cast<unsigned>(rows), 512, 0, st>>>(
+      static_cast<bf16*>(logits), static_cast<const int*>(targets),
+      static_cast<const float*>(wt), static_cast<float*>(loss_rows),
+      static_cast<float*>(lse_rows), V, cap, write_grad);
+  return cudaGetLastError();
+}
+
+PB_API int pb_sigmoid(const void* x, void* y, long n, cudaStream_t st) {
+  sigmoid_fwd_kernel<<<grid_for(n, 256), 256, 0, st>>>(static_cast<const bf16*>(x),
+                                                       static_cast<bf16*>(y), n);
+  return cudaGetLastError();
+}

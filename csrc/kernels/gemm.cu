@@ -1,0 +1,392 @@
+// Persistent warp-specialised bf16 GEMM on the 5th-gen tensor cores (sm_100a).
+//
+//   C[b] = alpha * A[b] * B[b]^T + beta * D[b]
+//
+// A is logically [M, K], B logically [N, K]. Either operand may be stored
+// K-major (row-major as written) or MN-major (the transpose, contraction index
+// outermost): that covers y = x W^T, dx = dy W, dW = dy^T x and the
+// Newton-Schulz products without materialising a transpose.
+//
+// Structure per CTA (one per SM, persistent over a swizzled tile order):
+//   warp 0     TMA producer: cp.async.bulk.tensor tiles, 128B swizzle, into a
+//              STAGES-deep shared-memory ring guarded by full/empty mbarriers
+//   warp 1     allocates tensor memory; one lane issues tcgen05.mma
+//              (128 x BN x 16 per instruction), tcgen05.commit frees ring slots
+//              and publishes the accumulator
+//   warps 2-5  epilogue: tcgen05.ld the fp32 accumulator (two accumulators in
+//              tensor memory so the next tile's main loop overlaps), scale,
+//              add D, convert, store
+// No cluster launch and no multicast: safe in multi-GPU code.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace pb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+
+struct GemmParams {
+  int M, N, K, batch;
+  void* C;
+  const void* D;
+  long ldc, strideC, ldd, strideD;
+  float alpha, beta;
+  int out_f32, d_f32;
+  int a_mn, b_mn;
+  int* status;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int STAGES = S::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* smA = smem;
+  uint8_t* smB = smem + STAGES * S::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int tiles_per_batch = num_m * num_n;
+  const long total_tiles = static_cast<long>(tiles_per_batch) * p.batch;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](long t, int& b, int& m_blk, int& n_blk) {
+    b = static_cast<int>(t / tiles_per_batch);
+    const int r = static_cast<int>(t % tiles_per_batch);
+    const int group = 8 * num_n;
+    const int g = r / group;
+    const int first_m = g * 8;
+    const int gsz = min(num_m - first_m, 8);
+    m_blk = first_m + (r % group) % gsz;
+    n_blk = (r % group) / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int b, m_blk, n_blk;
+        tile_coords(t, b, m_blk, n_blk);
+        const int m0 = m_blk * BM, n0 = n_blk * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full[s], S::STAGE_BYTES);
+          uint8_t* a_dst = smA + s * S::A_BYTES;
+          uint8_t* b_dst = smB + s * S::B_BYTES;
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_3d(a_dst, &tmA, &full[s], k0, m0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_3d(a_dst + c * 8192, &tmA, &full[s], m0 + c * 64, k0, b);
+          }
+          if (!p.b_mn) {
+            tma_load_3d(b_dst, &tmB, &full[s], k0, n0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_3d(b_dst + c * 8192, &tmB, &full[s], n0 + c * 64, k0, b);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(1, 1, BM, BN, p.a_mn ? 1u : 0u, p.b_mn ? 1u : 0u);
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[s], ph, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smA + s * S::A_BYTES);
+          const uint32_t b_addr = smem_u32(smB + s * S::B_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / 16; ++j) {
+            // K-major: 16 elements = 32 bytes along the swizzled row.
+            // MN-major: 16 k-rows = two 8-row groups of 1024 bytes.
+            const uint64_t ad = p.a_mn ? make_sdesc_sw128(a_addr + j * 2048, 8192, 1024)
+                                       : make_sdesc_sw128(a_addr + j * 32, 16, 1024);
+            const uint64_t bd = p.b_mn ? make_sdesc_sw128(b_addr + j * 2048, 8192, 1024)
+                                       : make_sdesc_sw128(b_addr + j * 32, 16, 1024);
+            umma_f16(d_tmem, ad, bd, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int b, m_blk, n_blk;
+      tile_coords(t, b, m_blk, n_blk);
+      const int row = m_blk * BM + q * 32 + lane;
+      const int n0 = n_blk * BN;
+      if (!mbar_wait(&tfull[acc], acc_ph, p.status)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const bool row_ok = row < p.M;
+      const size_t c_off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
+      const size_t d_off = static_cast<size_t>(b) * p.strideD + static_cast<size_t>(row) * p.ldd;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + c, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c;
+        if (row_ok && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          const bool full_chunk = (col0 + 32 <= p.N);
+          if (p.D != nullptr) {
+            if (p.d_f32) {
+              const float* dp = static_cast<const float*>(p.D) + d_off + col0;
+              if (full_chunk && (p.ldd % 4 == 0)) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float4 d4 = reinterpret_cast<const float4*>(dp)[i];
+                  v[4 * i] += p.beta * d4.x; v[4 * i + 1] += p.beta * d4.y;
+                  v[4 * i + 2] += p.beta * d4.z; v[4 * i + 3] += p.beta * d4.w;
+                }
+              } else {
+                for (int i = 0; i < 32 && col0 + i < p.N; ++i) v[i] += p.beta * dp[i];
+              }
+            } else {
+              const bf16* dp = static_cast<const bf16*>(p.D) + d_off + col0;
+              if (full_chunk && (p.ldd % 8 == 0)) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  float f[8];
+                  unpack8(reinterpret_cast<const bf16x8*>(dp)[i], f);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[8 * i + j] += p.beta * f[j];
+                }
+              } else {
+                for (int i = 0; i < 32 && col0 + i < p.N; ++i)
+                  v[i] += p.beta * bf16_to_f32(dp[i]);
+              }
+            }
+          }
+          if (p.out_f32) {
+            float* cp = static_cast<float*>(p.C) + c_off + col0;
+            if (full_chunk && (p.ldc % 4 == 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(cp)[i] =
+                    make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) cp[i] = v[i];
+            }
+          } else {
+            bf16* cp = static_cast<bf16*>(p.C) + c_off + col0;
+            if (full_chunk && (p.ldc % 8 == 0)) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) reinterpret_cast<bf16x8*>(cp)[i] = pack8(v + 8 * i);
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) cp[i] = f32_to_bf16(v[i]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != PB_OK) {
+    // A wait ran out somewhere: give copies that may still be in flight a
+    // bounded moment to land before shared memory is released.
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 3-D map over a [batch][outer][inner] bf16 (or 1-byte) tensor, 128B swizzle.
+int make_tmap_3d(CUtensorMap* tm, const void* base, int elem_bytes, uint64_t inner,
+                 uint64_t outer, uint64_t batch, uint64_t ld_elems, uint64_t batch_stride_elems,
+                 uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[3] = {inner, outer, batch};
+  cuuint64_t strides[2] = {ld_elems * elem_bytes,
+                           (batch > 1 ? batch_stride_elems : ld_elems * outer) * elem_bytes};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt =
+      elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUresult r =
+      fn(tm, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+static int g_num_sms = 0;
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int BN>
+int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_ctas,
+                cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmSmem<BN>::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const long tiles =
+      static_cast<long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
+  int grid = num_sms();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = static_cast<int>(tiles);
+  gemm_bf16_kernel<BN><<<grid, 192, GemmSmem<BN>::TOTAL, st>>>(tmA, tmB, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace pb
+
+using namespace pb;
+
+// C = alpha * A * B^T + beta * D.  See the header comment for the layouts.
+//   a_mn == 0: A stored [M, K] with row stride lda;  a_mn == 1: stored [K, M], row stride lda
+//   b_mn == 0: B stored [N, K] with row stride ldb;  b_mn == 1: stored [K, N], row stride ldb
+// Strides are in elements. Base pointers 16-byte aligned, lda/ldb multiples of 8.
+// `status` (device int, may be null) latches a non-zero code if a bounded wait ran out.
+// `max_ctas` > 0 limits the persistent grid (leaves SMs for a concurrent kernel).
+PB_API int pb_gemm_bf16(const void* A, const void* B, void* C, const void* D, int M, int N, int K,
+                        int batch, long lda, long ldb, long ldc, long ldd, long strideA,
+                        long strideB, long strideC, long strideD, int a_mn, int b_mn, int out_f32,
+                        int d_f32, float alpha, float beta, int* status, int max_ctas,
+                        cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return PB_BAD_ARG;
+  if ((lda % 8) != 0 || (ldb % 8) != 0) return PB_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return PB_BAD_ARG;
+  if (batch > 1 && ((strideA % 8) != 0 || (strideB % 8) != 0)) return PB_BAD_ARG;
+  const bool bn256 = N > 128;
+  const int BN = bn256 ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  int r;
+  if (!a_mn)
+    r = make_tmap_3d(&tmA, A, 2, K, M, batch, lda, strideA, BK, BM);
+  else
+    r = make_tmap_3d(&tmA, A, 2, M, K, batch, lda, strideA, 64, BK);
+  if (r != 0) return 1000 + r;
+  if (!b_mn)
+    r = make_tmap_3d(&tmB, B, 2, K, N, batch, ldb, strideB, BK, BN);
+  else
+    r = make_tmap_3d(&tmB, B, 2, N, K, batch, ldb, strideB, 64, BK);
+  if (r != 0) return 2000 + r;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.C = C; p.D = D;
+  p.ldc = ldc; p.strideC = strideC; p.ldd = ldd; p.strideD = strideD;
+  p.alpha = alpha; p.beta = beta;
+  p.out_f32 = out_f32; p.d_f32 = d_f32;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.status = status;
+  return bn256 ? launch_gemm<256>(tmA, tmB, p, max_ctas, st)
+               : launch_gemm<128>(tmA, tmB, p, max_ctas, st);
+}

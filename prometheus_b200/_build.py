@@ -1,0 +1,129 @@
+"""In-tree build of the native libraries.
+
+Two shared objects are produced next to the package (never installed into
+site-packages, so a process that loads them shows the in-tree path):
+
+* ``prometheus_b200/_lib/libpb200_kernels.so`` — every ``csrc/kernels/*.cu`` and
+  ``csrc/comm/*.cu`` compiled by ``nvcc`` for ``sm_100a`` only. The kernels
+  export a plain C ABI (raw device pointers + a stream handle) and are bound
+  with ``ctypes``; nothing in them depends on the PyTorch headers, so a file
+  compiles in seconds.
+* ``prometheus_b200/_lib/_pb200_native*.so`` — the C++17 systems code under
+  ``csrc/native`` (checkpoint store, data loader, controller, observability,
+  harness) bound with pybind11.
+
+``python -m prometheus_b200._build`` builds both; ``build_all()`` is what
+``__graft_entry__.build()`` calls. Objects are rebuilt only when their source
+(or a shared header) is newer.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+LIB_DIR = Path(__file__).resolve().parent / "_lib"
+OBJ_DIR = ROOT / "build" / "obj"
+
+KERNEL_LIB = LIB_DIR / "libpb200_kernels.so"
+NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
+              "-Xcompiler", "-fvisibility=hidden"]
+
+
+def native_lib_path() -> Path:
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    return LIB_DIR / f"_pb200_native{suffix}"
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _newer(src_list, target: Path) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(Path(s).stat().st_mtime > t for s in src_list)
+
+
+def _run(cmd, verbose=False):
+    if verbose:
+        print(" ".join(str(c) for c in cmd), flush=True)
+    r = subprocess.run([str(c) for c in cmd], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"build failed: {' '.join(str(c) for c in cmd)}\n{r.stdout}\n{r.stderr}")
+    return r.stdout + r.stderr
+
+
+def kernel_sources() -> list[Path]:
+    return sorted(list((CSRC / "kernels").glob("*.cu")) + list((CSRC / "comm").glob("*.cu")))
+
+
+def build_kernels(verbose: bool = False, force: bool = False) -> Path:
+    """Compile every .cu for sm_100a and link libpb200_kernels.so."""
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    nvcc = _nvcc()
+    headers = list((CSRC / "kernels").glob("*.cuh")) + list((CSRC / "comm").glob("*.cuh"))
+    srcs = kernel_sources()
+    objs, jobs = [], []
+    for src in srcs:
+        obj = OBJ_DIR / (src.parent.name + "_" + src.stem + ".o")
+        objs.append(obj)
+        if force or _newer([src, *headers], obj):
+            jobs.append([nvcc, *NVCC_ARCH, *NVCC_FLAGS, "-I", CSRC / "kernels", "-I", CSRC / "comm",
+                         "-c", src, "-o", obj])
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(lambda c: _run(c, verbose), jobs))
+    if force or jobs or _newer(objs, KERNEL_LIB):
+        _run([nvcc, *NVCC_ARCH, "-shared", "-o", KERNEL_LIB, *objs], verbose)
+    return KERNEL_LIB
+
+
+def build_native(verbose: bool = False, force: bool = False) -> Path | None:
+    """Compile csrc/native/*.cpp into the pybind11 module (host only, no CUDA)."""
+    srcs = sorted((CSRC / "native").glob("*.cpp"))
+    if not srcs:
+        return None
+    import pybind11
+
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    headers = list((CSRC / "native").glob("*.hpp")) + list((CSRC / "native").glob("*.h"))
+    inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+           "-I", CSRC / "native"]
+    flags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function"]
+    objs, jobs = [], []
+    for src in srcs:
+        obj = OBJ_DIR / ("native_" + src.stem + ".o")
+        objs.append(obj)
+        if force or _newer([src, *headers], obj):
+            jobs.append(["g++", *flags, *inc, "-c", src, "-o", obj])
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(lambda c: _run(c, verbose), jobs))
+    out = native_lib_path()
+    if force or jobs or _newer(objs, out):
+        _run(["g++", "-shared", "-o", out, *objs, "-lpthread"], verbose)
+    return out
+
+
+def build_all(verbose: bool = False, force: bool = False) -> None:
+    build_kernels(verbose, force)
+    build_native(verbose, force)
+
+
+if __name__ == "__main__":
+    build_all(verbose="-v" in sys.argv, force="--force" in sys.argv)
+    print("built:", KERNEL_LIB, native_lib_path())

@@ -1,0 +1,100 @@
+"""ctypes binding of ``libpb200_kernels.so`` (the hand-written sm_100a kernels).
+
+Every exported function takes raw device pointers, sizes and a CUDA stream
+handle and returns 0 on success (a CUDA error code or a small positive library
+code otherwise). ``call(name, *args)`` raises on a non-zero return, so a
+missing or failing kernel is never silently replaced by a PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libpb200_kernels.so"
+_lib = None
+
+P, I, L, F = c_void_p, c_int, c_long, c_float
+
+_SIGS = {
+    "pb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "pb_rmsnorm_bwd_nparts": [I, I],
+    "pb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
+    "pb_rope": [P, P, L, I, I, I, I, F, I, P],
+    "pb_swiglu_fwd": [P, P, L, I, P],
+    "pb_swiglu_bwd": [P, P, P, L, I, P],
+    "pb_l2norm_fwd": [P, P, L, I, F, P],
+    "pb_l2norm_bwd": [P, P, P, L, I, P],
+    "pb_softcap_ce": [P, P, P, P, P, L, I, F, I, P],
+    "pb_sigmoid": [P, P, L, P],
+    "pb_sumsq_nparts": [L],
+    "pb_sumsq_f32": [P, L, P, P, I, P],
+    "pb_sumsq_bf16": [P, L, P, P, I, P],
+    "pb_adamw": [P, P, P, P, P, L, F, F, F, F, F, I, P, F, F, P],
+    "pb_muon_prepare": [P, P, P, L, F, P, F, F, P, P],
+    "pb_muon_apply": [P, P, P, L, F, F, F, P],
+    "pb_cast_f32_bf16": [P, P, L, F, P],
+    "pb_axpy_bf16_f32": [P, P, L, F, P],
+    "pb_transpose_bf16": [P, P, I, I, I, P],
+    "pb_gemm_bf16": [P, P, P, P, I, I, I, I, L, L, L, L, L, L, L, L, I, I, I, I, F, F, P, I, P],
+}
+
+
+class KernelLibraryMissing(RuntimeError):
+    """The compiled kernel library is absent: run ``python -m prometheus_b200._build``."""
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def register(name: str, argtypes: list) -> None:
+    """Declare the signature of another exported symbol (used by sibling op modules)."""
+    _SIGS[name] = argtypes
+    if _lib is not None and hasattr(_lib, name):
+        fn = getattr(_lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+
+
+def load():
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise KernelLibraryMissing(f"{_LIB_PATH} not built")
+        _lib = ctypes.CDLL(str(_LIB_PATH))
+        for name, argtypes in _SIGS.items():
+            if hasattr(_lib, name):
+                fn = getattr(_lib, name)
+                fn.argtypes = argtypes
+                fn.restype = c_int
+    return _lib
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int | None:
+    """Device pointer of a tensor (None passes a null pointer)."""
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def call(name: str, *args) -> None:
+    fn = getattr(load(), name)
+    rc = fn(*args)
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc}")
+
+
+def query(name: str, *args) -> int:
+    """Call a host-only helper that returns a value instead of a status."""
+    return getattr(load(), name)(*args)
