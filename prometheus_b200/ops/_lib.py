@@ -38,6 +38,8 @@ _SIGS = {
     "pb_cast_f32_bf16": [P, P, L, F, P],
     "pb_axpy_bf16_f32": [P, P, L, F, P],
     "pb_transpose_bf16": [P, P, I, I, I, P],
+    "pb_wait_flag_probe": [P, I, L, P, P],
+    "pb_set_flag": [P, I, P],
     "pb_gemm_bf16": [P, P, P, P, I, I, I, I, L, L, L, L, L, L, L, L, I, I, I, I, F, F, P, I, P],
 }
 
@@ -88,9 +90,16 @@ def ptr(t) -> int | None:
     return t.data_ptr()
 
 
+# kernels launched by one call of each entry point (for launch accounting)
+_LAUNCHES = {"pb_rmsnorm_bwd": 2, "pb_sumsq_f32": 2, "pb_sumsq_bf16": 2, "pb_muon_prepare": 3}
+launch_count = 0
+
+
 def call(name: str, *args) -> None:
+    global launch_count
     fn = getattr(load(), name)
     rc = fn(*args)
+    launch_count += _LAUNCHES.get(name, 1)
     if rc != 0:
         raise RuntimeError(f"{name} failed with code {rc}")
 

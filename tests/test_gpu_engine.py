@@ -1,0 +1,63 @@
+"""The fused trainer against the fp32 parameter-tree step (needs a B200)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def small_hybrid():
+    from prometheus_b200 import model
+
+    return model.ModelConfig(
+        d_model=256, n_layers=4, n_dense=4, n_moe=0, n_linear_attn=3, n_mla=1,
+        n_routed_experts=1, n_shared_experts=0, top_k=1, expert_hidden=512, mtp_heads=0,
+        core_block_layers=4, recurrence_train_mean=1.0, recurrence_max=1, vocab_size=1024,
+        max_context=256, prelude_layers=0, coda_layers=0, adapter_hidden=256,
+        n_heads=4, d_head=64, n_kv_heads=2, softmax_kind="gqa", softmax_every=4,
+        delta_beta="sigmoid", chunk=64, dense_hidden=512)
+
+
+def test_engine_matches_tree_step():
+    from prometheus_b200 import engine, model, train
+
+    cfg = small_hybrid()
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10,
+                                  adamw_wd=0.0)
+    params = model.init_params(cfg, 0)
+    tr = engine.Trainer(cfg, tcfg, params=params, micro_batch=2)
+    g = torch.Generator().manual_seed(0)
+    tokens = torch.randint(0, cfg.vocab_size, (4, 128), generator=g)
+    # reference: fp32 tree step on the GPU
+    dev_params = train._map_tree(params, lambda _n, p: p.cuda())
+    opt = train.init_opt_state(dev_params, tcfg, muon_all_matrices=True)
+    batch = train.Batch(tokens=tokens.cuda(), loss_mask=torch.ones(4, 128, device="cuda"),
+                        positions=torch.arange(128))
+    ref = train.train_step(dev_params, opt, batch, cfg, tcfg, step=1, muon_transfer=True,
+                           muon_weight_decay=0.0, muon_all_matrices=True)
+    out = tr.step(tokens.cuda())
+    assert abs(out["loss"].item() - ref.loss.ce.item()) < 3e-2 * ref.loss.ce.item()
+    assert abs(out["grad_norm"].item() - ref.grad_norm.item()) < 0.1 * ref.grad_norm.item()
+    got = model.flatten_params(tr.export_tree())
+    want = model.flatten_params(ref.params)
+    before = model.flatten_params(params)
+    for name in ("layers.0.W_q", "layers.1.ffn_gate", "layers.3.W_k", "layers.2.W_o", "embed",
+                 "layers.0.pre_ffn_norm", "layers.0.W_beta"):
+        du_ref = (want[name].cpu() - before[name]).float()
+        du_got = (got[name] - before[name]).float()
+        cos = torch.nn.functional.cosine_similarity(du_ref.flatten(), du_got.flatten(), dim=0)
+        assert cos.item() > 0.9, f"{name}: update cosine {cos.item():.3f}"
+        assert 0.7 < du_got.norm().item() / (du_ref.norm().item() + 1e-12) < 1.4, name
+
+
+def test_engine_overfits_fixed_batch():
+    from prometheus_b200 import engine, train
+
+    cfg = small_hybrid()
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10)
+    tr = engine.Trainer(cfg, tcfg, seed=1, micro_batch=2)
+    tokens = torch.randint(0, cfg.vocab_size, (4, 128), device="cuda",
+                           generator=torch.Generator(device="cuda").manual_seed(0))
+    losses = [tr.step(tokens)["loss"].item() for _ in range(12)]
+    assert losses[-1] < losses[0] - 0.5, losses
+    from prometheus_b200.ops import functional as ops
+    ops.check_status("cuda")

@@ -1,0 +1,211 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same op (needs a B200)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+BF16 = torch.bfloat16
+
+
+def _r(*shape, seed=0, scale=1.0, dtype=BF16):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(dtype)
+
+
+def _close(got, ref, tol=2e-2):
+    got, ref = got.float(), ref.float()
+    err = (got - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err <= tol * scale, f"max err {err:.4g} vs scale {scale:.4g}"
+
+
+def test_kernel_library_is_loaded_in_tree():
+    from prometheus_b200.ops import _lib
+
+    _lib.load()
+    assert "prometheus_b200/_lib/libpb200_kernels.so" in open("/proc/self/maps").read()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (384, 512, 1024),
+                                   (200, 328, 264), (4096, 2048, 2048)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    from prometheus_b200.ops import functional as ops
+
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need the MN extent to be a multiple of 8")
+    a = _r(K, M, seed=1) if a_mn else _r(M, K, seed=1)
+    b = _r(K, N, seed=2) if b_mn else _r(N, K, seed=2)
+    c = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    ref = ops.gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn)
+    _close(c, ref)
+    ops.check_status("cuda")
+
+
+def test_gemm_batched_epilogue_variants():
+    from prometheus_b200.ops import functional as ops
+
+    a, b = _r(3, 256, 192, seed=1), _r(3, 320, 192, seed=2)
+    d = _r(3, 256, 320, seed=3)
+    c = ops.gemm(a, b, d=d, alpha=0.5, beta=-2.0)
+    _close(c, ops.gemm_ref(a, b, d=d, alpha=0.5, beta=-2.0))
+    acc = torch.randn(256, 320, device="cuda")
+    ref = acc + ops.gemm_ref(a[0], b[0])
+    ops.gemm(a[0], b[0], out=acc, d=acc, beta=1.0)
+    _close(acc, ref)
+    c32 = ops.gemm(a, b, out_dtype=torch.float32)
+    assert c32.dtype == torch.float32
+    _close(c32, ops.gemm_ref(a, b), tol=5e-3)
+    ops.check_status("cuda")
+
+
+def test_gemm_limited_grid_and_many_tiles():
+    from prometheus_b200.ops import functional as ops
+
+    a, b = _r(2048, 512, seed=1), _r(1536, 512, seed=2)
+    _close(ops.gemm(a, b, max_ctas=16), ops.gemm_ref(a, b))
+    ops.check_status("cuda")
+
+
+@pytest.mark.parametrize("rows,d", [(37, 256), (1000, 2048), (64, 384), (5, 128)])
+def test_rmsnorm_fwd_bwd(rows, d):
+    from prometheus_b200.ops import functional as ops
+
+    x = _r(rows, d, seed=1).requires_grad_(True)
+    res = _r(rows, d, seed=2).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).requires_grad_(True)
+    y, h = ops.add_rmsnorm(x, res, w)
+    gy, gh = _r(rows, d, seed=3), _r(rows, d, seed=4)
+    (y.float() * gy.float()).sum().add((h.float() * gh.float()).sum()).backward()
+    xr, rr, wr = (t.detach().float().requires_grad_(True) for t in (x, res, w))
+    yr, hr = ops.rmsnorm_ref(xr, wr, res=rr)
+    # the kernel rounds h to bf16 before normalising
+    _close(h, hr, 1e-2)
+    _close(y, yr, 2e-2)
+    ((yr * gy.float()).sum() + (hr * gh.float()).sum()).backward()
+    _close(x.grad, xr.grad, 3e-2)
+    _close(res.grad, rr.grad, 3e-2)
+    _close(w.grad, wr.grad, 3e-2)
+    y1 = ops.rmsnorm(x.detach(), w.detach())
+    _close(y1, ops.rmsnorm_ref(x.detach(), w.detach()), 2e-2)
+
+
+def test_rope_matches_model_and_inverts():
+    from prometheus_b200 import model
+    from prometheus_b200.ops import functional as ops
+
+    B, S, H, D = 2, 300, 3, 128
+    x = _r(B, S, H, D, seed=1)
+    y = ops.rope_(x, seq_len=S)
+    ref, _ = model.rope(x.float(), x.float(), torch.arange(S, device="cuda"), partial=False)
+    _close(y, ref, 1e-2)
+    xg = x.clone().requires_grad_(True)
+    g = _r(B, S, H, D, seed=2)
+    (ops.rope_(xg, seq_len=S).float() * g.float()).sum().backward()
+    xr = x.float().requires_grad_(True)
+    (model.rope(xr, xr, torch.arange(S, device="cuda"), partial=False)[0] * g.float()).sum().backward()
+    _close(xg.grad, xr.grad, 1e-2)
+    # large positions keep full precision (no fast-math sincos)
+    pos = torch.full((B * S,), 131071, dtype=torch.int32, device="cuda")
+    y2 = ops.rope_(x, seq_len=S, pos=pos)
+    ref2, _ = model.rope(x.float(), x.float(), torch.full((S,), 131071.0, device="cuda"), partial=False)
+    _close(y2, ref2, 1e-2)
+
+
+def test_swiglu_fwd_bwd():
+    from prometheus_b200.ops import functional as ops
+
+    gu = _r(77, 2 * 512, seed=1).requires_grad_(True)
+    g = _r(77, 512, seed=2)
+    out = ops.swiglu(gu)
+    (out.float() * g.float()).sum().backward()
+    gr = gu.detach().float().requires_grad_(True)
+    ref = ops.swiglu_ref(gr)
+    (ref * g.float()).sum().backward()
+    _close(out, ref)
+    _close(gu.grad, gr.grad)
+
+
+def test_l2norm_fwd_bwd():
+    from prometheus_b200.ops import functional as ops
+
+    x = _r(50, 4, 128, seed=1).requires_grad_(True)
+    g = _r(50, 4, 128, seed=2)
+    y = ops.l2norm(x)
+    (y.float() * g.float()).sum().backward()
+    xr = x.detach().float().requires_grad_(True)
+    yr = xr / xr.norm(dim=-1, keepdim=True).clamp(min=1e-6)
+    (yr * g.float()).sum().backward()
+    _close(y, yr)
+    _close(x.grad, xr.grad, 3e-2)
+
+
+@pytest.mark.parametrize("cap", [30.0, 0.0])
+def test_softcap_ce_fused(cap):
+    from prometheus_b200.ops import functional as ops
+
+    rows, d, V = 300, 256, 4096
+    h = _r(rows, d, seed=1).requires_grad_(True)
+    U = _r(V, d, seed=2, scale=0.3).requires_grad_(True)
+    tgt = torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32)
+    wt = (torch.rand(rows, device="cuda") > 0.2).float() / rows
+    loss = ops.softcap_cross_entropy(h, U, tgt, wt, cap, chunk_rows=128)
+    loss.backward()
+    hr, Ur = h.detach().float().requires_grad_(True), U.detach().float().requires_grad_(True)
+    ref = ops.softcap_cross_entropy_ref(hr, Ur, tgt, wt, cap)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) <= 2e-2 * abs(ref.item())
+    _close(h.grad, hr.grad, 5e-2)
+    _close(U.grad, Ur.grad, 5e-2)
+
+
+def test_optimizer_kernels():
+    from prometheus_b200 import train
+    from prometheus_b200.ops import _lib
+    from prometheus_b200.ops._lib import call, ptr, stream_ptr
+
+    n = 100_003
+    g = torch.randn(n, device="cuda")
+    scratch = torch.empty(_lib.query("pb_sumsq_nparts", n) + 8, device="cuda")
+    out = torch.zeros(1, device="cuda")
+    call("pb_sumsq_f32", ptr(g), n, ptr(scratch), ptr(out), 0, stream_ptr())
+    assert out.item() == pytest.approx((g.double() ** 2).sum().item(), rel=1e-5)
+    p, m, v = torch.randn(n, device="cuda"), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    lp = torch.empty(n, dtype=BF16, device="cuda")
+    gn = (g ** 2).sum().reshape(1)
+    clip = 1.0
+    s = clip / (gn.sqrt() + 1e-6)
+    rp, rm, rv = train.adamw_update(p, g * s, m, v, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8,
+                                    wd=0.1, step=3)
+    call("pb_adamw", ptr(p), ptr(g), ptr(m), ptr(v), ptr(lp), n, 1e-3, 0.9, 0.95, 1e-8, 0.1, 3,
+         ptr(gn), clip, 1.0, stream_ptr())
+    torch.testing.assert_close(p, rp, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(m, rm, rtol=1e-5, atol=1e-7)
+    torch.testing.assert_close(v, rv, rtol=1e-5, atol=1e-9)
+    torch.testing.assert_close(lp.float(), rp, rtol=1e-2, atol=1e-3)
+    # Muon prepare: momentum + normalised Nesterov
+    r, c = 64, 96
+    gm, mom = torch.randn(r * c, device="cuda"), torch.randn(r * c, device="cuda")
+    x0 = torch.empty(r * c, dtype=BF16, device="cuda")
+    new_m = 0.95 * mom + gm
+    nes = gm + 0.95 * new_m
+    call("pb_muon_prepare", ptr(gm), ptr(mom), ptr(x0), r * c, 0.95, None, 0.0, 1.0, ptr(scratch),
+         stream_ptr())
+    torch.testing.assert_close(mom, new_m, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(x0.float(), nes / nes.norm(), rtol=1e-2, atol=1e-3)
+
+
+def test_bounded_wait_reports_timeout_instead_of_hanging():
+    """A device-side wait on a flag nobody sets returns a status code within its budget."""
+    from prometheus_b200.ops import _lib
+    from prometheus_b200.ops._lib import call, ptr, stream_ptr
+
+    if not hasattr(_lib.load(), "pb_wait_flag_probe"):
+        pytest.skip("probe not built")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    call("pb_wait_flag_probe", ptr(flag), 1, 2_000_000, ptr(status), stream_ptr())
+    torch.cuda.synchronize()
+    assert status.item() == 2

@@ -140,3 +140,18 @@ def test_compile_cache(tmp_path):
     assert c.lookup(b"torn") is None
     blob = (tmp_path / "cc" / kernels.program_hash(b"prog")).read_bytes()
     assert blob[:4] == b"CC01" and int.from_bytes(blob[4:12], "big") == 8
+
+
+def test_affine_scan_delta_matches_recurrent():
+    from prometheus_b200.ops import delta
+
+    b, s, h, dk, dv = 2, 100, 2, 8, 6
+    q, k = _rand(b, s, h, dk, seed=1), _rand(b, s, h, dk, seed=2)
+    k = k / k.norm(dim=-1, keepdim=True)
+    v = _rand(b, s, h, dv, seed=3)
+    beta = torch.sigmoid(_rand(b, s, h, seed=4))
+    s0 = _rand(b, h, dk, dv, seed=5) * 0.1
+    o_ref, s_ref = kernels.delta_rule_recurrent(q, k, v, beta, s0)
+    o, st = delta.delta_rule_scan(q, k, v, beta, s0, chunk=16)
+    torch.testing.assert_close(o, o_ref, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(st, s_ref, rtol=1e-4, atol=1e-4)
