@@ -81,9 +81,39 @@ def delta_rule_scan(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, s0: Tensor | 
     return out, after[:, :, -1]
 
 
+class _DeltaScanFn(torch.autograd.Function):
+    """Delta rule with recomputation: only the bf16 inputs are kept for the backward, which
+    re-runs the chunk-parallel scan under autograd (no per-token or per-level state saved)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, beta, state, chunk):
+        with torch.no_grad():
+            out, st = delta_rule_scan(q.float(), k.float(), v.float(), beta.float(),
+                                      None if state is None else state.float(), chunk)
+        ctx.save_for_backward(q, k, v, beta, state)
+        ctx.chunk = chunk
+        return out.to(q.dtype), st
+
+    @staticmethod
+    def backward(ctx, go, gs):
+        q, k, v, beta, state = ctx.saved_tensors
+        leaves = [t.detach().float().requires_grad_(True) for t in (q, k, v, beta)]
+        s0 = None if state is None else state.detach().float().requires_grad_(True)
+        with torch.enable_grad():
+            out, st = delta_rule_scan(*leaves, s0, ctx.chunk)
+            outs, grads = [out], [go.float()]
+            if gs is not None:
+                outs.append(st)
+                grads.append(gs.float())
+            wrt = leaves + ([s0] if s0 is not None else [])
+            gr = torch.autograd.grad(outs, wrt, grads, allow_unused=True)
+        gq, gk, gv, gb = (g.to(t.dtype) if g is not None else None
+                          for g, t in zip(gr[:4], (q, k, v, beta)))
+        gst = gr[4] if s0 is not None else None
+        return gq, gk, gv, gb, gst, None
+
+
 def delta_rule(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tensor | None = None,
                chunk: int = 64):
     """CUDA entry: bf16 in, bf16 out, fp32 state."""
-    out, st = delta_rule_scan(q.float(), k.float(), v.float(), beta.float(),
-                              None if state is None else state.float(), chunk)
-    return out.to(q.dtype), st
+    return _DeltaScanFn.apply(q, k, v, beta, state, chunk)
