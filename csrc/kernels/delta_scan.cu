@@ -1,0 +1,433 @@
+// Chunked delta-rule state scan on tcgen05 (sm_100a), forward and backward.
+//
+// The chunk-local WY operands (W = T b K, U^ = T b V, M = tril(Q K^T)) do not depend
+// on the running state; what is sequential is, per (batch, head), the walk over
+// chunks of 64 tokens with the 128 x 128 fp32 state S:
+//
+//   forward   Y = W S            U = U^ - Y          O = Q S + M U      S += K^T U
+//   backward  dU = M^T dO + K dS                     dS += Q^T dO - W^T dU
+//
+// One CTA owns one (batch, head) sequence. The state lives in tensor memory for the
+// whole walk (fp32, 128 lanes x 128 columns); every product is a tcgen05.mma with
+// M = 128, N = 128; the bf16 image of the state and of U that the MMAs consume as
+// their B operand is rewritten in shared memory each chunk in the 128-byte-swizzled
+// layout TMA itself produces; Q/K/W/M/dO tiles arrive by TMA through a two-stage
+// ring. Tiles with 64 token rows are used as 128-row A operands: the upper 64
+// accumulator rows are then meaningless and are never read.
+//
+// warps 0-3: tensor-memory <-> registers <-> shared/global (lane = state row or token)
+// warp 4   : MMA issue (one lane)          warp 5: TMA producer (one lane)
+//
+// Reference semantics: kernels/__init__.py:357-376 (per-token recurrence, post-update
+// read) of the reference; the chunked algebra is this library's own.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace pb {
+
+int make_tmap_3d(CUtensorMap* tm, const void* base, int elem_bytes, uint64_t inner,
+                 uint64_t outer, uint64_t batch, uint64_t ld_elems, uint64_t batch_stride_elems,
+                 uint32_t box_inner, uint32_t box_outer);
+
+namespace dscan {
+
+constexpr int C = 64;    // tokens per chunk
+constexpr int D = 128;   // head dim (keys and values)
+constexpr int TILE_W = 0, TILE_Q = 16384, TILE_K = 32768, TILE_M = 49152, TILE_DO = 57344;
+constexpr int STAGE_FWD = 57344;           // W, Q, K (16 KB each) + M (8 KB)
+constexpr int STAGE_BWD = 57344 + 16384;   // + dO
+constexpr int XB_BYTES = 32768, UB_BYTES = 16384;
+constexpr int TMEM_COLS = 512;
+constexpr uint32_t COL_X = 0, COL_Y = 128, COL_O = 256;
+
+struct Params {
+  int n_chunks;        // chunks per sequence
+  int n_seq;           // batch * heads
+  const bf16* uhat;    // [G*64, 128]            (forward)
+  bf16* out;           // [G*64, 128]  O         (forward)
+  bf16* u_out;         // [G*64, 128]  U or dU
+  bf16* xb_out;        // [G, 128, 128] bf16 image of the state entering each chunk
+  const float* x_init; // [n_seq, 128, 128] or null (zeros)
+  float* x_final;      // [n_seq, 128, 128] or null
+  int* status;
+};
+
+template <bool BWD>
+struct Smem {
+  static constexpr int STAGE = BWD ? STAGE_BWD : STAGE_FWD;
+  static constexpr int XB = 2 * STAGE;
+  static constexpr int UB = XB + XB_BYTES;
+  static constexpr int BARS = UB + UB_BYTES;
+  static constexpr int TOTAL = BARS + 256 + 1024;
+};
+
+// 16-byte store of 8 bf16 into a [rows][64 n] 128B-swizzled MN-major operand chunk.
+__device__ __forceinline__ void st_swz(uint8_t* chunk_base, int krow, int c16, const bf16x8& v) {
+  *reinterpret_cast<bf16x8*>(chunk_base + krow * 128 + ((c16 ^ (krow & 7)) << 4)) = v;
+}
+
+template <bool BWD>
+__global__ void __launch_bounds__(192, 1)
+delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmQ,
+                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmM,
+                  const __grid_constant__ CUtensorMap tmDO, const Params p) {
+  using S = Smem<BWD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* xb = smem + S::XB;
+  uint8_t* ub = smem + S::UB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BARS);
+  uint64_t* full = bars;          // [2]
+  uint64_t* empty = bars + 2;     // [2]
+  uint64_t* x_ready = bars + 4;
+  uint64_t* y_done = bars + 5;
+  uint64_t* u_ready = bars + 6;
+  uint64_t* o_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = blockIdx.x;
+  const int N = p.n_chunks;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&full[0], 1); mbar_init(&full[1], 1);
+    mbar_init(&empty[0], 1); mbar_init(&empty[1], 1);
+    mbar_init(x_ready, 128); mbar_init(u_ready, 128);
+    mbar_init(y_done, 1); mbar_init(o_done, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmM);
+    if (BWD) tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 5) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      for (int it = 0; it < N; ++it) {
+        const int n = BWD ? (N - 1 - it) : it;
+        const int s = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, p.status)) break;
+        mbar_arrive_expect_tx(&full[s], S::STAGE);
+        uint8_t* st = smem + s * S::STAGE;
+        const int row = (seq * N + n) * C;
+        tma_load_3d(st + TILE_W, &tmW, &full[s], 0, row, 0);
+        tma_load_3d(st + TILE_W + 8192, &tmW, &full[s], 64, row, 0);
+        tma_load_3d(st + TILE_Q, &tmQ, &full[s], 0, row, 0);
+        tma_load_3d(st + TILE_Q + 8192, &tmQ, &full[s], 64, row, 0);
+        tma_load_3d(st + TILE_K, &tmK, &full[s], 0, row, 0);
+        tma_load_3d(st + TILE_K + 8192, &tmK, &full[s], 64, row, 0);
+        tma_load_3d(st + TILE_M, &tmM, &full[s], 0, row, 0);
+        if (BWD) {
+          tma_load_3d(st + TILE_DO, &tmDO, &full[s], 0, row, 0);
+          tma_load_3d(st + TILE_DO + 8192, &tmDO, &full[s], 64, row, 0);
+        }
+      }
+    }
+  } else if (warp == 4) {
+    // -------------------------------- MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t id_kn = make_idesc(1, 1, 128, 128, 0, 1);  // A K-major, B MN-major
+      const uint32_t id_nn = make_idesc(1, 1, 128, 128, 1, 1);  // A MN-major, B MN-major
+      const uint32_t xb_a = smem_u32(xb), ub_a = smem_u32(ub);
+      for (int it = 0; it < N; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (it >> 1) & 1, cph = it & 1;
+        const uint32_t st = smem_u32(smem + s * S::STAGE);
+        if (!mbar_wait(&full[s], ph, p.status)) break;
+        if (!mbar_wait(x_ready, cph, p.status)) break;
+        tc_fence_after();
+        if (!BWD) {
+          // Y = W X ; O = Q X
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            umma_f16(tmem + COL_Y,
+                     make_sdesc_sw128(st + TILE_W + (j >> 2) * 8192 + (j & 3) * 32, 16, 1024),
+                     make_sdesc_sw128(xb_a + j * 2048, 16384, 1024), id_kn, j > 0);
+          umma_commit(y_done);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            umma_f16(tmem + COL_O,
+                     make_sdesc_sw128(st + TILE_Q + (j >> 2) * 8192 + (j & 3) * 32, 16, 1024),
+                     make_sdesc_sw128(xb_a + j * 2048, 16384, 1024), id_kn, j > 0);
+        } else {
+          // Y = M^T dO + K X
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            umma_f16(tmem + COL_Y, make_sdesc_sw128(st + TILE_M + j * 2048, 8192, 1024),
+                     make_sdesc_sw128(st + TILE_DO + j * 2048, 8192, 1024), id_nn, j > 0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            umma_f16(tmem + COL_Y,
+                     make_sdesc_sw128(st + TILE_K + (j >> 2) * 8192 + (j & 3) * 32, 16, 1024),
+                     make_sdesc_sw128(xb_a + j * 2048, 16384, 1024), id_kn, 1);
+          umma_commit(y_done);
+          // X += Q^T dO   (independent of dU: keeps the tensor core busy meanwhile)
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            umma_f16(tmem + COL_X, make_sdesc_sw128(st + TILE_Q + j * 2048, 8192, 1024),
+                     make_sdesc_sw128(st + TILE_DO + j * 2048, 8192, 1024), id_nn, 1);
+        }
+        if (!mbar_wait(u_ready, cph, p.status)) break;
+        tc_fence_after();
+        if (!BWD) {
+          // O += M U ; X += K^T U
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            umma_f16(tmem + COL_O, make_sdesc_sw128(st + TILE_M + j * 32, 16, 1024),
+                     make_sdesc_sw128(ub_a + j * 2048, 8192, 1024), id_kn, 1);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            umma_f16(tmem + COL_X, make_sdesc_sw128(st + TILE_K + j * 2048, 8192, 1024),
+                     make_sdesc_sw128(ub_a + j * 2048, 8192, 1024), id_nn, 1);
+        } else {
+          // X += W^T (-dU)
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            umma_f16(tmem + COL_X, make_sdesc_sw128(st + TILE_W + j * 2048, 8192, 1024),
+                     make_sdesc_sw128(ub_a + j * 2048, 8192, 1024), id_nn, 1);
+        }
+        umma_commit(o_done);
+        umma_commit(&empty[s]);
+      }
+    }
+  } else {
+    // ------------------------- state / token row threads -------------------------
+    const int r = threadIdx.x;  // 0..127: tensor-memory lane = state row (or token row < 64)
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    // initial state into tensor memory
+    {
+      const float* x0 = p.x_init ? p.x_init + (static_cast<size_t>(seq) * D + r) * D : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = x0 ? __float_as_uint(x0[c + i]) : 0u;
+        tmem_st_32x32b_x32(lane_addr + COL_X + c, v);
+      }
+      tmem_st_wait();
+    }
+    bool ok = true;
+    for (int it = 0; it < N && ok; ++it) {
+      const int n = BWD ? (N - 1 - it) : it;
+      const uint32_t cph = it & 1;
+      const size_t g = static_cast<size_t>(seq) * N + n;
+      if (it > 0) {
+        if (!mbar_wait(o_done, cph ^ 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+        if (!BWD && r < C) {
+          // output rows of the previous chunk
+          const int np = n - 1;
+          bf16* op = p.out + ((static_cast<size_t>(seq) * N + np) * C + r) * D;
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(lane_addr + COL_O + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              bf16x8 pk;
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                pk.v[j] = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]),
+                                                __uint_as_float(v[8 * i + 2 * j + 1]));
+              reinterpret_cast<bf16x8*>(op + c)[i] = pk;
+            }
+          }
+        } else if (!BWD) {
+          // keep the warp-wide tcgen05.ld aligned for warps 2-3 (nothing to read)
+        }
+      }
+      // bf16 image of the state: shared memory (MMA operand) and global (for the other pass)
+      {
+        bf16* xg = p.xb_out + (g * D + r) * D;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(lane_addr + COL_X + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            bf16x8 pk;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              pk.v[j] = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]),
+                                              __uint_as_float(v[8 * i + 2 * j + 1]));
+            const int col = c + 8 * i;
+            st_swz(xb + (col >> 6) * 16384, r, (col & 63) >> 3, pk);
+            reinterpret_cast<bf16x8*>(xg + c)[i] = pk;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(x_ready);
+      if (!mbar_wait(y_done, cph, p.status)) { ok = false; break; }
+      tc_fence_after();
+      if (r < C) {
+        const size_t row = (g * C + r) * D;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(lane_addr + COL_Y + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float y[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = __uint_as_float(v[8 * i + j]);
+            const int col = c + 8 * i;
+            if (!BWD) {
+              float uh[8];
+              unpack8(*reinterpret_cast<const bf16x8*>(p.uhat + row + col), uh);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) y[j] = uh[j] - y[j];  // U = U^ - W S
+            }
+            bf16x8 pk;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) pk.v[j] = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+            *reinterpret_cast<bf16x8*>(p.u_out + row + col) = pk;
+            if (BWD) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                pk.v[j] = __floats2bfloat162_rn(-y[2 * j], -y[2 * j + 1]);  // operand is -dU
+            }
+            st_swz(ub + (col >> 6) * 8192, r, (col & 63) >> 3, pk);
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(u_ready);
+    }
+    // drain: last chunk's output rows and the final state
+    if (ok && N > 0) {
+      if (mbar_wait(o_done, (N - 1) & 1, p.status)) {
+        tc_fence_after();
+        if (!BWD && r < C) {
+          bf16* op = p.out + ((static_cast<size_t>(seq) * N + (N - 1)) * C + r) * D;
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(lane_addr + COL_O + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              bf16x8 pk;
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                pk.v[j] = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]),
+                                                __uint_as_float(v[8 * i + 2 * j + 1]));
+              reinterpret_cast<bf16x8*>(op + c)[i] = pk;
+            }
+          }
+        }
+        if (p.x_final != nullptr) {
+          float* xf = p.x_final + (static_cast<size_t>(seq) * D + r) * D;
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(lane_addr + COL_X + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              reinterpret_cast<float4*>(xf + c)[i] =
+                  make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                              __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != PB_OK) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies in flight land
+    __syncthreads();
+  }
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+template <bool BWD>
+int launch(const void* W, const void* Q, const void* K, const void* M, const void* dO,
+           const Params& p, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<BWD>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Smem<BWD>::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const uint64_t rows = static_cast<uint64_t>(p.n_seq) * p.n_chunks * C;
+  CUtensorMap tW, tQ, tK, tM, tD;
+  int r = 0;
+  r |= make_tmap_3d(&tW, W, 2, D, rows, 1, D, 0, 64, C);
+  r |= make_tmap_3d(&tQ, Q, 2, D, rows, 1, D, 0, 64, C);
+  r |= make_tmap_3d(&tK, K, 2, D, rows, 1, D, 0, 64, C);
+  r |= make_tmap_3d(&tM, M, 2, C, rows, 1, C, 0, 64, C);
+  r |= make_tmap_3d(&tD, BWD ? dO : Q, 2, D, rows, 1, D, 0, 64, C);
+  if (r != 0) return 1000 + r;
+  delta_scan_kernel<BWD><<<p.n_seq, 192, Smem<BWD>::TOTAL, st>>>(tW, tQ, tK, tM, tD, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace dscan
+}  // namespace pb
+
+using namespace pb;
+
+// Forward walk. All per-chunk tensors are row-major [(n_seq * n_chunks * 64), 128]
+// bf16 (M: [.., 64]), chunk g = seq * n_chunks + n occupying rows [64 g, 64 g + 64).
+//   out   <- O            u_out <- U            xb_out[g] <- bf16(S entering chunk g)
+//   x_init / x_final: fp32 [n_seq, 128, 128] (x_init may be null = zero state)
+PB_API int pb_delta_scan_fwd(const void* W, const void* Uhat, const void* Q, const void* K,
+                             const void* M, void* out, void* u_out, void* xb_out,
+                             const void* x_init, void* x_final, int n_seq, int n_chunks,
+                             int* status, cudaStream_t st) {
+  if (n_seq <= 0 || n_chunks <= 0) return PB_BAD_ARG;
+  dscan::Params p;
+  p.n_chunks = n_chunks; p.n_seq = n_seq;
+  p.uhat = static_cast<const bf16*>(Uhat);
+  p.out = static_cast<bf16*>(out);
+  p.u_out = static_cast<bf16*>(u_out);
+  p.xb_out = static_cast<bf16*>(xb_out);
+  p.x_init = static_cast<const float*>(x_init);
+  p.x_final = static_cast<float*>(x_final);
+  p.status = status;
+  return dscan::launch<false>(W, Q, K, M, nullptr, p, st);
+}
+
+// Backward walk (chunks in reverse). x_init = gradient of the final state (or null),
+//   u_out <- dU      xb_out[g] <- bf16(dS leaving chunk g, i.e. before chunk g is applied)
+//   x_final <- gradient of the initial state
+PB_API int pb_delta_scan_bwd(const void* W, const void* Q, const void* K, const void* M,
+                             const void* dO, void* du_out, void* dxb_out, const void* x_init,
+                             void* x_final, int n_seq, int n_chunks, int* status,
+                             cudaStream_t st) {
+  if (n_seq <= 0 || n_chunks <= 0) return PB_BAD_ARG;
+  dscan::Params p;
+  p.n_chunks = n_chunks; p.n_seq = n_seq;
+  p.uhat = nullptr;
+  p.out = nullptr;
+  p.u_out = static_cast<bf16*>(du_out);
+  p.xb_out = static_cast<bf16*>(dxb_out);
+  p.x_init = static_cast<const float*>(x_init);
+  p.x_final = static_cast<float*>(x_final);
+  p.status = status;
+  return dscan::launch<true>(W, Q, K, M, dO, p, st);
+}

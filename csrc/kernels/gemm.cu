@@ -202,6 +202,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
           const bool full_chunk = (col0 + 32 <= p.N);
+          // All indexing below is compile-time so v stays in registers; ragged
+          // edges use the same unrolled loops with a per-element predicate.
           if (p.D != nullptr) {
             if (p.d_f32) {
               const float* dp = static_cast<const float*>(p.D) + d_off + col0;
@@ -213,7 +215,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                   v[4 * i + 2] += p.beta * d4.z; v[4 * i + 3] += p.beta * d4.w;
                 }
               } else {
-                for (int i = 0; i < 32 && col0 + i < p.N; ++i) v[i] += p.beta * dp[i];
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) v[i] += p.beta * dp[i];
               }
             } else {
               const bf16* dp = static_cast<const bf16*>(p.D) + d_off + col0;
@@ -226,8 +230,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                   for (int j = 0; j < 8; ++j) v[8 * i + j] += p.beta * f[j];
                 }
               } else {
-                for (int i = 0; i < 32 && col0 + i < p.N; ++i)
-                  v[i] += p.beta * bf16_to_f32(dp[i]);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) v[i] += p.beta * bf16_to_f32(dp[i]);
               }
             }
           }
@@ -239,15 +244,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 reinterpret_cast<float4*>(cp)[i] =
                     make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
             } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) cp[i] = v[i];
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) cp[i] = v[i];
             }
           } else {
             bf16* cp = static_cast<bf16*>(p.C) + c_off + col0;
             if (full_chunk && (p.ldc % 8 == 0)) {
 #pragma unroll
-              for (int i = 0; i < 4; ++i) reinterpret_cast<bf16x8*>(cp)[i] = pack8(v + 8 * i);
+              for (int i = 0; i < 4; ++i) {
+                bf16x8 pk;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  pk.v[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+                reinterpret_cast<bf16x8*>(cp)[i] = pk;
+              }
             } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) cp[i] = f32_to_bf16(v[i]);
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) cp[i] = f32_to_bf16(v[i]);
             }
           }
         }

@@ -113,7 +113,126 @@ class _DeltaScanFn(torch.autograd.Function):
         return gq, gk, gv, gb, gst, None
 
 
+class _BmmNT(torch.autograd.Function):
+    """Batched ``a @ b^T`` on the tcgen05 GEMM (bf16 in/out), with its two gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, a, b, fp32_out=False):
+        from .functional import gemm
+
+        ctx.save_for_backward(a, b)
+        return gemm(a, b, out_dtype=torch.float32 if fp32_out else torch.bfloat16)
+
+    @staticmethod
+    def backward(ctx, g):
+        from .functional import gemm
+
+        a, b = ctx.saved_tensors
+        g = g.to(torch.bfloat16).contiguous()
+        return gemm(g, b, b_mn=True), gemm(g, a, a_mn=True, b_mn=True), None
+
+
+class _BmmNN(torch.autograd.Function):
+    """Batched ``a @ b`` on the tcgen05 GEMM (b consumed MN-major, no transpose copy)."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        from .functional import gemm
+
+        ctx.save_for_backward(a, b)
+        return gemm(a, b, b_mn=True)
+
+    @staticmethod
+    def backward(ctx, g):
+        from .functional import gemm
+
+        a, b = ctx.saved_tensors
+        g = g.contiguous()
+        return gemm(g, b), gemm(a, g, a_mn=True, b_mn=True)
+
+
+class _ScanFn(torch.autograd.Function):
+    """The sequential part on the tcgen05 scan kernels. Inputs are the per-chunk operands
+    ``[G, 64, 128]`` (M: ``[G, 64, 64]``), G = batch * heads * chunks."""
+
+    @staticmethod
+    def forward(ctx, w, uhat, qc, kc, m, s0, n_seq, n_chunks):
+        from ._lib import call, ptr, stream_ptr
+        from .functional import status_word
+
+        dev = w.device
+        g = n_seq * n_chunks
+        out = torch.empty((g, 64, 128), dtype=torch.bfloat16, device=dev)
+        u = torch.empty_like(out)
+        sb = torch.empty((g, 128, 128), dtype=torch.bfloat16, device=dev)
+        sfin = torch.empty((n_seq, 128, 128), dtype=torch.float32, device=dev)
+        s0c = None if s0 is None else s0.float().contiguous()
+        call("pb_delta_scan_fwd", ptr(w), ptr(uhat), ptr(qc), ptr(kc), ptr(m), ptr(out), ptr(u),
+             ptr(sb), ptr(s0c), ptr(sfin), n_seq, n_chunks, ptr(status_word(dev)), stream_ptr())
+        ctx.save_for_backward(w, qc, kc, m, u, sb)
+        ctx.dims = (n_seq, n_chunks)
+        ctx.has_s0 = s0 is not None
+        return out, sfin
+
+    @staticmethod
+    def backward(ctx, d_out, d_sfin):
+        from ._lib import call, ptr, stream_ptr
+        from .functional import gemm, status_word
+
+        w, qc, kc, m, u, sb = ctx.saved_tensors
+        n_seq, n_chunks = ctx.dims
+        dev = w.device
+        d_out = d_out.contiguous()
+        du = torch.empty_like(u)
+        dsb = torch.empty_like(sb)
+        ds0 = torch.empty((n_seq, 128, 128), dtype=torch.float32, device=dev)
+        dfin = None if d_sfin is None else d_sfin.float().contiguous()
+        call("pb_delta_scan_bwd", ptr(w), ptr(qc), ptr(kc), ptr(m), ptr(d_out), ptr(du), ptr(dsb),
+             ptr(dfin), ptr(ds0), n_seq, n_chunks, ptr(status_word(dev)), stream_ptr())
+        d_w = gemm(du, sb, alpha=-1.0)            # dW = -dU S^T
+        d_m = torch.tril(gemm(d_out, u))          # dM = tril(dO U^T)
+        d_q = gemm(d_out, sb)                     # dQ = dO S^T
+        d_k = gemm(u, dsb)                        # dK = U dS'^T
+        return d_w, du, d_q, d_k, d_m, (ds0 if ctx.has_s0 else None), None, None
+
+
+def delta_rule_fused(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tensor | None):
+    """Chunk-local WY operands with batched tcgen05 GEMMs (+ one batched triangular solve),
+    then the state walk on the scan kernels. bf16, head dim 128, chunk 64."""
+    b, s, h, d = q.shape
+    c = 64
+    pad = (-s) % c
+    if pad:
+        q = torch.nn.functional.pad(q, (0, 0, 0, 0, 0, pad))
+        k = torch.nn.functional.pad(k, (0, 0, 0, 0, 0, pad))
+        v = torch.nn.functional.pad(v, (0, 0, 0, 0, 0, pad))
+        beta = torch.nn.functional.pad(beta, (0, 0, 0, pad))
+    n = (s + pad) // c
+    g = b * h * n
+
+    def chunks(x):
+        return x.reshape(b, n, c, h, d).permute(0, 3, 1, 2, 4).reshape(g, c, d).contiguous()
+
+    qc, kc, vc = chunks(q), chunks(k), chunks(v)
+    bc = beta.float().reshape(b, n, c, h).permute(0, 3, 1, 2).reshape(g, c)
+    kk = _BmmNT.apply(kc, kc, True)
+    a = torch.tril(kk, diagonal=-1) * bc[:, :, None]
+    eye = torch.eye(c, dtype=torch.float32, device=q.device)
+    t = torch.linalg.solve_triangular(eye + a, eye.expand(g, c, c).contiguous(), upper=False)
+    ap = (t * bc[:, None, :]).to(q.dtype)                 # A' = T diag(beta)
+    w = _BmmNN.apply(ap, kc)
+    uhat = _BmmNN.apply(ap, vc)
+    m = torch.tril(_BmmNT.apply(qc, kc))
+    s0 = None if state is None else state.reshape(b * h, d, d)
+    out, sfin = _ScanFn.apply(w, uhat, qc, kc, m, s0, b * h, n)
+    out = out.reshape(b, h, n, c, d).permute(0, 2, 3, 1, 4).reshape(b, n * c, h, d)[:, :s]
+    return out, sfin.reshape(b, h, d, d)
+
+
 def delta_rule(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tensor | None = None,
                chunk: int = 64):
-    """CUDA entry: bf16 in, bf16 out, fp32 state."""
+    """CUDA entry: bf16 in, bf16 out, fp32 state. Head dim 128 with chunk 64 runs the fused
+    tcgen05 path; other geometries use the chunk-parallel scan with recomputation."""
+    if q.shape[-1] == 128 and v.shape[-1] == 128 and chunk == 64:
+        return delta_rule_fused(q, k, v, beta, state)
     return _DeltaScanFn.apply(q, k, v, beta, state, chunk)

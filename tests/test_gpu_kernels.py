@@ -209,3 +209,33 @@ def test_bounded_wait_reports_timeout_instead_of_hanging():
     call("pb_wait_flag_probe", ptr(flag), 1, 2_000_000, ptr(status), stream_ptr())
     torch.cuda.synchronize()
     assert status.item() == 2
+
+
+@pytest.mark.parametrize("B,S,H", [(1, 64, 1), (1, 128, 2), (2, 448, 3), (1, 200, 2)])
+def test_delta_rule_fused_matches_recurrence(B, S, H):
+    from prometheus_b200 import kernels
+    from prometheus_b200.ops import functional as ops
+
+    D = 128
+    q = torch.nn.functional.normalize(_r(B, S, H, D, seed=1).float(), dim=-1).to(BF16)
+    k = torch.nn.functional.normalize(_r(B, S, H, D, seed=2).float(), dim=-1).to(BF16)
+    v = _r(B, S, H, D, seed=3)
+    beta = torch.sigmoid(_r(B, S, H, seed=4).float()).to(BF16)
+    s0 = _r(B, H, D, D, seed=5, scale=0.05, dtype=torch.float32)
+    go = _r(B, S, H, D, seed=6)
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, beta)]
+    s0l = s0.clone().requires_grad_(True)
+    out, st = kernels.chunked_delta_rule(*leaves, s0l)
+    torch.cuda.synchronize()
+    ops.check_status("cuda")
+    (out.float() * go.float()).sum().add(st.sum() * 0.01).backward()
+    ref_leaves = [t.float().clone().requires_grad_(True) for t in (q, k, v, beta)]
+    s0r = s0.clone().requires_grad_(True)
+    o_ref, s_ref = kernels.delta_rule_recurrent(*ref_leaves, s0r)
+    (o_ref * go.float()).sum().add(s_ref.sum() * 0.01).backward()
+    _close(out, o_ref, 3e-2)
+    _close(st, s_ref, 3e-2)
+    for name, a, b in zip("qkvb", leaves, ref_leaves):
+        _close(a.grad, b.grad, 6e-2)
+    _close(s0l.grad, s0r.grad, 6e-2)
+    ops.check_status("cuda")
