@@ -1,0 +1,149 @@
+"""Per-kernel micro-benchmarks (CUDA-event timed, L2 flushed between iterations).
+
+    python -m prometheus_b200.ops.microbench gemm --m 16384 --n 2048 --k 2048
+    python -m prometheus_b200.ops.microbench delta --seqs 32 --seq-len 4096
+    python -m prometheus_b200.ops.microbench rmsnorm --rows 131072 --d 2048
+    python -m prometheus_b200.ops.microbench ce --rows 4096 --vocab 131072
+
+Each prints one JSON line with the achieved rate and its fraction of the measured peak
+(``MEASURED_PEAKS.json`` at the repository root when present, else the stated fallback).
+Used for the roofline lines in ``profiles/`` and as the small case for ``ncu`` captures.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+BF16 = torch.bfloat16
+
+
+def peaks() -> dict:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+
+
+def timeit(fn, iters=10, warmup=3, flush=True) -> float:
+    """Median milliseconds per call; a 256 MB write between calls evicts the 126 MB L2."""
+    junk = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if junk is not None:
+            junk.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def bench_gemm(a):
+    from . import functional as ops
+
+    x = torch.randn((a.k, a.m) if a.a_mn else (a.m, a.k), device="cuda").to(BF16)
+    w = torch.randn((a.k, a.n) if a.b_mn else (a.n, a.k), device="cuda").to(BF16)
+    ms = timeit(lambda: ops.gemm(x, w, a_mn=a.a_mn, b_mn=a.b_mn), a.iters)
+    tf = 2.0 * a.m * a.n * a.k / ms / 1e9
+    out = {"kernel": "gemm_bf16", "m": a.m, "n": a.n, "k": a.k, "a_mn": a.a_mn, "b_mn": a.b_mn,
+           "ms": ms, "tflops": tf, "frac_of_peak": tf / peaks()["bf16_tflops"]}
+    if a.compare:
+        xr = x.t() if a.a_mn else x
+        wr = w if a.b_mn else w.t()
+        ms_l = timeit(lambda: xr @ wr, a.iters)
+        out["library_ms"] = ms_l
+        out["library_tflops"] = 2.0 * a.m * a.n * a.k / ms_l / 1e9
+    return out
+
+
+def bench_delta(a):
+    from .. import kernels
+
+    B, S, H, D = a.seqs, a.seq_len, 16, 128
+    q = torch.nn.functional.normalize(torch.randn(B, S, H, D, device="cuda"), dim=-1).to(BF16)
+    k = torch.nn.functional.normalize(torch.randn(B, S, H, D, device="cuda"), dim=-1).to(BF16)
+    v = torch.randn(B, S, H, D, device="cuda").to(BF16)
+    beta = torch.rand(B, S, H, device="cuda").to(BF16)
+    leaves = [t.requires_grad_(True) for t in (q, k, v, beta)]
+    go = torch.randn(B, S, H, D, device="cuda").to(BF16)
+
+    def fwd():
+        with torch.no_grad():
+            kernels.chunked_delta_rule(q, k, v, beta)
+
+    def fwdbwd():
+        o, _ = kernels.chunked_delta_rule(*leaves)
+        o.backward(go)
+
+    ms_f, ms_fb = timeit(fwd, a.iters), timeit(fwdbwd, a.iters)
+    chunks = B * H * S // 64
+    flops_scan = chunks * 2.0 * (3 * 64 * 128 * 128 + 64 * 64 * 128)
+    return {"kernel": "delta_rule", "seqs": B, "seq_len": S, "heads": H, "fwd_ms": ms_f,
+            "fwd_bwd_ms": ms_fb, "scan_fwd_tflops_if_all_scan": flops_scan / ms_f / 1e9}
+
+
+def bench_rmsnorm(a):
+    from . import functional as ops
+
+    x = torch.randn(a.rows, a.d, device="cuda").to(BF16)
+    r = torch.randn(a.rows, a.d, device="cuda").to(BF16)
+    w = torch.ones(a.d, device="cuda")
+    ms = timeit(lambda: ops.add_rmsnorm(x, r, w), a.iters)
+    gbs = 4 * a.rows * a.d * 2 / ms / 1e6
+    return {"kernel": "add_rmsnorm_fwd", "rows": a.rows, "d": a.d, "ms": ms, "gbs": gbs,
+            "frac_of_peak": gbs / peaks()["hbm_gbs"]}
+
+
+def bench_ce(a):
+    from ._lib import call, ptr, stream_ptr
+
+    logits = torch.randn(a.rows, a.vocab, device="cuda").to(BF16)
+    tgt = torch.randint(0, a.vocab, (a.rows,), device="cuda", dtype=torch.int32)
+    wt = torch.full((a.rows,), 1.0 / a.rows, device="cuda")
+    loss = torch.empty(a.rows, device="cuda")
+    ms = timeit(lambda: call("pb_softcap_ce", ptr(logits), ptr(tgt), ptr(wt), ptr(loss), None,
+                             a.rows, a.vocab, 30.0, 1, stream_ptr()), a.iters)
+    gbs = 2 * a.rows * a.vocab * 2 / ms / 1e6
+    return {"kernel": "softcap_ce", "rows": a.rows, "vocab": a.vocab, "ms": ms, "gbs": gbs,
+            "frac_of_peak": gbs / peaks()["hbm_gbs"]}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="which", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8192)
+    g.add_argument("--n", type=int, default=8192)
+    g.add_argument("--k", type=int, default=8192)
+    g.add_argument("--a-mn", action="store_true")
+    g.add_argument("--b-mn", action="store_true")
+    g.add_argument("--compare", action="store_true")
+    d = sub.add_parser("delta")
+    d.add_argument("--seqs", type=int, default=4)
+    d.add_argument("--seq-len", type=int, default=4096)
+    r = sub.add_parser("rmsnorm")
+    r.add_argument("--rows", type=int, default=131072)
+    r.add_argument("--d", type=int, default=2048)
+    c = sub.add_parser("ce")
+    c.add_argument("--rows", type=int, default=4096)
+    c.add_argument("--vocab", type=int, default=131072)
+    for s in (g, d, r, c):
+        s.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    out = {"gemm": bench_gemm, "delta": bench_delta, "rmsnorm": bench_rmsnorm, "ce": bench_ce}[a.which](a)
+    out["peaks"] = peaks()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
