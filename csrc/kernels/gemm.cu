@@ -34,6 +34,7 @@ struct GemmParams {
   float alpha, beta;
   int out_f32, d_f32;
   int a_mn, b_mn;
+  int debug;  // bit 1: skip the epilogue's global stores (timing experiments only)
   int* status;
 };
 
@@ -197,7 +198,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32b_x32(t_addr + c, r);
         tmem_ld_wait();
         const int col0 = n0 + c;
-        if (row_ok && col0 < p.N) {
+        if (row_ok && col0 < p.N && !(p.debug & 2)) {
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
@@ -364,6 +365,13 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
 
 using namespace pb;
 
+static int g_gemm_debug = 0;
+// Timing experiments: bit 0 forces the 128-wide tile, bit 1 drops the epilogue stores.
+PB_API int pb_gemm_set_debug(int flags) {
+  g_gemm_debug = flags;
+  return 0;
+}
+
 // C = alpha * A * B^T + beta * D.  See the header comment for the layouts.
 //   a_mn == 0: A stored [M, K] with row stride lda;  a_mn == 1: stored [K, M], row stride lda
 //   b_mn == 0: B stored [N, K] with row stride ldb;  b_mn == 1: stored [K, N], row stride ldb
@@ -380,7 +388,7 @@ PB_API int pb_gemm_bf16(const void* A, const void* B, void* C, const void* D, in
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return PB_BAD_ARG;
   if (batch > 1 && ((strideA % 8) != 0 || (strideB % 8) != 0)) return PB_BAD_ARG;
-  const bool bn256 = N > 128;
+  const bool bn256 = N > 128 && !(g_gemm_debug & 1);
   const int BN = bn256 ? 256 : 128;
   CUtensorMap tmA, tmB;
   int r;
@@ -402,6 +410,7 @@ PB_API int pb_gemm_bf16(const void* A, const void* B, void* C, const void* D, in
   p.out_f32 = out_f32; p.d_f32 = d_f32;
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.status = status;
+  p.debug = g_gemm_debug;
   return bn256 ? launch_gemm<256>(tmA, tmB, p, max_ctas, st)
                : launch_gemm<128>(tmA, tmB, p, max_ctas, st);
 }

@@ -42,6 +42,7 @@ _SIGS = {
     "pb_set_flag": [P, I, P],
     "pb_delta_scan_fwd": [P, P, P, P, P, P, P, P, P, P, I, I, P, P],
     "pb_delta_scan_bwd": [P, P, P, P, P, P, P, P, P, I, I, P, P],
+    "pb_gemm_set_debug": [I],
     "pb_gemm_bf16": [P, P, P, P, I, I, I, I, L, L, L, L, L, L, L, L, I, I, I, I, F, F, P, I, P],
 }
 

@@ -51,6 +51,10 @@ def timeit(fn, iters=10, warmup=3, flush=True) -> float:
 def bench_gemm(a):
     from . import functional as ops
 
+    if a.debug:
+        from ._lib import call
+
+        call("pb_gemm_set_debug", a.debug)
     x = torch.randn((a.k, a.m) if a.a_mn else (a.m, a.k), device="cuda").to(BF16)
     w = torch.randn((a.k, a.n) if a.b_mn else (a.n, a.k), device="cuda").to(BF16)
     ms = timeit(lambda: ops.gemm(x, w, a_mn=a.a_mn, b_mn=a.b_mn), a.iters)
@@ -128,6 +132,7 @@ def main():
     g.add_argument("--a-mn", action="store_true")
     g.add_argument("--b-mn", action="store_true")
     g.add_argument("--compare", action="store_true")
+    g.add_argument("--debug", type=int, default=0, help="timing experiments, see pb_gemm_set_debug")
     d = sub.add_parser("delta")
     d.add_argument("--seqs", type=int, default=4)
     d.add_argument("--seq-len", type=int, default=4096)
