@@ -545,3 +545,58 @@ PB_API int pb_sigmoid(const void* x, void* y, long n, cudaStream_t st) {
                                                        static_cast<bf16*>(y), n);
   return cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc on the path where they need
+// the kernel: code running inside a memory pool that owns the whole device, a
+// runtime that pre-plans every byte before it starts (inference servers, real-time
+// loops), or a plug-in that is only handed its input and output buffers. The
+// regular entry point pb_rmsnorm_bwd needs a caller-provided scratch buffer for the
+// per-CTA partial sums of dw; this variant keeps that scratch in a fixed
+// file-scope device array instead, so the caller passes inputs and outputs only.
+//
+// Limits and rules (also stated in pb200_noalloc.h):
+//  * d <= PB_NOALLOC_MAX_D (2048) and d % 8 == 0; larger widths are rejected with
+//    PB_BAD_ARG and nothing is launched.
+//  * The array (PB_NOALLOC_MAX_PARTS x PB_NOALLOC_MAX_D floats, about 4.6 MiB) is
+//    part of the library image: every GPU that loads the library holds it until
+//    the process exits.
+//  * The first call on each device looks up the array's device address
+//    (cudaGetSymbolAddress, with that device current). Make that first call before
+//    any stream capture begins on the device.
+//  * All calls on a device share the one array. The kernel overwrites every partial
+//    row it later folds, so nothing needs clearing between calls, but two calls
+//    that overlap on the GPU (different streams) race on it: serialise them.
+// ---------------------------------------------------------------------------
+#define PB_NOALLOC_MAX_D 2048
+#define PB_NOALLOC_MAX_PARTS (148 * 4)
+#define PB_NOALLOC_MAX_DEVICES 64
+
+static __device__ __align__(256) float g_noalloc_rms_partials[PB_NOALLOC_MAX_PARTS * PB_NOALLOC_MAX_D];
+
+// Host-side cache of the array's device address, one slot per device ordinal.
+// (In host code the symbol name is only a handle; the address must be queried.)
+static float* g_noalloc_addr[PB_NOALLOC_MAX_DEVICES] = {nullptr};
+
+PB_API int pb_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void* w, const void* rstd,
+                                  const void* dres, void* dx, void* dw, int accumulate, int rows,
+                                  int d, cudaStream_t st) {
+  if (rows <= 0 || d <= 0 || d % 8 != 0 || d > PB_NOALLOC_MAX_D) return PB_BAD_ARG;
+  const int nparts = pb_rmsnorm_bwd_nparts(rows, d);
+  if (nparts > PB_NOALLOC_MAX_PARTS) return PB_BAD_ARG;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= PB_NOALLOC_MAX_DEVICES) return PB_BAD_ARG;
+  if (g_noalloc_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_rms_partials);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_noalloc_addr[dev] = static_cast<float*>(ptr);
+  }
+  return pb_rmsnorm_bwd(dy, h, w, rstd, dres, dx, dw, g_noalloc_addr[dev], accumulate, rows, d, st);
+}
+
+PB_API int pb_rmsnorm_bwd_noalloc_max_d() { return PB_NOALLOC_MAX_D; }
