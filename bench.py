@@ -43,7 +43,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro-batch", type=int, default=4)
+    ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (invalid as a result)")

@@ -34,6 +34,7 @@ struct GemmParams {
   float alpha, beta;
   int out_f32, d_f32;
   int a_mn, b_mn;
+  int tma_store;  // epilogue stages tiles in shared memory and stores them with TMA
   int debug;  // bit 1: skip the epilogue's global stores (timing experiments only)
   int* status;
 };
@@ -44,13 +45,14 @@ struct GemmSmem {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int EPI_BYTES = 4 * 2 * 4096;  // per epilogue warp: two 32-row x 128 B slabs
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int BN>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   using S = GemmSmem<BN>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -58,7 +60,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* smA = smem;
   uint8_t* smB = smem + STAGES * S::A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint8_t* smEpi = smem + STAGES * S::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES + S::EPI_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* tfull = bars + 2 * STAGES;
@@ -192,6 +195,85 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool row_ok = row < p.M;
       const size_t c_off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
       const size_t d_off = static_cast<size_t>(b) * p.strideD + static_cast<size_t>(row) * p.ldd;
+      if (p.tma_store) {
+        // Stage 32 rows x 128 bytes per warp in the TMA swizzle layout, then one bulk
+        // tensor store per slab: coalesced, asynchronous, clipped at the matrix edge.
+        uint8_t* my_epi = smEpi + (warp - 2) * 8192;
+        const int cols_per_slab = p.out_f32 ? 32 : 64;
+        const int y0 = m_blk * BM + q * 32;
+#pragma unroll 1
+        for (int sl = 0; sl * cols_per_slab < BN; ++sl) {
+          const int x0 = n0 + sl * cols_per_slab;
+          uint8_t* buf = my_epi + (sl & 1) * 4096;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll 1
+          for (int hf = 0; hf * 32 < cols_per_slab; ++hf) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_addr + sl * cols_per_slab + hf * 32, r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+            const int col0 = x0 + hf * 32;
+            if (p.D != nullptr && row_ok && col0 < p.N) {
+              const bool full_chunk = (col0 + 32 <= p.N);
+              if (p.d_f32) {
+                const float* dp = static_cast<const float*>(p.D) + d_off + col0;
+                if (full_chunk && (p.ldd % 4 == 0)) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const float4 d4 = reinterpret_cast<const float4*>(dp)[i];
+                    v[4 * i] += p.beta * d4.x; v[4 * i + 1] += p.beta * d4.y;
+                    v[4 * i + 2] += p.beta * d4.z; v[4 * i + 3] += p.beta * d4.w;
+                  }
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    if (col0 + i < p.N) v[i] += p.beta * dp[i];
+                }
+              } else {
+                const bf16* dp = static_cast<const bf16*>(p.D) + d_off + col0;
+                if (full_chunk && (p.ldd % 8 == 0)) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    float f[8];
+                    unpack8(reinterpret_cast<const bf16x8*>(dp)[i], f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[8 * i + j] += p.beta * f[j];
+                  }
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    if (col0 + i < p.N) v[i] += p.beta * bf16_to_f32(dp[i]);
+                }
+              }
+            }
+            uint8_t* rowp = buf + lane * 128;
+            if (p.out_f32) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                *reinterpret_cast<float4*>(rowp + ((i ^ (lane & 7)) << 4)) =
+                    make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                bf16x8 pk;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  pk.v[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+                *reinterpret_cast<bf16x8*>(rowp + (((hf * 4 + i) ^ (lane & 7)) << 4)) = pk;
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && x0 < p.N && y0 < p.M && !(p.debug & 2)) {
+            tma_store_3d(&tmC, buf, x0, y0, b);
+          }
+          if (lane == 0) tma_store_commit();
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -275,6 +357,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   }
 
+  if (warp >= 2 && lane == 0) tma_store_wait<0>();  // staged tiles must be read out before exit
   tc_fence_before();
   __syncthreads();
   if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != PB_OK) {
@@ -321,8 +404,9 @@ int make_tmap_3d(CUtensorMap* tm, const void* base, int elem_bytes, uint64_t inn
                            (batch > 1 ? batch_stride_elems : ld_elems * outer) * elem_bytes};
   cuuint32_t box[3] = {box_inner, box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  const CUtensorMapDataType dt =
-      elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUtensorMapDataType dt = elem_bytes == 2   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                   : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const CUresult r =
       fn(tm, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -342,7 +426,8 @@ int num_sms() {
 }
 
 template <int BN>
-int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_ctas,
+int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                const GemmParams& p, int max_ctas,
                 cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
@@ -357,7 +442,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = static_cast<int>(tiles);
-  gemm_bf16_kernel<BN><<<grid, 192, GemmSmem<BN>::TOTAL, st>>>(tmA, tmB, p);
+  gemm_bf16_kernel<BN><<<grid, 192, GemmSmem<BN>::TOTAL, st>>>(tmA, tmB, tmC, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -366,7 +451,8 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
 using namespace pb;
 
 static int g_gemm_debug = 0;
-// Timing experiments: bit 0 forces the 128-wide tile, bit 1 drops the epilogue stores.
+// Timing experiments: bit 0 forces the 128-wide tile, bit 1 drops the epilogue stores,
+// bit 2 selects the direct-store epilogue.
 PB_API int pb_gemm_set_debug(int flags) {
   g_gemm_debug = flags;
   return 0;
@@ -411,6 +497,15 @@ PB_API int pb_gemm_bf16(const void* A, const void* B, void* C, const void* D, in
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.status = status;
   p.debug = g_gemm_debug;
-  return bn256 ? launch_gemm<256>(tmA, tmB, p, max_ctas, st)
-               : launch_gemm<128>(tmA, tmB, p, max_ctas, st);
+  // TMA-store epilogue when the output rows are 16-byte aligned; else direct stores.
+  const int cbytes = out_f32 ? 4 : 2;
+  CUtensorMap tmC = tmA;
+  p.tma_store = 0;
+  if (!(g_gemm_debug & 4) && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+      (ldc * cbytes) % 16 == 0 && (batch == 1 || (strideC * cbytes) % 16 == 0)) {
+    if (make_tmap_3d(&tmC, C, cbytes, N, M, batch, ldc, strideC, out_f32 ? 32 : 64, 32) == 0)
+      p.tma_store = 1;
+  }
+  return bn256 ? launch_gemm<256>(tmA, tmB, tmC, p, max_ctas, st)
+               : launch_gemm<128>(tmA, tmB, tmC, p, max_ctas, st);
 }
