@@ -135,7 +135,7 @@ class Trainer:
             ws.append(w)
 
         def vec(name, n, tree_name):
-            ws.append(Weight(name=name, shape=(n,), group="adam", lp=False,
+            ws.append(Weight(name=name, shape=(n,), group="vec", lp=False,
                              sources=[(tree_name, 0, n, None, None)]))
 
         def src(tree_name, r0, rows):
@@ -186,41 +186,87 @@ class Trainer:
                 w.off = w.units[0].off
                 for a, b in zip(w.units, w.units[1:]):
                     assert b.off == a.off + a.rows * a.cols
-        off = 0
-        for w in ws:
-            if w.group == "adam":
-                w.off = off
-                off += int(math.prod(w.shape))
-                off = (off + 7) // 8 * 8
-        self.n_adam = off
+        for grp in ("adam", "vec"):
+            off = 0
+            for w in ws:
+                if w.group == grp:
+                    w.off = off
+                    off += int(math.prod(w.shape))
+                    off = (off + 7) // 8 * 8
+            setattr(self, "n_" + grp, off)
 
     def _allocate(self) -> None:
         dev = self.device
         f32 = dict(dtype=torch.float32, device=dev)
-        self.muon_master = torch.zeros(self.n_muon, **f32)
-        self.muon_grad = torch.zeros(self.n_muon, **f32)
-        self.muon_mom = torch.zeros(self.n_muon, **f32)
-        self.muon_lp = torch.zeros(self.n_muon, dtype=BF16, device=dev)
-        self.adam_master = torch.zeros(self.n_adam, **f32)
-        self.adam_grad = torch.zeros(self.n_adam, **f32)
-        self.adam_m = torch.zeros(self.n_adam, **f32)
-        self.adam_v = torch.zeros(self.n_adam, **f32)
-        self.adam_lp = torch.zeros(self.n_adam, dtype=BF16, device=dev)
-        max_unit = max((r * c * len(us) for (r, c), us in self.unit_classes.items()),
-                       default=1)
-        self.ns_x = [torch.empty(max_unit, dtype=BF16, device=dev) for _ in range(2)]
-        max_g = max((min(r, c) ** 2 * len(us) for (r, c), us in self.unit_classes.items()),
-                    default=1)
-        self.ns_g = [torch.empty(max_g, dtype=BF16, device=dev) for _ in range(2)]
-        nparts = max(_lib.query("pb_sumsq_nparts", max(self.n_muon, self.n_adam, 1)), 1)
+        self.sym = None
+        n_m, n_a, n_v = self.n_muon, self.n_adam, self.n_vec
+        if self.world > 1 and self.grad_sync in ("auto", "p2p"):
+            # Gradients and bf16 working weights live in symmetric memory: peers read the
+            # former (reduce to owner) and write the latter (update + broadcast).
+            from .parallel.symm import SymmetricBuffer, SymmetricGroup
+
+            ok, err = 1, None
+            try:
+                self.sym = SymmetricGroup(self.pg)
+                self.sym_grad = SymmetricBuffer(4 * (n_m + n_a + n_v), self.pg)
+                self.sym_lp = SymmetricBuffer(2 * (n_m + n_a), self.pg)
+            except RuntimeError as e:      # peer mapping refused on this machine
+                ok, err = 0, e
+            flag = torch.tensor([ok], dtype=torch.int32, device=dev)
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN, group=self.pg)
+            if int(flag.item()) == 0:
+                if self.grad_sync == "p2p":
+                    raise RuntimeError(f"symmetric memory unavailable: {err}")
+                self.sym = None
+        if self.sym is not None:
+            self.muon_grad = self.sym_grad.view(torch.float32, n_m, 0)
+            self.adam_grad = self.sym_grad.view(torch.float32, n_a, 4 * n_m)
+            self.vec_grad = self.sym_grad.view(torch.float32, n_v, 4 * (n_m + n_a))
+            self.muon_lp = self.sym_lp.view(BF16, n_m, 0)
+            self.adam_lp = self.sym_lp.view(BF16, n_a, 2 * n_m)
+        else:
+            self.muon_grad = torch.zeros(n_m, **f32)
+            self.adam_grad = torch.zeros(n_a, **f32)
+            self.vec_grad = torch.zeros(n_v, **f32)
+            self.muon_lp = torch.zeros(n_m, dtype=BF16, device=dev)
+            self.adam_lp = torch.zeros(n_a, dtype=BF16, device=dev)
+        self.muon_master = torch.zeros(n_m, **f32)
+        self.muon_mom = torch.zeros(n_m, **f32)
+        self.adam_master = torch.zeros(n_a, **f32)
+        self.adam_m = torch.zeros(n_a, **f32)
+        self.adam_v = torch.zeros(n_a, **f32)
+        self.vec_master = torch.zeros(n_v, **f32)
+        self.vec_m = torch.zeros(n_v, **f32)
+        self.vec_v = torch.zeros(n_v, **f32)
+        # ownership: rank r updates units [lo, hi) of every Muon shape class and one
+        # contiguous slice of the AdamW slab; fp32 vectors are updated by every rank.
+        from .parallel.fsdp import split_bounds
+
+        w_, r_ = (self.world, self.rank) if self.sym is not None else (1, 0)
+        self.own_units = {key: split_bounds(len(us), w_, r_)
+                          for key, us in self.unit_classes.items()}
+        a_lo, a_hi = split_bounds(n_a // 8, w_, r_)
+        self.own_adam = (a_lo * 8, a_hi * 8)
+        max_unit = max((r * c * (self.own_units[(r, c)][1] - self.own_units[(r, c)][0])
+                        for (r, c) in self.unit_classes), default=1)
+        self.ns_x = [torch.empty(max(max_unit, 1), dtype=BF16, device=dev) for _ in range(2)]
+        max_g = max((min(r, c) ** 2 * (self.own_units[(r, c)][1] - self.own_units[(r, c)][0])
+                     for (r, c) in self.unit_classes), default=1)
+        self.ns_g = [torch.empty(max(max_g, 1), dtype=BF16, device=dev) for _ in range(2)]
+        nparts = max(_lib.query("pb_sumsq_nparts", max(n_m, n_a, n_v, 1)), 1)
+        if self.sym is not None:
+            nparts = max(nparts, _lib.query("pb_reduce_nparts", max(n_m, n_a, n_v, 1)))
         self.opt_scratch = torch.empty(nparts + 8, **f32)
         self.gnorm_sq = torch.zeros(1, **f32)
+        self.local_sq = torch.zeros(1, **f32)
+        self.vec_sq = torch.zeros(1, **f32)
+        bufs = {"muon": (self.muon_master, self.muon_grad, self.muon_lp),
+                "adam": (self.adam_master, self.adam_grad, self.adam_lp),
+                "vec": (self.vec_master, self.vec_grad, None)}
         self.p: dict[str, Tensor] = {}
         for w in self.weights.values():
             n = int(math.prod(w.shape))
-            master = self.muon_master if w.group == "muon" else self.adam_master
-            grad = self.muon_grad if w.group == "muon" else self.adam_grad
-            lpbuf = self.muon_lp if w.group == "muon" else self.adam_lp
+            master, grad, lpbuf = bufs[w.group]
             t = (lpbuf if w.lp else master)[w.off:w.off + n].view(w.shape)
             t.requires_grad_(True)
             t.main_grad = grad[w.off:w.off + n].view(w.shape)
@@ -247,6 +293,9 @@ class Trainer:
                     dst[r0:r0 + rows].copy_(src.to(self.device))
             self.muon_lp.copy_(self.muon_master)
             self.adam_lp.copy_(self.adam_master)
+        if self.sym is not None:
+            torch.cuda.synchronize()
+            torch.distributed.barrier(self.pg)
 
     def export_tree(self) -> dict:
         """Parameter tree (reference layout, fp32, on CPU) from the master buffers."""
@@ -338,17 +387,50 @@ class Trainer:
 
     # ---------------------------------------------------------------- optimizer
     def _sync_grads(self) -> None:
-        if self.world == 1:
+        """Make the owned gradient slices (and all vector gradients) global sums and put the
+        squared global gradient norm in ``self.gnorm_sq``."""
+        st = stream_ptr()
+        if self.world > 1 and self.sym is None:
+            import torch.distributed as dist
+
+            for g in (self.muon_grad, self.adam_grad, self.vec_grad):
+                dist.all_reduce(g, group=self.pg)
+        if self.sym is None:
+            call("pb_sumsq_f32", ptr(self.muon_grad), self.n_muon, ptr(self.opt_scratch),
+                 ptr(self.gnorm_sq), 0, st)
+            call("pb_sumsq_f32", ptr(self.adam_grad), self.n_adam, ptr(self.opt_scratch),
+                 ptr(self.gnorm_sq), 1, st)
+            call("pb_sumsq_f32", ptr(self.vec_grad), self.n_vec, ptr(self.opt_scratch),
+                 ptr(self.gnorm_sq), 1, st)
             return
-        import torch.distributed as dist
+        sym = self.sym
+        sym.barrier(0)                      # every rank's backward is complete
+        first = True
+        for (rows, cols), units in sorted(self.unit_classes.items()):
+            lo_u, hi_u = self.own_units[(rows, cols)]
+            if hi_u > lo_u:
+                lo = units[0].off + lo_u * rows * cols
+                sym.reduce_to_owner(self.sym_grad, 0, lo, (hi_u - lo_u) * rows * cols,
+                                    self.muon_grad, self.opt_scratch, self.local_sq, not first)
+                first = False
+        a_lo, a_hi = self.own_adam
+        if a_hi > a_lo:
+            sym.reduce_to_owner(self.sym_grad, 4 * self.n_muon, a_lo, a_hi - a_lo, self.adam_grad,
+                                self.opt_scratch, self.local_sq, not first)
+            first = False
+        if first:
+            self.local_sq.zero_()
+        # vectors: every rank folds all peers (same order, same bits) into a private copy
+        if not hasattr(self, "vec_sum"):
+            self.vec_sum = torch.zeros_like(self.vec_master)
+        sym.reduce_to_owner(self.sym_grad, 4 * (self.n_muon + self.n_adam), 0, self.n_vec,
+                            self.vec_sum, self.opt_scratch, self.vec_sq, False)
+        sym.allreduce_scalar(self.local_sq, self.gnorm_sq)   # also: all reads of grads done
+        self.gnorm_sq.add_(self.vec_sq)
 
-        for g in (self.muon_grad, self.adam_grad):
-            dist.all_reduce(g, group=self.pg)
-
-    def _newton_schulz_class(self, rows: int, cols: int, units: list[Unit], steps: int) -> Tensor:
-        """Batched quintic Newton-Schulz over all units of one shape, in bf16 on the
+    def _newton_schulz_class(self, rows: int, cols: int, nb: int, steps: int) -> Tensor:
+        """Batched quintic Newton-Schulz over ``nb`` matrices of one shape, in bf16 on the
         tcgen05 GEMM. Input: self.ns_x[0] holds the normalised Nesterov momenta."""
-        nb = len(units)
         x = self.ns_x[0][: nb * rows * cols].view(nb, rows, cols)
         y = self.ns_x[1][: nb * rows * cols].view(nb, rows, cols)
         m = min(rows, cols)
@@ -367,46 +449,60 @@ class Trainer:
             else:
                 ops.gemm(x, pm, out=y, d=x, alpha=1.0, beta=a)            # aX + X P
             x, y = y, x
-            self.launches += 3
         return x
 
     def optimizer_step(self, lr_mult: float, gscale: float = 1.0) -> None:
-        """Clip, AdamW slab, batched Muon; refreshes the bf16 working copies."""
+        """Clip, AdamW slabs, batched Muon on the owned matrices; refreshes the bf16 working
+        copies (on every rank when the weights live in symmetric memory)."""
         tc = self.tcfg
         st = stream_ptr()
         clip = float(tc.grad_clip)
-        call("pb_sumsq_f32", ptr(self.muon_grad), self.n_muon, ptr(self.opt_scratch),
-             ptr(self.gnorm_sq), 0, st)
-        call("pb_sumsq_f32", ptr(self.adam_grad), self.n_adam, ptr(self.opt_scratch),
-             ptr(self.gnorm_sq), 1, st)
-        self.launches += 4
         step = self.step_count
-        call("pb_adamw", ptr(self.adam_master), ptr(self.adam_grad), ptr(self.adam_m),
-             ptr(self.adam_v), ptr(self.adam_lp), self.n_adam, float(tc.adamw_lr) * lr_mult,
-             float(tc.adamw_beta1), float(tc.adamw_beta2), float(tc.adamw_eps),
-             float(tc.adamw_wd), step, ptr(self.gnorm_sq), clip, gscale, st)
-        self.launches += 1
+        hp = (float(tc.adamw_lr) * lr_mult, float(tc.adamw_beta1), float(tc.adamw_beta2),
+              float(tc.adamw_eps), float(tc.adamw_wd))
+        vec_grad = self.vec_sum if self.sym is not None else self.vec_grad
+        call("pb_adamw", ptr(self.vec_master), ptr(vec_grad), ptr(self.vec_m), ptr(self.vec_v),
+             None, self.n_vec, *hp, step, ptr(self.gnorm_sq), clip, gscale, st)
+        a_lo, a_hi = self.own_adam
+        if self.sym is None:
+            call("pb_adamw", ptr(self.adam_master), ptr(self.adam_grad), ptr(self.adam_m),
+                 ptr(self.adam_v), ptr(self.adam_lp), self.n_adam, *hp, step, ptr(self.gnorm_sq),
+                 clip, gscale, st)
+        elif a_hi > a_lo:
+            call("pb_adamw_bcast", ptr(self.adam_master), ptr(self.adam_grad), ptr(self.adam_m),
+                 ptr(self.adam_v), self.sym_lp.peer_ptrs(2 * self.n_muon), self.world, a_lo,
+                 a_hi - a_lo, *hp, step, ptr(self.gnorm_sq), clip, gscale, st)
         lr = float(tc.muon_lr) * lr_mult
         beta = float(tc.muon_momentum)
         for (rows, cols), units in sorted(self.unit_classes.items()):
+            lo_u, hi_u = self.own_units[(rows, cols)]
+            nb = hi_u - lo_u
+            if nb == 0:
+                continue
             n = rows * cols
-            base = units[0].off
+            base = units[0].off + lo_u * n
             x0 = self.ns_x[0]
-            for j, u in enumerate(units):
-                assert u.off == base + j * n
-                call("pb_muon_prepare", ptr(self.muon_grad[u.off:]), ptr(self.muon_mom[u.off:]),
+            for j in range(nb):
+                off = base + j * n
+                call("pb_muon_prepare", ptr(self.muon_grad[off:]), ptr(self.muon_mom[off:]),
                      ptr(x0[j * n:]), n, beta, ptr(self.gnorm_sq), clip, gscale,
                      ptr(self.opt_scratch), st)
-                self.launches += 3
-            xo = self._newton_schulz_class(rows, cols, units, int(tc.muon_ns_steps))
-            call("pb_muon_apply", ptr(self.muon_master[base:]), ptr(xo),
-                 ptr(self.muon_lp[base:]), n * len(units), lr, T.muon_rms_scale(rows, cols),
-                 self.muon_wd, st)
-            self.launches += 1
+            xo = self._newton_schulz_class(rows, cols, nb, int(tc.muon_ns_steps))
+            scale = T.muon_rms_scale(rows, cols)
+            if self.sym is None:
+                call("pb_muon_apply", ptr(self.muon_master[base:]), ptr(xo),
+                     ptr(self.muon_lp[base:]), n * nb, lr, scale, self.muon_wd, st)
+            else:
+                call("pb_muon_apply_bcast", ptr(self.muon_master), ptr(xo),
+                     self.sym_lp.peer_ptrs(0), self.world, base, n * nb, lr, scale,
+                     self.muon_wd, st)
+        if self.sym is not None:
+            self.sym.barrier(3)             # every peer's stores into my weights have landed
 
     def zero_grad(self) -> None:
         self.muon_grad.zero_()
         self.adam_grad.zero_()
+        self.vec_grad.zero_()
 
     # --------------------------------------------------------------------- step
     def step(self, tokens: Tensor, loss_mask: Tensor | None = None) -> dict:

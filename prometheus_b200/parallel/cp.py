@@ -1,0 +1,214 @@
+"""Context parallelism: sequence split, ring schedule, ring attention with an online-softmax
+fold, and the delta-rule chunk-state hand-off.
+
+Softmax layers follow the reference (``parallel/cp.py:45-324``): equal contiguous chunks,
+ring step ``t`` sees KV owner ``(rank - t) mod n``, fold state ``(m, l, acc)`` starting at
+``(-inf, 0, 0)``, causal mask by global index with the ``-1e9`` sentinel, softmax floor
+``1e-12``.
+
+Delta-rule layers (no counterpart in the reference): over one rank's slice the state map is
+affine, ``S_out = P S_in + R`` with ``P = prod_chunks (I - K^T W)`` and ``R`` the state
+reached from zero. Ranks build ``(P_r, R_r)`` locally in parallel, exchange those small
+operands (heads x 128 x 128 fp32), prefix-compose them in rank order, and then run the
+chunk walk once with the true incoming state. ``delta_state_handoff`` is that composition.
+"""
+from __future__ import annotations
+
+import math
+from typing import Sequence
+
+import torch
+
+Tensor = torch.Tensor
+_MASK = -1e9
+_FLOOR = 1e-12
+
+
+def _err(msg):
+    from . import MeshError
+
+    raise MeshError(msg)
+
+
+def _int(v, name):
+    if isinstance(v, bool) or not isinstance(v, int):
+        _err(f"{name} must be a Python int")
+    return v
+
+
+def cp_split_seq(x, n: int, rank: int, *, axis: int = 1) -> Tensor:
+    n, rank, axis = _int(n, "n"), _int(rank, "rank"), _int(axis, "axis")
+    if n < 1:
+        _err(f"n must be >= 1, got {n}")
+    if rank < 0 or rank >= n:
+        _err(f"rank {rank} out of range for n={n}")
+    t = torch.as_tensor(x)
+    a = axis + t.ndim if axis < 0 else axis
+    if a < 0 or a >= t.ndim:
+        _err(f"axis {axis} out of range for ndim={t.ndim}")
+    dim = t.shape[a]
+    if dim < n:
+        _err(f"dimension {dim} is smaller than n={n}")
+    if dim % n != 0:
+        _err(f"dimension {dim} is not divisible by n={n}")
+    chunk = dim // n
+    return t if n == 1 else t.narrow(a, rank * chunk, chunk)
+
+
+def cp_ring_schedule(n: int, rank: int) -> tuple:
+    n, rank = _int(n, "n"), _int(rank, "rank")
+    if n < 1:
+        _err(f"n must be >= 1, got {n}")
+    if rank < 0 or rank >= n:
+        _err(f"rank {rank} out of range for n={n}")
+    return tuple((rank - t) % n for t in range(n))
+
+
+def online_softmax_step(state, q, k, v, *, q_offset: int, k_offset: int, causal: bool,
+                        scale: float):
+    """Fold one KV block into ``(m, l, acc)``. q: (B,Cq,H,D); k, v: (B,Ck,Hkv,D)."""
+    m, ell, acc = state
+    g = q.shape[2] // k.shape[2]
+    if g > 1:
+        k, v = k.repeat_interleave(g, dim=2), v.repeat_interleave(g, dim=2)
+    scores = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
+    if causal:
+        qi = q_offset + torch.arange(q.shape[1], device=q.device)
+        ki = k_offset + torch.arange(k.shape[1], device=q.device)
+        scores = torch.where(ki[None, :] > qi[:, None], torch.full_like(scores, _MASK), scores)
+    m_new = torch.maximum(m, scores.amax(dim=-1, keepdim=True))
+    alpha = torch.exp(m - m_new)
+    p = torch.exp(scores - m_new)
+    ell = alpha * ell + p.sum(dim=-1, keepdim=True)
+    acc = alpha * acc + torch.einsum("bhqk,bkhd->bhqd", p, v.float())
+    return m_new, ell, acc
+
+
+def ring_attention_rank(q, ks: Sequence, vs: Sequence, rank: int, *, causal: bool = True,
+                        scale: float | None = None) -> Tensor:
+    """Attention output of ``rank``'s query block against every KV block, folded in ring
+    order. ``ks[r]``/``vs[r]`` are rank r's blocks (equal lengths)."""
+    n = len(ks)
+    if n < 1 or len(vs) != n:
+        _err("ks and vs must be non-empty and the same length")
+    if rank < 0 or rank >= n:
+        _err(f"rank {rank} out of range for n={n}")
+    q = torch.as_tensor(q)
+    b, c, h, d = q.shape
+    for name, blocks in (("k", ks), ("v", vs)):
+        for t in blocks:
+            if t.ndim != 4 or t.shape[0] != b or t.shape[1] != c:
+                _err(f"{name} block shape {tuple(t.shape)} incompatible with q {tuple(q.shape)}")
+    sc = 1.0 / math.sqrt(d) if scale is None else float(scale)
+    dv = vs[0].shape[-1]
+    state = (torch.full((b, h, c, 1), -math.inf, dtype=torch.float32, device=q.device),
+             torch.zeros((b, h, c, 1), dtype=torch.float32, device=q.device),
+             torch.zeros((b, h, c, dv), dtype=torch.float32, device=q.device))
+    for owner in cp_ring_schedule(n, rank):
+        state = online_softmax_step(state, q, ks[owner], vs[owner], q_offset=rank * c,
+                                    k_offset=owner * c, causal=causal, scale=sc)
+    _, ell, acc = state
+    return (acc / torch.clamp(ell, min=_FLOOR)).permute(0, 2, 1, 3)
+
+
+def ring_attention(q, k, v, n: int, *, causal: bool = True, scale: float | None = None) -> Tensor:
+    """All ranks in one call: split, run every rank's fold, concatenate along the sequence."""
+    qs = [cp_split_seq(q, n, r) for r in range(n)]
+    ks = [cp_split_seq(k, n, r) for r in range(n)]
+    vs = [cp_split_seq(v, n, r) for r in range(n)]
+    return torch.cat([ring_attention_rank(qs[r], ks, vs, r, causal=causal, scale=scale)
+                      for r in range(n)], dim=1)
+
+
+def ring_attention_distributed(q, k, v, *, group=None, causal: bool = True,
+                               scale: float | None = None) -> Tensor:
+    """One rank's share over ``torch.distributed``: KV blocks travel to the next rank with
+    non-blocking send/recv while the current block is folded."""
+    import torch.distributed as dist
+
+    n, rank = dist.get_world_size(group), dist.get_rank(group)
+    b, c, h, d = q.shape
+    sc = 1.0 / math.sqrt(d) if scale is None else float(scale)
+    state = (torch.full((b, h, c, 1), -math.inf, dtype=torch.float32, device=q.device),
+             torch.zeros((b, h, c, 1), dtype=torch.float32, device=q.device),
+             torch.zeros((b, h, c, v.shape[-1]), dtype=torch.float32, device=q.device))
+    cur_k, cur_v = k.contiguous(), v.contiguous()
+    nxt = (rank + 1) % n
+    prv = (rank - 1) % n
+    if group is not None:
+        nxt, prv = dist.get_global_rank(group, nxt), dist.get_global_rank(group, prv)
+    for t, owner in enumerate(cp_ring_schedule(n, rank)):
+        reqs = []
+        if t + 1 < n:
+            nk, nv = torch.empty_like(cur_k), torch.empty_like(cur_v)
+            ops = [dist.P2POp(dist.isend, cur_k, nxt, group), dist.P2POp(dist.isend, cur_v, nxt, group),
+                   dist.P2POp(dist.irecv, nk, prv, group), dist.P2POp(dist.irecv, nv, prv, group)]
+            reqs = dist.batch_isend_irecv(ops)
+        state = online_softmax_step(state, q, cur_k, cur_v, q_offset=rank * c,
+                                    k_offset=owner * c, causal=causal, scale=sc)
+        for r in reqs:
+            r.wait()
+        if t + 1 < n:
+            cur_k, cur_v = nk, nv
+    _, ell, acc = state
+    return (acc / torch.clamp(ell, min=_FLOOR)).permute(0, 2, 1, 3)
+
+
+# ---------------------------------------------------------------------------
+# delta-rule state hand-off
+# ---------------------------------------------------------------------------
+def compose_affine(first, second):
+    """Map applying ``first`` then ``second``: (P2 P1, P2 R1 + R2)."""
+    p1, r1 = first
+    p2, r2 = second
+    return p2 @ p1, p2 @ r1 + r2
+
+
+def slice_affine_map(k, v, beta, chunk: int = 64):
+    """(P, R) of one rank's slice: state leaving the slice = P @ state entering + R.
+    k: (B,S,H,Dk) L2-normalised keys, v: (B,S,H,Dv), beta: (B,S,H)."""
+    from ..kernels import wy_chunk_operands
+    from ..ops.delta import affine_inclusive_scan, chunk_affine_maps
+
+    b, s, h, dk = k.shape
+    if s % chunk != 0:
+        _err(f"slice length {s} must be a multiple of the chunk {chunk}")
+    n = s // chunk
+
+    def chunks(x):
+        return x.float().reshape(b, n, chunk, h, x.shape[-1]).permute(0, 3, 1, 2, 4)
+
+    kc, vc = chunks(k), chunks(v)
+    bc = beta.float().reshape(b, n, chunk, h).permute(0, 3, 1, 2)
+    w, uhat = wy_chunk_operands(kc, vc, bc)
+    p, r = chunk_affine_maps(kc, w, uhat)
+    pacc, racc = affine_inclusive_scan(p, r)
+    return pacc[:, :, -1], racc[:, :, -1]
+
+
+def delta_state_handoff(maps: Sequence, s0: Tensor | None = None) -> list:
+    """Incoming state of every rank from all ranks' slice maps (exclusive prefix composition
+    in rank order). ``maps[r] = (P_r, R_r)`` with shapes (B,H,Dk,Dk) and (B,H,Dk,Dv)."""
+    if not maps:
+        _err("maps must be non-empty")
+    p0, r0 = maps[0]
+    state = torch.zeros_like(r0) if s0 is None else s0.float()
+    out = []
+    for p, r in maps:
+        out.append(state)
+        state = p @ state + r
+    return out
+
+
+def delta_state_handoff_distributed(local_map, *, group=None, s0: Tensor | None = None) -> Tensor:
+    """One rank's incoming state: all-gather the (P, R) operands (a few MB) and compose the
+    prefix locally; every rank does the same tiny computation, no serial rank-to-rank wait."""
+    import torch.distributed as dist
+
+    n, rank = dist.get_world_size(group), dist.get_rank(group)
+    p, r = local_map
+    ps = [torch.empty_like(p) for _ in range(n)]
+    rs = [torch.empty_like(r) for _ in range(n)]
+    dist.all_gather(ps, p.contiguous(), group=group)
+    dist.all_gather(rs, r.contiguous(), group=group)
+    return delta_state_handoff(list(zip(ps, rs)), s0)[rank]
