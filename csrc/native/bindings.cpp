@@ -7,6 +7,8 @@ namespace py = pybind11;
 
 void bind_loader(py::module_& m);
 void bind_ckpt(py::module_& m);
+void bind_control(py::module_& m);
+void bind_obs(py::module_& m);
 
 PYBIND11_MODULE(_pb200_native, m) {
   m.doc() = "C++ systems components of prometheus_b200 (loader, checkpoints, control, ...)";
@@ -25,4 +27,8 @@ PYBIND11_MODULE(_pb200_native, m) {
   bind_loader(loader);
   auto ckpt = m.def_submodule("ckpt", "content-addressed sharded checkpoints");
   bind_ckpt(ckpt);
+  auto control = m.def_submodule("control", "elastic controller, rungs, scaling-law fit");
+  bind_control(control);
+  auto obs = m.def_submodule("obs", "metrics, tracing, run registry, spike log");
+  bind_obs(obs);
 }

