@@ -9,6 +9,7 @@ void bind_loader(py::module_& m);
 void bind_ckpt(py::module_& m);
 void bind_control(py::module_& m);
 void bind_obs(py::module_& m);
+void bind_harness_core(py::module_& m);
 
 PYBIND11_MODULE(_pb200_native, m) {
   m.doc() = "C++ systems components of prometheus_b200 (loader, checkpoints, control, ...)";
@@ -31,4 +32,5 @@ PYBIND11_MODULE(_pb200_native, m) {
   bind_control(control);
   auto obs = m.def_submodule("obs", "metrics, tracing, run registry, spike log");
   bind_obs(obs);
+  bind_harness_core(m);
 }

@@ -252,6 +252,40 @@ struct Json {
     write(out);
     return out;
   }
+  // Two-space indented text (serde_json::to_string_pretty layout), keys sorted.
+  std::string dump_pretty() const {
+    std::string out;
+    write_pretty(out, 0);
+    return out;
+  }
+  void write_pretty(std::string& out, int depth) const {
+    const std::string pad(static_cast<size_t>(depth + 1) * 2, ' ');
+    const std::string close(static_cast<size_t>(depth) * 2, ' ');
+    if (kind == Array) {
+      if (a->empty()) { out += "[]"; return; }
+      out += "[\n";
+      for (size_t i = 0; i < a->size(); ++i) {
+        out += pad;
+        (*a)[i].write_pretty(out, depth + 1);
+        out += i + 1 < a->size() ? ",\n" : "\n";
+      }
+      out += close + "]";
+    } else if (kind == Object) {
+      if (o->empty()) { out += "{}"; return; }
+      out += "{\n";
+      size_t i = 0;
+      for (const auto& kv : *o) {
+        out += pad;
+        write_string(out, kv.first);
+        out += ": ";
+        kv.second.write_pretty(out, depth + 1);
+        out += ++i < o->size() ? ",\n" : "\n";
+      }
+      out += close + "}";
+    } else {
+      write(out);
+    }
+  }
   void write(std::string& out) const {
     switch (kind) {
       case Null: out += "null"; break;
