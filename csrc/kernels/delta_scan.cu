@@ -11,8 +11,8 @@
 // whole walk (fp32, 128 lanes x 128 columns); every product is a tcgen05.mma with
 // M = 128, N = 128; the bf16 image of the state and of U that the MMAs consume as
 // their B operand is rewritten in shared memory each chunk in the 128-byte-swizzled
-// layout TMA itself produces; Q/K/W/M/dO tiles arrive by TMA through a two-stage
-// ring. Tiles with 64 token rows are used as 128-row A operands: the upper 64
+// layout TMA itself produces; Q/K/W/M and U^ (or dO) tiles arrive by TMA through a
+// two-stage ring, and every output leaves by a TMA store from shared memory. Tiles with 64 token rows are used as 128-row A operands: the upper 64
 // accumulator rows are then meaningless and are never read.
 //
 // warps 0-3: tensor-memory <-> registers <-> shared/global (lane = state row or token)
@@ -35,19 +35,14 @@ namespace dscan {
 constexpr int C = 64;    // tokens per chunk
 constexpr int D = 128;   // head dim (keys and values)
 constexpr int TILE_W = 0, TILE_Q = 16384, TILE_K = 32768, TILE_M = 49152, TILE_DO = 57344;
-constexpr int STAGE_FWD = 57344;           // W, Q, K (16 KB each) + M (8 KB)
-constexpr int STAGE_BWD = 57344 + 16384;   // + dO
-constexpr int XB_BYTES = 32768, UB_BYTES = 16384;
+constexpr int STAGE_BYTES = 57344 + 16384;  // W, Q, K (16 KB each), M (8 KB), U^ or dO (16 KB)
+constexpr int XB_BYTES = 32768, UB_BYTES = 16384, OB_BYTES = 16384;
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t COL_X = 0, COL_Y = 128, COL_O = 256;
 
 struct Params {
   int n_chunks;        // chunks per sequence
   int n_seq;           // batch * heads
-  const bf16* uhat;    // [G*64, 128]            (forward)
-  bf16* out;           // [G*64, 128]  O         (forward)
-  bf16* u_out;         // [G*64, 128]  U or dU
-  bf16* xb_out;        // [G, 128, 128] bf16 image of the state entering each chunk
   const float* x_init; // [n_seq, 128, 128] or null (zeros)
   float* x_final;      // [n_seq, 128, 128] or null
   int* status;
@@ -55,10 +50,11 @@ struct Params {
 
 template <bool BWD>
 struct Smem {
-  static constexpr int STAGE = BWD ? STAGE_BWD : STAGE_FWD;
+  static constexpr int STAGE = STAGE_BYTES;
   static constexpr int XB = 2 * STAGE;
   static constexpr int UB = XB + XB_BYTES;
-  static constexpr int BARS = UB + UB_BYTES;
+  static constexpr int OB = UB + UB_BYTES;
+  static constexpr int BARS = OB + OB_BYTES;
   static constexpr int TOTAL = BARS + 256 + 1024;
 };
 
@@ -71,13 +67,16 @@ template <bool BWD>
 __global__ void __launch_bounds__(192, 1)
 delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmQ,
                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmM,
-                  const __grid_constant__ CUtensorMap tmDO, const Params p) {
+                  const __grid_constant__ CUtensorMap tmDO, const __grid_constant__ CUtensorMap tmXB,
+                  const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmO,
+                  const Params p) {
   using S = Smem<BWD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* xb = smem + S::XB;
   uint8_t* ub = smem + S::UB;
+  uint8_t* ob = smem + S::OB;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BARS);
   uint64_t* full = bars;          // [2]
   uint64_t* empty = bars + 2;     // [2]
@@ -99,7 +98,7 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     fence_barrier_init();
     tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmM);
-    if (BWD) tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&tmDO);
   }
   if (warp == 4) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -128,10 +127,8 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         tma_load_3d(st + TILE_K, &tmK, &full[s], 0, row, 0);
         tma_load_3d(st + TILE_K + 8192, &tmK, &full[s], 64, row, 0);
         tma_load_3d(st + TILE_M, &tmM, &full[s], 0, row, 0);
-        if (BWD) {
-          tma_load_3d(st + TILE_DO, &tmDO, &full[s], 0, row, 0);
-          tma_load_3d(st + TILE_DO + 8192, &tmDO, &full[s], 64, row, 0);
-        }
+        tma_load_3d(st + TILE_DO, &tmDO, &full[s], 0, row, 0);
+        tma_load_3d(st + TILE_DO + 8192, &tmDO, &full[s], 64, row, 0);
       }
     }
   } else if (warp == 4) {
@@ -203,9 +200,12 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
   } else {
     // ------------------------- state / token row threads -------------------------
+    // Every result leaves through shared memory and a TMA store (coalesced, asynchronous):
+    // the bf16 state image is stored from the very tile the MMAs read, U / -dU from the
+    // operand tile, O from a staging tile. Thread 0 issues and tracks the stores.
     const int r = threadIdx.x;  // 0..127: tensor-memory lane = state row (or token row < 64)
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-    // initial state into tensor memory
+    auto sync_rows = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
     {
       const float* x0 = p.x_init ? p.x_init + (static_cast<size_t>(seq) * D + r) * D : nullptr;
 #pragma unroll 1
@@ -217,44 +217,13 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
       tmem_st_wait();
     }
-    bool ok = true;
-    for (int it = 0; it < N && ok; ++it) {
-      const int n = BWD ? (N - 1 - it) : it;
-      const uint32_t cph = it & 1;
-      const size_t g = static_cast<size_t>(seq) * N + n;
-      if (it > 0) {
-        if (!mbar_wait(o_done, cph ^ 1, p.status)) { ok = false; break; }
-        tc_fence_after();
-        if (!BWD && r < C) {
-          // output rows of the previous chunk
-          const int np = n - 1;
-          bf16* op = p.out + ((static_cast<size_t>(seq) * N + np) * C + r) * D;
-#pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(lane_addr + COL_O + c, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              bf16x8 pk;
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                pk.v[j] = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]),
-                                                __uint_as_float(v[8 * i + 2 * j + 1]));
-              reinterpret_cast<bf16x8*>(op + c)[i] = pk;
-            }
-          }
-        } else if (!BWD) {
-          // keep the warp-wide tcgen05.ld aligned for warps 2-3 (nothing to read)
-        }
-      }
-      // bf16 image of the state: shared memory (MMA operand) and global (for the other pass)
-      {
-        bf16* xg = p.xb_out + (g * D + r) * D;
+    // rows of the previous chunk's output: tensor memory -> staging tile
+    auto stage_out = [&]() {
+      if (!BWD && r < C) {
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
           uint32_t v[32];
-          tmem_ld_32x32b_x32(lane_addr + COL_X + c, v);
+          tmem_ld_32x32b_x32(lane_addr + COL_O + c, v);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -264,18 +233,59 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
               pk.v[j] = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]),
                                               __uint_as_float(v[8 * i + 2 * j + 1]));
             const int col = c + 8 * i;
-            st_swz(xb + (col >> 6) * 16384, r, (col & 63) >> 3, pk);
-            reinterpret_cast<bf16x8*>(xg + c)[i] = pk;
+            st_swz(ob + (col >> 6) * 8192, r, (col & 63) >> 3, pk);
           }
+        }
+      }
+    };
+    bool ok = true;
+    for (int it = 0; it < N && ok; ++it) {
+      const int n = BWD ? (N - 1 - it) : it;
+      const uint32_t cph = it & 1;
+      const int g = seq * N + n;
+      if (it > 0) {
+        if (!mbar_wait(o_done, cph ^ 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+      }
+      // all earlier bulk stores have finished reading xb / ub / ob before they are rewritten
+      if (r == 0) tma_store_wait_read<0>();
+      sync_rows();
+      if (it > 0) stage_out();
+      // bf16 image of the state entering this chunk
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + COL_X + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          bf16x8 pk;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            pk.v[j] = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]),
+                                            __uint_as_float(v[8 * i + 2 * j + 1]));
+          const int col = c + 8 * i;
+          st_swz(xb + (col >> 6) * 16384, r, (col & 63) >> 3, pk);
         }
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(x_ready);
+      sync_rows();
+      if (r == 0) {
+        if (!BWD && it > 0) {
+          const int prow = (seq * N + (n - 1)) * C;
+          tma_store_3d(&tmO, ob, 0, prow, 0);
+          tma_store_3d(&tmO, ob + 8192, 64, prow, 0);
+        }
+        tma_store_3d(&tmXB, xb, 0, g * D, 0);
+        tma_store_3d(&tmXB, xb + 16384, 64, g * D, 0);
+        tma_store_commit();
+      }
       if (!mbar_wait(y_done, cph, p.status)) { ok = false; break; }
       tc_fence_after();
       if (r < C) {
-        const size_t row = (g * C + r) * D;
+        const uint8_t* uh = smem + (it & 1) * S::STAGE + TILE_DO;
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
           uint32_t v[32];
@@ -288,20 +298,19 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             for (int j = 0; j < 8; ++j) y[j] = __uint_as_float(v[8 * i + j]);
             const int col = c + 8 * i;
             if (!BWD) {
-              float uh[8];
-              unpack8(*reinterpret_cast<const bf16x8*>(p.uhat + row + col), uh);
+              float uhv[8];
+              unpack8(*reinterpret_cast<const bf16x8*>(uh + (col >> 6) * 8192 + r * 128 +
+                                                       ((((col & 63) >> 3) ^ (r & 7)) << 4)),
+                      uhv);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) y[j] = uh[j] - y[j];  // U = U^ - W S
+              for (int j = 0; j < 8; ++j) y[j] = uhv[j] - y[j];  // U = U^ - W S
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) y[j] = -y[j];          // operand (and output) is -dU
             }
             bf16x8 pk;
 #pragma unroll
             for (int j = 0; j < 4; ++j) pk.v[j] = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
-            *reinterpret_cast<bf16x8*>(p.u_out + row + col) = pk;
-            if (BWD) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                pk.v[j] = __floats2bfloat162_rn(-y[2 * j], -y[2 * j + 1]);  // operand is -dU
-            }
             st_swz(ub + (col >> 6) * 8192, r, (col & 63) >> 3, pk);
           }
         }
@@ -309,28 +318,27 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(u_ready);
+      sync_rows();
+      if (r == 0) {
+        tma_store_3d(&tmU, ub, 0, g * C, 0);
+        tma_store_3d(&tmU, ub + 8192, 64, g * C, 0);
+        tma_store_commit();
+      }
     }
     // drain: last chunk's output rows and the final state
     if (ok && N > 0) {
       if (mbar_wait(o_done, (N - 1) & 1, p.status)) {
         tc_fence_after();
-        if (!BWD && r < C) {
-          bf16* op = p.out + ((static_cast<size_t>(seq) * N + (N - 1)) * C + r) * D;
-#pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(lane_addr + COL_O + c, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              bf16x8 pk;
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                pk.v[j] = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]),
-                                                __uint_as_float(v[8 * i + 2 * j + 1]));
-              reinterpret_cast<bf16x8*>(op + c)[i] = pk;
-            }
-          }
+        if (r == 0) tma_store_wait_read<0>();
+        sync_rows();
+        stage_out();
+        fence_proxy_async_smem();
+        sync_rows();
+        if (r == 0 && !BWD) {
+          const int prow = (seq * N + (N - 1)) * C;
+          tma_store_3d(&tmO, ob, 0, prow, 0);
+          tma_store_3d(&tmO, ob + 8192, 64, prow, 0);
+          tma_store_commit();
         }
         if (p.x_final != nullptr) {
           float* xf = p.x_final + (static_cast<size_t>(seq) * D + r) * D;
@@ -348,6 +356,7 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
       }
     }
+    if (r == 0) tma_store_wait<0>();
   }
 
   tc_fence_before();
@@ -363,8 +372,8 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 }
 
 template <bool BWD>
-int launch(const void* W, const void* Q, const void* K, const void* M, const void* dO,
-           const Params& p, cudaStream_t st) {
+int launch(const void* W, const void* Q, const void* K, const void* M, const void* fifth,
+           void* xb_out, void* u_out, void* o_out, const Params& p, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<BWD>,
@@ -373,16 +382,21 @@ int launch(const void* W, const void* Q, const void* K, const void* M, const voi
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  const uint64_t rows = static_cast<uint64_t>(p.n_seq) * p.n_chunks * C;
-  CUtensorMap tW, tQ, tK, tM, tD;
+  const uint64_t G = static_cast<uint64_t>(p.n_seq) * p.n_chunks;
+  const uint64_t rows = G * C;
+  CUtensorMap tW, tQ, tK, tM, tD, tXB, tU, tO;
   int r = 0;
   r |= make_tmap_3d(&tW, W, 2, D, rows, 1, D, 0, 64, C);
   r |= make_tmap_3d(&tQ, Q, 2, D, rows, 1, D, 0, 64, C);
   r |= make_tmap_3d(&tK, K, 2, D, rows, 1, D, 0, 64, C);
   r |= make_tmap_3d(&tM, M, 2, C, rows, 1, C, 0, 64, C);
-  r |= make_tmap_3d(&tD, BWD ? dO : Q, 2, D, rows, 1, D, 0, 64, C);
+  r |= make_tmap_3d(&tD, fifth, 2, D, rows, 1, D, 0, 64, C);
+  r |= make_tmap_3d(&tXB, xb_out, 2, D, G * D, 1, D, 0, 64, D);
+  r |= make_tmap_3d(&tU, u_out, 2, D, rows, 1, D, 0, 64, C);
+  r |= make_tmap_3d(&tO, BWD ? u_out : o_out, 2, D, rows, 1, D, 0, 64, C);
   if (r != 0) return 1000 + r;
-  delta_scan_kernel<BWD><<<p.n_seq, 192, Smem<BWD>::TOTAL, st>>>(tW, tQ, tK, tM, tD, p);
+  delta_scan_kernel<BWD><<<p.n_seq, 192, Smem<BWD>::TOTAL, st>>>(tW, tQ, tK, tM, tD, tXB, tU, tO,
+                                                                 p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -402,32 +416,25 @@ PB_API int pb_delta_scan_fwd(const void* W, const void* Uhat, const void* Q, con
   if (n_seq <= 0 || n_chunks <= 0) return PB_BAD_ARG;
   dscan::Params p;
   p.n_chunks = n_chunks; p.n_seq = n_seq;
-  p.uhat = static_cast<const bf16*>(Uhat);
-  p.out = static_cast<bf16*>(out);
-  p.u_out = static_cast<bf16*>(u_out);
-  p.xb_out = static_cast<bf16*>(xb_out);
   p.x_init = static_cast<const float*>(x_init);
   p.x_final = static_cast<float*>(x_final);
   p.status = status;
-  return dscan::launch<false>(W, Q, K, M, nullptr, p, st);
+  return dscan::launch<false>(W, Q, K, M, Uhat, xb_out, u_out, out, p, st);
 }
 
 // Backward walk (chunks in reverse). x_init = gradient of the final state (or null),
-//   u_out <- dU      xb_out[g] <- bf16(dS leaving chunk g, i.e. before chunk g is applied)
+//   ndu_out <- -dU (note the sign)
+//   dxb_out[g] <- bf16(dS leaving chunk g, i.e. before chunk g is applied)
 //   x_final <- gradient of the initial state
 PB_API int pb_delta_scan_bwd(const void* W, const void* Q, const void* K, const void* M,
-                             const void* dO, void* du_out, void* dxb_out, const void* x_init,
+                             const void* dO, void* ndu_out, void* dxb_out, const void* x_init,
                              void* x_final, int n_seq, int n_chunks, int* status,
                              cudaStream_t st) {
   if (n_seq <= 0 || n_chunks <= 0) return PB_BAD_ARG;
   dscan::Params p;
   p.n_chunks = n_chunks; p.n_seq = n_seq;
-  p.uhat = nullptr;
-  p.out = nullptr;
-  p.u_out = static_cast<bf16*>(du_out);
-  p.xb_out = static_cast<bf16*>(dxb_out);
   p.x_init = static_cast<const float*>(x_init);
   p.x_final = static_cast<float*>(x_final);
   p.status = status;
-  return dscan::launch<true>(W, Q, K, M, dO, p, st);
+  return dscan::launch<true>(W, Q, K, M, dO, dxb_out, ndu_out, nullptr, p, st);
 }

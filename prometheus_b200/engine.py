@@ -297,13 +297,36 @@ class Trainer:
             torch.cuda.synchronize()
             torch.distributed.barrier(self.pg)
 
+    def gather_masters(self) -> dict:
+        """Full fp32 master buffers per group on every rank. With ownership sharding each
+        rank only keeps the masters of the matrices it owns up to date, so the owned ranges
+        are summed across ranks (everything else contributes zeros)."""
+        if self.sym is None:
+            return {"muon": self.muon_master, "adam": self.adam_master, "vec": self.vec_master}
+        import torch.distributed as dist
+
+        muon = torch.zeros_like(self.muon_master)
+        for (rows, cols), units in self.unit_classes.items():
+            lo_u, hi_u = self.own_units[(rows, cols)]
+            lo = units[0].off + lo_u * rows * cols
+            hi = units[0].off + hi_u * rows * cols
+            muon[lo:hi] = self.muon_master[lo:hi]
+        adam = torch.zeros_like(self.adam_master)
+        a_lo, a_hi = self.own_adam
+        adam[a_lo:a_hi] = self.adam_master[a_lo:a_hi]
+        dist.all_reduce(muon, group=self.pg)
+        dist.all_reduce(adam, group=self.pg)
+        return {"muon": muon, "adam": adam, "vec": self.vec_master}
+
     def export_tree(self) -> dict:
         """Parameter tree (reference layout, fp32, on CPU) from the master buffers."""
         cfg = self.cfg
         nh, dh, nkv = M.head_geometry(cfg)
         out: dict[str, Tensor] = {}
+        full = self.gather_masters()
         for w in self.weights.values():
-            src = self.p[w.name].master.detach().cpu()
+            n = int(math.prod(w.shape))
+            src = full[w.group][w.off:w.off + n].view(w.shape).cpu()
             for tree_name, r0, rows, how, _ in w.sources:
                 blk = src[r0:r0 + rows]
                 if how == "t2":

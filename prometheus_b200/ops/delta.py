@@ -183,13 +183,14 @@ class _ScanFn(torch.autograd.Function):
         n_seq, n_chunks = ctx.dims
         dev = w.device
         d_out = d_out.contiguous()
-        du = torch.empty_like(u)
+        ndu = torch.empty_like(u)          # the kernel writes -dU
         dsb = torch.empty_like(sb)
         ds0 = torch.empty((n_seq, 128, 128), dtype=torch.float32, device=dev)
         dfin = None if d_sfin is None else d_sfin.float().contiguous()
-        call("pb_delta_scan_bwd", ptr(w), ptr(qc), ptr(kc), ptr(m), ptr(d_out), ptr(du), ptr(dsb),
+        call("pb_delta_scan_bwd", ptr(w), ptr(qc), ptr(kc), ptr(m), ptr(d_out), ptr(ndu), ptr(dsb),
              ptr(dfin), ptr(ds0), n_seq, n_chunks, ptr(status_word(dev)), stream_ptr())
-        d_w = gemm(du, sb, alpha=-1.0)            # dW = -dU S^T
+        du = -ndu
+        d_w = gemm(ndu, sb)                       # dW = -dU S^T
         d_m = torch.tril(gemm(d_out, u))          # dM = tril(dO U^T)
         d_q = gemm(d_out, sb)                     # dQ = dO S^T
         d_k = gemm(u, dsb)                        # dK = U dS'^T

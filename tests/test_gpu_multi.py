@@ -17,5 +17,17 @@ def test_two_rank_symmetric_memory_and_trainer():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29517",
            str(Path(__file__).parent / "_multi_gpu_worker.py")]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0 and "MULTI_GPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    import signal
+    import tempfile
+
+    with tempfile.TemporaryFile("w+") as log:
+        proc = subprocess.Popen(cmd, env=env, stdout=log, stderr=subprocess.STDOUT,
+                                start_new_session=True)
+        try:
+            rc = proc.wait(timeout=240)
+        except subprocess.TimeoutExpired:
+            os.killpg(proc.pid, signal.SIGKILL)      # the whole process group we started
+            rc = -9
+        log.seek(0)
+        text = log.read()
+    assert rc == 0 and "MULTI_GPU_OK" in text, text[-4000:]
