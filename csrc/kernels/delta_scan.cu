@@ -43,6 +43,8 @@ constexpr uint32_t COL_X = 0, COL_Y = 128, COL_O = 256;
 struct Params {
   int n_chunks;        // chunks per sequence
   int n_seq;           // batch * heads
+  int heads;           // > 0: Q, K, O and dO live in [batch * seq_len, ld] (head h at columns 128 h)
+  int seq_len;         //      instead of the per-chunk layout
   const float* x_init; // [n_seq, 128, 128] or null (zeros)
   float* x_final;      // [n_seq, 128, 128] or null
   int* status;
@@ -89,6 +91,9 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = blockIdx.x;
   const int N = p.n_chunks;
+  const bool tokmaj = p.heads > 0;
+  const int tok0 = tokmaj ? (seq / p.heads) * p.seq_len : seq * N * C;  // first token row
+  const int tx = tokmaj ? (seq % p.heads) * D : 0;
 
   if (threadIdx.x == 0) {
     mbar_init(&full[0], 1); mbar_init(&full[1], 1);
@@ -120,15 +125,21 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         mbar_arrive_expect_tx(&full[s], S::STAGE);
         uint8_t* st = smem + s * S::STAGE;
         const int row = (seq * N + n) * C;
+        const int trow = tok0 + n * C;
         tma_load_3d(st + TILE_W, &tmW, &full[s], 0, row, 0);
         tma_load_3d(st + TILE_W + 8192, &tmW, &full[s], 64, row, 0);
-        tma_load_3d(st + TILE_Q, &tmQ, &full[s], 0, row, 0);
-        tma_load_3d(st + TILE_Q + 8192, &tmQ, &full[s], 64, row, 0);
-        tma_load_3d(st + TILE_K, &tmK, &full[s], 0, row, 0);
-        tma_load_3d(st + TILE_K + 8192, &tmK, &full[s], 64, row, 0);
+        tma_load_3d(st + TILE_Q, &tmQ, &full[s], tx, trow, 0);
+        tma_load_3d(st + TILE_Q + 8192, &tmQ, &full[s], tx + 64, trow, 0);
+        tma_load_3d(st + TILE_K, &tmK, &full[s], tx, trow, 0);
+        tma_load_3d(st + TILE_K + 8192, &tmK, &full[s], tx + 64, trow, 0);
         tma_load_3d(st + TILE_M, &tmM, &full[s], 0, row, 0);
-        tma_load_3d(st + TILE_DO, &tmDO, &full[s], 0, row, 0);
-        tma_load_3d(st + TILE_DO + 8192, &tmDO, &full[s], 64, row, 0);
+        if (BWD) {
+          tma_load_3d(st + TILE_DO, &tmDO, &full[s], tx, trow, 0);
+          tma_load_3d(st + TILE_DO + 8192, &tmDO, &full[s], tx + 64, trow, 0);
+        } else {
+          tma_load_3d(st + TILE_DO, &tmDO, &full[s], 0, row, 0);
+          tma_load_3d(st + TILE_DO + 8192, &tmDO, &full[s], 64, row, 0);
+        }
       }
     }
   } else if (warp == 4) {
@@ -274,9 +285,9 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       sync_rows();
       if (r == 0) {
         if (!BWD && it > 0) {
-          const int prow = (seq * N + (n - 1)) * C;
-          tma_store_3d(&tmO, ob, 0, prow, 0);
-          tma_store_3d(&tmO, ob + 8192, 64, prow, 0);
+          const int prow = tok0 + (n - 1) * C;
+          tma_store_3d(&tmO, ob, tx, prow, 0);
+          tma_store_3d(&tmO, ob + 8192, tx + 64, prow, 0);
         }
         tma_store_3d(&tmXB, xb, 0, g * D, 0);
         tma_store_3d(&tmXB, xb + 16384, 64, g * D, 0);
@@ -335,9 +346,9 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         fence_proxy_async_smem();
         sync_rows();
         if (r == 0 && !BWD) {
-          const int prow = (seq * N + (N - 1)) * C;
-          tma_store_3d(&tmO, ob, 0, prow, 0);
-          tma_store_3d(&tmO, ob + 8192, 64, prow, 0);
+          const int prow = tok0 + (N - 1) * C;
+          tma_store_3d(&tmO, ob, tx, prow, 0);
+          tma_store_3d(&tmO, ob + 8192, tx + 64, prow, 0);
           tma_store_commit();
         }
         if (p.x_final != nullptr) {
@@ -373,7 +384,7 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
 template <bool BWD>
 int launch(const void* W, const void* Q, const void* K, const void* M, const void* fifth,
-           void* xb_out, void* u_out, void* o_out, const Params& p, cudaStream_t st) {
+           void* xb_out, void* u_out, void* o_out, int ld, const Params& p, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<BWD>,
@@ -386,14 +397,20 @@ int launch(const void* W, const void* Q, const void* K, const void* M, const voi
   const uint64_t rows = G * C;
   CUtensorMap tW, tQ, tK, tM, tD, tXB, tU, tO;
   int r = 0;
+  // token-major tensors: [batch * seq_len, ld]; per-chunk tensors: [G * 64, 128]
+  const bool tokmaj = p.heads > 0;
+  const uint64_t t_inner = tokmaj ? static_cast<uint64_t>(p.heads) * D : D;
+  const uint64_t t_ld = tokmaj ? static_cast<uint64_t>(ld) : D;
   r |= make_tmap_3d(&tW, W, 2, D, rows, 1, D, 0, 64, C);
-  r |= make_tmap_3d(&tQ, Q, 2, D, rows, 1, D, 0, 64, C);
-  r |= make_tmap_3d(&tK, K, 2, D, rows, 1, D, 0, 64, C);
+  r |= make_tmap_3d(&tQ, Q, 2, t_inner, rows * D / t_inner, 1, t_ld, 0, 64, C);
+  r |= make_tmap_3d(&tK, K, 2, t_inner, rows * D / t_inner, 1, t_ld, 0, 64, C);
   r |= make_tmap_3d(&tM, M, 2, C, rows, 1, C, 0, 64, C);
-  r |= make_tmap_3d(&tD, fifth, 2, D, rows, 1, D, 0, 64, C);
+  if (BWD) r |= make_tmap_3d(&tD, fifth, 2, t_inner, rows * D / t_inner, 1, t_ld, 0, 64, C);
+  else r |= make_tmap_3d(&tD, fifth, 2, D, rows, 1, D, 0, 64, C);
   r |= make_tmap_3d(&tXB, xb_out, 2, D, G * D, 1, D, 0, 64, D);
   r |= make_tmap_3d(&tU, u_out, 2, D, rows, 1, D, 0, 64, C);
-  r |= make_tmap_3d(&tO, BWD ? u_out : o_out, 2, D, rows, 1, D, 0, 64, C);
+  if (BWD) r |= make_tmap_3d(&tO, u_out, 2, D, rows, 1, D, 0, 64, C);
+  else r |= make_tmap_3d(&tO, o_out, 2, t_inner, rows * D / t_inner, 1, t_ld, 0, 64, C);
   if (r != 0) return 1000 + r;
   delta_scan_kernel<BWD><<<p.n_seq, 192, Smem<BWD>::TOTAL, st>>>(tW, tQ, tK, tM, tD, tXB, tU, tO,
                                                                  p);
@@ -407,19 +424,23 @@ using namespace pb;
 
 // Forward walk. All per-chunk tensors are row-major [(n_seq * n_chunks * 64), 128]
 // bf16 (M: [.., 64]), chunk g = seq * n_chunks + n occupying rows [64 g, 64 g + 64).
+// With heads > 0, Q, K and out (and dO in the backward walk) are instead token-major
+// [batch * n_chunks * 64, ld] with head h = seq % heads at columns [128 h, 128 h + 128).
 //   out   <- O            u_out <- U            xb_out[g] <- bf16(S entering chunk g)
 //   x_init / x_final: fp32 [n_seq, 128, 128] (x_init may be null = zero state)
 PB_API int pb_delta_scan_fwd(const void* W, const void* Uhat, const void* Q, const void* K,
                              const void* M, void* out, void* u_out, void* xb_out,
                              const void* x_init, void* x_final, int n_seq, int n_chunks,
-                             int* status, cudaStream_t st) {
-  if (n_seq <= 0 || n_chunks <= 0) return PB_BAD_ARG;
+                             int heads, int ld, int* status, cudaStream_t st) {
+  if (n_seq <= 0 || n_chunks <= 0 || heads < 0) return PB_BAD_ARG;
+  if (heads > 0 && (n_seq % heads != 0 || ld < heads * dscan::D || ld % 8 != 0)) return PB_BAD_ARG;
   dscan::Params p;
   p.n_chunks = n_chunks; p.n_seq = n_seq;
+  p.heads = heads; p.seq_len = n_chunks * dscan::C;
   p.x_init = static_cast<const float*>(x_init);
   p.x_final = static_cast<float*>(x_final);
   p.status = status;
-  return dscan::launch<false>(W, Q, K, M, Uhat, xb_out, u_out, out, p, st);
+  return dscan::launch<false>(W, Q, K, M, Uhat, xb_out, u_out, out, ld, p, st);
 }
 
 // Backward walk (chunks in reverse). x_init = gradient of the final state (or null),
@@ -428,13 +449,15 @@ PB_API int pb_delta_scan_fwd(const void* W, const void* Uhat, const void* Q, con
 //   x_final <- gradient of the initial state
 PB_API int pb_delta_scan_bwd(const void* W, const void* Q, const void* K, const void* M,
                              const void* dO, void* ndu_out, void* dxb_out, const void* x_init,
-                             void* x_final, int n_seq, int n_chunks, int* status,
-                             cudaStream_t st) {
-  if (n_seq <= 0 || n_chunks <= 0) return PB_BAD_ARG;
+                             void* x_final, int n_seq, int n_chunks, int heads, int ld,
+                             int* status, cudaStream_t st) {
+  if (n_seq <= 0 || n_chunks <= 0 || heads < 0) return PB_BAD_ARG;
+  if (heads > 0 && (n_seq % heads != 0 || ld < heads * dscan::D || ld % 8 != 0)) return PB_BAD_ARG;
   dscan::Params p;
   p.n_chunks = n_chunks; p.n_seq = n_seq;
+  p.heads = heads; p.seq_len = n_chunks * dscan::C;
   p.x_init = static_cast<const float*>(x_init);
   p.x_final = static_cast<float*>(x_final);
   p.status = status;
-  return dscan::launch<true>(W, Q, K, M, dO, dxb_out, ndu_out, nullptr, p, st);
+  return dscan::launch<true>(W, Q, K, M, dO, dxb_out, ndu_out, nullptr, ld, p, st);
 }

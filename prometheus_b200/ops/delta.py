@@ -151,83 +151,112 @@ class _BmmNN(torch.autograd.Function):
         return gemm(g, b), gemm(a, g, a_mn=True, b_mn=True)
 
 
-class _ScanFn(torch.autograd.Function):
-    """The sequential part on the tcgen05 scan kernels. Inputs are the per-chunk operands
-    ``[G, 64, 128]`` (M: ``[G, 64, 64]``), G = batch * heads * chunks."""
+def _to_chunks(x: Tensor, n: int) -> Tensor:
+    """[B, n*64, H, D] -> per-chunk [B*H*n, 64, D] (chunk g = (b*H + h)*n + i)."""
+    b, s, h, d = x.shape
+    return x.reshape(b, n, 64, h, d).permute(0, 3, 1, 2, 4).reshape(b * h * n, 64, d).contiguous()
+
+
+def _from_chunks(x: Tensor, b: int, h: int, n: int) -> Tensor:
+    d = x.shape[-1]
+    return x.reshape(b, h, n, 64, d).permute(0, 2, 3, 1, 4).reshape(b, n * 64, h, d)
+
+
+class _DeltaFusedFn(torch.autograd.Function):
+    """Delta rule, head dim 128, chunk 64, sequence a multiple of 64, on three kernels: the
+    chunk-local WY operands (``pb_delta_prep_fwd``), the forward state walk and the backward
+    state walk. q, k, v are read in place from their ``[B, S, H, 128]`` layout and the output
+    is written in that layout. The chunk-local part of the backward is batched tcgen05 GEMMs."""
 
     @staticmethod
-    def forward(ctx, w, uhat, qc, kc, m, s0, n_seq, n_chunks):
+    def forward(ctx, q, k, v, beta, s0):
         from ._lib import call, ptr, stream_ptr
         from .functional import status_word
 
-        dev = w.device
-        g = n_seq * n_chunks
-        out = torch.empty((g, 64, 128), dtype=torch.bfloat16, device=dev)
-        u = torch.empty_like(out)
-        sb = torch.empty((g, 128, 128), dtype=torch.bfloat16, device=dev)
-        sfin = torch.empty((n_seq, 128, 128), dtype=torch.float32, device=dev)
-        s0c = None if s0 is None else s0.float().contiguous()
-        call("pb_delta_scan_fwd", ptr(w), ptr(uhat), ptr(qc), ptr(kc), ptr(m), ptr(out), ptr(u),
-             ptr(sb), ptr(s0c), ptr(sfin), n_seq, n_chunks, ptr(status_word(dev)), stream_ptr())
-        ctx.save_for_backward(w, qc, kc, m, u, sb)
-        ctx.dims = (n_seq, n_chunks)
+        b, s, h, d = q.shape
+        n = s // 64
+        g = b * h * n
+        dev = q.device
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        beta = beta.contiguous()
+        bf = torch.bfloat16
+        w = torch.empty((g, 64, 128), dtype=bf, device=dev)
+        uhat = torch.empty_like(w)
+        m = torch.empty((g, 64, 64), dtype=bf, device=dev)
+        ap = torch.empty_like(m)
+        t = torch.empty_like(m)
+        status = ptr(status_word(dev))
+        call("pb_delta_prep_fwd", ptr(q), ptr(k), ptr(v), ptr(beta),
+             1 if beta.dtype == torch.float32 else 0, ptr(w), ptr(uhat), ptr(m), ptr(ap), ptr(t),
+             b, s, h, h * d, status, 0, stream_ptr())
+        out = torch.empty_like(q)
+        u = torch.empty_like(w)
+        sb = torch.empty((g, 128, 128), dtype=bf, device=dev)
+        sfin = torch.empty((b * h, 128, 128), dtype=torch.float32, device=dev)
+        s0c = None if s0 is None else s0.reshape(b * h, d, d).float().contiguous()
+        call("pb_delta_scan_fwd", ptr(w), ptr(uhat), ptr(q), ptr(k), ptr(m), ptr(out), ptr(u),
+             ptr(sb), ptr(s0c), ptr(sfin), b * h, n, h, h * d, status, stream_ptr())
+        ctx.save_for_backward(q, k, v, beta, w, m, ap, t, u, sb)
         ctx.has_s0 = s0 is not None
-        return out, sfin
+        return out, sfin.reshape(b, h, d, d)
 
     @staticmethod
     def backward(ctx, d_out, d_sfin):
         from ._lib import call, ptr, stream_ptr
         from .functional import gemm, status_word
 
-        w, qc, kc, m, u, sb = ctx.saved_tensors
-        n_seq, n_chunks = ctx.dims
-        dev = w.device
+        q, k, v, beta, w, m, ap, t, u, sb = ctx.saved_tensors
+        b, s, h, d = q.shape
+        n = s // 64
+        g = b * h * n
+        dev = q.device
         d_out = d_out.contiguous()
         ndu = torch.empty_like(u)          # the kernel writes -dU
         dsb = torch.empty_like(sb)
-        ds0 = torch.empty((n_seq, 128, 128), dtype=torch.float32, device=dev)
-        dfin = None if d_sfin is None else d_sfin.float().contiguous()
-        call("pb_delta_scan_bwd", ptr(w), ptr(qc), ptr(kc), ptr(m), ptr(d_out), ptr(ndu), ptr(dsb),
-             ptr(dfin), ptr(ds0), n_seq, n_chunks, ptr(status_word(dev)), stream_ptr())
-        du = -ndu
-        d_w = gemm(ndu, sb)                       # dW = -dU S^T
-        d_m = torch.tril(gemm(d_out, u))          # dM = tril(dO U^T)
-        d_q = gemm(d_out, sb)                     # dQ = dO S^T
-        d_k = gemm(u, dsb)                        # dK = U dS'^T
-        return d_w, du, d_q, d_k, d_m, (ds0 if ctx.has_s0 else None), None, None
+        ds0 = torch.empty((b * h, 128, 128), dtype=torch.float32, device=dev)
+        dfin = None if d_sfin is None else d_sfin.reshape(b * h, d, d).float().contiguous()
+        call("pb_delta_scan_bwd", ptr(w), ptr(q), ptr(k), ptr(m), ptr(d_out), ptr(ndu), ptr(dsb),
+             ptr(dfin), ptr(ds0), b * h, n, h, h * d, ptr(status_word(dev)), stream_ptr())
+        qc, kc, vc, doc = (_to_chunks(x, n) for x in (q, k, v, d_out))
+        bc = beta.float().reshape(b, n, 64, h).permute(0, 3, 1, 2).reshape(g, 64)
+        # through the state walk
+        d_w = gemm(ndu, sb)                                   # dW = -dU S^T
+        d_m = torch.tril(gemm(doc, u))                        # dM = tril(dO U^T)
+        d_q = gemm(doc, sb)                                   # dQ = dO S^T
+        d_k = gemm(u, dsb)                                    # dK = U dS'^T
+        # through W = A' K, U^ = A' V (dU^ = dU = -ndu)
+        dap = gemm(d_w, kc, out_dtype=torch.float32) - gemm(ndu, vc, out_dtype=torch.float32)
+        d_k += gemm(ap, d_w, a_mn=True, b_mn=True)            # A'^T dW
+        d_v = -gemm(ap, ndu, a_mn=True, b_mn=True)            # A'^T dU
+        # through A' = T diag(beta), T = (I + A)^-1, A = diag(beta) tril(K K^T, -1)
+        d_beta = (dap * t.float()).sum(dim=-2)
+        x = gemm(dap.to(torch.bfloat16), ap)                  # dA' A'^T
+        d_a = -gemm(t, x, a_mn=True, b_mn=True, out_dtype=torch.float32)   # -T^T (dA' A'^T)
+        gk = torch.tril(gemm(kc, kc, out_dtype=torch.float32), diagonal=-1)
+        d_beta += (d_a * gk).sum(dim=-1)
+        d_g = torch.tril(d_a * bc[:, :, None], diagonal=-1)
+        d_gs = (d_g + d_g.transpose(-1, -2)).to(torch.bfloat16)
+        d_k += gemm(d_gs, kc, b_mn=True)
+        # through M = tril(Q K^T)
+        d_q += gemm(d_m, kc, b_mn=True)
+        d_k += gemm(d_m, qc, a_mn=True, b_mn=True)
+        d_beta = d_beta.reshape(b, h, n, 64).permute(0, 2, 3, 1).reshape(b, s, h).to(beta.dtype)
+        return (_from_chunks(d_q, b, h, n), _from_chunks(d_k, b, h, n), _from_chunks(d_v, b, h, n),
+                d_beta, (ds0.reshape(b, h, d, d) if ctx.has_s0 else None))
 
 
 def delta_rule_fused(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tensor | None):
-    """Chunk-local WY operands with batched tcgen05 GEMMs (+ one batched triangular solve),
-    then the state walk on the scan kernels. bf16, head dim 128, chunk 64."""
-    b, s, h, d = q.shape
-    c = 64
-    pad = (-s) % c
+    """bf16, head dim 128, chunk 64 (sequences are zero-padded to a multiple of 64: padded
+    tokens have beta = 0 and k = 0, so they leave the state untouched)."""
+    s = q.shape[1]
+    pad = (-s) % 64
     if pad:
         q = torch.nn.functional.pad(q, (0, 0, 0, 0, 0, pad))
         k = torch.nn.functional.pad(k, (0, 0, 0, 0, 0, pad))
         v = torch.nn.functional.pad(v, (0, 0, 0, 0, 0, pad))
         beta = torch.nn.functional.pad(beta, (0, 0, 0, pad))
-    n = (s + pad) // c
-    g = b * h * n
-
-    def chunks(x):
-        return x.reshape(b, n, c, h, d).permute(0, 3, 1, 2, 4).reshape(g, c, d).contiguous()
-
-    qc, kc, vc = chunks(q), chunks(k), chunks(v)
-    bc = beta.float().reshape(b, n, c, h).permute(0, 3, 1, 2).reshape(g, c)
-    kk = _BmmNT.apply(kc, kc, True)
-    a = torch.tril(kk, diagonal=-1) * bc[:, :, None]
-    eye = torch.eye(c, dtype=torch.float32, device=q.device)
-    t = torch.linalg.solve_triangular(eye + a, eye.expand(g, c, c).contiguous(), upper=False)
-    ap = (t * bc[:, None, :]).to(q.dtype)                 # A' = T diag(beta)
-    w = _BmmNN.apply(ap, kc)
-    uhat = _BmmNN.apply(ap, vc)
-    m = torch.tril(_BmmNT.apply(qc, kc))
-    s0 = None if state is None else state.reshape(b * h, d, d)
-    out, sfin = _ScanFn.apply(w, uhat, qc, kc, m, s0, b * h, n)
-    out = out.reshape(b, h, n, c, d).permute(0, 2, 3, 1, 4).reshape(b, n * c, h, d)[:, :s]
-    return out, sfin.reshape(b, h, d, d)
+    out, sfin = _DeltaFusedFn.apply(q, k, v, beta, state)
+    return (out[:, :s] if pad else out), sfin
 
 
 def delta_rule(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tensor | None = None,
