@@ -43,6 +43,7 @@ _SIGS = {
     "pb_delta_scan_fwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
     "pb_delta_scan_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
     "pb_delta_prep_fwd": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, P, I, P],
+    "pb_delta_prep_bwd": [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, I, P],
     "pb_gemm_set_debug": [I],
     "pb_gemm_bf16": [P, P, P, P, I, I, I, I, L, L, L, L, L, L, L, L, I, I, I, I, F, F, P, I, P],
 }

@@ -217,32 +217,43 @@ class _DeltaFusedFn(torch.autograd.Function):
         dfin = None if d_sfin is None else d_sfin.reshape(b * h, d, d).float().contiguous()
         call("pb_delta_scan_bwd", ptr(w), ptr(q), ptr(k), ptr(m), ptr(d_out), ptr(ndu), ptr(dsb),
              ptr(dfin), ptr(ds0), b * h, n, h, h * d, ptr(status_word(dev)), stream_ptr())
-        qc, kc, vc, doc = (_to_chunks(x, n) for x in (q, k, v, d_out))
-        bc = beta.float().reshape(b, n, 64, h).permute(0, 3, 1, 2).reshape(g, 64)
-        # through the state walk
+        doc = _to_chunks(d_out, n)
         d_w = gemm(ndu, sb)                                   # dW = -dU S^T
-        d_m = torch.tril(gemm(doc, u))                        # dM = tril(dO U^T)
-        d_q = gemm(doc, sb)                                   # dQ = dO S^T
-        d_k = gemm(u, dsb)                                    # dK = U dS'^T
-        # through W = A' K, U^ = A' V (dU^ = dU = -ndu)
-        dap = gemm(d_w, kc, out_dtype=torch.float32) - gemm(ndu, vc, out_dtype=torch.float32)
-        d_k += gemm(ap, d_w, a_mn=True, b_mn=True)            # A'^T dW
-        d_v = -gemm(ap, ndu, a_mn=True, b_mn=True)            # A'^T dU
-        # through A' = T diag(beta), T = (I + A)^-1, A = diag(beta) tril(K K^T, -1)
-        d_beta = (dap * t.float()).sum(dim=-2)
-        x = gemm(dap.to(torch.bfloat16), ap)                  # dA' A'^T
-        d_a = -gemm(t, x, a_mn=True, b_mn=True, out_dtype=torch.float32)   # -T^T (dA' A'^T)
-        gk = torch.tril(gemm(kc, kc, out_dtype=torch.float32), diagonal=-1)
-        d_beta += (d_a * gk).sum(dim=-1)
-        d_g = torch.tril(d_a * bc[:, :, None], diagonal=-1)
-        d_gs = (d_g + d_g.transpose(-1, -2)).to(torch.bfloat16)
-        d_k += gemm(d_gs, kc, b_mn=True)
-        # through M = tril(Q K^T)
-        d_q += gemm(d_m, kc, b_mn=True)
-        d_k += gemm(d_m, qc, a_mn=True, b_mn=True)
-        d_beta = d_beta.reshape(b, h, n, 64).permute(0, 2, 3, 1).reshape(b, s, h).to(beta.dtype)
-        return (_from_chunks(d_q, b, h, n), _from_chunks(d_k, b, h, n), _from_chunks(d_v, b, h, n),
-                d_beta, (ds0.reshape(b, h, d, d) if ctx.has_s0 else None))
+        d_m = gemm(doc, u)                                    # dM = dO U^T (masked in the kernel)
+        d_qs = gemm(doc, sb)                                  # walk's dQ = dO S^T
+        d_ks = gemm(u, dsb)                                   # walk's dK = U dS'^T
+        d_q, d_k, d_v = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+        d_beta = torch.empty_like(beta)
+        call("pb_delta_prep_bwd", ptr(q), ptr(k), ptr(v), ptr(beta),
+             1 if beta.dtype == torch.float32 else 0, ptr(ap), ptr(t), ptr(d_w), ptr(ndu), ptr(d_m),
+             ptr(d_qs), ptr(d_ks), ptr(d_q), ptr(d_k), ptr(d_v), ptr(d_beta), b, s, h, h * d,
+             ptr(status_word(dev)), 0, stream_ptr())
+        return d_q, d_k, d_v, d_beta, (ds0.reshape(b, h, d, d) if ctx.has_s0 else None)
+
+
+def delta_prep_backward_ref(q, k, v, beta, ap, t, d_w, ndu, d_m, d_qs, d_ks):
+    """The chunk-local backward in batched fp32 PyTorch (oracle for ``pb_delta_prep_bwd``).
+    Per-chunk operands ``[G, 64, .]``; q, k, v, beta token-major. Returns dq, dk, dv, dbeta."""
+    b, s, h, d = q.shape
+    n = s // 64
+    g = b * h * n
+    qc, kc, vc = (_to_chunks(x, n).float() for x in (q, k, v))
+    bc = beta.float().reshape(b, n, 64, h).permute(0, 3, 1, 2).reshape(g, 64)
+    ap, t, d_w, ndu = ap.float(), t.float(), d_w.float(), ndu.float()
+    d_m = torch.tril(d_m.float())
+    dap = d_w @ kc.transpose(-1, -2) - ndu @ vc.transpose(-1, -2)
+    d_k = d_ks.float() + ap.transpose(-1, -2) @ d_w
+    d_v = -(ap.transpose(-1, -2) @ ndu)
+    d_beta = (dap * t).sum(dim=-2)
+    d_a = -(t.transpose(-1, -2) @ (dap @ ap.transpose(-1, -2)))
+    gk = torch.tril(kc @ kc.transpose(-1, -2), diagonal=-1)
+    d_beta = d_beta + (d_a * gk).sum(dim=-1)
+    d_g = torch.tril(d_a * bc[:, :, None], diagonal=-1)
+    d_k = d_k + (d_g + d_g.transpose(-1, -2)) @ kc + d_m.transpose(-1, -2) @ qc
+    d_q = d_qs.float() + d_m @ kc
+    d_beta = d_beta.reshape(b, h, n, 64).permute(0, 2, 3, 1).reshape(b, s, h)
+    return (_from_chunks(d_q, b, h, n), _from_chunks(d_k, b, h, n), _from_chunks(d_v, b, h, n),
+            d_beta)
 
 
 def delta_rule_fused(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tensor | None):

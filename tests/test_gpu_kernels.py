@@ -239,3 +239,48 @@ def test_delta_rule_fused_matches_recurrence(B, S, H):
         _close(a.grad, b.grad, 6e-2)
     _close(s0l.grad, s0r.grad, 6e-2)
     ops.check_status("cuda")
+
+
+def test_delta_prep_bwd_kernel_matches_fp32_oracle():
+    """The fused chunk-local backward against the same algebra in batched fp32 PyTorch."""
+    from prometheus_b200.ops import delta as dl
+    from prometheus_b200.ops import functional as ops
+    from prometheus_b200.ops._lib import call, ptr, stream_ptr
+
+    B, S, H, D = 2, 192, 3, 128
+    n = S // 64
+    G = B * H * n
+    q = torch.nn.functional.normalize(_r(B, S, H, D, seed=1).float(), dim=-1).to(BF16)
+    k = torch.nn.functional.normalize(_r(B, S, H, D, seed=2).float(), dim=-1).to(BF16)
+    v = _r(B, S, H, D, seed=3)
+    beta = torch.sigmoid(_r(B, S, H, seed=4).float()).to(BF16)
+    w, uh = torch.empty(G, 64, 128, dtype=BF16, device="cuda"), torch.empty(G, 64, 128, dtype=BF16, device="cuda")
+    m, ap, t = (torch.empty(G, 64, 64, dtype=BF16, device="cuda") for _ in range(3))
+    st = ptr(ops.status_word("cuda"))
+    call("pb_delta_prep_fwd", ptr(q), ptr(k), ptr(v), ptr(beta), 0, ptr(w), ptr(uh), ptr(m), ptr(ap),
+         ptr(t), B, S, H, H * D, st, 0, stream_ptr())
+    # forward operands against their definition
+    kc, vc, qc = (dl._to_chunks(x, n).float() for x in (k, v, q))
+    bc = beta.float().reshape(B, n, 64, H).permute(0, 3, 1, 2).reshape(G, 64)
+    a = torch.tril(kc @ kc.transpose(-1, -2), diagonal=-1) * bc[:, :, None]
+    eye = torch.eye(64, device="cuda")
+    t_ref = torch.linalg.solve_triangular(eye + a, eye.expand(G, 64, 64).contiguous(), upper=False)
+    _close(t, t_ref, 2e-2)
+    _close(ap, t_ref * bc[:, None, :], 2e-2)
+    _close(w, (t_ref * bc[:, None, :]) @ kc, 2e-2)
+    _close(uh, (t_ref * bc[:, None, :]) @ vc, 2e-2)
+    _close(m, torch.tril(qc @ kc.transpose(-1, -2)), 2e-2)
+    d_w, ndu, d_qs, d_ks = (_r(G, 64, 128, seed=10 + i, scale=0.5) for i in range(4))
+    d_m = _r(G, 64, 64, seed=20, scale=0.5)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    db = torch.empty_like(beta)
+    call("pb_delta_prep_bwd", ptr(q), ptr(k), ptr(v), ptr(beta), 0, ptr(ap), ptr(t), ptr(d_w),
+         ptr(ndu), ptr(d_m), ptr(d_qs), ptr(d_ks), ptr(dq), ptr(dk), ptr(dv), ptr(db), B, S, H, H * D,
+         st, 0, stream_ptr())
+    torch.cuda.synchronize()
+    ops.check_status("cuda")
+    rq, rk, rv, rb = dl.delta_prep_backward_ref(q, k, v, beta, ap, t, d_w, ndu, d_m, d_qs, d_ks)
+    _close(dq, rq, 3e-2)
+    _close(dk, rk, 3e-2)
+    _close(dv, rv, 3e-2)
+    _close(db, rb, 3e-2)
