@@ -1,0 +1,209 @@
+"""Checkpoint / resume for the GPU trainer on the native content-addressed store.
+
+A checkpoint is the reference's on-disk object (ckpt/src/lib.rs:28-59 of the reference): a
+``prometheus.checkpoint`` v1 manifest naming every weight shard and optimizer shard by
+sha256, plus the shard blobs. ``capture`` turns a live :class:`~prometheus_b200.engine.Trainer`
+into one (fp32 masters per engine weight; Muon momentum or AdamW moments per weight; the step
+count; the data-loader envelope), ``apply`` puts one back, and :class:`TrainerCheckpointer`
+drives the native ``Checkpointer`` (two in-memory replicas every step, persistent saves on a
+background thread, cross-rack copies) the way the reference's train loop is specified to
+(ckpt/src/lib.rs:427-526, 617-673).
+
+With ownership sharding (world > 1) each rank only keeps its own matrices' masters and
+optimizer state current. ``capture`` therefore first sums the owned ranges across ranks, so
+every rank holds the full state and rank 0's checkpoint is complete; ``apply`` loads the
+full state on every rank. Restoring is bit-exact: blobs are the raw little-endian buffers.
+"""
+from __future__ import annotations
+
+import datetime as _dt
+import hashlib
+import json
+import math
+from typing import Any
+
+import torch
+
+from . import native
+
+ZERO_HASH = "0" * 64
+
+
+def _ck():
+    return native.ckpt
+
+
+def model_config_hash(cfg) -> str:
+    """sha256 of the canonical (sorted-key, compact) JSON of the model configuration."""
+    from dataclasses import asdict, is_dataclass
+
+    d = asdict(cfg) if is_dataclass(cfg) else dict(cfg)
+    d = {k: (v.name if hasattr(v, "name") and not isinstance(v, (str, int, float)) else v)
+         for k, v in d.items()}
+    return hashlib.sha256(json.dumps(d, sort_keys=True, separators=(",", ":"),
+                                     default=str).encode()).hexdigest()
+
+
+def _bytes(t: torch.Tensor) -> bytes:
+    return t.detach().contiguous().cpu().numpy().tobytes()
+
+
+def _full_state(tr) -> dict[str, torch.Tensor]:
+    """All flat fp32 state buffers, complete on every rank."""
+    bufs = {"muon.master": tr.muon_master, "muon.mom": tr.muon_mom,
+            "adam.master": tr.adam_master, "adam.m": tr.adam_m, "adam.v": tr.adam_v,
+            "vec.master": tr.vec_master, "vec.m": tr.vec_m, "vec.v": tr.vec_v}
+    if getattr(tr, "sym", None) is None:
+        return bufs
+    import torch.distributed as dist
+
+    out = dict(bufs)
+    ranges = []
+    for (rows, cols), units in tr.unit_classes.items():
+        lo_u, hi_u = tr.own_units[(rows, cols)]
+        ranges.append((units[0].off + lo_u * rows * cols, units[0].off + hi_u * rows * cols))
+    for key in ("muon.master", "muon.mom"):
+        full = torch.zeros_like(bufs[key])
+        for lo, hi in ranges:
+            full[lo:hi] = bufs[key][lo:hi]
+        dist.all_reduce(full, group=tr.pg)
+        out[key] = full
+    a_lo, a_hi = tr.own_adam
+    for key in ("adam.master", "adam.m", "adam.v"):
+        full = torch.zeros_like(bufs[key])
+        full[a_lo:a_hi] = bufs[key][a_lo:a_hi]
+        dist.all_reduce(full, group=tr.pg)
+        out[key] = full
+    return out
+
+
+def capture(tr, *, rung: int = 0, data_mix_hash: str = ZERO_HASH, tokenizer_id: str = "byte-fallback",
+            loader_state: dict | None = None, parent: str | None = None,
+            created_at: str | None = None, git_commit: str | None = None):
+    """Snapshot a Trainer into a native ``Checkpoint`` (collective when world > 1)."""
+    C = _ck()
+    state = _full_state(tr)
+    weights, opt, wmeta, ometa = [], [], [], []
+    for w in tr.weights.values():
+        n = int(math.prod(w.shape))
+        sl = slice(w.off, w.off + n)
+        g = w.group
+        blob = _bytes(state[f"{g}.master"][sl])
+        weights.append(C.ShardBlob(w.name, 0, blob))
+        wmeta.append(C.WeightMeta(w.name, 0, list(w.shape), "fp32", C.sha256_hex(blob), []))
+        if g == "muon":
+            parts = [("mom", "muon", state["muon.mom"][sl])]
+        else:
+            parts = [("m", "adamw", state[f"{g}.m"][sl]), ("v", "adamw", state[f"{g}.v"][sl])]
+        for suffix, kind, t in parts:
+            ob = _bytes(t)
+            opt.append(C.ShardBlob(f"{w.name}.{suffix}", 0, ob))
+            ometa.append(C.OptimizerMeta(f"{w.name}.{suffix}", 0, kind, C.sha256_hex(ob)))
+    m = C.Manifest()
+    m.step = int(tr.step_count)
+    m.rung = int(rung)
+    m.model_config_hash = model_config_hash(tr.cfg)
+    m.data_mix_hash = data_mix_hash
+    m.tokenizer_id = tokenizer_id
+    m.precision = ("bf16", "none")
+    m.dp = int(tr.world)
+    m.weights, m.optimizer = wmeta, ometa
+    if loader_state is not None:
+        m.loader_state_json = json.dumps(loader_state, sort_keys=True, separators=(",", ":"))
+    rng = [("torch.cpu", torch.get_rng_state())]
+    if torch.cuda.is_available():
+        rng.append(("torch.cuda", torch.cuda.get_rng_state(tr.device)))
+    m.rng = [C.RngState(scope, int(tr.rank), hashlib.sha256(_bytes(s)).hexdigest()) for scope, s in rng]
+    m.created_at = created_at or _dt.datetime.now(_dt.timezone.utc).strftime("%Y-%m-%dT%H:%M:%SZ")
+    m.parent_checkpoint_id = parent
+    m.git_commit = git_commit
+    ident = hashlib.sha256()
+    for x in wmeta:
+        ident.update(x.content_hash.encode())
+    for x in ometa:
+        ident.update(x.content_hash.encode())
+    ident.update(str(m.step).encode())
+    m.checkpoint_id = ident.hexdigest()
+    return C.Checkpoint(m, weights, opt)
+
+
+def apply(tr, ckpt, *, strict_config: bool = True) -> dict[str, Any] | None:
+    """Load a checkpoint into a Trainer (same model configuration). Returns the data-loader
+    envelope stored with it (or None)."""
+    m = ckpt.manifest
+    if strict_config and m.model_config_hash != model_config_hash(tr.cfg):
+        raise ValueError("checkpoint was written for a different model configuration")
+    wb = {b.name: b.bytes for b in ckpt.weights}
+    ob = {b.name: b.bytes for b in ckpt.optimizer}
+    dev = tr.device
+
+    def put(dst: torch.Tensor, raw: bytes, what: str):
+        if len(raw) != dst.numel() * 4:
+            raise ValueError(f"{what}: {len(raw)} bytes for {dst.numel()} fp32 values")
+        src = torch.frombuffer(bytearray(raw), dtype=torch.float32)
+        dst.copy_(src.to(dev))
+
+    with torch.no_grad():
+        for w in tr.weights.values():
+            n = int(math.prod(w.shape))
+            sl = slice(w.off, w.off + n)
+            g = w.group
+            master = {"muon": tr.muon_master, "adam": tr.adam_master, "vec": tr.vec_master}[g]
+            put(master[sl], wb[w.name], w.name)
+            if g == "muon":
+                put(tr.muon_mom[sl], ob[w.name + ".mom"], w.name + ".mom")
+            else:
+                mm, vv = (tr.adam_m, tr.adam_v) if g == "adam" else (tr.vec_m, tr.vec_v)
+                put(mm[sl], ob[w.name + ".m"], w.name + ".m")
+                put(vv[sl], ob[w.name + ".v"], w.name + ".v")
+        tr.muon_lp.copy_(tr.muon_master)
+        tr.adam_lp.copy_(tr.adam_master)
+    tr.step_count = int(m.step)
+    if getattr(tr, "sym", None) is not None:
+        torch.cuda.synchronize()
+        torch.distributed.barrier(tr.pg)
+    raw = getattr(m, "loader_state_json", "")
+    return json.loads(raw) if raw and raw != "{}" else None
+
+
+class TrainerCheckpointer:
+    """The save policy of the reference's train loop on the native ``Checkpointer``: an
+    in-memory checkpoint (two replicas) whenever asked, a persistent one written by a
+    background thread so the step loop never waits on the file system, and restore by id or
+    from the newest in-memory replica."""
+
+    def __init__(self, root: str | None = None, *, racks: list[str] | None = None):
+        C = _ck()
+        self.store = C.DirStore(root) if root is not None else C.MemoryStore()
+        self.cp = C.Checkpointer(self.store)
+        self.racks = racks
+        self.pending = None
+        self.last_id: str | None = None
+
+    def save_memory(self, tr, **kw) -> str:
+        ck = capture(tr, parent=self.last_id, **kw)
+        if tr.rank == 0:
+            self.last_id = self.cp.save_in_memory(ck)
+        else:
+            self.last_id = ck.manifest.checkpoint_id
+        return self.last_id
+
+    def save_persistent(self, tr, *, wait: bool = False, **kw) -> str:
+        ck = capture(tr, parent=self.last_id, **kw)
+        self.last_id = ck.manifest.checkpoint_id
+        if tr.rank == 0:
+            self.wait()
+            self.pending = self.cp.save_persistent_async(ck)
+            if wait:
+                self.wait()
+        return self.last_id
+
+    def wait(self) -> None:
+        if self.pending is not None:
+            self.pending.wait()
+            self.pending = None
+
+    def restore(self, tr, checkpoint_id: str | None = None):
+        self.wait()
+        ck = self.cp.restore(checkpoint_id) if checkpoint_id else self.cp.restore_latest_memory()
+        return apply(tr, ck)

@@ -1,0 +1,68 @@
+"""Trainer <-> native checkpoint bridge on CPU, with a stand-in for the GPU trainer that has
+the same flat-buffer layout."""
+import types
+
+import pytest
+import torch
+
+from prometheus_b200 import checkpoint, model
+
+
+def _fake_trainer(seed):
+    g = torch.Generator().manual_seed(seed)
+    W = types.SimpleNamespace
+    weights = {
+        "layers.0.q": W(name="layers.0.q", shape=(4, 6), group="muon", off=0),
+        "layers.0.o": W(name="layers.0.o", shape=(6, 4), group="muon", off=24),
+        "embed": W(name="embed", shape=(8, 4), group="adam", off=0),
+        "final_norm": W(name="final_norm", shape=(4,), group="vec", off=0),
+    }
+    r = lambda n: torch.randn(n, generator=g)
+    tr = W(weights=weights, cfg=model.tiny_config(), device=torch.device("cpu"), world=1, rank=0,
+           sym=None, step_count=7,
+           muon_master=r(48), muon_mom=r(48), adam_master=r(32), adam_m=r(32), adam_v=r(32).abs(),
+           vec_master=r(4), vec_m=r(4), vec_v=r(4).abs(),
+           muon_lp=torch.zeros(48, dtype=torch.bfloat16), adam_lp=torch.zeros(32, dtype=torch.bfloat16))
+    return tr
+
+
+def test_capture_apply_roundtrip_and_manifest(tmp_path):
+    a, b = _fake_trainer(0), _fake_trainer(1)
+    ck = checkpoint.capture(a, loader_state={"epoch": 1, "cursor": 5}, created_at="2026-01-01T00:00:00Z")
+    m = ck.manifest
+    assert m.step == 7 and len(m.checkpoint_id) == 64
+    assert [w.name for w in m.weights] == list(a.weights)
+    assert {o.name: o.kind for o in m.optimizer} == {
+        "layers.0.q.mom": "muon", "layers.0.o.mom": "muon", "embed.m": "adamw", "embed.v": "adamw",
+        "final_norm.m": "adamw", "final_norm.v": "adamw"}
+    # same state -> same id; different state -> different id
+    assert checkpoint.capture(a, created_at="x").manifest.checkpoint_id == m.checkpoint_id
+    assert checkpoint.capture(b).manifest.checkpoint_id != m.checkpoint_id
+    saver = checkpoint.TrainerCheckpointer(str(tmp_path / "s"))
+    cid = saver.save_persistent(a, wait=True, loader_state={"epoch": 1, "cursor": 5})
+    assert cid == m.checkpoint_id
+    assert saver.restore(b, cid) == {"cursor": 5, "epoch": 1}
+    for name in ("muon_master", "muon_mom", "adam_master", "adam_m", "adam_v", "vec_master", "vec_m",
+                 "vec_v"):
+        assert torch.equal(getattr(a, name), getattr(b, name)), name
+    assert b.step_count == 7
+    assert torch.equal(b.muon_lp, a.muon_master.to(torch.bfloat16))
+    # in-memory path
+    c = _fake_trainer(2)
+    saver.save_memory(a)
+    saver.restore(c)
+    assert torch.equal(c.adam_v, a.adam_v)
+
+
+def test_apply_rejects_other_model_and_bad_sizes():
+    a = _fake_trainer(0)
+    ck = checkpoint.capture(a)
+    other = _fake_trainer(0)
+    other.cfg = model.with_overrides(model.tiny_config(), vocab_size=512)
+    with pytest.raises(ValueError):
+        checkpoint.apply(other, ck)
+    short = _fake_trainer(0)
+    short.weights["embed"].shape = (9, 4)
+    short.adam_master = torch.zeros(36)
+    with pytest.raises(ValueError):
+        checkpoint.apply(short, ck)

@@ -61,3 +61,34 @@ def test_engine_overfits_fixed_batch():
     assert losses[-1] < losses[0] - 0.5, losses
     from prometheus_b200.ops import functional as ops
     ops.check_status("cuda")
+
+
+def test_checkpoint_resume_is_bitwise(tmp_path):
+    """Train 2 steps, checkpoint through the native store, train 2 more; a fresh Trainer
+    restored from the checkpoint reproduces the last two steps bit for bit."""
+    from prometheus_b200 import checkpoint, engine, model, train
+
+    cfg = small_hybrid()
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=10, decay_steps=2)
+    toks = [torch.randint(0, cfg.vocab_size, (2, 128), generator=torch.Generator().manual_seed(s)).cuda()
+            for s in range(4)]
+    a = engine.Trainer(cfg, tcfg, seed=3, device="cuda", micro_batch=2)
+    for t in toks[:2]:
+        a.step(t)
+    saver = checkpoint.TrainerCheckpointer(str(tmp_path / "store"))
+    cid = saver.save_persistent(a, wait=True, loader_state={"epoch": 0, "cursor": 2})
+    mem_id = saver.save_memory(a)
+    assert cid == mem_id and len(cid) == 64
+    losses_a = [float(a.step(t)["loss"]) for t in toks[2:]]
+    b = engine.Trainer(cfg, tcfg, seed=99, device="cuda", micro_batch=2)   # different init
+    fresh = checkpoint.TrainerCheckpointer(str(tmp_path / "store"))
+    loader_state = fresh.restore(b, cid)
+    assert loader_state == {"cursor": 2, "epoch": 0} and b.step_count == 2
+    losses_b = [float(b.step(t)["loss"]) for t in toks[2:]]
+    assert losses_a == losses_b
+    for name in ("muon_master", "muon_mom", "adam_master", "adam_m", "adam_v", "vec_master"):
+        assert torch.equal(getattr(a, name), getattr(b, name)), name
+    with pytest.raises(ValueError):
+        other = model.with_overrides(cfg, vocab_size=cfg.vocab_size * 2)
+        checkpoint.apply(engine.Trainer(other, tcfg, seed=0, device="cuda", micro_batch=2),
+                         fresh.cp.restore(cid))
