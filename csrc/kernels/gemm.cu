@@ -37,6 +37,14 @@ struct GemmParams {
   int tma_store;  // epilogue stages tiles in shared memory and stores them with TMA
   int debug;  // bit 1: skip the epilogue's global stores (timing experiments only)
   int* status;
+  // Grouped modes (both null for the plain GEMM):
+  //  mblk_group[m_blk]: rows of A / C are grouped (128-aligned) and row block m_blk multiplies
+  //    batch entry mblk_group[m_blk] of B (negative: the block is padding and is skipped).
+  //  k_off / k_len[b]: batch entry b contracts over rows [k_off[b], k_off[b] + k_len[b]) of the
+  //    two MN-major operands, which are shared by all entries (k_len a multiple of 64; 0 skips).
+  const int* mblk_group;
+  const int* k_off;
+  const int* k_len;
 };
 
 template <int BN>
@@ -107,6 +115,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     m_blk = first_m + (r % group) % gsz;
     n_blk = (r % group) / gsz;
   };
+  // operand batch indices, first contraction row and contraction blocks of a tile
+  auto tile_group = [&](int b, int m_blk, int& b_a, int& b_b, int& k_base, int& nkb) {
+    b_a = b; b_b = b; k_base = 0; nkb = num_kb;
+    if (p.mblk_group != nullptr) {
+      b_b = p.mblk_group[m_blk];
+      return b_b >= 0;
+    }
+    if (p.k_len != nullptr) {
+      b_a = b_b = 0;
+      k_base = p.k_off[b];
+      nkb = p.k_len[b] / BK;
+      return nkb > 0;
+    }
+    return true;
+  };
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -118,25 +141,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int b, m_blk, n_blk;
         tile_coords(t, b, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int b_a, b_b, k_base, nkb;
+        if (!tile_group(b, m_blk, b_a, b_b, k_base, nkb)) continue;
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, p.status)) { ok = false; break; }
           mbar_arrive_expect_tx(&full[s], S::STAGE_BYTES);
           uint8_t* a_dst = smA + s * S::A_BYTES;
           uint8_t* b_dst = smB + s * S::B_BYTES;
-          const int k0 = kb * BK;
+          const int k0 = k_base + kb * BK;
           if (!p.a_mn) {
-            tma_load_3d(a_dst, &tmA, &full[s], k0, m0, b);
+            tma_load_3d(a_dst, &tmA, &full[s], k0, m0, b_a);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
-              tma_load_3d(a_dst + c * 8192, &tmA, &full[s], m0 + c * 64, k0, b);
+              tma_load_3d(a_dst + c * 8192, &tmA, &full[s], m0 + c * 64, k0, b_a);
           }
           if (!p.b_mn) {
-            tma_load_3d(b_dst, &tmB, &full[s], k0, n0, b);
+            tma_load_3d(b_dst, &tmB, &full[s], k0, n0, b_b);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_3d(b_dst + c * 8192, &tmB, &full[s], n0 + c * 64, k0, b);
+              tma_load_3d(b_dst + c * 8192, &tmB, &full[s], n0 + c * 64, k0, b_b);
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -152,10 +177,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t acc_ph = 0;
       bool ok = true;
       for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int nkb = num_kb;
+        if (p.mblk_group != nullptr || p.k_len != nullptr) {
+          int b, m_blk, n_blk, b_a, b_b, k_base;
+          tile_coords(t, b, m_blk, n_blk);
+          if (!tile_group(b, m_blk, b_a, b_b, k_base, nkb)) continue;
+        }
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&full[s], ph, p.status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smA + s * S::A_BYTES);
@@ -189,6 +220,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tile_coords(t, b, m_blk, n_blk);
       const int row = m_blk * BM + q * 32 + lane;
       const int n0 = n_blk * BN;
+      {
+        int b_a, b_b, k_base, nkb;
+        if (!tile_group(b, m_blk, b_a, b_b, k_base, nkb)) continue;
+      }
       if (!mbar_wait(&tfull[acc], acc_ph, p.status)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
@@ -464,29 +499,80 @@ PB_API int pb_gemm_set_debug(int flags) {
 // Strides are in elements. Base pointers 16-byte aligned, lda/ldb multiples of 8.
 // `status` (device int, may be null) latches a non-zero code if a bounded wait ran out.
 // `max_ctas` > 0 limits the persistent grid (leaves SMs for a concurrent kernel).
+static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M, int N, int K,
+                     int batch, long lda, long ldb, long ldc, long ldd, long strideA,
+                     long strideB, long strideC, long strideD, int a_mn, int b_mn, int out_f32,
+                     int d_f32, float alpha, float beta, int* status, int max_ctas,
+                     cudaStream_t st, const int* mblk_group, int b_batch, const int* k_off,
+                     const int* k_len);
+
 PB_API int pb_gemm_bf16(const void* A, const void* B, void* C, const void* D, int M, int N, int K,
                         int batch, long lda, long ldb, long ldc, long ldd, long strideA,
                         long strideB, long strideC, long strideD, int a_mn, int b_mn, int out_f32,
                         int d_f32, float alpha, float beta, int* status, int max_ctas,
                         cudaStream_t st) {
+  return gemm_impl(A, B, C, D, M, N, K, batch, lda, ldb, ldc, ldd, strideA, strideB, strideC,
+                   strideD, a_mn, b_mn, out_f32, d_f32, alpha, beta, status, max_ctas, st, nullptr,
+                   0, nullptr, nullptr);
+}
+
+// Grouped product for mixture-of-experts layers: C[rows of block m] = A[rows] * B[g(m)]^T,
+// A [M, K] and C [M, N] with their rows grouped by expert in 128-row blocks, B [groups, N, K]
+// (or [groups, K, N] with b_mn); mblk_group (device, one int per 128-row block) names the
+// group of each block, negative = padding block, skipped (its C rows are left untouched).
+PB_API int pb_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, int N, int K,
+                                int groups, long lda, long ldb, long ldc, long strideB, int b_mn,
+                                const int* mblk_group, int* status, int max_ctas,
+                                cudaStream_t st) {
+  if (groups <= 0 || mblk_group == nullptr) return PB_BAD_ARG;
+  return gemm_impl(A, B, C, nullptr, M, N, K, 1, lda, ldb, ldc, 0, 0, strideB, 0, 0, 0, b_mn, 0, 0,
+                   1.f, 0.f, status, max_ctas, st, mblk_group, groups, nullptr, nullptr);
+}
+
+// Grouped weight gradient: for every group g, C[g] (+)= A[rows_g]^T * B[rows_g] where
+// rows_g = [k_off[g], k_off[g] + k_len[g]) of the row-grouped A [R, M] and B [R, N] (k_len a
+// multiple of 64, device arrays). C, D: [groups, M, N]; beta = 1 with D = C accumulates.
+// Groups with k_len 0 are skipped (C left untouched).
+PB_API int pb_gemm_bf16_grouped_wgrad(const void* A, const void* B, void* C, const void* D, int M,
+                                      int N, int R, int groups, long lda, long ldb, long ldc,
+                                      long strideC, int out_f32, int d_f32, float beta,
+                                      const int* k_off, const int* k_len, int* status,
+                                      int max_ctas, cudaStream_t st) {
+  if (groups <= 0 || k_off == nullptr || k_len == nullptr) return PB_BAD_ARG;
+  return gemm_impl(A, B, C, D, M, N, R, groups, lda, ldb, ldc, ldc, 0, 0, strideC, strideC, 1, 1,
+                   out_f32, d_f32, 1.f, beta, status, max_ctas, st, nullptr, 0, k_off, k_len);
+}
+
+static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M, int N, int K,
+                     int batch, long lda, long ldb, long ldc, long ldd, long strideA,
+                     long strideB, long strideC, long strideD, int a_mn, int b_mn, int out_f32,
+                     int d_f32, float alpha, float beta, int* status, int max_ctas,
+                     cudaStream_t st, const int* mblk_group, int b_batch, const int* k_off,
+                     const int* k_len) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return PB_BAD_ARG;
   if ((lda % 8) != 0 || (ldb % 8) != 0) return PB_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return PB_BAD_ARG;
-  if (batch > 1 && ((strideA % 8) != 0 || (strideB % 8) != 0)) return PB_BAD_ARG;
+  if (batch > 1 && k_len == nullptr && ((strideA % 8) != 0 || (strideB % 8) != 0))
+    return PB_BAD_ARG;
+  // operand batch counts: shared 2-D operands in the grouped weight gradient, per-group B
+  // in the grouped forward product
+  const int batch_a = (k_len != nullptr) ? 1 : batch;
+  const int batch_b = (k_len != nullptr) ? 1 : (mblk_group != nullptr ? b_batch : batch);
+  if (mblk_group != nullptr && (strideB % 8) != 0) return PB_BAD_ARG;
   const bool bn256 = N > 128 && !(g_gemm_debug & 1);
   const int BN = bn256 ? 256 : 128;
   CUtensorMap tmA, tmB;
   int r;
   if (!a_mn)
-    r = make_tmap_3d(&tmA, A, 2, K, M, batch, lda, strideA, BK, BM);
+    r = make_tmap_3d(&tmA, A, 2, K, M, batch_a, lda, strideA, BK, BM);
   else
-    r = make_tmap_3d(&tmA, A, 2, M, K, batch, lda, strideA, 64, BK);
+    r = make_tmap_3d(&tmA, A, 2, M, K, batch_a, lda, strideA, 64, BK);
   if (r != 0) return 1000 + r;
   if (!b_mn)
-    r = make_tmap_3d(&tmB, B, 2, K, N, batch, ldb, strideB, BK, BN);
+    r = make_tmap_3d(&tmB, B, 2, K, N, batch_b, ldb, strideB, BK, BN);
   else
-    r = make_tmap_3d(&tmB, B, 2, N, K, batch, ldb, strideB, 64, BK);
+    r = make_tmap_3d(&tmB, B, 2, N, K, batch_b, ldb, strideB, 64, BK);
   if (r != 0) return 2000 + r;
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.batch = batch;
@@ -497,6 +583,7 @@ PB_API int pb_gemm_bf16(const void* A, const void* B, void* C, const void* D, in
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.status = status;
   p.debug = g_gemm_debug;
+  p.mblk_group = mblk_group; p.k_off = k_off; p.k_len = k_len;
   // TMA-store epilogue when the output rows are 16-byte aligned; else direct stores.
   const int cbytes = out_f32 ? 4 : 2;
   CUtensorMap tmC = tmA;

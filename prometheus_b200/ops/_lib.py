@@ -44,6 +44,15 @@ _SIGS = {
     "pb_delta_scan_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
     "pb_delta_prep_fwd": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, P, I, P],
     "pb_delta_prep_bwd": [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, I, P],
+    "pb_gemm_bf16_grouped": [P, P, P, I, I, I, I, L, L, L, L, I, P, P, I, P],
+    "pb_gemm_bf16_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, L, L, I, I, F, P, P, P, I, P],
+    "pb_moe_route": [P, P, I, I, I, P, P, P, P],
+    "pb_moe_route_bwd": [P, P, P, P, I, I, I, P, P],
+    "pb_moe_sort_nblocks": [I, I],
+    "pb_moe_sort": [P, I, I, I, P, P, P, P, P, P, I, P],
+    "pb_moe_permute": [P, P, P, I, I, I, L, P, P, P, I, P],
+    "pb_moe_combine": [P, P, P, P, I, I, I, P, P],
+    "pb_moe_combine_bwd": [P, P, P, I, I, I, P, P],
     "pb_gemm_set_debug": [I],
     "pb_gemm_bf16": [P, P, P, P, I, I, I, I, L, L, L, L, L, L, L, L, I, I, I, I, F, F, P, I, P],
 }
