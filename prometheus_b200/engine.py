@@ -83,7 +83,8 @@ class _EmbedFn(torch.autograd.Function):
 
 
 class Trainer:
-    """Single-process-per-GPU trainer for the dense hybrid configurations."""
+    """Single-process-per-GPU trainer for the hybrid configurations: delta-rule and GQA
+    attention layers, dense SwiGLU or mixture-of-experts (routed + shared) FFNs."""
 
     def __init__(self, model_config: M.ModelConfig, train_config: T.TrainConfig, *,
                  params: dict | None = None, seed: int = 0, device="cuda", micro_batch: int = 4,
@@ -91,8 +92,6 @@ class Trainer:
                  grad_sync: str = "auto"):
         M.validate_config(model_config)
         T.validate_train_config(train_config)
-        if model_config.n_moe != 0:
-            raise NotImplementedError("MoE layers run through prometheus_b200.parallel.ep")
         self.cfg, self.tcfg = model_config, train_config
         self.device = torch.device(device)
         self.micro_batch = int(micro_batch)
@@ -108,6 +107,9 @@ class Trainer:
         self.ce_chunk_rows = int(ce_chunk_rows)
         self.step_count = 0
         self.launches = 0
+        self.router_bias: dict[int, Tensor] = {}
+        self.router_bias_rate = 1e-3
+        self.last_router = None
         _lib.load()
         if params is None:
             params = M.init_params(model_config, seed)
@@ -147,6 +149,7 @@ class Trainer:
                          sources=[("unembed", 0, cfg.vocab_size, None, None)]))
         vec("final_norm", d, "final_norm")
         self.layer_kinds = []
+        self.moe_layers: list[int] = []
         for i in range(cfg.n_layers):
             p = f"layers.{i}."
             kind = M.attention_kind(i, cfg)
@@ -162,10 +165,27 @@ class Trainer:
             if kind is M.AttentionKind.LINEAR and cfg.delta_beta == "sigmoid":
                 mat(p + "beta", (nh, d), [src(p + "W_beta", 0, nh)])
             mat(p + "o", (d, nh * dh), [(p + "W_o", 0, d, "o", None)])
-            hid = cfg.dense_hidden if cfg.dense_hidden is not None else cfg.expert_hidden
-            mat(p + "gate_up", (2 * hid, d),
-                [src(p + "ffn_gate", 0, hid), src(p + "ffn_up", hid, hid)], unit_rows=[hid, hid])
-            mat(p + "down", (d, hid), [src(p + "ffn_down", 0, d)])
+            if M.ffn_kind(i, cfg) is M.FfnKind.DENSE:
+                hid = cfg.dense_hidden if cfg.dense_hidden is not None else cfg.expert_hidden
+                mat(p + "gate_up", (2 * hid, d),
+                    [src(p + "ffn_gate", 0, hid), src(p + "ffn_up", hid, hid)],
+                    unit_rows=[hid, hid])
+                mat(p + "down", (d, hid), [src(p + "ffn_down", 0, d)])
+            else:
+                # routed experts followed by the shared experts (always-on, gate 1), all the
+                # same shape: one grouped product covers both
+                n_r, n_s, hid = cfg.n_routed_experts, cfg.n_shared_experts, cfg.expert_hidden
+                self.moe_layers.append(i)
+                mat(p + "router", (n_r, d), [src(p + "router", 0, n_r)])
+                gu_src, dn_src = [], []
+                for e in range(n_r + n_s):
+                    kind_, idx = ("routed", e) if e < n_r else ("shared", e - n_r)
+                    gu_src.append((p + kind_ + "_gate", 2 * e * hid, hid, ("e", idx), None))
+                    gu_src.append((p + kind_ + "_up", (2 * e + 1) * hid, hid, ("e", idx), None))
+                    dn_src.append((p + kind_ + "_down", e * d, d, ("e", idx), None))
+                mat(p + "moe_gu", (2 * hid * (n_r + n_s), d), gu_src,
+                    unit_rows=[hid] * (2 * (n_r + n_s)))
+                mat(p + "moe_down", (d * (n_r + n_s), hid), dn_src, unit_rows=[d] * (n_r + n_s))
         self.weights = {w.name: w for w in ws}
         # Muon flat layout: units grouped by (rows, cols) so each class is one batched NS.
         classes: dict[tuple, list[Unit]] = {}
@@ -276,6 +296,8 @@ class Trainer:
     # ------------------------------------------------------------ tree <-> flat
     @staticmethod
     def _to_engine(t: Tensor, how) -> Tensor:
+        if isinstance(how, tuple):          # ("e", index): one expert of a stacked tensor
+            return _t2(t[how[1]])
         if how == "t2":
             return _t2(t)
         if how == "o":
@@ -293,6 +315,13 @@ class Trainer:
                     dst[r0:r0 + rows].copy_(src.to(self.device))
             self.muon_lp.copy_(self.muon_master)
             self.adam_lp.copy_(self.adam_master)
+            self.router_bias = {}
+            for i in self.moe_layers:
+                name = f"layers.{i}.router_bias"
+                if self.cfg.router_bias:
+                    b = flat.get(name)
+                    self.router_bias[i] = (torch.zeros(self.cfg.n_routed_experts)
+                                           if b is None else b.detach().float().clone()).to(self.device)
         if self.sym is not None:
             torch.cuda.synchronize()
             torch.distributed.barrier(self.pg)
@@ -324,11 +353,15 @@ class Trainer:
         nh, dh, nkv = M.head_geometry(cfg)
         out: dict[str, Tensor] = {}
         full = self.gather_masters()
+        stacked: dict[str, dict[int, Tensor]] = {}
         for w in self.weights.values():
             n = int(math.prod(w.shape))
             src = full[w.group][w.off:w.off + n].view(w.shape).cpu()
             for tree_name, r0, rows, how, _ in w.sources:
                 blk = src[r0:r0 + rows]
+                if isinstance(how, tuple):
+                    stacked.setdefault(tree_name, {})[how[1]] = blk.t().contiguous()
+                    continue
                 if how == "t2":
                     t = blk.t().contiguous()
                     leaf = tree_name.split(".")[-1]
@@ -339,6 +372,10 @@ class Trainer:
                 else:
                     t = blk.clone()
                 out[tree_name] = t
+        for tree_name, parts in stacked.items():
+            out[tree_name] = torch.stack([parts[j] for j in range(len(parts))])
+        for i, b in self.router_bias.items():
+            out[f"layers.{i}.router_bias"] = b.detach().cpu().clone()
         return M.unflatten_params(out)
 
     # ------------------------------------------------------------------ forward
@@ -360,6 +397,21 @@ class Trainer:
         o, _ = kernels.chunked_delta_rule(q, k, v, beta, None,
                                           kernels.LinearAttnConfig(chunk=cfg.chunk))
         return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
+
+    def _moe_layer(self, n2: Tensor, i: int) -> Tensor:
+        from .ops import moe
+
+        cfg = self.cfg
+        pre = f"layers.{i}."
+        n_e = cfg.n_routed_experts + cfg.n_shared_experts
+        hid = cfg.expert_hidden
+        w_gu = self.p[pre + "moe_gu"]
+        w_dn = self.p[pre + "moe_down"]
+        out, probs, ids = moe.moe_ffn(n2, self.p[pre + "router"], self.router_bias.get(i),
+                                      w_gu, w_dn, cfg.top_k, n_shared=cfg.n_shared_experts,
+                                      shapes=((n_e, 2 * hid, cfg.d_model), (n_e, cfg.d_model, hid)))
+        self.last_router = (probs, ids)
+        return out
 
     def _gqa_layer(self, n: Tensor, i: int, B: int, S: int) -> Tensor:
         cfg = self.cfg
@@ -391,8 +443,11 @@ class Trainer:
             else:
                 a = self._gqa_layer(n, i, B, S)
             n2, h = ops.add_rmsnorm(a, h, self.p[pre + "pre_ffn_norm"])
-            gu = ops.linear(n2, self.p[pre + "gate_up"])
-            f = ops.linear(ops.swiglu(gu), self.p[pre + "down"])
+            if pre + "gate_up" in self.p:
+                gu = ops.linear(n2, self.p[pre + "gate_up"])
+                f = ops.linear(ops.swiglu(gu), self.p[pre + "down"])
+            else:
+                f = self._moe_layer(n2, i)
             nxt = f"layers.{i + 1}.pre_attn_norm" if i + 1 < cfg.n_layers else "final_norm"
             n, h = ops.add_rmsnorm(f, h, self.p[nxt])
         return n
@@ -405,8 +460,21 @@ class Trainer:
         wt = loss_mask.float().clone()
         wt[:, 0] = 0.0                          # mask[:, 1:] aligned to the predicting position
         wt = torch.roll(wt, -1, dims=1).reshape(-1) / denom
-        return ops.softcap_cross_entropy(hid, self.p["unembed"], targets, wt.contiguous(),
-                                         float(self.tcfg.softcap), self.ce_chunk_rows)
+        ce = ops.softcap_cross_entropy(hid, self.p["unembed"], targets, wt.contiguous(),
+                                       float(self.tcfg.softcap), self.ce_chunk_rows)
+        if self.moe_layers and self.tcfg.z_loss_weight:
+            # mean squared log-sum-exp of the last MoE layer's router probabilities
+            probs, _ = self.last_router
+            z = torch.logsumexp(probs, dim=-1).square().mean()
+            ce = ce + float(self.tcfg.z_loss_weight) * z * (self._micro_weight(loss_mask, denom))
+        return ce
+
+    @staticmethod
+    def _micro_weight(loss_mask: Tensor, denom) -> Tensor:
+        """Share of the step's loss tokens in this micro-batch (auxiliary terms are weighted by
+        it so that they sum to one step-level mean)."""
+        m = loss_mask.float()[:, 1:].sum()
+        return m / denom
 
     # ---------------------------------------------------------------- optimizer
     def _sync_grads(self) -> None:
@@ -545,10 +613,26 @@ class Trainer:
         denom = denom.clamp(min=1.0)
         total = torch.zeros((), dtype=torch.float32, device=tokens.device)
         mb = self.micro_batch
+        load = None
         for b0 in range(0, tokens.shape[0], mb):
             l = self.loss(tokens[b0:b0 + mb], loss_mask[b0:b0 + mb], denom)
             l.backward()
             total += l.detach()
+            if self.router_bias:
+                ids = self.last_router[1].reshape(-1).long()
+                c = torch.bincount(ids, minlength=self.cfg.n_routed_experts).float()
+                load = c if load is None else load + c
+        if load is not None:
+            # aux-loss-free balancing: b <- b - u sign(load - mean), load = share of the
+            # assignments in the last MoE layer, applied to every router bias
+            if self.world > 1:
+                import torch.distributed as dist
+
+                dist.all_reduce(load, group=self.pg)
+            load = load / load.sum().clamp(min=1.0)
+            delta = torch.sign(load - load.mean()) * self.router_bias_rate
+            for b in self.router_bias.values():
+                b.sub_(delta)
         self._sync_grads()
         if self.world > 1:
             import torch.distributed as dist

@@ -118,25 +118,35 @@ def grouped_wgrad(a: Tensor, b: Tensor, pl: Placement, out: Tensor, accumulate: 
     return out
 
 
-def _acc_grad(w: Tensor, fn):
+def _acc_grad(w: Tensor, shape3, fn):
     """Weight gradient into ``w.main_grad`` (fp32 accumulate) when present, else returned."""
     mg = getattr(w, "main_grad", None)
     if mg is not None:
-        fn(mg.view(w.shape), True)
+        fn(mg.view(shape3), True)
         return None
-    return fn(torch.empty(w.shape, dtype=BF16, device=w.device), False)
+    return fn(torch.empty(shape3, dtype=BF16, device=w.device), False).view(w.shape)
 
 
 class _MoeFfnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, router_w, router_bias, w_gu, w_down, top_k):
+    def forward(ctx, x, router_w, router_bias, w_gu_p, w_down_p, top_k, n_shared, shapes):
         from .functional import gemm
 
+        w_gu = w_gu_p.view(shapes[0]) if shapes is not None else w_gu_p
+        w_down = w_down_p.view(shapes[1]) if shapes is not None else w_down_p
         T, d = x.shape
-        E, two_h, _ = w_gu.shape
+        E, two_h, _ = w_gu.shape          # routed + shared
         h = two_h // 2
         logits = gemm(x, router_w, out_dtype=torch.float32)
-        probs, ids, gates = route(logits, router_bias, top_k)
+        probs, ids_r, gates_r = route(logits, router_bias, top_k)
+        if n_shared:
+            # shared experts: every token, gate 1, appended as extra slots
+            extra = torch.arange(E - n_shared, E, dtype=torch.int32, device=x.device)
+            ids = torch.cat([ids_r, extra.expand(T, n_shared)], dim=1).contiguous()
+            gates = torch.cat([gates_r, torch.ones((T, n_shared), dtype=torch.float32,
+                                                   device=x.device)], dim=1).contiguous()
+        else:
+            ids, gates = ids_r, gates_r
         pl = place(ids, E)
         xp = permute(x, pl)
         gu = grouped_gemm(xp, w_gu, pl)
@@ -144,37 +154,44 @@ class _MoeFfnFn(torch.autograd.Function):
         call("pb_swiglu_fwd", ptr(gu), ptr(hs), pl.rows, h, stream_ptr())
         y = grouped_gemm(hs, w_down, pl)
         out = combine(y, pl, gates, T)
-        ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids, gates, xp, gu, hs, y)
+        ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids_r, gates, xp, gu, hs, y)
         ctx.pl = pl
-        ctx.refs = (router_w, w_gu, w_down)
-        ctx.mark_non_differentiable(probs, ids)
-        return out, probs, ids
+        ctx.refs = (router_w, w_gu_p, w_down_p)
+        ctx.top_k = top_k
+        ctx.mark_non_differentiable(ids_r)
+        return out, probs, ids_r
 
     @staticmethod
-    def backward(ctx, d_out, _dp, _di):
+    def backward(ctx, d_out, d_probs, _di):
         from .functional import gemm
 
         x, router_w, w_gu, w_down, probs, ids, gates, xp, gu, hs, y = ctx.saved_tensors
         router_ref, gu_ref, down_ref = ctx.refs
         pl = ctx.pl
         T, d = x.shape
-        E, two_h, _ = w_gu.shape
+        E_all, two_h, _ = w_gu.shape
+        E = router_w.shape[0]
         h = two_h // 2
-        k = pl.top_k
+        k = pl.top_k                       # routed + shared slots
+        k_r = ctx.top_k
         d_out = d_out.contiguous()
         dgates = torch.empty((T, k), dtype=torch.float32, device=x.device)
         call("pb_moe_combine_bwd", ptr(y), ptr(d_out), ptr(pl.row_of), T * k, k, d, ptr(dgates),
              stream_ptr())
         dyp = permute(d_out, pl, scale=gates.reshape(-1))
         dh = grouped_gemm(dyp, w_down, pl, b_mn=True)
-        g_down = _acc_grad(down_ref, lambda o, acc: grouped_wgrad(dyp, hs, pl, o, acc))
+        g_down = _acc_grad(down_ref, w_down.shape, lambda o, acc: grouped_wgrad(dyp, hs, pl, o, acc))
         dgu = torch.empty_like(gu)
         call("pb_swiglu_bwd", ptr(dh), ptr(gu), ptr(dgu), pl.rows, h, stream_ptr())
-        g_gu = _acc_grad(gu_ref, lambda o, acc: grouped_wgrad(dgu, xp, pl, o, acc))
+        g_gu = _acc_grad(gu_ref, w_gu.shape, lambda o, acc: grouped_wgrad(dgu, xp, pl, o, acc))
         dxp = grouped_gemm(dgu, w_gu, pl, b_mn=True)
         dlogits = torch.empty((T, E), dtype=torch.float32, device=x.device)
-        call("pb_moe_route_bwd", ptr(dgates), ptr(gates), ptr(probs), ptr(ids), T, E, k, ptr(dlogits),
+        dg_r = dgates if k_r == k else dgates[:, :k_r].contiguous()
+        g_r = gates if k_r == k else gates[:, :k_r].contiguous()
+        call("pb_moe_route_bwd", ptr(dg_r), ptr(g_r), ptr(probs), ptr(ids), T, E, k_r, ptr(dlogits),
              stream_ptr())
+        if d_probs is not None:
+            dlogits = dlogits + d_probs * probs * (1.0 - probs)
         dl = dlogits.to(BF16)
         # dx = sum over slots of dxp rows + dlogits @ router_w
         dx_r = gemm(dl, router_w, b_mn=True)
@@ -186,19 +203,29 @@ class _MoeFfnFn(torch.autograd.Function):
                  beta=1.0)
         else:
             g_router = gemm(dl, x, a_mn=True, b_mn=True)
-        return dx, g_router, None, g_gu, g_down, None
+        return dx, g_router, None, g_gu, g_down, None, None, None
 
 
 def moe_ffn(x: Tensor, router_w: Tensor, router_bias: Tensor | None, w_gu: Tensor, w_down: Tensor,
-            top_k: int):
-    """Routed-expert FFN. x [T, d] bf16; router_w [E, d]; w_gu [E, 2h, d] (gate rows then up
-    rows); w_down [E, d, h]. Returns (out [T, d], probs [T, E] fp32, ids [T, k] int32)."""
-    return _MoeFfnFn.apply(x, router_w, router_bias, w_gu, w_down, int(top_k))
+            top_k: int, n_shared: int = 0, shapes=None):
+    """Routed (+ shared) expert FFN. x [T, d] bf16; router_w [E, d]; w_gu [E + n_shared, 2h, d]
+    (gate rows then up rows per expert; the shared experts last); w_down [E + n_shared, d, h].
+    ``shapes`` gives those two 3-D shapes when the weights are passed as flat 2-D parameters.
+    Returns (out [T, d], probs [T, E] fp32, ids [T, k] int32); out and probs are differentiable."""
+    return _MoeFfnFn.apply(x, router_w, router_bias, w_gu, w_down, int(top_k), int(n_shared), shapes)
 
 
-def moe_ffn_ref(x, router_w, router_bias, w_gu, w_down, top_k):
+def moe_ffn_ref(x, router_w, router_bias, w_gu, w_down, top_k, n_shared=0):
     """fp32 PyTorch statement of the same layer (oracle for the tests)."""
     xf = x.float()
+    if n_shared:
+        E = router_w.shape[0]
+        routed, probs, ids = moe_ffn_ref(x, router_w, router_bias, w_gu[:E], w_down[:E], top_k)
+        hh = w_gu.shape[1] // 2
+        for j in range(E, E + n_shared):
+            gu = xf @ w_gu[j].float().t()
+            routed = routed + (torch.nn.functional.silu(gu[:, :hh]) * gu[:, hh:]) @ w_down[j].float().t()
+        return routed, probs, ids
     probs = torch.sigmoid(xf @ router_w.float().t())
     sel = probs if router_bias is None else probs + router_bias.float()
     ids = torch.argsort(-sel, dim=-1, stable=True)[:, :top_k]

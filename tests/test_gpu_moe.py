@@ -88,7 +88,8 @@ def test_grouped_gemms_match_per_expert_products():
     assert tot[4] == 0
 
 
-def test_moe_ffn_matches_fp32_reference():
+@pytest.mark.parametrize("n_shared", [0, 2])
+def test_moe_ffn_matches_fp32_reference(n_shared):
     from prometheus_b200.ops import functional as ops
     from prometheus_b200.ops import moe
 
@@ -96,16 +97,18 @@ def test_moe_ffn_matches_fp32_reference():
     x = _r(T, d, seed=1).requires_grad_(True)
     rw = _r(E, d, seed=2, scale=0.2).requires_grad_(True)
     bias = _r(E, seed=3, scale=0.05, dtype=torch.float32)
-    wgu = _r(E, 2 * h, d, seed=4, scale=0.08).requires_grad_(True)
-    wd = _r(E, d, h, seed=5, scale=0.08).requires_grad_(True)
+    wgu = _r(E + n_shared, 2 * h, d, seed=4, scale=0.08).requires_grad_(True)
+    wd = _r(E + n_shared, d, h, seed=5, scale=0.08).requires_grad_(True)
     go = _r(T, d, seed=6)
-    out, probs, ids = moe.moe_ffn(x, rw, bias, wgu, wd, k)
-    (out.float() * go.float()).sum().backward()
+    out, probs, ids = moe.moe_ffn(x, rw, bias, wgu, wd, k, n_shared=n_shared)
+    zw = 0.3
+    ((out.float() * go.float()).sum() + zw * torch.logsumexp(probs, -1).square().mean()).backward()
     torch.cuda.synchronize()
     ops.check_status("cuda")
     leaves = [t.detach().float().requires_grad_(True) for t in (x, rw, wgu, wd)]
-    o_ref, p_ref, i_ref = moe.moe_ffn_ref(leaves[0], leaves[1], bias, leaves[2], leaves[3], k)
-    (o_ref * go.float()).sum().backward()
+    o_ref, p_ref, i_ref = moe.moe_ffn_ref(leaves[0], leaves[1], bias, leaves[2], leaves[3], k,
+                                          n_shared=n_shared)
+    ((o_ref * go.float()).sum() + zw * torch.logsumexp(p_ref, -1).square().mean()).backward()
     assert (ids == i_ref).float().mean().item() > 0.995   # bf16 logits may flip near-ties
     _close(out, o_ref, 3e-2)
     _close(probs, p_ref, 1e-2)
