@@ -157,14 +157,24 @@ class Trainer:
             vec(p + "pre_attn_norm", d, p + "pre_attn_norm")
             vec(p + "pre_ffn_norm", d, p + "pre_ffn_norm")
             if kind is M.AttentionKind.MLA:
-                raise NotImplementedError("the fused engine runs linear and GQA layers")
-            kvh = nh if kind is M.AttentionKind.LINEAR else nkv
-            mat(p + "q", (nh * dh, d), [src(p + "W_q", 0, nh * dh)])
-            mat(p + "k", (kvh * dh, d), [src(p + "W_k", 0, kvh * dh)])
-            mat(p + "v", (kvh * dh, d), [src(p + "W_v", 0, kvh * dh)])
-            if kind is M.AttentionKind.LINEAR and cfg.delta_beta == "sigmoid":
-                mat(p + "beta", (nh, d), [src(p + "W_beta", 0, nh)])
-            mat(p + "o", (d, nh * dh), [(p + "W_o", 0, d, "o", None)])
+                # keys = [up-projected compressed KV | shared rotary key], values = the
+                # up-projected part (model/__init__.py:435-482, 737-750 of the reference)
+                dn = dh
+                dr = max(2, (dh // 2) // 2 * 2)
+                self.mla_dims = (dn, dr, dh)
+                mat(p + "q", (nh * (dn + dr), d), [src(p + "W_q", 0, nh * (dn + dr))])
+                mat(p + "kv_c", (dh, d), [src(p + "W_kv_compress", 0, dh)])
+                mat(p + "kv_up", (nh * dn, dh), [src(p + "W_kv_up", 0, nh * dn)])
+                mat(p + "rope_k", (dr, d), [src(p + "W_rope_k", 0, dr)])
+                mat(p + "o", (d, nh * dn), [(p + "W_o", 0, d, "o", None)])
+            else:
+                kvh = nh if kind is M.AttentionKind.LINEAR else nkv
+                mat(p + "q", (nh * dh, d), [src(p + "W_q", 0, nh * dh)])
+                mat(p + "k", (kvh * dh, d), [src(p + "W_k", 0, kvh * dh)])
+                mat(p + "v", (kvh * dh, d), [src(p + "W_v", 0, kvh * dh)])
+                if kind is M.AttentionKind.LINEAR and cfg.delta_beta == "sigmoid":
+                    mat(p + "beta", (nh, d), [src(p + "W_beta", 0, nh)])
+                mat(p + "o", (d, nh * dh), [(p + "W_o", 0, d, "o", None)])
             if M.ffn_kind(i, cfg) is M.FfnKind.DENSE:
                 hid = cfg.dense_hidden if cfg.dense_hidden is not None else cfg.expert_hidden
                 mat(p + "gate_up", (2 * hid, d),
@@ -365,7 +375,9 @@ class Trainer:
                 if how == "t2":
                     t = blk.t().contiguous()
                     leaf = tree_name.split(".")[-1]
-                    if leaf in ("W_q", "W_k", "W_v"):
+                    if leaf == "W_q" or leaf == "W_kv_up":
+                        t = t.reshape(t.shape[0], nh, -1)
+                    elif leaf in ("W_k", "W_v"):
                         t = t.reshape(t.shape[0], -1, dh)
                 elif how == "o":
                     t = blk.t().contiguous().reshape(nh, dh, cfg.d_model)
@@ -397,6 +409,30 @@ class Trainer:
         o, _ = kernels.chunked_delta_rule(q, k, v, beta, None,
                                           kernels.LinearAttnConfig(chunk=cfg.chunk))
         return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
+
+    def _mla_layer(self, n: Tensor, i: int, B: int, S: int) -> Tensor:
+        """Latent-KV softmax attention. Projections run on the tcgen05 GEMM; the rotary
+        split, the unit-weight QK RMSNorm and the softmax core are PyTorch (the reference's
+        tiny / flagship geometries, not a benchmark path)."""
+        cfg = self.cfg
+        nh = M.head_geometry(cfg)[0]
+        dn, dr, _ = self.mla_dims
+        pre = f"layers.{i}."
+        q = ops.linear(n, self.p[pre + "q"]).view(B, S, nh, dn + dr)
+        ckv = ops.linear(n, self.p[pre + "kv_c"])
+        k_nope = ops.linear(ckv, self.p[pre + "kv_up"]).view(B, S, nh, dn)
+        rk = ops.linear(n, self.p[pre + "rope_k"]).view(B, S, 1, dr).expand(B, S, nh, dr)
+        pos = torch.arange(S, dtype=torch.float32, device=n.device)
+        q_rope, rk = M.rope(q[..., dn:].float(), rk.float(), pos, partial=False, base=cfg.rope_base)
+        qf = torch.cat([q[..., :dn].float(), q_rope], dim=-1)
+        kf = torch.cat([k_nope.float(), rk], dim=-1)
+        qf = qf * torch.rsqrt(qf.square().mean(-1, keepdim=True) + 1e-6)
+        kf = kf * torch.rsqrt(kf.square().mean(-1, keepdim=True) + 1e-6)
+        o = F.scaled_dot_product_attention(qf.transpose(1, 2).to(BF16), kf.transpose(1, 2).to(BF16),
+                                           k_nope.transpose(1, 2), is_causal=True,
+                                           scale=1.0 / math.sqrt(dn + dr))
+        o = o.transpose(1, 2).reshape(B * S, nh * dn)
+        return ops.linear(o, self.p[pre + "o"])
 
     def _moe_layer(self, n2: Tensor, i: int) -> Tensor:
         from .ops import moe
@@ -440,6 +476,8 @@ class Trainer:
             pre = f"layers.{i}."
             if self.layer_kinds[i] is M.AttentionKind.LINEAR:
                 a = self._delta_layer(n, i, B, S)
+            elif self.layer_kinds[i] is M.AttentionKind.MLA:
+                a = self._mla_layer(n, i, B, S)
             else:
                 a = self._gqa_layer(n, i, B, S)
             n2, h = ops.add_rmsnorm(a, h, self.p[pre + "pre_ffn_norm"])

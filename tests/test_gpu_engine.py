@@ -132,3 +132,29 @@ def test_moe_engine_matches_tree_forward_and_trains():
     assert any(b.abs().sum().item() > 0 for b in tr.router_bias.values())
     from prometheus_b200.ops import functional as ops
     ops.check_status("cuda")
+
+
+def test_tiny_reference_config_mla_moe_runs_in_the_engine():
+    """The reference's tiny configuration (MLA softmax layers, 8 routed experts top-2 + shared,
+    head dim 64): engine loss equals the fp32 tree model's, tree round-trips, loss goes down."""
+    from prometheus_b200 import engine, model, train
+
+    cfg = model.tiny_config()
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10)
+    params = model.init_params(cfg, 0)
+    tr = engine.Trainer(cfg, tcfg, params=params, micro_batch=2)
+    back = model.flatten_params(tr.export_tree())
+    want = model.flatten_params(params)
+    assert {"layers.3.W_kv_up", "layers.3.W_rope_k", "layers.3.W_kv_compress"} <= set(back)
+    for name, t in back.items():
+        assert torch.equal(t.float(), want[name].float()) and t.shape == want[name].shape, name
+    S = min(cfg.max_context, 128)
+    tokens = torch.randint(0, cfg.vocab_size, (4, S), generator=torch.Generator().manual_seed(0))
+    dev_params = train._map_tree(params, lambda _n, p: p.cuda())
+    batch = train.Batch(tokens=tokens.cuda(), loss_mask=torch.ones(4, S, device="cuda"),
+                        positions=torch.arange(S))
+    ref_total, (ce, mtp, z, _) = train.compute_loss(dev_params, batch, cfg, tcfg)
+    want_loss = float(ref_total - mtp)           # the engine has no MTP heads yet
+    losses = [tr.step(tokens.cuda())["loss"].item() for _ in range(10)]
+    assert abs(losses[0] - want_loss) < 3e-2 * want_loss, (losses[0], want_loss)
+    assert losses[-1] < losses[0] - 0.2, losses
