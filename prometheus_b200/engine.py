@@ -148,6 +148,16 @@ class Trainer:
         ws.append(Weight("unembed", (cfg.vocab_size, d), "adam", True,
                          sources=[("unembed", 0, cfg.vocab_size, None, None)]))
         vec("final_norm", d, "final_norm")
+        for j in range(cfg.mtp_heads):
+            vec(f"mtp.{j}.norm", d, f"mtp.{j}.norm")
+            mat(f"mtp.{j}.proj", (d, d), [src(f"mtp.{j}.proj", 0, d)])
+            ws.append(Weight(f"mtp.{j}.unembed", (cfg.vocab_size, d), "adam", True,
+                             sources=[(f"mtp.{j}.unembed", 0, cfg.vocab_size, None, None)]))
+        # latent adapter (thought vector -> residual stream): 2-layer SiLU MLP + RMSNorm
+        ah = cfg.adapter_hidden if cfg.adapter_hidden is not None else d
+        mat("adapter_w1", (ah, d), [src("adapter_w1", 0, ah)])
+        mat("adapter_w2", (d, ah), [src("adapter_w2", 0, d)])
+        vec("adapter_norm", d, "adapter_norm")
         self.layer_kinds = []
         self.moe_layers: list[int] = []
         for i in range(cfg.n_layers):
@@ -490,8 +500,12 @@ class Trainer:
             n, h = ops.add_rmsnorm(f, h, self.p[nxt])
         return n
 
-    def loss(self, tokens: Tensor, loss_mask: Tensor, denom: Tensor | float) -> Tensor:
-        """Masked mean next-token CE (soft-capped) of one micro-batch, scaled by 1/denom."""
+    def loss(self, tokens: Tensor, loss_mask: Tensor, denom: Tensor | float,
+             mtp_denoms: list | None = None) -> Tensor:
+        """Masked mean next-token CE (soft-capped) of one micro-batch, scaled by 1/denom, plus
+        the multi-token-prediction heads (head j predicts j + 1 tokens ahead from
+        ``rmsnorm(h) @ proj + h`` with its own unembedding; mean over heads) and the router
+        z-loss."""
         B, S = tokens.shape
         hid = self.forward_hidden(tokens)
         targets = torch.roll(tokens, -1, dims=1).reshape(-1).to(torch.int32)
@@ -500,6 +514,20 @@ class Trainer:
         wt = torch.roll(wt, -1, dims=1).reshape(-1) / denom
         ce = ops.softcap_cross_entropy(hid, self.p["unembed"], targets, wt.contiguous(),
                                        float(self.tcfg.softcap), self.ce_chunk_rows)
+        n_mtp = self.cfg.mtp_heads
+        for j in range(n_mtp):
+            off = j + 1
+            if off >= S:
+                continue
+            m = loss_mask.float()
+            wj = torch.zeros_like(m)
+            wj[:, : S - off] = m[:, off:] * m[:, : S - off]
+            dj = mtp_denoms[j] if mtp_denoms is not None else wj.sum().clamp(min=1.0)
+            tj = torch.roll(tokens, -off, dims=1).reshape(-1).to(torch.int32)
+            mh = ops.linear(ops.rmsnorm(hid, self.p[f"mtp.{j}.norm"]), self.p[f"mtp.{j}.proj"]) + hid
+            ce = ce + ops.softcap_cross_entropy(mh, self.p[f"mtp.{j}.unembed"], tj,
+                                                (wj.reshape(-1) / (dj * n_mtp)).contiguous(),
+                                                float(self.tcfg.softcap), self.ce_chunk_rows)
         if self.moe_layers and self.tcfg.z_loss_weight:
             # mean squared log-sum-exp of the last MoE layer's router probabilities
             probs, _ = self.last_router
@@ -650,10 +678,21 @@ class Trainer:
             dist.all_reduce(denom, group=self.pg)
         denom = denom.clamp(min=1.0)
         total = torch.zeros((), dtype=torch.float32, device=tokens.device)
+        mtp_denoms = None
+        if self.cfg.mtp_heads:
+            S = tokens.shape[1]
+            m = loss_mask.float()
+            dj = torch.stack([(m[:, j + 1:] * m[:, : S - j - 1]).sum()
+                              for j in range(self.cfg.mtp_heads)])
+            if self.world > 1:
+                import torch.distributed as dist
+
+                dist.all_reduce(dj, group=self.pg)
+            mtp_denoms = list(dj.clamp(min=1.0))
         mb = self.micro_batch
         load = None
         for b0 in range(0, tokens.shape[0], mb):
-            l = self.loss(tokens[b0:b0 + mb], loss_mask[b0:b0 + mb], denom)
+            l = self.loss(tokens[b0:b0 + mb], loss_mask[b0:b0 + mb], denom, mtp_denoms)
             l.backward()
             total += l.detach()
             if self.router_bias:
