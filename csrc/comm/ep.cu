@@ -1,0 +1,255 @@
+// Expert-parallel token exchange over symmetric memory (one process per GPU, NVLink peer
+// loads / stores; no library collective on the path).
+//
+// Rank r owns experts [r * El, (r + 1) * El). Per MoE layer and direction:
+//
+//   pb_ep_layout    every rank reads all ranks' per-expert pair counts (peer loads) and
+//                   derives, identically everywhere, each owner's receive layout: expert
+//                   segments on 128-row boundaries, inside a segment the rows of source 0,
+//                   then source 1, ... It emits the owner-side tables for the grouped GEMMs
+//                   (segment offsets, row totals, padded lengths, expert of each 128-row block)
+//                   and the sender-side table send_base[e] = first row of my pairs for expert e
+//                   in its owner's buffer. Needing more rows than the buffers hold latches
+//                   PB_EP_OVERFLOW in the status word and the excess pairs are dropped.
+//   pb_ep_dispatch  push: every local (token, slot) row (x gate, in the backward) is stored
+//                   straight into the owner's receive buffer (16-byte peer stores) and its
+//                   (owner, row) is remembered
+//   pb_ep_combine   pull: out[t] = sum_s gate[t, s] * ybuf_owner(t, s)[row(t, s)] by peer loads
+//   pb_ep_rowdot / pb_ep_pull_scalar   gate gradient: the owner forms <y_row, dy_row>, the
+//                   source reads it back and divides by the gate it scaled dy with
+//
+// Ordering between the phases is the caller's bounded device barrier (pb_barrier_all).
+// Reference semantics: kernels/__init__.py ep_dispatch / ep_combine of the reference
+// (token -> expert-owner exchange with stable ordering); the data path is this library's own.
+#include "common.cuh"
+
+namespace pb {
+
+constexpr int EP_MAX_RANKS = 8;
+constexpr int EP_MAX_E = 512;
+constexpr int PB_EP_OVERFLOW = 4;
+
+struct EpPeers {
+  void* p[EP_MAX_RANKS];
+};
+
+// counts.p[s]: int [E] = pairs of source s per global expert. One block.
+__global__ void ep_layout_kernel(EpPeers counts, int rank, int world, int E, int max_rows,
+                                 int* __restrict__ expert_off,   // [El + 1]
+                                 int* __restrict__ totals,       // [El]
+                                 int* __restrict__ k_len,        // [El]
+                                 int* __restrict__ mblk_group,   // [max_rows / 128]
+                                 int* __restrict__ send_base,    // [E]
+                                 int* status) {
+  __shared__ int tot[EP_MAX_E];      // pairs per expert over all sources
+  __shared__ int before[EP_MAX_E];   // pairs of sources < rank
+  __shared__ int seg[EP_MAX_E + 1];  // segment start of expert e inside its owner's buffer
+  const int El = E / world;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int t = 0, b = 0;
+    for (int s = 0; s < world; ++s) {
+      const int c = __ldcv(static_cast<const int*>(counts.p[s]) + e);
+      if (s < rank) b += c;
+      t += c;
+    }
+    tot[e] = t;
+    before[e] = b;
+  }
+  __syncthreads();
+  if (threadIdx.x < world) {          // one thread per owner: aligned prefix over its experts
+    const int q = threadIdx.x;
+    int run = 0;
+    for (int j = 0; j < El; ++j) {
+      seg[q * El + j] = run;
+      run += (tot[q * El + j] + 127) / 128 * 128;
+    }
+    if (q == rank) seg[E] = run;
+    if (run > max_rows && status != nullptr) atomicCAS(status, 0, PB_EP_OVERFLOW);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) send_base[e] = seg[e] + before[e];
+  const int mine = rank * El;
+  const int used = min(seg[E], max_rows / 128 * 128);
+  for (int j = threadIdx.x; j <= El; j += blockDim.x) {
+    const int start = (j < El) ? seg[mine + j] : seg[E];
+    expert_off[j] = min(start, used);
+    if (j < El) {
+      const int end = min(start + (tot[mine + j] + 127) / 128 * 128, used);
+      totals[j] = max(0, min(tot[mine + j], used - min(start, used)));
+      k_len[j] = max(0, end - min(start, used));
+    }
+  }
+  for (int m = threadIdx.x; m < max_rows / 128; m += blockDim.x) {
+    const int row = m * 128;
+    int g = -1;
+    if (row < used) {
+      int lo = 0, hi = El;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (seg[mine + mid] <= row) lo = mid; else hi = mid;
+      }
+      g = lo;
+    }
+    mblk_group[m] = g;
+  }
+}
+
+// One warp per local pair. local_off: my own 128-padded placement offsets (from the local
+// stable sort), row_of_local its rows; dest row = send_base[e] + (row_of_local - local_off[e]).
+__global__ void ep_dispatch_kernel(const bf16* __restrict__ src, long ld_src,
+                                   const int* __restrict__ ids, const int* __restrict__ row_of_local,
+                                   const int* __restrict__ local_off, const int* __restrict__ send_base,
+                                   const float* __restrict__ scale, int n_pairs, int k, int d, int El,
+                                   int max_rows, EpPeers xbuf, int* __restrict__ dest_rank,
+                                   int* __restrict__ dest_row) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= n_pairs) return;
+  const int e = ids[w];
+  const int q = e / El;
+  const int row = send_base[e] + (row_of_local[w] - local_off[e]);
+  const bool ok = row < max_rows;
+  if (lane == 0) {
+    dest_rank[w] = q;
+    dest_row[w] = ok ? row : -1;
+  }
+  if (!ok) return;
+  const bf16* s = src + static_cast<size_t>(w / k) * ld_src;
+  bf16* o = static_cast<bf16*>(xbuf.p[q]) + static_cast<size_t>(row) * d;
+  const float g = scale ? scale[w] : 1.f;
+  for (int c = lane * 8; c < d; c += 256) {
+    bf16x8 v = *reinterpret_cast<const bf16x8*>(s + c);
+    if (scale) {
+      float f[8];
+      unpack8(v, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] *= g;
+      v = pack8(f);
+    }
+    *reinterpret_cast<bf16x8*>(o + c) = v;
+  }
+}
+
+// out[t] = sum_s gate * ybuf[dest_rank][dest_row] (+ add[t]); one warp per token.
+__global__ void ep_combine_kernel(EpPeers ybuf, const int* __restrict__ dest_rank,
+                                  const int* __restrict__ dest_row, const float* __restrict__ gates,
+                                  const bf16* __restrict__ add, int T, int k, int d,
+                                  bf16* __restrict__ out) {
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (t >= T) return;
+  for (int c = lane * 8; c < d; c += 256) {
+    float acc[8];
+    if (add != nullptr) unpack8(*reinterpret_cast<const bf16x8*>(add + static_cast<size_t>(t) * d + c), acc);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    }
+    for (int s = 0; s < k; ++s) {
+      const size_t i = static_cast<size_t>(t) * k + s;
+      const int row = dest_row[i];
+      if (row < 0) continue;
+      const float g = gates ? gates[i] : 1.f;
+      const bf16* y = static_cast<const bf16*>(ybuf.p[dest_rank[i]]) + static_cast<size_t>(row) * d + c;
+      const uint4 raw = __ldcv(reinterpret_cast<const uint4*>(y));
+      float f[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(&raw), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(g, f[j], acc[j]);
+    }
+    *reinterpret_cast<bf16x8*>(out + static_cast<size_t>(t) * d + c) = pack8(acc);
+  }
+}
+
+// dot[r] = <a[r], b[r]> for r < *rows_used; one warp per row
+__global__ void ep_rowdot_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b,
+                                 const int* __restrict__ rows_used, int d, float* __restrict__ dot) {
+  const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (r >= *rows_used) return;
+  float acc = 0.f;
+  for (int c = lane * 8; c < d; c += 256) {
+    float f[8], g[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(a + static_cast<size_t>(r) * d + c), f);
+    unpack8(*reinterpret_cast<const bf16x8*>(b + static_cast<size_t>(r) * d + c), g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc = fmaf(f[j], g[j], acc);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) dot[r] = acc;
+}
+
+// out[i] = dotbuf[dest_rank[i]][dest_row[i]] / div[i]
+__global__ void ep_pull_scalar_kernel(EpPeers dotbuf, const int* __restrict__ dest_rank,
+                                      const int* __restrict__ dest_row, const float* __restrict__ div,
+                                      int n, float* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int row = dest_row[i];
+  float v = 0.f;
+  if (row >= 0) {
+    v = __ldcv(static_cast<const float*>(dotbuf.p[dest_rank[i]]) + row);
+    const float g = div ? div[i] : 1.f;
+    v = (fabsf(g) > 1e-20f) ? v / g : 0.f;
+  }
+  out[i] = v;
+}
+
+}  // namespace pb
+
+using namespace pb;
+
+static EpPeers make_peers(void* const* ptrs, int world) {
+  EpPeers p;
+  for (int i = 0; i < EP_MAX_RANKS; ++i) p.p[i] = i < world ? ptrs[i] : nullptr;
+  return p;
+}
+
+PB_API int pb_ep_layout(void* const* count_ptrs, int rank, int world, int E, int max_rows,
+                        int* expert_off, int* totals, int* k_len, int* mblk_group, int* send_base,
+                        int* status, cudaStream_t st) {
+  if (world <= 0 || world > EP_MAX_RANKS || E <= 0 || E > EP_MAX_E || E % world != 0 ||
+      max_rows % 128 != 0)
+    return PB_BAD_ARG;
+  ep_layout_kernel<<<1, 512, 0, st>>>(make_peers(count_ptrs, world), rank, world, E, max_rows,
+                                      expert_off, totals, k_len, mblk_group, send_base, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+PB_API int pb_ep_dispatch(const void* src, long ld_src, const int* ids, const int* row_of_local,
+                          const int* local_off, const int* send_base, const float* scale,
+                          int n_pairs, int k, int d, int El, int max_rows, void* const* xbuf_ptrs,
+                          int world, int* dest_rank, int* dest_row, cudaStream_t st) {
+  if (n_pairs <= 0 || d % 8 != 0 || El <= 0) return PB_BAD_ARG;
+  const int grid = static_cast<int>((static_cast<long>(n_pairs) * 32 + 255) / 256);
+  ep_dispatch_kernel<<<grid, 256, 0, st>>>(static_cast<const bf16*>(src), ld_src, ids, row_of_local,
+                                           local_off, send_base, scale, n_pairs, k, d, El, max_rows,
+                                           make_peers(xbuf_ptrs, world), dest_rank, dest_row);
+  return static_cast<int>(cudaGetLastError());
+}
+
+PB_API int pb_ep_combine(void* const* ybuf_ptrs, int world, const int* dest_rank,
+                         const int* dest_row, const float* gates, const void* add, int T, int k, int d,
+                         void* out, cudaStream_t st) {
+  if (T <= 0 || d % 8 != 0) return PB_BAD_ARG;
+  const int grid = static_cast<int>((static_cast<long>(T) * 32 + 255) / 256);
+  ep_combine_kernel<<<grid, 256, 0, st>>>(make_peers(ybuf_ptrs, world), dest_rank, dest_row, gates,
+                                          static_cast<const bf16*>(add), T, k, d,
+                                          static_cast<bf16*>(out));
+  return static_cast<int>(cudaGetLastError());
+}
+
+PB_API int pb_ep_rowdot(const void* a, const void* b, const int* rows_used, int max_rows, int d,
+                        float* dot, cudaStream_t st) {
+  if (max_rows <= 0 || d % 8 != 0) return PB_BAD_ARG;
+  const int grid = static_cast<int>((static_cast<long>(max_rows) * 32 + 255) / 256);
+  ep_rowdot_kernel<<<grid, 256, 0, st>>>(static_cast<const bf16*>(a), static_cast<const bf16*>(b),
+                                         rows_used, d, dot);
+  return static_cast<int>(cudaGetLastError());
+}
+
+PB_API int pb_ep_pull_scalar(void* const* dot_ptrs, int world, const int* dest_rank,
+                             const int* dest_row, const float* div, int n, float* out,
+                             cudaStream_t st) {
+  if (n <= 0) return PB_BAD_ARG;
+  ep_pull_scalar_kernel<<<(n + 255) / 256, 256, 0, st>>>(make_peers(dot_ptrs, world), dest_rank,
+                                                         dest_row, div, n, out);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -121,8 +121,6 @@ __global__ void count_kernel(const int* __restrict__ ids, int n_pairs, int pairs
 // One block. Turns block_counts into exclusive per-block bases, and writes
 //   expert_off[e] (128-aligned segment starts, expert_off[E] = rows in use), totals[e],
 //   k_len[e] = padded segment length, mblk_group[m] for m < max_mblk (-1 beyond the data).
-// e_lo / e_cnt restrict the expert range this rank owns when the ids are global (EP); experts
-// outside it get empty segments.
 __global__ void scan_kernel(int* __restrict__ block_counts, int nblocks, int E,
                             int* __restrict__ expert_off, int* __restrict__ totals,
                             int* __restrict__ k_len, int* __restrict__ mblk_group, int max_mblk) {
@@ -329,6 +327,13 @@ PB_API int pb_moe_permute(const void* src, const int* row_of, const float* scale
       static_cast<const bf16*>(src), row_of, scale, n_pairs, k, d, ld_src, static_cast<bf16*>(dst));
   if (expert_off != nullptr)
     moe::zero_pad_kernel<<<E, 256, 0, st>>>(static_cast<bf16*>(dst), d, expert_off, totals);
+  return static_cast<int>(cudaGetLastError());
+}
+
+PB_API int pb_moe_zero_pad(void* buf, int d, const int* expert_off, const int* totals, int E,
+                           cudaStream_t st) {
+  if (E <= 0 || d % 8 != 0) return PB_BAD_ARG;
+  moe::zero_pad_kernel<<<E, 256, 0, st>>>(static_cast<bf16*>(buf), d, expert_off, totals);
   return static_cast<int>(cudaGetLastError());
 }
 

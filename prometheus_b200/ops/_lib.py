@@ -52,6 +52,7 @@ _SIGS = {
     "pb_moe_sort": [P, I, I, I, P, P, P, P, P, P, I, P],
     "pb_moe_permute": [P, P, P, I, I, I, L, P, P, P, I, P],
     "pb_moe_combine": [P, P, P, P, I, I, I, P, P],
+    "pb_moe_zero_pad": [P, I, P, P, I, P],
     "pb_moe_combine_bwd": [P, P, P, I, I, I, P, P],
     "pb_gemm_set_debug": [I],
     "pb_gemm_bf16": [P, P, P, P, I, I, I, I, L, L, L, L, L, L, L, L, I, I, I, I, F, F, P, I, P],

@@ -1,0 +1,189 @@
+"""Expert parallelism: the MoE FFN with its experts spread over the ranks of one box.
+
+Rank r owns routed experts ``[r * El, (r + 1) * El)``. Tokens reach their experts and come
+back through symmetric memory (``csrc/comm/ep.cu``): the sender stores its rows straight into
+the owner's receive buffer over NVLink (push), the owner runs the grouped tcgen05 GEMMs on
+what arrived, and the sender reads its results back out of the owner's buffer (pull) while
+applying the gates. The only synchronisation is the bounded device barrier between phases;
+there is no host round trip and no library collective in the layer.
+
+Reference behaviour: ``kernels/__init__.py`` ``ep_dispatch`` / ``ep_combine`` of the reference
+(stable token order per expert, capacity overflow reported rather than silently reordered) and
+``model/__init__.py:485-598`` for the routing math.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import _lib
+from ..ops import moe as M
+from ..ops._lib import call, ptr, stream_ptr
+from .symm import PP, SymmetricBuffer, SymmetricGroup
+
+P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
+_lib.register("pb_ep_layout", [PP, I, I, I, I, P, P, P, P, P, P, P])
+_lib.register("pb_ep_dispatch", [P, L, P, P, P, P, P, I, I, I, I, I, PP, I, P, P, P])
+_lib.register("pb_ep_combine", [PP, I, P, P, P, P, I, I, I, P, P])
+_lib.register("pb_ep_rowdot", [P, P, P, I, I, P, P])
+_lib.register("pb_ep_pull_scalar", [PP, I, P, P, P, I, P, P])
+
+BF16 = torch.bfloat16
+Tensor = torch.Tensor
+
+
+class EpContext:
+    """Symmetric buffers of one expert-parallel group (shared by all MoE layers).
+
+    ``max_rows``: rows a rank can receive per layer (multiple of 128). A layer that needs more
+    latches an overflow code in the status word (``SymmetricGroup.check``) and drops the excess
+    pairs; size it as ``capacity_factor * tokens_per_rank * top_k`` plus 127 rows per local expert.
+    """
+
+    def __init__(self, sym: SymmetricGroup, d_model: int, n_experts: int, max_rows: int):
+        self.sym = sym
+        self.world, self.rank = sym.world, sym.rank
+        if n_experts % self.world:
+            raise ValueError("the expert count must be divisible by the expert-parallel size")
+        self.E, self.El, self.d = n_experts, n_experts // self.world, d_model
+        self.max_rows = (int(max_rows) + 127) // 128 * 128
+        g = sym.group
+        self.counts = SymmetricBuffer(4 * n_experts, g)
+        self.xbuf = SymmetricBuffer(2 * self.max_rows * d_model, g)
+        self.ybuf = SymmetricBuffer(2 * self.max_rows * d_model, g)
+        self.dotbuf = SymmetricBuffer(4 * self.max_rows, g)
+        self.counts_local = self.counts.view(torch.int32, n_experts)
+        self.x_local = self.xbuf.view(BF16, self.max_rows * d_model).view(self.max_rows, d_model)
+        self.y_local = self.ybuf.view(BF16, self.max_rows * d_model).view(self.max_rows, d_model)
+        self.dot_local = self.dotbuf.view(torch.float32, self.max_rows)
+
+    def layout(self):
+        dev = self.x_local.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        pl = M.Placement(row_of=None, expert_off=torch.empty(self.El + 1, **i32),
+                         totals=torch.empty(self.El, **i32), k_len=torch.empty(self.El, **i32),
+                         mblk_group=torch.empty(self.max_rows // 128, **i32), rows=self.max_rows,
+                         n_experts=self.El, top_k=0)
+        send_base = torch.empty(self.E, **i32)
+        call("pb_ep_layout", self.counts.ptrs, self.rank, self.world, self.E, self.max_rows,
+             ptr(pl.expert_off), ptr(pl.totals), ptr(pl.k_len), ptr(pl.mblk_group), ptr(send_base),
+             ptr(self.sym.status), stream_ptr())
+        return pl, send_base
+
+    def dispatch(self, x: Tensor, ids: Tensor, local: M.Placement, send_base: Tensor,
+                 scale: Tensor | None):
+        T, k = ids.shape
+        dev = x.device
+        dest_rank = torch.empty(T * k, dtype=torch.int32, device=dev)
+        dest_row = torch.empty(T * k, dtype=torch.int32, device=dev)
+        call("pb_ep_dispatch", ptr(x), x.stride(0), ptr(ids), ptr(local.row_of), ptr(local.expert_off),
+             ptr(send_base), ptr(scale), T * k, k, self.d, self.El, self.max_rows, self.xbuf.ptrs,
+             self.world, ptr(dest_rank), ptr(dest_row), stream_ptr())
+        return dest_rank, dest_row
+
+    def combine(self, dest_rank, dest_row, gates, T: int, k: int, add: Tensor | None = None) -> Tensor:
+        out = torch.empty((T, self.d), dtype=BF16, device=dest_rank.device)
+        call("pb_ep_combine", self.ybuf.ptrs, self.world, ptr(dest_rank), ptr(dest_row), ptr(gates),
+             ptr(add), T, k, self.d, ptr(out), stream_ptr())
+        return out
+
+    def zero_pad(self, pl: M.Placement) -> None:
+        call("pb_moe_zero_pad", ptr(self.x_local), self.d, ptr(pl.expert_off), ptr(pl.totals),
+             self.El, stream_ptr())
+
+
+class _EpMoeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, router_w, router_bias, w_gu_p, w_down_p, top_k, ep, shapes):
+        from ..ops.functional import gemm
+
+        w_gu = w_gu_p.view(shapes[0]) if shapes is not None else w_gu_p      # [El, 2h, d]
+        w_down = w_down_p.view(shapes[1]) if shapes is not None else w_down_p
+        T, d = x.shape
+        h = w_gu.shape[1] // 2
+        sym = ep.sym
+        logits = gemm(x, router_w, out_dtype=torch.float32)
+        probs, ids, gates = M.route(logits, router_bias, top_k)
+        local = M.place(ids, ep.E)
+        sym.barrier(7)                          # the previous layer's pulls are over everywhere
+        ep.counts_local.copy_(local.totals)
+        sym.barrier(4)
+        pl, send_base = ep.layout()
+        dest_rank, dest_row = ep.dispatch(x, ids, local, send_base, None)
+        sym.barrier(5)                          # every row has landed
+        ep.zero_pad(pl)
+        xp = ep.x_local.clone()
+        gu = M.grouped_gemm(xp, w_gu, pl)
+        hs = torch.empty((pl.rows, h), dtype=BF16, device=x.device)
+        call("pb_swiglu_fwd", ptr(gu), ptr(hs), pl.rows, h, stream_ptr())
+        y = M.grouped_gemm(hs, w_down, pl)
+        ep.y_local.copy_(y)
+        sym.barrier(6)                          # results are ready to be pulled
+        out = ep.combine(dest_rank, dest_row, gates, T, top_k)
+        ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids, gates, xp, gu, hs, y,
+                              dest_rank, dest_row, send_base)
+        ctx.pl, ctx.local, ctx.ep = pl, local, ep
+        ctx.refs = (router_w, w_gu_p, w_down_p)
+        ctx.mark_non_differentiable(ids)
+        return out, probs, ids
+
+    @staticmethod
+    def backward(ctx, d_out, d_probs, _di):
+        from ..ops.functional import gemm
+
+        (x, router_w, w_gu, w_down, probs, ids, gates, xp, gu, hs, y, dest_rank, dest_row,
+         send_base) = ctx.saved_tensors
+        router_ref, gu_ref, down_ref = ctx.refs
+        pl, local, ep = ctx.pl, ctx.local, ctx.ep
+        sym = ep.sym
+        T, d = x.shape
+        k = ids.shape[1]
+        E = router_w.shape[0]
+        h = w_gu.shape[1] // 2
+        d_out = d_out.contiguous()
+        gflat = gates.reshape(-1)
+        sym.barrier(7)
+        ep.dispatch(d_out, ids, local, send_base, gflat)       # dY rows = gate * dOut[t]
+        sym.barrier(4)
+        ep.zero_pad(pl)
+        dyp = ep.x_local.clone()
+        call("pb_ep_rowdot", ptr(y), ptr(dyp), ptr(pl.expert_off[ep.El:]), pl.rows, d,
+             ptr(ep.dot_local), stream_ptr())
+        dh = M.grouped_gemm(dyp, w_down, pl, b_mn=True)
+        g_down = M._acc_grad(down_ref, w_down.shape, lambda o, acc: M.grouped_wgrad(dyp, hs, pl, o, acc))
+        dgu = torch.empty_like(gu)
+        call("pb_swiglu_bwd", ptr(dh), ptr(gu), ptr(dgu), pl.rows, h, stream_ptr())
+        g_gu = M._acc_grad(gu_ref, w_gu.shape, lambda o, acc: M.grouped_wgrad(dgu, xp, pl, o, acc))
+        dxp = M.grouped_gemm(dgu, w_gu, pl, b_mn=True)
+        ep.y_local.copy_(dxp)
+        sym.barrier(5)
+        dgates = torch.empty((T, k), dtype=torch.float32, device=x.device)
+        call("pb_ep_pull_scalar", ep.dotbuf.ptrs, ep.world, ptr(dest_rank), ptr(dest_row), ptr(gflat),
+             T * k, ptr(dgates), stream_ptr())
+        dlogits = torch.empty((T, E), dtype=torch.float32, device=x.device)
+        call("pb_moe_route_bwd", ptr(dgates), ptr(gates), ptr(probs), ptr(ids), T, E, k, ptr(dlogits),
+             stream_ptr())
+        if d_probs is not None:
+            dlogits = dlogits + d_probs * probs * (1.0 - probs)
+        dl = dlogits.to(BF16)
+        dx_r = gemm(dl, router_w, b_mn=True)
+        dx = ep.combine(dest_rank, dest_row, None, T, k, add=dx_r)
+        sym.barrier(6)
+        mg = getattr(router_ref, "main_grad", None)
+        g_router = None
+        if mg is not None:
+            gemm(dl, x, a_mn=True, b_mn=True, out=mg.view(router_w.shape), d=mg.view(router_w.shape),
+                 beta=1.0)
+        else:
+            g_router = gemm(dl, x, a_mn=True, b_mn=True)
+        return dx, g_router, None, g_gu, g_down, None, None, None
+
+
+def ep_moe_ffn(x: Tensor, router_w: Tensor, router_bias: Tensor | None, w_gu_local: Tensor,
+               w_down_local: Tensor, top_k: int, ep: EpContext, shapes=None):
+    """Routed-expert FFN with the experts sharded over ``ep``'s ranks. x [T, d] are this rank's
+    tokens; router_w [E, d] is replicated; w_gu_local [El, 2h, d] and w_down_local [El, d, h]
+    are this rank's experts. Returns (out [T, d], probs [T, E], ids [T, k]). Collective: every
+    rank of the group must call it (same layer order), forward and backward."""
+    return _EpMoeFn.apply(x, router_w, router_bias, w_gu_local, w_down_local, int(top_k), ep, shapes)

@@ -10,6 +10,74 @@ sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
 sys.path.insert(0, str(Path(__file__).resolve().parent))
 
 
+def ep_main():
+    """Expert-parallel MoE FFN over peer memory == the single-rank layer on the same tokens."""
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    from datetime import timedelta
+
+    dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=90))
+    from prometheus_b200.ops import functional as ops
+    from prometheus_b200.ops import moe
+    from prometheus_b200.parallel.ep import EpContext, ep_moe_ffn
+    from prometheus_b200.parallel.symm import SymmetricGroup
+
+    T, d, E, h, k = 384, 256, 8, 192, 2
+    El = E // world
+    gen = torch.Generator(device=dev).manual_seed(0)            # same weights on every rank
+    r = lambda *s, scale=1.0: (torch.randn(*s, device=dev, generator=gen) * scale).bfloat16()
+    rw, wgu, wd = r(E, d, scale=0.2), r(E, 2 * h, d, scale=0.08), r(E, d, h, scale=0.08)
+    bias = (torch.randn(E, device=dev, generator=gen) * 0.05).float()
+    gen_x = torch.Generator(device=dev).manual_seed(100 + rank)  # different tokens per rank
+    x = (torch.randn(T, d, device=dev, generator=gen_x)).bfloat16().requires_grad_(True)
+    go = (torch.randn(T, d, device=dev, generator=gen_x)).bfloat16()
+    grp = SymmetricGroup(wait_budget_s=10.0)
+    ep = EpContext(grp, d, E, max_rows=world * T * k + El * 128)
+    rw_l = rw.clone().requires_grad_(True)
+    wgu_l = wgu[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    wd_l = wd[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    for it in range(2):                                          # twice: buffers are reused
+        for t in (x, rw_l, wgu_l, wd_l):
+            t.grad = None
+        out, probs, ids = ep_moe_ffn(x, rw_l, bias, wgu_l, wd_l, k, ep)
+        (out.float() * go.float()).sum().backward()
+    torch.cuda.synchronize()
+    grp.check()
+    ops.check_status(dev)
+    # reference: the all-local layer on my tokens with the full expert set
+    leaves = [t.detach().clone().requires_grad_(True) for t in (x, rw, wgu, wd)]
+    o_ref, p_ref, i_ref = moe.moe_ffn(leaves[0], leaves[1], bias, leaves[2], leaves[3], k)
+    (o_ref.float() * go.float()).sum().backward()
+    torch.cuda.synchronize()
+
+    def close(a, b, tol, what):
+        err = (a.float() - b.float()).abs().max().item()
+        sc = b.float().abs().max().item() + 1e-6
+        assert err <= tol * sc, f"{what}: err {err:.4g} scale {sc:.4g}"
+
+    assert torch.equal(ids, i_ref)
+    close(out, o_ref, 1e-2, "out")
+    close(x.grad, leaves[0].grad, 2e-2, "dx")
+    close(rw_l.grad, leaves[1].grad, 2e-2, "d_router")
+    # expert gradients: my experts see the tokens of every rank
+    full_gu, full_d = leaves[2].grad.float().clone(), leaves[3].grad.float().clone()
+    dist.all_reduce(full_gu)
+    dist.all_reduce(full_d)
+    close(wgu_l.grad, full_gu[rank * El:(rank + 1) * El], 2e-2, "d_gate_up")
+    close(wd_l.grad, full_d[rank * El:(rank + 1) * El], 2e-2, "d_down")
+    # overflow is reported, not silent
+    small = EpContext(grp, d, E, max_rows=128)
+    ep_moe_ffn(x.detach(), rw, bias, wgu[rank * El:(rank + 1) * El], wd[rank * El:(rank + 1) * El], k, small)
+    torch.cuda.synchronize()
+    assert int(grp.status.item()) == 4
+    grp.status.zero_()
+    dist.barrier()
+    if rank == 0:
+        print("EP_OK")
+    dist.destroy_process_group()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -92,7 +160,7 @@ def main():
 
 if __name__ == "__main__":
     try:
-        main()
+        ep_main() if sys.argv[1:] == ["ep"] else main()
     except BaseException:
         import traceback
 

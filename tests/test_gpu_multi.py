@@ -10,13 +10,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_rank_symmetric_memory_and_trainer():
-    world = 2
+def _run_ranks(world, port, marker, *args):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", "29517",
-           str(Path(__file__).parent / "_multi_gpu_worker.py")]
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
+           str(Path(__file__).parent / "_multi_gpu_worker.py"), *args]
     import signal
     import tempfile
 
@@ -30,4 +28,14 @@ def test_two_rank_symmetric_memory_and_trainer():
             rc = -9
         log.seek(0)
         text = log.read()
-    assert rc == 0 and "MULTI_GPU_OK" in text, text[-4000:]
+    assert rc == 0 and marker in text, text[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_symmetric_memory_and_trainer():
+    _run_ranks(2, 29517, "MULTI_GPU_OK")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_expert_parallel_moe():
+    _run_ranks(2, 29519, "EP_OK", "ep")
