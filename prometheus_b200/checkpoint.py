@@ -58,15 +58,20 @@ def _full_state(tr) -> dict[str, torch.Tensor]:
     import torch.distributed as dist
 
     out = dict(bufs)
-    ranges = []
-    for (rows, cols), units in tr.unit_classes.items():
-        lo_u, hi_u = tr.own_units[(rows, cols)]
-        ranges.append((units[0].off + lo_u * rows * cols, units[0].off + hi_u * rows * cols))
+    ranges, local_ranges = [], []
+    for key, units in tr.unit_classes.items():
+        rows, cols = key[:2]
+        lo_u, hi_u = tr.own_units[key]
+        rng = (units[0].off + lo_u * rows * cols, units[0].off + hi_u * rows * cols)
+        # expert-parallel weights are each rank's own: kept local here, saved as per-rank shards
+        (local_ranges if len(key) > 2 else ranges).append(rng)
     for key in ("muon.master", "muon.mom"):
         full = torch.zeros_like(bufs[key])
         for lo, hi in ranges:
             full[lo:hi] = bufs[key][lo:hi]
         dist.all_reduce(full, group=tr.pg)
+        for lo, hi in local_ranges:
+            full[lo:hi] = bufs[key][lo:hi]
         out[key] = full
     a_lo, a_hi = tr.own_adam
     for key in ("adam.master", "adam.m", "adam.v"):
@@ -84,21 +89,41 @@ def capture(tr, *, rung: int = 0, data_mix_hash: str = ZERO_HASH, tokenizer_id: 
     C = _ck()
     state = _full_state(tr)
     weights, opt, wmeta, ometa = [], [], [], []
+    sharded = getattr(tr, "world", 1) > 1 and getattr(tr, "sym", None) is not None
+
+    def per_rank(t: torch.Tensor, local: bool):
+        """[(shard_rank, bytes)]: one shard, or one per rank for expert-parallel weights."""
+        if not (local and sharded):
+            return [(0, _bytes(t))]
+        import torch.distributed as dist
+
+        parts = [torch.empty_like(t) for _ in range(tr.world)]
+        dist.all_gather(parts, t.contiguous(), group=tr.pg)
+        return [(r, _bytes(p)) for r, p in enumerate(parts)]
+
     for w in tr.weights.values():
         n = int(math.prod(w.shape))
         sl = slice(w.off, w.off + n)
         g = w.group
-        blob = _bytes(state[f"{g}.master"][sl])
-        weights.append(C.ShardBlob(w.name, 0, blob))
-        wmeta.append(C.WeightMeta(w.name, 0, list(w.shape), "fp32", C.sha256_hex(blob), []))
+        local = bool(getattr(w, "local", False))
+        axes = ["ep"] if local and sharded else []
+        for r, blob in per_rank(state[f"{g}.master"][sl], local):
+            weights.append(C.ShardBlob(w.name, r, blob))
+            wmeta.append(C.WeightMeta(w.name, r, list(w.shape), "fp32", C.sha256_hex(blob), axes))
         if g == "muon":
             parts = [("mom", "muon", state["muon.mom"][sl])]
         else:
             parts = [("m", "adamw", state[f"{g}.m"][sl]), ("v", "adamw", state[f"{g}.v"][sl])]
         for suffix, kind, t in parts:
-            ob = _bytes(t)
-            opt.append(C.ShardBlob(f"{w.name}.{suffix}", 0, ob))
-            ometa.append(C.OptimizerMeta(f"{w.name}.{suffix}", 0, kind, C.sha256_hex(ob)))
+            for r, ob in per_rank(t, local):
+                opt.append(C.ShardBlob(f"{w.name}.{suffix}", r, ob))
+                ometa.append(C.OptimizerMeta(f"{w.name}.{suffix}", r, kind, C.sha256_hex(ob)))
+    # aux-loss-free balancing biases: state without an optimizer (same on every rank)
+    for i, b in sorted(getattr(tr, "router_bias", {}).items()):
+        blob = _bytes(b.float())
+        name = f"layers.{i}.router_bias"
+        weights.append(C.ShardBlob(name, 0, blob))
+        wmeta.append(C.WeightMeta(name, 0, [int(b.numel())], "fp32", C.sha256_hex(blob), []))
     m = C.Manifest()
     m.step = int(tr.step_count)
     m.rung = int(rung)
@@ -107,6 +132,7 @@ def capture(tr, *, rung: int = 0, data_mix_hash: str = ZERO_HASH, tokenizer_id: 
     m.tokenizer_id = tokenizer_id
     m.precision = ("bf16", "none")
     m.dp = int(tr.world)
+    m.ep = int(tr.world) if getattr(tr, "ep", False) else 1
     m.weights, m.optimizer = wmeta, ometa
     if loader_state is not None:
         m.loader_state_json = json.dumps(loader_state, sort_keys=True, separators=(",", ":"))
@@ -133,8 +159,16 @@ def apply(tr, ckpt, *, strict_config: bool = True) -> dict[str, Any] | None:
     m = ckpt.manifest
     if strict_config and m.model_config_hash != model_config_hash(tr.cfg):
         raise ValueError("checkpoint was written for a different model configuration")
-    wb = {b.name: b.bytes for b in ckpt.weights}
-    ob = {b.name: b.bytes for b in ckpt.optimizer}
+    me = int(getattr(tr, "rank", 0))
+
+    def by_name(blobs):
+        out = {}
+        for b in blobs:     # a rank's own shard wins over shard 0
+            if b.name not in out or b.shard_rank == me:
+                out[b.name] = b.bytes
+        return out
+
+    wb, ob = by_name(ckpt.weights), by_name(ckpt.optimizer)
     dev = tr.device
 
     def put(dst: torch.Tensor, raw: bytes, what: str):
@@ -158,6 +192,10 @@ def apply(tr, ckpt, *, strict_config: bool = True) -> dict[str, Any] | None:
                 put(vv[sl], ob[w.name + ".v"], w.name + ".v")
         tr.muon_lp.copy_(tr.muon_master)
         tr.adam_lp.copy_(tr.adam_master)
+        for i, b in getattr(tr, "router_bias", {}).items():
+            name = f"layers.{i}.router_bias"
+            if name in wb:
+                put(b, wb[name], name)
     tr.step_count = int(m.step)
     if getattr(tr, "sym", None) is not None:
         torch.cuda.synchronize()

@@ -61,6 +61,8 @@ class Weight:
     off: int = 0
     units: list = field(default_factory=list)
     sources: list = field(default_factory=list)   # [(tree_name, row0, rows, to_engine, to_tree)]
+    local: bool = False   # expert-parallel: this rank's experts only (no gradient reduction,
+                          # no broadcast of the update)
 
 
 def _t2(x: Tensor) -> Tensor:
@@ -89,7 +91,8 @@ class Trainer:
     def __init__(self, model_config: M.ModelConfig, train_config: T.TrainConfig, *,
                  params: dict | None = None, seed: int = 0, device="cuda", micro_batch: int = 4,
                  muon_weight_decay: float = 0.0, process_group=None, ce_chunk_rows: int = 4096,
-                 grad_sync: str = "auto"):
+                 grad_sync: str = "auto", expert_parallel: bool = False,
+                 ep_capacity_factor: float = 2.0):
         M.validate_config(model_config)
         T.validate_train_config(train_config)
         self.cfg, self.tcfg = model_config, train_config
@@ -104,6 +107,11 @@ class Trainer:
             self.world = torch.distributed.get_world_size(process_group)
             self.rank = torch.distributed.get_rank(process_group)
         self.grad_sync = grad_sync
+        self.ep = bool(expert_parallel) and self.world > 1 and model_config.n_moe > 0
+        self.ep_capacity_factor = float(ep_capacity_factor)
+        self.ep_ctx = None
+        if self.ep and model_config.n_routed_experts % self.world:
+            raise ValueError("expert parallelism needs n_routed_experts divisible by the world size")
         self.ce_chunk_rows = int(ce_chunk_rows)
         self.step_count = 0
         self.launches = 0
@@ -124,10 +132,11 @@ class Trainer:
         d = cfg.d_model
         ws: list[Weight] = []
 
-        def mat(name, shape, sources, unit_rows=None):
-            w = Weight(name=name, shape=tuple(shape), group="muon", lp=True, sources=sources)
+        def mat(name, shape, sources, unit_rows=None, local=False):
+            w = Weight(name=name, shape=tuple(shape), group="muon", lp=True, sources=sources,
+                       local=local)
             rows, cols = shape
-            if min(rows if unit_rows is None else min(unit_rows), cols) < 32:
+            if min(rows if unit_rows is None else min(unit_rows), cols) < 32 and not local:
                 w.group = "adam"
             else:
                 r0 = 0
@@ -198,6 +207,22 @@ class Trainer:
                 self.moe_layers.append(i)
                 mat(p + "router", (n_r, d), [src(p + "router", 0, n_r)])
                 gu_src, dn_src = [], []
+                if self.ep:
+                    # this rank's routed experts only; shared experts are replicated dense FFNs
+                    el = n_r // self.world
+                    for j in range(el):
+                        e = self.rank * el + j
+                        gu_src.append((p + "routed_gate", 2 * j * hid, hid, ("e", e), None))
+                        gu_src.append((p + "routed_up", (2 * j + 1) * hid, hid, ("e", e), None))
+                        dn_src.append((p + "routed_down", j * d, d, ("e", e), None))
+                    mat(p + "moe_gu", (2 * hid * el, d), gu_src, unit_rows=[hid] * (2 * el), local=True)
+                    mat(p + "moe_down", (d * el, hid), dn_src, unit_rows=[d] * el, local=True)
+                    for j in range(n_s):
+                        mat(p + f"shared{j}_gate_up", (2 * hid, d),
+                            [(p + "shared_gate", 0, hid, ("e", j), None),
+                             (p + "shared_up", hid, hid, ("e", j), None)], unit_rows=[hid, hid])
+                        mat(p + f"shared{j}_down", (d, hid), [(p + "shared_down", 0, d, ("e", j), None)])
+                    continue
                 for e in range(n_r + n_s):
                     kind_, idx = ("routed", e) if e < n_r else ("shared", e - n_r)
                     gu_src.append((p + kind_ + "_gate", 2 * e * hid, hid, ("e", idx), None))
@@ -211,7 +236,8 @@ class Trainer:
         classes: dict[tuple, list[Unit]] = {}
         for w in ws:
             for u in w.units:
-                classes.setdefault((u.rows, u.cols), []).append(u)
+                key = (u.rows, u.cols, 1) if w.local else (u.rows, u.cols)
+                classes.setdefault(key, []).append(u)
         self.unit_classes = classes
         off = 0
         for key in sorted(classes):
@@ -283,15 +309,15 @@ class Trainer:
         from .parallel.fsdp import split_bounds
 
         w_, r_ = (self.world, self.rank) if self.sym is not None else (1, 0)
-        self.own_units = {key: split_bounds(len(us), w_, r_)
+        self.own_units = {key: ((0, len(us)) if len(key) > 2 else split_bounds(len(us), w_, r_))
                           for key, us in self.unit_classes.items()}
         a_lo, a_hi = split_bounds(n_a // 8, w_, r_)
         self.own_adam = (a_lo * 8, a_hi * 8)
-        max_unit = max((r * c * (self.own_units[(r, c)][1] - self.own_units[(r, c)][0])
-                        for (r, c) in self.unit_classes), default=1)
+        max_unit = max((k_[0] * k_[1] * (self.own_units[k_][1] - self.own_units[k_][0])
+                        for k_ in self.unit_classes), default=1)
         self.ns_x = [torch.empty(max(max_unit, 1), dtype=BF16, device=dev) for _ in range(2)]
-        max_g = max((min(r, c) ** 2 * (self.own_units[(r, c)][1] - self.own_units[(r, c)][0])
-                     for (r, c) in self.unit_classes), default=1)
+        max_g = max((min(k_[0], k_[1]) ** 2 * (self.own_units[k_][1] - self.own_units[k_][0])
+                     for k_ in self.unit_classes), default=1)
         self.ns_g = [torch.empty(max(max_g, 1), dtype=BF16, device=dev) for _ in range(2)]
         nparts = max(_lib.query("pb_sumsq_nparts", max(n_m, n_a, n_v, 1)), 1)
         if self.sym is not None:
@@ -355,16 +381,23 @@ class Trainer:
         import torch.distributed as dist
 
         muon = torch.zeros_like(self.muon_master)
-        for (rows, cols), units in self.unit_classes.items():
-            lo_u, hi_u = self.own_units[(rows, cols)]
+        local_ranges = []
+        for key, units in self.unit_classes.items():
+            rows, cols = key[:2]
+            lo_u, hi_u = self.own_units[key]
             lo = units[0].off + lo_u * rows * cols
             hi = units[0].off + hi_u * rows * cols
-            muon[lo:hi] = self.muon_master[lo:hi]
+            if len(key) > 2:
+                local_ranges.append((lo, hi))      # this rank's experts: not summed
+            else:
+                muon[lo:hi] = self.muon_master[lo:hi]
         adam = torch.zeros_like(self.adam_master)
         a_lo, a_hi = self.own_adam
         adam[a_lo:a_hi] = self.adam_master[a_lo:a_hi]
         dist.all_reduce(muon, group=self.pg)
         dist.all_reduce(adam, group=self.pg)
+        for lo, hi in local_ranges:
+            muon[lo:hi] = self.muon_master[lo:hi]
         return {"muon": muon, "adam": adam, "vec": self.vec_master}
 
     def export_tree(self) -> dict:
@@ -394,6 +427,16 @@ class Trainer:
                 else:
                     t = blk.clone()
                 out[tree_name] = t
+        if self.ep:
+            # every rank holds a slice of the routed experts: exchange them (host side)
+            import torch.distributed as dist
+
+            every = [None] * self.world
+            dist.all_gather_object(every, {k: v for k, v in stacked.items() if "routed_" in k},
+                                   group=self.pg)
+            for part in every:
+                for tree_name, blocks in part.items():
+                    stacked.setdefault(tree_name, {}).update(blocks)
         for tree_name, parts in stacked.items():
             out[tree_name] = torch.stack([parts[j] for j in range(len(parts))])
         for i, b in self.router_bias.items():
@@ -449,10 +492,26 @@ class Trainer:
 
         cfg = self.cfg
         pre = f"layers.{i}."
-        n_e = cfg.n_routed_experts + cfg.n_shared_experts
         hid = cfg.expert_hidden
         w_gu = self.p[pre + "moe_gu"]
         w_dn = self.p[pre + "moe_down"]
+        if self.ep:
+            from .parallel.ep import EpContext, ep_moe_ffn
+
+            T_ = n2.shape[0]
+            el = cfg.n_routed_experts // self.world
+            if self.ep_ctx is None:
+                rows = int(self.ep_capacity_factor * T_ * cfg.top_k) + 128 * el
+                self.ep_ctx = EpContext(self.sym, cfg.d_model, cfg.n_routed_experts, rows)
+            out, probs, ids = ep_moe_ffn(n2, self.p[pre + "router"], self.router_bias.get(i), w_gu,
+                                         w_dn, cfg.top_k, self.ep_ctx,
+                                         shapes=((el, 2 * hid, cfg.d_model), (el, cfg.d_model, hid)))
+            for j in range(cfg.n_shared_experts):
+                gu = ops.linear(n2, self.p[pre + f"shared{j}_gate_up"])
+                out = out + ops.linear(ops.swiglu(gu), self.p[pre + f"shared{j}_down"])
+            self.last_router = (probs, ids)
+            return out
+        n_e = cfg.n_routed_experts + cfg.n_shared_experts
         out, probs, ids = moe.moe_ffn(n2, self.p[pre + "router"], self.router_bias.get(i),
                                       w_gu, w_dn, cfg.top_k, n_shared=cfg.n_shared_experts,
                                       shapes=((n_e, 2 * hid, cfg.d_model), (n_e, cfg.d_model, hid)))
@@ -563,12 +622,17 @@ class Trainer:
         sym = self.sym
         sym.barrier(0)                      # every rank's backward is complete
         first = True
-        for (rows, cols), units in sorted(self.unit_classes.items()):
-            lo_u, hi_u = self.own_units[(rows, cols)]
+        for key, units in sorted(self.unit_classes.items()):
+            rows, cols = key[:2]
+            lo_u, hi_u = self.own_units[key]
             if hi_u > lo_u:
                 lo = units[0].off + lo_u * rows * cols
-                sym.reduce_to_owner(self.sym_grad, 0, lo, (hi_u - lo_u) * rows * cols,
-                                    self.muon_grad, self.opt_scratch, self.local_sq, not first)
+                if len(key) > 2:       # this rank's experts: the local gradient is the gradient
+                    call("pb_sumsq_f32", ptr(self.muon_grad[lo:]), (hi_u - lo_u) * rows * cols,
+                         ptr(self.opt_scratch), ptr(self.local_sq), 0 if first else 1, st)
+                else:
+                    sym.reduce_to_owner(self.sym_grad, 0, lo, (hi_u - lo_u) * rows * cols,
+                                        self.muon_grad, self.opt_scratch, self.local_sq, not first)
                 first = False
         a_lo, a_hi = self.own_adam
         if a_hi > a_lo:
@@ -631,8 +695,9 @@ class Trainer:
                  a_hi - a_lo, *hp, step, ptr(self.gnorm_sq), clip, gscale, st)
         lr = float(tc.muon_lr) * lr_mult
         beta = float(tc.muon_momentum)
-        for (rows, cols), units in sorted(self.unit_classes.items()):
-            lo_u, hi_u = self.own_units[(rows, cols)]
+        for key, units in sorted(self.unit_classes.items()):
+            rows, cols = key[:2]
+            lo_u, hi_u = self.own_units[key]
             nb = hi_u - lo_u
             if nb == 0:
                 continue
@@ -646,7 +711,7 @@ class Trainer:
                      ptr(self.opt_scratch), st)
             xo = self._newton_schulz_class(rows, cols, nb, int(tc.muon_ns_steps))
             scale = T.muon_rms_scale(rows, cols)
-            if self.sym is None:
+            if self.sym is None or len(key) > 2:
                 call("pb_muon_apply", ptr(self.muon_master[base:]), ptr(xo),
                      ptr(self.muon_lp[base:]), n * nb, lr, scale, self.muon_wd, st)
             else:

@@ -78,6 +78,64 @@ def ep_main():
     dist.destroy_process_group()
 
 
+def ep_engine_main():
+    """Trainer with expert-parallel MoE layers == the replicated-expert trainer."""
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    from datetime import timedelta
+
+    dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=90))
+    from prometheus_b200 import checkpoint, engine, model, train
+    from test_gpu_engine import small_moe
+
+    cfg = small_moe()
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=50, decay_steps=5)
+    params = model.init_params(cfg, 0)
+    tokens = torch.randint(0, cfg.vocab_size, (2 * world, 128),
+                           generator=torch.Generator().manual_seed(3)).to(dev)
+    mine = tokens[2 * rank:2 * rank + 2]
+    runs = {}
+    for ep in (True, False):
+        tr = engine.Trainer(cfg, tcfg, params=params, device=dev, micro_batch=2, grad_sync="p2p",
+                            expert_parallel=ep)
+        assert tr.ep == ep and tr.sym is not None
+        losses = [tr.step(mine)["loss"].item() for _ in range(3)]
+        tr.sym.check()
+        runs[ep] = (losses, tr)
+    la, lb = runs[True][0], runs[False][0]
+    assert abs(la[0] - lb[0]) < 5e-3 * lb[0], (la, lb)
+    for a, b in zip(la, lb):
+        assert abs(a - b) < 2e-2 * b, (la, lb)
+    tr = runs[True][1]
+    # the local expert slabs really are this rank's experts
+    el = cfg.n_routed_experts // world
+    assert tr.p["layers.1.moe_gu"].shape == (2 * cfg.expert_hidden * el, cfg.d_model)
+    tree = model.flatten_params(tr.export_tree())
+    assert tree["layers.1.routed_gate"].shape[0] == cfg.n_routed_experts
+    ref_tree = model.flatten_params(runs[False][1].export_tree())
+    f0 = model.flatten_params(params)
+    for name in ("layers.1.routed_gate", "layers.2.routed_down", "layers.1.shared_up", "layers.1.router"):
+        ua, ub = (tree[name] - f0[name]).float(), (ref_tree[name] - f0[name]).float()
+        rel = (ua - ub).norm().item() / (ub.norm().item() + 1e-12)
+        assert rel < 0.5, (name, rel)
+    # checkpoint: per-rank expert shards, restored bit-exactly into a fresh EP trainer
+    ck = checkpoint.capture(tr)
+    ranks = sorted({w.shard_rank for w in ck.manifest.weights if w.name == "layers.1.moe_gu"})
+    assert ranks == list(range(world)) and ck.manifest.ep == world
+    fresh = engine.Trainer(cfg, tcfg, seed=5, device=dev, micro_batch=2, grad_sync="p2p",
+                           expert_parallel=True)
+    checkpoint.apply(fresh, ck)
+    assert torch.equal(fresh.muon_master, checkpoint._full_state(tr)["muon.master"])
+    l1 = tr.step(mine)["loss"].item()
+    l2 = fresh.step(mine)["loss"].item()
+    assert l1 == l2, (l1, l2)
+    dist.barrier()
+    if rank == 0:
+        print("EP_ENGINE_OK", la, lb)
+    dist.destroy_process_group()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -160,7 +218,7 @@ def main():
 
 if __name__ == "__main__":
     try:
-        ep_main() if sys.argv[1:] == ["ep"] else main()
+        {"ep": ep_main, "ep_engine": ep_engine_main}.get((sys.argv[1:] or [""])[0], main)()
     except BaseException:
         import traceback
 

@@ -39,3 +39,8 @@ def test_two_rank_symmetric_memory_and_trainer():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_expert_parallel_moe():
     _run_ranks(2, 29519, "EP_OK", "ep")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_expert_parallel_trainer():
+    _run_ranks(2, 29521, "EP_ENGINE_OK", "ep_engine")
