@@ -10,6 +10,7 @@ void bind_ckpt(py::module_& m);
 void bind_control(py::module_& m);
 void bind_obs(py::module_& m);
 void bind_harness_core(py::module_& m);
+void bind_harness_queue(py::module_& m);
 
 PYBIND11_MODULE(_pb200_native, m) {
   m.doc() = "C++ systems components of prometheus_b200 (loader, checkpoints, control, ...)";
@@ -33,4 +34,5 @@ PYBIND11_MODULE(_pb200_native, m) {
   auto obs = m.def_submodule("obs", "metrics, tracing, run registry, spike log");
   bind_obs(obs);
   bind_harness_core(m);
+  bind_harness_queue(m);
 }
