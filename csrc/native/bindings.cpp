@@ -11,6 +11,7 @@ void bind_control(py::module_& m);
 void bind_obs(py::module_& m);
 void bind_harness_core(py::module_& m);
 void bind_harness_queue(py::module_& m);
+void bind_harness_control(py::module_& m);
 
 PYBIND11_MODULE(_pb200_native, m) {
   m.doc() = "C++ systems components of prometheus_b200 (loader, checkpoints, control, ...)";
@@ -35,4 +36,5 @@ PYBIND11_MODULE(_pb200_native, m) {
   bind_obs(obs);
   bind_harness_core(m);
   bind_harness_queue(m);
+  bind_harness_control(m);
 }
