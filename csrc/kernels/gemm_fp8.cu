@@ -1,0 +1,354 @@
+// Block-scaled FP8 (e4m3) GEMM on tcgen05 and the quantisers that feed it (sm_100a).
+//
+//   C[M, N] (bf16) = sum over K-blocks kb of  sa[kb, m] * sb[n / 128, kb] * (Aq_kb . Bq_kb^T)
+//
+// Aq [M, K] e4m3 with one fp32 scale per row per 128 contraction elements (stored
+// [K / 128, M] so a warp reads consecutive rows), Bq [N, K] e4m3 with one scale per
+// 128 x 128 block. Exactly the arithmetic of quantise -> dequantise -> fp32 matmul, with the
+// dequantisation applied to the 128-deep partial products instead of to the operands.
+//
+// One CTA per SM, persistent over 128 x 128 output tiles:
+//   warp 0   TMA producer: per K-block one 128 x 128 B tile of A and of B (128 bytes per row =
+//            one swizzle atom), 6-stage ring
+//   warp 1   MMA issuer: four kind::f8f6f4 MMAs (K = 32) per K-block into one of two
+//            tensor-memory accumulators, fresh (not accumulated) for every K-block
+//   warps 2-5  promotion + epilogue: each thread owns one output row; per K-block it reads the
+//            128 partial sums of its row from tensor memory, scales them by sa * sb and adds
+//            them to 128 fp32 registers; after the last K-block the row goes out as bf16
+//            through a swizzled staging tile and a TMA store
+// Grouped mode (mixture-of-experts): row block m multiplies expert mblk_group[m] of a
+// [groups, N, K] weight tensor with scales [groups, N / 128, K / 128]; negative = skip.
+//
+// Quantisers: pb_fp8_quant_rows (1 x 128 blocks, writes q and the [K / 128, M] scales) and
+// pb_fp8_quant_blocks (128 x 128 blocks). scale = amax / 448, or 1 for an all-zero block.
+//
+// Reference semantics: kernels/__init__.py fp8_quantize / fp8_linear of the reference
+// (block 128, e4m3, scale = amax / 448).
+#include <cuda.h>
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace pb {
+
+int make_tmap_3d(CUtensorMap* tm, const void* base, int elem_bytes, uint64_t inner,
+                 uint64_t outer, uint64_t batch, uint64_t ld_elems, uint64_t batch_stride_elems,
+                 uint32_t box_inner, uint32_t box_outer);
+int num_sms();
+
+namespace f8 {
+
+constexpr int BM = 128, BN = 128, BK = 128;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int EPI_BYTES = 4 * 2 * 4096;
+constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+
+struct Params {
+  int M, N, K;
+  const float* sa;     // [K / 128, M]
+  const float* sb;     // [groups, ceil(N / 128), K / 128]
+  const int* mblk_group;
+  int* status;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmC, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* smA = smem;
+  uint8_t* smB = smem + STAGES * A_BYTES;
+  uint8_t* smEpi = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + EPI_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int nkb = p.K / BK;
+  const long total = static_cast<long>(num_m) * num_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 128);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // n-major inside groups of 8 row blocks, like the bf16 kernel: B tiles stay in L2
+  auto coords = [&](long t, int& m_blk, int& n_blk) {
+    const int r = static_cast<int>(t);
+    const int group = 8 * num_n;
+    const int first_m = (r / group) * 8;
+    const int gsz = min(num_m - first_m, 8);
+    m_blk = first_m + (r % group) % gsz;
+    n_blk = (r % group) / gsz;
+  };
+  auto group_of = [&](int m_blk) { return p.mblk_group ? p.mblk_group[m_blk] : 0; };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        coords(t, m_blk, n_blk);
+        const int g = group_of(m_blk);
+        if (g < 0) continue;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_3d(smA + s * A_BYTES, &tmA, &full[s], kb * BK, m_blk * BM, 0);
+          tma_load_3d(smB + s * B_BYTES, &tmB, &full[s], kb * BK, n_blk * BN, g);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(0, 0, BM, BN, 0, 0);   // e4m3 x e4m3, both K-major
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t it = 0;        // K-blocks issued so far: picks the accumulator and its phase
+      bool ok = true;
+      for (long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        coords(t, m_blk, n_blk);
+        if (group_of(m_blk) < 0) continue;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int acc = it & 1;
+          if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
+          if (!mbar_wait(&full[s], ph, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smA + s * A_BYTES);
+          const uint32_t b_addr = smem_u32(smB + s * B_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / 32; ++j)
+            umma_f8(tmem_base + acc * BN, make_sdesc_sw128(a_addr + j * 32, 16, 1024),
+                    make_sdesc_sw128(b_addr + j * 32, 16, 1024), idesc, j > 0 ? 1u : 0u);
+          umma_commit(&empty[s]);
+          umma_commit(&tfull[acc]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;            // tensor-memory lane quarter of this warp
+    const int n_sb = p.K / BK;
+    uint32_t it = 0;
+    bool ok = true;
+    uint8_t* my_epi = smEpi + (warp - 2) * 8192;
+    for (long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      int m_blk, n_blk;
+      coords(t, m_blk, n_blk);
+      const int g = group_of(m_blk);
+      if (g < 0) continue;
+      const int row = m_blk * BM + q * 32 + lane;
+      const int srow = min(row, p.M - 1);
+      const float* sb = p.sb + (static_cast<size_t>(g) * num_n + n_blk) * n_sb;
+      float acc[BN];
+#pragma unroll
+      for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int a = it & 1;
+        const float scale = p.sa[static_cast<size_t>(kb) * p.M + srow] * sb[kb];
+        if (!mbar_wait(&tfull[a], (it >> 1) & 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + a * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(scale, __uint_as_float(r[i]), acc[c + i]);
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty[a]);
+      }
+      if (!ok) break;
+      // row -> bf16 -> two 64-column slabs in the TMA swizzle layout -> bulk tensor stores
+      const int y0 = m_blk * BM + q * 32;
+#pragma unroll
+      for (int sl = 0; sl < 2; ++sl) {
+        uint8_t* buf = my_epi + sl * 4096;
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          bf16x8 pk;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            pk.v[j] = __floats2bfloat162_rn(acc[sl * 64 + 8 * i + 2 * j], acc[sl * 64 + 8 * i + 2 * j + 1]);
+          *reinterpret_cast<bf16x8*>(rowp + ((i ^ (lane & 7)) << 4)) = pk;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        const int x0 = n_blk * BN + sl * 64;
+        if (lane == 0 && x0 < p.N && y0 < p.M) tma_store_3d(&tmC, buf, x0, y0, 0);
+        if (lane == 0) tma_store_commit();
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != PB_OK) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies in flight land
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------------------ quantisers
+__device__ __forceinline__ uint32_t to_e4m3x4(float a, float b, float c, float d) {
+  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+// One warp per (row, 128-element block); K a multiple of 128.
+__global__ void quant_rows_kernel(const bf16* __restrict__ x, long ld, int M, int K,
+                                  uint8_t* __restrict__ q, float* __restrict__ scales) {
+  const long w = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nkb = K / 128;
+  if (w >= static_cast<long>(M) * nkb) return;
+  const int row = static_cast<int>(w / nkb), kb = static_cast<int>(w % nkb);
+  const bf16* src = x + static_cast<size_t>(row) * ld + kb * 128 + lane * 4;
+  const uint2 raw = *reinterpret_cast<const uint2*>(src);
+  const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  const float f0 = __low2float(p0), f1 = __high2float(p0), f2 = __low2float(p1), f3 = __high2float(p1);
+  const float amax = warp_max(fmaxf(fmaxf(fabsf(f0), fabsf(f1)), fmaxf(fabsf(f2), fabsf(f3))));
+  const float scale = amax > 0.f ? amax / 448.f : 1.f;
+  // true division (not a reciprocal multiply): ties must round as in x / scale
+  *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(row) * K + kb * 128 + lane * 4) =
+      to_e4m3x4(__fdiv_rn(f0, scale), __fdiv_rn(f1, scale), __fdiv_rn(f2, scale), __fdiv_rn(f3, scale));
+  if (lane == 0) scales[static_cast<size_t>(kb) * M + row] = scale;
+}
+
+// One CTA (256 threads) per 128 x 128 block of a [N, K] matrix (edges clipped).
+__global__ void quant_blocks_kernel(const bf16* __restrict__ w, long ld, int N, int K,
+                                    uint8_t* __restrict__ q, float* __restrict__ scales) {
+  __shared__ float red[33];
+  const int nb = blockIdx.y, kb = blockIdx.x;
+  const int r0 = nb * 128, c0 = kb * 128;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < 128 * 32; i += blockDim.x) {
+    const int r = r0 + i / 32, c = c0 + (i % 32) * 4;
+    if (r < N && c < K) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(w + static_cast<size_t>(r) * ld + c);
+      const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+      const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+      amax = fmaxf(amax, fmaxf(fmaxf(fabsf(__low2float(p0)), fabsf(__high2float(p0))),
+                               fmaxf(fabsf(__low2float(p1)), fabsf(__high2float(p1)))));
+    }
+  }
+  amax = block_max(amax, red);
+  const float scale = amax > 0.f ? amax / 448.f : 1.f;
+  for (int i = threadIdx.x; i < 128 * 32; i += blockDim.x) {
+    const int r = r0 + i / 32, c = c0 + (i % 32) * 4;
+    if (r < N && c < K) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(w + static_cast<size_t>(r) * ld + c);
+      const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+      const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+      *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(r) * K + c) =
+          to_e4m3x4(__fdiv_rn(__low2float(p0), scale), __fdiv_rn(__high2float(p0), scale),
+                    __fdiv_rn(__low2float(p1), scale), __fdiv_rn(__high2float(p1), scale));
+    }
+  }
+  if (threadIdx.x == 0) scales[static_cast<size_t>(nb) * gridDim.x + kb] = scale;
+}
+
+}  // namespace f8
+}  // namespace pb
+
+using namespace pb;
+
+// x [M, K] bf16 (row stride ld, K % 128 == 0) -> q [M, K] e4m3, scales [K / 128, M] fp32.
+PB_API int pb_fp8_quant_rows(const void* x, long ld, int M, int K, void* q, float* scales,
+                             cudaStream_t st) {
+  if (M <= 0 || K <= 0 || K % 128 != 0 || ld % 4 != 0) return PB_BAD_ARG;
+  const long warps = static_cast<long>(M) * (K / 128);
+  const long blocks = (warps * 32 + 255) / 256;
+  f8::quant_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+      static_cast<const bf16*>(x), ld, M, K, static_cast<uint8_t*>(q), scales);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// w [groups * N, K] bf16 (K % 128 == 0, N % 128 == 0 when groups > 1) -> q e4m3 same shape,
+// scales [groups * ceil(N / 128), K / 128].
+PB_API int pb_fp8_quant_blocks(const void* w, long ld, int rows, int K, void* q, float* scales,
+                               cudaStream_t st) {
+  if (rows <= 0 || K <= 0 || K % 128 != 0 || ld % 4 != 0) return PB_BAD_ARG;
+  dim3 grid(K / 128, (rows + 127) / 128);
+  f8::quant_blocks_kernel<<<grid, 256, 0, st>>>(static_cast<const bf16*>(w), ld, rows, K,
+                                                static_cast<uint8_t*>(q), scales);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// C [M, N] bf16 = block-scaled Aq [M, K] x Bq [groups, N, K]^T. K % 128 == 0, N % 8 == 0.
+// sa [K / 128, M]; sb [groups, ceil(N / 128), K / 128]; mblk_group null (groups == 1) or one
+// int per 128-row block of A / C.
+PB_API int pb_gemm_fp8_blockscaled(const void* Aq, const float* sa, const void* Bq, const float* sb,
+                                   void* C, int M, int N, int K, int groups, long ldc,
+                                   const int* mblk_group, int* status, int max_ctas,
+                                   cudaStream_t st) {
+  using namespace f8;
+  if (M <= 0 || N <= 0 || K <= 0 || K % BK != 0 || groups <= 0 || (ldc * 2) % 16 != 0)
+    return PB_BAD_ARG;
+  if (groups > 1 && (mblk_group == nullptr || N % BN != 0)) return PB_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(Aq) & 15) || (reinterpret_cast<uintptr_t>(Bq) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15))
+    return PB_BAD_ARG;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  CUtensorMap tmA, tmB, tmC;
+  int r = make_tmap_3d(&tmA, Aq, 1, K, M, 1, K, 0, BK, BM);
+  if (r != 0) return 1000 + r;
+  r = make_tmap_3d(&tmB, Bq, 1, K, N, groups, K, static_cast<uint64_t>(N) * K, BK, BN);
+  if (r != 0) return 2000 + r;
+  r = make_tmap_3d(&tmC, C, 2, N, M, 1, ldc, 0, 64, 32);
+  if (r != 0) return 3000 + r;
+  Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.sa = sa; p.sb = sb; p.mblk_group = mblk_group; p.status = status;
+  const long tiles = static_cast<long>((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int grid = num_sms();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = static_cast<int>(tiles);
+  gemm_fp8_kernel<<<grid, 192, SMEM_TOTAL, st>>>(tmA, tmB, tmC, p);
+  return static_cast<int>(cudaGetLastError());
+}

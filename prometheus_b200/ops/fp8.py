@@ -1,0 +1,107 @@
+"""Block-scaled FP8 (e4m3) linear algebra on the GPU: quantisers + the tcgen05 FP8 GEMM.
+
+``quantize_rows`` (activations, 1 x 128 blocks) and ``quantize_blocks`` (weights, 128 x 128
+blocks) produce e4m3 bytes and fp32 scales with the reference's rule (scale = amax / 448, 1 for
+an all-zero block; kernels/__init__.py ``fp8_quantize`` of the reference). ``gemm_fp8``
+multiplies them with the scales applied to each 128-deep partial product, which equals
+dequantise-then-matmul in exact arithmetic. ``fp8_linear`` is the differentiable layer: FP8
+forward, straight-through bf16 backward (the reference's ``fp8_linear`` contract).
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import call, ptr, stream_ptr
+
+Tensor = torch.Tensor
+BF16 = torch.bfloat16
+
+
+def quantize_rows(x: Tensor):
+    """x [M, K] bf16 (K % 128 == 0) -> (q [M, K] uint8 holding e4m3, scales [K / 128, M] fp32)."""
+    M, K = x.shape
+    assert x.dtype == BF16 and K % 128 == 0 and x.stride(1) == 1
+    q = torch.empty((M, K), dtype=torch.uint8, device=x.device)
+    s = torch.empty((K // 128, M), dtype=torch.float32, device=x.device)
+    call("pb_fp8_quant_rows", ptr(x), x.stride(0), M, K, ptr(q), ptr(s), stream_ptr())
+    return q, s
+
+
+def quantize_blocks(w: Tensor):
+    """w [N, K] or [E, N, K] bf16 -> (q same shape uint8, scales [(E,) ceil(N/128), K/128])."""
+    assert w.dtype == BF16 and w.is_contiguous() and w.shape[-1] % 128 == 0
+    K = w.shape[-1]
+    rows = w.numel() // K
+    if w.ndim == 3:
+        assert w.shape[1] % 128 == 0, "grouped weights need 128-aligned rows per expert"
+    q = torch.empty(w.shape, dtype=torch.uint8, device=w.device)
+    nb = (rows + 127) // 128
+    s = torch.empty((nb, K // 128), dtype=torch.float32, device=w.device)
+    call("pb_fp8_quant_blocks", ptr(w), K, rows, K, ptr(q), ptr(s), stream_ptr())
+    if w.ndim == 3:
+        s = s.view(w.shape[0], w.shape[1] // 128, K // 128)
+    return q, s
+
+
+def dequantize_rows(q: Tensor, s: Tensor) -> Tensor:
+    return q.view(torch.float8_e4m3fn).float() * s.t().repeat_interleave(128, dim=1)
+
+
+def dequantize_blocks(q: Tensor, s: Tensor) -> Tensor:
+    n = q.shape[-2]
+    full = s.repeat_interleave(128, dim=-2)[..., :n, :].repeat_interleave(128, dim=-1)
+    return q.view(torch.float8_e4m3fn).float() * full
+
+
+def gemm_fp8(aq: Tensor, sa: Tensor, bq: Tensor, sb: Tensor, *, mblk_group: Tensor | None = None,
+             max_ctas: int = 0) -> Tensor:
+    """C [M, N] bf16 = (aq, sa) @ (bq, sb)^T. bq [N, K], or [E, N, K] with ``mblk_group`` (one
+    int32 per 128-row block of aq naming its expert, negative = skip that block)."""
+    from .functional import status_word
+
+    M, K = aq.shape
+    groups = bq.shape[0] if bq.ndim == 3 else 1
+    N = bq.shape[-2]
+    assert bq.shape[-1] == K and (groups == 1 or mblk_group is not None)
+    out = torch.empty((M, N), dtype=BF16, device=aq.device)
+    call("pb_gemm_fp8_blockscaled", ptr(aq), ptr(sa), ptr(bq), ptr(sb), ptr(out), M, N, K, groups, N,
+         ptr(mblk_group), ptr(status_word(aq.device)), int(max_ctas), stream_ptr())
+    return out
+
+
+class _Fp8LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        xq, sx = quantize_rows(x2)
+        wq, sw = quantize_blocks(w)
+        ctx.save_for_backward(x2, w)
+        ctx.w_ref = w
+        ctx.xshape = x.shape
+        return gemm_fp8(xq, sx, wq, sw).reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .functional import gemm
+
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = gemm(dy2, w, b_mn=True).reshape(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(ctx.w_ref, "main_grad", None)
+            if mg is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, d=mg, beta=1.0)
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+        return dx, dw
+
+
+def fp8_linear(x: Tensor, w: Tensor) -> Tensor:
+    """y = q(x) @ q(w)^T with 1 x 128 activation blocks and 128 x 128 weight blocks (w stored
+    (out, in)); straight-through bf16 gradients, fp32 ``main_grad`` accumulation as ``linear``."""
+    return _Fp8LinearFn.apply(x, w)

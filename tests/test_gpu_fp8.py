@@ -1,0 +1,92 @@
+"""FP8 quantisers and the block-scaled tcgen05 GEMM against fp32 PyTorch (needs a B200)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+
+
+def _r(*shape, seed=0, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).to(BF16)
+
+
+def test_quantisers_match_the_reference_rule():
+    from prometheus_b200 import kernels
+    from prometheus_b200.ops import fp8
+
+    x = _r(300, 512, seed=1, scale=3.0)
+    x[5, 128:256] = 0                                   # an all-zero block keeps scale 1
+    q, s = fp8.quantize_rows(x)
+    # oracle on the CPU: there amax / 448 is a true division, as in the reference (on the GPU
+    # PyTorch turns division by a scalar into a multiply by its rounded reciprocal)
+    ref = kernels.fp8_quantize(x.float().cpu(), block=128)
+    assert s.shape == (4, 300)
+    assert torch.equal(s.t().cpu(), ref.scale)
+    assert s[1, 5].item() == 1.0
+    assert torch.equal(q.view(torch.int8).cpu(), ref.q)
+    torch.testing.assert_close(fp8.dequantize_rows(q, s).cpu(), kernels.fp8_dequantize(ref))
+    w = _r(200, 384, seed=2, scale=0.05)
+    qw, sw = fp8.quantize_blocks(w)
+    refw = kernels.fp8_quantize_2d(w.float().cpu(), block=128)
+    assert sw.shape == (2, 3)
+    assert torch.equal(sw.cpu(), refw.scale)
+    assert torch.equal(qw.view(torch.int8).cpu(), refw.q)
+    torch.testing.assert_close(fp8.dequantize_blocks(qw, sw).cpu(), kernels.fp8_dequantize(refw))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 200, 384), (1024, 1408, 2048), (77, 2048, 256)])
+def test_fp8_gemm_equals_dequantised_matmul(M, N, K):
+    from prometheus_b200.ops import fp8
+    from prometheus_b200.ops import functional as ops
+
+    x, w = _r(M, K, seed=1), _r(N, K, seed=2, scale=0.05)
+    xq, sx = fp8.quantize_rows(x)
+    wq, sw = fp8.quantize_blocks(w)
+    got = fp8.gemm_fp8(xq, sx, wq, sw)
+    torch.cuda.synchronize()
+    ops.check_status("cuda")
+    ref = fp8.dequantize_rows(xq, sx) @ fp8.dequantize_blocks(wq, sw).t()
+    err = (got.float() - ref).abs().max().item()
+    assert err <= 1e-2 * ref.abs().max().item(), err          # bf16 output rounding only
+    # and the quantisation error itself is what one expects of e4m3 (a few percent)
+    exact = x.float() @ w.float().t()
+    rel = (got.float() - exact).norm().item() / exact.norm().item()
+    assert rel < 0.06, rel
+
+
+def test_fp8_linear_and_grouped_gemm():
+    from prometheus_b200 import kernels
+    from prometheus_b200.ops import fp8, moe
+    from prometheus_b200.ops import functional as ops
+
+    x = _r(4, 96, 256, seed=1).requires_grad_(True)
+    w = _r(384, 256, seed=2, scale=0.05).requires_grad_(True)
+    y = fp8.fp8_linear(x, w)
+    y.float().square().sum().backward()
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = kernels.fp8_linear(xr, wr, 128, weight_2d=True)
+    yr.square().sum().backward()
+    assert (y.float() - yr).abs().max().item() <= 2e-2 * yr.abs().max().item()
+    # straight-through gradients use the unquantised operands: close to the reference's, which
+    # uses the dequantised ones
+    for a, b in ((x.grad, xr.grad), (w.grad, wr.grad)):
+        rel = (a.float() - b).norm().item() / b.norm().item()
+        assert rel < 0.08, rel
+    # grouped: rows of expert e use weight e
+    T, E, k, K, N = 500, 4, 2, 256, 256
+    ids = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).to(torch.int32)
+    pl = moe.place(ids.contiguous(), E)
+    xp = moe.permute(_r(T, K, seed=3), pl)
+    wg = _r(E, N, K, seed=4, scale=0.05)
+    xq, sx = fp8.quantize_rows(xp)
+    wq, sw = fp8.quantize_blocks(wg)
+    got = fp8.gemm_fp8(xq, sx, wq, sw, mblk_group=pl.mblk_group)
+    torch.cuda.synchronize()
+    ops.check_status("cuda")
+    off, tot = pl.expert_off.cpu().tolist(), pl.totals.cpu().tolist()
+    xd, wd = fp8.dequantize_rows(xq, sx), fp8.dequantize_blocks(wq, sw)
+    for e in range(E):
+        seg = slice(off[e], off[e] + tot[e])
+        ref = xd[seg] @ wd[e].t()
+        assert (got[seg].float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
