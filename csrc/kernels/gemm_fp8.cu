@@ -7,15 +7,16 @@
 // 128 x 128 block. Exactly the arithmetic of quantise -> dequantise -> fp32 matmul, with the
 // dequantisation applied to the 128-deep partial products instead of to the operands.
 //
-// One CTA per SM, persistent over 128 x 128 output tiles:
-//   warp 0   TMA producer: per K-block one 128 x 128 B tile of A and of B (128 bytes per row =
-//            one swizzle atom), 6-stage ring
-//   warp 1   MMA issuer: four kind::f8f6f4 MMAs (K = 32) per K-block into one of two
-//            tensor-memory accumulators, fresh (not accumulated) for every K-block
-//   warps 2-5  promotion + epilogue: each thread owns one output row; per K-block it reads the
-//            128 partial sums of its row from tensor memory, scales them by sa * sb and adds
-//            them to 128 fp32 registers; after the last K-block the row goes out as bf16
-//            through a swizzled staging tile and a TMA store
+// One CTA per SM, persistent over 128 x 256 output tiles:
+//   warp 0   TMA producer: per K-block a 128 x 128 B tile of A and a 256 x 128 B tile of B
+//            (128 bytes per row = one swizzle atom), 4-stage ring
+//   warp 1   MMA issuer: four kind::f8f6f4 MMAs (M 128, N 256, K 32) per K-block into one of
+//            two 256-column tensor-memory accumulators, fresh (not accumulated) per K-block
+//   warps 2-9  promotion + epilogue, two groups of four warps, one per 128-column half (one B
+//            scale each): every thread owns one output row of its half; per K-block it reads
+//            the 128 partial sums from tensor memory (two 64-column batches per wait), scales
+//            them by sa * sb and adds them to 128 fp32 registers; after the last K-block the
+//            row goes out as bf16 through a swizzled staging slab and TMA stores
 // Grouped mode (mixture-of-experts): row block m multiplies expert mblk_group[m] of a
 // [groups, N, K] weight tensor with scales [groups, N / 128, K / 128]; negative = skip.
 //
@@ -38,10 +39,11 @@ int num_sms();
 
 namespace f8 {
 
-constexpr int BM = 128, BN = 128, BK = 128;
-constexpr int STAGES = 6;
+constexpr int BM = 128, BN = 256, BK = 128, HALF = 128;
+constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int EPI_BYTES = 4 * 2 * 4096;
+constexpr int EPI_BYTES = 8 * 4096;
+constexpr int THREADS = 320;
 constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
 
 struct Params {
@@ -52,7 +54,7 @@ struct Params {
   int* status;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -80,7 +82,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 128);
+      mbar_init(&tempty[a], 256);
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -155,10 +157,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
   } else {
     const int q = warp & 3;            // tensor-memory lane quarter of this warp
+    const int half = (warp - 2) >> 2;  // which 128 columns of the tile
     const int n_sb = p.K / BK;
+    const int n_sb_rows = (p.N + HALF - 1) / HALF;
     uint32_t it = 0;
     bool ok = true;
-    uint8_t* my_epi = smEpi + (warp - 2) * 8192;
+    uint8_t* buf = smEpi + (warp - 2) * 4096;
     for (long t = blockIdx.x; t < total && ok; t += gridDim.x) {
       int m_blk, n_blk;
       coords(t, m_blk, n_blk);
@@ -166,34 +170,39 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (g < 0) continue;
       const int row = m_blk * BM + q * 32 + lane;
       const int srow = min(row, p.M - 1);
-      const float* sb = p.sb + (static_cast<size_t>(g) * num_n + n_blk) * n_sb;
-      float acc[BN];
+      const int sb_row = min(n_blk * 2 + half, n_sb_rows - 1);
+      const float* sb = p.sb + (static_cast<size_t>(g) * n_sb_rows + sb_row) * n_sb;
+      float acc[HALF];
 #pragma unroll
-      for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+      for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int a = it & 1;
         const float scale = p.sa[static_cast<size_t>(kb) * p.M + srow] * sb[kb];
         if (!mbar_wait(&tfull[a], (it >> 1) & 1, p.status)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t t_addr = tmem_base + a * BN + (static_cast<uint32_t>(q * 32) << 16);
+        const uint32_t t_addr =
+            tmem_base + a * BN + half * HALF + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_addr + c, r);
+        for (int c = 0; c < HALF; c += 64) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(t_addr + c, r0);
+          tmem_ld_32x32b_x32(t_addr + c + 32, r1);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(scale, __uint_as_float(r[i]), acc[c + i]);
+          for (int i = 0; i < 32; ++i) {
+            acc[c + i] = fmaf(scale, __uint_as_float(r0[i]), acc[c + i]);
+            acc[c + 32 + i] = fmaf(scale, __uint_as_float(r1[i]), acc[c + 32 + i]);
+          }
         }
         tc_fence_before();
         mbar_arrive(&tempty[a]);
       }
       if (!ok) break;
-      // row -> bf16 -> two 64-column slabs in the TMA swizzle layout -> bulk tensor stores
+      // row -> bf16 -> 64-column slabs in the TMA swizzle layout -> bulk tensor stores
       const int y0 = m_blk * BM + q * 32;
 #pragma unroll
       for (int sl = 0; sl < 2; ++sl) {
-        uint8_t* buf = my_epi + sl * 4096;
-        if (lane == 0) tma_store_wait_read<1>();
+        if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
         uint8_t* rowp = buf + lane * 128;
 #pragma unroll
@@ -206,7 +215,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         fence_proxy_async_smem();
         __syncwarp();
-        const int x0 = n_blk * BN + sl * 64;
+        const int x0 = n_blk * BN + half * HALF + sl * 64;
         if (lane == 0 && x0 < p.N && y0 < p.M) tma_store_3d(&tmC, buf, x0, y0, 0);
         if (lane == 0) tma_store_commit();
       }
@@ -324,7 +333,7 @@ PB_API int pb_gemm_fp8_blockscaled(const void* Aq, const float* sa, const void* 
   using namespace f8;
   if (M <= 0 || N <= 0 || K <= 0 || K % BK != 0 || groups <= 0 || (ldc * 2) % 16 != 0)
     return PB_BAD_ARG;
-  if (groups > 1 && (mblk_group == nullptr || N % BN != 0)) return PB_BAD_ARG;
+  if (groups > 1 && (mblk_group == nullptr || N % HALF != 0)) return PB_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(Aq) & 15) || (reinterpret_cast<uintptr_t>(Bq) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
     return PB_BAD_ARG;
@@ -349,6 +358,6 @@ PB_API int pb_gemm_fp8_blockscaled(const void* Aq, const float* sa, const void* 
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = static_cast<int>(tiles);
-  gemm_fp8_kernel<<<grid, 192, SMEM_TOTAL, st>>>(tmA, tmB, tmC, p);
+  gemm_fp8_kernel<<<grid, THREADS, SMEM_TOTAL, st>>>(tmA, tmB, tmC, p);
   return static_cast<int>(cudaGetLastError());
 }

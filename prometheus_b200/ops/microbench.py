@@ -70,6 +70,48 @@ def bench_gemm(a):
     return out
 
 
+def bench_fp8(a):
+    from . import fp8
+
+    x = torch.randn((a.m, a.k), device="cuda").to(BF16)
+    w = (torch.randn((a.n, a.k), device="cuda") * 0.05).to(BF16)
+    xq, sx = fp8.quantize_rows(x)
+    wq, sw = fp8.quantize_blocks(w)
+    ms = timeit(lambda: fp8.gemm_fp8(xq, sx, wq, sw), a.iters)
+    ms_q = timeit(lambda: fp8.quantize_rows(x), a.iters)
+    tf = 2.0 * a.m * a.n * a.k / ms / 1e9
+    return {"kernel": "gemm_fp8_blockscaled", "m": a.m, "n": a.n, "k": a.k, "ms": ms, "tflops": tf,
+            "vs_bf16_peak": tf / peaks()["bf16_tflops"], "quant_rows_ms": ms_q,
+            "quant_rows_gbs": (a.m * a.k * 3 + a.m * a.k // 32) / ms_q / 1e6}
+
+
+def bench_moe(a):
+    """One MoE FFN layer (router, placement, grouped GEMMs, combine), forward + backward."""
+    from . import moe
+
+    T, d, E, h, k = a.tokens, a.d, a.experts, a.hidden, a.top_k
+    x = torch.randn(T, d, device="cuda").to(BF16).requires_grad_(True)
+    rw = (torch.randn(E, d, device="cuda") * 0.02).to(BF16).requires_grad_(True)
+    wgu = (torch.randn(E, 2 * h, d, device="cuda") * 0.02).to(BF16).requires_grad_(True)
+    wd = (torch.randn(E, d, h, device="cuda") * 0.02).to(BF16).requires_grad_(True)
+    go = torch.randn(T, d, device="cuda").to(BF16)
+
+    def fwd():
+        return moe.moe_ffn(x, rw, None, wgu, wd, k)[0]
+
+    def both():
+        for t in (x, rw, wgu, wd):
+            t.grad = None
+        fwd().backward(go)
+
+    ms_f = timeit(fwd, a.iters)
+    ms_b = timeit(both, a.iters)
+    flops = 2.0 * T * k * 3 * d * h
+    return {"kernel": "moe_ffn", "tokens": T, "experts": E, "top_k": k, "d": d, "hidden": h,
+            "fwd_ms": ms_f, "fwd_bwd_ms": ms_b, "fwd_tflops": flops / ms_f / 1e9,
+            "fwd_bwd_tflops": 3 * flops / ms_b / 1e9, "peaks": peaks()}
+
+
 def bench_delta(a):
     from .. import kernels
 
@@ -134,6 +176,16 @@ def main():
     g.add_argument("--compare", action="store_true")
     g.add_argument("--debug", type=int, default=0, help="timing experiments, see pb_gemm_set_debug")
     d = sub.add_parser("delta")
+    f = sub.add_parser("fp8")
+    f.add_argument("--m", type=int, default=8192)
+    f.add_argument("--n", type=int, default=8192)
+    f.add_argument("--k", type=int, default=8192)
+    mo = sub.add_parser("moe")
+    mo.add_argument("--tokens", type=int, default=32768)
+    mo.add_argument("--experts", type=int, default=8)
+    mo.add_argument("--top-k", type=int, default=6)
+    mo.add_argument("--d", type=int, default=2048)
+    mo.add_argument("--hidden", type=int, default=1408)
     d.add_argument("--seqs", type=int, default=4)
     d.add_argument("--seq-len", type=int, default=4096)
     r = sub.add_parser("rmsnorm")
@@ -142,10 +194,11 @@ def main():
     c = sub.add_parser("ce")
     c.add_argument("--rows", type=int, default=4096)
     c.add_argument("--vocab", type=int, default=131072)
-    for s in (g, d, r, c):
+    for s in (g, d, r, c, f, mo):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
-    out = {"gemm": bench_gemm, "delta": bench_delta, "rmsnorm": bench_rmsnorm, "ce": bench_ce}[a.which](a)
+    out = {"gemm": bench_gemm, "delta": bench_delta, "rmsnorm": bench_rmsnorm, "ce": bench_ce,
+           "fp8": bench_fp8, "moe": bench_moe}[a.which](a)
     out["peaks"] = peaks()
     print(json.dumps(out))
 
