@@ -92,7 +92,7 @@ class Trainer:
                  params: dict | None = None, seed: int = 0, device="cuda", micro_batch: int = 4,
                  muon_weight_decay: float = 0.0, process_group=None, ce_chunk_rows: int = 4096,
                  grad_sync: str = "auto", expert_parallel: bool = False,
-                 ep_capacity_factor: float = 2.0):
+                 ep_capacity_factor: float = 2.0, fp8: bool = False):
         M.validate_config(model_config)
         T.validate_train_config(train_config)
         self.cfg, self.tcfg = model_config, train_config
@@ -109,6 +109,9 @@ class Trainer:
         self.grad_sync = grad_sync
         self.ep = bool(expert_parallel) and self.world > 1 and model_config.n_moe > 0
         self.ep_capacity_factor = float(ep_capacity_factor)
+        # block-scaled FP8 forward for the FFN / expert products (1 x 128 activations,
+        # 128 x 128 weights), straight-through bf16 backward
+        self.fp8 = bool(fp8)
         self.ep_ctx = None
         if self.ep and model_config.n_routed_experts % self.world:
             raise ValueError("expert parallelism needs n_routed_experts divisible by the world size")
@@ -463,6 +466,13 @@ class Trainer:
                                           kernels.LinearAttnConfig(chunk=cfg.chunk))
         return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
 
+    def _ffn_linear(self, x: Tensor, w: Tensor) -> Tensor:
+        if self.fp8 and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
+            from .ops import fp8
+
+            return fp8.fp8_linear(x, w)
+        return ops.linear(x, w)
+
     def _mla_layer(self, n: Tensor, i: int, B: int, S: int) -> Tensor:
         """Latent-KV softmax attention. Projections run on the tcgen05 GEMM; the rotary
         split, the unit-weight QK RMSNorm and the softmax core are PyTorch (the reference's
@@ -514,7 +524,8 @@ class Trainer:
         n_e = cfg.n_routed_experts + cfg.n_shared_experts
         out, probs, ids = moe.moe_ffn(n2, self.p[pre + "router"], self.router_bias.get(i),
                                       w_gu, w_dn, cfg.top_k, n_shared=cfg.n_shared_experts,
-                                      shapes=((n_e, 2 * hid, cfg.d_model), (n_e, cfg.d_model, hid)))
+                                      shapes=((n_e, 2 * hid, cfg.d_model), (n_e, cfg.d_model, hid)),
+                                      fp8=self.fp8)
         self.last_router = (probs, ids)
         return out
 
@@ -551,8 +562,8 @@ class Trainer:
                 a = self._gqa_layer(n, i, B, S)
             n2, h = ops.add_rmsnorm(a, h, self.p[pre + "pre_ffn_norm"])
             if pre + "gate_up" in self.p:
-                gu = ops.linear(n2, self.p[pre + "gate_up"])
-                f = ops.linear(ops.swiglu(gu), self.p[pre + "down"])
+                gu = self._ffn_linear(n2, self.p[pre + "gate_up"])
+                f = self._ffn_linear(ops.swiglu(gu), self.p[pre + "down"])
             else:
                 f = self._moe_layer(n2, i)
             nxt = f"layers.{i + 1}.pre_attn_norm" if i + 1 < cfg.n_layers else "final_norm"

@@ -129,7 +129,7 @@ def _acc_grad(w: Tensor, shape3, fn):
 
 class _MoeFfnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, router_w, router_bias, w_gu_p, w_down_p, top_k, n_shared, shapes):
+    def forward(ctx, x, router_w, router_bias, w_gu_p, w_down_p, top_k, n_shared, shapes, fp8=False):
         from .functional import gemm
 
         w_gu = w_gu_p.view(shapes[0]) if shapes is not None else w_gu_p
@@ -149,10 +149,10 @@ class _MoeFfnFn(torch.autograd.Function):
             ids, gates = ids_r, gates_r
         pl = place(ids, E)
         xp = permute(x, pl)
-        gu = grouped_gemm(xp, w_gu, pl)
+        gu = _expert_gemm(xp, w_gu, pl, fp8)
         hs = torch.empty((pl.rows, h), dtype=BF16, device=x.device)
         call("pb_swiglu_fwd", ptr(gu), ptr(hs), pl.rows, h, stream_ptr())
-        y = grouped_gemm(hs, w_down, pl)
+        y = _expert_gemm(hs, w_down, pl, fp8)
         out = combine(y, pl, gates, T)
         ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids_r, gates, xp, gu, hs, y)
         ctx.pl = pl
@@ -203,16 +203,30 @@ class _MoeFfnFn(torch.autograd.Function):
                  beta=1.0)
         else:
             g_router = gemm(dl, x, a_mn=True, b_mn=True)
-        return dx, g_router, None, g_gu, g_down, None, None, None
+        return dx, g_router, None, g_gu, g_down, None, None, None, None
+
+
+def _expert_gemm(a: Tensor, w: Tensor, pl: Placement, use_fp8: bool) -> Tensor:
+    """Forward expert product: bf16 grouped GEMM, or 1 x 128 / 128 x 128 block-scaled FP8 when
+    the shapes allow (contraction and output width multiples of 128)."""
+    if use_fp8 and a.shape[1] % 128 == 0 and w.shape[1] % 128 == 0:
+        from . import fp8
+
+        aq, sa = fp8.quantize_rows(a)
+        wq, sw = fp8.quantize_blocks(w.contiguous())
+        return fp8.gemm_fp8(aq, sa, wq, sw, mblk_group=pl.mblk_group)
+    return grouped_gemm(a, w, pl)
 
 
 def moe_ffn(x: Tensor, router_w: Tensor, router_bias: Tensor | None, w_gu: Tensor, w_down: Tensor,
-            top_k: int, n_shared: int = 0, shapes=None):
+            top_k: int, n_shared: int = 0, shapes=None, fp8: bool = False):
     """Routed (+ shared) expert FFN. x [T, d] bf16; router_w [E, d]; w_gu [E + n_shared, 2h, d]
     (gate rows then up rows per expert; the shared experts last); w_down [E + n_shared, d, h].
     ``shapes`` gives those two 3-D shapes when the weights are passed as flat 2-D parameters.
+    ``fp8``: forward expert products in block-scaled FP8 (straight-through bf16 backward).
     Returns (out [T, d], probs [T, E] fp32, ids [T, k] int32); out and probs are differentiable."""
-    return _MoeFfnFn.apply(x, router_w, router_bias, w_gu, w_down, int(top_k), int(n_shared), shapes)
+    return _MoeFfnFn.apply(x, router_w, router_bias, w_gu, w_down, int(top_k), int(n_shared), shapes,
+                           bool(fp8))
 
 
 def moe_ffn_ref(x, router_w, router_bias, w_gu, w_down, top_k, n_shared=0):

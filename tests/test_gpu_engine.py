@@ -159,3 +159,23 @@ def test_tiny_reference_config_mla_moe_runs_in_the_engine():
     losses = [tr.step(tokens.cuda())["loss"].item() for _ in range(10)]
     assert abs(losses[0] - want_loss) < 3e-2 * want_loss, (losses[0], want_loss)
     assert losses[-1] < losses[0] - 0.2, losses
+
+
+def test_fp8_forward_option_trains_dense_and_moe():
+    """Block-scaled FP8 forward (FFN and expert products): first-step loss within FP8 error of
+    the bf16 engine, and the loss still goes down."""
+    from prometheus_b200 import engine, model, train
+
+    for cfg in (model.with_overrides(small_hybrid(), dense_hidden=512),
+                model.with_overrides(small_moe(), expert_hidden=128)):
+        tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10)
+        params = model.init_params(cfg, 0)
+        tokens = torch.randint(0, cfg.vocab_size, (4, 128), device="cuda",
+                               generator=torch.Generator(device="cuda").manual_seed(0))
+        ref = engine.Trainer(cfg, tcfg, params=params, micro_batch=2).step(tokens)["loss"].item()
+        tr = engine.Trainer(cfg, tcfg, params=params, micro_batch=2, fp8=True)
+        losses = [tr.step(tokens)["loss"].item() for _ in range(8)]
+        assert abs(losses[0] - ref) < 2e-2 * ref, (losses[0], ref)
+        assert losses[-1] < losses[0] - 0.3, losses
+    from prometheus_b200.ops import functional as ops
+    ops.check_status("cuda")
