@@ -14,6 +14,8 @@ void bind_harness_queue(py::module_& m);
 void bind_harness_control(py::module_& m);
 void bind_harness_lab(py::module_& m);
 void bind_harness_faults(py::module_& m);
+void bind_rl_core(py::module_& m);
+void bind_rl_envs(py::module_& m);
 
 PYBIND11_MODULE(_pb200_native, m) {
   m.doc() = "C++ systems components of prometheus_b200 (loader, checkpoints, control, ...)";
@@ -41,4 +43,6 @@ PYBIND11_MODULE(_pb200_native, m) {
   bind_harness_control(m);
   bind_harness_lab(m);
   bind_harness_faults(m);
+  bind_rl_core(m);
+  bind_rl_envs(m);
 }

@@ -1,0 +1,810 @@
+// Sandboxes, exact verifiers and reward models of the RL stack:
+//
+//   envs       sandbox pool: images -> snapshots -> identical forks (GRPO groups of 16, pairs),
+//              an emulated tool surface (shell, python, editor, notes, offline browser, lean,
+//              sub-agent spawn), agent vs grader file views, writes under /grader blocked and
+//              recorded as tamper flags, no network egress, no credential-like variables
+//              (reference: rl/envs/src/lib.rs:29-39, 196-503; rl/envs/src/engine.rs:14-30, 340-810)
+//   verifiers  exact checkers: hidden tests + mutants in a sandbox, rational-arithmetic
+//              equivalence, tiny proof kernel, ARC grid pass@2, market relative log score
+//              (reference: verifiers/src/lib.rs:36-39, 412-713; engine.rs; math.rs)
+//   rewards    rubric panel over a judge (disagreement lowers the score), contrastive pair
+//              filters, tampering detector, held-out hack recall
+//              (reference: rl/rewards/src/lib.rs:32, 100-141, 200-554)
+#include <pybind11/functional.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cmath>
+#include <map>
+#include <set>
+
+#include "common.hpp"
+
+namespace py = pybind11;
+using namespace pbn;
+
+namespace {
+
+using Files = std::map<std::string, std::string>;
+
+bool is_grader_path(const std::string& p) { return p == "/grader" || p.rfind("/grader/", 0) == 0; }
+std::string lower(std::string s) {
+  for (char& c : s) c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
+  return s;
+}
+std::string trim(const std::string& s) {
+  size_t a = 0, b = s.size();
+  while (a < b && std::isspace(static_cast<unsigned char>(s[a]))) ++a;
+  while (b > a && std::isspace(static_cast<unsigned char>(s[b - 1]))) --b;
+  return s.substr(a, b - a);
+}
+
+// ----------------------------------------------------------------------------------- envs
+struct Image {
+  std::string id;
+  Files agent_files, hidden_tests;
+  std::map<std::string, std::string> env;
+};
+struct TamperFlag {
+  std::string sandbox, path, call_id;
+  uint64_t now_ms = 0;
+};
+struct ToolResponse {
+  std::string call_id, tool, stdout_bytes, stdout_hash, stderr_text;
+  bool ok = false;
+  uint64_t duration_ms = 0;
+  std::optional<std::string> child_sandbox;
+};
+struct Sandbox {
+  Files files, hidden;
+  bool live = true;
+  uint32_t gpu_used_s = 0;
+};
+struct PoolConfig {
+  size_t capacity = 64;
+  std::map<std::string, std::pair<std::string, uint64_t>> offline_pages;   // url -> (body, snapshot time)
+  uint64_t web_cutoff_unix_s = 0;
+  std::optional<uint32_t> gpu_walltime_s;
+  uint32_t default_timeout_s = 60;
+};
+
+const std::set<std::string> kNetworkBins = {"curl", "wget", "nc", "netcat", "ssh", "scp", "sftp", "nmap",
+                                            "ping", "telnet", "ftp", "host", "dig", "nslookup"};
+const std::set<std::string> kTools = {"shell", "python", "editor", "notes", "browser", "lean", "spawn"};
+
+std::vector<std::string> tokenize(const std::string& cmd) {
+  std::vector<std::string> out;
+  std::string cur;
+  char quote = 0;
+  for (char c : cmd) {
+    if (quote) {
+      if (c == quote) quote = 0;
+      else cur.push_back(c);
+    } else if (c == '"' || c == '\'') {
+      quote = c;
+    } else if (std::isspace(static_cast<unsigned char>(c))) {
+      if (!cur.empty()) out.push_back(cur);
+      cur.clear();
+    } else {
+      cur.push_back(c);
+    }
+  }
+  if (!cur.empty()) out.push_back(cur);
+  return out;
+}
+
+std::optional<int64_t> eval_int_expr(const std::string& s) {   // digits with + - * only
+  std::vector<int64_t> terms;
+  int64_t sign = 1, cur = 0, prod = 1;
+  bool have = false, in_prod = false;
+  auto close_term = [&] {
+    if (in_prod) prod *= cur;
+    else prod = cur;
+    terms.push_back(sign * prod);
+    in_prod = false;
+  };
+  for (size_t i = 0; i <= s.size(); ++i) {
+    const char c = i < s.size() ? s[i] : '+';
+    if (std::isspace(static_cast<unsigned char>(c))) continue;
+    if (std::isdigit(static_cast<unsigned char>(c))) {
+      cur = have ? cur * 10 + (c - '0') : (c - '0');
+      have = true;
+    } else if (c == '*') {
+      if (!have) return std::nullopt;
+      prod = in_prod ? prod * cur : cur;
+      in_prod = true;
+      have = false;
+    } else if (c == '+' || c == '-') {
+      if (!have) return std::nullopt;
+      close_term();
+      sign = c == '-' ? -1 : 1;
+      have = false;
+    } else {
+      return std::nullopt;
+    }
+  }
+  int64_t total = 0;
+  for (int64_t t : terms) total += t;
+  return total;
+}
+
+class Pool {
+ public:
+  explicit Pool(PoolConfig c) : cfg_(std::move(c)) {}
+  size_t live_count() const {
+    size_t n = 0;
+    for (auto& kv : boxes_) n += kv.second.live ? 1 : 0;
+    return n;
+  }
+  const std::vector<TamperFlag>& tamper_flags() const { return tamper_; }
+
+  std::string register_image(const Image& img) {
+    for (auto& kv : img.env) {
+      std::string up = kv.first;
+      for (char& c : up) c = static_cast<char>(std::toupper(static_cast<unsigned char>(c)));
+      if (up.find("SECRET") != std::string::npos || up.find("TOKEN") != std::string::npos ||
+          up.find("PASSWORD") != std::string::npos || up.find("CREDENTIAL") != std::string::npos ||
+          up.rfind("AWS_", 0) == 0 || up.rfind("SSH_", 0) == 0)
+        throw Error("CredentialInSandbox", "credential-like variable in sandbox image: " + kv.first);
+    }
+    for (auto& kv : img.hidden_tests)
+      if (!is_grader_path(kv.first)) throw Error("HiddenTestsVisible", "hidden tests must live under /grader");
+    for (auto& kv : img.agent_files)
+      if (is_grader_path(kv.first)) throw Error("HiddenTestsVisible", "agent files must not live under /grader");
+    images_[img.id] = img;
+    return img.id;
+  }
+  std::string snapshot_from_image(const std::string& image) {
+    auto it = images_.find(image);
+    if (it == images_.end()) throw Error("UnknownImage", "unknown image " + image);
+    const std::string id = "snap-" + std::to_string(next_snap_++);
+    Sandbox s;
+    s.files = it->second.agent_files;
+    s.hidden = it->second.hidden_tests;
+    snaps_[id] = s;
+    return id;
+  }
+  // n identical copies of a snapshot (copy-on-write in spirit: forks never see each other)
+  std::vector<std::string> fork_group(const std::string& snap, size_t n) {
+    auto it = snaps_.find(snap);
+    if (it == snaps_.end()) throw Error("UnknownSnapshot", "unknown snapshot " + snap);
+    if (live_count() + n > cfg_.capacity)
+      throw Error("PoolExhausted", "pool exhausted: capacity " + std::to_string(cfg_.capacity));
+    std::vector<std::string> out;
+    for (size_t i = 0; i < n; ++i) {
+      const std::string id = "sb-" + std::to_string(next_box_++);
+      boxes_[id] = it->second;
+      boxes_[id].live = true;
+      out.push_back(id);
+    }
+    return out;
+  }
+  std::string snapshot(const std::string& sandbox) {
+    const Sandbox& b = live(sandbox);
+    const std::string id = "snap-" + std::to_string(next_snap_++);
+    snaps_[id] = b;
+    return id;
+  }
+  void kill(const std::string& sandbox) { live(sandbox).live = false; }
+  Files agent_view(const std::string& sandbox) const { return get(sandbox).files; }
+  Files grader_view(const std::string& sandbox) const {
+    const Sandbox& b = get(sandbox);
+    Files all = b.files;
+    for (auto& kv : b.hidden) all[kv.first] = kv.second;
+    return all;
+  }
+
+  ToolResponse call(const std::string& sandbox, const std::string& call_id, const std::string& tool,
+                    const Json& payload, std::optional<uint32_t> timeout_s, uint64_t now) {
+    if (!kTools.count(tool)) throw Error("BadToolRequest", "unknown tool " + tool);
+    live(sandbox);
+    const uint32_t limit = timeout_s.value_or(cfg_.default_timeout_s);
+    auto str = [&](const char* k) -> std::optional<std::string> {
+      const Json* v = payload.is_object() ? payload.find(k) : nullptr;
+      if (v && v->is_string()) return v->as_string();
+      return std::nullopt;
+    };
+    ToolResponse r;
+    r.call_id = call_id;
+    r.tool = tool;
+    auto ok = [&](const std::string& out) {
+      r.ok = true;
+      r.stdout_bytes = out;
+      r.stdout_hash = sha256_hex(out);
+      return r;
+    };
+    auto fail = [&](const std::string& msg) {
+      r.ok = false;
+      r.stderr_text = msg;
+      r.stdout_hash = sha256_hex(std::string());
+      return r;
+    };
+    auto blocked_write = [&](const std::string& path) {
+      tamper_.push_back({sandbox, path, call_id, now});
+      throw Error("TestFileWrite", "write to grader path blocked: " + path);
+    };
+    auto gpu_gate = [&](const std::string& text) {
+      const std::string l = lower(text);
+      const Json* g = payload.is_object() ? payload.find("gpu") : nullptr;
+      const bool wants = l.find("cuda") != std::string::npos || l.find("nvidia") != std::string::npos ||
+                         l.find("rocminfo") != std::string::npos || (g && g->is_bool() && g->as_bool());
+      if (!wants) return;
+      if (!cfg_.gpu_walltime_s) throw Error("Backend", "gpu not configured");
+      const Json* w = payload.find("work_s");
+      const uint32_t work = w && w->is_integer() ? static_cast<uint32_t>(w->as_u64()) : 1;
+      if (work > limit) throw Error("Timeout", "tool call timed out");
+      Sandbox& b = live(sandbox);
+      if (work > *cfg_.gpu_walltime_s || b.gpu_used_s + work > *cfg_.gpu_walltime_s)
+        throw Error("GpuTimeLimit", "gpu time limit");
+      b.gpu_used_s += work;
+    };
+
+    if (tool == "shell") {
+      const std::string cmd = str("command").value_or("");
+      gpu_gate(cmd);
+      const auto tk = tokenize(cmd);
+      if (tk.empty()) return fail("empty command");
+      if (kNetworkBins.count(tk[0])) throw Error("EgressDenied", "network egress denied");
+      if (tk[0] == "sleep") {
+        const uint32_t secs = tk.size() > 1 ? static_cast<uint32_t>(std::strtoul(tk[1].c_str(), nullptr, 10)) : 0;
+        if (secs > limit) throw Error("Timeout", "tool call timed out");
+        r.duration_ms = static_cast<uint64_t>(secs) * 1000;
+        return ok("");
+      }
+      for (size_t i = 0; i < tk.size(); ++i)
+        if (tk[i] == ">" && i + 1 < tk.size()) {
+          const std::string path = tk[i + 1];
+          if (is_grader_path(path)) blocked_write(path);
+          std::string body;
+          for (size_t j = tk[0] == "echo" ? 1 : 0; j < i; ++j) body += (body.empty() ? "" : " ") + tk[j];
+          live(sandbox).files[path] = body + "\n";
+          return ok("");
+        }
+      if (tk[0] == "echo") {
+        std::string out;
+        for (size_t j = 1; j < tk.size(); ++j) out += (j > 1 ? " " : "") + tk[j];
+        return ok(out + "\n");
+      }
+      if (tk[0] == "cat") {
+        if (tk.size() < 2) return fail("cat: missing path");
+        if (is_grader_path(tk[1])) return fail("not found");
+        const Files& f = live(sandbox).files;
+        auto it = f.find(tk[1]);
+        return it == f.end() ? fail("not found") : ok(it->second);
+      }
+      return fail("unsupported command");
+    }
+    if (tool == "python") {
+      const std::string code = str("code").value_or("");
+      gpu_gate(code);
+      const std::string l = lower(code);
+      for (const char* bad : {"import urllib", "from urllib", "import requests", "import socket", "from socket",
+                              "http.client", "import httpx", "aiohttp", "https://", "http://"})
+        if (l.find(bad) != std::string::npos) throw Error("LiveInternet", "live internet access denied");
+      const std::string t = trim(code);
+      if (t.rfind("open(", 0) == 0 &&
+          (t.find("write") != std::string::npos || t.find("'w'") != std::string::npos || t.find("\"w\"") != std::string::npos)) {
+        const std::string rest = trim(t.substr(5));
+        if (!rest.empty() && (rest[0] == '"' || rest[0] == '\'')) {
+          const size_t end = rest.find(rest[0], 1);
+          if (end != std::string::npos && is_grader_path(rest.substr(1, end - 1))) blocked_write(rest.substr(1, end - 1));
+        }
+      }
+      if (t.rfind("print(", 0) != 0 || t.back() != ')') return fail("unsupported python");
+      const std::string inner = trim(t.substr(6, t.size() - 7));
+      if (inner.rfind("open(", 0) == 0) {   // print(open('path').read())
+        const std::string rest = trim(inner.substr(5));
+        if (!rest.empty() && (rest[0] == '"' || rest[0] == '\'')) {
+          const size_t end = rest.find(rest[0], 1);
+          if (end != std::string::npos) {
+            const std::string path = rest.substr(1, end - 1);
+            std::string after = trim(rest.substr(end + 1));
+            if (after.rfind(")", 0) == 0 && trim(after.substr(1)).rfind(".read()", 0) == 0) {
+              if (is_grader_path(path)) return fail("not found");
+              const Files& f = live(sandbox).files;
+              auto it = f.find(path);
+              if (it == f.end()) return fail("not found");
+              std::string out = it->second;
+              if (out.empty() || out.back() != '\n') out.push_back('\n');
+              return ok(out);
+            }
+          }
+        }
+        return fail("unsupported python");
+      }
+      if (inner.size() >= 2 && (inner.front() == '"' || inner.front() == '\'') && inner.back() == inner.front())
+        return ok(inner.substr(1, inner.size() - 2) + "\n");
+      if (auto n = eval_int_expr(inner)) return ok(std::to_string(*n) + "\n");
+      return fail("unsupported python");
+    }
+    if (tool == "editor" || tool == "notes") {
+      const bool has_content = payload.is_object() && payload.find("content") != nullptr;
+      const std::string op = str("op").value_or(has_content ? "write" : "read");
+      const std::string path = str("path").value_or(tool == "notes" ? "/notes/memo.txt" : "");
+      if (path.empty()) throw Error("BadToolRequest", "missing path");
+      if (op == "write") {
+        if (is_grader_path(path)) blocked_write(path);
+        live(sandbox).files[path] = str("content").value_or("");
+        return ok("");
+      }
+      if (is_grader_path(path)) return fail("not found");
+      const Files& f = live(sandbox).files;
+      auto it = f.find(path);
+      return it == f.end() ? fail("not found") : ok(it->second);
+    }
+    if (tool == "browser") {
+      const std::string url = str("url").value_or("");
+      if (url.empty()) return fail("missing url");
+      auto it = cfg_.offline_pages.find(url);
+      if (it != cfg_.offline_pages.end())
+        return it->second.second <= cfg_.web_cutoff_unix_s ? ok(it->second.first) : fail("page after cutoff");
+      if (url.rfind("http://", 0) == 0 || url.rfind("https://", 0) == 0) throw Error("EgressDenied", "network egress denied");
+      return fail("missing url");
+    }
+    if (tool == "lean") {
+      const std::string code = str("code").value_or("");
+      if (trim(code).empty()) return fail("empty lean");
+      const std::string l = lower(code);
+      if (l.find("sorry") != std::string::npos || l.find("admit") != std::string::npos) return fail("incomplete proof");
+      return ok("ok\n");
+    }
+    // spawn: a sub-agent gets a fork of the caller's current state
+    const std::string snap = snapshot(sandbox);
+    const auto kids = fork_group(snap, 1);
+    r.child_sandbox = kids[0];
+    return ok(kids[0] + "\n");
+  }
+
+ private:
+  const Sandbox& get(const std::string& id) const {
+    auto it = boxes_.find(id);
+    if (it == boxes_.end()) throw Error("UnknownSandbox", "unknown sandbox " + id);
+    return it->second;
+  }
+  Sandbox& live(const std::string& id) {
+    auto it = boxes_.find(id);
+    if (it == boxes_.end()) throw Error("UnknownSandbox", "unknown sandbox " + id);
+    if (!it->second.live) throw Error("SandboxDead", "sandbox " + id + " was killed");
+    return it->second;
+  }
+  PoolConfig cfg_;
+  std::map<std::string, Image> images_;
+  std::map<std::string, Sandbox> snaps_, boxes_;
+  std::vector<TamperFlag> tamper_;
+  uint64_t next_snap_ = 1, next_box_ = 1;
+};
+
+// ------------------------------------------------------------------------------ verifiers
+struct Rat {
+  __int128 n = 0, d = 1;
+};
+__int128 gcd128(__int128 a, __int128 b) {
+  if (a < 0) a = -a;
+  if (b < 0) b = -b;
+  while (b != 0) {
+    const __int128 t = a % b;
+    a = b;
+    b = t;
+  }
+  return a == 0 ? 1 : a;
+}
+std::optional<Rat> mk_rat(__int128 n, __int128 d) {
+  if (d == 0) return std::nullopt;
+  const __int128 g = gcd128(n, d);
+  n /= g;
+  d /= g;
+  if (d < 0) {
+    n = -n;
+    d = -d;
+  }
+  return Rat{n, d};
+}
+bool mul_ok(__int128 a, __int128 b, __int128& out) { return !__builtin_mul_overflow(a, b, &out); }
+
+struct RatParser {
+  const std::string& s;
+  size_t i = 0;
+  bool eat(char c) {
+    if (i < s.size() && s[i] == c) {
+      ++i;
+      return true;
+    }
+    return false;
+  }
+  std::optional<Rat> expr() {
+    auto acc = term();
+    while (acc && i < s.size() && (s[i] == '+' || s[i] == '-')) {
+      const char op = s[i++];
+      auto rhs = term();
+      if (!rhs) return std::nullopt;
+      __int128 a, b, d;
+      if (!mul_ok(acc->n, rhs->d, a) || !mul_ok(rhs->n, acc->d, b) || !mul_ok(acc->d, rhs->d, d)) return std::nullopt;
+      __int128 n;
+      if (op == '+' ? __builtin_add_overflow(a, b, &n) : __builtin_sub_overflow(a, b, &n)) return std::nullopt;
+      acc = mk_rat(n, d);
+    }
+    return acc;
+  }
+  std::optional<Rat> term() {
+    auto acc = unary();
+    while (acc && i < s.size() && (s[i] == '*' || s[i] == '/')) {
+      const char op = s[i++];
+      auto rhs = unary();
+      if (!rhs) return std::nullopt;
+      __int128 n, d;
+      if (op == '*') {
+        if (!mul_ok(acc->n, rhs->n, n) || !mul_ok(acc->d, rhs->d, d)) return std::nullopt;
+      } else {
+        if (rhs->n == 0 || !mul_ok(acc->n, rhs->d, n) || !mul_ok(acc->d, rhs->n, d)) return std::nullopt;
+      }
+      acc = mk_rat(n, d);
+    }
+    return acc;
+  }
+  std::optional<Rat> unary() {
+    if (eat('-')) {
+      auto v = unary();
+      if (!v) return std::nullopt;
+      return Rat{-v->n, v->d};
+    }
+    return primary();
+  }
+  std::optional<Rat> primary() {
+    if (s.compare(i, 5, "\\frac") == 0) {
+      i += 5;
+      if (!eat('{')) return std::nullopt;
+      auto a = expr();
+      if (!a || !eat('}') || !eat('{')) return std::nullopt;
+      auto b = expr();
+      if (!b || !eat('}') || b->n == 0) return std::nullopt;
+      __int128 n, d;
+      if (!mul_ok(a->n, b->d, n) || !mul_ok(a->d, b->n, d)) return std::nullopt;
+      return mk_rat(n, d);
+    }
+    if (eat('(')) {
+      auto e = expr();
+      if (!e || !eat(')')) return std::nullopt;
+      return e;
+    }
+    return number();
+  }
+  std::optional<Rat> number() {
+    bool saw = false;
+    __int128 ip = 0;
+    while (i < s.size() && std::isdigit(static_cast<unsigned char>(s[i]))) {
+      saw = true;
+      if (__builtin_mul_overflow(ip, static_cast<__int128>(10), &ip) || __builtin_add_overflow(ip, static_cast<__int128>(s[i] - '0'), &ip))
+        return std::nullopt;
+      ++i;
+    }
+    __int128 frac = 0, den = 1;
+    if (i < s.size() && s[i] == '.') {
+      ++i;
+      bool sf = false;
+      while (i < s.size() && std::isdigit(static_cast<unsigned char>(s[i]))) {
+        sf = true;
+        if (__builtin_mul_overflow(frac, static_cast<__int128>(10), &frac) || __builtin_add_overflow(frac, static_cast<__int128>(s[i] - '0'), &frac) ||
+            __builtin_mul_overflow(den, static_cast<__int128>(10), &den))
+          return std::nullopt;
+        ++i;
+      }
+      if (!sf && !saw) return std::nullopt;
+      saw = saw || sf;
+    }
+    if (!saw) return std::nullopt;
+    __int128 n;
+    if (!mul_ok(ip, den, n) || __builtin_add_overflow(n, frac, &n)) return std::nullopt;
+    return mk_rat(n, den);
+  }
+};
+
+std::string math_canonicalize(const std::string& in) {
+  std::string s;
+  for (size_t i = 0; i < in.size();) {
+    if (in[i] == '$') {
+      ++i;
+    } else if (in.compare(i, 5, "\\left") == 0) {
+      i += 5;
+    } else if (in.compare(i, 6, "\\right") == 0) {
+      i += 6;
+    } else {
+      if (!std::isspace(static_cast<unsigned char>(in[i]))) s.push_back(in[i]);
+      ++i;
+    }
+  }
+  return s;
+}
+std::optional<Rat> eval_canon(const std::string& s) {
+  RatParser p{s};
+  auto v = p.expr();
+  if (!v || p.i != s.size()) return std::nullopt;
+  return v;
+}
+bool math_equivalent(const std::string& a, const std::string& b) {
+  const std::string l = math_canonicalize(a), r = math_canonicalize(b);
+  if (l == r) return true;
+  const auto x = eval_canon(l), y = eval_canon(r);
+  return x && y && x->n == y->n && x->d == y->d;
+}
+
+std::string collapse_ws(const std::string& s) {
+  std::string out;
+  bool space = false;
+  for (char c : trim(s)) {
+    if (std::isspace(static_cast<unsigned char>(c))) {
+      space = true;
+    } else {
+      if (space && !out.empty()) out.push_back(' ');
+      space = false;
+      out.push_back(c);
+    }
+  }
+  return out;
+}
+bool tiny_kernel_check(const std::string& theorem, const std::string& proof) {
+  const std::string th = collapse_ws(theorem), pr = collapse_ws(proof);
+  if (th.empty()) throw Error("Lean", "empty theorem");
+  if (pr.empty()) throw Error("Lean", "empty proof");
+  if (th == "true") return pr == "trivial";
+  if (th == "id") return pr == "fun x => x";
+  throw Error("Lean", "unknown theorem: " + th);
+}
+
+using Grid = std::vector<std::vector<uint8_t>>;
+void grid_valid(const Grid& g) {
+  if (g.empty() || g[0].empty() || g.size() > 30 || g[0].size() > 30) throw Error("BadGrid", "grid must be 1..30 by 1..30");
+  for (auto& row : g) {
+    if (row.size() != g[0].size()) throw Error("BadGrid", "ragged grid");
+    for (uint8_t c : row)
+      if (c > 9) throw Error("BadGrid", "cell out of range");
+  }
+}
+bool grid_pass_at_2(const Grid& expected, const std::vector<Grid>& attempts) {
+  if (attempts.size() > 2) throw Error("TooManyGrids", "at most 2 grid attempts");
+  grid_valid(expected);
+  for (auto& g : attempts) grid_valid(g);
+  for (auto& g : attempts)
+    if (g == expected) return true;
+  return false;
+}
+
+double relative_log_score(double model_p, double market_p, bool outcome) {
+  for (double p : {model_p, market_p})
+    if (!(p >= 0.0 && p <= 1.0)) throw Error("BadProbability", "probability out of [0, 1]");
+  constexpr double eps = 1e-12;
+  const double pm = std::min(std::max(outcome ? model_p : 1.0 - model_p, eps), 1.0 - eps);
+  const double pk = std::min(std::max(outcome ? market_p : 1.0 - market_p, eps), 1.0 - eps);
+  return std::log(pm) - std::log(pk);
+}
+
+struct CodeTask {
+  Image image;
+  std::string tool = "python";
+  Json payload;
+  uint32_t timeout_s = 60;
+  std::string expected_stdout;
+  std::vector<std::pair<std::string, Files>> mutants;
+};
+
+Image overlay(const Image& base, const Files& files, const std::string& id) {
+  for (auto& kv : files)
+    if (is_grader_path(kv.first)) throw Error("TestFileWrite", "write to grader path blocked: " + kv.first);
+  Image out = base;
+  out.id = id;
+  for (auto& kv : files) out.agent_files[kv.first] = kv.second;
+  return out;
+}
+bool run_hidden(Pool& pool, const Image& img, const CodeTask& task, uint64_t now) {
+  const std::string iid = pool.register_image(img);
+  const std::string snap = pool.snapshot_from_image(iid);
+  const std::string sb = pool.fork_group(snap, 1)[0];
+  ToolResponse resp;
+  try {
+    resp = pool.call(sb, "grade", task.tool, task.payload, task.timeout_s, now);
+  } catch (...) {
+    pool.kill(sb);
+    throw;
+  }
+  pool.kill(sb);
+  return resp.ok && resp.stdout_hash == sha256_hex(task.expected_stdout);
+}
+// score 1 iff the answer passes the hidden run; the tests must kill every mutant, and a task
+// without mutants cannot vouch for a pass.
+std::pair<double, bool> verify_sandboxed(Pool& pool, const CodeTask& task, const Files& answer, uint64_t now) {
+  for (auto& m : task.mutants)
+    if (run_hidden(pool, overlay(task.image, m.second, "mut-" + m.first), task, now))
+      throw Error("WeakTests", "tests pass on mutant " + m.first);
+  const bool passed = run_hidden(pool, overlay(task.image, answer, "ans"), task, now);
+  if (passed && task.mutants.empty()) throw Error("Unverifiable", "unverifiable: no mutants");
+  return {passed ? 1.0 : 0.0, passed};
+}
+
+// -------------------------------------------------------------------------------- rewards
+struct TrajectoryView {
+  bool wrote_test_file = false, special_cased = false, visible_passed = false, hidden_passed = false;
+  std::vector<std::string> test_write_paths;
+  bool is_hack() const { return wrote_test_file || special_cased || (visible_passed && !hidden_passed); }
+  std::vector<std::string> kinds() const {
+    std::vector<std::string> k;
+    if (wrote_test_file) k.push_back("test_write");
+    if (special_cased) k.push_back("special_case");
+    if (visible_passed && !hidden_passed) k.push_back("visible_pass_hidden_fail");
+    return k;
+  }
+};
+
+struct Criterion {
+  std::string id, prompt;
+  double weight = 1.0;
+};
+
+// graders x criteria -> per-grader weighted means; judge(prompt) returns a number in [0, 1]
+std::vector<std::pair<std::string, double>> rubric_score(const std::vector<Criterion>& rubric,
+                                                         const std::vector<std::string>& graders,
+                                                         const std::function<std::string(const std::string&)>& judge,
+                                                         const std::string& output) {
+  if (rubric.empty()) throw Error("EmptyRubric", "empty rubric");
+  if (graders.empty()) throw Error("EmptyPanel", "empty panel");
+  for (auto& c : rubric)
+    if (!std::isfinite(c.weight) || c.weight <= 0.0) throw Error("BadWeight", "criterion weight must be positive");
+  std::vector<std::pair<std::string, double>> out;
+  for (auto& g : graders) {
+    double num = 0.0, den = 0.0;
+    for (auto& c : rubric) {
+      const std::string reply = trim(judge("grader:" + g + "\ncriterion:" + c.id + "\n" + c.prompt + "\n\n" + output));
+      char* end = nullptr;
+      const double v = std::strtod(reply.c_str(), &end);
+      if (reply.empty() || *end != 0) throw Error("Unverifiable", "unverifiable: non-numeric grader reply: " + reply);
+      if (!std::isfinite(v) || v < 0.0 || v > 1.0) throw Error("BadScore", "grader score out of [0, 1]");
+      num += v * c.weight;
+      den += c.weight;
+    }
+    out.emplace_back(g, num / den);
+  }
+  return out;
+}
+// mean x (1 - spread): graders that disagree pull the reward down.
+double rubric_combine(const std::vector<double>& weighted) {
+  if (weighted.empty()) throw Error("EmptyPanel", "empty panel");
+  double sum = 0.0, mn = weighted[0], mx = weighted[0];
+  for (double w : weighted) {
+    sum += w;
+    mn = std::min(mn, w);
+    mx = std::max(mx, w);
+  }
+  return sum / static_cast<double>(weighted.size()) * (1.0 - (mx - mn));
+}
+
+Files to_files(const std::map<std::string, py::bytes>& m) {
+  Files f;
+  for (auto& kv : m) f[kv.first] = std::string(kv.second);
+  return f;
+}
+std::map<std::string, py::bytes> from_files(const Files& f) {
+  std::map<std::string, py::bytes> m;
+  for (auto& kv : f) m[kv.first] = py::bytes(kv.second);
+  return m;
+}
+
+}  // namespace
+
+void bind_rl_envs(py::module_& m) {
+  auto em = m.def_submodule("envs", "sandbox pool with an emulated tool surface");
+  em.attr("GRPO_GROUP") = 16;
+  em.attr("GRADER_ROOT") = "/grader";
+  em.attr("FORK_BUDGET_MS") = 200;
+  em.attr("TOOLS") = std::vector<std::string>(kTools.begin(), kTools.end());
+  py::class_<Image>(em, "Image")
+      .def(py::init([](std::string id, std::map<std::string, py::bytes> agent, std::map<std::string, py::bytes> hidden,
+                       std::map<std::string, std::string> env) {
+             return Image{std::move(id), to_files(agent), to_files(hidden), std::move(env)};
+           }),
+           py::arg("id"), py::arg("agent_files") = std::map<std::string, py::bytes>{},
+           py::arg("hidden_tests") = std::map<std::string, py::bytes>{},
+           py::arg("env") = std::map<std::string, std::string>{})
+      .def_readonly("id", &Image::id);
+  py::class_<TamperFlag>(em, "TamperFlag")
+      .def_readonly("sandbox", &TamperFlag::sandbox)
+      .def_readonly("path", &TamperFlag::path)
+      .def_readonly("call_id", &TamperFlag::call_id)
+      .def_readonly("now_ms", &TamperFlag::now_ms);
+  py::class_<ToolResponse>(em, "ToolResponse")
+      .def_readonly("call_id", &ToolResponse::call_id)
+      .def_readonly("tool", &ToolResponse::tool)
+      .def_readonly("ok", &ToolResponse::ok)
+      .def_property_readonly("stdout", [](const ToolResponse& r) { return py::bytes(r.stdout_bytes); })
+      .def_readonly("stdout_hash", &ToolResponse::stdout_hash)
+      .def_readonly("stderr", &ToolResponse::stderr_text)
+      .def_readonly("duration_ms", &ToolResponse::duration_ms)
+      .def_readonly("child_sandbox", &ToolResponse::child_sandbox);
+  py::class_<PoolConfig>(em, "PoolConfig")
+      .def(py::init([](size_t cap, std::map<std::string, std::pair<py::bytes, uint64_t>> pages, uint64_t cutoff,
+                       std::optional<uint32_t> gpu, uint32_t to) {
+             PoolConfig c;
+             c.capacity = cap;
+             for (auto& kv : pages) c.offline_pages[kv.first] = {std::string(kv.second.first), kv.second.second};
+             c.web_cutoff_unix_s = cutoff;
+             c.gpu_walltime_s = gpu;
+             c.default_timeout_s = to;
+             return c;
+           }),
+           py::arg("capacity") = 64, py::arg("offline_pages") = std::map<std::string, std::pair<py::bytes, uint64_t>>{},
+           py::arg("web_cutoff_unix_s") = 0, py::arg("gpu_walltime_s") = py::none(), py::arg("default_timeout_s") = 60);
+  py::class_<Pool>(em, "Pool")
+      .def(py::init<PoolConfig>(), py::arg("config") = PoolConfig{})
+      .def("live_count", &Pool::live_count)
+      .def_property_readonly("tamper_flags", &Pool::tamper_flags)
+      .def("register_image", &Pool::register_image)
+      .def("snapshot_from_image", &Pool::snapshot_from_image)
+      .def("fork_group", &Pool::fork_group, py::arg("snapshot"), py::arg("n") = 16)
+      .def("fork_pair", [](Pool& p, const std::string& s) { return p.fork_group(s, 2); })
+      .def("call", [](Pool& p, const std::string& sb, const std::string& call_id, const std::string& tool,
+                      const std::string& payload_json, std::optional<uint32_t> timeout_s, uint64_t now) {
+             return p.call(sb, call_id, tool, Json::parse(payload_json), timeout_s, now);
+           }, py::arg("sandbox"), py::arg("call_id"), py::arg("tool"), py::arg("payload_json") = "{}",
+           py::arg("timeout_s") = py::none(), py::arg("now") = 0)
+      .def("snapshot", &Pool::snapshot)
+      .def("kill", &Pool::kill)
+      .def("agent_view", [](const Pool& p, const std::string& sb) { return from_files(p.agent_view(sb)); })
+      .def("grader_view", [](const Pool& p, const std::string& sb) { return from_files(p.grader_view(sb)); });
+
+  auto vm = m.def_submodule("verifiers", "exact verifiers");
+  vm.attr("GRID_PASS_K") = 2;
+  vm.attr("PROB_EPS") = 1e-12;
+  vm.def("math_canonicalize", &math_canonicalize);
+  vm.def("math_equivalent", &math_equivalent);
+  vm.def("tiny_kernel_check", &tiny_kernel_check);
+  vm.def("grid_pass_at_2", &grid_pass_at_2);
+  vm.def("relative_log_score", &relative_log_score);
+  py::class_<CodeTask>(vm, "CodeTask")
+      .def(py::init([](Image image, std::string payload_json, py::bytes expected, uint32_t timeout_s, std::string tool,
+                       std::vector<std::pair<std::string, std::map<std::string, py::bytes>>> mutants) {
+             CodeTask t;
+             t.image = std::move(image);
+             t.payload = Json::parse(payload_json);
+             t.expected_stdout = expected;
+             t.timeout_s = timeout_s;
+             t.tool = std::move(tool);
+             for (auto& mu : mutants) t.mutants.emplace_back(mu.first, to_files(mu.second));
+             return t;
+           }),
+           py::arg("image"), py::arg("payload_json"), py::arg("expected_stdout"), py::arg("timeout_s") = 60,
+           py::arg("tool") = "python",
+           py::arg("mutants") = std::vector<std::pair<std::string, std::map<std::string, py::bytes>>>{});
+  vm.def("verify_sandboxed", [](Pool& pool, const CodeTask& task, std::map<std::string, py::bytes> answer, uint64_t now) {
+    return verify_sandboxed(pool, task, to_files(answer), now);
+  }, py::arg("pool"), py::arg("task"), py::arg("answer_files"), py::arg("now") = 0);
+
+  auto rm = m.def_submodule("rewards", "rubric panel, pair filters, tampering detector");
+  rm.attr("DISAGREE_EPS") = 0.25;
+  py::class_<TrajectoryView>(rm, "TrajectoryView")
+      .def(py::init([](bool w, bool s, bool v, bool h, std::vector<std::string> paths) {
+             return TrajectoryView{w, s, v, h, std::move(paths)};
+           }),
+           py::arg("wrote_test_file") = false, py::arg("special_cased") = false, py::arg("visible_passed") = false,
+           py::arg("hidden_passed") = false, py::arg("test_write_paths") = std::vector<std::string>{})
+      .def("is_confirmed_hack", &TrajectoryView::is_hack)
+      .def("kinds", &TrajectoryView::kinds);
+  py::class_<Criterion>(rm, "Criterion")
+      .def(py::init([](std::string id, std::string prompt, double w) { return Criterion{std::move(id), std::move(prompt), w}; }),
+           py::arg("id"), py::arg("prompt"), py::arg("weight") = 1.0);
+  rm.def("rubric_score", &rubric_score, py::arg("rubric"), py::arg("grader_ids"), py::arg("judge"), py::arg("output"));
+  rm.def("rubric_combine", &rubric_combine);
+  rm.def("tamper_pair_keep", [](const TrajectoryView& pos, const TrajectoryView& neg) {
+    if (!(neg.is_hack() && !pos.is_hack())) throw Error("UnconfirmedPair", "contrastive pair is not confirmed");
+  });
+  rm.def("rescore_keep", [](double pos, double neg) {
+    if (!(pos > neg)) throw Error("UnconfirmedPair", "contrastive pair is not confirmed");
+  });
+  rm.def("tamper_verify", [](const TrajectoryView& v) {
+    const bool hack = v.is_hack();
+    return py::make_tuple(hack ? 0.0 : 1.0, !hack, hack ? std::vector<std::string>{"tampering"} : std::vector<std::string>{});
+  });
+  rm.def("held_out_recall", [](const std::vector<TrajectoryView>& views) {
+    size_t flagged = 0;
+    for (auto& v : views) flagged += v.is_hack() ? 1 : 0;
+    return views.empty() ? 0.0 : static_cast<double>(flagged) / static_cast<double>(views.size());
+  });
+  rm.def("refuse_exact", [](const std::string& id) { throw Error("ExactVerifier", "exact verifier " + id + " must not be replaced by a learned reward"); });
+}
