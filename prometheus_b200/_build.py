@@ -115,7 +115,7 @@ def build_native(verbose: bool = False, force: bool = False) -> Path | None:
             list(ex.map(lambda c: _run(c, verbose), jobs))
     out = native_lib_path()
     if force or jobs or _newer(objs, out):
-        _run(["g++", "-shared", "-o", out, *objs, "-lpthread"], verbose)
+        _run(["g++", "-shared", "-o", out, *objs, "-lpthread", "-lz"], verbose)
     return out
 
 
