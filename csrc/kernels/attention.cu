@@ -1,0 +1,700 @@
+// Causal softmax attention with grouped KV heads on tcgen05 (sm_100a), head dim 128.
+//
+// Forward (flash-style, one CTA per 128 query rows of one head):
+//   S = Q K_j^T  (tensor memory, double-buffered)      P = exp2(S c - m)   (registers, one
+//   O += P V_j   (tensor memory)                                             query row per thread)
+// The running maximum is only raised when it would grow by more than 2^8 (the rescale of O is a
+// tensor-memory read-modify-write, so it is skipped while the stale maximum is safe); the final
+// O / l and the log-sum-exp use the maximum actually applied, which keeps the result exact.
+//
+// Backward, two kernels sharing one skeleton (no atomics, deterministic):
+//   dQ  : CTA = 128 query rows; streams 64-key tiles   S = Q K^T, dP = dO V^T, dS = P (dP - delta) c
+//         dQ += dS K
+//   dKV : CTA = 128 key rows of one KV head; streams 64-query tiles of every query head of the
+//         group  S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q
+// Every streamed tile is used twice from the same shared-memory image: as the K-major B operand
+// of the score product and as the MN-major B operand of the gradient product.
+//
+// warps 0-3: one tensor-memory lane (= row) per thread; warp 4: MMA issue; warp 5: TMA producer.
+// All tensors are token-major: Q/O/dO/dQ [batch * seq, ldq] with head h at columns 128 h,
+// K/V/dK/dV [batch * seq, ldkv] with KV head g at columns 128 g. seq must be a multiple of 128.
+//
+// Reference semantics: model/__init__.py gqa/mla attention (softmax(q k^T / sqrt(d)) v with a
+// causal mask) of the reference; the tiling is this library's own.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace pb {
+
+int make_tmap_3d(CUtensorMap* tm, const void* base, int elem_bytes, uint64_t inner,
+                 uint64_t outer, uint64_t batch, uint64_t ld_elems, uint64_t batch_stride_elems,
+                 uint32_t box_inner, uint32_t box_outer);
+
+namespace attn {
+
+constexpr int D = 128;
+constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 16-byte store of 8 bf16 into a [rows][64] 128B-swizzled chunk (row pitch 128 bytes).
+__device__ __forceinline__ void st_swz(uint8_t* chunk_base, int row, int c16, const bf16x8& v) {
+  *reinterpret_cast<bf16x8*>(chunk_base + row * 128 + ((c16 ^ (row & 7)) << 4)) = v;
+}
+__device__ __forceinline__ bf16x8 pack_bf16x8(const float* f) {
+  bf16x8 pk;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) pk.v[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  return pk;
+}
+__device__ __forceinline__ void sync_rows() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Warp-uniform bounded wait: the row warps run warp-collective tensor-memory loads, so either
+// every lane goes on or none does.
+__device__ __forceinline__ bool wait_all(uint64_t* bar, uint32_t parity, int* status) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, status));
+}
+
+// ------------------------------------------------------------------------------ forward
+namespace fwd {
+constexpr int Q_OFF = 0, K_OFF = 32768, V_OFF = 98304, P_OFF = 163840, BARS = 196608;
+constexpr int SMEM = BARS + 256 + 1024;
+constexpr uint32_t COL_S = 0, COL_O = 256, TMEM_COLS = 512;
+
+struct Params {
+  int seq, heads, kv_heads, n_qb;
+  float scale_log2;   // softmax scale * log2(e)
+  float* lse2;        // [batch, heads, seq], log2 domain
+  float* rowmax;      // [batch, heads, seq] largest scaled logit of the row, or null
+  int* status;
+};
+
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BARS);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_done = bars + 9;    // [2]
+  uint64_t* s_free = bars + 11;   // [2]
+  uint64_t* p_ready = bars + 13;
+  uint64_t* o_done = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = p.n_qb - 1 - static_cast<int>(blockIdx.x);  // longest rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (p.heads / p.kv_heads);
+  const int n_kv = qb + 1;
+  const int row0 = b * p.seq + qb * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_done[i], 1); mbar_init(&s_free[i], 128);
+    }
+    mbar_init(p_ready, 128); mbar_init(o_done, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 5) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, 32768);
+      tma_load_3d(smem + Q_OFF, &tmQ, q_full, h * D, row0, 0);
+      tma_load_3d(smem + Q_OFF + 16384, &tmQ, q_full, h * D + 64, row0, 0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int krow = b * p.seq + j * 128;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, p.status)) break;
+        mbar_arrive_expect_tx(&k_full[s], 32768);
+        tma_load_3d(smem + K_OFF + s * 32768, &tmK, &k_full[s], g * D, krow, 0);
+        tma_load_3d(smem + K_OFF + s * 32768 + 16384, &tmK, &k_full[s], g * D + 64, krow, 0);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, p.status)) break;
+        mbar_arrive_expect_tx(&v_full[s], 32768);
+        tma_load_3d(smem + V_OFF + s * 32768, &tmV, &v_full[s], g * D, krow, 0);
+        tma_load_3d(smem + V_OFF + s * 32768 + 16384, &tmV, &v_full[s], g * D + 64, krow, 0);
+      }
+    }
+  } else if (warp == 4) {
+    if (lane == 0) {
+      const uint32_t id_kk = make_idesc(1, 1, 128, 128, 0, 0);
+      const uint32_t id_kn = make_idesc(1, 1, 128, 128, 0, 1);
+      const uint32_t qa = smem_u32(smem + Q_OFF), pa = smem_u32(smem + P_OFF);
+      bool ok = mbar_wait(q_full, 0, p.status);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[s], ph, p.status)) return false;
+        if (!mbar_wait(&s_free[s], ph ^ 1, p.status)) return false;
+        tc_fence_after();
+        const uint32_t ka = smem_u32(smem + K_OFF + s * 32768);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj)
+          umma_f16(tmem + COL_S + s * 128,
+                   make_sdesc_sw128(qa + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024),
+                   make_sdesc_sw128(ka + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024), id_kk,
+                   jj > 0);
+        umma_commit(&s_done[s]);
+        umma_commit(&k_empty[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (j + 1 < n_kv && !issue_s(j + 1)) break;
+        if (!mbar_wait(p_ready, j & 1, p.status)) break;
+        if (!mbar_wait(&v_full[s], ph, p.status)) break;
+        tc_fence_after();
+        const uint32_t va = smem_u32(smem + V_OFF + s * 32768);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj)
+          umma_f16(tmem + COL_O, make_sdesc_sw128(pa + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024),
+                   make_sdesc_sw128(va + jj * 2048, 16384, 1024), id_kn, (j > 0) || (jj > 0));
+        umma_commit(o_done);
+        umma_commit(&v_empty[s]);
+      }
+    }
+  } else {
+    const int r = threadIdx.x;  // query row of the tile = tensor-memory lane
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    uint8_t* pbuf = smem + P_OFF;
+    const int qpos = qb * 128 + r;
+    float m_used = -INFINITY, m_true = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      const bool diag = (j == qb);
+      if (!wait_all(&s_done[s], ph, p.status)) { ok = false; break; }
+      tc_fence_after();
+      // pass 1: row maximum of the scaled scores
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + COL_S + s * 128 + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float x = __uint_as_float(v[i]) * p.scale_log2;
+          if (!diag || c + i <= r) mx = fmaxf(mx, x);
+        }
+      }
+      m_true = fmaxf(m_true, mx);
+      if (j > 0) {
+        // the previous P V product has finished: P may be rewritten, O may be rescaled
+        if (!wait_all(o_done, (j - 1) & 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, mx > m_used + RESCALE_THRESHOLD)) {
+          const float m_new = fmaxf(m_used, mx);
+          const float alpha = ex2(m_used - m_new);
+          l *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(lane_addr + COL_O + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32b_x32(lane_addr + COL_O + c, v);
+          }
+          tmem_st_wait();
+          m_used = m_new;
+        }
+      } else {
+        m_used = mx;
+      }
+      // pass 2: probabilities -> bf16 operand image
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + COL_S + s * 128 + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float f[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int col = c + 8 * i + k;
+            const float e = ex2(__uint_as_float(v[8 * i + k]) * p.scale_log2 - m_used);
+            f[k] = (!diag || col <= r) ? e : 0.f;
+            l += f[k];
+          }
+          const int col = c + 8 * i;
+          st_swz(pbuf + (col >> 6) * 16384, r, (col & 63) >> 3, pack_bf16x8(f));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&s_free[s]);
+      fence_proxy_async_smem();
+      mbar_arrive(p_ready);
+    }
+    if (ok && wait_all(o_done, (n_kv - 1) & 1, p.status)) {
+      tc_fence_after();
+      const float inv = 1.f / l;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + COL_O + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float f[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[8 * i + k]) * inv;
+          const int col = c + 8 * i;
+          st_swz(pbuf + (col >> 6) * 16384, r, (col & 63) >> 3, pack_bf16x8(f));
+        }
+      }
+      const size_t vi = (static_cast<size_t>(b) * p.heads + h) * p.seq + qpos;
+      p.lse2[vi] = m_used + log2f(l);
+      if (p.rowmax != nullptr) p.rowmax[vi] = m_true * 0.6931471805599453f;
+      fence_proxy_async_smem();
+      sync_rows();
+      if (r == 0) {
+        tma_store_3d(&tmO, pbuf, h * D, row0, 0);
+        tma_store_3d(&tmO, pbuf + 16384, h * D + 64, row0, 0);
+        tma_store_commit();
+        tma_store_wait<0>();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != PB_OK) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies in flight land
+    __syncthreads();
+  }
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+}  // namespace fwd
+
+// ----------------------------------------------------------------------------- backward
+namespace bwd {
+constexpr int RA_OFF = 0, RB_OFF = 32768, ST_OFF = 65536;       // stages: T1 16 KB + T2 16 KB
+constexpr int DS_OFF = ST_OFF + 2 * 32768, PT_OFF = DS_OFF + 2 * 16384;
+constexpr int VEC_OFF = PT_OFF + 2 * 16384, BARS = VEC_OFF + 2 * 512;
+constexpr int SMEM = BARS + 256 + 1024;
+constexpr uint32_t COL_X1 = 0, COL_X2 = 128, COL_ACC1 = 256, COL_ACC2 = 384, TMEM_COLS = 512;
+
+struct Params {
+  int seq, heads, kv_heads, n_blk;  // n_blk = seq / 128
+  float scale_log2, scale;
+  const float* lse2;    // [batch, heads, seq]
+  const float* delta;   // [batch, heads, seq]  rowsum(dO * O)
+  int* status;
+};
+
+// DKV = false: resident Q, dO (one head); streams K, V tiles; output dQ.
+// DKV = true : resident K, V (one KV head); streams Q, dO tiles of the group; outputs dK, dV.
+template <bool DKV>
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant__ CUtensorMap tmRB,
+                const __grid_constant__ CUtensorMap tmT1, const __grid_constant__ CUtensorMap tmT2,
+                const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
+                const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BARS);
+  uint64_t* r_full = bars;
+  uint64_t* t_full = bars + 1;    // [2]
+  uint64_t* t_empty = bars + 3;   // [2]
+  uint64_t* x_done = bars + 5;    // [2]
+  uint64_t* x_free = bars + 7;    // [2]
+  uint64_t* pd_ready = bars + 9;  // [2]
+  uint64_t* pd_free = bars + 11;  // [2]
+  uint64_t* acc_done = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = p.heads / p.kv_heads;
+  const int b = blockIdx.z;
+  // dQ: heavy blocks are the late query blocks; dKV: the early key blocks.
+  const int blk = DKV ? static_cast<int>(blockIdx.x) : p.n_blk - 1 - static_cast<int>(blockIdx.x);
+  const int hy = blockIdx.y;                       // query head (dQ) or KV head (dKV)
+  const int g = DKV ? hy : hy / group;
+  const int n64 = p.seq / 64;
+  const int t_first = DKV ? 2 * blk : 0;           // first streamed 64-row tile
+  const int t_count = DKV ? n64 - 2 * blk : 2 * blk + 2;
+  const int n_it = DKV ? group * t_count : t_count;
+  const int row0 = b * p.seq + blk * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(r_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 1);
+      mbar_init(&x_done[i], 1); mbar_init(&x_free[i], 128);
+      mbar_init(&pd_ready[i], 128); mbar_init(&pd_free[i], 1);
+    }
+    mbar_init(acc_done, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmRA); tma_prefetch_desc(&tmRB);
+    tma_prefetch_desc(&tmT1); tma_prefetch_desc(&tmT2);
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 5) {
+    if (lane == 0) {
+      const int rx = (DKV ? g : hy) * D;
+      mbar_arrive_expect_tx(r_full, 65536);
+      tma_load_3d(smem + RA_OFF, &tmRA, r_full, rx, row0, 0);
+      tma_load_3d(smem + RA_OFF + 16384, &tmRA, r_full, rx + 64, row0, 0);
+      tma_load_3d(smem + RB_OFF, &tmRB, r_full, rx, row0, 0);
+      tma_load_3d(smem + RB_OFF + 16384, &tmRB, r_full, rx + 64, row0, 0);
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        const int t = t_first + (DKV ? it % t_count : it);
+        const int tx = (DKV ? g * group + it / t_count : g) * D;
+        const int trow = b * p.seq + t * 64;
+        if (!mbar_wait(&t_empty[s], ph ^ 1, p.status)) break;
+        mbar_arrive_expect_tx(&t_full[s], 32768);
+        uint8_t* st = smem + ST_OFF + s * 32768;
+        tma_load_3d(st, &tmT1, &t_full[s], tx, trow, 0);
+        tma_load_3d(st + 8192, &tmT1, &t_full[s], tx + 64, trow, 0);
+        tma_load_3d(st + 16384, &tmT2, &t_full[s], tx, trow, 0);
+        tma_load_3d(st + 16384 + 8192, &tmT2, &t_full[s], tx + 64, trow, 0);
+      }
+    }
+  } else if (warp == 4) {
+    if (lane == 0) {
+      const uint32_t id_x = make_idesc(1, 1, 128, 64, 0, 0);     // A K-major, B K-major, N = 64
+      const uint32_t id_acc = make_idesc(1, 1, 128, 128, 0, 1);  // A K-major, B MN-major
+      const uint32_t ra = smem_u32(smem + RA_OFF), rb = smem_u32(smem + RB_OFF);
+      bool ok = mbar_wait(r_full, 0, p.status);
+      auto issue_x = [&](int it) -> bool {
+        const int s = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&t_full[s], ph, p.status)) return false;
+        if (!mbar_wait(&x_free[s], ph ^ 1, p.status)) return false;
+        tc_fence_after();
+        const uint32_t t1 = smem_u32(smem + ST_OFF + s * 32768), t2 = t1 + 16384;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj)
+          umma_f16(tmem + COL_X1 + s * 64,
+                   make_sdesc_sw128(ra + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024),
+                   make_sdesc_sw128(t1 + (jj >> 2) * 8192 + (jj & 3) * 32, 16, 1024), id_x, jj > 0);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj)
+          umma_f16(tmem + COL_X2 + s * 64,
+                   make_sdesc_sw128(rb + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024),
+                   make_sdesc_sw128(t2 + (jj >> 2) * 8192 + (jj & 3) * 32, 16, 1024), id_x, jj > 0);
+        umma_commit(&x_done[s]);
+        return true;
+      };
+      if (ok) ok = issue_x(0);
+      int it = 0;
+      for (; it < n_it && ok; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (it + 1 < n_it && !issue_x(it + 1)) break;
+        if (!mbar_wait(&pd_ready[s], ph, p.status)) break;
+        tc_fence_after();
+        const uint32_t t1 = smem_u32(smem + ST_OFF + s * 32768), t2 = t1 + 16384;
+        const uint32_t ds = smem_u32(smem + DS_OFF + s * 16384);
+        const uint32_t pt = smem_u32(smem + PT_OFF + s * 16384);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          umma_f16(tmem + COL_ACC1, make_sdesc_sw128(ds + jj * 32, 16, 1024),
+                   make_sdesc_sw128(t1 + jj * 2048, 8192, 1024), id_acc, (it > 0) || (jj > 0));
+        if (DKV) {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            umma_f16(tmem + COL_ACC2, make_sdesc_sw128(pt + jj * 32, 16, 1024),
+                     make_sdesc_sw128(t2 + jj * 2048, 8192, 1024), id_acc, (it > 0) || (jj > 0));
+        }
+        umma_commit(&t_empty[s]);
+        umma_commit(&pd_free[s]);
+      }
+      if (it == n_it) umma_commit(acc_done);
+    }
+  } else {
+    const int r = threadIdx.x;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const int pos = blk * 128 + r;   // query position (dQ) or key position (dKV) of this row
+    float row_lse = 0.f, row_delta = 0.f;
+    if (!DKV) {
+      const size_t vi = (static_cast<size_t>(b) * p.heads + hy) * p.seq + pos;
+      row_lse = p.lse2[vi];
+      row_delta = p.delta[vi];
+    }
+    // dKV: per-column log-sum-exp and delta of the streamed query tile, prefetched one
+    // iteration ahead by threads 0..63 (lse) and 64..127 (delta).
+    auto vec_src = [&](int it) -> const float* {
+      const int t = t_first + it % t_count;
+      const int h = g * group + it / t_count;
+      const float* base = (r < 64) ? p.lse2 : p.delta;
+      return base + (static_cast<size_t>(b) * p.heads + h) * p.seq + t * 64 + (r & 63);
+    };
+    float vec_next = (DKV && n_it > 0) ? *vec_src(0) : 0.f;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int s = it & 1;
+      const uint32_t ph = (it >> 1) & 1;
+      const int t = t_first + (DKV ? it % t_count : it);
+      float* vec = reinterpret_cast<float*>(smem + VEC_OFF + s * 512);
+      if (DKV) {
+        vec[r] = vec_next;   // [0,64) lse2, [64,128) delta; readers of two iterations ago are done
+        if (it + 1 < n_it) vec_next = *vec_src(it + 1);
+        sync_rows();
+      }
+      if (!wait_all(&x_done[s], ph, p.status)) { ok = false; break; }
+      if (!wait_all(&pd_free[s], ph ^ 1, p.status)) { ok = false; break; }
+      tc_fence_after();
+      // mask: dQ rows are queries, columns keys (key > query is masked);
+      //       dKV rows are keys, columns queries (query < key is masked)
+      const bool edge = DKV ? (t * 64 < blk * 128 + 127) : (t * 64 + 63 > blk * 128);
+      uint8_t* dsb = smem + DS_OFF + s * 16384;
+      uint8_t* ptb = smem + PT_OFF + s * 16384;
+#pragma unroll 1
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t x1[32], x2[32];
+        tmem_ld_32x32b_x32(lane_addr + COL_X1 + s * 64 + c, x1);
+        tmem_ld_32x32b_x32(lane_addr + COL_X2 + s * 64 + c, x2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float pf[8], df[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int col = c + 8 * i + k;
+            const float lse = DKV ? vec[col] : row_lse;
+            const float dl = DKV ? vec[64 + col] : row_delta;
+            float pr = ex2(__uint_as_float(x1[8 * i + k]) * p.scale_log2 - lse);
+            if (edge) {
+              const int other = t * 64 + col;
+              const bool masked = DKV ? (other < pos) : (other > pos);
+              if (masked) pr = 0.f;
+            }
+            pf[k] = pr;
+            df[k] = pr * (__uint_as_float(x2[8 * i + k]) - dl) * p.scale;
+          }
+          const int c16 = (c >> 3) + i;
+          st_swz(dsb, r, c16, pack_bf16x8(df));
+          if (DKV) st_swz(ptb, r, c16, pack_bf16x8(pf));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&x_free[s]);
+      fence_proxy_async_smem();
+      mbar_arrive(&pd_ready[s]);
+    }
+    if (ok && wait_all(acc_done, 0, p.status)) {
+      tc_fence_after();
+      // resident tiles are no longer read: reuse them as the staging for the TMA stores
+#pragma unroll 1
+      for (int a = 0; a < (DKV ? 2 : 1); ++a) {
+        uint8_t* stage = smem + (a == 0 ? RA_OFF : RB_OFF);
+        const uint32_t col0 = a == 0 ? COL_ACC1 : COL_ACC2;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(lane_addr + col0 + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float f[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[8 * i + k]);
+            const int col = c + 8 * i;
+            st_swz(stage + (col >> 6) * 16384, r, (col & 63) >> 3, pack_bf16x8(f));
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      sync_rows();
+      if (r == 0) {
+        const int ox = (DKV ? g : hy) * D;
+        tma_store_3d(&tmO1, smem + RA_OFF, ox, row0, 0);
+        tma_store_3d(&tmO1, smem + RA_OFF + 16384, ox + 64, row0, 0);
+        if (DKV) {
+          tma_store_3d(&tmO2, smem + RB_OFF, ox, row0, 0);
+          tma_store_3d(&tmO2, smem + RB_OFF + 16384, ox + 64, row0, 0);
+        }
+        tma_store_commit();
+        tma_store_wait<0>();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != PB_OK) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// delta[b, h, s] = sum_d dO * O  (one warp per row)
+__global__ void attn_delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ dout,
+                                  float* __restrict__ delta, int rows, int seq, int heads, int ldo,
+                                  int lddo) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= rows * heads) return;
+  const int tok = w / heads, h = w % heads;
+  const bf16* po = o + static_cast<size_t>(tok) * ldo + h * D + lane * 4;
+  const bf16* pd = dout + static_cast<size_t>(tok) * lddo + h * D + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(po), d = *reinterpret_cast<const uint2*>(pd);
+  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float2 x = __bfloat1622float2(a2[i]), y = __bfloat1622float2(d2[i]);
+    acc += x.x * y.x + x.y * y.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    const int bb = tok / seq, s = tok % seq;
+    delta[(static_cast<size_t>(bb) * heads + h) * seq + s] = acc;
+  }
+}
+}  // namespace bwd
+
+static bool bad_geometry(int batch, int seq, int heads, int kv_heads, int ldq, int ldkv) {
+  return batch <= 0 || seq <= 0 || seq % 128 != 0 || heads <= 0 || kv_heads <= 0 ||
+         heads % kv_heads != 0 || ldq < heads * D || ldkv < kv_heads * D || ldq % 8 != 0 ||
+         ldkv % 8 != 0;
+}
+
+}  // namespace attn
+}  // namespace pb
+
+using namespace pb;
+
+// out = softmax(scale * Q K^T + causal mask) V.  q/out: [batch * seq, ldq / ldo] bf16 with head h
+// at columns [128 h, 128 h + 128); k/v: [batch * seq, ldkv] with KV head g likewise.
+// lse2: fp32 [batch, heads, seq], log2 of the softmax denominator plus the applied maximum.
+// rowmax (optional): fp32 [batch, heads, seq], the largest scaled logit of each row.
+PB_API int pb_attn_fwd(const void* q, const void* k, const void* v, void* out, void* lse2,
+                       void* rowmax, int batch, int seq, int heads, int kv_heads, int ldq, int ldkv,
+                       int ldo, float scale, int* status, cudaStream_t st) {
+  using namespace attn;
+  if (bad_geometry(batch, seq, heads, kv_heads, ldq, ldkv) || ldo < heads * D || ldo % 8 != 0)
+    return PB_BAD_ARG;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(fwd::attn_fwd_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, fwd::SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const uint64_t rows = static_cast<uint64_t>(batch) * seq;
+  CUtensorMap tQ, tK, tV, tO;
+  int r = 0;
+  r |= make_tmap_3d(&tQ, q, 2, static_cast<uint64_t>(heads) * D, rows, 1, ldq, 0, 64, 128);
+  r |= make_tmap_3d(&tK, k, 2, static_cast<uint64_t>(kv_heads) * D, rows, 1, ldkv, 0, 64, 128);
+  r |= make_tmap_3d(&tV, v, 2, static_cast<uint64_t>(kv_heads) * D, rows, 1, ldkv, 0, 64, 128);
+  r |= make_tmap_3d(&tO, out, 2, static_cast<uint64_t>(heads) * D, rows, 1, ldo, 0, 64, 128);
+  if (r != 0) return 1000 + r;
+  fwd::Params p;
+  p.seq = seq; p.heads = heads; p.kv_heads = kv_heads; p.n_qb = seq / 128;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse2 = static_cast<float*>(lse2);
+  p.rowmax = static_cast<float*>(rowmax);
+  p.status = status;
+  fwd::attn_fwd_kernel<<<dim3(p.n_qb, heads, batch), 192, fwd::SMEM, st>>>(tQ, tK, tV, tO, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Gradients of pb_attn_fwd. delta: fp32 scratch [batch, heads, seq] (written here).
+// dq: [batch * seq, ldq]; dk, dv: [batch * seq, ldkv] (all bf16, fully overwritten).
+PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* out,
+                       const void* dout, const void* lse2, void* delta, void* dq, void* dk,
+                       void* dv, int batch, int seq, int heads, int kv_heads, int ldq, int ldkv,
+                       int ldo, float scale, int* status, cudaStream_t st) {
+  using namespace attn;
+  if (bad_geometry(batch, seq, heads, kv_heads, ldq, ldkv) || ldo < heads * D || ldo % 8 != 0)
+    return PB_BAD_ARG;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(bwd::attn_bwd_kernel<false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, bwd::SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(bwd::attn_bwd_kernel<true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, bwd::SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const uint64_t rows = static_cast<uint64_t>(batch) * seq;
+  const uint64_t qi = static_cast<uint64_t>(heads) * D, ki = static_cast<uint64_t>(kv_heads) * D;
+  {
+    const long long warps = static_cast<long long>(rows) * heads;
+    const int blocks = static_cast<int>((warps * 32 + 255) / 256);
+    bwd::attn_delta_kernel<<<blocks, 256, 0, st>>>(
+        static_cast<const bf16*>(out), static_cast<const bf16*>(dout), static_cast<float*>(delta),
+        static_cast<int>(rows), seq, heads, ldo, ldo);
+  }
+  bwd::Params p;
+  p.seq = seq; p.heads = heads; p.kv_heads = kv_heads; p.n_blk = seq / 128;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse2 = static_cast<const float*>(lse2);
+  p.delta = static_cast<const float*>(delta);
+  p.status = status;
+  int r = 0;
+  {
+    // dQ: resident Q, dO (128-row boxes); streamed K, V (64-row boxes)
+    CUtensorMap tQ, tDO, tK, tV, tDQ;
+    r |= make_tmap_3d(&tQ, q, 2, qi, rows, 1, ldq, 0, 64, 128);
+    r |= make_tmap_3d(&tDO, dout, 2, qi, rows, 1, ldo, 0, 64, 128);
+    r |= make_tmap_3d(&tK, k, 2, ki, rows, 1, ldkv, 0, 64, 64);
+    r |= make_tmap_3d(&tV, v, 2, ki, rows, 1, ldkv, 0, 64, 64);
+    r |= make_tmap_3d(&tDQ, dq, 2, qi, rows, 1, ldq, 0, 64, 128);
+    if (r != 0) return 1000 + r;
+    bwd::attn_bwd_kernel<false><<<dim3(p.n_blk, heads, batch), 192, bwd::SMEM, st>>>(
+        tQ, tDO, tK, tV, tDQ, tDQ, p);
+  }
+  {
+    // dK, dV: resident K, V; streamed Q, dO
+    CUtensorMap tK, tV, tQ, tDO, tDK, tDV;
+    r |= make_tmap_3d(&tK, k, 2, ki, rows, 1, ldkv, 0, 64, 128);
+    r |= make_tmap_3d(&tV, v, 2, ki, rows, 1, ldkv, 0, 64, 128);
+    r |= make_tmap_3d(&tQ, q, 2, qi, rows, 1, ldq, 0, 64, 64);
+    r |= make_tmap_3d(&tDO, dout, 2, qi, rows, 1, ldo, 0, 64, 64);
+    r |= make_tmap_3d(&tDK, dk, 2, ki, rows, 1, ldkv, 0, 64, 128);
+    r |= make_tmap_3d(&tDV, dv, 2, ki, rows, 1, ldkv, 0, 64, 128);
+    if (r != 0) return 2000 + r;
+    bwd::attn_bwd_kernel<true><<<dim3(p.n_blk, kv_heads, batch), 192, bwd::SMEM, st>>>(
+        tK, tV, tQ, tDO, tDK, tDV, p);
+  }
+  return static_cast<int>(cudaGetLastError());
+}

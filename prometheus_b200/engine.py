@@ -112,6 +112,10 @@ class Trainer:
         # block-scaled FP8 forward for the FFN / expert products (1 x 128 activations,
         # 128 x 128 weights), straight-through bf16 backward
         self.fp8 = bool(fp8)
+        # per-layer, per-head largest attention logit of the last forward (the statistic the
+        # MuonClip-style QK-clip monitors); filled by the attention kernel when switched on
+        self.track_max_logit = False
+        self.max_logits: dict[int, Tensor] = {}
         self.ep_ctx = None
         if self.ep and model_config.n_routed_experts % self.world:
             raise ValueError("expert parallelism needs n_routed_experts divisible by the world size")
@@ -540,7 +544,11 @@ class Trainer:
         k = ops.rope_(k, seq_len=S, base=cfg.rope_base)
         from .ops import attention
 
-        o = attention.causal_gqa(q, k, v)
+        if self.track_max_logit:
+            o, rowmax = attention.causal_gqa(q, k, v, return_max_logit=True)
+            self.max_logits[i] = rowmax.amax(dim=(0, 2))      # per head, for QK-clip
+        else:
+            o = attention.causal_gqa(q, k, v)
         return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
 
     def forward_hidden(self, tokens: Tensor, inputs_embeds: Tensor | None = None) -> Tensor:

@@ -42,6 +42,8 @@ _SIGS = {
     "pb_set_flag": [P, I, P],
     "pb_delta_scan_fwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
     "pb_delta_scan_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
+    "pb_attn_fwd": [P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P],
+    "pb_attn_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P],
     "pb_delta_prep_fwd": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, P, I, P],
     "pb_delta_prep_bwd": [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, I, P],
     "pb_gemm_bf16_grouped": [P, P, P, I, I, I, I, L, L, L, L, I, P, P, I, P],

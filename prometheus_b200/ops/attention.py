@@ -1,18 +1,101 @@
-"""Causal softmax attention with grouped KV heads (the 6 GQA layers of the hybrid).
+"""Causal softmax attention with grouped KV heads (the GQA layers of the hybrid).
 
-Current implementation: PyTorch's fused scaled-dot-product attention (a library
-kernel) with the same scale (1/sqrt(D)) and causal mask as ``model.gqa_attention``.
-The delta-rule layers (3 of every 4) and every GEMM run on this package's own
-kernels; a tcgen05 flash-attention kernel for these layers is the open item.
+On a GPU with head dim 128 this runs the package's own tcgen05 kernels
+(``csrc/kernels/attention.cu``): a flash-style forward with the scores and the output
+accumulator in tensor memory, and a two-kernel deterministic backward (dQ; dK/dV). q, k, v
+are read in place from their ``(B, S, H, 128)`` layout. Other geometries and the CPU use the
+plain fp32 formula, which is also the oracle of the tests
+(reference: model/__init__.py softmax attention with a causal mask, scale 1/sqrt(d)).
 """
 from __future__ import annotations
 
+import math
+
 import torch
-import torch.nn.functional as F
+from torch import Tensor
 
 
-def causal_gqa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-    """q: (B, S, Hq, D); k, v: (B, S, Hkv, D) -> (B, S, Hq, D)."""
-    o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                       is_causal=True, enable_gqa=True)
-    return o.transpose(1, 2).contiguous()
+def causal_gqa_ref(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None) -> Tensor:
+    """fp32 oracle. q: (B, S, Hq, D); k, v: (B, S, Hkv, D) -> (B, S, Hq, D) in q's dtype."""
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    qf = q.float().transpose(1, 2)
+    kf = k.float().transpose(1, 2).repeat_interleave(hq // hkv, dim=1)
+    vf = v.float().transpose(1, 2).repeat_interleave(hq // hkv, dim=1)
+    logits = qf @ kf.transpose(-1, -2) * scale
+    mask = torch.ones(s, s, dtype=torch.bool, device=q.device).tril()
+    logits = logits.masked_fill(~mask, float("-inf"))
+    return (torch.softmax(logits, dim=-1) @ vf).transpose(1, 2).to(q.dtype)
+
+
+class _AttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale, want_max):
+        from ._lib import call, ptr, stream_ptr
+        from .functional import status_word
+
+        b, s, hq, d = q.shape
+        hkv = k.shape[2]
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out = torch.empty_like(q)
+        lse2 = torch.empty((b, hq, s), dtype=torch.float32, device=q.device)
+        rowmax = torch.empty_like(lse2) if want_max else None
+        call("pb_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(out), ptr(lse2), ptr(rowmax), b, s, hq, hkv,
+             hq * d, hkv * d, hq * d, float(scale), ptr(status_word(q.device)), stream_ptr())
+        ctx.save_for_backward(q, k, v, out, lse2)
+        ctx.scale = float(scale)
+        if want_max:
+            ctx.mark_non_differentiable(rowmax)
+            return out, rowmax
+        return out, None
+
+    @staticmethod
+    def backward(ctx, d_out, _d_max):
+        from ._lib import call, ptr, stream_ptr
+        from .functional import status_word
+
+        q, k, v, out, lse2 = ctx.saved_tensors
+        b, s, hq, d = q.shape
+        hkv = k.shape[2]
+        d_out = d_out.contiguous()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty_like(lse2)
+        call("pb_attn_bwd", ptr(q), ptr(k), ptr(v), ptr(out), ptr(d_out), ptr(lse2), ptr(delta),
+             ptr(dq), ptr(dk), ptr(dv), b, s, hq, hkv, hq * d, hkv * d, hq * d, ctx.scale,
+             ptr(status_word(q.device)), stream_ptr())
+        return dq, dk, dv, None, None
+
+
+def _fused_ok(q: Tensor, k: Tensor) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and k.shape[-1] == 128
+            and q.shape[2] % k.shape[2] == 0)
+
+
+def causal_gqa(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None,
+               return_max_logit: bool = False):
+    """q: (B, S, Hq, D); k, v: (B, S, Hkv, D) -> (B, S, Hq, D).
+
+    With ``return_max_logit`` also returns the largest scaled logit per (batch, head, row),
+    the statistic QK-clip needs (reference: train/__init__.py qk_clip)."""
+    d = q.shape[-1]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    if not _fused_ok(q, k):
+        out = causal_gqa_ref(q, k, v, scale)
+        if not return_max_logit:
+            return out
+        hq, hkv = q.shape[2], k.shape[2]
+        kf = k.float().transpose(1, 2).repeat_interleave(hq // hkv, dim=1)
+        logits = q.float().transpose(1, 2) @ kf.transpose(-1, -2) * scale
+        s = q.shape[1]
+        mask = torch.ones(s, s, dtype=torch.bool, device=q.device).tril()
+        return out, logits.masked_fill(~mask, float("-inf")).amax(dim=-1)
+    s = q.shape[1]
+    pad = (-s) % 128
+    if pad:   # padded keys come after every real query, so the causal mask hides them
+        q, k, v = (torch.nn.functional.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
+    out, rowmax = _AttnFn.apply(q, k, v, scale, return_max_logit)
+    if pad:
+        out = out[:, :s]
+        rowmax = None if rowmax is None else rowmax[..., :s]
+    return (out, rowmax) if return_max_logit else out

@@ -4,6 +4,7 @@
     python -m prometheus_b200.ops.microbench delta --seqs 32 --seq-len 4096
     python -m prometheus_b200.ops.microbench rmsnorm --rows 131072 --d 2048
     python -m prometheus_b200.ops.microbench ce --rows 4096 --vocab 131072
+    python -m prometheus_b200.ops.microbench attn --batch 8 --seq-len 4096
 
 Each prints one JSON line with the achieved rate and its fraction of the measured peak
 (``MEASURED_PEAKS.json`` at the repository root when present, else the stated fallback).
@@ -164,6 +165,41 @@ def bench_ce(a):
             "frac_of_peak": gbs / peaks()["hbm_gbs"]}
 
 
+def bench_attn(a):
+    """Causal GQA attention, forward and forward+backward, against the library kernel PyTorch
+    dispatches to for the same call."""
+    import torch.nn.functional as F
+
+    from . import attention
+
+    q = torch.randn(a.batch, a.seq_len, a.heads, 128, device="cuda").to(BF16).requires_grad_()
+    k = torch.randn(a.batch, a.seq_len, a.kv_heads, 128, device="cuda").to(BF16).requires_grad_()
+    v = torch.randn(a.batch, a.seq_len, a.kv_heads, 128, device="cuda").to(BF16).requires_grad_()
+    go = torch.randn_like(q)
+
+    def ours(bwd):
+        o = attention.causal_gqa(q, k, v)
+        if bwd:
+            torch.autograd.grad(o, (q, k, v), go)
+
+    def lib(bwd):
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                           is_causal=True, enable_gqa=True)
+        if bwd:
+            torch.autograd.grad(o, (q, k, v), go.transpose(1, 2))
+
+    flops_fwd = 2 * 2 * a.batch * a.heads * a.seq_len * a.seq_len * 128 / 2   # causal half
+    out = {"kernel": "attn_causal_gqa", "batch": a.batch, "seq_len": a.seq_len, "heads": a.heads,
+           "kv_heads": a.kv_heads}
+    for name, fn in (("ours", ours), ("sdpa", lib)):
+        f = timeit(lambda: fn(False), a.iters)
+        fb = timeit(lambda: fn(True), a.iters)
+        out[name] = {"fwd_ms": f, "fwd_tflops": flops_fwd / f / 1e9, "fwd_bwd_ms": fb,
+                     "fwd_bwd_tflops": 3.5 * flops_fwd / fb / 1e9}
+    out["frac_of_peak_fwd"] = out["ours"]["fwd_tflops"] / peaks()["bf16_tflops"]
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="which", required=True)
@@ -194,11 +230,16 @@ def main():
     c = sub.add_parser("ce")
     c.add_argument("--rows", type=int, default=4096)
     c.add_argument("--vocab", type=int, default=131072)
-    for s in (g, d, r, c, f, mo):
+    at = sub.add_parser("attn")
+    at.add_argument("--batch", type=int, default=8)
+    at.add_argument("--seq-len", type=int, default=4096)
+    at.add_argument("--heads", type=int, default=16)
+    at.add_argument("--kv-heads", type=int, default=4)
+    for s in (g, d, r, c, f, mo, at):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
     out = {"gemm": bench_gemm, "delta": bench_delta, "rmsnorm": bench_rmsnorm, "ce": bench_ce,
-           "fp8": bench_fp8, "moe": bench_moe}[a.which](a)
+           "fp8": bench_fp8, "moe": bench_moe, "attn": bench_attn}[a.which](a)
     out["peaks"] = peaks()
     print(json.dumps(out))
 

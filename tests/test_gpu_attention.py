@@ -1,0 +1,82 @@
+"""tcgen05 causal GQA attention (forward, dQ, dK/dV) against the fp32 formula."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+BF16 = torch.bfloat16
+
+
+def _rand(b, s, hq, hkv, seed, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = (torch.randn(b, s, hq, 128, device="cuda", generator=g) * scale).to(BF16)
+    k = (torch.randn(b, s, hkv, 128, device="cuda", generator=g) * scale).to(BF16)
+    v = torch.randn(b, s, hkv, 128, device="cuda", generator=g).to(BF16)
+    return q, k, v
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-20)).item()
+
+
+@pytest.mark.parametrize("b,s,hq,hkv", [(1, 128, 1, 1), (2, 512, 4, 2), (1, 1024, 16, 4), (1, 320, 2, 1)])
+def test_attention_forward_and_backward_match_fp32(b, s, hq, hkv):
+    from prometheus_b200.ops import attention
+
+    q, k, v = _rand(b, s, hq, hkv, 1)
+    q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+    out, rowmax = attention.causal_gqa(q, k, v, return_max_logit=True)
+    go = torch.randn_like(out)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), go)
+
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = attention.causal_gqa_ref(qf, kf, vf)
+    rq, rk, rv = torch.autograd.grad(ref, (qf, kf, vf), go.float())
+    assert _rel(out, ref) < 1e-2
+    assert _rel(dq, rq) < 2e-2 and _rel(dk, rk) < 2e-2 and _rel(dv, rv) < 2e-2
+
+    kk = kf.detach().transpose(1, 2).repeat_interleave(hq // hkv, dim=1)
+    logits = qf.detach().transpose(1, 2) @ kk.transpose(-1, -2) / math.sqrt(128)
+    mask = torch.ones(s, s, dtype=torch.bool, device="cuda").tril()
+    want_max = logits.masked_fill(~mask, float("-inf")).amax(-1)
+    torch.testing.assert_close(rowmax, want_max, atol=2e-3, rtol=1e-3)
+
+
+def test_attention_large_logits_exercise_the_rescale_path():
+    """Scores that keep growing along the keys force the running maximum to be raised
+    repeatedly (more than 2^8 between blocks), so the tensor-memory rescale of O runs."""
+    from prometheus_b200.ops import attention
+
+    b, s, hq, hkv = 1, 768, 2, 2
+    q, k, v = _rand(b, s, hq, hkv, 3)
+    ramp = torch.linspace(0.0, 6.0, s, device="cuda").view(1, s, 1, 1)
+    k = (k.float() + ramp * q.float().mean(dim=(1,), keepdim=True).sign()).to(BF16)
+    q = (q.float() * 3.0).to(BF16)
+    out = attention.causal_gqa(q, k, v)
+    ref = attention.causal_gqa_ref(q.float(), k.float(), v.float())
+    assert torch.isfinite(out.float()).all()
+    assert _rel(out, ref) < 1.5e-2
+
+
+def test_attention_is_deterministic_and_matches_library_kernel():
+    import torch.nn.functional as F
+
+    from prometheus_b200.ops import attention
+
+    q, k, v = _rand(2, 1024, 8, 2, 5)
+    q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+    go = torch.randn(2, 1024, 8, 128, device="cuda").to(BF16)
+    runs = []
+    for _ in range(2):
+        o = attention.causal_gqa(q, k, v)
+        runs.append((o,) + torch.autograd.grad(o, (q, k, v), go))
+    for a, b_ in zip(*runs):
+        assert torch.equal(a, b_)
+    o2 = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                        is_causal=True, enable_gqa=True).transpose(1, 2)
+    g2 = torch.autograd.grad(o2, (q, k, v), go)
+    assert _rel(runs[0][0], o2) < 1e-2
+    for mine, lib in zip(runs[0][1:], g2):
+        assert _rel(mine, lib) < 2e-2
