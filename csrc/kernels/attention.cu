@@ -17,7 +17,7 @@
 //
 // warps 0-3: one tensor-memory lane (= row) per thread; warp 4: MMA issue; warp 5: TMA producer.
 // All tensors are token-major: Q/O/dO/dQ [batch * seq, ldq] with head h at columns 128 h,
-// K/V/dK/dV [batch * seq, ldkv] with KV head g at columns 128 g. seq must be a multiple of 128.
+// K/V/dK/dV [batch * seq, ldkv] with KV head g at columns 128 g. seq must be a multiple of 256 (forward) / 128 (backward).
 //
 // Reference semantics: model/__init__.py gqa/mla attention (softmax(q k^T / sqrt(d)) v with a
 // causal mask) of the reference; the tiling is this library's own.
@@ -60,19 +60,24 @@ __device__ __forceinline__ bool wait_all(uint64_t* bar, uint32_t parity, int* st
 
 // ------------------------------------------------------------------------------ forward
 namespace fwd {
-constexpr int Q_OFF = 0, K_OFF = 32768, V_OFF = 98304, P_OFF = 163840, BARS = 196608;
-constexpr int SMEM = BARS + 256 + 1024;
-constexpr uint32_t COL_S = 0, COL_O = 256, TMEM_COLS = 512;
+// shared memory: Q (two 128-row tiles), three K/V stages of 64 keys, two P buffers per tile
+constexpr int Q_OFF = 0, KV_OFF = 65536, KV_STAGES = 3, KV_STAGE = 32768;
+constexpr int P_OFF = KV_OFF + KV_STAGES * KV_STAGE, BARS = P_OFF + 65536;
+constexpr int SMEM = BARS + 512 + 1024;
+constexpr uint32_t COL_S = 0, COL_O = 256, TMEM_COLS = 512;   // S[tile][buf] 64 cols, O[tile] 128
 
 struct Params {
-  int seq, heads, kv_heads, n_qb;
+  int seq, heads, kv_heads;
   float scale_log2;   // softmax scale * log2(e)
   float* lse2;        // [batch, heads, seq], log2 domain
   float* rowmax;      // [batch, heads, seq] largest scaled logit of the row, or null
   int* status;
 };
 
-__global__ void __launch_bounds__(192, 1)
+// One CTA = 256 query rows of one head: two 128-row tiles, each owned by one warpgroup
+// (warps 0-3 and 4-7) so that one group's exponentials overlap the other's tensor-core work.
+// Keys and values arrive in blocks of 64.  warp 8: MMA issue, warp 9: TMA producer.
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                 const Params p) {
@@ -81,35 +86,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BARS);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_done = bars + 9;    // [2]
-  uint64_t* s_free = bars + 11;   // [2]
-  uint64_t* p_ready = bars + 13;
-  uint64_t* o_done = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* kv_full = bars + 1;    // [3]
+  uint64_t* kv_empty = bars + 4;   // [3]
+  uint64_t* s_done = bars + 8;     // [tile][buf]
+  uint64_t* s_free = bars + 12;    // [tile][buf]
+  uint64_t* p_ready = bars + 16;   // [tile]
+  uint64_t* o_done = bars + 18;    // [tile][buf]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = p.n_qb - 1 - static_cast<int>(blockIdx.x);  // longest rows first
+  const int cb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long rows first
   const int h = blockIdx.y, b = blockIdx.z;
   const int g = h / (p.heads / p.kv_heads);
-  const int n_kv = qb + 1;
-  const int row0 = b * p.seq + qb * 128;
+  const int row0 = b * p.seq + cb * 256;
+  const int nj1 = 4 * cb + 4;     // 64-key blocks seen by tile 1; tile 0 sees nj1 - 2
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_done[i], 1); mbar_init(&s_free[i], 128);
+    for (int i = 0; i < KV_STAGES; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&s_done[i], 1); mbar_init(&s_free[i], 128); mbar_init(&o_done[i], 1);
     }
-    mbar_init(p_ready, 128); mbar_init(o_done, 1);
+    mbar_init(&p_ready[0], 128); mbar_init(&p_ready[1], 128);
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -118,165 +120,169 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 5) {
+  if (warp == 9) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, 32768);
-      tma_load_3d(smem + Q_OFF, &tmQ, q_full, h * D, row0, 0);
-      tma_load_3d(smem + Q_OFF + 16384, &tmQ, q_full, h * D + 64, row0, 0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int krow = b * p.seq + j * 128;
-        if (!mbar_wait(&k_empty[s], ph ^ 1, p.status)) break;
-        mbar_arrive_expect_tx(&k_full[s], 32768);
-        tma_load_3d(smem + K_OFF + s * 32768, &tmK, &k_full[s], g * D, krow, 0);
-        tma_load_3d(smem + K_OFF + s * 32768 + 16384, &tmK, &k_full[s], g * D + 64, krow, 0);
-        if (!mbar_wait(&v_empty[s], ph ^ 1, p.status)) break;
-        mbar_arrive_expect_tx(&v_full[s], 32768);
-        tma_load_3d(smem + V_OFF + s * 32768, &tmV, &v_full[s], g * D, krow, 0);
-        tma_load_3d(smem + V_OFF + s * 32768 + 16384, &tmV, &v_full[s], g * D + 64, krow, 0);
+      mbar_arrive_expect_tx(q_full, 65536);
+      for (int t = 0; t < 2; ++t) {
+        tma_load_3d(smem + Q_OFF + t * 32768, &tmQ, q_full, h * D, row0 + t * 128, 0);
+        tma_load_3d(smem + Q_OFF + t * 32768 + 16384, &tmQ, q_full, h * D + 64, row0 + t * 128, 0);
+      }
+      for (int j = 0; j < nj1; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        const int krow = b * p.seq + j * 64;
+        if (!mbar_wait(&kv_empty[s], ph ^ 1, p.status)) break;
+        mbar_arrive_expect_tx(&kv_full[s], KV_STAGE);
+        uint8_t* st = smem + KV_OFF + s * KV_STAGE;
+        tma_load_3d(st, &tmK, &kv_full[s], g * D, krow, 0);
+        tma_load_3d(st + 8192, &tmK, &kv_full[s], g * D + 64, krow, 0);
+        tma_load_3d(st + 16384, &tmV, &kv_full[s], g * D, krow, 0);
+        tma_load_3d(st + 16384 + 8192, &tmV, &kv_full[s], g * D + 64, krow, 0);
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     if (lane == 0) {
-      const uint32_t id_kk = make_idesc(1, 1, 128, 128, 0, 0);
-      const uint32_t id_kn = make_idesc(1, 1, 128, 128, 0, 1);
-      const uint32_t qa = smem_u32(smem + Q_OFF), pa = smem_u32(smem + P_OFF);
+      const uint32_t id_s = make_idesc(1, 1, 128, 64, 0, 0);     // S = Q K^T, N = 64 keys
+      const uint32_t id_o = make_idesc(1, 1, 128, 128, 0, 1);    // O += P V, V MN-major
       bool ok = mbar_wait(q_full, 0, p.status);
+      // scores of block j for both tiles (tile 0 stops two blocks earlier)
       auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[s], ph, p.status)) return false;
-        if (!mbar_wait(&s_free[s], ph ^ 1, p.status)) return false;
-        tc_fence_after();
-        const uint32_t ka = smem_u32(smem + K_OFF + s * 32768);
+        const int s = j % KV_STAGES;
+        if (!mbar_wait(&kv_full[s], (j / KV_STAGES) & 1, p.status)) return false;
+        const uint32_t ka = smem_u32(smem + KV_OFF + s * KV_STAGE);
+        for (int t = 0; t < 2; ++t) {
+          if (t == 0 && j >= nj1 - 2) continue;
+          const int sb = t * 2 + (j & 1);
+          if (!mbar_wait(&s_free[sb], ((j >> 1) & 1) ^ 1, p.status)) return false;
+          tc_fence_after();
+          const uint32_t qa = smem_u32(smem + Q_OFF + t * 32768);
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj)
-          umma_f16(tmem + COL_S + s * 128,
-                   make_sdesc_sw128(qa + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024),
-                   make_sdesc_sw128(ka + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024), id_kk,
-                   jj > 0);
-        umma_commit(&s_done[s]);
-        umma_commit(&k_empty[s]);
+          for (int jj = 0; jj < 8; ++jj)
+            umma_f16(tmem + COL_S + sb * 64,
+                     make_sdesc_sw128(qa + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024),
+                     make_sdesc_sw128(ka + (jj >> 2) * 8192 + (jj & 3) * 32, 16, 1024), id_s,
+                     jj > 0);
+          umma_commit(&s_done[sb]);
+        }
         return true;
       };
       if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (j + 1 < n_kv && !issue_s(j + 1)) break;
-        if (!mbar_wait(p_ready, j & 1, p.status)) break;
-        if (!mbar_wait(&v_full[s], ph, p.status)) break;
-        tc_fence_after();
-        const uint32_t va = smem_u32(smem + V_OFF + s * 32768);
+      for (int j = 0; j < nj1 && ok; ++j) {
+        const int s = j % KV_STAGES;
+        if (j + 1 < nj1 && !issue_s(j + 1)) break;
+        const uint32_t va = smem_u32(smem + KV_OFF + s * KV_STAGE + 16384);
+        for (int t = 0; t < 2; ++t) {
+          if (t == 0 && j >= nj1 - 2) continue;
+          if (!mbar_wait(&p_ready[t], j & 1, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t pa = smem_u32(smem + P_OFF + t * 32768 + (j & 1) * 16384);
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj)
-          umma_f16(tmem + COL_O, make_sdesc_sw128(pa + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024),
-                   make_sdesc_sw128(va + jj * 2048, 16384, 1024), id_kn, (j > 0) || (jj > 0));
-        umma_commit(o_done);
-        umma_commit(&v_empty[s]);
+          for (int jj = 0; jj < 4; ++jj)
+            umma_f16(tmem + COL_O + t * 128, make_sdesc_sw128(pa + jj * 32, 16, 1024),
+                     make_sdesc_sw128(va + jj * 2048, 8192, 1024), id_o, (j > 0) || (jj > 0));
+          umma_commit(&o_done[t * 2 + (j & 1)]);
+        }
+        umma_commit(&kv_empty[s]);
       }
     }
   } else {
-    const int r = threadIdx.x;  // query row of the tile = tensor-memory lane
-    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-    uint8_t* pbuf = smem + P_OFF;
-    const int qpos = qb * 128 + r;
+    const int t = warp >> 2;               // tile / warpgroup
+    const int r = threadIdx.x & 127;       // query row of the tile = tensor-memory lane
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const int qpos = cb * 256 + t * 128 + r;
+    const int q0 = cb * 256 + t * 128;
+    const int nj = nj1 - (t == 0 ? 2 : 0);
+    auto sync_group = [&] {
+      if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+      else asm volatile("bar.sync 2, 128;" ::: "memory");
+    };
     float m_used = -INFINITY, m_true = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
-      const int s = j & 1;
+    for (int j = 0; j < nj && ok; ++j) {
+      const int sb = t * 2 + (j & 1);
       const uint32_t ph = (j >> 1) & 1;
-      const bool diag = (j == qb);
-      if (!wait_all(&s_done[s], ph, p.status)) { ok = false; break; }
+      const bool edge = j * 64 + 63 > q0;
+      if (!wait_all(&s_done[sb], ph, p.status)) { ok = false; break; }
       tc_fence_after();
-      // pass 1: row maximum of the scaled scores
+      uint32_t v[64];
+      tmem_ld_32x32b_x32(lane_addr + COL_S + sb * 64, v);
+      tmem_ld_32x32b_x32(lane_addr + COL_S + sb * 64 + 32, v + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_free[sb]);           // the scores are in registers now
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(lane_addr + COL_S + s * 128 + c, v);
-        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float x = __uint_as_float(v[i]) * p.scale_log2;
-          if (!diag || c + i <= r) mx = fmaxf(mx, x);
-        }
+      for (int i = 0; i < 64; ++i) {
+        float x = __uint_as_float(v[i]) * p.scale_log2;
+        if (edge && j * 64 + i > qpos) x = -INFINITY;
+        v[i] = __float_as_uint(x);
+        mx = fmaxf(mx, x);
       }
       m_true = fmaxf(m_true, mx);
-      if (j > 0) {
-        // the previous P V product has finished: P may be rewritten, O may be rescaled
-        if (!wait_all(o_done, (j - 1) & 1, p.status)) { ok = false; break; }
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, mx > m_used + RESCALE_THRESHOLD)) {
-          const float m_new = fmaxf(m_used, mx);
-          const float alpha = ex2(m_used - m_new);
-          l *= alpha;
-#pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(lane_addr + COL_O + c, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32b_x32(lane_addr + COL_O + c, v);
-          }
-          tmem_st_wait();
-          m_used = m_new;
-        }
-      } else {
+      if (j == 0) {
         m_used = mx;
-      }
-      // pass 2: probabilities -> bf16 operand image
+      } else if (__any_sync(0xffffffffu, mx > m_used + RESCALE_THRESHOLD)) {
+        // raise the applied maximum: O of this tile must be idle (previous P V finished)
+        if (!wait_all(&o_done[t * 2 + ((j - 1) & 1)], ((j - 1) >> 1) & 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const float m_new = fmaxf(m_used, mx);
+        const float alpha = ex2(m_used - m_new);
+        l *= alpha;
 #pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(lane_addr + COL_S + s * 128 + c, v);
-        tmem_ld_wait();
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + COL_O + t * 128 + c, o);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float f[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int col = c + 8 * i + k;
-            const float e = ex2(__uint_as_float(v[8 * i + k]) * p.scale_log2 - m_used);
-            f[k] = (!diag || col <= r) ? e : 0.f;
-            l += f[k];
-          }
-          const int col = c + 8 * i;
-          st_swz(pbuf + (col >> 6) * 16384, r, (col & 63) >> 3, pack_bf16x8(f));
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x32(lane_addr + COL_O + t * 128 + c, o);
         }
+        tmem_st_wait();
+        m_used = m_new;
       }
-      tc_fence_before();
-      mbar_arrive(&s_free[s]);
+      // the P buffer of two blocks ago has been consumed
+      if (j >= 2 && !wait_all(&o_done[sb], ((j - 2) >> 1) & 1, p.status)) { ok = false; break; }
+      uint8_t* pbuf = smem + P_OFF + t * 32768 + (j & 1) * 16384;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float f[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          f[k] = ex2(__uint_as_float(v[8 * i + k]) - m_used);   // masked entries are -inf -> 0
+          l += f[k];
+        }
+        st_swz(pbuf, r, i, pack_bf16x8(f));
+      }
       fence_proxy_async_smem();
-      mbar_arrive(p_ready);
+      tc_fence_before();
+      mbar_arrive(&p_ready[t]);
     }
-    if (ok && wait_all(o_done, (n_kv - 1) & 1, p.status)) {
+    if (ok && wait_all(&o_done[t * 2 + ((nj - 1) & 1)], ((nj - 1) >> 1) & 1, p.status)) {
       tc_fence_after();
+      uint8_t* obuf = smem + P_OFF + t * 32768;   // both P buffers of the tile, now idle
       const float inv = 1.f / l;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(lane_addr + COL_O + c, v);
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(lane_addr + COL_O + t * 128 + c, o);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           float f[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[8 * i + k]) * inv;
+          for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(o[8 * i + k]) * inv;
           const int col = c + 8 * i;
-          st_swz(pbuf + (col >> 6) * 16384, r, (col & 63) >> 3, pack_bf16x8(f));
+          st_swz(obuf + (col >> 6) * 16384, r, (col & 63) >> 3, pack_bf16x8(f));
         }
       }
       const size_t vi = (static_cast<size_t>(b) * p.heads + h) * p.seq + qpos;
       p.lse2[vi] = m_used + log2f(l);
       if (p.rowmax != nullptr) p.rowmax[vi] = m_true * 0.6931471805599453f;
       fence_proxy_async_smem();
-      sync_rows();
+      sync_group();
       if (r == 0) {
-        tma_store_3d(&tmO, pbuf, h * D, row0, 0);
-        tma_store_3d(&tmO, pbuf + 16384, h * D + 64, row0, 0);
+        tma_store_3d(&tmO, obuf, h * D, row0 + t * 128, 0);
+        tma_store_3d(&tmO, obuf + 16384, h * D + 64, row0 + t * 128, 0);
         tma_store_commit();
         tma_store_wait<0>();
       }
@@ -289,7 +295,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies in flight land
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -314,8 +320,11 @@ struct Params {
 
 // DKV = false: resident Q, dO (one head); streams K, V tiles; output dQ.
 // DKV = true : resident K, V (one KV head); streams Q, dO tiles of the group; outputs dK, dV.
+// Two warpgroups (warps 0-3, 4-7) take the streamed tiles alternately, each with its own score
+// buffers in tensor memory and its own dS / P^T operand buffers, and accumulate into the same
+// gradient accumulators.  warp 8: MMA issue, warp 9: TMA producer.
 template <bool DKV>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant__ CUtensorMap tmRB,
                 const __grid_constant__ CUtensorMap tmT1, const __grid_constant__ CUtensorMap tmT2,
                 const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
@@ -359,7 +368,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
     tma_prefetch_desc(&tmRA); tma_prefetch_desc(&tmRB);
     tma_prefetch_desc(&tmT1); tma_prefetch_desc(&tmT2);
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -368,7 +377,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 5) {
+  if (warp == 9) {
     if (lane == 0) {
       const int rx = (DKV ? g : hy) * D;
       mbar_arrive_expect_tx(r_full, 65536);
@@ -391,7 +400,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
         tma_load_3d(st + 16384 + 8192, &tmT2, &t_full[s], tx + 64, trow, 0);
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     if (lane == 0) {
       const uint32_t id_x = make_idesc(1, 1, 128, 64, 0, 0);     // A K-major, B K-major, N = 64
       const uint32_t id_acc = make_idesc(1, 1, 128, 128, 0, 1);  // A K-major, B MN-major
@@ -444,8 +453,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
       if (it == n_it) umma_commit(acc_done);
     }
   } else {
-    const int r = threadIdx.x;
-    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const int wg = warp >> 2;          // warpgroup = score buffer = parity of its iterations
+    const int r = threadIdx.x & 127;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    auto sync_group = [&] {
+      if (wg == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+      else asm volatile("bar.sync 2, 128;" ::: "memory");
+    };
     const int pos = blk * 128 + r;   // query position (dQ) or key position (dKV) of this row
     float row_lse = 0.f, row_delta = 0.f;
     if (!DKV) {
@@ -461,17 +475,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
       const float* base = (r < 64) ? p.lse2 : p.delta;
       return base + (static_cast<size_t>(b) * p.heads + h) * p.seq + t * 64 + (r & 63);
     };
-    float vec_next = (DKV && n_it > 0) ? *vec_src(0) : 0.f;
+    float vec_next = (DKV && wg < n_it) ? *vec_src(wg) : 0.f;
     bool ok = true;
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it & 1;
+    for (int it = wg; it < n_it && ok; it += 2) {
+      const int s = wg;
       const uint32_t ph = (it >> 1) & 1;
       const int t = t_first + (DKV ? it % t_count : it);
       float* vec = reinterpret_cast<float*>(smem + VEC_OFF + s * 512);
       if (DKV) {
-        vec[r] = vec_next;   // [0,64) lse2, [64,128) delta; readers of two iterations ago are done
-        if (it + 1 < n_it) vec_next = *vec_src(it + 1);
-        sync_rows();
+        sync_group();        // the group's readers of the previous tile are done
+        vec[r] = vec_next;   // [0,64) lse2, [64,128) delta
+        if (it + 2 < n_it) vec_next = *vec_src(it + 2);
+        sync_group();
       }
       if (!wait_all(&x_done[s], ph, p.status)) { ok = false; break; }
       if (!wait_all(&pd_free[s], ph ^ 1, p.status)) { ok = false; break; }
@@ -514,37 +529,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
       fence_proxy_async_smem();
       mbar_arrive(&pd_ready[s]);
     }
-    if (ok && wait_all(acc_done, 0, p.status)) {
+    // every row thread gets here (no early exit above), so the group barriers below are safe
+    if (wait_all(acc_done, 0, p.status) && ok) {
       tc_fence_after();
-      // resident tiles are no longer read: reuse them as the staging for the TMA stores
+      // resident tiles are no longer read: reuse them as the staging for the TMA stores.
+      // dKV: group 0 drains dK, group 1 drains dV.  dQ: each group drains 64 columns.
+      uint8_t* stage = smem + ((DKV && wg == 1) ? RB_OFF : RA_OFF);
+      const uint32_t col0 = (DKV && wg == 1) ? COL_ACC2 : COL_ACC1;
+      const int c_lo = DKV ? 0 : wg * 64, c_hi = DKV ? D : wg * 64 + 64;
 #pragma unroll 1
-      for (int a = 0; a < (DKV ? 2 : 1); ++a) {
-        uint8_t* stage = smem + (a == 0 ? RA_OFF : RB_OFF);
-        const uint32_t col0 = a == 0 ? COL_ACC1 : COL_ACC2;
-#pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(lane_addr + col0 + c, v);
-          tmem_ld_wait();
+      for (int c = c_lo; c < c_hi; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + col0 + c, v);
+        tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float f[8];
+        for (int i = 0; i < 4; ++i) {
+          float f[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[8 * i + k]);
-            const int col = c + 8 * i;
-            st_swz(stage + (col >> 6) * 16384, r, (col & 63) >> 3, pack_bf16x8(f));
-          }
+          for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[8 * i + k]);
+          const int col = c + 8 * i;
+          st_swz(stage + (col >> 6) * 16384, r, (col & 63) >> 3, pack_bf16x8(f));
         }
       }
       fence_proxy_async_smem();
-      sync_rows();
+      sync_group();
       if (r == 0) {
         const int ox = (DKV ? g : hy) * D;
-        tma_store_3d(&tmO1, smem + RA_OFF, ox, row0, 0);
-        tma_store_3d(&tmO1, smem + RA_OFF + 16384, ox + 64, row0, 0);
         if (DKV) {
-          tma_store_3d(&tmO2, smem + RB_OFF, ox, row0, 0);
-          tma_store_3d(&tmO2, smem + RB_OFF + 16384, ox + 64, row0, 0);
+          const CUtensorMap* tm = wg == 0 ? &tmO1 : &tmO2;
+          tma_store_3d(tm, stage, ox, row0, 0);
+          tma_store_3d(tm, stage + 16384, ox + 64, row0, 0);
+        } else {
+          tma_store_3d(&tmO1, stage + wg * 16384, ox + wg * 64, row0, 0);
         }
         tma_store_commit();
         tma_store_wait<0>();
@@ -558,7 +574,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -609,7 +625,8 @@ PB_API int pb_attn_fwd(const void* q, const void* k, const void* v, void* out, v
                        void* rowmax, int batch, int seq, int heads, int kv_heads, int ldq, int ldkv,
                        int ldo, float scale, int* status, cudaStream_t st) {
   using namespace attn;
-  if (bad_geometry(batch, seq, heads, kv_heads, ldq, ldkv) || ldo < heads * D || ldo % 8 != 0)
+  if (bad_geometry(batch, seq, heads, kv_heads, ldq, ldkv) || ldo < heads * D || ldo % 8 != 0 ||
+      seq % 256 != 0)
     return PB_BAD_ARG;
   static bool attr_set = false;
   if (!attr_set) {
@@ -622,17 +639,17 @@ PB_API int pb_attn_fwd(const void* q, const void* k, const void* v, void* out, v
   CUtensorMap tQ, tK, tV, tO;
   int r = 0;
   r |= make_tmap_3d(&tQ, q, 2, static_cast<uint64_t>(heads) * D, rows, 1, ldq, 0, 64, 128);
-  r |= make_tmap_3d(&tK, k, 2, static_cast<uint64_t>(kv_heads) * D, rows, 1, ldkv, 0, 64, 128);
-  r |= make_tmap_3d(&tV, v, 2, static_cast<uint64_t>(kv_heads) * D, rows, 1, ldkv, 0, 64, 128);
+  r |= make_tmap_3d(&tK, k, 2, static_cast<uint64_t>(kv_heads) * D, rows, 1, ldkv, 0, 64, 64);
+  r |= make_tmap_3d(&tV, v, 2, static_cast<uint64_t>(kv_heads) * D, rows, 1, ldkv, 0, 64, 64);
   r |= make_tmap_3d(&tO, out, 2, static_cast<uint64_t>(heads) * D, rows, 1, ldo, 0, 64, 128);
   if (r != 0) return 1000 + r;
   fwd::Params p;
-  p.seq = seq; p.heads = heads; p.kv_heads = kv_heads; p.n_qb = seq / 128;
+  p.seq = seq; p.heads = heads; p.kv_heads = kv_heads;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse2 = static_cast<float*>(lse2);
   p.rowmax = static_cast<float*>(rowmax);
   p.status = status;
-  fwd::attn_fwd_kernel<<<dim3(p.n_qb, heads, batch), 192, fwd::SMEM, st>>>(tQ, tK, tV, tO, p);
+  fwd::attn_fwd_kernel<<<dim3(seq / 256, heads, batch), 320, fwd::SMEM, st>>>(tQ, tK, tV, tO, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -680,7 +697,7 @@ PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* 
     r |= make_tmap_3d(&tV, v, 2, ki, rows, 1, ldkv, 0, 64, 64);
     r |= make_tmap_3d(&tDQ, dq, 2, qi, rows, 1, ldq, 0, 64, 128);
     if (r != 0) return 1000 + r;
-    bwd::attn_bwd_kernel<false><<<dim3(p.n_blk, heads, batch), 192, bwd::SMEM, st>>>(
+    bwd::attn_bwd_kernel<false><<<dim3(p.n_blk, heads, batch), 320, bwd::SMEM, st>>>(
         tQ, tDO, tK, tV, tDQ, tDQ, p);
   }
   {
@@ -693,7 +710,7 @@ PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* 
     r |= make_tmap_3d(&tDK, dk, 2, ki, rows, 1, ldkv, 0, 64, 128);
     r |= make_tmap_3d(&tDV, dv, 2, ki, rows, 1, ldkv, 0, 64, 128);
     if (r != 0) return 2000 + r;
-    bwd::attn_bwd_kernel<true><<<dim3(p.n_blk, kv_heads, batch), 192, bwd::SMEM, st>>>(
+    bwd::attn_bwd_kernel<true><<<dim3(p.n_blk, kv_heads, batch), 320, bwd::SMEM, st>>>(
         tK, tV, tQ, tDO, tDK, tDV, p);
   }
   return static_cast<int>(cudaGetLastError());

@@ -21,6 +21,7 @@
 #include <set>
 
 #include "common.hpp"
+#include "providers.hpp"
 
 namespace py = pybind11;
 using namespace pbn;
@@ -941,6 +942,81 @@ class LocalEngine {
   bool up_ = true;
 };
 
+// Generation routed through the provider failover order; the local engine is always the last
+// resort (reference: serve/src/lib.rs:284-363).
+constexpr const char* kLastResort = "sglang";
+
+class Router {
+ public:
+  Router(std::vector<std::string> hosted, LocalEngine engine, AimdConfig aimd)
+      : failover_(with_last_resort(std::move(hosted))), aimd_(aimd), engine_(std::move(engine)) {
+    // the swarm starts wide open; outages shrink it
+    while (aimd_.window() < aimd.max_window) {
+      const uint32_t before = aimd_.window();
+      aimd_.on_success(0);
+      if (aimd_.window() <= before) break;
+    }
+  }
+  void mark_down(const std::string& id) {
+    bool already = false;
+    for (auto& d : failover_.down()) already = already || d == id;
+    const bool hosted_up = id != kLastResort && !already;
+    failover_.mark_down(id);
+    if (hosted_up) aimd_.on_outage();
+  }
+  void mark_up(const std::string& id) { failover_.mark_up(id); }
+  std::vector<std::tuple<size_t, std::string, std::string>> generate(const std::vector<std::string>& prompts,
+                                                                     uint32_t max_tokens, float temperature) const {
+    std::string current;
+    try {
+      current = failover_.current();
+    } catch (const Error& e) {
+      if (e.kind == "NoProvider") throw Error("EngineDown", "engine is down");
+      throw;
+    }
+    if (current != kLastResort) throw Error("Hosted", "hosted provider " + current + " has no local backend");
+    return engine_.generate(prompts, max_tokens, temperature);
+  }
+  const Failover& failover() const { return failover_; }
+  uint32_t window() const { return aimd_.window(); }
+  LocalEngine& engine() { return engine_; }
+
+ private:
+  static std::vector<std::string> with_last_resort(std::vector<std::string> p) {
+    if (p.empty() || p.back() != kLastResort) p.push_back(kLastResort);
+    return p;
+  }
+  Failover failover_;
+  Aimd aimd_;
+  LocalEngine engine_;
+};
+
+struct Deployment {
+  std::string job, endpoint, model;
+  uint32_t gpus = 0;
+};
+
+// Submits the stock serving script through the Slurm client (any object with the client's
+// submit / cancel methods); refuses a GPU count the client would refuse before any I/O.
+class Deployer {
+ public:
+  Deployer(py::object client, std::string script) : client_(std::move(client)), script_(std::move(script)) {}
+  Deployment submit(const LocalEngine& cfg, const std::string& run_id, const std::string& suffix,
+                    const std::string& walltime) const {
+    if (cfg.gpus() != 1 && cfg.gpus() != 2 && cfg.gpus() != 4)
+      throw Error("BadGpuCount", "gpus must be one of [1, 2, 4], got " + std::to_string(cfg.gpus()));
+    const std::string job = py::cast<std::string>(client_.attr("submit")(run_id, suffix, script_, walltime, cfg.gpus()));
+    return Deployment{job, "http://127.0.0.1:" + std::to_string(cfg.port()), cfg.model(), cfg.gpus()};
+  }
+  void teardown(const Deployment& d) const { client_.attr("cancel")(d.job); }
+  const std::string& script() const { return script_; }
+  py::object client() const { return client_; }
+
+ private:
+  py::object client_;
+  std::string script_;
+};
+
 }  // namespace
 
 void bind_data_pipeline(py::module_& m) {
@@ -1099,4 +1175,27 @@ void bind_data_pipeline(py::module_& m) {
       .def_property_readonly("gpus", &LocalEngine::gpus)
       .def_property_readonly("max_batch", &LocalEngine::max_batch)
       .def_property_readonly("port", &LocalEngine::port);
+  py::class_<Router>(sm, "Router")
+      .def(py::init<std::vector<std::string>, LocalEngine, AimdConfig>(), py::arg("hosted"), py::arg("engine"),
+           py::arg("aimd") = AimdConfig{})
+      .def("mark_down", &Router::mark_down)
+      .def("mark_up", &Router::mark_up)
+      .def("generate", &Router::generate, py::arg("prompts"), py::arg("max_tokens"), py::arg("temperature") = 0.0f)
+      .def("last_resort", [](const Router&) { return std::string(kLastResort); })
+      .def_property_readonly("providers", [](const Router& r) { return r.failover().providers(); })
+      .def_property_readonly("down", [](const Router& r) { return r.failover().down(); })
+      .def("current", [](const Router& r) { return r.failover().current(); })
+      .def_property_readonly("window", &Router::window)
+      .def_property_readonly("engine", &Router::engine, py::return_value_policy::reference_internal);
+  py::class_<Deployment>(sm, "Deployment")
+      .def_readonly("job", &Deployment::job)
+      .def_readonly("endpoint", &Deployment::endpoint)
+      .def_readonly("model", &Deployment::model)
+      .def_readonly("gpus", &Deployment::gpus);
+  py::class_<Deployer>(sm, "Deployer")
+      .def(py::init<py::object, std::string>(), py::arg("client"), py::arg("script"))
+      .def("submit", &Deployer::submit, py::arg("engine"), py::arg("run_id"), py::arg("suffix"), py::arg("walltime"))
+      .def("teardown", &Deployer::teardown)
+      .def_property_readonly("script", &Deployer::script)
+      .def_property_readonly("client", &Deployer::client);
 }

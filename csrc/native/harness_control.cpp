@@ -14,6 +14,7 @@
 #include <cmath>
 
 #include "cas.hpp"
+#include "providers.hpp"
 #include "raft.hpp"
 
 namespace py = pybind11;

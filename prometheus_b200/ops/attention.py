@@ -91,7 +91,7 @@ def causal_gqa(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None,
         mask = torch.ones(s, s, dtype=torch.bool, device=q.device).tril()
         return out, logits.masked_fill(~mask, float("-inf")).amax(dim=-1)
     s = q.shape[1]
-    pad = (-s) % 128
+    pad = (-s) % 256
     if pad:   # padded keys come after every real query, so the causal mask hides them
         q, k, v = (torch.nn.functional.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
     out, rowmax = _AttnFn.apply(q, k, v, scale, return_max_logit)

@@ -188,6 +188,10 @@ def bench_attn(a):
         if bwd:
             torch.autograd.grad(o, (q, k, v), go.transpose(1, 2))
 
+    if a.once:      # one forward + backward of our kernels and nothing else: the ncu small case
+        ours(True)
+        torch.cuda.synchronize()
+        return {"kernel": "attn_causal_gqa", "once": True}
     flops_fwd = 2 * 2 * a.batch * a.heads * a.seq_len * a.seq_len * 128 / 2   # causal half
     out = {"kernel": "attn_causal_gqa", "batch": a.batch, "seq_len": a.seq_len, "heads": a.heads,
            "kv_heads": a.kv_heads}
@@ -235,6 +239,7 @@ def main():
     at.add_argument("--seq-len", type=int, default=4096)
     at.add_argument("--heads", type=int, default=16)
     at.add_argument("--kv-heads", type=int, default=4)
+    at.add_argument("--once", action="store_true")
     for s in (g, d, r, c, f, mo, at):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()

@@ -325,3 +325,55 @@ def test_local_engine_generate_and_body():
     assert body["model"] == "m" and [c["index"] for c in body["choices"]] == [0, 1]
     assert body["choices"][0]["message"] == {"role": "assistant", "content": out[0][1]}
     assert body["choices"][1]["finish_reason"] == "stop"
+
+
+def test_router_failover_and_deployer():
+    eng = SV.LocalEngine("m", 1, 4, 30000)
+    r = SV.Router(["hosted-a", "hosted-b"], eng, native.providers.AimdConfig(min_window=1, max_window=8))
+    assert r.providers == ["hosted-a", "hosted-b", "sglang"] and r.last_resort() == "sglang" and r.window == 8
+    assert SV.Router(["x", "sglang"], eng).providers == ["x", "sglang"]
+    with pytest.raises(NativeError) as e:
+        r.generate(["p"], 2)
+    assert _kind(e) == "Hosted" and r.current() == "hosted-a"
+    r.mark_down("hosted-a")
+    assert r.window == 4 and r.current() == "hosted-b"
+    r.mark_down("hosted-a")                      # already down: the window is not cut twice
+    assert r.window == 4
+    r.mark_down("hosted-b")
+    assert r.window == 2 and r.current() == "sglang"
+    out = r.generate(["p", "q"], 2)
+    assert out == eng.generate(["p", "q"], 2)
+    r.mark_down("sglang")                        # the last resort does not count as a hosted outage
+    assert r.window == 2
+    with pytest.raises(NativeError) as e:
+        r.generate(["p"], 2)
+    assert _kind(e) == "EngineDown"
+    r.mark_up("sglang"); r.mark_up("hosted-a")
+    assert r.current() == "hosted-a" and r.down == ["hosted-b"]
+    with pytest.raises(NativeError) as e:
+        r.mark_down("nobody")
+    assert _kind(e) == "NotFound"
+    r.engine.mark_down()
+    r.mark_down("hosted-a")
+    with pytest.raises(NativeError) as e:
+        r.generate(["p"], 1)
+    assert _kind(e) == "EngineDown"
+
+    class FakeSlurm:
+        def __init__(self):
+            self.calls = []
+
+        def submit(self, run_id, suffix, script, walltime, gpus):
+            self.calls.append(("submit", run_id, suffix, script, walltime, gpus))
+            return "4242"
+
+        def cancel(self, job):
+            self.calls.append(("cancel", job))
+
+    fake = FakeSlurm()
+    dep = SV.Deployer(fake, "serve/sglang.sbatch")
+    d = dep.submit(SV.LocalEngine("big", 4, 8, 31000), "run-1", "serve", "02:00:00")
+    assert (d.job, d.endpoint, d.model, d.gpus) == ("4242", "http://127.0.0.1:31000", "big", 4)
+    dep.teardown(d)
+    assert fake.calls == [("submit", "run-1", "serve", "serve/sglang.sbatch", "02:00:00", 4), ("cancel", "4242")]
+    assert dep.script == "serve/sglang.sbatch" and dep.client is fake
