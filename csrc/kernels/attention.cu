@@ -23,6 +23,8 @@
 // causal mask) of the reference; the tiling is this library's own.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace pb {
@@ -144,24 +146,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0) {
       const uint32_t id_s = make_idesc(1, 1, 128, 64, 0, 0);     // S = Q K^T, N = 64 keys
       const uint32_t id_o = make_idesc(1, 1, 128, 128, 0, 1);    // O += P V, V MN-major
+      constexpr uint32_t HI = sdesc_hi_sw128(1024);
+      // descriptor low words are kept in registers: one add per operand per MMA
+      const uint32_t q_lo0 = sdesc_lo(smem_u32(smem + Q_OFF), 16);
+      const uint32_t p_lo0 = sdesc_lo(smem_u32(smem + P_OFF), 16);
+      const uint32_t kv0 = smem_u32(smem + KV_OFF);
       bool ok = mbar_wait(q_full, 0, p.status);
       // scores of block j for both tiles (tile 0 stops two blocks earlier)
       auto issue_s = [&](int j) -> bool {
         const int s = j % KV_STAGES;
         if (!mbar_wait(&kv_full[s], (j / KV_STAGES) & 1, p.status)) return false;
-        const uint32_t ka = smem_u32(smem + KV_OFF + s * KV_STAGE);
+        const uint32_t k_lo = sdesc_lo(kv0 + s * KV_STAGE, 16);
         for (int t = 0; t < 2; ++t) {
           if (t == 0 && j >= nj1 - 2) continue;
           const int sb = t * 2 + (j & 1);
           if (!mbar_wait(&s_free[sb], ((j >> 1) & 1) ^ 1, p.status)) return false;
           tc_fence_after();
-          const uint32_t qa = smem_u32(smem + Q_OFF + t * 32768);
+          const uint32_t q_lo = q_lo0 + t * (32768 >> 4);
+          const uint32_t d = tmem + COL_S + sb * 64;
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj)
-            umma_f16(tmem + COL_S + sb * 64,
-                     make_sdesc_sw128(qa + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024),
-                     make_sdesc_sw128(ka + (jj >> 2) * 8192 + (jj & 3) * 32, 16, 1024), id_s,
-                     jj > 0);
+            umma_f16_words(d, q_lo + (((jj >> 2) * 16384 + (jj & 3) * 32) >> 4), HI,
+                           k_lo + (((jj >> 2) * 8192 + (jj & 3) * 32) >> 4), HI, id_s, jj > 0);
           umma_commit(&s_done[sb]);
         }
         return true;
@@ -170,16 +176,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int j = 0; j < nj1 && ok; ++j) {
         const int s = j % KV_STAGES;
         if (j + 1 < nj1 && !issue_s(j + 1)) break;
-        const uint32_t va = smem_u32(smem + KV_OFF + s * KV_STAGE + 16384);
+        const uint32_t v_lo = sdesc_lo(kv0 + s * KV_STAGE + 16384, 8192);
         for (int t = 0; t < 2; ++t) {
           if (t == 0 && j >= nj1 - 2) continue;
           if (!mbar_wait(&p_ready[t], j & 1, p.status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t pa = smem_u32(smem + P_OFF + t * 32768 + (j & 1) * 16384);
+          const uint32_t p_lo = p_lo0 + ((t * 32768 + (j & 1) * 16384) >> 4);
+          const uint32_t d = tmem + COL_O + t * 128;
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj)
-            umma_f16(tmem + COL_O + t * 128, make_sdesc_sw128(pa + jj * 32, 16, 1024),
-                     make_sdesc_sw128(va + jj * 2048, 8192, 1024), id_o, (j > 0) || (jj > 0));
+            umma_f16_words(d, p_lo + ((jj * 32) >> 4), HI, v_lo + ((jj * 2048) >> 4), HI, id_o,
+                           (j > 0) || (jj > 0));
           umma_commit(&o_done[t * 2 + (j & 1)]);
         }
         umma_commit(&kv_empty[s]);
@@ -210,14 +217,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&s_free[sb]);           // the scores are in registers now
-      float mx = -INFINITY;
+      if (edge) {   // only the blocks on the diagonal pay for the mask
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        float x = __uint_as_float(v[i]) * p.scale_log2;
-        if (edge && j * 64 + i > qpos) x = -INFINITY;
-        v[i] = __float_as_uint(x);
-        mx = fmaxf(mx, x);
+        for (int i = 0; i < 64; ++i)
+          if (j * 64 + i > qpos) v[i] = 0xff800000u;   // -inf
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       m_true = fmaxf(m_true, mx);
       if (j == 0) {
         m_used = mx;
@@ -243,16 +251,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // the P buffer of two blocks ago has been consumed
       if (j >= 2 && !wait_all(&o_done[sb], ((j - 2) >> 1) & 1, p.status)) { ok = false; break; }
       uint8_t* pbuf = smem + P_OFF + t * 32768 + (j & 1) * 16384;
+      const float neg_m = -m_used;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float f[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          f[k] = ex2(__uint_as_float(v[8 * i + k]) - m_used);   // masked entries are -inf -> 0
-          l += f[k];
+          // one fused multiply-add and one exponential per score; masked entries are -inf -> 0
+          f[k] = ex2(fmaf(__uint_as_float(v[8 * i + k]), p.scale_log2, neg_m));
+          l4[k & 3] += f[k];
         }
         st_swz(pbuf, r, i, pack_bf16x8(f));
       }
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&p_ready[t]);
@@ -404,7 +416,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
     if (lane == 0) {
       const uint32_t id_x = make_idesc(1, 1, 128, 64, 0, 0);     // A K-major, B K-major, N = 64
       const uint32_t id_acc = make_idesc(1, 1, 128, 128, 0, 1);  // A K-major, B MN-major
-      const uint32_t ra = smem_u32(smem + RA_OFF), rb = smem_u32(smem + RB_OFF);
+      constexpr uint32_t HI = sdesc_hi_sw128(1024);
+      const uint32_t ra_lo = sdesc_lo(smem_u32(smem + RA_OFF), 16);
+      const uint32_t rb_lo = sdesc_lo(smem_u32(smem + RB_OFF), 16);
+      const uint32_t st0 = smem_u32(smem + ST_OFF);
+      const uint32_t ds_lo0 = sdesc_lo(smem_u32(smem + DS_OFF), 16);
+      const uint32_t pt_lo0 = sdesc_lo(smem_u32(smem + PT_OFF), 16);
       bool ok = mbar_wait(r_full, 0, p.status);
       auto issue_x = [&](int it) -> bool {
         const int s = it & 1;
@@ -412,17 +429,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
         if (!mbar_wait(&t_full[s], ph, p.status)) return false;
         if (!mbar_wait(&x_free[s], ph ^ 1, p.status)) return false;
         tc_fence_after();
-        const uint32_t t1 = smem_u32(smem + ST_OFF + s * 32768), t2 = t1 + 16384;
+        const uint32_t t1_lo = sdesc_lo(st0 + s * 32768, 16), t2_lo = t1_lo + (16384 >> 4);
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj)
-          umma_f16(tmem + COL_X1 + s * 64,
-                   make_sdesc_sw128(ra + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024),
-                   make_sdesc_sw128(t1 + (jj >> 2) * 8192 + (jj & 3) * 32, 16, 1024), id_x, jj > 0);
+          umma_f16_words(tmem + COL_X1 + s * 64, ra_lo + (((jj >> 2) * 16384 + (jj & 3) * 32) >> 4),
+                         HI, t1_lo + (((jj >> 2) * 8192 + (jj & 3) * 32) >> 4), HI, id_x, jj > 0);
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj)
-          umma_f16(tmem + COL_X2 + s * 64,
-                   make_sdesc_sw128(rb + (jj >> 2) * 16384 + (jj & 3) * 32, 16, 1024),
-                   make_sdesc_sw128(t2 + (jj >> 2) * 8192 + (jj & 3) * 32, 16, 1024), id_x, jj > 0);
+          umma_f16_words(tmem + COL_X2 + s * 64, rb_lo + (((jj >> 2) * 16384 + (jj & 3) * 32) >> 4),
+                         HI, t2_lo + (((jj >> 2) * 8192 + (jj & 3) * 32) >> 4), HI, id_x, jj > 0);
         umma_commit(&x_done[s]);
         return true;
       };
@@ -434,18 +449,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
         if (it + 1 < n_it && !issue_x(it + 1)) break;
         if (!mbar_wait(&pd_ready[s], ph, p.status)) break;
         tc_fence_after();
-        const uint32_t t1 = smem_u32(smem + ST_OFF + s * 32768), t2 = t1 + 16384;
-        const uint32_t ds = smem_u32(smem + DS_OFF + s * 16384);
-        const uint32_t pt = smem_u32(smem + PT_OFF + s * 16384);
+        // the streamed tiles again, now as MN-major B operands (64-wide chunks 8 KB apart)
+        const uint32_t t1_mn = sdesc_lo(st0 + s * 32768, 8192), t2_mn = t1_mn + (16384 >> 4);
+        const uint32_t ds_lo = ds_lo0 + ((s * 16384) >> 4), pt_lo = pt_lo0 + ((s * 16384) >> 4);
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj)
-          umma_f16(tmem + COL_ACC1, make_sdesc_sw128(ds + jj * 32, 16, 1024),
-                   make_sdesc_sw128(t1 + jj * 2048, 8192, 1024), id_acc, (it > 0) || (jj > 0));
+          umma_f16_words(tmem + COL_ACC1, ds_lo + ((jj * 32) >> 4), HI, t1_mn + ((jj * 2048) >> 4),
+                         HI, id_acc, (it > 0) || (jj > 0));
         if (DKV) {
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj)
-            umma_f16(tmem + COL_ACC2, make_sdesc_sw128(pt + jj * 32, 16, 1024),
-                     make_sdesc_sw128(t2 + jj * 2048, 8192, 1024), id_acc, (it > 0) || (jj > 0));
+            umma_f16_words(tmem + COL_ACC2, pt_lo + ((jj * 32) >> 4), HI,
+                           t2_mn + ((jj * 2048) >> 4), HI, id_acc, (it > 0) || (jj > 0));
         }
         umma_commit(&t_empty[s]);
         umma_commit(&pd_free[s]);
@@ -496,34 +511,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
       const bool edge = DKV ? (t * 64 < blk * 128 + 127) : (t * 64 + 63 > blk * 128);
       uint8_t* dsb = smem + DS_OFF + s * 16384;
       uint8_t* ptb = smem + PT_OFF + s * 16384;
+      auto tile_rows = [&](auto EDGE) {
 #pragma unroll 1
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t x1[32], x2[32];
-        tmem_ld_32x32b_x32(lane_addr + COL_X1 + s * 64 + c, x1);
-        tmem_ld_32x32b_x32(lane_addr + COL_X2 + s * 64 + c, x2);
-        tmem_ld_wait();
+        for (int c = 0; c < 64; c += 32) {
+          uint32_t x1[32], x2[32];
+          tmem_ld_32x32b_x32(lane_addr + COL_X1 + s * 64 + c, x1);
+          tmem_ld_32x32b_x32(lane_addr + COL_X2 + s * 64 + c, x2);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float pf[8], df[8];
+          for (int i = 0; i < 4; ++i) {
+            float pf[8], df[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int col = c + 8 * i + k;
-            const float lse = DKV ? vec[col] : row_lse;
-            const float dl = DKV ? vec[64 + col] : row_delta;
-            float pr = ex2(__uint_as_float(x1[8 * i + k]) * p.scale_log2 - lse);
-            if (edge) {
-              const int other = t * 64 + col;
-              const bool masked = DKV ? (other < pos) : (other > pos);
-              if (masked) pr = 0.f;
+            for (int k = 0; k < 8; ++k) {
+              const int col = c + 8 * i + k;
+              const float lse = DKV ? vec[col] : row_lse;
+              const float dl = DKV ? vec[64 + col] : row_delta;
+              float pr = ex2(fmaf(__uint_as_float(x1[8 * i + k]), p.scale_log2, -lse));
+              if (decltype(EDGE)::value) {
+                const int other = t * 64 + col;
+                const bool masked = DKV ? (other < pos) : (other > pos);
+                if (masked) pr = 0.f;
+              }
+              pf[k] = pr;
+              df[k] = pr * ((__uint_as_float(x2[8 * i + k]) - dl) * p.scale);
             }
-            pf[k] = pr;
-            df[k] = pr * (__uint_as_float(x2[8 * i + k]) - dl) * p.scale;
+            const int c16 = (c >> 3) + i;
+            st_swz(dsb, r, c16, pack_bf16x8(df));
+            if (DKV) st_swz(ptb, r, c16, pack_bf16x8(pf));
           }
-          const int c16 = (c >> 3) + i;
-          st_swz(dsb, r, c16, pack_bf16x8(df));
-          if (DKV) st_swz(ptb, r, c16, pack_bf16x8(pf));
         }
-      }
+      };
+      if (edge) tile_rows(std::true_type{});
+      else tile_rows(std::false_type{});
       tc_fence_before();
       mbar_arrive(&x_free[s]);
       fence_proxy_async_smem();
@@ -626,7 +645,7 @@ PB_API int pb_attn_fwd(const void* q, const void* k, const void* v, void* out, v
                        int ldo, float scale, int* status, cudaStream_t st) {
   using namespace attn;
   if (bad_geometry(batch, seq, heads, kv_heads, ldq, ldkv) || ldo < heads * D || ldo % 8 != 0 ||
-      seq % 256 != 0)
+      seq % 256 != 0 || !(scale > 0.f))
     return PB_BAD_ARG;
   static bool attr_set = false;
   if (!attr_set) {
@@ -660,7 +679,8 @@ PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* 
                        void* dv, int batch, int seq, int heads, int kv_heads, int ldq, int ldkv,
                        int ldo, float scale, int* status, cudaStream_t st) {
   using namespace attn;
-  if (bad_geometry(batch, seq, heads, kv_heads, ldq, ldkv) || ldo < heads * D || ldo % 8 != 0)
+  if (bad_geometry(batch, seq, heads, kv_heads, ldq, ldkv) || ldo < heads * D || ldo % 8 != 0 ||
+      !(scale > 0.f))
     return PB_BAD_ARG;
   static bool attr_set = false;
   if (!attr_set) {
