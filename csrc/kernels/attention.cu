@@ -107,9 +107,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(q_full, 1);
     for (int i = 0; i < KV_STAGES; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < 4; ++i) {
-      mbar_init(&s_done[i], 1); mbar_init(&s_free[i], 128); mbar_init(&o_done[i], 1);
+      mbar_init(&s_done[i], 1); mbar_init(&s_free[i], 4); mbar_init(&o_done[i], 1);
     }
-    mbar_init(&p_ready[0], 128); mbar_init(&p_ready[1], 128);
+    mbar_init(&p_ready[0], 4); mbar_init(&p_ready[1], 4);   // one arrival per warp
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
@@ -216,7 +216,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_ld_32x32b_x32(lane_addr + COL_S + sb * 64 + 32, v + 32);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&s_free[sb]);           // the scores are in registers now
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[sb]);   // the scores are in registers now
       if (edge) {   // only the blocks on the diagonal pay for the mask
 #pragma unroll
         for (int i = 0; i < 64; ++i)
@@ -267,7 +268,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&p_ready[t]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[t]);
     }
     if (ok && wait_all(&o_done[t * 2 + ((nj - 1) & 1)], ((nj - 1) >> 1) & 1, p.status)) {
       tc_fence_after();
@@ -372,8 +374,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
     mbar_init(r_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 1);
-      mbar_init(&x_done[i], 1); mbar_init(&x_free[i], 128);
-      mbar_init(&pd_ready[i], 128); mbar_init(&pd_free[i], 1);
+      mbar_init(&x_done[i], 1); mbar_init(&x_free[i], 4);    // one arrival per warp
+      mbar_init(&pd_ready[i], 4); mbar_init(&pd_free[i], 1);
     }
     mbar_init(acc_done, 1);
     fence_barrier_init();
@@ -544,9 +546,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
       if (edge) tile_rows(std::true_type{});
       else tile_rows(std::false_type{});
       tc_fence_before();
-      mbar_arrive(&x_free[s]);
       fence_proxy_async_smem();
-      mbar_arrive(&pd_ready[s]);
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&x_free[s]);
+        mbar_arrive(&pd_ready[s]);
+      }
     }
     // every row thread gets here (no early exit above), so the group barriers below are safe
     if (wait_all(acc_done, 0, p.status) && ok) {
