@@ -38,6 +38,22 @@ namespace attn {
 constexpr int D = 128;
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
+// Optional cycle accounting of the forward row warps (compile with -DPB_ATTN_PROF): thread 0 of
+// each warpgroup adds the clocks it spent in each phase of a block to a device array.
+#ifdef PB_ATTN_PROF
+__device__ unsigned long long g_attn_prof[8];
+#define PB_PROF_START long long prof_t = clock64();
+#define PB_PROF(i)                                                                  \
+  if (r == 0) {                                                                     \
+    const long long prof_n = clock64();                                             \
+    atomicAdd(&g_attn_prof[i], static_cast<unsigned long long>(prof_n - prof_t));  \
+    prof_t = prof_n;                                                                \
+  }
+#else
+#define PB_PROF_START
+#define PB_PROF(i)
+#endif
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -78,8 +94,9 @@ struct Params {
 
 // One CTA = 256 query rows of one head: two 128-row tiles, each owned by one warpgroup
 // (warps 0-3 and 4-7) so that one group's exponentials overlap the other's tensor-core work.
-// Keys and values arrive in blocks of 64.  warp 8: MMA issue, warp 9: TMA producer.
-__global__ void __launch_bounds__(320, 1)
+// Keys and values arrive in blocks of 64.  warps 8 and 9: MMA issue for tile 0 and tile 1 (a
+// single issuing thread cannot keep up with 24 small MMAs per block), warp 10: TMA producer.
+__global__ void __launch_bounds__(352, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                 const Params p) {
@@ -88,13 +105,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BARS);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;    // [3]
-  uint64_t* kv_empty = bars + 4;   // [3]
-  uint64_t* s_done = bars + 8;     // [tile][buf]
-  uint64_t* s_free = bars + 12;    // [tile][buf]
-  uint64_t* p_ready = bars + 16;   // [tile]
-  uint64_t* o_done = bars + 18;    // [tile][buf]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+  uint64_t* kv_full = bars + 1;    // [4]
+  uint64_t* kv_empty = bars + 5;   // [4]
+  uint64_t* s_done = bars + 9;     // [tile][buf]
+  uint64_t* s_free = bars + 13;    // [tile][buf]
+  uint64_t* p_ready = bars + 17;   // [tile]
+  uint64_t* o_done = bars + 19;    // [tile][buf]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long rows first
@@ -105,7 +122,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < KV_STAGES; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < KV_STAGES; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 2); }
     for (int i = 0; i < 4; ++i) {
       mbar_init(&s_done[i], 1); mbar_init(&s_free[i], 4); mbar_init(&o_done[i], 1);
     }
@@ -122,7 +139,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 9) {
+  if (warp == 10) {
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, 65536);
       for (int t = 0; t < 2; ++t) {
@@ -142,54 +159,52 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tma_load_3d(st + 16384 + 8192, &tmV, &kv_full[s], g * D + 64, krow, 0);
       }
     }
-  } else if (warp == 8) {
+  } else if (warp >= 8) {
     if (lane == 0) {
+      const int t = warp - 8;                                     // the tile this thread issues for
+      const int nj = nj1 - (t == 0 ? 2 : 0);
       const uint32_t id_s = make_idesc(1, 1, 128, 64, 0, 0);     // S = Q K^T, N = 64 keys
       const uint32_t id_o = make_idesc(1, 1, 128, 128, 0, 1);    // O += P V, V MN-major
       constexpr uint32_t HI = sdesc_hi_sw128(1024);
       // descriptor low words are kept in registers: one add per operand per MMA
-      const uint32_t q_lo0 = sdesc_lo(smem_u32(smem + Q_OFF), 16);
-      const uint32_t p_lo0 = sdesc_lo(smem_u32(smem + P_OFF), 16);
+      const uint32_t q_lo = sdesc_lo(smem_u32(smem + Q_OFF + t * 32768), 16);
+      const uint32_t p_lo0 = sdesc_lo(smem_u32(smem + P_OFF + t * 32768), 16);
       const uint32_t kv0 = smem_u32(smem + KV_OFF);
+      const uint32_t d_o = tmem + COL_O + t * 128;
       bool ok = mbar_wait(q_full, 0, p.status);
-      // scores of block j for both tiles (tile 0 stops two blocks earlier)
       auto issue_s = [&](int j) -> bool {
         const int s = j % KV_STAGES;
+        const int sb = t * 2 + (j & 1);
         if (!mbar_wait(&kv_full[s], (j / KV_STAGES) & 1, p.status)) return false;
+        if (!mbar_wait(&s_free[sb], ((j >> 1) & 1) ^ 1, p.status)) return false;
+        tc_fence_after();
         const uint32_t k_lo = sdesc_lo(kv0 + s * KV_STAGE, 16);
-        for (int t = 0; t < 2; ++t) {
-          if (t == 0 && j >= nj1 - 2) continue;
-          const int sb = t * 2 + (j & 1);
-          if (!mbar_wait(&s_free[sb], ((j >> 1) & 1) ^ 1, p.status)) return false;
-          tc_fence_after();
-          const uint32_t q_lo = q_lo0 + t * (32768 >> 4);
-          const uint32_t d = tmem + COL_S + sb * 64;
+        const uint32_t d = tmem + COL_S + sb * 64;
 #pragma unroll
-          for (int jj = 0; jj < 8; ++jj)
-            umma_f16_words(d, q_lo + (((jj >> 2) * 16384 + (jj & 3) * 32) >> 4), HI,
-                           k_lo + (((jj >> 2) * 8192 + (jj & 3) * 32) >> 4), HI, id_s, jj > 0);
-          umma_commit(&s_done[sb]);
-        }
+        for (int jj = 0; jj < 8; ++jj)
+          umma_f16_words(d, q_lo + (((jj >> 2) * 16384 + (jj & 3) * 32) >> 4), HI,
+                         k_lo + (((jj >> 2) * 8192 + (jj & 3) * 32) >> 4), HI, id_s, jj > 0);
+        umma_commit(&s_done[sb]);
         return true;
       };
+      // the scores run two blocks ahead of the P V products, so neither the row warps nor
+      // the P V issue ever wait for a K/V tile that is still in flight
       if (ok) ok = issue_s(0);
-      for (int j = 0; j < nj1 && ok; ++j) {
+      if (ok && nj > 1) ok = issue_s(1);
+      for (int j = 0; j < nj && ok; ++j) {
         const int s = j % KV_STAGES;
-        if (j + 1 < nj1 && !issue_s(j + 1)) break;
+        if (!mbar_wait(&p_ready[t], j & 1, p.status)) break;
+        tc_fence_after();
         const uint32_t v_lo = sdesc_lo(kv0 + s * KV_STAGE + 16384, 8192);
-        for (int t = 0; t < 2; ++t) {
-          if (t == 0 && j >= nj1 - 2) continue;
-          if (!mbar_wait(&p_ready[t], j & 1, p.status)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t p_lo = p_lo0 + ((t * 32768 + (j & 1) * 16384) >> 4);
-          const uint32_t d = tmem + COL_O + t * 128;
+        const uint32_t p_lo = p_lo0 + (((j & 1) * 16384) >> 4);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
-            umma_f16_words(d, p_lo + ((jj * 32) >> 4), HI, v_lo + ((jj * 2048) >> 4), HI, id_o,
-                           (j > 0) || (jj > 0));
-          umma_commit(&o_done[t * 2 + (j & 1)]);
-        }
-        umma_commit(&kv_empty[s]);
+        for (int jj = 0; jj < 4; ++jj)
+          umma_f16_words(d_o, p_lo + ((jj * 32) >> 4), HI, v_lo + ((jj * 2048) >> 4), HI, id_o,
+                         (j > 0) || (jj > 0));
+        umma_commit(&o_done[t * 2 + (j & 1)]);
+        umma_commit(&kv_empty[s]);   // needs both tiles' commits (tile 0 skips the last two blocks,
+                                     // whose stages are never refilled)
+        if (j + 2 < nj && !issue_s(j + 2)) break;
       }
     }
   } else {
@@ -209,8 +224,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int sb = t * 2 + (j & 1);
       const uint32_t ph = (j >> 1) & 1;
       const bool edge = j * 64 + 63 > q0;
+      PB_PROF_START
       if (!wait_all(&s_done[sb], ph, p.status)) { ok = false; break; }
       tc_fence_after();
+      PB_PROF(0)
       uint32_t v[64];
       tmem_ld_32x32b_x32(lane_addr + COL_S + sb * 64, v);
       tmem_ld_32x32b_x32(lane_addr + COL_S + sb * 64 + 32, v + 32);
@@ -218,6 +235,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[sb]);   // the scores are in registers now
+      PB_PROF(1)
       if (edge) {   // only the blocks on the diagonal pay for the mask
 #pragma unroll
         for (int i = 0; i < 64; ++i)
@@ -228,6 +246,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       m_true = fmaxf(m_true, mx);
+      PB_PROF(2)
       if (j == 0) {
         m_used = mx;
       } else if (__any_sync(0xffffffffu, mx > m_used + RESCALE_THRESHOLD)) {
@@ -249,8 +268,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_st_wait();
         m_used = m_new;
       }
-      // the P buffer of two blocks ago has been consumed
-      if (j >= 2 && !wait_all(&o_done[sb], ((j - 2) >> 1) & 1, p.status)) { ok = false; break; }
+      PB_PROF(3)
+      // P buffer j & 1 was last read by the P V product of block j - 2, which this thread's
+      // issuer queued before S(j): the completed s_done wait above already covers it
       uint8_t* pbuf = smem + P_OFF + t * 32768 + (j & 1) * 16384;
       const float neg_m = -m_used;
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -266,10 +286,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         st_swz(pbuf, r, i, pack_bf16x8(f));
       }
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      PB_PROF(4)
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t]);
+      PB_PROF(5)
+#ifdef PB_ATTN_PROF
+      if (r == 0) atomicAdd(&g_attn_prof[6], 1ull);
+#endif
     }
     if (ok && wait_all(&o_done[t * 2 + ((nj - 1) & 1)], ((nj - 1) >> 1) & 1, p.status)) {
       tc_fence_after();
@@ -336,9 +361,11 @@ struct Params {
 // DKV = true : resident K, V (one KV head); streams Q, dO tiles of the group; outputs dK, dV.
 // Two warpgroups (warps 0-3, 4-7) take the streamed tiles alternately, each with its own score
 // buffers in tensor memory and its own dS / P^T operand buffers, and accumulate into the same
-// gradient accumulators.  warp 8: MMA issue, warp 9: TMA producer.
+// gradient accumulators.  MMA issue is spread over three warps because one thread cannot issue
+// 20+ small MMAs per tile fast enough: warp 8 the first score product, warp 9 the second,
+// warp 10 the gradient accumulations; warp 11: TMA producer.
 template <bool DKV>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(384, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant__ CUtensorMap tmRB,
                 const __grid_constant__ CUtensorMap tmT1, const __grid_constant__ CUtensorMap tmT2,
                 const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
@@ -374,7 +401,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
     mbar_init(r_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 1);
-      mbar_init(&x_done[i], 1); mbar_init(&x_free[i], 4);    // one arrival per warp
+      mbar_init(&x_done[i], 2); mbar_init(&x_free[i], 4);    // two issuing threads; one arrival per row warp
       mbar_init(&pd_ready[i], 4); mbar_init(&pd_free[i], 1);
     }
     mbar_init(acc_done, 1);
@@ -391,7 +418,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 9) {
+  if (warp == 11) {
     if (lane == 0) {
       const int rx = (DKV ? g : hy) * D;
       mbar_arrive_expect_tx(r_full, 65536);
@@ -414,41 +441,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
         tma_load_3d(st + 16384 + 8192, &tmT2, &t_full[s], tx + 64, trow, 0);
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == 8 || warp == 9) {
+    // score products: warp 8 issues X1 = RA T1^T, warp 9 issues X2 = RB T2^T
     if (lane == 0) {
+      const int which = warp - 8;
       const uint32_t id_x = make_idesc(1, 1, 128, 64, 0, 0);     // A K-major, B K-major, N = 64
+      constexpr uint32_t HI = sdesc_hi_sw128(1024);
+      const uint32_t r_lo = sdesc_lo(smem_u32(smem + (which == 0 ? RA_OFF : RB_OFF)), 16);
+      const uint32_t st0 = smem_u32(smem + ST_OFF + which * 16384);
+      const uint32_t col = which == 0 ? COL_X1 : COL_X2;
+      bool ok = mbar_wait(r_full, 0, p.status);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&t_full[s], ph, p.status)) break;
+        if (!mbar_wait(&x_free[s], ph ^ 1, p.status)) break;
+        tc_fence_after();
+        const uint32_t t_lo = sdesc_lo(st0 + s * 32768, 16);
+        const uint32_t d = tmem + col + s * 64;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj)
+          umma_f16_words(d, r_lo + (((jj >> 2) * 16384 + (jj & 3) * 32) >> 4), HI,
+                         t_lo + (((jj >> 2) * 8192 + (jj & 3) * 32) >> 4), HI, id_x, jj > 0);
+        umma_commit(&x_done[s]);
+      }
+    }
+  } else if (warp == 10) {
+    // gradient accumulations, all from this one thread so that they stay ordered
+    if (lane == 0) {
       const uint32_t id_acc = make_idesc(1, 1, 128, 128, 0, 1);  // A K-major, B MN-major
       constexpr uint32_t HI = sdesc_hi_sw128(1024);
-      const uint32_t ra_lo = sdesc_lo(smem_u32(smem + RA_OFF), 16);
-      const uint32_t rb_lo = sdesc_lo(smem_u32(smem + RB_OFF), 16);
       const uint32_t st0 = smem_u32(smem + ST_OFF);
       const uint32_t ds_lo0 = sdesc_lo(smem_u32(smem + DS_OFF), 16);
       const uint32_t pt_lo0 = sdesc_lo(smem_u32(smem + PT_OFF), 16);
-      bool ok = mbar_wait(r_full, 0, p.status);
-      auto issue_x = [&](int it) -> bool {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&t_full[s], ph, p.status)) return false;
-        if (!mbar_wait(&x_free[s], ph ^ 1, p.status)) return false;
-        tc_fence_after();
-        const uint32_t t1_lo = sdesc_lo(st0 + s * 32768, 16), t2_lo = t1_lo + (16384 >> 4);
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj)
-          umma_f16_words(tmem + COL_X1 + s * 64, ra_lo + (((jj >> 2) * 16384 + (jj & 3) * 32) >> 4),
-                         HI, t1_lo + (((jj >> 2) * 8192 + (jj & 3) * 32) >> 4), HI, id_x, jj > 0);
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj)
-          umma_f16_words(tmem + COL_X2 + s * 64, rb_lo + (((jj >> 2) * 16384 + (jj & 3) * 32) >> 4),
-                         HI, t2_lo + (((jj >> 2) * 8192 + (jj & 3) * 32) >> 4), HI, id_x, jj > 0);
-        umma_commit(&x_done[s]);
-        return true;
-      };
-      if (ok) ok = issue_x(0);
       int it = 0;
-      for (; it < n_it && ok; ++it) {
+      for (; it < n_it; ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (it + 1 < n_it && !issue_x(it + 1)) break;
         if (!mbar_wait(&pd_ready[s], ph, p.status)) break;
         tc_fence_after();
         // the streamed tiles again, now as MN-major B operands (64-wide chunks 8 KB apart)
@@ -464,6 +493,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
             umma_f16_words(tmem + COL_ACC2, pt_lo + ((jj * 32) >> 4), HI,
                            t2_mn + ((jj * 2048) >> 4), HI, id_acc, (it > 0) || (jj > 0));
         }
+        // the score products of this tile finished before the row warps could signal pd_ready,
+        // so the completion of these MMAs releases the whole stage
         umma_commit(&t_empty[s]);
         umma_commit(&pd_free[s]);
       }
@@ -673,7 +704,7 @@ PB_API int pb_attn_fwd(const void* q, const void* k, const void* v, void* out, v
   p.lse2 = static_cast<float*>(lse2);
   p.rowmax = static_cast<float*>(rowmax);
   p.status = status;
-  fwd::attn_fwd_kernel<<<dim3(seq / 256, heads, batch), 320, fwd::SMEM, st>>>(tQ, tK, tV, tO, p);
+  fwd::attn_fwd_kernel<<<dim3(seq / 256, heads, batch), 352, fwd::SMEM, st>>>(tQ, tK, tV, tO, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -722,7 +753,7 @@ PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* 
     r |= make_tmap_3d(&tV, v, 2, ki, rows, 1, ldkv, 0, 64, 64);
     r |= make_tmap_3d(&tDQ, dq, 2, qi, rows, 1, ldq, 0, 64, 128);
     if (r != 0) return 1000 + r;
-    bwd::attn_bwd_kernel<false><<<dim3(p.n_blk, heads, batch), 320, bwd::SMEM, st>>>(
+    bwd::attn_bwd_kernel<false><<<dim3(p.n_blk, heads, batch), 384, bwd::SMEM, st>>>(
         tQ, tDO, tK, tV, tDQ, tDQ, p);
   }
   {
@@ -735,8 +766,19 @@ PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* 
     r |= make_tmap_3d(&tDK, dk, 2, ki, rows, 1, ldkv, 0, 64, 128);
     r |= make_tmap_3d(&tDV, dv, 2, ki, rows, 1, ldkv, 0, 64, 128);
     if (r != 0) return 2000 + r;
-    bwd::attn_bwd_kernel<true><<<dim3(p.n_blk, kv_heads, batch), 320, bwd::SMEM, st>>>(
+    bwd::attn_bwd_kernel<true><<<dim3(p.n_blk, kv_heads, batch), 384, bwd::SMEM, st>>>(
         tK, tV, tQ, tDO, tDK, tDV, p);
   }
   return static_cast<int>(cudaGetLastError());
 }
+
+#ifdef PB_ATTN_PROF
+PB_API int pb_attn_prof_read(unsigned long long* out8, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out8, attn::g_attn_prof, sizeof(unsigned long long) * 8);
+  if (e == cudaSuccess && reset) {
+    unsigned long long z[8] = {};
+    e = cudaMemcpyToSymbol(attn::g_attn_prof, z, sizeof z);
+  }
+  return static_cast<int>(e);
+}
+#endif
