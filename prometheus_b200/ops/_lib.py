@@ -42,6 +42,14 @@ _SIGS = {
     "pb_set_flag": [P, I, P],
     "pb_delta_scan_fwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
     "pb_delta_scan_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
+    "pb_latent_gather": [P, P, I, I, I, I, I, P],
+    "pb_latent_scatter": [P, P, I, I, I, I, I, P],
+    "pb_latent_norm_scatter": [P, P, P, P, P, I, I, I, I, I, F, P],
+    "pb_silu_fwd": [P, P, L, P],
+    "pb_silu_bwd": [P, P, P, L, P],
+    "pb_cp_buffer_bytes": [I],
+    "pb_cp_push": [P, P, P, I, I, I, I, I, P],
+    "pb_cp_compose": [P, P, P, I, I, I, I, I, L, P, P],
     "pb_attn_fwd": [P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P],
     "pb_attn_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P],
     "pb_delta_prep_fwd": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, P, I, P],

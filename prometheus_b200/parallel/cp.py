@@ -212,3 +212,104 @@ def delta_state_handoff_distributed(local_map, *, group=None, s0: Tensor | None 
     dist.all_gather(ps, p.contiguous(), group=group)
     dist.all_gather(rs, r.contiguous(), group=group)
     return delta_state_handoff(list(zip(ps, rs)), s0)[rank]
+
+
+# ---------------------------------------------------------------------------
+# delta-rule layer over a context-parallel group, on peer memory
+# ---------------------------------------------------------------------------
+class DeltaCpContext:
+    """Symmetric buffers and epochs of the device-side state hand-off (``csrc/comm/cp.cu``).
+
+    One context serves every delta-rule layer of a model with ``batch * heads`` states of
+    128 x 128; a device barrier before each push keeps a rank from overwriting slots a peer
+    is still composing from."""
+
+    def __init__(self, bh: int, group=None, wait_budget_s: float = 20.0):
+        from ..ops._lib import query
+        from .symm import SymmetricBuffer, SymmetricGroup
+
+        self.group = group
+        self.sym = SymmetricGroup(group, wait_budget_s)
+        self.world, self.rank = self.sym.world, self.sym.rank
+        self.bh = int(bh)
+        self.buf = SymmetricBuffer(query("pb_cp_buffer_bytes", self.bh), group)
+        self.ptrs = self.buf.peer_ptrs(0)
+        self.epoch = [0, 0]
+        self.budget_ns = int(wait_budget_s * 1e9)
+
+    def handoff(self, p: Tensor, r: Tensor, s0: Tensor | None = None, reverse: bool = False) -> Tensor:
+        """State entering this rank (forward) or state gradient leaving it (reverse), from
+        every rank's ``(P, R)``; fp32 ``(bh, 128, 128)`` in and out."""
+        from ..ops._lib import call, ptr, stream_ptr
+
+        d = 1 if reverse else 0
+        p = p.reshape(self.bh, 128, 128).float().contiguous()
+        r = r.reshape(self.bh, 128, 128).float().contiguous()
+        s0c = None if s0 is None else s0.reshape(self.bh, 128, 128).float().contiguous()
+        out = torch.empty_like(r)
+        self.sym.barrier(2 + d)                 # peers have finished reading the previous maps
+        self.epoch[d] += 1
+        call("pb_cp_push", ptr(p), ptr(r), self.ptrs, self.rank, self.world, self.bh, d,
+             self.epoch[d], stream_ptr())
+        call("pb_cp_compose", self.buf.local_ptr, ptr(s0c), ptr(out), self.rank, self.world, self.bh,
+             d, self.epoch[d], self.budget_ns, ptr(self.sym.status), stream_ptr())
+        return out
+
+    def check(self) -> None:
+        self.sym.check()
+
+    def close(self) -> None:
+        self.buf.close()
+
+
+class _DeltaCpFn(torch.autograd.Function):
+    """Delta rule over a sequence split across the ranks of ``ctx_cp``.
+
+    forward   three local passes: (1) from the zero state -> R, (2) keys only, from the
+              identity -> P, (3) after the hand-off, from the true incoming state -> output.
+              Rank 0 keeps the output of pass (1).
+    backward  the local backward is affine in the gradient of the final state with the
+              transposed linear part P^T, so: (1) local backward with a zero final-state
+              gradient -> Q, (2) reverse hand-off of (P, Q), (3) local backward with the true
+              final-state gradient."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, beta, cp):
+        from ..ops.delta import delta_rule_fused
+
+        b, s, h, d = q.shape
+        with torch.no_grad():
+            out0, r_map = delta_rule_fused(q, k, v, beta, None)
+            eye = torch.eye(d, device=q.device, dtype=torch.float32).expand(b, h, d, d).contiguous()
+            _, p_map = delta_rule_fused(q, k, torch.zeros_like(v), beta, eye)
+            s_in = cp.handoff(p_map, r_map).reshape(b, h, d, d)
+            if cp.rank == 0:
+                out = out0
+            else:
+                out, _ = delta_rule_fused(q, k, v, beta, s_in)
+        ctx.save_for_backward(q, k, v, beta, s_in, p_map)
+        ctx.cp = cp
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        from ..ops.delta import delta_rule_fused
+
+        q, k, v, beta, s_in, p_map = ctx.saved_tensors
+        cp = ctx.cp
+        with torch.enable_grad():
+            leaves = [t.detach().requires_grad_() for t in (q, k, v, beta, s_in)]
+            out, s_fin = delta_rule_fused(*leaves)
+            (q_map,) = torch.autograd.grad(out, leaves[4], d_out, retain_graph=True)
+            g_fin = cp.handoff(p_map, q_map, reverse=True).reshape_as(s_fin)
+            dq, dk, dv, dbeta = torch.autograd.grad((out, s_fin), leaves[:4], (d_out, g_fin))
+        return dq, dk, dv, dbeta, None
+
+
+def delta_rule_cp(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, cp: DeltaCpContext) -> Tensor:
+    """This rank's slice of the delta-rule output for a sequence split contiguously over the
+    ranks of ``cp`` (rank order = sequence order). Shapes as ``ops.delta.delta_rule_fused``;
+    head dim 128, slice length a multiple of 64."""
+    if q.shape[0] * q.shape[2] != cp.bh:
+        _err(f"context was built for batch*heads = {cp.bh}, got {q.shape[0] * q.shape[2]}")
+    return _DeltaCpFn.apply(q, k, v, beta, cp)

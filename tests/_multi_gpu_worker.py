@@ -216,9 +216,56 @@ def main():
     dist.destroy_process_group()
 
 
+def cp_delta_main():
+    """Delta rule over a sequence split across ranks (device-side state hand-off) == the same
+    layer on the whole sequence on one GPU, forward and gradients; twice, since buffers are reused."""
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    from datetime import timedelta
+
+    dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=90))
+    from prometheus_b200.ops import functional as ops
+    from prometheus_b200.ops.delta import delta_rule_fused
+    from prometheus_b200.parallel.cp import DeltaCpContext, delta_rule_cp
+
+    B, S, H, D = 2, 256 * world, 3, 128
+    gen = torch.Generator(device=dev).manual_seed(7)             # same full sequence on every rank
+    q = torch.randn(B, S, H, D, device=dev, generator=gen).bfloat16()
+    k = torch.nn.functional.normalize(torch.randn(B, S, H, D, device=dev, generator=gen), dim=-1).bfloat16()
+    v = torch.randn(B, S, H, D, device=dev, generator=gen).bfloat16()
+    beta = torch.sigmoid(torch.randn(B, S, H, device=dev, generator=gen)).float()
+    go = torch.randn(B, S, H, D, device=dev, generator=gen).bfloat16()
+    lo, hi = rank * S // world, (rank + 1) * S // world
+    cp = DeltaCpContext(B * H, wait_budget_s=10.0)
+    for it in range(2):
+        mine = [t[:, lo:hi].clone().requires_grad_(True) for t in (q, k, v, beta)]
+        out = delta_rule_cp(*mine, cp)
+        (out.float() * go[:, lo:hi].float()).sum().backward()
+    torch.cuda.synchronize()
+    cp.check()
+    ops.check_status(dev)
+    full = [t.clone().requires_grad_(True) for t in (q, k, v, beta)]
+    ref, _ = delta_rule_fused(*full, None)
+    (ref.float() * go.float()).sum().backward()
+    torch.cuda.synchronize()
+
+    def close(a, b, tol, what):
+        err = (a.float() - b.float()).norm().item()
+        sc = b.float().norm().item() + 1e-6
+        assert err <= tol * sc, f"rank {rank} {what}: err {err:.4g} norm {sc:.4g}"
+
+    close(out, ref[:, lo:hi], 2e-2, "out")
+    for name, m, f in zip("qkvb", mine, full):
+        close(m.grad, f.grad[:, lo:hi], 4e-2, "d" + name)
+    dist.barrier()
+    if rank == 0:
+        print("CP_DELTA_OK")
+
+
 if __name__ == "__main__":
     try:
-        {"ep": ep_main, "ep_engine": ep_engine_main}.get((sys.argv[1:] or [""])[0], main)()
+        {"ep": ep_main, "ep_engine": ep_engine_main, "cp_delta": cp_delta_main}.get((sys.argv[1:] or [""])[0], main)()
     except BaseException:
         import traceback
 

@@ -44,3 +44,8 @@ def test_two_rank_expert_parallel_moe():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_expert_parallel_trainer():
     _run_ranks(2, 29521, "EP_ENGINE_OK", "ep_engine")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_context_parallel_delta_rule():
+    _run_ranks(2, 29523, "CP_DELTA_OK", "cp_delta")
