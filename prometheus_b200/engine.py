@@ -115,6 +115,7 @@ class Trainer:
         # per-layer, per-head largest attention logit of the last forward (the statistic the
         # MuonClip-style QK-clip monitors); filled by the attention kernel when switched on
         self.track_max_logit = False
+        self.latent_slots: tuple | None = None      # see set_latent_slots
         self.max_logits: dict[int, Tensor] = {}
         self.ep_ctx = None
         if self.ep and model_config.n_routed_experts % self.world:
@@ -578,6 +579,43 @@ class Trainer:
             n, h = ops.add_rmsnorm(f, h, self.p[nxt])
         return n
 
+    def set_latent_slots(self, slot_start: int, k: int, n_sweeps: int = 4,
+                         truncated_sweeps: int | None = None) -> None:
+        """Latent training layout (prefix | K latent slots | answer): positions
+        ``slot_start .. slot_start + k`` of every sequence are latent slots whose input
+        embeddings are solved by ``n_sweeps`` Jacobi sweeps (each a full forward); gradient
+        flows through the last ``truncated_sweeps`` sweeps. ``k = 0`` switches it off. The
+        caller's loss mask should exclude the slot positions."""
+        if k == 0:
+            self.latent_slots = None
+            return
+        if slot_start < 1 or k < 0 or n_sweeps < 1:
+            raise ValueError("latent slots need slot_start >= 1, k >= 0, n_sweeps >= 1")
+        trunc = n_sweeps if truncated_sweeps is None else int(truncated_sweeps)
+        if trunc < 1 or trunc > n_sweeps:
+            raise ValueError("truncated_sweeps not in 1..=n_sweeps")
+        self.latent_slots = (int(slot_start), int(k), int(n_sweeps), trunc)
+
+    def forward_hidden_latent(self, tokens: Tensor) -> Tensor:
+        """``forward_hidden`` with the latent slots of ``set_latent_slots`` solved by Jacobi
+        sweeps; the per-sweep embedding update is ``ops.latent.jacobi_step`` (gather, adapter
+        MLP on the tcgen05 GEMM, fused normalise + scatter)."""
+        from .ops import latent as LK
+
+        start, k, sweeps, trunc = self.latent_slots
+        B, S = tokens.shape
+        d = self.cfg.d_model
+        embeds = _EmbedFn.apply(tokens, self.p["embed"]).reshape(B, S, d)
+        cur, hidden = embeds, None
+        for i in range(sweeps):
+            if sweeps - trunc > 0 and i == sweeps - trunc:
+                cur = cur.detach()
+            hidden = self.forward_hidden(tokens, inputs_embeds=cur)
+            if i + 1 < sweeps:
+                cur = LK.jacobi_step(hidden.reshape(B, S, d), embeds, self.p["adapter_w1"],
+                                     self.p["adapter_w2"], self.p["adapter_norm"], start, k)
+        return hidden
+
     def loss(self, tokens: Tensor, loss_mask: Tensor, denom: Tensor | float,
              mtp_denoms: list | None = None) -> Tensor:
         """Masked mean next-token CE (soft-capped) of one micro-batch, scaled by 1/denom, plus
@@ -585,7 +623,7 @@ class Trainer:
         ``rmsnorm(h) @ proj + h`` with its own unembedding; mean over heads) and the router
         z-loss."""
         B, S = tokens.shape
-        hid = self.forward_hidden(tokens)
+        hid = self.forward_hidden_latent(tokens) if self.latent_slots else self.forward_hidden(tokens)
         targets = torch.roll(tokens, -1, dims=1).reshape(-1).to(torch.int32)
         wt = loss_mask.float().clone()
         wt[:, 0] = 0.0                          # mask[:, 1:] aligned to the predicting position

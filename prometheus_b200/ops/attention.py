@@ -81,6 +81,13 @@ def causal_gqa(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None,
     d = q.shape[-1]
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     if not _fused_ok(q, k):
+        if q.is_cuda and not return_max_logit:
+            # head dims other than 128 (test-sized models): the library kernel, not the
+            # O(S^2)-memory formula
+            o = torch.nn.functional.scaled_dot_product_attention(
+                q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
+                enable_gqa=True, scale=scale)
+            return o.transpose(1, 2).contiguous()
         out = causal_gqa_ref(q, k, v, scale)
         if not return_max_logit:
             return out
