@@ -45,6 +45,19 @@ struct GemmParams {
   const int* mblk_group;
   const int* k_off;
   const int* k_len;
+  // All-gather mode (ag_ready null for every other GEMM): B is this rank's full-size copy of a
+  // matrix whose rows [q R, (q + 1) R) are owned by rank q. Two copier warps per CTA pull the
+  // other ranks' rows from their buffers (ag_src[q], same layout) into B in 8-row items, ring
+  // order starting after this rank, and add the rows they landed to ag_ready[n_blk]; the TMA
+  // producer of a tile waits until its panel holds ag_epoch x (remote rows of the panel).
+  // Tiles walk the panels in the same ring order, all row blocks of a panel before the next.
+  const void* ag_src[8];
+  void* ag_dst;
+  uint32_t* ag_ready;
+  long ag_ld;
+  int ag_rank, ag_world, ag_rows_per_rank;
+  uint32_t ag_epoch;
+  uint64_t ag_budget_ns;
 };
 
 template <int BN>
@@ -58,7 +71,7 @@ struct GemmSmem {
 };
 
 template <int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(256, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   using S = GemmSmem<BN>;
@@ -108,6 +121,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto tile_coords = [&](long t, int& b, int& m_blk, int& n_blk) {
     b = static_cast<int>(t / tiles_per_batch);
     const int r = static_cast<int>(t % tiles_per_batch);
+    if (p.ag_ready != nullptr) {   // panels in ring order from this rank's first panel
+      m_blk = r % num_m;
+      n_blk = ((p.ag_rank * p.ag_rows_per_rank) / BN + r / num_m) % num_n;
+      return;
+    }
     const int group = 8 * num_n;
     const int g = r / group;
     const int first_m = g * 8;
@@ -143,6 +161,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int m0 = m_blk * BM, n0 = n_blk * BN;
         int b_a, b_b, k_base, nkb;
         if (!tile_group(b, m_blk, b_a, b_b, k_base, nkb)) continue;
+        if (p.ag_ready != nullptr) {
+          // rows of this panel that other ranks own must have landed in B
+          const int lo = max(n0, p.ag_rank * p.ag_rows_per_rank);
+          const int hi = min(min(n0 + BN, p.N), (p.ag_rank + 1) * p.ag_rows_per_rank);
+          const int remote = min(n0 + BN, p.N) - n0 - max(hi - lo, 0);
+          if (remote > 0) {
+            if (!wait_flag_ge(p.ag_ready + n_blk, p.ag_epoch * static_cast<uint32_t>(remote),
+                              p.ag_budget_ns, p.status)) { ok = false; break; }
+            // the rows were written by ordinary stores; the bulk loads below read through the
+            // asynchronous proxy
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+          }
+        }
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, p.status)) { ok = false; break; }
           mbar_arrive_expect_tx(&full[s], S::STAGE_BYTES);
@@ -207,6 +238,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         umma_commit(&tfull[acc]);
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------- all-gather copier (idle in every other mode) -------------------
+    if (p.ag_ready != nullptr) {
+      const int R = p.ag_rows_per_rank;
+      const int items_per_rank = (R + 7) / 8;
+      const long n_items = static_cast<long>(p.ag_world - 1) * items_per_rank;
+      const int vec_per_row = p.K / 8;   // 16-byte vectors
+      for (long it = static_cast<long>(blockIdx.x) * 2 + (warp - 6); it < n_items;
+           it += static_cast<long>(gridDim.x) * 2) {
+        const int src = (p.ag_rank + 1 + static_cast<int>(it / items_per_rank)) % p.ag_world;
+        const int r0 = src * R + static_cast<int>(it % items_per_rank) * 8;
+        const int nrows = min(8, (src + 1) * R - r0);
+        const bf16x8* sp = static_cast<const bf16x8*>(p.ag_src[src]);
+        bf16x8* dp = static_cast<bf16x8*>(p.ag_dst);
+        for (int rr = 0; rr < nrows; ++rr) {
+          const size_t base = (static_cast<size_t>(r0 + rr) * p.ag_ld) / 8;
+          int j = lane;
+          for (; j + 96 < vec_per_row; j += 128) {   // four peer loads in flight per lane
+            const bf16x8 a = sp[base + j], b = sp[base + j + 32], c = sp[base + j + 64],
+                         d = sp[base + j + 96];
+            dp[base + j] = a; dp[base + j + 32] = b; dp[base + j + 64] = c; dp[base + j + 96] = d;
+          }
+          for (; j < vec_per_row; j += 32) dp[base + j] = sp[base + j];
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.ag_ready + r0 / BN, static_cast<uint32_t>(nrows));
       }
     }
   } else {
@@ -392,7 +452,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   }
 
-  if (warp >= 2 && lane == 0) tma_store_wait<0>();  // staged tiles must be read out before exit
+  if (warp >= 2 && warp < 6 && lane == 0) tma_store_wait<0>();  // staged tiles must be read out before exit
   tc_fence_before();
   __syncthreads();
   if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != PB_OK) {
@@ -477,7 +537,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = static_cast<int>(tiles);
-  gemm_bf16_kernel<BN><<<grid, 192, GemmSmem<BN>::TOTAL, st>>>(tmA, tmB, tmC, p);
+  gemm_bf16_kernel<BN><<<grid, 256, GemmSmem<BN>::TOTAL, st>>>(tmA, tmB, tmC, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -505,6 +565,40 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
                      int d_f32, float alpha, float beta, int* status, int max_ctas,
                      cudaStream_t st, const int* mblk_group, int b_batch, const int* k_off,
                      const int* k_len);
+
+// all-gather arguments of the call in progress (host side, set only by pb_gemm_bf16_ag)
+struct AgArgs {
+  const void* src[8];
+  uint32_t* ready;
+  int rank, world, rows_per_rank;
+  uint32_t epoch;
+  uint64_t budget_ns;
+};
+static thread_local const AgArgs* g_ag = nullptr;
+
+// C = A W^T where W [N, K] is sharded by rows over `world` ranks and gathered by the kernel
+// itself: w_ptrs[q] is rank q's full-size buffer (its own rows valid), w_ptrs[rank] doubles as the
+// local destination. ready: uint32 [ceil(N / 256)] on this GPU, zero before the first call and
+// owned by this weight; epoch counts the calls (1, 2, ...). N / world must be a multiple of 8,
+// N > 128. Peers must not rewrite their rows while the call runs.
+PB_API int pb_gemm_bf16_ag(const void* A, void* const* w_ptrs, void* C, int M, int N, int K, long lda,
+                           long ldw, long ldc, int rank, int world, void* ready, int epoch,
+                           long budget_ns, int* status, cudaStream_t st) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || N % world != 0 ||
+      (N / world) % 8 != 0 || N <= 128 || K % 8 != 0 || epoch <= 0 || ready == nullptr)
+    return PB_BAD_ARG;
+  AgArgs a;
+  for (int i = 0; i < 8; ++i) a.src[i] = i < world ? w_ptrs[i] : nullptr;
+  a.ready = static_cast<uint32_t*>(ready);
+  a.rank = rank; a.world = world; a.rows_per_rank = N / world;
+  a.epoch = static_cast<uint32_t>(epoch);
+  a.budget_ns = static_cast<uint64_t>(budget_ns);
+  g_ag = &a;
+  const int rc = gemm_impl(A, w_ptrs[rank], C, nullptr, M, N, K, 1, lda, ldw, ldc, ldc, 0, 0, 0, 0, 0, 0,
+                           0, 0, 1.f, 0.f, status, 0, st, nullptr, 0, nullptr, nullptr);
+  g_ag = nullptr;
+  return rc;
+}
 
 PB_API int pb_gemm_bf16(const void* A, const void* B, void* C, const void* D, int M, int N, int K,
                         int batch, long lda, long ldb, long ldc, long ldd, long strideA,
@@ -584,6 +678,14 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
   p.status = status;
   p.debug = g_gemm_debug;
   p.mblk_group = mblk_group; p.k_off = k_off; p.k_len = k_len;
+  p.ag_ready = nullptr;
+  if (g_ag != nullptr) {
+    for (int i = 0; i < 8; ++i) p.ag_src[i] = g_ag->src[i];
+    p.ag_dst = const_cast<void*>(B);
+    p.ag_ready = g_ag->ready; p.ag_ld = ldb;
+    p.ag_rank = g_ag->rank; p.ag_world = g_ag->world; p.ag_rows_per_rank = g_ag->rows_per_rank;
+    p.ag_epoch = g_ag->epoch; p.ag_budget_ns = g_ag->budget_ns;
+  }
   // TMA-store epilogue when the output rows are 16-byte aligned; else direct stores.
   const int cbytes = out_f32 ? 4 : 2;
   CUtensorMap tmC = tmA;

@@ -47,6 +47,7 @@ _SIGS = {
     "pb_latent_norm_scatter": [P, P, P, P, P, I, I, I, I, I, F, P],
     "pb_silu_fwd": [P, P, L, P],
     "pb_silu_bwd": [P, P, P, L, P],
+    "pb_gemm_bf16_ag": [P, P, P, I, I, I, L, L, L, I, I, P, I, L, P, P],
     "pb_cp_buffer_bytes": [I],
     "pb_cp_push": [P, P, P, I, I, I, I, I, P],
     "pb_cp_compose": [P, P, P, I, I, I, I, I, L, P, P],

@@ -136,3 +136,58 @@ def plan_ownership(counts: Sequence[int], world: int) -> list[list[tuple[int, in
     if world < 1:
         _err("world must be >= 1")
     return [[split_bounds(int(c), world, r) for c in counts] for r in range(world)]
+
+
+# ---------------------------------------------------------------------------
+# fused all-gather + GEMM over peer memory
+# ---------------------------------------------------------------------------
+class AgWeight:
+    """A weight ``(N, K)`` bf16 sharded by rows over the ranks of a group, held in symmetric
+    memory so that the consuming GEMM gathers it itself.
+
+    Every rank allocates the full ``N x K`` buffer; rows ``[rank R, (rank + 1) R)`` with
+    ``R = N / world`` are the rank's authoritative shard, the other rows are landing space.
+    ``linear(x)`` launches one kernel (``pb_gemm_bf16_ag``): copier warps pull the peers' rows
+    over NVLink panel by panel while the tensor-core tiles of the panels already present run,
+    starting with the rank's own panel. Forward only (the trainer keeps replicated bf16
+    weights refreshed by the update kernels; this is the FSDP-style alternative for weights
+    that should stay sharded)."""
+
+    def __init__(self, n: int, k: int, group=None, wait_budget_s: float = 20.0):
+        from .symm import SymmetricBuffer, SymmetricGroup
+
+        self.sym = SymmetricGroup(group, wait_budget_s)
+        self.world, self.rank = self.sym.world, self.sym.rank
+        if n % self.world or (n // self.world) % 8 or n <= 128 or k % 8:
+            _err("AgWeight needs N divisible by world with shards of a multiple of 8 rows, N > 128, K % 8 == 0")
+        self.n, self.k = int(n), int(k)
+        self.rows = n // self.world
+        self.buf = SymmetricBuffer(n * k * 2, group)
+        self.full = self.buf.view(torch.bfloat16, n * k).view(n, k)
+        self.ptrs = self.buf.peer_ptrs(0)
+        self.ready = torch.zeros((n + 255) // 256, dtype=torch.int32, device=self.full.device)
+        self.epoch = 0
+        self.budget_ns = int(wait_budget_s * 1e9)
+
+    @property
+    def shard(self) -> Tensor:
+        """This rank's rows (a view into the symmetric buffer; write the weights here)."""
+        return self.full[self.rank * self.rows:(self.rank + 1) * self.rows]
+
+    def linear(self, x: Tensor) -> Tensor:
+        """``x @ W^T`` for ``x`` of shape ``(M, K)`` bf16 -> ``(M, N)`` bf16."""
+        from ..ops._lib import call, ptr, stream_ptr
+        from ..ops.functional import status_word
+
+        x = x.contiguous()
+        m = x.shape[0]
+        out = torch.empty((m, self.n), dtype=torch.bfloat16, device=x.device)
+        self.sym.barrier(3)            # every rank's shard is final and nobody still reads old rows
+        self.epoch += 1
+        call("pb_gemm_bf16_ag", ptr(x), self.ptrs, ptr(out), m, self.n, self.k, self.k, self.k, self.n,
+             self.rank, self.world, ptr(self.ready), self.epoch, self.budget_ns,
+             ptr(status_word(x.device)), stream_ptr())
+        return out
+
+    def close(self) -> None:
+        self.buf.close()

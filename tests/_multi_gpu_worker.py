@@ -258,14 +258,85 @@ def cp_delta_main():
     close(out, ref[:, lo:hi], 2e-2, "out")
     for name, m, f in zip("qkvb", mine, full):
         close(m.grad, f.grad[:, lo:hi], 4e-2, "d" + name)
+    # exposed time of one hand-off (device barrier + push + bounded wait + compose), max over ranks
+    pm = torch.randn(B * H, 128, 128, device=dev) * 0.05
+    rm = torch.randn(B * H, 128, 128, device=dev)
+    for _ in range(3):
+        cp.handoff(pm, rm)
+    torch.cuda.synchronize(); dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        cp.handoff(pm, rm)
+    e1.record(); torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / 20], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    cp.check()
     dist.barrier()
     if rank == 0:
+        print(f"CP_HANDOFF_TIMING {t.item() * 1000:.1f} us per hand-off ({B * H} states of 128x128 fp32, world {world})")
         print("CP_DELTA_OK")
+
+
+def ag_gemm_main():
+    """Row-sharded weight gathered inside the GEMM kernel == matmul with the full weight."""
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    from datetime import timedelta
+
+    dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=90))
+    from prometheus_b200.ops import functional as ops
+    from prometheus_b200.parallel.fsdp import AgWeight
+
+    for (M, N, K) in ((1024, 1024, 512), (4096, 2816, 2048)):   # 2816 / 256 = 11 panels: one straddles the ranks
+        gen = torch.Generator(device=dev).manual_seed(5)
+        w = (torch.randn(N, K, device=dev, generator=gen) * 0.05).bfloat16()       # same on every rank
+        x = torch.randn(M, K, device=dev, generator=torch.Generator(device=dev).manual_seed(50 + rank)).bfloat16()
+        agw = AgWeight(N, K, wait_budget_s=10.0)
+        for it in range(3):                     # the landing rows are rewritten on every call
+            agw.full.zero_()
+            agw.shard.copy_(w[rank * agw.rows:(rank + 1) * agw.rows] * (it + 1))
+            y = agw.linear(x)
+            torch.cuda.synchronize()
+            ops.check_status(dev)
+            agw.sym.check()
+            ref = (x.float() @ (w.float() * (it + 1)).t())
+            err = (y.float() - ref).abs().max().item()
+            assert err <= 2e-2 * ref.abs().max().item(), f"rank {rank} {M}x{N}x{K} call {it}: err {err}"
+            assert torch.equal(agw.full, (w * (it + 1)).bfloat16()), "gathered weight differs"
+        dist.barrier()
+        agw.close()
+    # timing against the plain GEMM on the already gathered weight (device events, max over ranks)
+    M, N, K = 16384, 2048, 2048
+    agw = AgWeight(N, K, wait_budget_s=10.0)
+    agw.shard.normal_(0, 0.02)
+    x = torch.randn(M, K, device=dev).bfloat16()
+    def timed(fn, n=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+    t_ag = timed(lambda: agw.linear(x))
+    t_plain = timed(lambda: ops.gemm(x, agw.full))
+    gathered = [torch.empty_like(agw.shard) for _ in range(world)]
+    t_nccl = timed(lambda: (dist.all_gather(gathered, agw.shard), ops.gemm(x, agw.full)))
+    if rank == 0:
+        print(f"AG_GEMM_TIMING fused {t_ag:.4f} ms, plain gemm {t_plain:.4f} ms, nccl all_gather + gemm {t_nccl:.4f} ms "
+              f"(M {M} N {N} K {K}, world {world})")
+        print("AG_GEMM_OK")
 
 
 if __name__ == "__main__":
     try:
-        {"ep": ep_main, "ep_engine": ep_engine_main, "cp_delta": cp_delta_main}.get((sys.argv[1:] or [""])[0], main)()
+        {"ep": ep_main, "ep_engine": ep_engine_main, "cp_delta": cp_delta_main, "ag_gemm": ag_gemm_main}.get((sys.argv[1:] or [""])[0], main)()
     except BaseException:
         import traceback
 

@@ -49,3 +49,8 @@ def test_two_rank_expert_parallel_trainer():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_context_parallel_delta_rule():
     _run_ranks(2, 29523, "CP_DELTA_OK", "cp_delta")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_all_gather_gemm():
+    _run_ranks(2, 29525, "AG_GEMM_OK", "ag_gemm")
