@@ -20,6 +20,7 @@ void bind_data_pipeline(py::module_& m);
 void bind_rl_tasks(py::module_& m);
 void bind_synth(py::module_& m);
 void bind_contracts(py::module_& m);
+void bind_verify_stages(py::module_& m);
 
 PYBIND11_MODULE(_pb200_native, m) {
   m.doc() = "C++ systems components of prometheus_b200 (loader, checkpoints, control, ...)";
@@ -53,4 +54,5 @@ PYBIND11_MODULE(_pb200_native, m) {
   bind_rl_tasks(m);
   bind_synth(m);
   bind_contracts(m);
+  bind_verify_stages(m);
 }
