@@ -223,3 +223,19 @@ def test_ops_rollout_quorum_shadow_promote_and_rollback(tmp_path):
     ops.start_shadow(store, 51)
     ops.shadow_fail("diverged", store, 52)
     assert ops.state == "rolled_back:diverged" and "kernel.shadow" not in store.pins
+
+
+def test_harness_command_line(tmp_path, capsys):
+    from prometheus_b200.native import harness
+
+    assert harness.main([]) == 0 and "usage: harness" in capsys.readouterr().out
+    assert harness.main(["frobnicate"]) == 1 and "unknown command" in capsys.readouterr().err
+    assert harness.main(["status"]) == 1
+    capsys.readouterr()
+    args = ["--ops-dir", str(tmp_path / "ops"), "--raft-dir", str(tmp_path / "raft")]
+    assert harness.main(["status"] + args) == 0
+    text = capsys.readouterr().out
+    assert text.startswith("kernel_version:") and "nodes:" in text
+    assert harness.main(["--json", "status"] + args) == 0          # reopened from the same directories
+    js = json.loads(capsys.readouterr().out)
+    assert js["state"] == "idle" and len(js["nodes"]) == 3
