@@ -1,0 +1,68 @@
+"""tokenizer / synth Python faces and the genome seed loader."""
+import pytest
+
+from prometheus_b200 import contracts, genome_seed, native, synth
+from prometheus_b200 import tokenizer as T
+
+
+def test_tokenizer_face(tmp_path):
+    docs = ["the cat sat on the mat. the cat ate."] * 4 + ["a dog and a cat"]
+    t = T.Tokenizer.train(docs, T.TrainConfig("tok-a", 300))
+    ids = t.encode("the cat")
+    assert t.decode(ids) == "the cat" and t.vocab_size == 300 and len(ids) < len("the cat")
+    assert t.encode_grid([0, 9, 3]) == [T.FIRST_ARC, T.FIRST_ARC + 9, T.FIRST_ARC + 3]
+    assert t.decode_bytes(t.encode_bytes(b"\xff\x00a")) == b"\xff\x00a"
+    b, m = t.encode_batch(["the cat", "a"], add_bos=True, add_eos=True)
+    assert b.shape == m.shape == (2, len(ids) + 2) and b[1, -1] == t.special_tokens["pad"] and m[1].sum() == 3
+    assert t.encode_batch(["the cat"], max_len=2)[0].shape == (1, 2)
+    t.freeze("2026-01-01T00:00:00Z")
+    pointer = t.save(tmp_path / "tok")
+    assert pointer["schema_id"] == "prometheus.vocab" and (tmp_path / "tok" / "vocab.jsonl").exists()
+    contracts.validate(t.to_contract())
+    contracts.validate(pointer)
+    back = T.Tokenizer.load(tmp_path / "tok")
+    assert back.encode("the cat") == ids and back.vocab_hash == t.vocab_hash and back.frozen
+    with pytest.raises(T.TokenizerError):
+        T.Tokenizer.train(docs, T.TrainConfig("x", 100))
+    with pytest.raises(T.TokenizerError):
+        T.Tokenizer.load(tmp_path / "missing")
+    assert T.baseline_byte_tokens_per_word("ab cd") == 2.5 > 0
+
+
+def test_synth_face_connects_engine_and_tokenizer():
+    eng = native.serve.LocalEngine("m", 1, 2, 30000)
+    gen = synth.engine_generator(eng)
+    outs = gen(["a", "b", "c"], 3, 0.0)                       # three prompts through a batch limit of two
+    assert len(outs) == 3 and outs[0] == eng.generate(["a"], 3, 0.0)[0][1]
+    o = synth.Orchestrator(gen, max_tokens=4, styles=["news"])
+    assert [r.style for r in o.rephrase_many([("d", "Cats purr.")])] == ["news"]
+    t = T.Tokenizer.train(["x y z"] * 3, T.TrainConfig("g", 272))
+    assert synth.grid_tokens(t, [[1, 2], [3, 4]]) == [261, 262, 263, 264]
+    assert synth.STYLES[0] == "encyclopedia" and "math" in synth.DOMAINS
+    assert synth.extract_answer("x\nAnswer: 7") == "7"
+
+
+def test_genome_seed_loader(tmp_path):
+    seed = genome_seed.load_seed()
+    assert genome_seed.role_names(seed) == genome_seed.ROLES
+    assert [p.name for p in seed.programs] == ["loop"] and seed.tools and seed.skills
+    text = genome_seed.instructions_for(seed, "tester")
+    assert text.startswith("# Tester") and "# Seed loop" in text
+    with pytest.raises(genome_seed.GenomeError):
+        genome_seed.instructions_for(seed, "overlord")
+    (tmp_path / "roles").mkdir()
+    (tmp_path / "roles" / "director.md").write_text("# D")
+    with pytest.raises(genome_seed.GenomeError) as e:
+        genome_seed.load_seed(tmp_path)
+    assert "researcher" in str(e.value)
+    with pytest.raises(genome_seed.GenomeError):
+        genome_seed.load_seed(tmp_path / "nope")
+    for r in genome_seed.ROLES[1:]:
+        (tmp_path / "roles" / f"{r}.md").write_text(f"# {r}")
+    (tmp_path / "roles" / "archivist.md").write_text("# extra")
+    assert genome_seed.role_names(genome_seed.load_seed(tmp_path)) == genome_seed.ROLES + ("archivist",)
+    # the kernel accepts the composed instructions
+    k = native.kernel.Kernel(str(tmp_path / "ledger.jsonl"), str(tmp_path / "mirror"), str(tmp_path / "log"))
+    (tmp_path / "mirror").mkdir(exist_ok=True)
+    agent = k.spawn("director", genome_seed.instructions_for(seed, "director"), native.kernel.Quota(10, 1, 1), "loop")
+    assert agent.depth == 0
