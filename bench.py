@@ -47,6 +47,10 @@ def parse_args():
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (invalid as a result)")
+    ap.add_argument("--config", default="dense", choices=["dense", "latent", "moe16b"],
+                    help="dense: the headline 1.3B hybrid (default). latent: the same model with 1024-token "
+                         "prefix + 8 latent slots + 512-token answer, 4 Jacobi sweeps, 8 sequences per GPU. "
+                         "moe16b: 28-layer 64-expert top-6 MoE with FP8 linears, expert parallel over the ranks.")
     return ap.parse_args()
 
 
@@ -151,14 +155,33 @@ def main() -> int:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    model_name = MODEL_NAME
+    trainer_kw = {}
+    if args.config == "latent":
+        args.seq_len = 1024 + 8 + 512
+        if args.seqs_per_gpu == SEQS_PER_GPU:
+            args.seqs_per_gpu = 8
+        model_name += " + latent slots (prefix 1024 | K=8 | answer 512, 4 Jacobi sweeps)"
     cfg = model.config_dense_1p3b(max_context=args.seq_len)
+    if args.config == "moe16b":
+        cfg = model.with_overrides(model.config_moe_16b(), max_context=args.seq_len)
+        if args.seqs_per_gpu == SEQS_PER_GPU:
+            args.seqs_per_gpu = 8
+        trainer_kw = dict(fp8=True, expert_parallel=world > 1)
+        model_name = "moe-16B (28L d2048, 64 routed top-6 + 2 shared experts h1408, FP8 e4m3 block-scaled linears)"
     if args.layers:
         cfg = model.with_overrides(cfg, n_layers=args.layers, n_dense=args.layers,
                                    n_linear_attn=args.layers * 3 // 4, n_mla=args.layers // 4,
                                    core_block_layers=args.layers)
     tcfg = train.train_config_for(cfg, warmup_steps=100, stable_steps=10_000, decay_steps=1000)
     torch.manual_seed(1234)
-    tr = engine.Trainer(cfg, tcfg, seed=0, device=dev, micro_batch=args.micro_batch)
+    tr = engine.Trainer(cfg, tcfg, seed=0, device=dev, micro_batch=args.micro_batch, **trainer_kw)
+    step_kw = {}
+    if args.config == "latent":
+        tr.set_latent_slots(1024, 8, 4)
+        mask = torch.ones(args.seqs_per_gpu, args.seq_len, device=dev)
+        mask[:, 1024:1032] = 0
+        step_kw = dict(loss_mask=mask)
 
     B, S = args.seqs_per_gpu, args.seq_len
     gen = torch.Generator().manual_seed(1000 + rank)
@@ -173,7 +196,7 @@ def main() -> int:
         torch.cuda.synchronize()
 
     for i in range(args.warmup):
-        tr.step(dev_tokens[i % len(dev_tokens)])
+        tr.step(dev_tokens[i % len(dev_tokens)], **step_kw)
     sync_all()
 
     sampler = ClockSampler(local_rank)
@@ -184,7 +207,7 @@ def main() -> int:
     sync_all()
     e0.record()
     for i in range(args.steps):
-        out = tr.step(dev_tokens[i % len(dev_tokens)])
+        out = tr.step(dev_tokens[i % len(dev_tokens)], **step_kw)
     e1.record()
     sync_all()
     ms = e0.elapsed_time(e1)
@@ -197,7 +220,8 @@ def main() -> int:
     f0.record()
     e2e_loss = 0.0
     for i in range(args.steps):
-        res = tr.step_from_host(host_tokens[i % len(host_tokens)])
+        res = tr.step_from_host(host_tokens[i % len(host_tokens)],
+                                *( [step_kw["loss_mask"].cpu().pin_memory()] if step_kw else [] ))
         e2e_loss = res["loss"]
     f1.record()
     sync_all()
@@ -218,9 +242,10 @@ def main() -> int:
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (seeded uniform tokens, random-init weights)",
             "config": {
-                "model": MODEL_NAME if not args.layers else f"DEBUG {args.layers} layers",
+                "model": model_name if not args.layers else f"DEBUG {args.layers} layers",
                 "global_batch": B * world, "seq_len": S,
-                "parallelism": f"dp{world}" if world > 1 else "single",
+                "parallelism": (f"dp{world}" + ("+ep" + str(world) if args.config == "moe16b" else ""))
+                if world > 1 else "single",
                 "micro_batch": args.micro_batch,
                 "l2": "per-step working set (3.5 GB bf16 weights + activations) exceeds the 126 MB L2",
             },
