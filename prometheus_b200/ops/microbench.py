@@ -5,6 +5,7 @@
     python -m prometheus_b200.ops.microbench rmsnorm --rows 131072 --d 2048
     python -m prometheus_b200.ops.microbench ce --rows 4096 --vocab 131072
     python -m prometheus_b200.ops.microbench attn --batch 8 --seq-len 4096
+    python -m prometheus_b200.ops.microbench elementwise --rows 32768 [--only rope]
 
 Each prints one JSON line with the achieved rate and its fraction of the measured peak
 (``MEASURED_PEAKS.json`` at the repository root when present, else the stated fallback).
@@ -165,6 +166,69 @@ def bench_ce(a):
             "frac_of_peak": gbs / peaks()["hbm_gbs"]}
 
 
+def bench_elementwise(a):
+    """Every HBM-bound kernel of the training step on the 1.3B shapes: achieved bytes / time
+    against the measured copy bandwidth. Bytes are the algorithmic minimum (each input read once,
+    each output written once)."""
+    from . import fp8, moe
+    from . import functional as ops
+    from . import latent as LK
+    from ._lib import call, ptr, stream_ptr
+
+    rows, d, hid = a.rows, 2048, 5632
+    peak = peaks()["hbm_gbs"]
+    out = {"kernel": "elementwise_suite", "rows": rows, "results": {}}
+
+    def add(name, nbytes, fn, only=None):
+        if a.only and a.only != name:
+            return
+        ms = timeit(fn, a.iters)
+        gbs = nbytes / ms / 1e6
+        out["results"][name] = {"ms": ms, "gbs": gbs, "frac_of_measured_copy": gbs / peak}
+
+    x = torch.randn(rows, d, device="cuda").to(BF16)
+    r = torch.randn(rows, d, device="cuda").to(BF16)
+    w = torch.ones(d, device="cuda")
+    add("add_rmsnorm_fwd", 4 * rows * d * 2, lambda: ops.add_rmsnorm(x, r, w))
+    xg = x.clone().requires_grad_(True)
+    y = ops.rmsnorm(xg, w)
+    gy = torch.randn_like(y)
+    add("rmsnorm_bwd", 3 * rows * d * 2, lambda: torch.autograd.grad(y, xg, gy, retain_graph=True))
+    gu = torch.randn(rows, 2 * hid, device="cuda").to(BF16)
+    add("swiglu_fwd", 3 * rows * hid * 2, lambda: ops.swiglu(gu))
+    gug = gu.clone().requires_grad_(True)
+    sy = ops.swiglu(gug)
+    gs = torch.randn_like(sy)
+    add("swiglu_bwd", 5 * rows * hid * 2, lambda: torch.autograd.grad(sy, gug, gs, retain_graph=True))
+    S = 4096
+    q = torch.randn(rows // S, S, 16, 128, device="cuda").to(BF16)
+    add("rope", 2 * rows * d * 2, lambda: ops.rope_(q, seq_len=S))
+    add("l2norm_fwd", 2 * rows * d * 2, lambda: ops.l2norm(q))
+    add("fp8_quant_rows", rows * d * 3 + rows * d // 32, lambda: fp8.quantize_rows(x))
+    wq = torch.randn(hid, d, device="cuda").to(BF16)
+    add("fp8_quant_blocks", hid * d * 3, lambda: fp8.quantize_blocks(wq))
+    E, k = 64, 6
+    rw = (torch.randn(E, d, device="cuda") * 0.02).to(BF16)
+    logits = ops.gemm(x, rw).float()
+    add("moe_route", 2 * rows * E * 4 + rows * k * 8, lambda: moe.route(logits, None, k))
+    vocab, ce_rows = 131072, min(rows, 4096)
+    lg = torch.randn(ce_rows, vocab, device="cuda").to(BF16)
+    tgt = torch.randint(0, vocab, (ce_rows,), device="cuda", dtype=torch.int32)
+    wt = torch.full((ce_rows,), 1.0 / ce_rows, device="cuda")
+    loss = torch.empty(ce_rows, device="cuda")
+    add("softcap_ce_fwd_bwd", 2 * ce_rows * vocab * 2,
+        lambda: call("pb_softcap_ce", ptr(lg), ptr(tgt), ptr(wt), ptr(loss), None, ce_rows, vocab, 30.0, 1,
+                     stream_ptr()))
+    B, Sl, K = 64, 1544, 8
+    hidden = torch.randn(B, Sl, d, device="cuda").to(BF16)
+    emb = torch.randn(B, Sl, d, device="cuda").to(BF16)
+    w1 = (torch.randn(d, d, device="cuda") * 0.02).to(BF16)
+    w2 = (torch.randn(d, d, device="cuda") * 0.02).to(BF16)
+    with torch.no_grad():
+        add("latent_jacobi_step", 2 * B * Sl * d * 2, lambda: LK.jacobi_step(hidden, emb, w1, w2, w, 1024, K))
+    return out
+
+
 def bench_attn(a):
     """Causal GQA attention, forward and forward+backward, against the library kernel PyTorch
     dispatches to for the same call."""
@@ -234,17 +298,21 @@ def main():
     c = sub.add_parser("ce")
     c.add_argument("--rows", type=int, default=4096)
     c.add_argument("--vocab", type=int, default=131072)
+    el = sub.add_parser("elementwise")
+    el.add_argument("--rows", type=int, default=32768)
+    el.add_argument("--only", default="")
     at = sub.add_parser("attn")
     at.add_argument("--batch", type=int, default=8)
     at.add_argument("--seq-len", type=int, default=4096)
     at.add_argument("--heads", type=int, default=16)
     at.add_argument("--kv-heads", type=int, default=4)
     at.add_argument("--once", action="store_true")
-    for s in (g, d, r, c, f, mo, at):
+    for s in (g, d, r, c, f, mo, at, el):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
     out = {"gemm": bench_gemm, "delta": bench_delta, "rmsnorm": bench_rmsnorm, "ce": bench_ce,
-           "fp8": bench_fp8, "moe": bench_moe, "attn": bench_attn}[a.which](a)
+           "fp8": bench_fp8, "moe": bench_moe, "attn": bench_attn,
+           "elementwise": bench_elementwise}[a.which](a)
     out["peaks"] = peaks()
     print(json.dumps(out))
 

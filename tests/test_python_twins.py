@@ -66,3 +66,19 @@ def test_genome_seed_loader(tmp_path):
     (tmp_path / "mirror").mkdir(exist_ok=True)
     agent = k.spawn("director", genome_seed.instructions_for(seed, "director"), native.kernel.Quota(10, 1, 1), "loop")
     assert agent.depth == 0
+
+
+def test_ci_checks(tmp_path):
+    from prometheus_b200.utils import ci_checks
+
+    assert ci_checks.main(["tree"]) == 0
+    (tmp_path / "prometheus_b200").mkdir()
+    (tmp_path / "prometheus_b200" / "bad.py").write_text("import os\nfrom tests import helper\n")
+    assert ci_checks.check_test_imports(tmp_path) == ["production code imports tests/: prometheus_b200/bad.py"]
+    junit = tmp_path / "j.xml"
+    junit.write_text('<testsuite><testcase classname="a" name="ok"/>'
+                     '<testcase classname="a" name="gpu"><skipped message="needs two GPUs"/></testcase>'
+                     '<testcase classname="a" name="lazy"><skipped message="flaky, later"/></testcase></testsuite>')
+    errs = ci_checks.check_skips(junit)
+    assert len(errs) == 1 and "a::lazy" in errs[0] and ci_checks.main(["skips", str(junit)]) == 1
+    assert ci_checks.main([]) == 2
