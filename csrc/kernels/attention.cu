@@ -85,7 +85,8 @@ constexpr int SMEM = BARS + 512 + 1024;
 constexpr uint32_t COL_S = 0, COL_O = 256, TMEM_COLS = 512;   // S[tile][buf] 64 cols, O[tile] 128
 
 struct Params {
-  int seq, heads, kv_heads;
+  int seq, heads, kv_heads;   // seq: query rows per batch entry
+  int seq_kv, q_off;          // key rows per batch entry; global position of query row 0
   float scale_log2;   // softmax scale * log2(e)
   float* lse2;        // [batch, heads, seq], log2 domain
   float* rowmax;      // [batch, heads, seq] largest scaled logit of the row, or null
@@ -117,8 +118,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int cb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long rows first
   const int h = blockIdx.y, b = blockIdx.z;
   const int g = h / (p.heads / p.kv_heads);
+  const int gb = cb + p.q_off / 256;   // position of this CTA's rows among all keys
   const int row0 = b * p.seq + cb * 256;
-  const int nj1 = 4 * cb + 4;     // 64-key blocks seen by tile 1; tile 0 sees nj1 - 2
+  const int nj1 = 4 * gb + 4;     // 64-key blocks seen by tile 1; tile 0 sees nj1 - 2
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -149,7 +151,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int j = 0; j < nj1; ++j) {
         const int s = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
-        const int krow = b * p.seq + j * 64;
+        const int krow = b * p.seq_kv + j * 64;
         if (!mbar_wait(&kv_empty[s], ph ^ 1, p.status)) break;
         mbar_arrive_expect_tx(&kv_full[s], KV_STAGE);
         uint8_t* st = smem + KV_OFF + s * KV_STAGE;
@@ -211,8 +213,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int t = warp >> 2;               // tile / warpgroup
     const int r = threadIdx.x & 127;       // query row of the tile = tensor-memory lane
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const int qpos = cb * 256 + t * 128 + r;
-    const int q0 = cb * 256 + t * 128;
+    const int qpos = gb * 256 + t * 128 + r;     // global position (for the causal mask)
+    const int q0 = gb * 256 + t * 128;
     const int nj = nj1 - (t == 0 ? 2 : 0);
     auto sync_group = [&] {
       if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -314,7 +316,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           st_swz(obuf + (col >> 6) * 16384, r, (col & 63) >> 3, pack_bf16x8(f));
         }
       }
-      const size_t vi = (static_cast<size_t>(b) * p.heads + h) * p.seq + qpos;
+      const size_t vi = (static_cast<size_t>(b) * p.heads + h) * p.seq + cb * 256 + t * 128 + r;
       p.lse2[vi] = m_used + log2f(l);
       if (p.rowmax != nullptr) p.rowmax[vi] = m_true * 0.6931471805599453f;
       fence_proxy_async_smem();
@@ -350,7 +352,8 @@ constexpr int SMEM = BARS + 256 + 1024;
 constexpr uint32_t COL_X1 = 0, COL_X2 = 128, COL_ACC1 = 256, COL_ACC2 = 384, TMEM_COLS = 512;
 
 struct Params {
-  int seq, heads, kv_heads, n_blk;  // n_blk = seq / 128
+  int seq, heads, kv_heads, n_blk;  // seq: query rows per batch entry; n_blk: 128-row blocks of the grid
+  int seq_kv, q_off;                // key rows per batch entry; global position of query row 0
   float scale_log2, scale;
   const float* lse2;    // [batch, heads, seq]
   const float* delta;   // [batch, heads, seq]  rowsum(dO * O)
@@ -391,11 +394,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
   const int blk = DKV ? static_cast<int>(blockIdx.x) : p.n_blk - 1 - static_cast<int>(blockIdx.x);
   const int hy = blockIdx.y;                       // query head (dQ) or KV head (dKV)
   const int g = DKV ? hy : hy / group;
-  const int n64 = p.seq / 64;
-  const int t_first = DKV ? 2 * blk : 0;           // first streamed 64-row tile
-  const int t_count = DKV ? n64 - 2 * blk : 2 * blk + 2;
+  // dQ: blk is a local query block, streamed tiles are global key tiles 0 .. diagonal.
+  // dKV: blk is a global key block, streamed tiles are the local query tiles at or after it.
+  const int gblk = DKV ? blk : blk + p.q_off / 128;
+  const int q_off64 = p.q_off / 64;
+  const int t_first = DKV ? max(0, 2 * blk - q_off64) : 0;
+  const int t_count = DKV ? max(0, p.seq / 64 - t_first) : 2 * gblk + 2;
   const int n_it = DKV ? group * t_count : t_count;
-  const int row0 = b * p.seq + blk * 128;
+  const int row0 = b * (DKV ? p.seq_kv : p.seq) + blk * 128;
+  const int t_seq = DKV ? p.seq : p.seq_kv;        // rows per batch entry of the streamed tensors
 
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
@@ -431,7 +438,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
         const uint32_t ph = (it >> 1) & 1;
         const int t = t_first + (DKV ? it % t_count : it);
         const int tx = (DKV ? g * group + it / t_count : g) * D;
-        const int trow = b * p.seq + t * 64;
+        const int trow = b * t_seq + t * 64;
         if (!mbar_wait(&t_empty[s], ph ^ 1, p.status)) break;
         mbar_arrive_expect_tx(&t_full[s], 32768);
         uint8_t* st = smem + ST_OFF + s * 32768;
@@ -508,10 +515,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
       if (wg == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
       else asm volatile("bar.sync 2, 128;" ::: "memory");
     };
-    const int pos = blk * 128 + r;   // query position (dQ) or key position (dKV) of this row
+    const int pos = gblk * 128 + r;   // global query position (dQ) or key position (dKV) of this row
     float row_lse = 0.f, row_delta = 0.f;
     if (!DKV) {
-      const size_t vi = (static_cast<size_t>(b) * p.heads + hy) * p.seq + pos;
+      const size_t vi = (static_cast<size_t>(b) * p.heads + hy) * p.seq + blk * 128 + r;
       row_lse = p.lse2[vi];
       row_delta = p.delta[vi];
     }
@@ -541,7 +548,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
       tc_fence_after();
       // mask: dQ rows are queries, columns keys (key > query is masked);
       //       dKV rows are keys, columns queries (query < key is masked)
-      const bool edge = DKV ? (t * 64 < blk * 128 + 127) : (t * 64 + 63 > blk * 128);
+      const int tg = DKV ? t + q_off64 : t;     // global index of the streamed tile
+      const bool edge = DKV ? (tg * 64 < gblk * 128 + 127) : (tg * 64 + 63 > gblk * 128);
       uint8_t* dsb = smem + DS_OFF + s * 16384;
       uint8_t* ptb = smem + PT_OFF + s * 16384;
       auto tile_rows = [&](auto EDGE) {
@@ -561,7 +569,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
               const float dl = DKV ? vec[64 + col] : row_delta;
               float pr = ex2(fmaf(__uint_as_float(x1[8 * i + k]), p.scale_log2, -lse));
               if (decltype(EDGE)::value) {
-                const int other = t * 64 + col;
+                const int other = tg * 64 + col;
                 const bool masked = DKV ? (other < pos) : (other > pos);
                 if (masked) pr = 0.f;
               }
@@ -601,7 +609,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
         for (int i = 0; i < 4; ++i) {
           float f[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[8 * i + k]);
+          // a key block with no local query at or after it gets an all-zero gradient
+          for (int k = 0; k < 8; ++k) f[k] = n_it > 0 ? __uint_as_float(v[8 * i + k]) : 0.f;
           const int col = c + 8 * i;
           st_swz(stage + (col >> 6) * 16384, r, (col & 63) >> 3, pack_bf16x8(f));
         }
@@ -673,15 +682,21 @@ static bool bad_geometry(int batch, int seq, int heads, int kv_heads, int ldq, i
 using namespace pb;
 
 // out = softmax(scale * Q K^T + causal mask) V.  q/out: [batch * seq, ldq / ldo] bf16 with head h
-// at columns [128 h, 128 h + 128); k/v: [batch * seq, ldkv] with KV head g likewise.
+// at columns [128 h, 128 h + 128); k/v: [batch * seq_kv, ldkv] with KV head g likewise.
+// Query row i of a batch entry sits at global position q_off + i and sees keys 0 .. q_off + i
+// (q_off = 0 and seq_kv = seq is ordinary causal attention; a context-parallel rank passes its
+// slice of the queries, the gathered keys and its offset). seq, q_off multiples of 256;
+// seq_kv >= q_off + seq, a multiple of 128.
 // lse2: fp32 [batch, heads, seq], log2 of the softmax denominator plus the applied maximum.
 // rowmax (optional): fp32 [batch, heads, seq], the largest scaled logit of each row.
-PB_API int pb_attn_fwd(const void* q, const void* k, const void* v, void* out, void* lse2,
-                       void* rowmax, int batch, int seq, int heads, int kv_heads, int ldq, int ldkv,
-                       int ldo, float scale, int* status, cudaStream_t st) {
+PB_API int pb_attn_fwd_cp(const void* q, const void* k, const void* v, void* out, void* lse2,
+                          void* rowmax, int batch, int seq, int seq_kv, int q_off, int heads,
+                          int kv_heads, int ldq, int ldkv, int ldo, float scale, int* status,
+                          cudaStream_t st) {
   using namespace attn;
   if (bad_geometry(batch, seq, heads, kv_heads, ldq, ldkv) || ldo < heads * D || ldo % 8 != 0 ||
-      seq % 256 != 0 || !(scale > 0.f))
+      seq % 256 != 0 || !(scale > 0.f) || q_off < 0 || q_off % 256 != 0 || seq_kv % 128 != 0 ||
+      seq_kv < q_off + seq)
     return PB_BAD_ARG;
   static bool attr_set = false;
   if (!attr_set) {
@@ -690,16 +705,17 @@ PB_API int pb_attn_fwd(const void* q, const void* k, const void* v, void* out, v
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  const uint64_t rows = static_cast<uint64_t>(batch) * seq;
+  const uint64_t rows = static_cast<uint64_t>(batch) * seq, krows = static_cast<uint64_t>(batch) * seq_kv;
   CUtensorMap tQ, tK, tV, tO;
   int r = 0;
   r |= make_tmap_3d(&tQ, q, 2, static_cast<uint64_t>(heads) * D, rows, 1, ldq, 0, 64, 128);
-  r |= make_tmap_3d(&tK, k, 2, static_cast<uint64_t>(kv_heads) * D, rows, 1, ldkv, 0, 64, 64);
-  r |= make_tmap_3d(&tV, v, 2, static_cast<uint64_t>(kv_heads) * D, rows, 1, ldkv, 0, 64, 64);
+  r |= make_tmap_3d(&tK, k, 2, static_cast<uint64_t>(kv_heads) * D, krows, 1, ldkv, 0, 64, 64);
+  r |= make_tmap_3d(&tV, v, 2, static_cast<uint64_t>(kv_heads) * D, krows, 1, ldkv, 0, 64, 64);
   r |= make_tmap_3d(&tO, out, 2, static_cast<uint64_t>(heads) * D, rows, 1, ldo, 0, 64, 128);
   if (r != 0) return 1000 + r;
   fwd::Params p;
   p.seq = seq; p.heads = heads; p.kv_heads = kv_heads;
+  p.seq_kv = seq_kv; p.q_off = q_off;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse2 = static_cast<float*>(lse2);
   p.rowmax = static_cast<float*>(rowmax);
@@ -708,15 +724,24 @@ PB_API int pb_attn_fwd(const void* q, const void* k, const void* v, void* out, v
   return static_cast<int>(cudaGetLastError());
 }
 
-// Gradients of pb_attn_fwd. delta: fp32 scratch [batch, heads, seq] (written here).
-// dq: [batch * seq, ldq]; dk, dv: [batch * seq, ldkv] (all bf16, fully overwritten).
-PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* out,
-                       const void* dout, const void* lse2, void* delta, void* dq, void* dk,
-                       void* dv, int batch, int seq, int heads, int kv_heads, int ldq, int ldkv,
+PB_API int pb_attn_fwd(const void* q, const void* k, const void* v, void* out, void* lse2,
+                       void* rowmax, int batch, int seq, int heads, int kv_heads, int ldq, int ldkv,
                        int ldo, float scale, int* status, cudaStream_t st) {
+  return pb_attn_fwd_cp(q, k, v, out, lse2, rowmax, batch, seq, seq, 0, heads, kv_heads, ldq, ldkv,
+                        ldo, scale, status, st);
+}
+
+// Gradients of pb_attn_fwd_cp. delta: fp32 scratch [batch, heads, seq] (written here).
+// dq: [batch * seq, ldq]; dk, dv: [batch * seq_kv, ldkv] (all bf16, fully overwritten; key rows
+// that no local query sees get zeros).
+PB_API int pb_attn_bwd_cp(const void* q, const void* k, const void* v, const void* out,
+                          const void* dout, const void* lse2, void* delta, void* dq, void* dk,
+                          void* dv, int batch, int seq, int seq_kv, int q_off, int heads,
+                          int kv_heads, int ldq, int ldkv, int ldo, float scale, int* status,
+                          cudaStream_t st) {
   using namespace attn;
   if (bad_geometry(batch, seq, heads, kv_heads, ldq, ldkv) || ldo < heads * D || ldo % 8 != 0 ||
-      !(scale > 0.f))
+      !(scale > 0.f) || q_off < 0 || q_off % 128 != 0 || seq_kv % 128 != 0 || seq_kv < q_off + seq)
     return PB_BAD_ARG;
   static bool attr_set = false;
   if (!attr_set) {
@@ -728,7 +753,7 @@ PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* 
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  const uint64_t rows = static_cast<uint64_t>(batch) * seq;
+  const uint64_t rows = static_cast<uint64_t>(batch) * seq, krows = static_cast<uint64_t>(batch) * seq_kv;
   const uint64_t qi = static_cast<uint64_t>(heads) * D, ki = static_cast<uint64_t>(kv_heads) * D;
   {
     const long long warps = static_cast<long long>(rows) * heads;
@@ -738,7 +763,8 @@ PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* 
         static_cast<int>(rows), seq, heads, ldo, ldo);
   }
   bwd::Params p;
-  p.seq = seq; p.heads = heads; p.kv_heads = kv_heads; p.n_blk = seq / 128;
+  p.seq = seq; p.heads = heads; p.kv_heads = kv_heads;
+  p.seq_kv = seq_kv; p.q_off = q_off;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.lse2 = static_cast<const float*>(lse2);
   p.delta = static_cast<const float*>(delta);
@@ -749,27 +775,37 @@ PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* 
     CUtensorMap tQ, tDO, tK, tV, tDQ;
     r |= make_tmap_3d(&tQ, q, 2, qi, rows, 1, ldq, 0, 64, 128);
     r |= make_tmap_3d(&tDO, dout, 2, qi, rows, 1, ldo, 0, 64, 128);
-    r |= make_tmap_3d(&tK, k, 2, ki, rows, 1, ldkv, 0, 64, 64);
-    r |= make_tmap_3d(&tV, v, 2, ki, rows, 1, ldkv, 0, 64, 64);
+    r |= make_tmap_3d(&tK, k, 2, ki, krows, 1, ldkv, 0, 64, 64);
+    r |= make_tmap_3d(&tV, v, 2, ki, krows, 1, ldkv, 0, 64, 64);
     r |= make_tmap_3d(&tDQ, dq, 2, qi, rows, 1, ldq, 0, 64, 128);
     if (r != 0) return 1000 + r;
+    p.n_blk = seq / 128;
     bwd::attn_bwd_kernel<false><<<dim3(p.n_blk, heads, batch), 384, bwd::SMEM, st>>>(
         tQ, tDO, tK, tV, tDQ, tDQ, p);
   }
   {
-    // dK, dV: resident K, V; streamed Q, dO
+    // dK, dV: resident K, V (every key block of the gathered keys); streamed local Q, dO
     CUtensorMap tK, tV, tQ, tDO, tDK, tDV;
-    r |= make_tmap_3d(&tK, k, 2, ki, rows, 1, ldkv, 0, 64, 128);
-    r |= make_tmap_3d(&tV, v, 2, ki, rows, 1, ldkv, 0, 64, 128);
+    r |= make_tmap_3d(&tK, k, 2, ki, krows, 1, ldkv, 0, 64, 128);
+    r |= make_tmap_3d(&tV, v, 2, ki, krows, 1, ldkv, 0, 64, 128);
     r |= make_tmap_3d(&tQ, q, 2, qi, rows, 1, ldq, 0, 64, 64);
     r |= make_tmap_3d(&tDO, dout, 2, qi, rows, 1, ldo, 0, 64, 64);
-    r |= make_tmap_3d(&tDK, dk, 2, ki, rows, 1, ldkv, 0, 64, 128);
-    r |= make_tmap_3d(&tDV, dv, 2, ki, rows, 1, ldkv, 0, 64, 128);
+    r |= make_tmap_3d(&tDK, dk, 2, ki, krows, 1, ldkv, 0, 64, 128);
+    r |= make_tmap_3d(&tDV, dv, 2, ki, krows, 1, ldkv, 0, 64, 128);
     if (r != 0) return 2000 + r;
+    p.n_blk = seq_kv / 128;
     bwd::attn_bwd_kernel<true><<<dim3(p.n_blk, kv_heads, batch), 384, bwd::SMEM, st>>>(
         tK, tV, tQ, tDO, tDK, tDV, p);
   }
   return static_cast<int>(cudaGetLastError());
+}
+
+PB_API int pb_attn_bwd(const void* q, const void* k, const void* v, const void* out,
+                       const void* dout, const void* lse2, void* delta, void* dq, void* dk,
+                       void* dv, int batch, int seq, int heads, int kv_heads, int ldq, int ldkv,
+                       int ldo, float scale, int* status, cudaStream_t st) {
+  return pb_attn_bwd_cp(q, k, v, out, dout, lse2, delta, dq, dk, dv, batch, seq, seq, 0, heads,
+                        kv_heads, ldq, ldkv, ldo, scale, status, st);
 }
 
 #ifdef PB_ATTN_PROF

@@ -92,7 +92,7 @@ class Trainer:
                  params: dict | None = None, seed: int = 0, device="cuda", micro_batch: int = 4,
                  muon_weight_decay: float = 0.0, process_group=None, ce_chunk_rows: int = 4096,
                  grad_sync: str = "auto", expert_parallel: bool = False,
-                 ep_capacity_factor: float = 2.0, fp8: bool = False):
+                 ep_capacity_factor: float = 2.0, fp8: bool = False, context_parallel: bool = False):
         M.validate_config(model_config)
         T.validate_train_config(train_config)
         self.cfg, self.tcfg = model_config, train_config
@@ -112,6 +112,15 @@ class Trainer:
         # block-scaled FP8 forward for the FFN / expert products (1 x 128 activations,
         # 128 x 128 weights), straight-through bf16 backward
         self.fp8 = bool(fp8)
+        # context parallelism: the ranks of the group hold consecutive slices of every sequence
+        # (rank order = sequence order). Delta-rule layers hand their chunk state from rank to
+        # rank over peer memory, softmax layers gather K / V and run the offset attention kernel;
+        # weights and gradients are handled exactly as under data parallelism.
+        self.cp = bool(context_parallel) and self.world > 1
+        self.cp_ctx = None
+        if self.cp and (model_config.mtp_heads or model_config.n_mla or expert_parallel):
+            raise ValueError("context parallelism supports the delta-rule + GQA hybrids without MTP heads, "
+                             "MLA layers or expert parallelism")
         # per-layer, per-head largest attention logit of the last forward (the statistic the
         # MuonClip-style QK-clip monitors); filled by the attention kernel when switched on
         self.track_max_logit = False
@@ -467,8 +476,15 @@ class Trainer:
             beta = torch.sigmoid(_SmallLinear.apply(n, wb)).view(B, S, nh)
         else:
             beta = torch.ones((B, S, nh), dtype=BF16, device=n.device)
-        o, _ = kernels.chunked_delta_rule(q, k, v, beta, None,
-                                          kernels.LinearAttnConfig(chunk=cfg.chunk))
+        if self.cp:
+            from .parallel.cp import DeltaCpContext, delta_rule_cp
+
+            if self.cp_ctx is None or self.cp_ctx.bh != B * nh:
+                self.cp_ctx = DeltaCpContext(B * nh, self.pg)
+            o = delta_rule_cp(q, k, v, beta, self.cp_ctx)
+        else:
+            o, _ = kernels.chunked_delta_rule(q, k, v, beta, None,
+                                              kernels.LinearAttnConfig(chunk=cfg.chunk))
         return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
 
     def _ffn_linear(self, x: Tensor, w: Tensor) -> Tensor:
@@ -541,10 +557,18 @@ class Trainer:
         q = ops.linear(n, self.p[pre + "q"]).view(B, S, nh, dh)
         k = ops.linear(n, self.p[pre + "k"]).view(B, S, nkv, dh)
         v = ops.linear(n, self.p[pre + "v"]).view(B, S, nkv, dh)
-        q = ops.rope_(q, seq_len=S, base=cfg.rope_base)
-        k = ops.rope_(k, seq_len=S, base=cfg.rope_base)
+        pos = None
+        if self.cp:      # global positions of this rank's slice
+            pos = (torch.arange(S, dtype=torch.int32, device=n.device) + self.rank * S).repeat(B)
+        q = ops.rope_(q, seq_len=S, pos=pos, base=cfg.rope_base)
+        k = ops.rope_(k, seq_len=S, pos=pos, base=cfg.rope_base)
         from .ops import attention
 
+        if self.cp:
+            from .parallel.cp import cp_attention
+
+            o = cp_attention(q, k, v, self.pg)
+            return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
         if self.track_max_logit:
             o, rowmax = attention.causal_gqa(q, k, v, return_max_logit=True)
             self.max_logits[i] = rowmax.amax(dim=(0, 2))      # per head, for QK-clip
@@ -622,12 +646,21 @@ class Trainer:
         the multi-token-prediction heads (head j predicts j + 1 tokens ahead from
         ``rmsnorm(h) @ proj + h`` with its own unembedding; mean over heads) and the router
         z-loss."""
-        B, S = tokens.shape
-        hid = self.forward_hidden_latent(tokens) if self.latent_slots else self.forward_hidden(tokens)
-        targets = torch.roll(tokens, -1, dims=1).reshape(-1).to(torch.int32)
-        wt = loss_mask.float().clone()
-        wt[:, 0] = 0.0                          # mask[:, 1:] aligned to the predicting position
-        wt = torch.roll(wt, -1, dims=1).reshape(-1) / denom
+        if self.cp:
+            # tokens / mask carry one extra column: the first token of the next rank's slice
+            # (anything with mask 0 on the last rank), so every local position has its target
+            targets = tokens[:, 1:].reshape(-1).to(torch.int32)
+            wt = loss_mask.float()[:, 1:].reshape(-1) / denom
+            tokens, loss_mask = tokens[:, :-1].contiguous(), loss_mask[:, :-1].contiguous()
+            B, S = tokens.shape
+            hid = self.forward_hidden(tokens)
+        else:
+            B, S = tokens.shape
+            hid = self.forward_hidden_latent(tokens) if self.latent_slots else self.forward_hidden(tokens)
+            targets = torch.roll(tokens, -1, dims=1).reshape(-1).to(torch.int32)
+            wt = loss_mask.float().clone()
+            wt[:, 0] = 0.0                          # mask[:, 1:] aligned to the predicting position
+            wt = torch.roll(wt, -1, dims=1).reshape(-1) / denom
         ce = ops.softcap_cross_entropy(hid, self.p["unembed"], targets, wt.contiguous(),
                                        float(self.tcfg.softcap), self.ce_chunk_rows)
         n_mtp = self.cfg.mtp_heads
@@ -786,7 +819,9 @@ class Trainer:
     # --------------------------------------------------------------------- step
     def step(self, tokens: Tensor, loss_mask: Tensor | None = None) -> dict:
         """One optimizer step over a local batch (B_local, S) of token ids on the device.
-        Returns device scalars: loss (mean CE over the global batch) and grad_norm."""
+        Returns device scalars: loss (mean CE over the global batch) and grad_norm.
+        Under context parallelism the batch is this rank's slice plus one column (see
+        ``cp_slice``): ``(B, S_local + 1)``."""
         self.step_count += 1
         t = self.step_count
         sched = T.wsd_lr(t, self.tcfg)
@@ -842,6 +877,20 @@ class Trainer:
         self.zero_grad()
         return {"loss": total, "grad_norm": gnorm, "lr": sched, "step": t}
 
+
+    def cp_slice(self, tokens: Tensor, loss_mask: Tensor | None = None):
+        """This rank's slice of full sequences ``(B, S)`` for a context-parallel step:
+        ``(tokens (B, S/world + 1), mask (B, S/world + 1))`` with the extra column holding the next
+        slice's first token (mask 0 after the end of the sequence)."""
+        B, S = tokens.shape
+        if S % self.world:
+            raise ValueError("sequence length must be divisible by the context-parallel size")
+        sl = S // self.world
+        lo = self.rank * sl
+        mask = torch.ones_like(tokens, dtype=torch.float32) if loss_mask is None else loss_mask.float()
+        tok = torch.cat([tokens, tokens[:, :1]], dim=1)[:, lo:lo + sl + 1]
+        m = torch.cat([mask, torch.zeros_like(mask[:, :1])], dim=1)[:, lo:lo + sl + 1]
+        return tok.contiguous(), m.contiguous()
 
     def step_from_host(self, host_tokens: Tensor, host_mask: Tensor | None = None) -> dict:
         """Public end-to-end step: token ids (and optional mask) in pinned host memory are

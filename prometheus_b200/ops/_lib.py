@@ -52,6 +52,8 @@ _SIGS = {
     "pb_cp_push": [P, P, P, I, I, I, I, I, P],
     "pb_cp_compose": [P, P, P, I, I, I, I, I, L, P, P],
     "pb_attn_fwd": [P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P],
+    "pb_attn_fwd_cp": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
+    "pb_attn_bwd_cp": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
     "pb_attn_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P],
     "pb_delta_prep_fwd": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, P, I, P],
     "pb_delta_prep_bwd": [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, I, P],

@@ -67,6 +67,57 @@ class _AttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+class _AttnCpFn(torch.autograd.Function):
+    """Local queries at global offset ``q_off`` against the keys / values of the whole prefix."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, q_off, scale):
+        from ._lib import call, ptr, stream_ptr
+        from .functional import status_word
+
+        b, s, hq, d = q.shape
+        skv, hkv = k.shape[1], k.shape[2]
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out = torch.empty_like(q)
+        lse2 = torch.empty((b, hq, s), dtype=torch.float32, device=q.device)
+        call("pb_attn_fwd_cp", ptr(q), ptr(k), ptr(v), ptr(out), ptr(lse2), None, b, s, skv, int(q_off), hq,
+             hkv, hq * d, hkv * d, hq * d, float(scale), ptr(status_word(q.device)), stream_ptr())
+        ctx.save_for_backward(q, k, v, out, lse2)
+        ctx.geom = (int(q_off), float(scale))
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        from ._lib import call, ptr, stream_ptr
+        from .functional import status_word
+
+        q, k, v, out, lse2 = ctx.saved_tensors
+        q_off, scale = ctx.geom
+        b, s, hq, d = q.shape
+        skv, hkv = k.shape[1], k.shape[2]
+        d_out = d_out.contiguous()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty_like(lse2)
+        call("pb_attn_bwd_cp", ptr(q), ptr(k), ptr(v), ptr(out), ptr(d_out), ptr(lse2), ptr(delta), ptr(dq),
+             ptr(dk), ptr(dv), b, s, skv, q_off, hq, hkv, hq * d, hkv * d, hq * d, scale,
+             ptr(status_word(q.device)), stream_ptr())
+        return dq, dk, dv, None, None
+
+
+def causal_gqa_offset(q: Tensor, k: Tensor, v: Tensor, q_off: int, scale: float | None = None) -> Tensor:
+    """Causal attention of a query slice that starts at global position ``q_off`` against keys and
+    values that start at position 0: q ``(B, S, Hq, 128)``, k / v ``(B, S_kv, Hkv, 128)`` with
+    ``S_kv >= q_off + S``. ``S`` and ``q_off`` multiples of 256, ``S_kv`` of 128 (the
+    context-parallel layer pads). Gradients: ``dq`` for the slice, ``dk`` / ``dv`` for every key
+    row (zero for rows no query of the slice sees)."""
+    if not _fused_ok(q, k):
+        raise ValueError("causal_gqa_offset needs bf16 CUDA tensors with head dim 128")
+    if q.shape[1] % 256 or q_off % 256 or k.shape[1] % 128 or k.shape[1] < q_off + q.shape[1]:
+        raise ValueError("causal_gqa_offset: S and q_off must be multiples of 256, S_kv of 128, S_kv >= q_off + S")
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    return _AttnCpFn.apply(q, k, v, int(q_off), float(scale))
+
+
 def _fused_ok(q: Tensor, k: Tensor) -> bool:
     return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and k.shape[-1] == 128
             and q.shape[2] % k.shape[2] == 0)

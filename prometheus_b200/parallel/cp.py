@@ -313,3 +313,59 @@ def delta_rule_cp(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, cp: DeltaCpCont
     if q.shape[0] * q.shape[2] != cp.bh:
         _err(f"context was built for batch*heads = {cp.bh}, got {q.shape[0] * q.shape[2]}")
     return _DeltaCpFn.apply(q, k, v, beta, cp)
+
+
+# ---------------------------------------------------------------------------
+# softmax attention over a context-parallel group: gathered K / V + offset kernel
+# ---------------------------------------------------------------------------
+class _CpAttentionFn(torch.autograd.Function):
+    """Each rank holds one contiguous slice of the sequence. K and V of all ranks are
+    all-gathered (a few hundred MB at 131072 tokens with 4 KV heads), the tcgen05 kernel runs
+    the local queries against the gathered prefix with the rank's offset, and the key / value
+    gradients go back to their owners with a reduce-scatter."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, group):
+        import torch.distributed as dist
+
+        from ..ops.attention import _AttnCpFn
+
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        b, s, hkv, d = k.shape
+        kg = torch.empty((world, b, s, hkv, d), dtype=k.dtype, device=k.device)
+        vg = torch.empty_like(kg)
+        dist.all_gather_into_tensor(kg, k.contiguous(), group=group)
+        dist.all_gather_into_tensor(vg, v.contiguous(), group=group)
+        kf = kg.permute(1, 0, 2, 3, 4).reshape(b, world * s, hkv, d)
+        vf = vg.permute(1, 0, 2, 3, 4).reshape(b, world * s, hkv, d)
+        ctx.group, ctx.world, ctx.shape = group, world, (b, s, hkv, d)
+        with torch.enable_grad():
+            ql, kl, vl = q.detach().requires_grad_(), kf.detach().requires_grad_(), vf.detach().requires_grad_()
+            out = _AttnCpFn.apply(ql, kl, vl, rank * s, 1.0 / math.sqrt(d))
+        ctx.inner = (ql, kl, vl, out)
+        return out.detach()
+
+    @staticmethod
+    def backward(ctx, d_out):
+        import torch.distributed as dist
+
+        ql, kl, vl, out = ctx.inner
+        dq, dkf, dvf = torch.autograd.grad(out, (ql, kl, vl), d_out)
+        b, s, hkv, d = ctx.shape
+        w = ctx.world
+        # [B, W*S, ...] -> [W, B, S, ...] so that chunk r of the scatter is rank r's slice
+        dkg = dkf.reshape(b, w, s, hkv, d).permute(1, 0, 2, 3, 4).contiguous().float()
+        dvg = dvf.reshape(b, w, s, hkv, d).permute(1, 0, 2, 3, 4).contiguous().float()
+        dk = torch.empty((b, s, hkv, d), dtype=torch.float32, device=d_out.device)
+        dv = torch.empty_like(dk)
+        dist.reduce_scatter_tensor(dk, dkg, group=ctx.group)
+        dist.reduce_scatter_tensor(dv, dvg, group=ctx.group)
+        ctx.inner = None
+        return dq, dk.to(d_out.dtype), dv.to(d_out.dtype), None
+
+
+def cp_attention(q: Tensor, k: Tensor, v: Tensor, group=None) -> Tensor:
+    """Causal GQA attention for a sequence split contiguously over ``group`` (rank order =
+    sequence order). q ``(B, S_loc, Hq, 128)``, k / v ``(B, S_loc, Hkv, 128)`` bf16 on the GPU,
+    ``S_loc`` a multiple of 256."""
+    return _CpAttentionFn.apply(q, k, v, group)

@@ -334,9 +334,59 @@ def ag_gemm_main():
         print("AG_GEMM_OK")
 
 
+def cp_engine_main():
+    """A training step with every sequence split over the ranks (delta-state hand-off, gathered
+    K / V with the offset attention kernel) == the step of a single-GPU trainer on the whole
+    sequences: loss, gradient norm and the updated weights."""
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    from datetime import timedelta
+
+    dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=90))
+    from prometheus_b200 import engine, model, train
+    from prometheus_b200.ops import functional as ops
+
+    solo_groups = [dist.new_group([r]) for r in range(world)]
+    cfg = model.ModelConfig(
+        d_model=256, n_layers=4, n_dense=4, n_moe=0, n_linear_attn=3, n_mla=1, n_routed_experts=1,
+        n_shared_experts=0, top_k=1, expert_hidden=512, mtp_heads=0, core_block_layers=4,
+        recurrence_train_mean=1.0, recurrence_max=1, vocab_size=1024, max_context=2048, prelude_layers=0,
+        coda_layers=0, adapter_hidden=256, n_heads=2, d_head=128, n_kv_heads=1, softmax_kind="gqa",
+        softmax_every=4, delta_beta="sigmoid", chunk=64, dense_hidden=512)
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10)
+    params = model.init_params(cfg, 0)
+    S = 256 * world * 2
+    tokens = torch.randint(0, cfg.vocab_size, (2, S), generator=torch.Generator().manual_seed(3)).to(dev)
+    mask = torch.ones(2, S, device=dev)
+    mask[:, 5:9] = 0
+    ref = engine.Trainer(cfg, tcfg, params=params, device=dev, micro_batch=2, process_group=solo_groups[rank])
+    cp = engine.Trainer(cfg, tcfg, params=params, device=dev, micro_batch=2, context_parallel=True)
+    assert ref.world == 1 and cp.world == world and cp.cp
+    for step in range(2):
+        want = ref.step(tokens, mask)
+        got = cp.step(*cp.cp_slice(tokens, mask))
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        lw, lg = want["loss"].item(), got["loss"].item()
+        nw, ng = want["grad_norm"].item(), got["grad_norm"].item()
+        assert abs(lw - lg) < 2e-2 * abs(lw), f"rank {rank} step {step}: loss {lg} vs {lw}"
+        assert abs(nw - ng) < 6e-2 * nw, f"rank {rank} step {step}: grad norm {ng} vs {nw}"
+    a = model.flatten_params(ref.export_tree())
+    b = model.flatten_params(cp.export_tree())
+    start = model.flatten_params(params)
+    for name in ("layers.0.W_q", "layers.3.W_k", "layers.1.ffn_gate", "embed"):
+        da, db = (a[name] - start[name]).float().flatten(), (b[name] - start[name]).float().flatten()
+        cos = torch.nn.functional.cosine_similarity(da, db, dim=0).item()
+        assert cos > 0.9, f"{name}: update cosine {cos:.3f}"
+    dist.barrier()
+    if rank == 0:
+        print("CP_ENGINE_OK")
+
+
 if __name__ == "__main__":
     try:
-        {"ep": ep_main, "ep_engine": ep_engine_main, "cp_delta": cp_delta_main, "ag_gemm": ag_gemm_main}.get((sys.argv[1:] or [""])[0], main)()
+        {"ep": ep_main, "ep_engine": ep_engine_main, "cp_delta": cp_delta_main, "ag_gemm": ag_gemm_main, "cp_engine": cp_engine_main}.get((sys.argv[1:] or [""])[0], main)()
     except BaseException:
         import traceback
 

@@ -80,3 +80,37 @@ def test_attention_is_deterministic_and_matches_library_kernel():
     assert _rel(runs[0][0], o2) < 1e-2
     for mine, lib in zip(runs[0][1:], g2):
         assert _rel(mine, lib) < 2e-2
+
+
+@pytest.mark.parametrize("q_off,s_loc,s_kv", [(512, 256, 1024), (0, 512, 640), (768, 256, 1024)])
+def test_offset_attention_equals_a_slice_of_the_full_sequence(q_off, s_loc, s_kv):
+    """A query slice at a global offset against the whole prefix (the context-parallel case):
+    output and dq of the slice, and dk / dv of every key row (zero where nothing sees it)."""
+    from prometheus_b200.ops import attention
+
+    q, k, v = _rand(2, 1024, 4, 2, 11)
+    k, v = k[:, :s_kv].contiguous(), v[:, :s_kv].contiguous()
+    ql = q[:, q_off:q_off + s_loc].contiguous().requires_grad_()
+    kl, vl = k.clone().requires_grad_(), v.clone().requires_grad_()
+    out = attention.causal_gqa_offset(ql, kl, vl, q_off)
+    go = torch.randn_like(out)
+    dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), go)
+
+    s_all = max(s_kv, q_off + s_loc)
+    qf = torch.zeros(2, s_all, 4, 128, device="cuda")
+    qf[:, q_off:q_off + s_loc] = q[:, q_off:q_off + s_loc].float()
+    qf.requires_grad_()
+    kf = torch.zeros(2, s_all, 2, 128, device="cuda"); kf[:, :s_kv] = k.float(); kf.requires_grad_()
+    vf = torch.zeros(2, s_all, 2, 128, device="cuda"); vf[:, :s_kv] = v.float(); vf.requires_grad_()
+    ref = attention.causal_gqa_ref(qf, kf, vf)
+    gof = torch.zeros_like(ref)
+    gof[:, q_off:q_off + s_loc] = go.float()
+    rq, rk, rv = torch.autograd.grad(ref, (qf, kf, vf), gof)
+    assert _rel(out, ref[:, q_off:q_off + s_loc]) < 1e-2
+    assert _rel(dq, rq[:, q_off:q_off + s_loc]) < 2e-2
+    assert _rel(dk, rk[:, :s_kv]) < 2e-2 and _rel(dv, rv[:, :s_kv]) < 2e-2
+    unseen = q_off + s_loc
+    if unseen < s_kv:
+        assert dk[:, unseen:].abs().max() == 0 and dv[:, unseen:].abs().max() == 0
+    with pytest.raises(ValueError):
+        attention.causal_gqa_offset(ql, kl, vl, q_off + 128)

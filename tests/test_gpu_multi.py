@@ -54,3 +54,8 @@ def test_two_rank_context_parallel_delta_rule():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_all_gather_gemm():
     _run_ranks(2, 29525, "AG_GEMM_OK", "ag_gemm")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_context_parallel_trainer():
+    _run_ranks(2, 29527, "CP_ENGINE_OK", "cp_engine")

@@ -82,3 +82,29 @@ def test_ci_checks(tmp_path):
     errs = ci_checks.check_skips(junit)
     assert len(errs) == 1 and "a::lazy" in errs[0] and ci_checks.main(["skips", str(junit)]) == 1
     assert ci_checks.main([]) == 2
+
+
+def test_run_loop_on_cpu_with_overrides_and_spike_rollback():
+    import io
+    import json
+
+    from prometheus_b200 import run
+
+    out = io.StringIO()
+    sets = ["batch=2", "seq_len=64", "n_docs=16", "vocab_size=512", "steps=4", "ckpt_every=2", "peak_lr=0.01"]
+    res = run.run("tiny_fp32", sets, device="cpu", out=out)
+    lines = [json.loads(l) for l in out.getvalue().splitlines()]
+    assert [l["step"] for l in lines[:-1]] == [1, 2, 3, 4] and lines[-1]["summary"]["steps"] == 4
+    assert res["summary"]["sequences_packed"] > 4 and res["summary"]["last_memory_checkpoint_step"] == 4
+    assert all(h["loss"] == h["loss"] for h in res["history"])
+    again = run.run("tiny_fp32", sets, device="cpu", out=io.StringIO())
+    assert [h["loss"] for h in again["history"]] == [h["loss"] for h in res["history"]]     # deterministic loader + init
+    with pytest.raises(ValueError):
+        run.run("tiny_fp32", ["nonsense=1"], device="cpu", out=io.StringIO())
+    with pytest.raises(ValueError):
+        run.run("huge", [], device="cpu")
+    cfg, tcfg, opts = run.apply_overrides(["fp8=true", "top_k=1", "softcap=20.0"], run.PRESETS["tiny_fp32"](),
+                                          __import__("prometheus_b200").train.train_config_for(run.PRESETS["tiny_fp32"]()),
+                                          run.RunOptions())
+    assert opts.fp8 is True and cfg.top_k == 1 and tcfg.softcap == 20.0
+    assert set(run.PRESETS) == {"tiny_fp32", "dense_1p3b", "moe_16b", "long_context", "latent"}
