@@ -47,6 +47,9 @@ def parse_args():
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (invalid as a result)")
+    ap.add_argument("--grad-sync", default="auto", choices=["auto", "p2p", "nccl"],
+                    help="gradient path at N > 1: peer-memory reduce-to-owner + update-broadcast kernels "
+                         "(auto / p2p, the product) or NCCL collectives only (the baseline)")
     ap.add_argument("--config", default="dense", choices=["dense", "latent", "moe16b"],
                     help="dense: the headline 1.3B hybrid (default). latent: the same model with 1024-token "
                          "prefix + 8 latent slots + 512-token answer, 4 Jacobi sweeps, 8 sequences per GPU. "
@@ -175,7 +178,8 @@ def main() -> int:
                                    core_block_layers=args.layers)
     tcfg = train.train_config_for(cfg, warmup_steps=100, stable_steps=10_000, decay_steps=1000)
     torch.manual_seed(1234)
-    tr = engine.Trainer(cfg, tcfg, seed=0, device=dev, micro_batch=args.micro_batch, **trainer_kw)
+    tr = engine.Trainer(cfg, tcfg, seed=0, device=dev, micro_batch=args.micro_batch,
+                        grad_sync=args.grad_sync, **trainer_kw)
     step_kw = {}
     if args.config == "latent":
         tr.set_latent_slots(1024, 8, 4)
@@ -246,7 +250,7 @@ def main() -> int:
                 "global_batch": B * world, "seq_len": S,
                 "parallelism": (f"dp{world}" + ("+ep" + str(world) if args.config == "moe16b" else ""))
                 if world > 1 else "single",
-                "micro_batch": args.micro_batch,
+                "micro_batch": args.micro_batch, "grad_sync": args.grad_sync,
                 "l2": "per-step working set (3.5 GB bf16 weights + activations) exceeds the 126 MB L2",
             },
             "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"),
