@@ -173,7 +173,8 @@ def main() -> int:
         trainer_kw = dict(fp8=True, expert_parallel=world > 1)
         model_name = "moe-16B (28L d2048, 64 routed top-6 + 2 shared experts h1408, FP8 e4m3 block-scaled linears)"
     if args.layers:
-        cfg = model.with_overrides(cfg, n_layers=args.layers, n_dense=args.layers,
+        n_dense = 1 if args.config == "moe16b" else args.layers
+        cfg = model.with_overrides(cfg, n_layers=args.layers, n_dense=n_dense, n_moe=args.layers - n_dense,
                                    n_linear_attn=args.layers * 3 // 4, n_mla=args.layers // 4,
                                    core_block_layers=args.layers)
     tcfg = train.train_config_for(cfg, warmup_steps=100, stable_steps=10_000, decay_steps=1000)

@@ -37,6 +37,7 @@ from .ops._lib import call, ptr, stream_ptr
 
 Tensor = torch.Tensor
 BF16 = torch.bfloat16
+LAZY_INIT_PARAMS = 3_000_000_000      # above this many parameters the host never holds the model
 
 
 @dataclass
@@ -136,8 +137,12 @@ class Trainer:
         self.router_bias_rate = 1e-3
         self.last_router = None
         _lib.load()
+        self.seed = int(seed)
         if params is None:
-            params = M.init_params(model_config, seed)
+            # Large models are never materialised on the host: the trainer plans from shapes and
+            # draws each of its own weights on the device (an expert-parallel rank only its experts).
+            shapes = M.init_params(model_config, seed, shapes_only=True)
+            params = shapes if M.param_count(shapes) > LAZY_INIT_PARAMS else M.init_params(model_config, seed)
         self._plan(params)
         self._allocate()
         self.load_tree(params)
@@ -374,7 +379,15 @@ class Trainer:
             for w in self.weights.values():
                 dst = self.p[w.name].master
                 for tree_name, r0, rows, how, _ in w.sources:
-                    src = self._to_engine(flat[tree_name].detach().float(), how)
+                    leaf = flat[tree_name]
+                    if not leaf.is_meta:
+                        src = self._to_engine(leaf.detach().float(), how)
+                    elif isinstance(how, tuple):     # shapes-only tree: draw just this expert
+                        src = _t2(M.init_leaf(self.cfg, f"{tree_name}.{how[1]}", leaf.shape[1:], self.seed,
+                                              self.device))
+                    else:
+                        src = self._to_engine(M.init_leaf(self.cfg, tree_name, leaf.shape, self.seed,
+                                                          self.device), how)
                     dst[r0:r0 + rows].copy_(src.to(self.device))
             self.muon_lp.copy_(self.muon_master)
             self.adam_lp.copy_(self.adam_master)
@@ -384,7 +397,7 @@ class Trainer:
                 if self.cfg.router_bias:
                     b = flat.get(name)
                     self.router_bias[i] = (torch.zeros(self.cfg.n_routed_experts)
-                                           if b is None else b.detach().float().clone()).to(self.device)
+                                           if b is None or b.is_meta else b.detach().float().clone()).to(self.device)
         if self.sym is not None:
             torch.cuda.synchronize()
             torch.distributed.barrier(self.pg)

@@ -665,11 +665,14 @@ def _generator(rng: Any) -> torch.Generator:
     return g
 
 
-def init_params(config: ModelConfig, rng: Any, *, device=None, dtype=torch.float32) -> dict:
+def init_params(config: ModelConfig, rng: Any, *, device=None, dtype=torch.float32,
+                shapes_only: bool = False) -> dict:
     """Parameter tree with the reference's names. Matrices ~ N(0, init_scale^2) (hidden
-    matrices scaled by sqrt(mup_base_width / d_model) when muP is on), norms = 1."""
+    matrices scaled by sqrt(mup_base_width / d_model) when muP is on), norms = 1.
+    ``shapes_only`` returns the same tree of meta tensors (no memory, no random numbers): the
+    layout a trainer plans from before it initialises its own shards with ``init_leaf``."""
     validate_config(config)
-    gen = _generator(rng)
+    gen = None if shapes_only else _generator(rng)
     d = config.d_model
     n_heads, d_head, n_kv = head_geometry(config)
     _, _, d_nope, d_rope = _attn_geometry(d)
@@ -686,10 +689,14 @@ def init_params(config: ModelConfig, rng: Any, *, device=None, dtype=torch.float
         hid_std = std * math.sqrt(float(config.mup_base_width) / float(d))
 
     def w(shape, s=None) -> Tensor:
+        if shapes_only:
+            return torch.empty(shape, dtype=dtype, device="meta")
         t = torch.randn(shape, generator=gen, dtype=torch.float32) * (hid_std if s is None else s)
         return t.to(device=device, dtype=dtype)
 
     def ones(n) -> Tensor:
+        if shapes_only:
+            return torch.empty((n,), dtype=dtype, device="meta")
         return torch.ones((n,), dtype=dtype, device=device)
 
     layers = []
@@ -722,7 +729,7 @@ def init_params(config: ModelConfig, rng: Any, *, device=None, dtype=torch.float
             n_r, n_s = config.n_routed_experts, config.n_shared_experts
             layer["router"] = w((d, n_r))
             if config.router_bias:
-                layer["router_bias"] = torch.zeros((n_r,), dtype=dtype, device=device)
+                layer["router_bias"] = torch.zeros((n_r,), dtype=dtype, device="meta" if shapes_only else device)
             layer["routed_gate"] = w((n_r, d, hidden))
             layer["routed_up"] = w((n_r, d, hidden))
             layer["routed_down"] = w((n_r, hidden, d))
@@ -743,6 +750,28 @@ def init_params(config: ModelConfig, rng: Any, *, device=None, dtype=torch.float
         "adapter_w2": w((adapter_h, d)),
         "adapter_norm": ones(d),
     }
+
+
+def init_leaf(config: ModelConfig, name: str, shape, seed: int, device) -> Tensor:
+    """One leaf of the parameter tree, initialised on ``device`` from a generator keyed by
+    ``(seed, name)``: norms are ones, ``router_bias`` zeros, embeddings N(0, init_scale^2), every
+    other matrix N(0, (init_scale * sqrt(mup_base_width / d_model))^2). Same distribution as
+    ``init_params`` (not the same numbers: that one draws every leaf from a single CPU stream);
+    used for models too large to initialise on the host and for expert-parallel ranks, which only
+    create the experts they own."""
+    import zlib
+
+    leaf = name.rsplit(".", 1)[-1]
+    if leaf.endswith("norm"):
+        return torch.ones(tuple(shape), dtype=torch.float32, device=device)
+    if leaf == "router_bias":
+        return torch.zeros(tuple(shape), dtype=torch.float32, device=device)
+    std = float(config.init_scale)
+    if leaf not in ("embed", "unembed") and config.mup_base_width is not None:
+        std *= math.sqrt(float(config.mup_base_width) / float(config.d_model))
+    gen = torch.Generator(device=device)
+    gen.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) % (2 ** 63))
+    return torch.randn(tuple(shape), generator=gen, dtype=torch.float32, device=device) * std
 
 
 def param_count(params: Any) -> int:

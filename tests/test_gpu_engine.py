@@ -179,3 +179,29 @@ def test_fp8_forward_option_trains_dense_and_moe():
         assert losses[-1] < losses[0] - 0.3, losses
     from prometheus_b200.ops import functional as ops
     ops.check_status("cuda")
+
+
+def test_device_side_initialisation_of_large_models(monkeypatch):
+    """Above the host-initialisation limit the trainer plans from shapes and draws its weights on
+    the device: the statistics are those of init_params, runs are reproducible, training works."""
+    from prometheus_b200 import engine, model, train
+
+    monkeypatch.setattr(engine, "LAZY_INIT_PARAMS", 0)
+    cfg = small_moe()
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10)
+    tr = engine.Trainer(cfg, tcfg, seed=5, micro_batch=2)
+    tree = model.flatten_params(tr.export_tree())
+    ref = model.flatten_params(model.init_params(cfg, 5))
+    assert set(tree) == set(ref)
+    for name in ("layers.0.W_q", "layers.1.routed_gate", "embed", "layers.2.router"):
+        assert tree[name].shape == ref[name].shape
+        assert abs(tree[name].float().std().item() / ref[name].float().std().item() - 1) < 0.1, name
+    assert torch.all(tree["final_norm"] == 1) and torch.all(tree["layers.1.router_bias"] == 0)
+    e0, e1 = tree["layers.1.routed_gate"][0], tree["layers.1.routed_gate"][1]
+    assert not torch.equal(e0, e1)                                   # every expert has its own stream
+    again = model.flatten_params(engine.Trainer(cfg, tcfg, seed=5, micro_batch=2).export_tree())
+    assert all(torch.equal(tree[k], again[k]) for k in tree)
+    tokens = torch.randint(0, cfg.vocab_size, (4, 128), device="cuda",
+                           generator=torch.Generator(device="cuda").manual_seed(0))
+    losses = [tr.step(tokens)["loss"].item() for _ in range(8)]
+    assert losses[-1] < losses[0] - 0.2, losses
