@@ -933,7 +933,11 @@ class _SmallLinear(torch.autograd.Function):
         mg = getattr(ctx.w_ref, "main_grad", None)
         dw = None
         if mg is not None:
-            mg.addmm_(dy.float().t(), x.float())
+            # bf16 operands, fp32 accumulation and output: no fp32 copy of the activations
+            try:
+                mg.add_(torch.mm(dy.t().contiguous(), x, out_dtype=torch.float32))
+            except (TypeError, RuntimeError, NotImplementedError):
+                mg.addmm_(dy.float().t(), x.float())
         else:
             dw = dy.t() @ x
         return dy @ w, dw
