@@ -73,7 +73,7 @@ __device__ __forceinline__ void sync_rows() { asm volatile("bar.sync 1, 128;" ::
 // Warp-uniform bounded wait: the row warps run warp-collective tensor-memory loads, so either
 // every lane goes on or none does.
 __device__ __forceinline__ bool wait_all(uint64_t* bar, uint32_t parity, int* status) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, status));
+  return __all_sync(0xffffffffu, mbar_wait_spin(bar, parity, status));
 }
 
 // ------------------------------------------------------------------------------ forward
@@ -173,12 +173,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t p_lo0 = sdesc_lo(smem_u32(smem + P_OFF + t * 32768), 16);
       const uint32_t kv0 = smem_u32(smem + KV_OFF);
       const uint32_t d_o = tmem + COL_O + t * 128;
-      bool ok = mbar_wait(q_full, 0, p.status);
+      bool ok = mbar_wait_spin(q_full, 0, p.status);
       auto issue_s = [&](int j) -> bool {
         const int s = j % KV_STAGES;
         const int sb = t * 2 + (j & 1);
-        if (!mbar_wait(&kv_full[s], (j / KV_STAGES) & 1, p.status)) return false;
-        if (!mbar_wait(&s_free[sb], ((j >> 1) & 1) ^ 1, p.status)) return false;
+        if (!mbar_wait_spin(&kv_full[s], (j / KV_STAGES) & 1, p.status)) return false;
+        if (!mbar_wait_spin(&s_free[sb], ((j >> 1) & 1) ^ 1, p.status)) return false;
         tc_fence_after();
         const uint32_t k_lo = sdesc_lo(kv0 + s * KV_STAGE, 16);
         const uint32_t d = tmem + COL_S + sb * 64;
@@ -195,7 +195,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok && nj > 1) ok = issue_s(1);
       for (int j = 0; j < nj && ok; ++j) {
         const int s = j % KV_STAGES;
-        if (!mbar_wait(&p_ready[t], j & 1, p.status)) break;
+        if (!mbar_wait_spin(&p_ready[t], j & 1, p.status)) break;
         tc_fence_after();
         const uint32_t v_lo = sdesc_lo(kv0 + s * KV_STAGE + 16384, 8192);
         const uint32_t p_lo = p_lo0 + (((j & 1) * 16384) >> 4);
@@ -457,12 +457,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
       const uint32_t r_lo = sdesc_lo(smem_u32(smem + (which == 0 ? RA_OFF : RB_OFF)), 16);
       const uint32_t st0 = smem_u32(smem + ST_OFF + which * 16384);
       const uint32_t col = which == 0 ? COL_X1 : COL_X2;
-      bool ok = mbar_wait(r_full, 0, p.status);
+      bool ok = mbar_wait_spin(r_full, 0, p.status);
       for (int it = 0; it < n_it && ok; ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&t_full[s], ph, p.status)) break;
-        if (!mbar_wait(&x_free[s], ph ^ 1, p.status)) break;
+        if (!mbar_wait_spin(&t_full[s], ph, p.status)) break;
+        if (!mbar_wait_spin(&x_free[s], ph ^ 1, p.status)) break;
         tc_fence_after();
         const uint32_t t_lo = sdesc_lo(st0 + s * 32768, 16);
         const uint32_t d = tmem + col + s * 64;
@@ -485,7 +485,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
       for (; it < n_it; ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&pd_ready[s], ph, p.status)) break;
+        if (!mbar_wait_spin(&pd_ready[s], ph, p.status)) break;
         tc_fence_after();
         // the streamed tiles again, now as MN-major B operands (64-wide chunks 8 KB apart)
         const uint32_t t1_mn = sdesc_lo(st0 + s * 32768, 8192), t2_mn = t1_mn + (16384 >> 4);

@@ -154,6 +154,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return false;
 }
 
+// Same contract with the non-blocking probe: test_wait returns at once, so a waiter notices
+// the phase flip within a few cycles instead of after try_wait's suspend slice. For the short
+// dependent hops of a latency chain (softmax rows <-> MMA issue); keep try_wait where the wait
+// is long and the warp should stay out of the issue slots.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+#ifndef PB_MBAR_TEST_LIMIT
+#define PB_MBAR_TEST_LIMIT (1u << 27)
+#endif
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* status) {
+  for (uint32_t it = 0; it < PB_MBAR_TEST_LIMIT; ++it) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((it & 0xFFFFu) == 0xFFFFu && status != nullptr &&
+        *reinterpret_cast<volatile int*>(status) != PB_OK)
+      return false;
+  }
+  if (status != nullptr) atomicCAS(status, PB_OK, PB_TIMEOUT_MBAR);
+  return false;
+}
+
 // ---------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies), no cluster multicast anywhere
 // ---------------------------------------------------------------------------

@@ -137,7 +137,7 @@ delta_prep_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         umma_commit(mma1);
       }
     }
-    ok = mbar_wait(mma1, ph, p.status) && ok;
+    ok = mbar_wait_spin(mma1, ph, p.status) && ok;
     if (!__syncthreads_and(ok)) break;
     tc_fence_after();
 
@@ -207,7 +207,7 @@ delta_prep_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       tma_store_3d(&tmAP, smem + AP, 0, g * C, 0);
       tma_store_commit();
     }
-    ok = mbar_wait(mma2, ph, p.status);
+    ok = mbar_wait_spin(mma2, ph, p.status);
     if (!__syncthreads_and(ok)) break;
     tc_fence_after();
     // W -> K tile, U^ -> V tile (both products have finished reading them), then out
@@ -392,7 +392,7 @@ delta_prep_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         umma_commit(&mma[0]);
       }
     }
-    ok = mbar_wait(&mma[0], ph, p.status) && ok;
+    ok = mbar_wait_spin(&mma[0], ph, p.status) && ok;
     if (!__syncthreads_and(ok)) break;
     tc_fence_after();
     if (r == 0) {   // V is consumed: bring Q into its place
@@ -445,7 +445,7 @@ delta_prep_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       for (int j = 0; j < 4; ++j) umma_f16(tmem + 128, mn(ap, j), mn(dw, j), id_mm, j > 0);
       umma_commit(&mma[1]);
     }
-    ok = mbar_wait(&mma[1], ph, p.status);
+    ok = mbar_wait_spin(&mma[1], ph, p.status);
     if (!__syncthreads_and(ok)) break;
     tc_fence_after();
     float dbeta = 0.f;
@@ -471,7 +471,7 @@ delta_prep_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       for (int j = 0; j < 8; ++j) umma_f16(tmem + 64, k128(kt, j), k128(kt, j), id_kk64, j > 0);
       umma_commit(&mma[2]);
     }
-    ok = mbar_wait(&mma[2], ph, p.status);
+    ok = mbar_wait_spin(&mma[2], ph, p.status);
     if (!__syncthreads_and(ok)) break;
     tc_fence_after();
 #pragma unroll 1
@@ -514,7 +514,7 @@ delta_prep_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       }
       tma_store_wait_read<0>();   // dV has left the tile dK is staged in
     }
-    ok = mbar_wait(&mma[3], ph, p.status) && ok;
+    ok = mbar_wait_spin(&mma[3], ph, p.status) && ok;
     if (!__syncthreads_and(ok)) break;
     tc_fence_after();
     {

@@ -153,7 +153,7 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const uint32_t ph = (it >> 1) & 1, cph = it & 1;
         const uint32_t st = smem_u32(smem + s * S::STAGE);
         if (!mbar_wait(&full[s], ph, p.status)) break;
-        if (!mbar_wait(x_ready, cph, p.status)) break;
+        if (!mbar_wait_spin(x_ready, cph, p.status)) break;
         tc_fence_after();
         if (!BWD) {
           // Y = W X ; O = Q X
@@ -186,7 +186,7 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             umma_f16(tmem + COL_X, make_sdesc_sw128(st + TILE_Q + j * 2048, 8192, 1024),
                      make_sdesc_sw128(st + TILE_DO + j * 2048, 8192, 1024), id_nn, 1);
         }
-        if (!mbar_wait(u_ready, cph, p.status)) break;
+        if (!mbar_wait_spin(u_ready, cph, p.status)) break;
         tc_fence_after();
         if (!BWD) {
           // O += M U ; X += K^T U
@@ -255,7 +255,7 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const uint32_t cph = it & 1;
       const int g = seq * N + n;
       if (it > 0) {
-        if (!mbar_wait(o_done, cph ^ 1, p.status)) { ok = false; break; }
+        if (!mbar_wait_spin(o_done, cph ^ 1, p.status)) { ok = false; break; }
         tc_fence_after();
       }
       // all earlier bulk stores have finished reading xb / ub / ob before they are rewritten
@@ -293,7 +293,7 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         tma_store_3d(&tmXB, xb + 16384, 64, g * D, 0);
         tma_store_commit();
       }
-      if (!mbar_wait(y_done, cph, p.status)) { ok = false; break; }
+      if (!mbar_wait_spin(y_done, cph, p.status)) { ok = false; break; }
       tc_fence_after();
       if (r < C) {
         const uint8_t* uh = smem + (it & 1) * S::STAGE + TILE_DO;
@@ -338,7 +338,7 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     // drain: last chunk's output rows and the final state
     if (ok && N > 0) {
-      if (mbar_wait(o_done, (N - 1) & 1, p.status)) {
+      if (mbar_wait_spin(o_done, (N - 1) & 1, p.status)) {
         tc_fence_after();
         if (r == 0) tma_store_wait_read<0>();
         sync_rows();
