@@ -174,3 +174,29 @@ def migrate(payload: Mapping[str, Any], to_version: int) -> dict:
     if v == to_version:
         return copy.deepcopy(dict(payload))
     raise MigrationError(f"no migration from v{v} to v{to_version}")
+
+
+def generate_python(out_dir) -> None:
+    """Write pydantic models for every schema under ``out_dir`` (``types.py`` + ``__init__.py``);
+    reference ``contracts/__init__.py:250-257``."""
+    from .codegen import write_python
+
+    write_python(Path(out_dir))
+
+
+def generate_cpp(out_dir) -> None:
+    """Write ``contracts_types.hpp`` (structs with ``from_json`` / ``to_json`` over the native JSON
+    value) under ``out_dir``. The reference emits serde types for its Rust crates at this point
+    (``contracts/__init__.py:260-265``); the native layer here is C++."""
+    from .codegen import write_cpp
+
+    write_cpp(Path(out_dir))
+
+
+generate_native = generate_cpp
+
+
+def generate_all() -> None:
+    """Python types under ``contracts/generated``, the C++ header under ``csrc/native/generated``."""
+    generate_python(CONTRACTS_ROOT / "generated")
+    generate_cpp(CONTRACTS_ROOT.parent.parent / "csrc" / "native" / "generated")

@@ -115,6 +115,10 @@ def run_v1(*, gpus: int = 1) -> dict:
         finally:
             kernels.chunked_delta_rule = orig
     diff = float((ref - alt).abs().max())
+    # and against the NumPy float64 restatement that shares no code with the model
+    from .independent_forward import forward_logits
+
+    indep = float(abs(ref.numpy() - forward_logits(b.tokens, params, cfg, r=1)).max())
     # gradient check: central finite difference of the loss along one direction
     tcfg = train.train_config_for(cfg, warmup_steps=1, stable_steps=50, decay_steps=5)
     p = train._map_tree(params, lambda _n, t: t.clone().requires_grad_(True))
@@ -136,7 +140,7 @@ def run_v1(*, gpus: int = 1) -> dict:
     numeric = (shifted(+1) - shifted(-1)) / (2 * eps)
     grad_ok = abs(numeric - analytic) <= 5e-2 * max(1.0, abs(analytic))
     _, _, losses = _train(cfg, tcfg, params, [b] * 12)
-    result = {"logits_max_diff": diff, "grad_ok": bool(grad_ok), "overfit_ok": bool(losses[-1] < losses[0] - 0.3),
+    result = {"logits_max_diff": max(diff, indep), "recurrence_max_diff": diff, "independent_max_diff": indep, "grad_ok": bool(grad_ok), "overfit_ok": bool(losses[-1] < losses[0] - 0.3),
               "gpus": int(gpus), "grad_numeric": numeric, "grad_analytic": analytic, "losses": losses}
     if torch.cuda.is_available():
         from .. import engine

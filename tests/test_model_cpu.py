@@ -119,3 +119,22 @@ def test_gqa_attention_matches_sdpa():
         q.transpose(1, 2), k.repeat_interleave(2, 2).transpose(1, 2),
         v.repeat_interleave(2, 2).transpose(1, 2), is_causal=True).transpose(1, 2)
     torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-5)
+
+
+def test_forward_matches_the_independent_numpy_restatement():
+    """model.forward against the float64 per-token / per-head / per-expert statement of the same
+    definitions (reference: prometheus/verify/_torch_forward.py is the V1 oracle of its model)."""
+    import numpy as np
+
+    from prometheus_b200.verify.independent_forward import forward_logits
+
+    cases = [model.tiny_config(),                                   # delta + MLA, dense + MoE, recurrence
+             model.with_overrides(model.tiny_config(), softmax_kind="gqa", n_kv_heads=2)]
+    for cfg in cases:
+        params = model.init_params(cfg, 0)
+        tok = torch.randint(0, cfg.vocab_size, (2, 20), generator=torch.Generator().manual_seed(3))
+        for r in (1, 2):
+            with torch.no_grad():
+                got = model.forward(tok, params, cfg, r=r).logits.numpy()
+            want = forward_logits(tok, params, cfg, r=r)
+            assert np.abs(got - want).max() < 2e-5, (cfg.softmax_kind, r)
