@@ -428,11 +428,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
   if (warp == 11) {
     if (lane == 0) {
       const int rx = (DKV ? g : hy) * D;
-      mbar_arrive_expect_tx(r_full, 65536);
-      tma_load_3d(smem + RA_OFF, &tmRA, r_full, rx, row0, 0);
-      tma_load_3d(smem + RA_OFF + 16384, &tmRA, r_full, rx + 64, row0, 0);
-      tma_load_3d(smem + RB_OFF, &tmRB, r_full, rx, row0, 0);
-      tma_load_3d(smem + RB_OFF + 16384, &tmRB, r_full, rx + 64, row0, 0);
+      // A key block that no local query sees streams nothing: its resident tiles are not
+      // loaded either, because their buffers are the staging of the all-zero stores and no one
+      // would wait for the loads to land first.
+      if (n_it > 0) {
+        mbar_arrive_expect_tx(r_full, 65536);
+        tma_load_3d(smem + RA_OFF, &tmRA, r_full, rx, row0, 0);
+        tma_load_3d(smem + RA_OFF + 16384, &tmRA, r_full, rx + 64, row0, 0);
+        tma_load_3d(smem + RB_OFF, &tmRB, r_full, rx, row0, 0);
+        tma_load_3d(smem + RB_OFF + 16384, &tmRB, r_full, rx + 64, row0, 0);
+      }
       for (int it = 0; it < n_it; ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
@@ -457,7 +462,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmRA, const __grid_constant_
       const uint32_t r_lo = sdesc_lo(smem_u32(smem + (which == 0 ? RA_OFF : RB_OFF)), 16);
       const uint32_t st0 = smem_u32(smem + ST_OFF + which * 16384);
       const uint32_t col = which == 0 ? COL_X1 : COL_X2;
-      bool ok = mbar_wait_spin(r_full, 0, p.status);
+      bool ok = n_it == 0 || mbar_wait_spin(r_full, 0, p.status);
       for (int it = 0; it < n_it && ok; ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;

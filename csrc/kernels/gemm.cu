@@ -70,6 +70,173 @@ struct GemmSmem {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
+// One warp's share of a finished accumulator: 32 rows (tensor-memory lanes of `t_addr`) x BN
+// columns, scaled, D added, converted and stored. `y0` is the matrix row of lane 0, `n0` the
+// first column, `my_epi_base` the warp's 8 KB staging area for the TMA-store path.
+template <int BN>
+__device__ __forceinline__ void epilogue_rows(const GemmParams& p, const CUtensorMap* tmC,
+                                              uint32_t t_addr, uint8_t* my_epi_base, int b, int y0,
+                                              int n0, int lane) {
+  const int row = y0 + lane;
+  const bool row_ok = row < p.M;
+  const size_t c_off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
+  const size_t d_off = static_cast<size_t>(b) * p.strideD + static_cast<size_t>(row) * p.ldd;
+  if (p.tma_store) {
+    // Stage 32 rows x 128 bytes per warp in the TMA swizzle layout, then one bulk
+    // tensor store per slab: coalesced, asynchronous, clipped at the matrix edge.
+    uint8_t* my_epi = my_epi_base;
+    const int cols_per_slab = p.out_f32 ? 32 : 64;
+#pragma unroll 1
+    for (int sl = 0; sl * cols_per_slab < BN; ++sl) {
+      const int x0 = n0 + sl * cols_per_slab;
+      uint8_t* buf = my_epi + (sl & 1) * 4096;
+      if (lane == 0) tma_store_wait_read<1>();
+      __syncwarp();
+#pragma unroll 1
+      for (int hf = 0; hf * 32 < cols_per_slab; ++hf) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + sl * cols_per_slab + hf * 32, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        const int col0 = x0 + hf * 32;
+        if (p.D != nullptr && row_ok && col0 < p.N) {
+          const bool full_chunk = (col0 + 32 <= p.N);
+          if (p.d_f32) {
+            const float* dp = static_cast<const float*>(p.D) + d_off + col0;
+            if (full_chunk && (p.ldd % 4 == 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 d4 = reinterpret_cast<const float4*>(dp)[i];
+                v[4 * i] += p.beta * d4.x; v[4 * i + 1] += p.beta * d4.y;
+                v[4 * i + 2] += p.beta * d4.z; v[4 * i + 3] += p.beta * d4.w;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) v[i] += p.beta * dp[i];
+            }
+          } else {
+            const bf16* dp = static_cast<const bf16*>(p.D) + d_off + col0;
+            if (full_chunk && (p.ldd % 8 == 0)) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                float f[8];
+                unpack8(reinterpret_cast<const bf16x8*>(dp)[i], f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[8 * i + j] += p.beta * f[j];
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) v[i] += p.beta * bf16_to_f32(dp[i]);
+            }
+          }
+        }
+        uint8_t* rowp = buf + lane * 128;
+        if (p.out_f32) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(rowp + ((i ^ (lane & 7)) << 4)) =
+                make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            bf16x8 pk;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              pk.v[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+            *reinterpret_cast<bf16x8*>(rowp + (((hf * 4 + i) ^ (lane & 7)) << 4)) = pk;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && x0 < p.N && y0 < p.M && !(p.debug & 2)) {
+        tma_store_3d(tmC, buf, x0, y0, b);
+      }
+      if (lane == 0) tma_store_commit();
+    }
+  } else
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 32) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_addr + c, r);
+    tmem_ld_wait();
+    const int col0 = n0 + c;
+    if (row_ok && col0 < p.N && !(p.debug & 2)) {
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+      const bool full_chunk = (col0 + 32 <= p.N);
+      // All indexing below is compile-time so v stays in registers; ragged
+      // edges use the same unrolled loops with a per-element predicate.
+      if (p.D != nullptr) {
+        if (p.d_f32) {
+          const float* dp = static_cast<const float*>(p.D) + d_off + col0;
+          if (full_chunk && (p.ldd % 4 == 0)) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 d4 = reinterpret_cast<const float4*>(dp)[i];
+              v[4 * i] += p.beta * d4.x; v[4 * i + 1] += p.beta * d4.y;
+              v[4 * i + 2] += p.beta * d4.z; v[4 * i + 3] += p.beta * d4.w;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += p.beta * dp[i];
+          }
+        } else {
+          const bf16* dp = static_cast<const bf16*>(p.D) + d_off + col0;
+          if (full_chunk && (p.ldd % 8 == 0)) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float f[8];
+              unpack8(reinterpret_cast<const bf16x8*>(dp)[i], f);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[8 * i + j] += p.beta * f[j];
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += p.beta * bf16_to_f32(dp[i]);
+          }
+        }
+      }
+      if (p.out_f32) {
+        float* cp = static_cast<float*>(p.C) + c_off + col0;
+        if (full_chunk && (p.ldc % 4 == 0)) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            reinterpret_cast<float4*>(cp)[i] =
+                make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N) cp[i] = v[i];
+        }
+      } else {
+        bf16* cp = static_cast<bf16*>(p.C) + c_off + col0;
+        if (full_chunk && (p.ldc % 8 == 0)) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            bf16x8 pk;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              pk.v[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+            reinterpret_cast<bf16x8*>(cp)[i] = pk;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N) cp[i] = f32_to_bf16(v[i]);
+        }
+      }
+    }
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(256, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -278,7 +445,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int b, m_blk, n_blk;
       tile_coords(t, b, m_blk, n_blk);
-      const int row = m_blk * BM + q * 32 + lane;
       const int n0 = n_blk * BN;
       {
         int b_a, b_b, k_base, nkb;
@@ -287,164 +453,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait(&tfull[acc], acc_ph, p.status)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      const bool row_ok = row < p.M;
-      const size_t c_off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
-      const size_t d_off = static_cast<size_t>(b) * p.strideD + static_cast<size_t>(row) * p.ldd;
-      if (p.tma_store) {
-        // Stage 32 rows x 128 bytes per warp in the TMA swizzle layout, then one bulk
-        // tensor store per slab: coalesced, asynchronous, clipped at the matrix edge.
-        uint8_t* my_epi = smEpi + (warp - 2) * 8192;
-        const int cols_per_slab = p.out_f32 ? 32 : 64;
-        const int y0 = m_blk * BM + q * 32;
-#pragma unroll 1
-        for (int sl = 0; sl * cols_per_slab < BN; ++sl) {
-          const int x0 = n0 + sl * cols_per_slab;
-          uint8_t* buf = my_epi + (sl & 1) * 4096;
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-#pragma unroll 1
-          for (int hf = 0; hf * 32 < cols_per_slab; ++hf) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(t_addr + sl * cols_per_slab + hf * 32, r);
-            tmem_ld_wait();
-            float v[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-            const int col0 = x0 + hf * 32;
-            if (p.D != nullptr && row_ok && col0 < p.N) {
-              const bool full_chunk = (col0 + 32 <= p.N);
-              if (p.d_f32) {
-                const float* dp = static_cast<const float*>(p.D) + d_off + col0;
-                if (full_chunk && (p.ldd % 4 == 0)) {
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    const float4 d4 = reinterpret_cast<const float4*>(dp)[i];
-                    v[4 * i] += p.beta * d4.x; v[4 * i + 1] += p.beta * d4.y;
-                    v[4 * i + 2] += p.beta * d4.z; v[4 * i + 3] += p.beta * d4.w;
-                  }
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 32; ++i)
-                    if (col0 + i < p.N) v[i] += p.beta * dp[i];
-                }
-              } else {
-                const bf16* dp = static_cast<const bf16*>(p.D) + d_off + col0;
-                if (full_chunk && (p.ldd % 8 == 0)) {
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    float f[8];
-                    unpack8(reinterpret_cast<const bf16x8*>(dp)[i], f);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) v[8 * i + j] += p.beta * f[j];
-                  }
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 32; ++i)
-                    if (col0 + i < p.N) v[i] += p.beta * bf16_to_f32(dp[i]);
-                }
-              }
-            }
-            uint8_t* rowp = buf + lane * 128;
-            if (p.out_f32) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                *reinterpret_cast<float4*>(rowp + ((i ^ (lane & 7)) << 4)) =
-                    make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                bf16x8 pk;
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  pk.v[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-                *reinterpret_cast<bf16x8*>(rowp + (((hf * 4 + i) ^ (lane & 7)) << 4)) = pk;
-              }
-            }
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0 && x0 < p.N && y0 < p.M && !(p.debug & 2)) {
-            tma_store_3d(&tmC, buf, x0, y0, b);
-          }
-          if (lane == 0) tma_store_commit();
-        }
-      } else
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_addr + c, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c;
-        if (row_ok && col0 < p.N && !(p.debug & 2)) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-          const bool full_chunk = (col0 + 32 <= p.N);
-          // All indexing below is compile-time so v stays in registers; ragged
-          // edges use the same unrolled loops with a per-element predicate.
-          if (p.D != nullptr) {
-            if (p.d_f32) {
-              const float* dp = static_cast<const float*>(p.D) + d_off + col0;
-              if (full_chunk && (p.ldd % 4 == 0)) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float4 d4 = reinterpret_cast<const float4*>(dp)[i];
-                  v[4 * i] += p.beta * d4.x; v[4 * i + 1] += p.beta * d4.y;
-                  v[4 * i + 2] += p.beta * d4.z; v[4 * i + 3] += p.beta * d4.w;
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) v[i] += p.beta * dp[i];
-              }
-            } else {
-              const bf16* dp = static_cast<const bf16*>(p.D) + d_off + col0;
-              if (full_chunk && (p.ldd % 8 == 0)) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  float f[8];
-                  unpack8(reinterpret_cast<const bf16x8*>(dp)[i], f);
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) v[8 * i + j] += p.beta * f[j];
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) v[i] += p.beta * bf16_to_f32(dp[i]);
-              }
-            }
-          }
-          if (p.out_f32) {
-            float* cp = static_cast<float*>(p.C) + c_off + col0;
-            if (full_chunk && (p.ldc % 4 == 0)) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                reinterpret_cast<float4*>(cp)[i] =
-                    make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col0 + i < p.N) cp[i] = v[i];
-            }
-          } else {
-            bf16* cp = static_cast<bf16*>(p.C) + c_off + col0;
-            if (full_chunk && (p.ldc % 8 == 0)) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                bf16x8 pk;
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  pk.v[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-                reinterpret_cast<bf16x8*>(cp)[i] = pk;
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col0 + i < p.N) cp[i] = f32_to_bf16(v[i]);
-            }
-          }
-        }
-      }
+      epilogue_rows<BN>(p, &tmC, t_addr, smEpi + (warp - 2) * 8192, b, m_blk * BM + q * 32, n0, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -461,6 +470,199 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant (plain and batched products only): a cluster of two CTAs on neighbouring SMs
+// computes one 256 x 256 tile with tcgen05.mma.cta_group::2. Each CTA loads its 128 rows of A and
+// its 128 of the tile's 256 rows of B, so a k-block costs each SM 32 KB of shared-memory reads
+// instead of 48 KB: the operand reads of the single-CTA 128 x 256 tile take three quarters of the
+// shared-memory bandwidth, and the epilogue's staging traffic competes for the rest.
+//   even CTA: warp 0 loads, warp 1 lane 0 issues the pair's MMAs, warps 2-5 drain rows 0..127
+//   odd CTA:  warp 0 loads (completions counted on the even CTA's barrier), warps 2-5 drain
+//             rows 128..255 from its own tensor memory
+// Barriers: full[s] lives in the even CTA (2 x stage bytes); empty[s] and tfull[a] exist in both
+// and are signalled by one tcgen05.commit to both CTAs; tempty[a] lives in the even CTA and
+// collects the eight epilogue warps of the pair. Loads carry no cluster multicast.
+// ---------------------------------------------------------------------------
+struct Gemm2Smem {
+  static constexpr int A_BYTES = 128 * BK * 2;
+  static constexpr int B_BYTES = 128 * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int EPI_BYTES = 4 * 2 * 4096;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  using S = Gemm2Smem;
+  constexpr int STAGES = S::STAGES;
+  constexpr int BN = 256, BM2 = 256;
+  extern __shared__ uint8_t smem_raw[];
+  // the dynamic shared-memory window starts at the same offset in both CTAs, so the aligned
+  // carve-up below is identical in the pair (the pair MMA addresses both by one descriptor)
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* smA = smem;
+  uint8_t* smB = smem + STAGES * S::A_BYTES;
+  uint8_t* smEpi = smem + STAGES * S::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES + S::EPI_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0: even CTA (issues the MMAs), 1: odd CTA
+  const long pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int num_m = (p.M + BM2 - 1) / BM2;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int tiles_per_batch = num_m * num_n;
+  const long total_tiles = static_cast<long>(tiles_per_batch) * p.batch;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 8);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    // Each CTA allocates all 512 columns of its own SM (one CTA per SM by shared-memory size), so
+    // both accumulators start at column 0 in either CTA and one address serves the pair's MMA.
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  cluster_sync_all();      // barriers of both CTAs initialised before any remote arrival
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](long t, int& b, int& m_blk, int& n_blk) {
+    b = static_cast<int>(t / tiles_per_batch);
+    const int r = static_cast<int>(t % tiles_per_batch);
+    const int group = 8 * num_n;
+    const int g = r / group;
+    const int first_m = g * 8;
+    const int gsz = min(num_m - first_m, 8);
+    m_blk = first_m + (r % group) % gsz;
+    n_blk = (r % group) / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (long t = pair; t < total_tiles && ok; t += n_pairs) {
+        int b, m_blk, n_blk;
+        tile_coords(t, b, m_blk, n_blk);
+        const int m0 = m_blk * BM2 + static_cast<int>(rank) * 128;
+        const int n0 = n_blk * BN + static_cast<int>(rank) * 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status)) { ok = false; break; }
+          if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * S::STAGE_BYTES);
+          const uint32_t bar = cluster_map(smem_u32(&full[s]), 0);
+          uint8_t* a_dst = smA + s * S::A_BYTES;
+          uint8_t* b_dst = smB + s * S::B_BYTES;
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_3d_pair(a_dst, &tmA, bar, k0, m0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              tma_load_3d_pair(a_dst + c * 8192, &tmA, bar, m0 + c * 64, k0, b);
+          }
+          if (!p.b_mn) {
+            tma_load_3d_pair(b_dst, &tmB, bar, k0, n0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              tma_load_3d_pair(b_dst + c * 8192, &tmB, bar, n0 + c * 64, k0, b);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA) ------------------------------
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc(1, 1, BM2, BN, p.a_mn ? 1u : 0u, p.b_mn ? 1u : 0u);
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (long t = pair; t < total_tiles && ok; t += n_pairs) {
+        if (!mbar_wait_cluster(&tempty[acc], acc_ph ^ 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[s], ph, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smA + s * S::A_BYTES);
+          const uint32_t b_addr = smem_u32(smB + s * S::B_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / 16; ++j) {
+            const uint64_t ad = p.a_mn ? make_sdesc_sw128(a_addr + j * 2048, 8192, 1024)
+                                       : make_sdesc_sw128(a_addr + j * 32, 16, 1024);
+            const uint64_t bd = p.b_mn ? make_sdesc_sw128(b_addr + j * 2048, 8192, 1024)
+                                       : make_sdesc_sw128(b_addr + j * 32, 16, 1024);
+            umma_f16_pair(d_tmem, ad, bd, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[s], 3);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tfull[acc], 3);
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    const uint32_t tempty0 = cluster_map(smem_u32(&tempty[0]), 0);
+    for (long t = pair; t < total_tiles; t += n_pairs) {
+      int b, m_blk, n_blk;
+      tile_coords(t, b, m_blk, n_blk);
+      if (!mbar_wait(&tfull[acc], acc_ph, p.status)) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      epilogue_rows<BN>(p, &tmC, t_addr, smEpi + (warp - 2) * 8192, b,
+                        m_blk * BM2 + static_cast<int>(rank) * 128 + q * 32, n_blk * BN, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty0 + acc * 8);
+      if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+
+  if (warp >= 2 && lane == 0) tma_store_wait<0>();
+  tc_fence_before();
+  __syncthreads();
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != PB_OK) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  // neither CTA leaves (or frees tensor memory) while its peer may still signal its barriers,
+  // read its operand tiles or write its accumulators
+  cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * BN);
@@ -541,13 +743,51 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
   return static_cast<int>(cudaGetLastError());
 }
 
+// Launch of the CTA-pair kernel: clusters of two, as many pairs as can be resident.
+int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                 const GemmParams& p, int max_ctas, cudaStream_t st) {
+  static bool attr_set = false;
+  static int max_pairs = 0;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Gemm2Smem::TOTAL;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Gemm2Smem::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cfg.gridDim = dim3(num_sms() & ~1, 1, 1);
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, gemm2_bf16_kernel, &cfg);
+    if (e != cudaSuccess) { cudaGetLastError(); n = num_sms() / 2; }
+    max_pairs = n > 0 ? n : num_sms() / 2;
+    if (max_pairs > num_sms() / 2) max_pairs = num_sms() / 2;
+    attr_set = true;
+  }
+  const long tiles = static_cast<long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
+  long pairs = max_pairs;
+  if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
+  if (tiles < pairs) pairs = tiles;
+  if (pairs < 1) pairs = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel, tmA, tmB, tmC, p);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+int gemm2_pairs_resident() { return num_sms() / 2; }
+
 }  // namespace pb
 
 using namespace pb;
 
 static int g_gemm_debug = 0;
 // Timing experiments: bit 0 forces the 128-wide tile, bit 1 drops the epilogue stores,
-// bit 2 selects the direct-store epilogue.
+// bit 2 selects the direct-store epilogue, bit 3 keeps every product on the single-CTA kernel.
 PB_API int pb_gemm_set_debug(int flags) {
   g_gemm_debug = flags;
   return 0;
@@ -655,6 +895,12 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
   const int batch_b = (k_len != nullptr) ? 1 : (mblk_group != nullptr ? b_batch : batch);
   if (mblk_group != nullptr && (strideB % 8) != 0) return PB_BAD_ARG;
   const bool bn256 = N > 128 && !(g_gemm_debug & 1);
+  // CTA pairs (256 x 256 tiles) for plain and batched products with at least a full wave of
+  // pair tiles; grouped and all-gather modes, small problems and limited grids stay on one CTA
+  const long pair_tiles = static_cast<long>((M + 255) / 256) * ((N + 255) / 256) * batch;
+  const bool pair = bn256 && mblk_group == nullptr && k_len == nullptr && g_ag == nullptr &&
+                    !(g_gemm_debug & 8) && M > 128 && (max_ctas <= 0 || max_ctas >= num_sms()) &&
+                    pair_tiles >= gemm2_pairs_resident();
   const int BN = bn256 ? 256 : 128;
   CUtensorMap tmA, tmB;
   int r;
@@ -664,7 +910,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
     r = make_tmap_3d(&tmA, A, 2, M, K, batch_a, lda, strideA, 64, BK);
   if (r != 0) return 1000 + r;
   if (!b_mn)
-    r = make_tmap_3d(&tmB, B, 2, K, N, batch_b, ldb, strideB, BK, BN);
+    r = make_tmap_3d(&tmB, B, 2, K, N, batch_b, ldb, strideB, BK, pair ? 128 : BN);
   else
     r = make_tmap_3d(&tmB, B, 2, N, K, batch_b, ldb, strideB, 64, BK);
   if (r != 0) return 2000 + r;
@@ -695,6 +941,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
     if (make_tmap_3d(&tmC, C, cbytes, N, M, batch, ldc, strideC, out_f32 ? 32 : 64, 32) == 0)
       p.tma_store = 1;
   }
+  if (pair) return launch_gemm2(tmA, tmB, tmC, p, max_ctas, st);
   return bn256 ? launch_gemm<256>(tmA, tmB, tmC, p, max_ctas, st)
                : launch_gemm<128>(tmA, tmB, tmC, p, max_ctas, st);
 }

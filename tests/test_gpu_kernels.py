@@ -69,6 +69,54 @@ def test_gemm_limited_grid_and_many_tiles():
     ops.check_status("cuda")
 
 
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [
+    (4096, 2560, 320, False, False),      # 16 x 10 pair tiles, K not a multiple of 64
+    (2304 + 72, 2048 + 136, 512, False, False),   # ragged last row block (odd CTA all out of range) and column block
+    (2048, 5632, 1024, True, True),       # weight-gradient layout
+    (4096, 2048, 768, False, True),       # input-gradient layout
+    (3072, 3072, 256, True, False),
+])
+def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn):
+    """Products with at least one full wave of 256 x 256 tiles run on the two-CTA kernel
+    (tcgen05.mma.cta_group::2); same products on the single-CTA kernel for comparison."""
+    from prometheus_b200.ops import functional as ops
+    from prometheus_b200.ops._lib import call
+
+    a = _r(K, M, seed=1) if a_mn else _r(M, K, seed=1)
+    b = _r(K, N, seed=2) if b_mn else _r(N, K, seed=2)
+    ref = ops.gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn)
+    c = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    ops.check_status("cuda")
+    _close(c, ref)
+    try:
+        call("pb_gemm_set_debug", 8)       # every product on the single-CTA kernel
+        c1 = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    finally:
+        call("pb_gemm_set_debug", 0)
+    _close(c, c1, 2e-3)
+
+
+def test_gemm_cta_pair_batched_epilogue_variants():
+    from prometheus_b200.ops import functional as ops
+
+    a, b = _r(10, 768, 192, seed=1), _r(10, 768, 192, seed=2)       # 3 x 3 x 10 = 90 pair tiles
+    d = _r(10, 768, 768, seed=3)
+    c = ops.gemm(a, b, d=d, alpha=0.5, beta=-2.0)
+    _close(c, ops.gemm_ref(a, b, d=d, alpha=0.5, beta=-2.0))
+    c32 = ops.gemm(a, b, out_dtype=torch.float32)
+    _close(c32, ops.gemm_ref(a, b), tol=5e-3)
+    big_a, big_b = _r(4096, 256, seed=4), _r(2560, 256, seed=5)
+    acc = torch.randn(4096, 2560, device="cuda")
+    ref = acc + ops.gemm_ref(big_a, big_b)
+    ops.gemm(big_a, big_b, out=acc, d=acc, beta=1.0)
+    _close(acc, ref)
+    # a row stride that rules out the TMA store (direct-store epilogue)
+    odd = torch.empty(4096, 2563, device="cuda", dtype=torch.bfloat16)[:, :2560]
+    ops.gemm(big_a, big_b, out=odd)
+    _close(odd, ops.gemm_ref(big_a, big_b))
+    ops.check_status("cuda")
+
+
 @pytest.mark.parametrize("rows,d", [(37, 256), (1000, 2048), (64, 384), (5, 128)])
 def test_rmsnorm_fwd_bwd(rows, d):
     from prometheus_b200.ops import functional as ops
