@@ -220,6 +220,21 @@ __device__ __forceinline__ void tma_store_3d(const void* tmap, const void* smem_
       "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// L2 policy for data that is written once and not read again by this kernel (output tiles):
+// its lines are the first to go, so they do not push the operand panels out of the cache.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void tma_store_3d_hint(const void* tmap, const void* smem_src, int32_t x,
+                                                  int32_t y, int32_t z, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], "
+      "[%1], %5;" ::"l"(reinterpret_cast<uint64_t>(tmap)),
+      "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -350,16 +365,6 @@ __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const void* tma
       "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-// D[tmem of both CTAs] (+)= A * B over the pair; issued by one thread of the even CTA.
-__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                              uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // Completion of the pair's MMAs issued so far arrives on the barrier at the same shared-memory
 // offset in every CTA of `cta_mask`.
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
@@ -444,6 +449,20 @@ __device__ __forceinline__ void umma_f16_words(uint32_t tmem_d, uint32_t a_lo, u
       "mov.b64 db, {%3, %4};\n\t"
       "setp.ne.b32 p, %6, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Pair form of umma_f16_words (cta_group::2, issued by the even CTA).
+__device__ __forceinline__ void umma_f16_pair_words(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi,
+                                                    uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                    uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
       "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }

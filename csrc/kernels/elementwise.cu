@@ -60,80 +60,148 @@ __global__ void __launch_bounds__(128) rmsnorm_fwd_kernel(const bf16* __restrict
   }
 }
 
-// ---------------------------------------------------------------------------
-// RMSNorm backward. Persistent: each warp walks rows with a grid stride and
-// keeps its share of dw in registers (NV vectors of 8 columns per lane), then
-// the CTA writes one fp32 partial row to `dw_partial[blockIdx.x]`.
-//   xh = h * rstd;  g = dy * w;  dx = rstd * (g - xh * mean(g * xh)) (+ dres)
-// A second kernel folds the partial rows in a fixed order (deterministic).
-// ---------------------------------------------------------------------------
+// d = 256 NV (NV <= 8): the row lives in registers between the two passes and every load of the
+// row is issued before the first use. Same arithmetic as rmsnorm_fwd_kernel.
 template <int NV>
-__global__ void __launch_bounds__(128) rmsnorm_bwd_kernel(
-    const bf16* __restrict__ dy, const bf16* __restrict__ h, const float* __restrict__ w,
-    const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
-    float* __restrict__ dw_partial, int rows, int d) {
-  extern __shared__ float sdw[];  // [4 warps][d]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int wpb = blockDim.x >> 5;
-  float acc[NV * 8];
+__global__ void __launch_bounds__(128) rmsnorm_fwd_reg_kernel(
+    const bf16* __restrict__ x, const bf16* __restrict__ res, const float* __restrict__ w,
+    bf16* __restrict__ y, bf16* h_out, float* __restrict__ rstd_out, int rows, float eps) {
+  constexpr int d = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const size_t base = static_cast<size_t>(row) * d;
+  bf16x8 px[NV], pr[NV];
 #pragma unroll
-  for (int i = 0; i < NV * 8; ++i) acc[i] = 0.f;
-  const float inv_d = 1.f / static_cast<float>(d);
-  for (int row = blockIdx.x * wpb + warp; row < rows; row += gridDim.x * wpb) {
-    const size_t base = static_cast<size_t>(row) * d;
-    const float rstd = rstd_in[row];
-    bf16x8 pdy[NV], ph[NV];
-    float dot = 0.f;
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      const int col = (v * 32 + lane) * 8;
-      float a[8], b[8];
-      pdy[v] = *reinterpret_cast<const bf16x8*>(dy + base + col);
-      ph[v] = *reinterpret_cast<const bf16x8*>(h + base + col);
-      unpack8(pdy[v], a);
-      unpack8(ph[v], b);
-      const float4 w0 = *reinterpret_cast<const float4*>(w + col);
-      const float4 w1 = *reinterpret_cast<const float4*>(w + col + 4);
-      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float xhat = b[i] * rstd;
-        dot += a[i] * ww[i] * xhat;
-        acc[v * 8 + i] += a[i] * xhat;
-      }
-    }
-    dot = warp_sum(dot) * inv_d;
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      const int col = (v * 32 + lane) * 8;
-      float a[8], b[8], o[8];
-      unpack8(pdy[v], a);
-      unpack8(ph[v], b);
-      const float4 w0 = *reinterpret_cast<const float4*>(w + col);
-      const float4 w1 = *reinterpret_cast<const float4*>(w + col + 4);
-      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = rstd * (a[i] * ww[i] - b[i] * rstd * dot);
-      if (dres != nullptr) {
-        float r[8];
-        unpack8(*reinterpret_cast<const bf16x8*>(dres + base + col), r);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] += r[i];
-      }
-      *reinterpret_cast<bf16x8*>(dx + base + col) = pack8(o);
-    }
+  for (int v = 0; v < NV; ++v) {
+    px[v] = *reinterpret_cast<const bf16x8*>(x + base + (v * 32 + lane) * 8);
+    if (res != nullptr) pr[v] = *reinterpret_cast<const bf16x8*>(res + base + (v * 32 + lane) * 8);
   }
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    float f[8];
+    unpack8(px[v], f);
+    if (res != nullptr) {
+      float g[8];
+      unpack8(pr[v], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] += g[i];
+      px[v] = pack8(f);
+      unpack8(px[v], f);  // the norm sees the rounded residual stream
+      *reinterpret_cast<bf16x8*>(h_out + base + (v * 32 + lane) * 8) = px[v];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / static_cast<float>(d) + eps);
+  if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     const int col = (v * 32 + lane) * 8;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sdw[warp * d + col + i] = acc[v * 8 + i];
+    float f[8];
+    unpack8(px[v], f);
+    const float4 w0 = *reinterpret_cast<const float4*>(w + col);
+    const float4 w1 = *reinterpret_cast<const float4*>(w + col + 4);
+    f[0] *= rstd * w0.x; f[1] *= rstd * w0.y; f[2] *= rstd * w0.z; f[3] *= rstd * w0.w;
+    f[4] *= rstd * w1.x; f[5] *= rstd * w1.y; f[6] *= rstd * w1.z; f[7] *= rstd * w1.w;
+    *reinterpret_cast<bf16x8*>(y + base + col) = pack8(f);
   }
-  __syncthreads();
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    float s = 0.f;
-    for (int ww = 0; ww < wpb; ++ww) s += sdw[ww * d + c];
-    dw_partial[static_cast<size_t>(blockIdx.x) * d + c] = s;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm backward, d <= 2048. Persistent: a CTA of 256 threads walks groups of four rows with
+// a grid stride; thread t owns columns [8 t, 8 t + 8) of every row, so its share of dw stays
+// in eight registers for the whole kernel and is written once, as row blockIdx.x of
+// `dw_partial`. The loads of all four rows are issued before the first use, and the four row
+// dots share one block reduction (one __syncthreads per group; the scratch is double-buffered).
+//   xh = h * rstd;  g = dy * w;  dx = rstd * (g - xh * mean(g * xh)) (+ dres)
+// A second kernel folds the partial rows in a fixed order (deterministic).
+// ---------------------------------------------------------------------------
+constexpr int RMS_BWD_ROWS = 4;
+__global__ void __launch_bounds__(256, 2) rmsnorm_bwd_kernel(
+    const bf16* __restrict__ dy, const bf16* __restrict__ h, const float* __restrict__ w,
+    const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+    float* __restrict__ dw_partial, int rows, int d) {
+  constexpr int R = RMS_BWD_ROWS;
+  __shared__ float red[2][R][8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = threadIdx.x * 8;
+  const bool on = col < d;
+  float ww[8], acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { ww[i] = 0.f; acc[i] = 0.f; }
+  if (on) {
+    const float4 w0 = *reinterpret_cast<const float4*>(w + col);
+    const float4 w1 = *reinterpret_cast<const float4*>(w + col + 4);
+    ww[0] = w0.x; ww[1] = w0.y; ww[2] = w0.z; ww[3] = w0.w;
+    ww[4] = w1.x; ww[5] = w1.y; ww[6] = w1.z; ww[7] = w1.w;
+  }
+  const float inv_d = 1.f / static_cast<float>(d);
+  int buf = 0;
+  for (long row0 = static_cast<long>(blockIdx.x) * R; row0 < rows;
+       row0 += static_cast<long>(gridDim.x) * R) {
+    bf16x8 pdy[R], ph[R], pr[R];
+    float rs[R];
+    bool valid[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const long row = row0 + r;
+      valid[r] = on && row < rows;
+      rs[r] = row < rows ? rstd_in[row] : 0.f;
+      if (valid[r]) {
+        const size_t off = static_cast<size_t>(row) * d + col;
+        pdy[r] = *reinterpret_cast<const bf16x8*>(dy + off);
+        ph[r] = *reinterpret_cast<const bf16x8*>(h + off);
+        if (dres != nullptr) pr[r] = *reinterpret_cast<const bf16x8*>(dres + off);
+      }
+    }
+    float dot[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      dot[r] = 0.f;
+      if (valid[r]) {
+        float a[8], b[8];
+        unpack8(pdy[r], a);
+        unpack8(ph[r], b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float xhat = b[i] * rs[r];
+          dot[r] += a[i] * ww[i] * xhat;
+          acc[i] += a[i] * xhat;
+        }
+      }
+      dot[r] = warp_sum(dot[r]);
+      if (lane == 0) red[buf][r][warp] = dot[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (!valid[r]) continue;
+      float tot = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) tot += red[buf][r][k];
+      tot *= inv_d;
+      float a[8], b[8], o[8];
+      unpack8(pdy[r], a);
+      unpack8(ph[r], b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = rs[r] * (a[i] * ww[i] - b[i] * rs[r] * tot);
+      if (dres != nullptr) {
+        float q[8];
+        unpack8(pr[r], q);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += q[i];
+      }
+      *reinterpret_cast<bf16x8*>(dx + static_cast<size_t>(row0 + r) * d + col) = pack8(o);
+    }
+    buf ^= 1;
+  }
+  if (on) {
+    float* out = dw_partial + static_cast<size_t>(blockIdx.x) * d + col;
+    *reinterpret_cast<float4*>(out) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(out + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
 }
 
@@ -189,36 +257,61 @@ __global__ void fold_partials_kernel(const float* __restrict__ partial, float* _
 __global__ void rope_kernel(bf16* __restrict__ x, const int* __restrict__ pos, long tokens,
                             int heads, int D, int rot_pairs, int seq_len, float base,
                             int inverse) {
+  // One thread per (token, group of four pairs): the angles depend on the token and the pair
+  // only, so sine and cosine are computed once and reused for every head of the token.
   const int vec_per_head = D >> 3;
-  const long total = tokens * heads * vec_per_head;
+  const int rot_vecs = (rot_pairs + 3) >> 2;          // vectors that hold a rotated pair
+  const long total = tokens * rot_vecs;
   const float rot_dim = static_cast<float>(rot_pairs * 2);
   const float log2_base = log2f(base);
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
-    const int v = static_cast<int>(i % vec_per_head);
-    const long th = i / vec_per_head;
-    const long t = th / heads;
+    const int v = static_cast<int>(i % rot_vecs);
+    const long t = i / rot_vecs;
     const int pair0 = v * 4;
-    if (pair0 >= rot_pairs) continue;
     const float p = pos != nullptr ? static_cast<float>(pos[t])
                                    : static_cast<float>(t % seq_len);
-    bf16x8* ptr = reinterpret_cast<bf16x8*>(x) + i;
-    float f[8];
-    unpack8(*ptr, f);
+    float sn[4], cs[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int pr = pair0 + j;
-      if (pr < rot_pairs) {
-        const float inv_freq = exp2f(-2.f * static_cast<float>(pr) / rot_dim * log2_base);
-        float s, c;
-        sincosf(p * inv_freq, &s, &c);
-        if (inverse) s = -s;
-        const float e = f[2 * j], o = f[2 * j + 1];
-        f[2 * j] = e * c - o * s;
-        f[2 * j + 1] = e * s + o * c;
+      const float inv_freq = exp2f(-2.f * static_cast<float>(pr) / rot_dim * log2_base);
+      float s_, c_;
+      sincosf(p * inv_freq, &s_, &c_);
+      if (inverse) s_ = -s_;
+      if (pr >= rot_pairs) { s_ = 0.f; c_ = 1.f; }   // pass-through pair
+      sn[j] = s_; cs[j] = c_;
+    }
+    bf16x8* ptr = reinterpret_cast<bf16x8*>(x) + (t * heads) * vec_per_head + v;
+    int h = 0;
+    for (; h + 4 <= heads; h += 4) {        // four heads' loads in flight
+      bf16x8 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = ptr[static_cast<long>(h + u) * vec_per_head];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        unpack8(q[u], f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float e = f[2 * j], o = f[2 * j + 1];
+          f[2 * j] = e * cs[j] - o * sn[j];
+          f[2 * j + 1] = e * sn[j] + o * cs[j];
+        }
+        ptr[static_cast<long>(h + u) * vec_per_head] = pack8(f);
       }
     }
-    *ptr = pack8(f);
+    for (; h < heads; ++h) {
+      float f[8];
+      unpack8(ptr[static_cast<long>(h) * vec_per_head], f);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float e = f[2 * j], o = f[2 * j + 1];
+        f[2 * j] = e * cs[j] - o * sn[j];
+        f[2 * j + 1] = e * sn[j] + o * cs[j];
+      }
+      ptr[static_cast<long>(h) * vec_per_head] = pack8(f);
+    }
   }
 }
 
@@ -321,6 +414,84 @@ __global__ void l2norm_bwd_kernel(bf16* __restrict__ dxn, const bf16* __restrict
         __floats2bfloat162_rn(inv * (a.x - ya.x * dot), inv * (a.y - ya.y * dot));
     *reinterpret_cast<bf162*>(g + c + 2) =
         __floats2bfloat162_rn(inv * (b.x - yb.x * dot), inv * (b.y - yb.y * dot));
+  }
+}
+
+// D == 128 (the head width of every shipped model): half a warp per vector, one 16-byte access
+// per lane, eight vectors per warp with all their loads issued before the first reduction.
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__global__ void __launch_bounds__(256) l2norm128_fwd_kernel(bf16* __restrict__ x,
+                                                            float* __restrict__ inv_norm,
+                                                            long nvec, float eps) {
+  const int lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15;
+  const long v0 = (blockIdx.x * static_cast<long>(blockDim.x >> 5) + (threadIdx.x >> 5)) * 8;
+  bf16x8 p[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const long vec = v0 + j * 2 + half;
+    if (vec < nvec) p[j] = *reinterpret_cast<const bf16x8*>(x + vec * 128 + l16 * 8);
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const long vec = v0 + j * 2 + half;
+    float f[8];
+    float ss = 0.f;
+    if (vec < nvec) {
+      unpack8(p[j], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = half_warp_sum(ss);
+    if (vec < nvec) {
+      const float n = sqrtf(ss);
+      const float inv = 1.f / fmaxf(n, eps);
+      if (l16 == 0) inv_norm[vec] = n > eps ? inv : -inv;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] *= inv;
+      *reinterpret_cast<bf16x8*>(x + vec * 128 + l16 * 8) = pack8(f);
+    }
+  }
+}
+__global__ void __launch_bounds__(256) l2norm128_bwd_kernel(bf16* __restrict__ dxn,
+                                                            const bf16* __restrict__ xn,
+                                                            const float* __restrict__ inv_norm,
+                                                            long nvec) {
+  const int lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15;
+  const long v0 = (blockIdx.x * static_cast<long>(blockDim.x >> 5) + (threadIdx.x >> 5)) * 8;
+  bf16x8 pg[4], py[4];
+  float invs[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const long vec = v0 + j * 2 + half;
+    if (vec < nvec) {
+      pg[j] = *reinterpret_cast<const bf16x8*>(dxn + vec * 128 + l16 * 8);
+      py[j] = *reinterpret_cast<const bf16x8*>(xn + vec * 128 + l16 * 8);
+      invs[j] = inv_norm[vec];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const long vec = v0 + j * 2 + half;
+    float g[8], y[8];
+    float dot = 0.f;
+    if (vec < nvec) {
+      unpack8(pg[j], g);
+      unpack8(py[j], y);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot += g[i] * y[i];
+    }
+    dot = half_warp_sum(dot);
+    if (vec < nvec) {
+      float inv = invs[j];
+      if (inv < 0.f) { inv = -inv; dot = 0.f; }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) g[i] = inv * (g[i] - y[i] * dot);
+      *reinterpret_cast<bf16x8*>(dxn + vec * 128 + l16 * 8) = pack8(g);
+    }
   }
 }
 
@@ -437,6 +608,24 @@ PB_API int pb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y
                           void* rstd, int rows, int d, float eps, cudaStream_t st) {
   if (d % 8 != 0 || rows <= 0) return PB_BAD_ARG;
   const int wpb = 4;
+  if (d % 256 == 0 && d <= 2048) {
+    const bf16* x_ = static_cast<const bf16*>(x);
+    const bf16* r_ = static_cast<const bf16*>(res);
+    const float* w_ = static_cast<const float*>(w);
+    bf16* y_ = static_cast<bf16*>(y);
+    bf16* h_ = static_cast<bf16*>(h_out);
+    float* s_ = static_cast<float*>(rstd);
+    const int grid = (rows + wpb - 1) / wpb;
+    switch (d / 256) {
+#define PB_CASE(NV)                                                                              \
+  case NV:                                                                                       \
+    rmsnorm_fwd_reg_kernel<NV><<<grid, wpb * 32, 0, st>>>(x_, r_, w_, y_, h_, s_, rows, eps);    \
+    break;
+      PB_CASE(1) PB_CASE(2) PB_CASE(3) PB_CASE(4) PB_CASE(5) PB_CASE(6) PB_CASE(7) PB_CASE(8)
+#undef PB_CASE
+    }
+    return cudaGetLastError();
+  }
   rmsnorm_fwd_kernel<<<(rows + wpb - 1) / wpb, wpb * 32, 0, st>>>(
       static_cast<const bf16*>(x), static_cast<const bf16*>(res), static_cast<const float*>(w),
       static_cast<bf16*>(y), static_cast<bf16*>(h_out), static_cast<float*>(rstd), rows, d, eps);
@@ -445,8 +634,9 @@ PB_API int pb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y
 
 // Number of partial rows rmsnorm_bwd writes (scratch must hold that many x d floats).
 PB_API int pb_rmsnorm_bwd_nparts(int rows, int d) {
-  int g = 148 * 4;
-  const int per = (d % 256 == 0 && d <= 2048) ? 4 : 1;
+  const bool cols = d <= 2048;              // the column-owner kernel: two CTAs per SM
+  int g = cols ? 148 * 2 : 148 * 4;
+  const int per = cols ? RMS_BWD_ROWS : 1;
   const int need = (rows + per - 1) / per;
   return need < g ? (need < 1 ? 1 : need) : g;
 }
@@ -463,18 +653,8 @@ PB_API int pb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const vo
   const bf16* dr_ = static_cast<const bf16*>(dres);
   bf16* dx_ = static_cast<bf16*>(dx);
   float* part = static_cast<float*>(scratch);
-  if (d % 256 == 0 && d <= 2048) {
-    const size_t smem = 4 * d * sizeof(float);
-    switch (d / 256) {
-#define PB_CASE(NV)                                                                          \
-  case NV:                                                                                   \
-    rmsnorm_bwd_kernel<NV><<<grid, 128, smem, st>>>(dy_, h_, w_, r_, dr_, dx_, part, rows, d); \
-    break;
-      PB_CASE(1) PB_CASE(2) PB_CASE(3) PB_CASE(4) PB_CASE(5) PB_CASE(6) PB_CASE(7) PB_CASE(8)
-#undef PB_CASE
-      default:
-        return PB_BAD_ARG;
-    }
+  if (d <= 2048) {
+    rmsnorm_bwd_kernel<<<grid, 256, 0, st>>>(dy_, h_, w_, r_, dr_, dx_, part, rows, d);
   } else {
     const size_t smem = (d + 33) * sizeof(float);
     if (smem > 48 * 1024)
@@ -490,8 +670,9 @@ PB_API int pb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const vo
 PB_API int pb_rope(void* x, const void* pos, long tokens, int heads, int D, int rot_pairs,
                    int seq_len, float base, int inverse, cudaStream_t st) {
   if (D % 8 != 0) return PB_BAD_ARG;
-  const long total = tokens * heads * (D / 8);
-  rope_kernel<<<grid_for(total, 256), 256, 0, st>>>(static_cast<bf16*>(x),
+  const long total = tokens * ((rot_pairs + 3) / 4);
+  if (total <= 0) return 0;
+  rope_kernel<<<grid_for(total, 128), 128, 0, st>>>(static_cast<bf16*>(x),
                                                     static_cast<const int*>(pos), tokens, heads,
                                                     D, rot_pairs, seq_len, base, inverse);
   return cudaGetLastError();
@@ -514,6 +695,12 @@ PB_API int pb_swiglu_bwd(const void* dout, const void* gu, void* dgu, long rows,
 
 PB_API int pb_l2norm_fwd(void* x, void* inv_norm, long nvec, int D, float eps, cudaStream_t st) {
   if (D % 4 != 0) return PB_BAD_ARG;
+  if (D == 128 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const long warps = (nvec + 7) / 8;
+    l2norm128_fwd_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(
+        static_cast<bf16*>(x), static_cast<float*>(inv_norm), nvec, eps);
+    return cudaGetLastError();
+  }
   const int wpb = 8;
   l2norm_fwd_kernel<<<static_cast<unsigned>((nvec + wpb - 1) / wpb), wpb * 32, 0, st>>>(
       static_cast<bf16*>(x), static_cast<float*>(inv_norm), nvec, D, eps);
@@ -522,6 +709,13 @@ PB_API int pb_l2norm_fwd(void* x, void* inv_norm, long nvec, int D, float eps, c
 PB_API int pb_l2norm_bwd(void* dxn, const void* xn, const void* inv_norm, long nvec, int D,
                          cudaStream_t st) {
   if (D % 4 != 0) return PB_BAD_ARG;
+  if (D == 128 && ((reinterpret_cast<uintptr_t>(dxn) | reinterpret_cast<uintptr_t>(xn)) & 15) == 0) {
+    const long warps = (nvec + 7) / 8;
+    l2norm128_bwd_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(
+        static_cast<bf16*>(dxn), static_cast<const bf16*>(xn),
+        static_cast<const float*>(inv_norm), nvec);
+    return cudaGetLastError();
+  }
   const int wpb = 8;
   l2norm_bwd_kernel<<<static_cast<unsigned>((nvec + wpb - 1) / wpb), wpb * 32, 0, st>>>(
       static_cast<bf16*>(dxn), static_cast<const bf16*>(xn),

@@ -72,11 +72,12 @@ struct GemmSmem {
 
 // One warp's share of a finished accumulator: 32 rows (tensor-memory lanes of `t_addr`) x BN
 // columns, scaled, D added, converted and stored. `y0` is the matrix row of lane 0, `n0` the
-// first column, `my_epi_base` the warp's 8 KB staging area for the TMA-store path.
+// first column, `my_epi_base` the warp's 8 KB staging area for the TMA-store path; the warp
+// handles tile columns [col_lo, col_hi) (multiples of 64).
 template <int BN>
 __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const CUtensorMap* tmC,
                                               uint32_t t_addr, uint8_t* my_epi_base, int b, int y0,
-                                              int n0, int lane) {
+                                              int n0, int lane, int col_lo = 0, int col_hi = BN) {
   const int row = y0 + lane;
   const bool row_ok = row < p.M;
   const size_t c_off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
@@ -86,17 +87,21 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const CUtenso
     // tensor store per slab: coalesced, asynchronous, clipped at the matrix edge.
     uint8_t* my_epi = my_epi_base;
     const int cols_per_slab = p.out_f32 ? 32 : 64;
+    const uint64_t evict_first = l2_policy_evict_first();
+    const int halves = cols_per_slab / 32;
 #pragma unroll 1
-    for (int sl = 0; sl * cols_per_slab < BN; ++sl) {
+    for (int sl = col_lo / cols_per_slab; sl * cols_per_slab < col_hi; ++sl) {
       const int x0 = n0 + sl * cols_per_slab;
       uint8_t* buf = my_epi + (sl & 1) * 4096;
+      // the whole slab is requested from tensor memory before the wait for the staging buffer,
+      // so the two latencies overlap
+      uint32_t ra[32], rb[32];
+      tmem_ld_32x32b_x32(t_addr + sl * cols_per_slab, ra);
+      if (halves == 2) tmem_ld_32x32b_x32(t_addr + sl * cols_per_slab + 32, rb);
       if (lane == 0) tma_store_wait_read<1>();
       __syncwarp();
-#pragma unroll 1
-      for (int hf = 0; hf * 32 < cols_per_slab; ++hf) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_addr + sl * cols_per_slab + hf * 32, r);
-        tmem_ld_wait();
+      tmem_ld_wait();
+      auto chunk = [&](const uint32_t (&r)[32], const int hf) {
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
@@ -150,17 +155,20 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const CUtenso
             *reinterpret_cast<bf16x8*>(rowp + (((hf * 4 + i) ^ (lane & 7)) << 4)) = pk;
           }
         }
-      }
+      };
+      chunk(ra, 0);
+      if (halves == 2) chunk(rb, 1);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0 && x0 < p.N && y0 < p.M && !(p.debug & 2)) {
-        tma_store_3d(tmC, buf, x0, y0, b);
+        if (p.debug & 16) tma_store_3d(tmC, buf, x0, y0, b);
+        else tma_store_3d_hint(tmC, buf, x0, y0, b, evict_first);
       }
       if (lane == 0) tma_store_commit();
     }
   } else
 #pragma unroll 1
-  for (int c = 0; c < BN; c += 32) {
+  for (int c = col_lo; c < col_hi; c += 32) {
     uint32_t r[32];
     tmem_ld_32x32b_x32(t_addr + c, r);
     tmem_ld_wait();
@@ -369,6 +377,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       const uint32_t idesc = make_idesc(1, 1, BM, BN, p.a_mn ? 1u : 0u, p.b_mn ? 1u : 0u);
+      // descriptor words hoisted out of the loops: high words constant, low words
+      // (stage base + step * j) in 16-byte units, so the issue loop is a handful of instructions
+      constexpr uint32_t HI = sdesc_hi_sw128(1024);
+      const uint32_t a_lo0 = sdesc_lo(smem_u32(smA), p.a_mn ? 8192 : 16);
+      const uint32_t b_lo0 = sdesc_lo(smem_u32(smB), p.b_mn ? 8192 : 16);
+      const uint32_t a_step = (p.a_mn ? 2048u : 32u) >> 4, b_step = (p.b_mn ? 2048u : 32u) >> 4;
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -385,20 +399,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(&full[s], ph, p.status)) { ok = false; break; }
+          if (!mbar_wait_spin(&full[s], ph, p.status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smA + s * S::A_BYTES);
-          const uint32_t b_addr = smem_u32(smB + s * S::B_BYTES);
+          const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(s) * (S::A_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(s) * (S::B_BYTES >> 4);
+          // K-major: 16 elements = 32 bytes along the swizzled row.
+          // MN-major: 16 k-rows = two 8-row groups of 1024 bytes.
 #pragma unroll
-          for (int j = 0; j < BK / 16; ++j) {
-            // K-major: 16 elements = 32 bytes along the swizzled row.
-            // MN-major: 16 k-rows = two 8-row groups of 1024 bytes.
-            const uint64_t ad = p.a_mn ? make_sdesc_sw128(a_addr + j * 2048, 8192, 1024)
-                                       : make_sdesc_sw128(a_addr + j * 32, 16, 1024);
-            const uint64_t bd = p.b_mn ? make_sdesc_sw128(b_addr + j * 2048, 8192, 1024)
-                                       : make_sdesc_sw128(b_addr + j * 32, 16, 1024);
-            umma_f16(d_tmem, ad, bd, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-          }
+          for (int j = 0; j < BK / 16; ++j)
+            umma_f16_words(d_tmem, a_lo + j * a_step, HI, b_lo + j * b_step, HI, idesc,
+                           (kb > 0 || j > 0) ? 1u : 0u);
           umma_commit(&empty[s]);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -482,23 +492,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // its 128 of the tile's 256 rows of B, so a k-block costs each SM 32 KB of shared-memory reads
 // instead of 48 KB: the operand reads of the single-CTA 128 x 256 tile take three quarters of the
 // shared-memory bandwidth, and the epilogue's staging traffic competes for the rest.
-//   even CTA: warp 0 loads, warp 1 lane 0 issues the pair's MMAs, warps 2-5 drain rows 0..127
-//   odd CTA:  warp 0 loads (completions counted on the even CTA's barrier), warps 2-5 drain
+//   even CTA: warp 0 loads, warp 1 lane 0 issues the pair's MMAs, warps 2-9 drain rows 0..127
+//   odd CTA:  warp 0 loads (completions counted on the even CTA's barrier), warps 2-9 drain
 //             rows 128..255 from its own tensor memory
+// (eight epilogue warps, two per tensor-memory lane quarter: with four, draining a 256-column
+// accumulator took longer than a K = 2048 main loop)
 // Barriers: full[s] lives in the even CTA (2 x stage bytes); empty[s] and tfull[a] exist in both
 // and are signalled by one tcgen05.commit to both CTAs; tempty[a] lives in the even CTA and
-// collects the eight epilogue warps of the pair. Loads carry no cluster multicast.
+// collects the sixteen epilogue warps of the pair. Loads carry no cluster multicast.
 // ---------------------------------------------------------------------------
 struct Gemm2Smem {
   static constexpr int A_BYTES = 128 * BK * 2;
   static constexpr int B_BYTES = 128 * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = 6;
-  static constexpr int EPI_BYTES = 4 * 2 * 4096;
+  static constexpr int STAGES = 5;
+  static constexpr int EPI_WARPS = 8;
+  static constexpr int EPI_BYTES = EPI_WARPS * 2 * 4096;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+  static constexpr int THREADS = (2 + EPI_WARPS) * 32;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(Gemm2Smem::THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   using S = Gemm2Smem;
@@ -535,7 +549,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 8);
+      mbar_init(&tempty[a], 2 * S::EPI_WARPS);
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -603,6 +617,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // ------------------------------ MMA issuer (even CTA) ------------------------------
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = make_idesc(1, 1, BM2, BN, p.a_mn ? 1u : 0u, p.b_mn ? 1u : 0u);
+      // One issuing thread feeds both tensor cores: a k-block is four MMAs of 128 cycles each,
+      // so everything between two MMAs is kept to a few instructions. The descriptors' high
+      // words are constants; the low words are (stage base + step * j), all in 16-byte units.
+      constexpr uint32_t HI = sdesc_hi_sw128(1024);
+      const uint32_t a_lo0 = sdesc_lo(smem_u32(smA), p.a_mn ? 8192 : 16);
+      const uint32_t b_lo0 = sdesc_lo(smem_u32(smB), p.b_mn ? 8192 : 16);
+      const uint32_t a_step = (p.a_mn ? 2048u : 32u) >> 4, b_step = (p.b_mn ? 2048u : 32u) >> 4;
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -613,18 +634,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full[s], ph, p.status)) { ok = false; break; }
+          if (!mbar_wait_spin(&full[s], ph, p.status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smA + s * S::A_BYTES);
-          const uint32_t b_addr = smem_u32(smB + s * S::B_BYTES);
+          const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(s) * (S::A_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(s) * (S::B_BYTES >> 4);
 #pragma unroll
-          for (int j = 0; j < BK / 16; ++j) {
-            const uint64_t ad = p.a_mn ? make_sdesc_sw128(a_addr + j * 2048, 8192, 1024)
-                                       : make_sdesc_sw128(a_addr + j * 32, 16, 1024);
-            const uint64_t bd = p.b_mn ? make_sdesc_sw128(b_addr + j * 2048, 8192, 1024)
-                                       : make_sdesc_sw128(b_addr + j * 32, 16, 1024);
-            umma_f16_pair(d_tmem, ad, bd, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-          }
+          for (int j = 0; j < BK / 16; ++j)
+            umma_f16_pair_words(d_tmem, a_lo + j * a_step, HI, b_lo + j * b_step, HI, idesc,
+                                (kb > 0 || j > 0) ? 1u : 0u);
           umma_commit_pair(&empty[s], 3);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -645,8 +662,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!mbar_wait(&tfull[acc], acc_ph, p.status)) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      // two warps per lane quarter: warps 2-5 drain columns 0..127, warps 6-9 columns 128..255
+      const int c_lo = warp < 6 ? 0 : 128;
       epilogue_rows<BN>(p, &tmC, t_addr, smEpi + (warp - 2) * 8192, b,
-                        m_blk * BM2 + static_cast<int>(rank) * 128 + q * 32, n_blk * BN, lane);
+                        m_blk * BM2 + static_cast<int>(rank) * 128 + q * 32, n_blk * BN, lane, c_lo,
+                        c_lo + 128);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty0 + acc * 8);
@@ -752,7 +772,7 @@ int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorM
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(Gemm2Smem::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Gemm2Smem::TOTAL;
   cfg.stream = st;
   cfg.attrs = attr;
@@ -787,7 +807,8 @@ using namespace pb;
 
 static int g_gemm_debug = 0;
 // Timing experiments: bit 0 forces the 128-wide tile, bit 1 drops the epilogue stores,
-// bit 2 selects the direct-store epilogue, bit 3 keeps every product on the single-CTA kernel.
+// bit 2 selects the direct-store epilogue, bit 3 keeps every product on the single-CTA kernel,
+// bit 4 stores the output tiles without the evict-first L2 hint.
 PB_API int pb_gemm_set_debug(int flags) {
   g_gemm_debug = flags;
   return 0;

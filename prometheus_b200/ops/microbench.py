@@ -69,6 +69,71 @@ def bench_gemm(a):
         ms_l = timeit(lambda: xr @ wr, a.iters)
         out["library_ms"] = ms_l
         out["library_tflops"] = 2.0 * a.m * a.n * a.k / ms_l / 1e9
+    if a.sustain > 0:
+        # steady state under the power cap: each variant runs back to back for `sustain` seconds
+        # while NVML is polled for the SM clock and the board power (read-only queries)
+        import threading
+        import time
+
+        import pynvml
+
+        from ._lib import call
+
+        pynvml.nvmlInit()
+        hdl = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+        xr = x.t() if a.a_mn else x
+        wr = w if a.b_mn else w.t()
+        runs = [("library", None)] + [(f"debug={v}", int(v)) for v in (a.variants or "0").split(",")]
+        out["sustained"] = {}
+        for name, flag in runs:
+            if flag is not None:
+                call("pb_gemm_set_debug", flag)
+            fn = (lambda: xr @ wr) if flag is None else (lambda: ops.gemm(x, w, a_mn=a.a_mn, b_mn=a.b_mn))
+            for _ in range(5):
+                fn()
+            torch.cuda.synchronize()
+            samples, stop = [], threading.Event()
+
+            def poll():
+                while not stop.is_set():
+                    samples.append((pynvml.nvmlDeviceGetClockInfo(hdl, pynvml.NVML_CLOCK_SM),
+                                    pynvml.nvmlDeviceGetPowerUsage(hdl) / 1000.0))
+                    time.sleep(0.02)
+
+            th = threading.Thread(target=poll)
+            th.start()
+            n, t0 = 0, time.perf_counter()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            while time.perf_counter() - t0 < a.sustain:
+                for _ in range(50):
+                    fn()
+                n += 50
+                torch.cuda.synchronize()
+            e1.record()
+            torch.cuda.synchronize()
+            stop.set()
+            th.join()
+            ms_s = e0.elapsed_time(e1) / n
+            clk = sorted(c for c, _ in samples[len(samples) // 4:])
+            pw = sorted(w_ for _, w_ in samples[len(samples) // 4:])
+            out["sustained"][name] = {"tflops": round(2.0 * a.m * a.n * a.k / ms_s / 1e9, 1),
+                                      "sm_mhz_median": clk[len(clk) // 2] if clk else None,
+                                      "watts_median": round(pw[len(pw) // 2], 1) if pw else None}
+        call("pb_gemm_set_debug", a.debug)
+        return out
+    if a.variants:
+        # the same product under several pb_gemm_set_debug values, timed in this process one after
+        # the other (same GPU, same clocks): 0 = default dispatch, 8 = single-CTA kernel only
+        from ._lib import call
+
+        out["variants_tflops"] = {}
+        for rep in range(2):
+            for flag in [int(v) for v in a.variants.split(",")]:
+                call("pb_gemm_set_debug", flag)
+                ms_v = timeit(lambda: ops.gemm(x, w, a_mn=a.a_mn, b_mn=a.b_mn), a.iters)
+                out["variants_tflops"].setdefault(str(flag), []).append(round(2.0 * a.m * a.n * a.k / ms_v / 1e9, 1))
+        call("pb_gemm_set_debug", a.debug)
     return out
 
 
@@ -279,6 +344,9 @@ def main():
     g.add_argument("--b-mn", action="store_true")
     g.add_argument("--compare", action="store_true")
     g.add_argument("--debug", type=int, default=0, help="timing experiments, see pb_gemm_set_debug")
+    g.add_argument("--sustain", type=float, default=0.0,
+                   help="seconds per variant of back-to-back launches with NVML clock / power polling")
+    g.add_argument("--variants", default="", help="comma-separated pb_gemm_set_debug values to time side by side")
     d = sub.add_parser("delta")
     f = sub.add_parser("fp8")
     f.add_argument("--m", type=int, default=8192)
