@@ -916,12 +916,15 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
   const int batch_b = (k_len != nullptr) ? 1 : (mblk_group != nullptr ? b_batch : batch);
   if (mblk_group != nullptr && (strideB % 8) != 0) return PB_BAD_ARG;
   const bool bn256 = N > 128 && !(g_gemm_debug & 1);
-  // CTA pairs (256 x 256 tiles) for plain and batched products with at least a full wave of
-  // pair tiles; grouped and all-gather modes, small problems and limited grids stay on one CTA
+  // CTA pairs (256 x 256 tiles) for plain and batched products; grouped and all-gather modes and
+  // limited grids stay on one CTA. A pair tile covers two single-CTA tiles, so the waves fill
+  // alike, except when the last row block is at most half a pair tile: then the pair kernel
+  // needs enough tiles for that waste not to matter.
   const long pair_tiles = static_cast<long>((M + 255) / 256) * ((N + 255) / 256) * batch;
+  const int m_tail = M % 256;
   const bool pair = bn256 && mblk_group == nullptr && k_len == nullptr && g_ag == nullptr &&
                     !(g_gemm_debug & 8) && M > 128 && (max_ctas <= 0 || max_ctas >= num_sms()) &&
-                    pair_tiles >= gemm2_pairs_resident();
+                    (m_tail == 0 || m_tail > 128 || pair_tiles >= 2 * gemm2_pairs_resident());
   const int BN = bn256 ? 256 : 128;
   CUtensorMap tmA, tmB;
   int r;
