@@ -35,6 +35,7 @@ struct GemmParams {
   int out_f32, d_f32;
   int a_mn, b_mn;
   int tma_store;  // epilogue stages tiles in shared memory and stores them with TMA
+  int m_group;    // row blocks per rasterisation group (all column blocks of a group before the next)
   int debug;  // bit 1: skip the epilogue's global stores (timing experiments only)
   int* status;
   // Grouped modes (both null for the plain GEMM):
@@ -301,10 +302,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       n_blk = ((p.ag_rank * p.ag_rows_per_rank) / BN + r / num_m) % num_n;
       return;
     }
-    const int group = 8 * num_n;
+    const int group = p.m_group * num_n;
     const int g = r / group;
-    const int first_m = g * 8;
-    const int gsz = min(num_m - first_m, 8);
+    const int first_m = g * p.m_group;
+    const int gsz = min(num_m - first_m, p.m_group);
     m_blk = first_m + (r % group) % gsz;
     n_blk = (r % group) / gsz;
   };
@@ -569,10 +570,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   auto tile_coords = [&](long t, int& b, int& m_blk, int& n_blk) {
     b = static_cast<int>(t / tiles_per_batch);
     const int r = static_cast<int>(t % tiles_per_batch);
-    const int group = 8 * num_n;
+    const int group = p.m_group * num_n;
     const int g = r / group;
-    const int first_m = g * 8;
-    const int gsz = min(num_m - first_m, 8);
+    const int first_m = g * p.m_group;
+    const int gsz = min(num_m - first_m, p.m_group);
     m_blk = first_m + (r % group) % gsz;
     n_blk = (r % group) / gsz;
   };
@@ -808,7 +809,8 @@ using namespace pb;
 static int g_gemm_debug = 0;
 // Timing experiments: bit 0 forces the 128-wide tile, bit 1 drops the epilogue stores,
 // bit 2 selects the direct-store epilogue, bit 3 keeps every product on the single-CTA kernel,
-// bit 4 stores the output tiles without the evict-first L2 hint.
+// bit 4 stores the output tiles without the evict-first L2 hint, bit 5 fixes the rasterisation
+// group at 8 row blocks.
 PB_API int pb_gemm_set_debug(int flags) {
   g_gemm_debug = flags;
   return 0;
@@ -947,6 +949,19 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.status = status;
   p.debug = g_gemm_debug;
+  {
+    // Rasterisation: the A panels of a group of row blocks stay in L2 while the B panels stream
+    // past them once per group, so B is read from DRAM (row blocks / group) times. The group is
+    // as tall as lets its A panels take about 48 MB of the 126 MB L2, and at least 8 blocks so
+    // that a wave of tiles stays near-square when the panels are too long to be resident.
+    const long panel_bytes = static_cast<long>(pair ? 256 : BM) * K * 2;
+    long g = (48L << 20) / (panel_bytes > 0 ? panel_bytes : 1);
+    if (g < 8) g = 8;
+    if (g > 64) g = 64;
+    // a B that fits in L2 next to the group is not re-read whatever the group: keep the wave square
+    if (static_cast<long>(N) * K * 2 <= (32L << 20)) g = 8;
+    p.m_group = (g_gemm_debug & 32) ? 8 : static_cast<int>(g);
+  }
   p.mblk_group = mblk_group; p.k_off = k_off; p.k_len = k_len;
   p.ag_ready = nullptr;
   if (g_ag != nullptr) {
