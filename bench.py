@@ -49,7 +49,7 @@ def parse_args():
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "p2p", "nccl"],
                     help="gradient path at N > 1: peer-memory reduce-to-owner + update-broadcast kernels "
                          "(auto / p2p, the product) or NCCL collectives only (the baseline)")
-    ap.add_argument("--config", default="dense", choices=["dense", "latent", "moe16b"],
+    ap.add_argument("--config", default="dense", choices=["dense", "latent", "moe16b", "longctx"],
                     help="dense: the headline 1.3B hybrid (default). latent: the same model with 1024-token "
                          "prefix + 8 latent slots + 512-token answer, 4 Jacobi sweeps, 8 sequences per GPU. "
                          "moe16b: 28-layer 64-expert top-6 MoE with FP8 linears, expert parallel over the ranks.")
@@ -164,6 +164,14 @@ def main() -> int:
         if args.seqs_per_gpu == SEQS_PER_GPU:
             args.seqs_per_gpu = 8
         model_name += " + latent slots (prefix 1024 | K=8 | answer 512, 4 Jacobi sweeps)"
+    if args.config == "longctx":
+        # one sequence split over the ranks (context parallel), 16384 tokens per rank:
+        # 8 ranks hold the 131072-token sequence of the long-context configuration
+        args.seq_len = 16384 * world
+        args.seqs_per_gpu = 1
+        args.micro_batch = 1
+        trainer_kw = dict(context_parallel=world > 1)
+        model_name += f" at sequence length {args.seq_len} (context parallel over {world} rank(s))"
     cfg = model.config_dense_1p3b(max_context=args.seq_len)
     if args.config == "moe16b":
         cfg = model.with_overrides(model.config_moe_16b(), max_context=args.seq_len)
@@ -188,11 +196,24 @@ def main() -> int:
         step_kw = dict(loss_mask=mask)
 
     B, S = args.seqs_per_gpu, args.seq_len
-    gen = torch.Generator().manual_seed(1000 + rank)
+    cp = args.config == "longctx"
+    gen = torch.Generator().manual_seed(1000 + (0 if cp else rank))     # CP ranks slice the same sequence
     n_batches = args.steps + args.warmup
     host_tokens = [torch.randint(0, cfg.vocab_size, (B, S), generator=gen, dtype=torch.int64)
-                   .pin_memory() for _ in range(min(n_batches, 4))]
+                   for _ in range(min(n_batches, 4))]
+    host_masks = None
+    if cp and world > 1:
+        sliced = [tr.cp_slice(t, torch.ones(B, S)) for t in host_tokens]
+        host_tokens = [a.contiguous() for a, _ in sliced]
+        host_masks = [m.contiguous().pin_memory() for _, m in sliced]
+    host_tokens = [t.pin_memory() for t in host_tokens]
     dev_tokens = [t.to(dev) for t in host_tokens]
+    dev_masks = [m.to(dev) for m in host_masks] if host_masks else None
+
+    def kw_for(i, host=False):
+        if dev_masks is None:
+            return step_kw
+        return dict(loss_mask=(host_masks if host else dev_masks)[i % len(dev_masks)])
 
     def sync_all():
         if world > 1:
@@ -200,7 +221,7 @@ def main() -> int:
         torch.cuda.synchronize()
 
     for i in range(args.warmup):
-        tr.step(dev_tokens[i % len(dev_tokens)], **step_kw)
+        tr.step(dev_tokens[i % len(dev_tokens)], **kw_for(i))
     sync_all()
 
     sampler = ClockSampler(local_rank)
@@ -211,7 +232,7 @@ def main() -> int:
     sync_all()
     e0.record()
     for i in range(args.steps):
-        out = tr.step(dev_tokens[i % len(dev_tokens)], **step_kw)
+        out = tr.step(dev_tokens[i % len(dev_tokens)], **kw_for(i))
     e1.record()
     sync_all()
     ms = e0.elapsed_time(e1)
@@ -224,8 +245,10 @@ def main() -> int:
     f0.record()
     e2e_loss = 0.0
     for i in range(args.steps):
+        hkw = kw_for(i, host=True)
         res = tr.step_from_host(host_tokens[i % len(host_tokens)],
-                                *( [step_kw["loss_mask"].cpu().pin_memory()] if step_kw else [] ))
+                                *([hkw["loss_mask"] if hkw["loss_mask"].device.type == "cpu"
+                                   else hkw["loss_mask"].cpu().pin_memory()] if hkw else []))
         e2e_loss = res["loss"]
     f1.record()
     sync_all()
@@ -236,7 +259,7 @@ def main() -> int:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e = float(t[0]), float(t[1])
-    tokens_per_step = B * S * world
+    tokens_per_step = B * S * (1 if cp else world)
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (ms_e2e / 1e3)
     if rank == 0:
@@ -247,8 +270,8 @@ def main() -> int:
             "data": "synthetic (seeded uniform tokens, random-init weights)",
             "config": {
                 "model": model_name if not args.layers else f"DEBUG {args.layers} layers",
-                "global_batch": B * world, "seq_len": S,
-                "parallelism": (f"dp{world}" + ("+ep" + str(world) if args.config == "moe16b" else ""))
+                "global_batch": B * (1 if cp else world), "seq_len": S,
+                "parallelism": (f"cp{world}" if cp else f"dp{world}" + ("+ep" + str(world) if args.config == "moe16b" else ""))
                 if world > 1 else "single",
                 "micro_batch": args.micro_batch, "grad_sync": args.grad_sync,
                 "l2": "per-step working set (3.5 GB bf16 weights + activations) exceeds the 126 MB L2",
@@ -256,7 +279,8 @@ def main() -> int:
             "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"),
                        "reasons": clocks.get("reasons", [])},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 8},
+                    "h2d_bytes_per_step": int(host_tokens[0].numel() * 8 + (host_masks[0].numel() * 4 if host_masks else 0)),
+                    "d2h_bytes_per_step": 8},
             "gpu_launches": launches,
             "loss": last_loss, "e2e_loss": e2e_loss, "impl": "ours",
         }

@@ -120,11 +120,27 @@ __global__ void __launch_bounds__(128) rmsnorm_fwd_reg_kernel(
 // A second kernel folds the partial rows in a fixed order (deterministic).
 // ---------------------------------------------------------------------------
 constexpr int RMS_BWD_ROWS = 4;
+constexpr int RMS_BWD_SMEM = 2 * RMS_BWD_ROWS * 3 * 256 * 16;   // two groups x rows x {dy, h, dres} x 4 KB
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// The next group of rows is copied into shared memory (cp.async, each thread its own 16 bytes
+// per row and tensor, so no barrier guards the data) while the current group is reduced, so the
+// loads never drain at the per-group barrier.
 __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_kernel(
     const bf16* __restrict__ dy, const bf16* __restrict__ h, const float* __restrict__ w,
     const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
     float* __restrict__ dw_partial, int rows, int d) {
   constexpr int R = RMS_BWD_ROWS;
+  extern __shared__ __align__(16) uint8_t rms_stage[];   // [2][R][3][256] x 16 bytes
   __shared__ float red[2][R][8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col = threadIdx.x * 8;
@@ -139,29 +155,47 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_kernel(
     ww[4] = w1.x; ww[5] = w1.y; ww[6] = w1.z; ww[7] = w1.w;
   }
   const float inv_d = 1.f / static_cast<float>(d);
+  auto slot = [&](int buf, int r, int which) -> bf16x8* {
+    return reinterpret_cast<bf16x8*>(rms_stage) + ((buf * R + r) * 3 + which) * 256 + threadIdx.x;
+  };
+  auto issue = [&](long row0, int buf) {
+    if (on) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const long row = row0 + r;
+        if (row < rows) {
+          const size_t off = static_cast<size_t>(row) * d + col;
+          cp_async_16(slot(buf, r, 0), dy + off);
+          cp_async_16(slot(buf, r, 1), h + off);
+          if (dres != nullptr) cp_async_16(slot(buf, r, 2), dres + off);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+  const long stride = static_cast<long>(gridDim.x) * R;
   int buf = 0;
-  for (long row0 = static_cast<long>(blockIdx.x) * R; row0 < rows;
-       row0 += static_cast<long>(gridDim.x) * R) {
-    bf16x8 pdy[R], ph[R], pr[R];
-    float rs[R];
+  long row0 = static_cast<long>(blockIdx.x) * R;
+  if (row0 < rows) issue(row0, 0);
+  for (; row0 < rows; row0 += stride) {
+    if (row0 + stride < rows) {
+      issue(row0 + stride, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    bf16x8 pdy[R], ph[R];
+    float rs[R], dot[R];
     bool valid[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const long row = row0 + r;
       valid[r] = on && row < rows;
       rs[r] = row < rows ? rstd_in[row] : 0.f;
-      if (valid[r]) {
-        const size_t off = static_cast<size_t>(row) * d + col;
-        pdy[r] = *reinterpret_cast<const bf16x8*>(dy + off);
-        ph[r] = *reinterpret_cast<const bf16x8*>(h + off);
-        if (dres != nullptr) pr[r] = *reinterpret_cast<const bf16x8*>(dres + off);
-      }
-    }
-    float dot[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
       dot[r] = 0.f;
       if (valid[r]) {
+        pdy[r] = *slot(buf, r, 0);
+        ph[r] = *slot(buf, r, 1);
         float a[8], b[8];
         unpack8(pdy[r], a);
         unpack8(ph[r], b);
@@ -190,7 +224,7 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_kernel(
       for (int i = 0; i < 8; ++i) o[i] = rs[r] * (a[i] * ww[i] - b[i] * rs[r] * tot);
       if (dres != nullptr) {
         float q[8];
-        unpack8(pr[r], q);
+        unpack8(*slot(buf, r, 2), q);
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] += q[i];
       }
@@ -428,31 +462,34 @@ __global__ void __launch_bounds__(256) l2norm128_fwd_kernel(bf16* __restrict__ x
                                                             float* __restrict__ inv_norm,
                                                             long nvec, float eps) {
   const int lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15;
-  const long v0 = (blockIdx.x * static_cast<long>(blockDim.x >> 5) + (threadIdx.x >> 5)) * 8;
-  bf16x8 p[4];
+  const long wstride = static_cast<long>(gridDim.x) * (blockDim.x >> 5) * 8;
+  for (long v0 = (blockIdx.x * static_cast<long>(blockDim.x >> 5) + (threadIdx.x >> 5)) * 8;
+       v0 < nvec; v0 += wstride) {
+    bf16x8 p[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const long vec = v0 + j * 2 + half;
-    if (vec < nvec) p[j] = *reinterpret_cast<const bf16x8*>(x + vec * 128 + l16 * 8);
-  }
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const long vec = v0 + j * 2 + half;
-    float f[8];
-    float ss = 0.f;
-    if (vec < nvec) {
-      unpack8(p[j], f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    for (int j = 0; j < 4; ++j) {
+      const long vec = v0 + j * 2 + half;
+      if (vec < nvec) p[j] = *reinterpret_cast<const bf16x8*>(x + vec * 128 + l16 * 8);
     }
-    ss = half_warp_sum(ss);
-    if (vec < nvec) {
-      const float n = sqrtf(ss);
-      const float inv = 1.f / fmaxf(n, eps);
-      if (l16 == 0) inv_norm[vec] = n > eps ? inv : -inv;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] *= inv;
-      *reinterpret_cast<bf16x8*>(x + vec * 128 + l16 * 8) = pack8(f);
+    for (int j = 0; j < 4; ++j) {
+      const long vec = v0 + j * 2 + half;
+      float f[8];
+      float ss = 0.f;
+      if (vec < nvec) {
+        unpack8(p[j], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+      }
+      ss = half_warp_sum(ss);
+      if (vec < nvec) {
+        const float n = sqrtf(ss);
+        const float inv = 1.f / fmaxf(n, eps);
+        if (l16 == 0) inv_norm[vec] = n > eps ? inv : -inv;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] *= inv;
+        *reinterpret_cast<bf16x8*>(x + vec * 128 + l16 * 8) = pack8(f);
+      }
     }
   }
 }
@@ -461,36 +498,39 @@ __global__ void __launch_bounds__(256) l2norm128_bwd_kernel(bf16* __restrict__ d
                                                             const float* __restrict__ inv_norm,
                                                             long nvec) {
   const int lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15;
-  const long v0 = (blockIdx.x * static_cast<long>(blockDim.x >> 5) + (threadIdx.x >> 5)) * 8;
-  bf16x8 pg[4], py[4];
-  float invs[4];
+  const long wstride = static_cast<long>(gridDim.x) * (blockDim.x >> 5) * 8;
+  for (long v0 = (blockIdx.x * static_cast<long>(blockDim.x >> 5) + (threadIdx.x >> 5)) * 8;
+       v0 < nvec; v0 += wstride) {
+    bf16x8 pg[4], py[4];
+    float invs[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const long vec = v0 + j * 2 + half;
-    if (vec < nvec) {
-      pg[j] = *reinterpret_cast<const bf16x8*>(dxn + vec * 128 + l16 * 8);
-      py[j] = *reinterpret_cast<const bf16x8*>(xn + vec * 128 + l16 * 8);
-      invs[j] = inv_norm[vec];
+    for (int j = 0; j < 4; ++j) {
+      const long vec = v0 + j * 2 + half;
+      if (vec < nvec) {
+        pg[j] = *reinterpret_cast<const bf16x8*>(dxn + vec * 128 + l16 * 8);
+        py[j] = *reinterpret_cast<const bf16x8*>(xn + vec * 128 + l16 * 8);
+        invs[j] = inv_norm[vec];
+      }
     }
-  }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const long vec = v0 + j * 2 + half;
-    float g[8], y[8];
-    float dot = 0.f;
-    if (vec < nvec) {
-      unpack8(pg[j], g);
-      unpack8(py[j], y);
+    for (int j = 0; j < 4; ++j) {
+      const long vec = v0 + j * 2 + half;
+      float g[8], y[8];
+      float dot = 0.f;
+      if (vec < nvec) {
+        unpack8(pg[j], g);
+        unpack8(py[j], y);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dot += g[i] * y[i];
-    }
-    dot = half_warp_sum(dot);
-    if (vec < nvec) {
-      float inv = invs[j];
-      if (inv < 0.f) { inv = -inv; dot = 0.f; }
+        for (int i = 0; i < 8; ++i) dot += g[i] * y[i];
+      }
+      dot = half_warp_sum(dot);
+      if (vec < nvec) {
+        float inv = invs[j];
+        if (inv < 0.f) { inv = -inv; dot = 0.f; }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) g[i] = inv * (g[i] - y[i] * dot);
-      *reinterpret_cast<bf16x8*>(dxn + vec * 128 + l16 * 8) = pack8(g);
+        for (int i = 0; i < 8; ++i) g[i] = inv * (g[i] - y[i] * dot);
+        *reinterpret_cast<bf16x8*>(dxn + vec * 128 + l16 * 8) = pack8(g);
+      }
     }
   }
 }
@@ -654,7 +694,13 @@ PB_API int pb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const vo
   bf16* dx_ = static_cast<bf16*>(dx);
   float* part = static_cast<float*>(scratch);
   if (d <= 2048) {
-    rmsnorm_bwd_kernel<<<grid, 256, 0, st>>>(dy_, h_, w_, r_, dr_, dx_, part, rows, d);
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           RMS_BWD_SMEM);
+      attr_set = true;
+    }
+    rmsnorm_bwd_kernel<<<grid, 256, RMS_BWD_SMEM, st>>>(dy_, h_, w_, r_, dr_, dx_, part, rows, d);
   } else {
     const size_t smem = (d + 33) * sizeof(float);
     if (smem > 48 * 1024)
@@ -697,7 +743,7 @@ PB_API int pb_l2norm_fwd(void* x, void* inv_norm, long nvec, int D, float eps, c
   if (D % 4 != 0) return PB_BAD_ARG;
   if (D == 128 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
     const long warps = (nvec + 7) / 8;
-    l2norm128_fwd_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(
+    l2norm128_fwd_kernel<<<grid_for((warps + 7) / 8, 1, 148 * 8), 256, 0, st>>>(
         static_cast<bf16*>(x), static_cast<float*>(inv_norm), nvec, eps);
     return cudaGetLastError();
   }
@@ -711,7 +757,7 @@ PB_API int pb_l2norm_bwd(void* dxn, const void* xn, const void* inv_norm, long n
   if (D % 4 != 0) return PB_BAD_ARG;
   if (D == 128 && ((reinterpret_cast<uintptr_t>(dxn) | reinterpret_cast<uintptr_t>(xn)) & 15) == 0) {
     const long warps = (nvec + 7) / 8;
-    l2norm128_bwd_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(
+    l2norm128_bwd_kernel<<<grid_for((warps + 7) / 8, 1, 148 * 8), 256, 0, st>>>(
         static_cast<bf16*>(dxn), static_cast<const bf16*>(xn),
         static_cast<const float*>(inv_norm), nvec);
     return cudaGetLastError();

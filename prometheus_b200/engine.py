@@ -119,7 +119,8 @@ class Trainer:
         # weights and gradients are handled exactly as under data parallelism.
         self.cp = bool(context_parallel) and self.world > 1
         self.cp_ctx = None
-        if self.cp and (model_config.mtp_heads or model_config.n_mla or expert_parallel):
+        has_mla = any(M.attention_kind(i, model_config) is M.AttentionKind.MLA for i in range(model_config.n_layers))
+        if self.cp and (model_config.mtp_heads or has_mla or expert_parallel):
             raise ValueError("context parallelism supports the delta-rule + GQA hybrids without MTP heads, "
                              "MLA layers or expert parallelism")
         # per-layer, per-head largest attention logit of the last forward (the statistic the
