@@ -481,10 +481,10 @@ class Trainer:
         cfg = self.cfg
         nh, dh, _ = M.head_geometry(cfg)
         pre = f"layers.{i}."
-        q = ops.linear(n, self.p[pre + "q"]).view(B, S, nh, dh)
-        k = ops.linear(n, self.p[pre + "k"]).view(B, S, nh, dh)
+        # q and k are normalised over their own projection outputs (no copy)
+        q = ops.l2norm_(ops.linear(n, self.p[pre + "q"]), dh).view(B, S, nh, dh)
+        k = ops.l2norm_(ops.linear(n, self.p[pre + "k"]), dh).view(B, S, nh, dh)
         v = ops.linear(n, self.p[pre + "v"]).view(B, S, nh, dh)
-        q, k = ops.l2norm(q), ops.l2norm(k)
         if cfg.delta_beta == "sigmoid":
             wb = self.p[pre + "beta"]
             beta = torch.sigmoid(_SmallLinear.apply(n, wb)).view(B, S, nh)

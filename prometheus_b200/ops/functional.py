@@ -291,6 +291,40 @@ def l2norm(x: Tensor, eps: float = 1e-6) -> Tensor:
     return _L2NormFn.apply(x, eps)
 
 
+class _L2NormInplaceFn(torch.autograd.Function):
+    """The same normalisation written over its input, for a tensor that nothing else reads: the
+    fresh output of a projection whose backward needs only its own input and weight. The
+    gradient is transformed in place as well (it is the fresh output of the consumer's
+    backward). Saves the two device-to-device copies of the out-of-place form."""
+
+    @staticmethod
+    def forward(ctx, x, D, eps):
+        if not x.is_contiguous():
+            raise ValueError("l2norm_ needs a contiguous tensor")
+        ctx.mark_dirty(x)
+        nvec = x.numel() // D
+        inv = torch.empty(nvec, dtype=torch.float32, device=x.device)
+        call("pb_l2norm_fwd", ptr(x), ptr(inv), nvec, D, float(eps), stream_ptr())
+        ctx.save_for_backward(x, inv)
+        ctx.D = D
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        xn, inv = ctx.saved_tensors
+        g = g.contiguous()
+        call("pb_l2norm_bwd", ptr(g), ptr(xn), ptr(inv), xn.numel() // ctx.D, ctx.D, stream_ptr())
+        return g, None, None
+
+
+def l2norm_(x: Tensor, head_dim: int, eps: float = 1e-6) -> Tensor:
+    """In-place ``l2norm`` over consecutive groups of ``head_dim`` elements of a contiguous tensor
+    (``(tokens, heads * head_dim)`` straight out of a projection). Returns ``x``."""
+    if x.shape[-1] % head_dim:
+        raise ValueError("last dimension must be a multiple of head_dim")
+    return _L2NormInplaceFn.apply(x, head_dim, eps)
+
+
 # ---------------------------------------------------------------------------
 # soft-cap + cross-entropy over the vocabulary, fused with the unembedding GEMMs
 # ---------------------------------------------------------------------------

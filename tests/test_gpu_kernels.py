@@ -190,6 +190,26 @@ def test_l2norm_fwd_bwd():
     _close(x.grad, xr.grad, 3e-2)
 
 
+def test_l2norm_inplace_over_a_projection_output():
+    """The in-place form on the output of a linear layer: values and the gradients of the
+    layer's input and weight equal the out-of-place composition; D = 64 takes the generic kernel."""
+    from prometheus_b200.ops import functional as ops
+
+    for heads, D in ((4, 128), (8, 64)):
+        x = _r(300, 256, seed=1).requires_grad_(True)
+        w = _r(heads * D, 256, seed=2, scale=0.1).requires_grad_(True)
+        g = _r(300, heads, D, seed=3)
+        y = ops.l2norm_(ops.linear(x, w), D).view(300, heads, D)
+        (y.float() * g.float()).sum().backward()
+        xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+        pr = (xr @ wr.t()).view(300, heads, D)
+        yr = pr / pr.norm(dim=-1, keepdim=True).clamp(min=1e-6)
+        (yr * g.float()).sum().backward()
+        _close(y, yr)
+        _close(x.grad, xr.grad, 4e-2)
+        _close(w.grad if w.grad is not None else w.main_grad, wr.grad, 4e-2)
+
+
 @pytest.mark.parametrize("cap", [30.0, 0.0])
 def test_softcap_ce_fused(cap):
     from prometheus_b200.ops import functional as ops
