@@ -110,15 +110,6 @@ __global__ void sum_slots_kernel(const float* slots, int world, float* out) {
   }
 }
 
-__device__ __forceinline__ void load8(const float* p, float* f) {
-  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-}
-__device__ __forceinline__ void store8(float* p, const float* f) {
-  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
-  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
-}
-
 __device__ __forceinline__ float clip_scale_dev(const float* gnorm_sq, float clip) {
   if (gnorm_sq == nullptr || clip <= 0.f) return 1.f;
   const float n = sqrtf(fmaxf(*gnorm_sq, 0.f));
@@ -126,7 +117,6 @@ __device__ __forceinline__ float clip_scale_dev(const float* gnorm_sq, float cli
 }
 
 // AdamW on [lo, lo+n) of the slab; bf16 result stored into every rank's copy.
-template <int W>
 __global__ void __launch_bounds__(256) adamw_bcast_kernel(
     float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
     float* __restrict__ v, PeerPtrs lp, int world, long lo, long n, float lr, float b1, float b2,
@@ -136,31 +126,26 @@ __global__ void __launch_bounds__(256) adamw_bcast_kernel(
   const long n8 = n >> 3;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
-    const long e = lo + i * 8;      // lo and the slab bases are 32-byte aligned: float4 accesses
-    float o[8], gg[8], mm[8], vv[8], pp[8];
-    load8(g + e, gg); load8(m + e, mm); load8(v + e, vv); load8(p + e, pp);
+    const long e = lo + i * 8;
+    float o[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float gi = gg[j] * s;
-      mm[j] = b1 * mm[j] + (1.f - b1) * gi;
-      vv[j] = b2 * vv[j] + (1.f - b2) * gi * gi;
-      o[j] = pp[j] * (1.f - lr * wd) - lr * (mm[j] * inv_bc1) / (sqrtf(vv[j] * inv_bc2) + eps);
+      const float gi = g[e + j] * s;
+      const float mi = b1 * m[e + j] + (1.f - b1) * gi;
+      const float vi = b2 * v[e + j] + (1.f - b2) * gi * gi;
+      m[e + j] = mi;
+      v[e + j] = vi;
+      const float pi = p[e + j] * (1.f - lr * wd) - lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
+      p[e + j] = pi;
+      o[j] = pi;
     }
-    store8(m + e, mm); store8(v + e, vv); store8(p + e, o);
     const bf16x8 pk = pack8(o);
-    if (W > 0) {      // rank count known at compile time: the peer pointers stay in registers
-#pragma unroll
-      for (int r = 0; r < W; ++r)
-        *reinterpret_cast<bf16x8*>(static_cast<bf16*>(lp.p[r]) + e) = pk;
-    } else {
-      for (int r = 0; r < world; ++r)
-        *reinterpret_cast<bf16x8*>(static_cast<bf16*>(lp.p[r]) + e) = pk;
-    }
+    for (int r = 0; r < world; ++r)
+      *reinterpret_cast<bf16x8*>(static_cast<bf16*>(lp.p[r]) + e) = pk;
   }
 }
 
 // p -= lr (scale O + wd p) on [lo, lo+n); bf16 result stored into every rank's copy.
-template <int W>
 __global__ void __launch_bounds__(256) muon_apply_bcast_kernel(float* __restrict__ p,
                                                                const bf16* __restrict__ o,
                                                                PeerPtrs lp, int world, long lo,
@@ -170,21 +155,17 @@ __global__ void __launch_bounds__(256) muon_apply_bcast_kernel(float* __restrict
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
     const long e = lo + i * 8;
-    float ov[8], q[8], pp[8];
+    float ov[8], q[8];
     unpack8(*reinterpret_cast<const bf16x8*>(o + i * 8), ov);
-    load8(p + e, pp);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) q[j] = pp[j] - lr * (scale * ov[j] + wd * pp[j]);
-    store8(p + e, q);
-    const bf16x8 pk = pack8(q);
-    if (W > 0) {      // rank count known at compile time: the peer pointers stay in registers
-#pragma unroll
-      for (int r = 0; r < W; ++r)
-        *reinterpret_cast<bf16x8*>(static_cast<bf16*>(lp.p[r]) + e) = pk;
-    } else {
-      for (int r = 0; r < world; ++r)
-        *reinterpret_cast<bf16x8*>(static_cast<bf16*>(lp.p[r]) + e) = pk;
+    for (int j = 0; j < 8; ++j) {
+      const float pi = p[e + j];
+      q[j] = pi - lr * (scale * ov[j] + wd * pi);
+      p[e + j] = q[j];
     }
+    const bf16x8 pk = pack8(q);
+    for (int r = 0; r < world; ++r)
+      *reinterpret_cast<bf16x8*>(static_cast<bf16*>(lp.p[r]) + e) = pk;
   }
 }
 
@@ -283,24 +264,12 @@ PB_API int pb_adamw_bcast(void* p, const void* g, void* m, void* v, void* const*
                           cudaStream_t st) {
   if (step < 1 || world < 1 || world > MAX_RANKS || (lo & 7) != 0 || (n & 7) != 0) return PB_BAD_ARG;
   if (n == 0) return 0;
-  if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
-       reinterpret_cast<uintptr_t>(v)) & 15)
-    return PB_BAD_ARG;   // the slabs are read and written as float4
   const float inv_bc1 = 1.f / (1.f - powf(b1, static_cast<float>(step)));
   const float inv_bc2 = 1.f / (1.f - powf(b2, static_cast<float>(step)));
-#define PB_ADAMW(W)                                                                              \
-  adamw_bcast_kernel<W><<<cgrid(n, 16), 256, 0, st>>>(                                           \
-      static_cast<float*>(p), static_cast<const float*>(g), static_cast<float*>(m),              \
-      static_cast<float*>(v), make_peers(lp_ptrs, world), world, lo, n, lr, b1, b2, eps, wd,     \
-      inv_bc1, inv_bc2, static_cast<const float*>(gnorm_sq), clip, gscale)
-  switch (world) {
-    case 1: PB_ADAMW(1); break;
-    case 2: PB_ADAMW(2); break;
-    case 4: PB_ADAMW(4); break;
-    case 8: PB_ADAMW(8); break;
-    default: PB_ADAMW(0); break;
-  }
-#undef PB_ADAMW
+  adamw_bcast_kernel<<<cgrid(n, 16), 256, 0, st>>>(
+      static_cast<float*>(p), static_cast<const float*>(g), static_cast<float*>(m),
+      static_cast<float*>(v), make_peers(lp_ptrs, world), world, lo, n, lr, b1, b2, eps, wd,
+      inv_bc1, inv_bc2, static_cast<const float*>(gnorm_sq), clip, gscale);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -309,18 +278,8 @@ PB_API int pb_muon_apply_bcast(void* p, const void* o, void* const* lp_ptrs, int
                                long n, float lr, float scale, float wd, cudaStream_t st) {
   if (world < 1 || world > MAX_RANKS || (lo & 7) != 0 || (n & 7) != 0) return PB_BAD_ARG;
   if (n == 0) return 0;
-  if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(o)) & 15) return PB_BAD_ARG;
-#define PB_MUON(W)                                                                               \
-  muon_apply_bcast_kernel<W><<<cgrid(n, 16), 256, 0, st>>>(                                      \
-      static_cast<float*>(p), static_cast<const bf16*>(o), make_peers(lp_ptrs, world), world, lo, \
-      n, lr, scale, wd)
-  switch (world) {
-    case 1: PB_MUON(1); break;
-    case 2: PB_MUON(2); break;
-    case 4: PB_MUON(4); break;
-    case 8: PB_MUON(8); break;
-    default: PB_MUON(0); break;
-  }
-#undef PB_MUON
+  muon_apply_bcast_kernel<<<cgrid(n, 16), 256, 0, st>>>(
+      static_cast<float*>(p), static_cast<const bf16*>(o), make_peers(lp_ptrs, world), world, lo,
+      n, lr, scale, wd);
   return static_cast<int>(cudaGetLastError());
 }

@@ -104,11 +104,14 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w)
+        # the output is allocated here and returned as it is for 2-D inputs (not as a view of
+        # another tensor), so that a following in-place op (l2norm_) is legal for autograd
+        y = torch.empty((x2.shape[0], w.shape[0]), dtype=BF16, device=x.device)
+        gemm(x2, w, out=y)
         ctx.save_for_backward(x2, w)
         ctx.w_ref = w
         ctx.xshape = x.shape
-        return y.reshape(*x.shape[:-1], w.shape[0])
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
