@@ -482,9 +482,10 @@ class Trainer:
         nh, dh, _ = M.head_geometry(cfg)
         pre = f"layers.{i}."
         # q and k are normalised over their own projection outputs (no copy)
-        q = ops.l2norm_(ops.linear(n, self.p[pre + "q"]), dh).view(B, S, nh, dh)
-        k = ops.l2norm_(ops.linear(n, self.p[pre + "k"]), dh).view(B, S, nh, dh)
-        v = ops.linear(n, self.p[pre + "v"]).view(B, S, nh, dh)
+        q, k, v = ops.linear_multi(n, (self.p[pre + "q"], self.p[pre + "k"], self.p[pre + "v"]))
+        q = ops.l2norm_(q, dh).view(B, S, nh, dh)
+        k = ops.l2norm_(k, dh).view(B, S, nh, dh)
+        v = v.view(B, S, nh, dh)
         if cfg.delta_beta == "sigmoid":
             wb = self.p[pre + "beta"]
             beta = torch.sigmoid(_SmallLinear.apply(n, wb)).view(B, S, nh)
@@ -568,14 +569,14 @@ class Trainer:
         cfg = self.cfg
         nh, dh, nkv = M.head_geometry(cfg)
         pre = f"layers.{i}."
-        q = ops.linear(n, self.p[pre + "q"]).view(B, S, nh, dh)
-        k = ops.linear(n, self.p[pre + "k"]).view(B, S, nkv, dh)
-        v = ops.linear(n, self.p[pre + "v"]).view(B, S, nkv, dh)
+        q, k, v = ops.linear_multi(n, (self.p[pre + "q"], self.p[pre + "k"], self.p[pre + "v"]))
         pos = None
         if self.cp:      # global positions of this rank's slice
             pos = (torch.arange(S, dtype=torch.int32, device=n.device) + self.rank * S).repeat(B)
-        q = ops.rope_(q, seq_len=S, pos=pos, base=cfg.rope_base)
-        k = ops.rope_(k, seq_len=S, pos=pos, base=cfg.rope_base)
+        # rotary embedding over the projection outputs themselves (no copy)
+        q = ops.rope2d_(q, nh, seq_len=S, pos=pos, base=cfg.rope_base).view(B, S, nh, dh)
+        k = ops.rope2d_(k, nkv, seq_len=S, pos=pos, base=cfg.rope_base).view(B, S, nkv, dh)
+        v = v.view(B, S, nkv, dh)
         from .ops import attention
 
         if self.cp:

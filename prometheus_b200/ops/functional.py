@@ -135,6 +135,60 @@ def linear(x: Tensor, w: Tensor) -> Tensor:
     return _LinearFn.apply(x, w)
 
 
+class _LinearMultiFn(torch.autograd.Function):
+    """Several projections of one input (q, k, v of an attention layer): the forward is one GEMM per
+    weight, the backward adds the input gradients up inside the GEMM epilogues
+    (``dx = dy0 W0``, then ``dx = dy1 W1 + dx``, ...) instead of leaving autograd to sum separate
+    tensors with elementwise kernels. Weight gradients as in ``_LinearFn``."""
+
+    @staticmethod
+    def forward(ctx, x, *ws):
+        x2 = x.reshape(-1, x.shape[-1])
+        outs = []
+        for w in ws:
+            y = torch.empty((x2.shape[0], w.shape[0]), dtype=BF16, device=x.device)
+            gemm(x2, w, out=y)
+            outs.append(y if x.dim() == 2 else y.view(*x.shape[:-1], w.shape[0]))
+        ctx.save_for_backward(x2, *ws)
+        ctx.w_refs = ws
+        ctx.xshape = x.shape
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        x2, *ws = ctx.saved_tensors
+        dx = None
+        dws = []
+        for i, (dy, w) in enumerate(zip(dys, ws)):
+            if dy is None:
+                dws.append(None)
+                continue
+            dy2 = dy.reshape(-1, dy.shape[-1])
+            if not dy2.is_contiguous():
+                dy2 = dy2.contiguous()
+            if ctx.needs_input_grad[0]:
+                if dx is None:
+                    dx = gemm(dy2, w, b_mn=True)
+                else:
+                    gemm(dy2, w, b_mn=True, out=dx, d=dx, beta=1.0)
+            dw = None
+            if ctx.needs_input_grad[1 + i]:
+                mg = getattr(ctx.w_refs[i], "main_grad", None)
+                if mg is not None:
+                    gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, d=mg, beta=1.0)
+                else:
+                    dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+            dws.append(dw)
+        if dx is not None:
+            dx = dx.reshape(ctx.xshape)
+        return (dx, *dws)
+
+
+def linear_multi(x: Tensor, ws) -> tuple:
+    """``tuple(x @ W^T for W in ws)`` with the input gradients accumulated in the GEMM epilogues."""
+    return _LinearMultiFn.apply(x, *ws)
+
+
 # ---------------------------------------------------------------------------
 # RMSNorm (+ residual)
 # ---------------------------------------------------------------------------
@@ -235,6 +289,39 @@ def rope_(x: Tensor, *, seq_len: int, pos: Tensor | None = None, base: float = 1
     n_pairs = x.shape[-1] // 2
     rot = n_pairs if not partial else max(1, n_pairs // 2)
     return _RopeFn.apply(x, pos, seq_len, base, rot)
+
+
+class _RopeInplaceFn(torch.autograd.Function):
+    """Rotary embedding written over a fresh projection output ``(tokens, heads * D)`` (and, in the
+    backward, over the incoming gradient): no copies. Same kernel as ``rope_``."""
+
+    @staticmethod
+    def forward(ctx, x, heads, pos, seq_len, base, rot_pairs):
+        if not x.is_contiguous() or x.dim() != 2 or x.shape[1] % heads:
+            raise ValueError("rope2d_ needs a contiguous (tokens, heads * D) tensor")
+        ctx.mark_dirty(x)
+        D = x.shape[1] // heads
+        ctx.args = (x.shape[0], heads, D, rot_pairs, seq_len, base)
+        ctx.pos = pos
+        call("pb_rope", ptr(x), ptr(pos), x.shape[0], heads, D, rot_pairs, seq_len, float(base), 0,
+             stream_ptr())
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        tokens, heads, D, rot_pairs, seq_len, base = ctx.args
+        call("pb_rope", ptr(g), ptr(ctx.pos), tokens, heads, D, rot_pairs, seq_len, float(base), 1,
+             stream_ptr())
+        return g, None, None, None, None, None
+
+
+def rope2d_(x: Tensor, heads: int, *, seq_len: int, pos: Tensor | None = None, base: float = 10000.0,
+            partial: bool = False) -> Tensor:
+    """In-place rotary embedding of a projection output ``(tokens, heads * D)``; returns ``x``."""
+    n_pairs = (x.shape[-1] // heads) // 2
+    rot = n_pairs if not partial else max(1, n_pairs // 2)
+    return _RopeInplaceFn.apply(x, heads, pos, seq_len, base, rot)
 
 
 class _SwigluFn(torch.autograd.Function):

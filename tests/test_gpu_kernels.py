@@ -190,6 +190,37 @@ def test_l2norm_fwd_bwd():
     _close(x.grad, xr.grad, 3e-2)
 
 
+def test_linear_multi_and_inplace_rope_equal_the_separate_ops():
+    """Three projections of one input with the input gradients summed in the GEMM epilogues, rotary
+    embedding written over the projection outputs: values and all gradients against fp32."""
+    from prometheus_b200 import model
+    from prometheus_b200.ops import functional as ops
+
+    T, S, d, H, Hkv, D = 600, 300, 256, 4, 2, 128
+    x = _r(T, d, seed=1).requires_grad_(True)
+    ws = [_r(H * D, d, seed=2, scale=0.1).requires_grad_(True), _r(Hkv * D, d, seed=3, scale=0.1).requires_grad_(True),
+          _r(Hkv * D, d, seed=4, scale=0.1).requires_grad_(True)]
+    gs = [_r(T, H * D, seed=5), _r(T, Hkv * D, seed=6), _r(T, Hkv * D, seed=7)]
+    q, k, v = ops.linear_multi(x, ws)
+    q = ops.rope2d_(q, H, seq_len=S)
+    k = ops.rope2d_(k, Hkv, seq_len=S)
+    sum((o.float() * g.float()).sum() for o, g in zip((q, k, v), gs)).backward()
+
+    xr = x.detach().float().requires_grad_(True)
+    wr = [w.detach().float().requires_grad_(True) for w in ws]
+    pos = torch.arange(S, device="cuda")
+    qr = model.rope((xr @ wr[0].t()).view(T // S, S, H, D), (xr @ wr[0].t()).view(T // S, S, H, D), pos, partial=False)[0]
+    kr = model.rope((xr @ wr[1].t()).view(T // S, S, Hkv, D), (xr @ wr[1].t()).view(T // S, S, Hkv, D), pos, partial=False)[0]
+    vr = xr @ wr[2].t()
+    outs_r = (qr.reshape(T, H * D), kr.reshape(T, Hkv * D), vr)
+    sum((o * g.float()).sum() for o, g in zip(outs_r, gs)).backward()
+    for got, want in zip((q, k, v), outs_r):
+        _close(got, want)
+    _close(x.grad, xr.grad, 4e-2)
+    for w, r in zip(ws, wr):
+        _close(w.grad, r.grad, 4e-2)
+
+
 def test_l2norm_inplace_over_a_projection_output():
     """The in-place form on the output of a linear layer: values and the gradients of the
     layer's input and weight equal the out-of-place composition; D = 64 takes the generic kernel."""
