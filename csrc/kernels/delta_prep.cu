@@ -250,7 +250,7 @@ delta_prep_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
 //   dbeta_i += sum_{j<i} dA_ij G_ij                  dG = diag(beta) tril(dA, -1)
 //   dK += (dG + dG^T) K + tril(dM)^T Q               dQ += tril(dM) K
 //
-// Eleven tcgen05 products in four rounds with 64-row operands; the 64 x 64 intermediates
+// Eleven tcgen05 products in four passes with 64-row operands; the 64 x 64 intermediates
 // go through one shared-memory tile, re-used as K-major or MN-major operand as needed, so
 // no transposes are materialised. The column sum for dbeta is the diagonal of dA'^T T,
 // also a tensor-core product.
@@ -378,7 +378,7 @@ delta_prep_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const float beta = p.beta_f32 ? static_cast<const float*>(p.beta)[bidx]
                                   : bf16_to_f32(static_cast<const bf16*>(p.beta)[bidx]);
     bool ok = true;
-    // ---- round 1: dA' parts and dV ----
+    // ---- pass 1: dA' parts and dV ----
     if (r == 0) {
       ok = mbar_wait(full, ph, p.status);
       if (ok) {
@@ -431,7 +431,7 @@ delta_prep_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
-    // ---- round 2: X = dA' A'^T, Y = dA'^T T (diagonal = dbeta part), dK = A'^T dW ----
+    // ---- pass 2: X = dA' A'^T, Y = dA'^T T (diagonal = dbeta part), dK = A'^T dW ----
     if (r == 0) {
       tc_fence_after();
       tma_store_3d(&tmDV, smem + NDU, x0, row0, 0);
@@ -462,7 +462,7 @@ delta_prep_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
-    // ---- round 3: -dA = T^T X, G = K K^T ----
+    // ---- pass 3: -dA = T^T X, G = K K^T ----
     if (r == 0) {
       tc_fence_after();
 #pragma unroll
@@ -497,7 +497,7 @@ delta_prep_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
-    // ---- round 4: dK += dG K + dG^T K + tril(dM)^T Q ; dQ = tril(dM) K ----
+    // ---- pass 4: dK += dG K + dG^T K + tril(dM)^T Q ; dQ = tril(dM) K ----
     if (r == 0) {
       ok = mbar_wait(fullq, ph, p.status);
       if (ok) {
