@@ -179,8 +179,8 @@ def main() -> int:
             args.seqs_per_gpu = 8
         if args.micro_batch == 8:
             # top-6 routing keeps six expert-side copies of every token's activations per MoE
-            # layer: 8192 tokens per micro-batch keep the 27 MoE layers' saved activations near 22 GB
-            args.micro_batch = 2
+            # layer: 16384 tokens per micro-batch keep the 27 MoE layers' saved activations near 55 GB
+            args.micro_batch = 4
         trainer_kw = dict(fp8=True, expert_parallel=world > 1)
         model_name = "moe-16B (28L d2048, 64 routed top-6 + 2 shared experts h1408, FP8 e4m3 block-scaled linears)"
     if args.layers:
