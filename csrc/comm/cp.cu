@@ -171,13 +171,13 @@ PB_API int pb_cp_compose(void* local_buf, const void* s0, void* out, int rank, i
                          int reverse, int epoch, long budget_ns, int* status, cudaStream_t st) {
   if (world < 1 || world > cp::MAX_RANKS || rank < 0 || rank >= world || bh <= 0 || epoch <= 0)
     return PB_BAD_ARG;
-  static bool attr_set = false;
+  static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
   const int smem = 2 * cp::MAT * 4;
-  if (!attr_set) {
+  if (attr_once.need()) {
     cudaError_t e = cudaFuncSetAttribute(cp::cp_compose_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_once.done();
   }
   cp::cp_compose_kernel<<<bh, 256, smem, st>>>(local_buf, static_cast<const float*>(s0),
                                                static_cast<float*>(out), rank, world, bh, reverse,

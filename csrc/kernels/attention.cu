@@ -703,12 +703,12 @@ PB_API int pb_attn_fwd_cp(const void* q, const void* k, const void* v, void* out
       seq % 256 != 0 || !(scale > 0.f) || q_off < 0 || q_off % 256 != 0 || seq_kv % 128 != 0 ||
       seq_kv < q_off + seq)
     return PB_BAD_ARG;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
+  if (attr_once.need()) {
     cudaError_t e = cudaFuncSetAttribute(fwd::attn_fwd_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, fwd::SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_once.done();
   }
   const uint64_t rows = static_cast<uint64_t>(batch) * seq, krows = static_cast<uint64_t>(batch) * seq_kv;
   CUtensorMap tQ, tK, tV, tO;
@@ -748,15 +748,15 @@ PB_API int pb_attn_bwd_cp(const void* q, const void* k, const void* v, const voi
   if (bad_geometry(batch, seq, heads, kv_heads, ldq, ldkv) || ldo < heads * D || ldo % 8 != 0 ||
       !(scale > 0.f) || q_off < 0 || q_off % 128 != 0 || seq_kv % 128 != 0 || seq_kv < q_off + seq)
     return PB_BAD_ARG;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
+  if (attr_once.need()) {
     cudaError_t e = cudaFuncSetAttribute(bwd::attn_bwd_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, bwd::SMEM);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(bwd::attn_bwd_kernel<true>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, bwd::SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_once.done();
   }
   const uint64_t rows = static_cast<uint64_t>(batch) * seq, krows = static_cast<uint64_t>(batch) * seq_kv;
   const uint64_t qi = static_cast<uint64_t>(heads) * D, ki = static_cast<uint64_t>(kv_heads) * D;

@@ -14,6 +14,30 @@
 
 namespace pb {
 
+// One-time launcher set-up keyed by device. cudaFuncSetAttribute (the opt-in to more than
+// 48 KB of dynamic shared memory) and occupancy queries apply to the device that is current
+// when they are made, and one process may drive several GPUs, so a plain `static bool` would
+// leave every device after the first without the attribute. Usage:
+//   static DeviceOnce once;  if (once.need()) { ...set-up...; once.done(); }
+// Host threads may race on the first call of a device: the set-up is idempotent, the bits are
+// set with atomic read-modify-write builtins.
+struct DeviceOnce {
+  unsigned long long bits[4] = {0ull, 0ull, 0ull, 0ull};   // up to 256 device ordinals
+  static int current() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return dev < 0 ? 0 : (dev & 255);
+  }
+  bool need() const {
+    const int d = current();
+    return ((__atomic_load_n(&bits[d >> 6], __ATOMIC_ACQUIRE) >> (d & 63)) & 1ull) == 0ull;
+  }
+  void done() {
+    const int d = current();
+    __atomic_fetch_or(&bits[d >> 6], 1ull << (d & 63), __ATOMIC_RELEASE);
+  }
+};
+
 typedef __nv_bfloat16 bf16;
 typedef __nv_bfloat162 bf162;
 

@@ -561,12 +561,12 @@ PB_API int pb_delta_prep_fwd(const void* q, const void* k, const void* v, const 
   using namespace dprep;
   if (batch <= 0 || heads <= 0 || seq_len <= 0 || seq_len % C != 0 || ld < heads * D || ld % 8)
     return PB_BAD_ARG;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
+  if (attr_once.need()) {
     cudaError_t e = cudaFuncSetAttribute(delta_prep_fwd_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_once.done();
   }
   Params p;
   p.n_chunks = seq_len / C; p.heads = heads; p.seq_len = seq_len;
@@ -607,13 +607,13 @@ PB_API int pb_delta_prep_bwd(const void* q, const void* k, const void* v, const 
   using namespace dprep;
   if (batch <= 0 || heads <= 0 || seq_len <= 0 || seq_len % C != 0 || ld < heads * D || ld % 8)
     return PB_BAD_ARG;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
+  if (attr_once.need()) {
     cudaError_t e = cudaFuncSetAttribute(delta_prep_bwd_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          bwd::SMEM_BWD);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_once.done();
   }
   BwdParams p;
   p.n_chunks = seq_len / C; p.heads = heads; p.seq_len = seq_len;

@@ -385,13 +385,13 @@ delta_scan_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 template <bool BWD>
 int launch(const void* W, const void* Q, const void* K, const void* M, const void* fifth,
            void* xb_out, void* u_out, void* o_out, int ld, const Params& p, cudaStream_t st) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
+  if (attr_once.need()) {
     cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<BWD>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Smem<BWD>::TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_once.done();
   }
   const uint64_t G = static_cast<uint64_t>(p.n_seq) * p.n_chunks;
   const uint64_t rows = G * C;

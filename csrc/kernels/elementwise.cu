@@ -694,11 +694,11 @@ PB_API int pb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const vo
   bf16* dx_ = static_cast<bf16*>(dx);
   float* part = static_cast<float*>(scratch);
   if (d <= 2048) {
-    static bool attr_set = false;
-    if (!attr_set) {
+    static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
+    if (attr_once.need()) {
       cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            RMS_BWD_SMEM);
-      attr_set = true;
+      attr_once.done();
     }
     rmsnorm_bwd_kernel<<<grid, 256, RMS_BWD_SMEM, st>>>(dy_, h_, w_, r_, dr_, dx_, part, rows, d);
   } else {
@@ -800,7 +800,7 @@ PB_API int pb_sigmoid(const void* x, void* y, long n, cudaStream_t st) {
 // Limits and rules (also stated in pb200_noalloc.h):
 //  * d <= PB_NOALLOC_MAX_D (2048) and d % 8 == 0; larger widths are rejected with
 //    PB_BAD_ARG and nothing is launched.
-//  * The array (PB_NOALLOC_MAX_PARTS x PB_NOALLOC_MAX_D floats, about 4.6 MiB) is
+//  * The array (PB_NOALLOC_MAX_PARTS x PB_NOALLOC_MAX_D floats, about 2.3 MiB) is
 //    part of the library image: every GPU that loads the library holds it until
 //    the process exits.
 //  * The first call on each device looks up the array's device address
@@ -811,7 +811,8 @@ PB_API int pb_sigmoid(const void* x, void* y, long n, cudaStream_t st) {
 //    that overlap on the GPU (different streams) race on it: serialise them.
 // ---------------------------------------------------------------------------
 #define PB_NOALLOC_MAX_D 2048
-#define PB_NOALLOC_MAX_PARTS (148 * 4)
+// widths up to 2048 run the column-owner kernel, whose grid is at most two CTAs per SM
+#define PB_NOALLOC_MAX_PARTS (148 * 2)
 #define PB_NOALLOC_MAX_DEVICES 64
 
 static __device__ __align__(256) float g_noalloc_rms_partials[PB_NOALLOC_MAX_PARTS * PB_NOALLOC_MAX_D];
@@ -830,13 +831,15 @@ PB_API int pb_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void* w, 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= PB_NOALLOC_MAX_DEVICES) return PB_BAD_ARG;
-  if (g_noalloc_addr[dev] == nullptr) {
+  float* scratch = __atomic_load_n(&g_noalloc_addr[dev], __ATOMIC_ACQUIRE);
+  if (scratch == nullptr) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_noalloc_rms_partials);
     if (e != cudaSuccess) return static_cast<int>(e);
-    g_noalloc_addr[dev] = static_cast<float*>(ptr);
+    scratch = static_cast<float*>(ptr);
+    __atomic_store_n(&g_noalloc_addr[dev], scratch, __ATOMIC_RELEASE);
   }
-  return pb_rmsnorm_bwd(dy, h, w, rstd, dres, dx, dw, g_noalloc_addr[dev], accumulate, rows, d, st);
+  return pb_rmsnorm_bwd(dy, h, w, rstd, dres, dx, dw, scratch, accumulate, rows, d, st);
 }
 
 PB_API int pb_rmsnorm_bwd_noalloc_max_d() { return PB_NOALLOC_MAX_D; }

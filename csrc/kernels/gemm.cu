@@ -747,13 +747,13 @@ template <int BN>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                 const GemmParams& p, int max_ctas,
                 cudaStream_t st) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
+  if (attr_once.need()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          GemmSmem<BN>::TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_once.done();
   }
   const long tiles =
       static_cast<long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
@@ -767,7 +767,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
 // Launch of the CTA-pair kernel: clusters of two, as many pairs as can be resident.
 int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                  const GemmParams& p, int max_ctas, cudaStream_t st) {
-  static bool attr_set = false;
+  static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
   static int max_pairs = 0;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -778,7 +778,7 @@ int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorM
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (!attr_set) {
+  if (attr_once.need()) {
     cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Gemm2Smem::TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -788,7 +788,7 @@ int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorM
     if (e != cudaSuccess) { cudaGetLastError(); n = num_sms() / 2; }
     max_pairs = n > 0 ? n : num_sms() / 2;
     if (max_pairs > num_sms() / 2) max_pairs = num_sms() / 2;
-    attr_set = true;
+    attr_once.done();
   }
   const long tiles = static_cast<long>((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
   long pairs = max_pairs;

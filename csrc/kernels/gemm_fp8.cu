@@ -337,12 +337,12 @@ PB_API int pb_gemm_fp8_blockscaled(const void* Aq, const float* sa, const void* 
   if ((reinterpret_cast<uintptr_t>(Aq) & 15) || (reinterpret_cast<uintptr_t>(Bq) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
     return PB_BAD_ARG;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
+  if (attr_once.need()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_once.done();
   }
   CUtensorMap tmA, tmB, tmC;
   int r = make_tmap_3d(&tmA, Aq, 1, K, M, 1, K, 0, BK, BM);

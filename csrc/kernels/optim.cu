@@ -49,6 +49,17 @@ __global__ void fold_scalar_kernel(const float* __restrict__ partial, int nparts
   if (threadIdx.x == 0) out[0] = accumulate ? out[0] + s : s;
 }
 
+// out[j] = sum_b partial[j * nparts + b] for every matrix j = blockIdx.x: one warp each, the
+// same fixed order as fold_scalar_kernel.
+__global__ void fold_rows_kernel(const float* __restrict__ partial, int nparts,
+                                 float* __restrict__ out) {
+  const float* p = partial + static_cast<long>(blockIdx.x) * nparts;
+  float s = 0.f;
+  for (int b = threadIdx.x; b < nparts; b += 32) s += p[b];
+  s = warp_sum(s);
+  if (threadIdx.x == 0) out[blockIdx.x] = s;
+}
+
 // scale = clip / (norm + 1e-6) if norm > clip else 1   (clip <= 0: 1)
 __device__ __forceinline__ float clip_scale(const float* gnorm_sq, float clip) {
   if (gnorm_sq == nullptr || clip <= 0.f) return 1.f;
@@ -79,7 +90,9 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p,
   }
 }
 
-// m = beta*m + s*g;  partial sums of nesterov^2 with nesterov = s*g + beta*m
+// m = beta*m + s*g;  partial sums of nesterov^2 with nesterov = s*g + beta*m.
+// blockIdx.y selects one of gridDim.y equally sized matrices laid out back to back; the
+// partials of matrix j are partial[j * gridDim.x .. (j + 1) * gridDim.x).
 __global__ void __launch_bounds__(256) muon_momentum_kernel(const float* __restrict__ g,
                                                             float* __restrict__ m, long n,
                                                             float beta,
@@ -88,6 +101,9 @@ __global__ void __launch_bounds__(256) muon_momentum_kernel(const float* __restr
                                                             float* __restrict__ partial) {
   __shared__ float scratch[33];
   const float s = clip_scale(gnorm_sq, clip) * gscale;
+  g += static_cast<long>(blockIdx.y) * n;
+  m += static_cast<long>(blockIdx.y) * n;
+  partial += static_cast<long>(blockIdx.y) * gridDim.x;
   float acc = 0.f;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
@@ -109,7 +125,10 @@ __global__ void __launch_bounds__(256) muon_normalize_kernel(const float* __rest
                                                              float clip, float gscale,
                                                              const float* __restrict__ nes_sq) {
   const float s = clip_scale(gnorm_sq, clip) * gscale;
-  const float fro = sqrtf(fmaxf(*nes_sq, 0.f));
+  g += static_cast<long>(blockIdx.y) * n;
+  m += static_cast<long>(blockIdx.y) * n;
+  x0 += static_cast<long>(blockIdx.y) * n;
+  const float fro = sqrtf(fmaxf(nes_sq[blockIdx.y], 0.f));
   const float inv = fro > 1e-7f ? 1.f / fro : 0.f;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
@@ -160,6 +179,62 @@ __global__ void transpose_bf16_kernel(const bf16* __restrict__ in, bf16* __restr
     const int c = bx + j, r = by + threadIdx.x;
     if (r < rows && c < cols) out[boff + static_cast<size_t>(c) * rows + r] = tile[threadIdx.x][j];
   }
+}
+
+// QK-clip on observed logits. max_logit[h] is the largest scaled attention logit query head h
+// produced during the step; a head over `tau` has its logits pulled back to tau by scaling the
+// rows of its query projection and of its key projection. Query heads that share a key head
+// (G per group): the key rows take fk = sqrt(min(1, tau / max over the group)), query head h
+// takes min(1, tau / max_h) / fk, so every head's logits scale by exactly min(1, tau / max_h).
+// One block per weight row; rows [row0, row0 + rows) of the (heads * dh, cols) matrix are in
+// `master` (fp32, may be null) and `lp` (bf16, may be null).
+__global__ void __launch_bounds__(256) qk_clip_rescale_kernel(float* __restrict__ master,
+                                                              bf16* __restrict__ lp, int rows,
+                                                              int cols, int dh, int group,
+                                                              int n_q_heads, int is_k, long row0,
+                                                              const float* __restrict__ max_logit,
+                                                              float tau) {
+  const long r = blockIdx.x;
+  if (r >= rows) return;
+  const int head = static_cast<int>((row0 + r) / dh);
+  const int kv = is_k ? head : head / group;
+  float mg = 0.f;
+  for (int j = 0; j < group; ++j) {
+    const int h = kv * group + j;
+    if (h < n_q_heads) mg = fmaxf(mg, max_logit[h]);
+  }
+  const float fk = sqrtf(mg > tau ? tau / mg : 1.f);
+  float f = fk;
+  if (!is_k) {
+    const float mh = max_logit[head];
+    f = (mh > tau ? tau / mh : 1.f) / fk;
+  }
+  if (f == 1.f) return;
+  const long base = r * static_cast<long>(cols);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    if (master != nullptr) {
+      const float v = master[base + c] * f;
+      master[base + c] = v;
+      if (lp != nullptr) lp[base + c] = f32_to_bf16(v);
+    } else if (lp != nullptr) {
+      lp[base + c] = f32_to_bf16(bf16_to_f32(lp[base + c]) * f);
+    }
+  }
+}
+
+// 64-bit position-weighted checksum of a flat buffer of 32-bit words (silent-data-corruption
+// probe: every replica of a shard must produce the same value). Partials are combined with
+// integer adds, so the result does not depend on the grid.
+__global__ void __launch_bounds__(256) checksum_u32_kernel(const uint32_t* __restrict__ x, long n,
+                                                           unsigned long long* __restrict__ out) {
+  unsigned long long acc = 0ull;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const unsigned long long w = x[i];
+    acc += (w + 0x9E3779B97F4A7C15ull) * (static_cast<unsigned long long>(i) * 2ull + 1ull);
+  }
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) atomicAdd(out, acc);
 }
 
 static inline int ogrid(long n, int per_thread = 4) {
@@ -232,10 +307,61 @@ PB_API int pb_muon_prepare(const void* g, void* m, void* x0, long n, float beta,
   return cudaGetLastError();
 }
 
+// The same over `nb` matrices of `n` elements each, back to back in g, m and x0: three
+// launches for the whole shape class instead of three per matrix, bit-identical results.
+// scratch: nb * (pb_sumsq_nparts(n) + 1) floats.
+PB_API int pb_muon_prepare_batched(const void* g, void* m, void* x0, long n, int nb, float beta,
+                                   const void* gnorm_sq, float clip, float gscale, void* scratch,
+                                   cudaStream_t st) {
+  if (nb <= 0 || n <= 0) return PB_BAD_ARG;
+  const int parts = pb_sumsq_nparts(n);
+  float* part = static_cast<float*>(scratch);
+  float* nes_sq = part + static_cast<long>(parts) * nb;
+  for (int j0 = 0; j0 < nb; j0 += 32768) {      // gridDim.y limit is 65535
+    const int cnt = nb - j0 < 32768 ? nb - j0 : 32768;
+    const float* gj = static_cast<const float*>(g) + static_cast<long>(j0) * n;
+    float* mj = static_cast<float*>(m) + static_cast<long>(j0) * n;
+    bf16* xj = static_cast<bf16*>(x0) + static_cast<long>(j0) * n;
+    float* pj = part + static_cast<long>(j0) * parts;
+    muon_momentum_kernel<<<dim3(parts, cnt), 256, 0, st>>>(gj, mj, n, beta,
+                                                         static_cast<const float*>(gnorm_sq),
+                                                         clip, gscale, pj);
+    fold_rows_kernel<<<cnt, 32, 0, st>>>(pj, parts, nes_sq + j0);
+    muon_normalize_kernel<<<dim3(ogrid(n), cnt), 256, 0, st>>>(
+        gj, mj, xj, n, beta, static_cast<const float*>(gnorm_sq), clip, gscale, nes_sq + j0);
+  }
+  return cudaGetLastError();
+}
+
 PB_API int pb_muon_apply(void* p, const void* o, void* p_lp, long n, float lr, float scale,
                          float wd, cudaStream_t st) {
   muon_apply_kernel<<<ogrid(n), 256, 0, st>>>(static_cast<float*>(p), static_cast<const bf16*>(o),
                                               static_cast<bf16*>(p_lp), n, lr, scale, wd);
+  return cudaGetLastError();
+}
+
+// See qk_clip_rescale_kernel. rows / row0 select a row range of the projection (a row shard);
+// `group` = query heads per key head; is_k = 1 for the key projection (heads = key heads).
+PB_API int pb_qk_clip_rescale(void* master, void* lp, int rows, int cols, int dh, int group,
+                              int n_q_heads, int is_k, long row0, const void* max_logit,
+                              float tau, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (cols <= 0 || dh <= 0 || group <= 0 || n_q_heads <= 0 || tau <= 0.f || max_logit == nullptr ||
+      (master == nullptr && lp == nullptr))
+    return PB_BAD_ARG;
+  qk_clip_rescale_kernel<<<rows, 256, 0, st>>>(static_cast<float*>(master), static_cast<bf16*>(lp),
+                                               rows, cols, dh, group, n_q_heads, is_k, row0,
+                                               static_cast<const float*>(max_logit), tau);
+  return cudaGetLastError();
+}
+
+// out[0] (uint64, zeroed here) = checksum of n 32-bit words at x.
+PB_API int pb_checksum_u32(const void* x, long n, void* out, cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(out, 0, 8, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (n > 0)
+    checksum_u32_kernel<<<ogrid(n), 256, 0, st>>>(static_cast<const uint32_t*>(x), n,
+                                                  static_cast<unsigned long long*>(out));
   return cudaGetLastError();
 }
 

@@ -16,7 +16,7 @@
  *
  * Returns 0 on success, a CUDA error code, or 3 (bad argument) when d is not a
  * multiple of 8 or exceeds pb_rmsnorm_bwd_noalloc_max_d() (2048): nothing is
- * launched in that case. The array costs about 4.6 MiB on every GPU that loads the
+ * launched in that case. The array costs about 2.3 MiB on every GPU that loads the
  * library, for the life of the process. The first call on a device resolves the
  * array's address; make it before starting a stream capture on that device. All
  * calls on a device share the array, so calls that overlap on the GPU race:

@@ -85,6 +85,15 @@ class _EmbedFn(torch.autograd.Function):
         return None, None
 
 
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded device-side wait (peer flag, barrier, mbarrier) ran out during a step: the
+    gradients or weights of that step may be partial. Carries the latched code."""
+
+    def __init__(self, code: int, rank: int, step: int):
+        super().__init__(f"device-side wait timed out (code {code}) on rank {rank} at step {step}")
+        self.code, self.rank, self.step = int(code), int(rank), int(step)
+
+
 class Trainer:
     """Single-process-per-GPU trainer for the hybrid configurations: delta-rule and GQA
     attention layers, dense SwiGLU or mixture-of-experts (routed + shared) FFNs."""
@@ -93,7 +102,10 @@ class Trainer:
                  params: dict | None = None, seed: int = 0, device="cuda", micro_batch: int = 4,
                  muon_weight_decay: float = 0.0, process_group=None, ce_chunk_rows: int = 4096,
                  grad_sync: str = "auto", expert_parallel: bool = False,
-                 ep_capacity_factor: float = 2.0, fp8: bool = False, context_parallel: bool = False):
+                 ep_capacity_factor: float = 2.0, fp8: bool = False, context_parallel: bool = False,
+                 z_loss_mode: str = "layers_logits", router_bias_rule: str = "count",
+                 allow_fallback: bool = False, recurrence: int = 1,
+                 truncated_recurrence: int = M.TRUNCATED_RECURRENCE, check_status_every: int = 1):
         M.validate_config(model_config)
         T.validate_train_config(train_config)
         self.cfg, self.tcfg = model_config, train_config
@@ -132,6 +144,36 @@ class Trainer:
         if self.ep and model_config.n_routed_experts % self.world:
             raise ValueError("expert parallelism needs n_routed_experts divisible by the world size")
         self.ce_chunk_rows = int(ce_chunk_rows)
+        # router z-loss: "layers_logits" = mean over the MoE layer applications of
+        # mean(logsumexp(router logits)^2), the model's own definition
+        # (model/__init__.py:975-995 of the reference); "last_probs" = the reference train
+        # step's form, the last MoE layer's sigmoid scores (train/__init__.py:785,909).
+        if z_loss_mode not in ("layers_logits", "last_probs"):
+            raise ValueError("z_loss_mode must be 'layers_logits' or 'last_probs'")
+        self.z_loss_mode = z_loss_mode
+        # aux-loss-free balancing statistic, per MoE layer: "count" = share of the top-k
+        # assignments (what the dispatch really sends to an expert), "probs" = mean router
+        # score per expert (the reference's rule, train/__init__.py:810).
+        if router_bias_rule not in ("count", "probs"):
+            raise ValueError("router_bias_rule must be 'count' or 'probs'")
+        self.router_bias_rule = router_bias_rule
+        # head dims the tcgen05 delta-rule / attention kernels do not cover raise unless the
+        # caller opts into the PyTorch / library forms (test-sized models)
+        self.allow_fallback = bool(allow_fallback)
+        # depth recurrence: the core block runs `recurrence` times per forward with the prelude
+        # output injected from the second iteration on; gradient flows through the last
+        # `truncated_recurrence` iterations (model/__init__.py:932-970 of the reference)
+        if int(recurrence) < 1 or int(truncated_recurrence) < 1:
+            raise ValueError("recurrence and truncated_recurrence must be >= 1")
+        self.recurrence = int(recurrence)
+        self.truncated_recurrence = int(truncated_recurrence)
+        # the kernels latch a status word when a bounded wait runs out; every
+        # `check_status_every`-th step reads it back with the loss and raises (0: never)
+        self.check_status_every = int(check_status_every)
+        self.router_records: list = []
+        self._router_load: dict[int, Tensor] = {}
+        self.moe_load: Tensor | None = None          # (MoE layers, experts) load shares, last step
+        self.last_max_logits: Tensor | None = None   # (GQA layers, heads) largest logits, last step
         self.step_count = 0
         self.launches = 0
         self.router_bias: dict[int, Tensor] = {}
@@ -345,6 +387,9 @@ class Trainer:
         nparts = max(_lib.query("pb_sumsq_nparts", max(n_m, n_a, n_v, 1)), 1)
         if self.sym is not None:
             nparts = max(nparts, _lib.query("pb_reduce_nparts", max(n_m, n_a, n_v, 1)))
+        for k_ in self.unit_classes:        # batched Muon prepare: (partials + 1) per owned matrix
+            nb_ = self.own_units[k_][1] - self.own_units[k_][0]
+            nparts = max(nparts, nb_ * (_lib.query("pb_sumsq_nparts", k_[0] * k_[1]) + 1))
         self.opt_scratch = torch.empty(nparts + 8, **f32)
         self.gnorm_sq = torch.zeros(1, **f32)
         self.local_sq = torch.zeros(1, **f32)
@@ -482,15 +527,18 @@ class Trainer:
         nh, dh, _ = M.head_geometry(cfg)
         pre = f"layers.{i}."
         # q and k are normalised over their own projection outputs (no copy)
-        q, k, v = ops.linear_multi(n, (self.p[pre + "q"], self.p[pre + "k"], self.p[pre + "v"]))
+        if cfg.delta_beta == "sigmoid":
+            # the per-head write gate rides along as a fourth (skinny) projection of the same
+            # input on the same kernel; its input gradient folds into the shared dx epilogue
+            q, k, v, bl = ops.linear_multi(n, (self.p[pre + "q"], self.p[pre + "k"], self.p[pre + "v"],
+                                               self.p[pre + "beta"]))
+            beta = torch.sigmoid(bl).view(B, S, nh)
+        else:
+            q, k, v = ops.linear_multi(n, (self.p[pre + "q"], self.p[pre + "k"], self.p[pre + "v"]))
+            beta = torch.ones((B, S, nh), dtype=BF16, device=n.device)
         q = ops.l2norm_(q, dh).view(B, S, nh, dh)
         k = ops.l2norm_(k, dh).view(B, S, nh, dh)
         v = v.view(B, S, nh, dh)
-        if cfg.delta_beta == "sigmoid":
-            wb = self.p[pre + "beta"]
-            beta = torch.sigmoid(_SmallLinear.apply(n, wb)).view(B, S, nh)
-        else:
-            beta = torch.ones((B, S, nh), dtype=BF16, device=n.device)
         if self.cp:
             from .parallel.cp import DeltaCpContext, delta_rule_cp
 
@@ -499,7 +547,8 @@ class Trainer:
             o = delta_rule_cp(q, k, v, beta, self.cp_ctx)
         else:
             o, _ = kernels.chunked_delta_rule(q, k, v, beta, None,
-                                              kernels.LinearAttnConfig(chunk=cfg.chunk))
+                                              kernels.LinearAttnConfig(chunk=cfg.chunk),
+                                              allow_fallback=self.allow_fallback)
         return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
 
     def _ffn_linear(self, x: Tensor, w: Tensor) -> Tensor:
@@ -514,6 +563,9 @@ class Trainer:
         split, the unit-weight QK RMSNorm and the softmax core are PyTorch (the reference's
         tiny / flagship geometries, not a benchmark path)."""
         cfg = self.cfg
+        if not self.allow_fallback:
+            raise ValueError("MLA layers run their softmax core on the library attention; "
+                             "construct the Trainer with allow_fallback=True to use them")
         nh = M.head_geometry(cfg)[0]
         dn, dr, _ = self.mla_dims
         pre = f"layers.{i}."
@@ -549,21 +601,41 @@ class Trainer:
             if self.ep_ctx is None:
                 rows = int(self.ep_capacity_factor * T_ * cfg.top_k) + 128 * el
                 self.ep_ctx = EpContext(self.sym, cfg.d_model, cfg.n_routed_experts, rows)
-            out, probs, ids = ep_moe_ffn(n2, self.p[pre + "router"], self.router_bias.get(i), w_gu,
-                                         w_dn, cfg.top_k, self.ep_ctx,
-                                         shapes=((el, 2 * hid, cfg.d_model), (el, cfg.d_model, hid)))
+            out, probs, ids, logits = ep_moe_ffn(
+                n2, self.p[pre + "router"], self.router_bias.get(i), w_gu, w_dn, cfg.top_k, self.ep_ctx,
+                shapes=((el, 2 * hid, cfg.d_model), (el, cfg.d_model, hid)), return_logits=True)
             for j in range(cfg.n_shared_experts):
                 gu = ops.linear(n2, self.p[pre + f"shared{j}_gate_up"])
                 out = out + ops.linear(ops.swiglu(gu), self.p[pre + f"shared{j}_down"])
-            self.last_router = (probs, ids)
+            self._record_router(i, probs, ids, logits)
             return out
         n_e = cfg.n_routed_experts + cfg.n_shared_experts
-        out, probs, ids = moe.moe_ffn(n2, self.p[pre + "router"], self.router_bias.get(i),
-                                      w_gu, w_dn, cfg.top_k, n_shared=cfg.n_shared_experts,
-                                      shapes=((n_e, 2 * hid, cfg.d_model), (n_e, cfg.d_model, hid)),
-                                      fp8=self.fp8)
-        self.last_router = (probs, ids)
+        out, probs, ids, logits = moe.moe_ffn(
+            n2, self.p[pre + "router"], self.router_bias.get(i), w_gu, w_dn, cfg.top_k,
+            n_shared=cfg.n_shared_experts,
+            shapes=((n_e, 2 * hid, cfg.d_model), (n_e, cfg.d_model, hid)), fp8=self.fp8,
+            return_logits=True)
+        self._record_router(i, probs, ids, logits)
         return out
+
+    def _record_router(self, layer: int, probs: Tensor, ids: Tensor, logits: Tensor) -> None:
+        """One MoE layer application of the current micro-batch: the z-loss term (kept in the
+        graph) and the per-layer balancing statistic (detached)."""
+        self.last_router = (probs, ids)
+        if self.tcfg.z_loss_weight and self.z_loss_mode == "layers_logits":
+            z = torch.logsumexp(logits, dim=-1).square().mean()
+        else:
+            z = None
+        self.router_records.append((layer, z, probs))
+        if self.router_bias:
+            with torch.no_grad():
+                if self.router_bias_rule == "count":
+                    stat = torch.bincount(ids.reshape(-1).long(),
+                                          minlength=self.cfg.n_routed_experts).float()
+                else:
+                    stat = probs.detach().sum(dim=0)
+            acc = self._router_load.get(layer)
+            self._router_load[layer] = stat if acc is None else acc + stat
 
     def _gqa_layer(self, n: Tensor, i: int, B: int, S: int) -> Tensor:
         cfg = self.cfg
@@ -585,23 +657,26 @@ class Trainer:
             o = cp_attention(q, k, v, self.pg)
             return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
         if self.track_max_logit:
-            o, rowmax = attention.causal_gqa(q, k, v, return_max_logit=True)
-            self.max_logits[i] = rowmax.amax(dim=(0, 2))      # per head, for QK-clip
+            o, rowmax = attention.causal_gqa(q, k, v, return_max_logit=True,
+                                             allow_fallback=self.allow_fallback)
+            m = rowmax.amax(dim=(0, 2)).float()               # per head, for QK-clip
+            prev = self.max_logits.get(i)
+            self.max_logits[i] = m if prev is None else torch.maximum(prev, m)
         else:
-            o = attention.causal_gqa(q, k, v)
+            o = attention.causal_gqa(q, k, v, allow_fallback=self.allow_fallback)
         return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
 
-    def forward_hidden(self, tokens: Tensor, inputs_embeds: Tensor | None = None) -> Tensor:
-        """Final-norm hidden states (B*S, d) in bf16 for a (B, S) token batch."""
+    def _layers(self, x: Tensor, res: Tensor | None, start: int, count: int, B: int, S: int):
+        """Layers ``start .. start + count`` on a residual stream held as a pending sum
+        ``x + res`` (``res`` None: the stream is ``x``). The add is fused into the next
+        normalisation, so the pair is also what comes back."""
         cfg = self.cfg
-        B, S = tokens.shape
-        if inputs_embeds is None:
-            h = _EmbedFn.apply(tokens, self.p["embed"]).reshape(B * S, cfg.d_model)
-        else:
-            h = inputs_embeds.reshape(B * S, cfg.d_model)
-        n = ops.rmsnorm(h, self.p["layers.0.pre_attn_norm"])
-        for i in range(cfg.n_layers):
+        for i in range(start, start + count):
             pre = f"layers.{i}."
+            if res is None:
+                n, h = ops.rmsnorm(x, self.p[pre + "pre_attn_norm"]), x
+            else:
+                n, h = ops.add_rmsnorm(x, res, self.p[pre + "pre_attn_norm"])
             if self.layer_kinds[i] is M.AttentionKind.LINEAR:
                 a = self._delta_layer(n, i, B, S)
             elif self.layer_kinds[i] is M.AttentionKind.MLA:
@@ -614,8 +689,70 @@ class Trainer:
                 f = self._ffn_linear(ops.swiglu(gu), self.p[pre + "down"])
             else:
                 f = self._moe_layer(n2, i)
-            nxt = f"layers.{i + 1}.pre_attn_norm" if i + 1 < cfg.n_layers else "final_norm"
-            n, h = ops.add_rmsnorm(f, h, self.p[nxt])
+            x, res = f, h
+        return x, res
+
+    def _adapt_thoughts(self, thoughts: Tensor) -> Tensor:
+        """Thought vectors (B, n, d) -> residual-stream rows: SiLU MLP + RMSNorm, the products
+        on the tcgen05 GEMM (model/__init__.py:601-614 of the reference)."""
+        from .ops import latent as LK
+
+        B, n, d = thoughts.shape
+        t2 = thoughts.to(BF16).reshape(B * n, d).contiguous()
+        a = ops.linear(LK._SiluFn.apply(ops.linear(t2, self.p["adapter_w1"])), self.p["adapter_w2"])
+        return ops.rmsnorm(a, self.p["adapter_norm"]).view(B, n, d)
+
+    def forward_hidden(self, tokens: Tensor, inputs_embeds: Tensor | None = None, *,
+                       r: int | None = None, thoughts: Tensor | None = None) -> Tensor:
+        """Final-norm hidden states (B*S, d) in bf16 for a (B, S) token batch.
+
+        ``r`` core-block iterations (default: the trainer's ``recurrence``): iteration 0 runs the
+        core block on the prelude output, every later one on ``carry + prelude output``; the
+        carry entering the last ``truncated_recurrence`` iterations is detached, so the earlier
+        iterations run without a graph. ``thoughts`` (B, n, d) are adapter-mapped and prepended;
+        their positions are dropped from the result. Reference: model/__init__.py:866-881,
+        928-971."""
+        cfg = self.cfg
+        B, S = tokens.shape
+        if inputs_embeds is None:
+            h = _EmbedFn.apply(tokens, self.p["embed"]).reshape(B, S, cfg.d_model)
+        else:
+            h = inputs_embeds.reshape(B, S, cfg.d_model)
+        n_th = 0
+        if thoughts is not None and thoughts.shape[1] > 0:
+            n_th = int(thoughts.shape[1])
+            h = torch.cat([self._adapt_thoughts(thoughts), h], dim=1)
+            S = S + n_th
+        h = h.reshape(B * S, cfg.d_model)
+        r_used = self.recurrence if r is None else int(r)
+        if r_used < 1:
+            raise ValueError("r must be >= 1")
+        prelude, core, coda = M._recurrent_split(cfg)
+        x, res = self._layers(h, None, 0, prelude, B, S)
+        if r_used == 1:
+            x, res = self._layers(x, res, prelude, core, B, S)
+        else:
+            injected = x if res is None else x + res
+            cut = r_used - min(self.truncated_recurrence, r_used)
+
+            def iterate(carry, first):
+                if first:
+                    return self._layers(injected, None, prelude, core, B, S)
+                xs, rs = carry
+                return self._layers(xs + rs, injected, prelude, core, B, S)
+
+            carry = None
+            with torch.no_grad():          # iterations whose output is cut off from the graph
+                for it in range(cut):
+                    carry = iterate(carry, it == 0)
+            for it in range(cut, r_used):
+                carry = iterate(carry, it == 0)
+            x, res = carry
+        x, res = self._layers(x, res, prelude + core, coda, B, S)
+        n = ops.rmsnorm(x, self.p["final_norm"]) if res is None else \
+            ops.add_rmsnorm(x, res, self.p["final_norm"])[0]
+        if n_th:
+            n = n.view(B, S, cfg.d_model)[:, n_th:].reshape(B * (S - n_th), cfg.d_model)
         return n
 
     def set_latent_slots(self, slot_start: int, k: int, n_sweeps: int = 4,
@@ -661,6 +798,7 @@ class Trainer:
         the multi-token-prediction heads (head j predicts j + 1 tokens ahead from
         ``rmsnorm(h) @ proj + h`` with its own unembedding; mean over heads) and the router
         z-loss."""
+        self.router_records = []
         if self.cp:
             # tokens / mask carry one extra column: the first token of the next rank's slice
             # (anything with mask 0 on the last rank), so every local position has its target
@@ -692,11 +830,16 @@ class Trainer:
             ce = ce + ops.softcap_cross_entropy(mh, self.p[f"mtp.{j}.unembed"], tj,
                                                 (wj.reshape(-1) / (dj * n_mtp)).contiguous(),
                                                 float(self.tcfg.softcap), self.ce_chunk_rows)
-        if self.moe_layers and self.tcfg.z_loss_weight:
-            # mean squared log-sum-exp of the last MoE layer's router probabilities
-            probs, _ = self.last_router
-            z = torch.logsumexp(probs, dim=-1).square().mean()
+        if self.moe_layers and self.tcfg.z_loss_weight and self.router_records:
+            if self.z_loss_mode == "layers_logits":
+                # mean over every MoE layer application of mean(logsumexp(logits)^2)
+                zs = [z for _, z, _ in self.router_records if z is not None]
+                z = torch.stack(zs).mean()
+            else:
+                # the reference train step's form: the last MoE layer's sigmoid scores
+                z = torch.logsumexp(self.router_records[-1][2], dim=-1).square().mean()
             ce = ce + float(self.tcfg.z_loss_weight) * z * (self._micro_weight(loss_mask, denom))
+        self.router_records = []
         return ce
 
     @staticmethod
@@ -808,12 +951,11 @@ class Trainer:
                 continue
             n = rows * cols
             base = units[0].off + lo_u * n
-            x0 = self.ns_x[0]
-            for j in range(nb):
-                off = base + j * n
-                call("pb_muon_prepare", ptr(self.muon_grad[off:]), ptr(self.muon_mom[off:]),
-                     ptr(x0[j * n:]), n, beta, ptr(self.gnorm_sq), clip, gscale,
-                     ptr(self.opt_scratch), st)
+            # momentum, Nesterov and Frobenius normalisation of the whole shape class: three
+            # launches whatever the number of matrices
+            call("pb_muon_prepare_batched", ptr(self.muon_grad[base:]), ptr(self.muon_mom[base:]),
+                 ptr(self.ns_x[0]), n, nb, beta, ptr(self.gnorm_sq), clip, gscale,
+                 ptr(self.opt_scratch), st)
             xo = self._newton_schulz_class(rows, cols, nb, int(tc.muon_ns_steps))
             scale = T.muon_rms_scale(rows, cols)
             if self.sym is None or len(key) > 2:
@@ -840,7 +982,14 @@ class Trainer:
         self.step_count += 1
         t = self.step_count
         sched = T.wsd_lr(t, self.tcfg)
-        lr_mult = sched / float(self.tcfg.peak_lr)
+        peak = float(self.tcfg.peak_lr)
+        lr_mult = sched / peak if peak > 0 else 0.0
+        self._router_load = {}
+        clip_qk = float(self.tcfg.qk_clip) > 0 and not self.cp and any(
+            k_ is M.AttentionKind.GQA for k_ in self.layer_kinds) and \
+            M.head_geometry(self.cfg)[1] == 128
+        self.track_max_logit = clip_qk
+        self.max_logits = {}
         if loss_mask is None:
             loss_mask = torch.ones_like(tokens, dtype=torch.float32)
         denom = loss_mask[:, 1:].sum().float()
@@ -862,35 +1011,84 @@ class Trainer:
                 dist.all_reduce(dj, group=self.pg)
             mtp_denoms = list(dj.clamp(min=1.0))
         mb = self.micro_batch
-        load = None
         for b0 in range(0, tokens.shape[0], mb):
             l = self.loss(tokens[b0:b0 + mb], loss_mask[b0:b0 + mb], denom, mtp_denoms)
             l.backward()
             total += l.detach()
-            if self.router_bias:
-                ids = self.last_router[1].reshape(-1).long()
-                c = torch.bincount(ids, minlength=self.cfg.n_routed_experts).float()
-                load = c if load is None else load + c
-        if load is not None:
-            # aux-loss-free balancing: b <- b - u sign(load - mean), load = share of the
-            # assignments in the last MoE layer, applied to every router bias
+        if self.router_bias and self._router_load:
+            # aux-loss-free balancing, every MoE layer from its own load:
+            # b_i <- b_i - u sign(load_i - mean(load_i))
+            layers = sorted(self._router_load)
+            load = torch.stack([self._router_load[i] for i in layers])
             if self.world > 1:
                 import torch.distributed as dist
 
                 dist.all_reduce(load, group=self.pg)
-            load = load / load.sum().clamp(min=1.0)
-            delta = torch.sign(load - load.mean()) * self.router_bias_rate
-            for b in self.router_bias.values():
-                b.sub_(delta)
+            load = load / load.sum(dim=1, keepdim=True).clamp(min=1.0)
+            delta = torch.sign(load - load.mean(dim=1, keepdim=True)) * self.router_bias_rate
+            for row, i in enumerate(layers):
+                self.router_bias[i].sub_(delta[row])
+            self.moe_load = load            # (MoE layers, experts) shares, for the metrics
         self._sync_grads()
         if self.world > 1:
             import torch.distributed as dist
 
             dist.all_reduce(total, group=self.pg)
         self.optimizer_step(lr_mult)
+        if clip_qk and self.max_logits:
+            self._qk_clip()
         gnorm = self.gnorm_sq.sqrt()
         self.zero_grad()
-        return {"loss": total, "grad_norm": gnorm, "lr": sched, "step": t}
+        return {"loss": total, "grad_norm": gnorm, "lr": sched, "step": t,
+                "status": self.status_tensor()}
+
+    def _qk_clip(self) -> None:
+        """QK-clip on the logits the attention kernel saw this step: heads whose largest scaled
+        logit exceeded ``qk_clip`` have the rows of their query / key projections scaled so that
+        the same inputs would give exactly ``qk_clip`` (``pb_qk_clip_rescale``). Every rank
+        applies the same factors (the maxima are reduced over the ranks) to its bf16 copy and to
+        the fp32 masters it holds. Reference: train/__init__.py:478-500, 791-807 (there on the
+        weight rows themselves; here on observed logits)."""
+        cfg = self.cfg
+        nh, dh, nkv = M.head_geometry(cfg)
+        layers = sorted(self.max_logits)
+        m = torch.stack([self.max_logits[i] for i in layers]).contiguous()
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(m, op=dist.ReduceOp.MAX, group=self.pg)
+        tau = float(self.tcfg.qk_clip)
+        st = stream_ptr()
+        for row, i in enumerate(layers):
+            pre = f"layers.{i}."
+            for name, is_k, heads in ((pre + "q", 0, nh), (pre + "k", 1, nkv)):
+                w = self.p[name]
+                args = (heads * dh, cfg.d_model, dh, nh // nkv, nh, is_k, 0, ptr(m[row]), tau, st)
+                if self.sym is None:
+                    call("pb_qk_clip_rescale", ptr(w.master), ptr(w), *args)
+                else:
+                    # replicas must stay bit-identical: every rank rescales its bf16 copy from
+                    # the copy itself; the fp32 master is rescaled where it lives
+                    call("pb_qk_clip_rescale", ptr(w.master), None, *args)
+                    call("pb_qk_clip_rescale", None, ptr(w), *args)
+        self.last_max_logits = m
+
+    def status_tensor(self) -> Tensor:
+        """Device int32: non-zero when a bounded device-side wait of this rank's kernels or of the
+        peer-memory collectives ran out since the last check."""
+        st = ops.status_word(self.device)
+        if self.sym is not None:
+            return torch.maximum(st, self.sym.status.to(st.device))
+        return st
+
+    def raise_on_status(self, code: int) -> None:
+        """Turn a latched wait-timeout code into an exception and clear the words, so a step that
+        ran on partial gradients or stale weights is never silently kept."""
+        if code:
+            ops.status_word(self.device).zero_()
+            if self.sym is not None:
+                self.sym.status.zero_()
+            raise DeviceWaitTimeout(code, self.rank, self.step_count)
 
 
     def cp_slice(self, tokens: Tensor, loss_mask: Tensor | None = None):
@@ -914,32 +1112,10 @@ class Trainer:
         tok = host_tokens.to(self.device, non_blocking=True)
         mask = None if host_mask is None else host_mask.to(self.device, non_blocking=True)
         out = self.step(tok, mask)
-        host = torch.stack([out["loss"], out["grad_norm"].reshape(())]).cpu()
+        # the status word rides in the same read-back as the loss: no extra synchronisation
+        host = torch.stack([out["loss"], out["grad_norm"].reshape(()),
+                            out["status"].reshape(()).float()]).cpu()
+        if self.check_status_every and out["step"] % self.check_status_every == 0:
+            self.raise_on_status(int(host[2]))
         return {"loss": float(host[0]), "grad_norm": float(host[1]), "lr": out["lr"],
-                "step": out["step"]}
-
-
-class _SmallLinear(torch.autograd.Function):
-    """Skinny projection (a handful of output features, e.g. the per-head write gate):
-    library matmul, fp32 main-grad accumulation. Not a hot op (N = heads)."""
-
-    @staticmethod
-    def forward(ctx, x, w):
-        ctx.save_for_backward(x, w)
-        ctx.w_ref = w
-        return x @ w.t()
-
-    @staticmethod
-    def backward(ctx, dy):
-        x, w = ctx.saved_tensors
-        mg = getattr(ctx.w_ref, "main_grad", None)
-        dw = None
-        if mg is not None:
-            # bf16 operands, fp32 accumulation and output: no fp32 copy of the activations
-            try:
-                mg.add_(torch.mm(dy.t().contiguous(), x, out_dtype=torch.float32))
-            except (TypeError, RuntimeError, NotImplementedError):
-                mg.addmm_(dy.float().t(), x.float())
-        else:
-            dw = dy.t() @ x
-        return dy @ w, dw
+                "step": out["step"], "status": int(host[2])}

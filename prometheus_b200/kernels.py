@@ -198,14 +198,15 @@ def _chunked_delta_torch(q, k, v, beta, s0, chunk: int):
 
 
 def chunked_delta_rule(q, k, v, beta, state=None, config: LinearAttnConfig | None = None, *,
-                       initial_state=None):
+                       initial_state=None, allow_fallback: bool = False):
     """Gated delta-rule linear attention.
 
     q, k: (batch, seq, heads, dim_k); v: (batch, seq, heads, dim_v); beta: (batch, seq,
     heads) write gate. state: (batch, heads, dim_k, dim_v), zeros if None. Returns
     (output shaped like v, next_state). q and k are used as given (no L2 normalisation,
-    no 1/sqrt(d) scale). CUDA bf16 inputs run the fused sm_100a kernel; anything else
-    runs the fp32 torch implementation of the same chunked algorithm.
+    no 1/sqrt(d) scale). CUDA bf16 inputs run the fused sm_100a kernels (head dim 128,
+    chunk 64; another geometry raises unless ``allow_fallback``); CPU and fp32 inputs run
+    the fp32 torch implementation of the same chunked algorithm.
     """
     cfg = LinearAttnConfig() if config is None else config
     if cfg.chunk < 1:
@@ -215,7 +216,8 @@ def chunked_delta_rule(q, k, v, beta, state=None, config: LinearAttnConfig | Non
     if isinstance(q, Tensor) and q.is_cuda and q.dtype == torch.bfloat16:
         from .ops import delta as _delta_op
 
-        return _delta_op.delta_rule(q, k, v, beta, state, chunk=int(cfg.chunk))
+        return _delta_op.delta_rule(q, k, v, beta, state, chunk=int(cfg.chunk),
+                                    allow_fallback=allow_fallback)
     qf, kf, vf, bf, s0 = _validate_delta(q, k, v, beta, state)
     return _chunked_delta_torch(qf, kf, vf, bf, s0, int(cfg.chunk))
 

@@ -34,7 +34,10 @@ _SIGS = {
     "pb_sumsq_bf16": [P, L, P, P, I, P],
     "pb_adamw": [P, P, P, P, P, L, F, F, F, F, F, I, P, F, F, P],
     "pb_muon_prepare": [P, P, P, L, F, P, F, F, P, P],
+    "pb_muon_prepare_batched": [P, P, P, L, I, F, P, F, F, P, P],
     "pb_muon_apply": [P, P, P, L, F, F, F, P],
+    "pb_qk_clip_rescale": [P, P, I, I, I, I, I, I, L, P, F, P],
+    "pb_checksum_u32": [P, L, P, P],
     "pb_cast_f32_bf16": [P, P, L, F, P],
     "pb_axpy_bf16_f32": [P, P, L, F, P],
     "pb_transpose_bf16": [P, P, I, I, I, P],
@@ -122,7 +125,8 @@ def ptr(t) -> int | None:
 
 
 # kernels launched by one call of each entry point (for launch accounting)
-_LAUNCHES = {"pb_rmsnorm_bwd": 2, "pb_sumsq_f32": 2, "pb_sumsq_bf16": 2, "pb_muon_prepare": 3}
+_LAUNCHES = {"pb_rmsnorm_bwd": 2, "pb_sumsq_f32": 2, "pb_sumsq_bf16": 2, "pb_muon_prepare": 3,
+             "pb_muon_prepare_batched": 3}
 launch_count = 0
 
 

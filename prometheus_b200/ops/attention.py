@@ -123,15 +123,28 @@ def _fused_ok(q: Tensor, k: Tensor) -> bool:
             and q.shape[2] % k.shape[2] == 0)
 
 
+class UnsupportedGeometry(ValueError):
+    """A CUDA call whose shape the tcgen05 kernel does not cover, made without
+    ``allow_fallback=True``."""
+
+
 def causal_gqa(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None,
-               return_max_logit: bool = False):
+               return_max_logit: bool = False, allow_fallback: bool = False):
     """q: (B, S, Hq, D); k, v: (B, S, Hkv, D) -> (B, S, Hq, D).
 
     With ``return_max_logit`` also returns the largest scaled logit per (batch, head, row),
-    the statistic QK-clip needs (reference: train/__init__.py qk_clip)."""
+    the statistic QK-clip needs (reference: train/__init__.py qk_clip).
+
+    On a GPU the tcgen05 kernel covers bf16 with head dim 128; any other CUDA geometry raises
+    ``UnsupportedGeometry`` unless ``allow_fallback`` is set (then the library kernel or the
+    fp32 formula runs: test-sized models only). CPU tensors always use the fp32 formula."""
     d = q.shape[-1]
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     if not _fused_ok(q, k):
+        if q.is_cuda and not allow_fallback:
+            raise UnsupportedGeometry(
+                f"causal_gqa: no tcgen05 kernel for dtype {q.dtype}, head dim {d}, heads "
+                f"{q.shape[2]}/{k.shape[2]}; pass allow_fallback=True for the library form")
         if q.is_cuda and not return_max_logit:
             # head dims other than 128 (test-sized models): the library kernel, not the
             # O(S^2)-memory formula

@@ -270,10 +270,21 @@ def delta_rule_fused(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tenso
     return (out[:, :s] if pad else out), sfin
 
 
+class UnsupportedGeometry(ValueError):
+    """A CUDA call whose shape the tcgen05 kernels do not cover, made without
+    ``allow_fallback=True``."""
+
+
 def delta_rule(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tensor | None = None,
-               chunk: int = 64):
+               chunk: int = 64, allow_fallback: bool = False):
     """CUDA entry: bf16 in, bf16 out, fp32 state. Head dim 128 with chunk 64 runs the fused
-    tcgen05 path; other geometries use the chunk-parallel scan with recomputation."""
+    tcgen05 path. Other geometries raise ``UnsupportedGeometry`` unless ``allow_fallback`` is
+    set, in which case the chunk-parallel PyTorch scan with recomputation runs (test-sized
+    models only)."""
     if q.shape[-1] == 128 and v.shape[-1] == 128 and chunk == 64:
         return delta_rule_fused(q, k, v, beta, state)
+    if not allow_fallback:
+        raise UnsupportedGeometry(
+            f"delta_rule: no tcgen05 kernel for head dims {q.shape[-1]}/{v.shape[-1]} with chunk "
+            f"{chunk}; pass allow_fallback=True for the PyTorch scan")
     return _DeltaScanFn.apply(q, k, v, beta, state, chunk)

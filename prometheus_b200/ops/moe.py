@@ -159,10 +159,10 @@ class _MoeFfnFn(torch.autograd.Function):
         ctx.refs = (router_w, w_gu_p, w_down_p)
         ctx.top_k = top_k
         ctx.mark_non_differentiable(ids_r)
-        return out, probs, ids_r
+        return out, probs, ids_r, logits
 
     @staticmethod
-    def backward(ctx, d_out, d_probs, _di):
+    def backward(ctx, d_out, d_probs, _di, d_logits=None):
         from .functional import gemm
 
         x, router_w, w_gu, w_down, probs, ids, gates, xp, gu, hs, y = ctx.saved_tensors
@@ -192,6 +192,8 @@ class _MoeFfnFn(torch.autograd.Function):
              stream_ptr())
         if d_probs is not None:
             dlogits = dlogits + d_probs * probs * (1.0 - probs)
+        if d_logits is not None:
+            dlogits = dlogits + d_logits
         dl = dlogits.to(BF16)
         # dx = sum over slots of dxp rows + dlogits @ router_w
         dx_r = gemm(dl, router_w, b_mn=True)
@@ -219,14 +221,16 @@ def _expert_gemm(a: Tensor, w: Tensor, pl: Placement, use_fp8: bool) -> Tensor:
 
 
 def moe_ffn(x: Tensor, router_w: Tensor, router_bias: Tensor | None, w_gu: Tensor, w_down: Tensor,
-            top_k: int, n_shared: int = 0, shapes=None, fp8: bool = False):
+            top_k: int, n_shared: int = 0, shapes=None, fp8: bool = False, return_logits: bool = False):
     """Routed (+ shared) expert FFN. x [T, d] bf16; router_w [E, d]; w_gu [E + n_shared, 2h, d]
     (gate rows then up rows per expert; the shared experts last); w_down [E + n_shared, d, h].
     ``shapes`` gives those two 3-D shapes when the weights are passed as flat 2-D parameters.
     ``fp8``: forward expert products in block-scaled FP8 (straight-through bf16 backward).
-    Returns (out [T, d], probs [T, E] fp32, ids [T, k] int32); out and probs are differentiable."""
-    return _MoeFfnFn.apply(x, router_w, router_bias, w_gu, w_down, int(top_k), int(n_shared), shapes,
-                           bool(fp8))
+    Returns (out [T, d], probs [T, E] fp32, ids [T, k] int32); out and probs are differentiable.
+    ``return_logits`` appends the router logits [T, E] fp32 (differentiable: the router z-loss)."""
+    res = _MoeFfnFn.apply(x, router_w, router_bias, w_gu, w_down, int(top_k), int(n_shared), shapes,
+                          bool(fp8))
+    return res if return_logits else res[:3]
 
 
 def moe_ffn_ref(x, router_w, router_bias, w_gu, w_down, top_k, n_shared=0):

@@ -126,10 +126,10 @@ class _EpMoeFn(torch.autograd.Function):
         ctx.pl, ctx.local, ctx.ep = pl, local, ep
         ctx.refs = (router_w, w_gu_p, w_down_p)
         ctx.mark_non_differentiable(ids)
-        return out, probs, ids
+        return out, probs, ids, logits
 
     @staticmethod
-    def backward(ctx, d_out, d_probs, _di):
+    def backward(ctx, d_out, d_probs, _di, d_logits=None):
         from ..ops.functional import gemm
 
         (x, router_w, w_gu, w_down, probs, ids, gates, xp, gu, hs, y, dest_rank, dest_row,
@@ -166,6 +166,8 @@ class _EpMoeFn(torch.autograd.Function):
              stream_ptr())
         if d_probs is not None:
             dlogits = dlogits + d_probs * probs * (1.0 - probs)
+        if d_logits is not None:
+            dlogits = dlogits + d_logits
         dl = dlogits.to(BF16)
         dx_r = gemm(dl, router_w, b_mn=True)
         dx = ep.combine(dest_rank, dest_row, None, T, k, add=dx_r)
@@ -181,9 +183,12 @@ class _EpMoeFn(torch.autograd.Function):
 
 
 def ep_moe_ffn(x: Tensor, router_w: Tensor, router_bias: Tensor | None, w_gu_local: Tensor,
-               w_down_local: Tensor, top_k: int, ep: EpContext, shapes=None):
+               w_down_local: Tensor, top_k: int, ep: EpContext, shapes=None,
+               return_logits: bool = False):
     """Routed-expert FFN with the experts sharded over ``ep``'s ranks. x [T, d] are this rank's
     tokens; router_w [E, d] is replicated; w_gu_local [El, 2h, d] and w_down_local [El, d, h]
     are this rank's experts. Returns (out [T, d], probs [T, E], ids [T, k]). Collective: every
-    rank of the group must call it (same layer order), forward and backward."""
-    return _EpMoeFn.apply(x, router_w, router_bias, w_gu_local, w_down_local, int(top_k), ep, shapes)
+    rank of the group must call it (same layer order), forward and backward. ``return_logits``
+    appends the router logits [T, E] fp32 (differentiable)."""
+    res = _EpMoeFn.apply(x, router_w, router_bias, w_gu_local, w_down_local, int(top_k), ep, shapes)
+    return res if return_logits else res[:3]

@@ -5,16 +5,20 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def small_hybrid():
+def small_hybrid(**kw):
+    """Head dim 128: the delta-rule and attention layers of the compared step run the tcgen05
+    kernels, not a PyTorch form."""
     from prometheus_b200 import model
 
-    return model.ModelConfig(
+    base = dict(
         d_model=256, n_layers=4, n_dense=4, n_moe=0, n_linear_attn=3, n_mla=1,
         n_routed_experts=1, n_shared_experts=0, top_k=1, expert_hidden=512, mtp_heads=0,
         core_block_layers=4, recurrence_train_mean=1.0, recurrence_max=1, vocab_size=1024,
         max_context=256, prelude_layers=0, coda_layers=0, adapter_hidden=256,
-        n_heads=4, d_head=64, n_kv_heads=2, softmax_kind="gqa", softmax_every=4,
+        n_heads=2, d_head=128, n_kv_heads=1, softmax_kind="gqa", softmax_every=4,
         delta_beta="sigmoid", chunk=64, dense_hidden=512)
+    base.update(kw)
+    return model.ModelConfig(**base)
 
 
 def test_engine_matches_tree_step():
@@ -45,8 +49,8 @@ def test_engine_matches_tree_step():
         du_ref = (want[name].cpu() - before[name]).float()
         du_got = (got[name] - before[name]).float()
         cos = torch.nn.functional.cosine_similarity(du_ref.flatten(), du_got.flatten(), dim=0)
-        assert cos.item() > 0.9, f"{name}: update cosine {cos.item():.3f}"
-        assert 0.7 < du_got.norm().item() / (du_ref.norm().item() + 1e-12) < 1.4, name
+        assert cos.item() > 0.95, f"{name}: update cosine {cos.item():.3f}"
+        assert 0.85 < du_got.norm().item() / (du_ref.norm().item() + 1e-12) < 1.18, name
 
 
 def test_engine_overfits_fixed_batch():
@@ -94,16 +98,18 @@ def test_checkpoint_resume_is_bitwise(tmp_path):
                          fresh.cp.restore(cid))
 
 
-def small_moe():
+def small_moe(**kw):
     from prometheus_b200 import model
 
-    return model.ModelConfig(
+    base = dict(
         d_model=256, n_layers=4, n_dense=1, n_moe=3, n_linear_attn=3, n_mla=1,
         n_routed_experts=8, n_shared_experts=1, top_k=2, expert_hidden=128, mtp_heads=0,
         core_block_layers=4, recurrence_train_mean=1.0, recurrence_max=1, vocab_size=1024,
         max_context=256, prelude_layers=0, coda_layers=0, adapter_hidden=256,
-        n_heads=4, d_head=64, n_kv_heads=2, softmax_kind="gqa", softmax_every=4,
+        n_heads=2, d_head=128, n_kv_heads=1, softmax_kind="gqa", softmax_every=4,
         delta_beta="sigmoid", chunk=64, dense_hidden=512, router_bias=True)
+    base.update(kw)
+    return model.ModelConfig(**base)
 
 
 def test_moe_engine_matches_tree_forward_and_trains():
@@ -125,11 +131,15 @@ def test_moe_engine_matches_tree_forward_and_trains():
     dev_params = train._map_tree(params, lambda _n, p: p.cuda())
     batch = train.Batch(tokens=tokens.cuda(), loss_mask=torch.ones(4, 128, device="cuda"),
                         positions=torch.arange(128))
-    ref_total, _ = train.compute_loss(dev_params, batch, cfg, tcfg)
+    ref_total, _ = train.compute_loss(dev_params, batch, cfg, tcfg, z_on_logits=True)
     losses = [tr.step(tokens.cuda())["loss"].item() for _ in range(10)]
     assert abs(losses[0] - float(ref_total)) < 3e-2 * float(ref_total), (losses[0], float(ref_total))
     assert losses[-1] < losses[0] - 0.3, losses
-    assert any(b.abs().sum().item() > 0 for b in tr.router_bias.values())
+    assert all(b.abs().sum().item() > 0 for b in tr.router_bias.values())
+    # every MoE layer is steered by its own load, so the biases of two layers differ
+    b1, b2 = tr.router_bias[1], tr.router_bias[2]
+    assert not torch.equal(b1, b2)
+    assert tr.moe_load.shape == (3, cfg.n_routed_experts)
     from prometheus_b200.ops import functional as ops
     ops.check_status("cuda")
 
@@ -142,7 +152,13 @@ def test_tiny_reference_config_mla_moe_runs_in_the_engine():
     cfg = model.tiny_config()
     tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10)
     params = model.init_params(cfg, 0)
-    tr = engine.Trainer(cfg, tcfg, params=params, micro_batch=2)
+    # head dim 64 and MLA: outside the tcgen05 kernels' geometry, so the library forms are
+    # asked for explicitly; without the flag the trainer refuses
+    with pytest.raises(ValueError):
+        engine.Trainer(cfg, tcfg, params=params, micro_batch=2).step(
+            torch.randint(0, cfg.vocab_size, (2, 64), device="cuda"))
+    tr = engine.Trainer(cfg, tcfg, params=params, micro_batch=2, allow_fallback=True,
+                        z_loss_mode="last_probs")
     back = model.flatten_params(tr.export_tree())
     want = model.flatten_params(params)
     assert {"layers.3.W_kv_up", "layers.3.W_rope_k", "layers.3.W_kv_compress"} <= set(back)
@@ -205,3 +221,136 @@ def test_device_side_initialisation_of_large_models(monkeypatch):
                            generator=torch.Generator(device="cuda").manual_seed(0))
     losses = [tr.step(tokens)["loss"].item() for _ in range(8)]
     assert losses[-1] < losses[0] - 0.2, losses
+
+
+def test_depth_recurrence_matches_tree_forward_and_cuts_the_gradient():
+    """r = 3 core iterations with a prelude / core / coda split and gradient through the last
+    two: the engine's loss equals the fp32 tree model's at the same r, and nothing upstream of
+    the cut receives gradient from the iterations before it."""
+    from prometheus_b200 import engine, model, train
+
+    cfg = small_hybrid(prelude_layers=1, core_block_layers=2, coda_layers=1, recurrence_max=4)
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10)
+    params = model.init_params(cfg, 0)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 128), generator=torch.Generator().manual_seed(0)).cuda()
+    dev_params = train._map_tree(params, lambda _n, p: p.cuda())
+    batch = train.Batch(tokens=tokens, loss_mask=torch.ones(2, 128, device="cuda"),
+                        positions=torch.arange(128))
+    for r, trunc in ((3, 2), (2, 4), (1, 1)):
+        tr = engine.Trainer(cfg, tcfg, params=params, micro_batch=2, recurrence=r,
+                            truncated_recurrence=trunc)
+        with torch.no_grad():
+            hid = tr.forward_hidden(tokens).float()
+            want = model.forward(tokens, dev_params, cfg, r=r, truncated_recurrence=trunc).hidden
+        rel = (hid - want.reshape(hid.shape)).norm() / want.norm()
+        assert rel.item() < 3e-2, (r, rel.item())
+        ref_total, _ = train.compute_loss(dev_params, batch, cfg, tcfg, r=r)
+        got = tr.step(tokens)["loss"].item()
+        assert abs(got - float(ref_total)) < 3e-2 * float(ref_total), (r, got, float(ref_total))
+    # the cut: the gradient of a core-block weight equals the fp32 tree model's under the same
+    # truncation (one iteration of gradient, then all three), so nothing leaks through the detach
+    mask = torch.ones(2, 128, device="cuda")
+
+    def tree_grad(trunc):
+        live = train._map_tree(dev_params, lambda _n, p: p.clone().requires_grad_(True))
+        out = model.forward(tokens, live, cfg, r=3, truncated_recurrence=trunc)
+        ce = train.cross_entropy(train.soft_cap(out.logits[:, :-1, :], float(tcfg.softcap)),
+                                 tokens[:, 1:], mask[:, 1:])
+        wq = live["layers"][1]["W_q"]
+        (g,) = torch.autograd.grad(ce, [wq])
+        return g.reshape(g.shape[0], -1).t()            # engine layout (out, in)
+
+    grads = {}
+    for trunc in (1, 3):
+        tr = engine.Trainer(cfg, tcfg, params=params, micro_batch=2, recurrence=3,
+                            truncated_recurrence=trunc)
+        tr.loss(tokens, mask, mask[:, 1:].sum()).backward()
+        grads[trunc] = tr.p["layers.1.q"].main_grad.clone()
+        want = tree_grad(trunc)
+        cos = torch.nn.functional.cosine_similarity(grads[trunc].flatten(), want.flatten(), dim=0)
+        assert cos.item() > 0.95, (trunc, cos.item())
+        assert 0.85 < grads[trunc].norm().item() / want.norm().item() < 1.18, trunc
+        assert tr.p["layers.0.q"].main_grad.abs().sum() > 0     # the injection path stays live
+    assert not torch.allclose(grads[1], grads[3])
+
+
+def test_thoughts_are_prepended_and_dropped():
+    from prometheus_b200 import engine, model, train
+
+    cfg = small_hybrid()
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10)
+    params = model.init_params(cfg, 0)
+    tr = engine.Trainer(cfg, tcfg, params=params, micro_batch=2)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 120), generator=torch.Generator().manual_seed(0)).cuda()
+    thoughts = torch.randn(2, 8, cfg.d_model, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    dev_params = train._map_tree(params, lambda _n, p: p.cuda())
+    with torch.no_grad():
+        hid = tr.forward_hidden(tokens, thoughts=thoughts).float()
+        want = model.forward(tokens, dev_params, cfg, r=1, thoughts=thoughts).hidden
+    assert hid.shape == (2 * 120, cfg.d_model)
+    rel = (hid - want.reshape(hid.shape)).norm() / want.norm()
+    assert rel.item() < 3e-2, rel.item()
+
+
+def test_qk_clip_rescales_heads_over_the_threshold():
+    """A head whose observed logit exceeds qk_clip has its query / key rows scaled so that the
+    same inputs give exactly the threshold; heads under it are untouched (bit for bit)."""
+    from prometheus_b200 import engine, model, train
+    from prometheus_b200.ops._lib import call, ptr, stream_ptr
+
+    # the kernel against the formula, grouped heads (4 query heads on 2 key heads)
+    nh, nkv, dh, d = 4, 2, 128, 64
+    wq = torch.randn(nh * dh, d, device="cuda")
+    wk = torch.randn(nkv * dh, d, device="cuda")
+    wq_lp, wk_lp = wq.bfloat16(), wk.bfloat16()
+    mx = torch.tensor([50.0, 400.0, 120.0, 90.0], device="cuda")
+    tau = 100.0
+    q0, k0 = wq.clone(), wk.clone()
+    call("pb_qk_clip_rescale", ptr(wq), ptr(wq_lp), nh * dh, d, dh, nh // nkv, nh, 0, 0, ptr(mx), tau, stream_ptr())
+    call("pb_qk_clip_rescale", ptr(wk), ptr(wk_lp), nkv * dh, d, dh, nh // nkv, nh, 1, 0, ptr(mx), tau, stream_ptr())
+    torch.cuda.synchronize()
+    for h in range(nh):
+        g = h // 2
+        fq = wq[h * dh] / q0[h * dh]
+        fk = wk[g * dh] / k0[g * dh]
+        want = min(1.0, tau / mx[h].item())
+        assert torch.allclose(fq * fk, torch.full_like(fq, want), rtol=1e-5), h
+    assert torch.allclose(wq_lp.float(), wq, rtol=1e-2, atol=1e-3)
+    # in the trainer: a tiny threshold clips every head of the softmax layer
+    cfg = small_hybrid()
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10, qk_clip=1e-3)
+    tr = engine.Trainer(cfg, tcfg, seed=2, micro_batch=2)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 128), device="cuda",
+                           generator=torch.Generator(device="cuda").manual_seed(0))
+    tr.step(tokens)
+    assert tr.last_max_logits is not None and tr.last_max_logits.shape == (1, 2)
+    assert (tr.last_max_logits > 1e-3).all()
+    with torch.no_grad():
+        tr.track_max_logit = True
+        tr.max_logits = {}
+        tr.forward_hidden(tokens)
+        after = tr.max_logits[3]
+    # the weights moved by the optimizer step too, so the bound is loose: far below the
+    # unclipped logits, near the threshold
+    assert (after < 0.1 * tr.last_max_logits[0]).all(), (after, tr.last_max_logits)
+
+
+def test_latched_wait_timeout_reaches_the_host_step():
+    """A bounded device wait that runs out latches the status word; the public step reads it
+    back with the loss and raises instead of returning a number."""
+    from prometheus_b200 import engine, train
+    from prometheus_b200.ops import functional as ops
+    from prometheus_b200.ops._lib import call, ptr, stream_ptr
+
+    cfg = small_hybrid()
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=100, decay_steps=10)
+    tr = engine.Trainer(cfg, tcfg, seed=1, micro_batch=2)
+    host = torch.randint(0, cfg.vocab_size, (2, 128)).pin_memory()
+    ok = tr.step_from_host(host)
+    assert ok["status"] == 0
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    call("pb_wait_flag_probe", ptr(flag), 1, 2_000_000, ptr(ops.status_word("cuda")), stream_ptr())
+    with pytest.raises(engine.DeviceWaitTimeout) as err:
+        tr.step_from_host(host)
+    assert err.value.code == 2
+    assert tr.step_from_host(host)["status"] == 0          # the word was cleared

@@ -56,6 +56,10 @@ def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
         gw = dy.float() * w
         ref_dx = rstd[:, None] * (gw - xh * (gw * xh).mean(-1, keepdim=True)) + dres.float()
         assert (dx_b.float() - ref_dx).abs().max().item() <= 3e-2 * ref_dx.abs().max().item()
+        ref_dw = (dy.float() * xh).sum(0)
+        assert (dw_b - ref_dw).abs().max().item() <= 2e-2 * ref_dw.abs().max().item()
+        cos = torch.nn.functional.cosine_similarity(dw_b, ref_dw, dim=0).item()
+        assert cos > 0.9999, cos
 
 
 def test_noalloc_rejects_widths_beyond_its_fixed_scratch():
