@@ -13,7 +13,11 @@ L2-normed q/k), every 4th layer softmax GQA 16q/4kv + RoPE, SwiGLU 5632, vocab
 tokens, random-init weights. Every timed step is a full forward, backward,
 gradient synchronisation and optimizer step.
 
-Rank 0 prints one JSON line. ``--impl reference`` reports whether the unmodified
+Rank 0 prints one JSON line: the dense model's tokens/s as ``value`` with ``mfu`` (model FLOPs
+against the measured cuBLAS bf16 rate) and ``exposed_comm_ms`` (step time minus the same steps
+without peer traffic), and under ``secondary.moe16b`` the 16B FP8 expert-parallel
+mixture-of-experts configuration measured in the same run where it fits in memory.
+``--impl reference`` reports whether the unmodified
 reference (JAX) can run the same metric on this machine.
 """
 from __future__ import annotations
@@ -49,6 +53,13 @@ def parse_args():
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "p2p", "nccl"],
                     help="gradient path at N > 1: peer-memory reduce-to-owner + update-broadcast kernels "
                          "(auto / p2p, the product) or NCCL collectives only (the baseline)")
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "dp", "fsdp"],
+                    help="N > 1: fsdp (auto) = bf16 weights as 1/N shards gathered layer by layer, optimizer "
+                         "state for owned matrices only; dp = replicated weights, ownership-sharded optimizer")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the 16B mixture-of-experts measurement that follows the dense one")
+    ap.add_argument("--no-exposed", action="store_true",
+                    help="skip the extra timed steps without peer traffic (exposed_comm_ms reads 0)")
     ap.add_argument("--config", default="dense", choices=["dense", "latent", "moe16b", "longctx"],
                     help="dense: the headline 1.3B hybrid (default). latent: the same model with 1024-token "
                          "prefix + 8 latent slots + 512-token answer, 4 Jacobi sweeps, 8 sequences per GPU. "
@@ -133,78 +144,87 @@ class ClockSampler:
         return out
 
 
-def main() -> int:
-    args = parse_args()
-    if args.impl == "reference":
-        return reference_arm(args)
+def estimate_rank_bytes(cfg, world: int, expert_parallel: bool, tokens_per_micro: int) -> int:
+    """Rough device bytes one rank needs to train ``cfg``: bf16 weight + fp32 gradient, master
+    and one moment per parameter it holds, plus the saved activations of one micro-batch."""
+    from prometheus_b200 import model
 
+    shapes = model.init_params(cfg, 0, shapes_only=True)
+    flat = model.flatten_params(shapes)
+    held = 0
+    for name, t in flat.items():
+        n = int(t.numel())
+        held += n // world if (expert_parallel and ".routed_" in name) else n
+    # saved activations per layer, in units of one (tokens x d_model) bf16 tensor: about 20 for
+    # a dense layer, 12 + 3 per routed slot for a mixture-of-experts layer
+    act = tokens_per_micro * cfg.d_model * 2 * cfg.n_layers * ((12 + 3 * cfg.top_k) if cfg.n_moe else 20)
+    return held * 14 + act
+
+
+def measure(args, config: str, world: int, rank: int, local_rank: int, dev, steps: int, warmup: int,
+            with_clocks: bool, with_exposed: bool) -> dict:
+    """Build the trainer of one configuration and time it: ``steps`` device-timed steps, the
+    same through the public host API, and (optionally) the steps again without peer traffic."""
     import torch
     import torch.distributed as dist
 
     from prometheus_b200 import engine, model, train
     from prometheus_b200.ops import _lib
+    from prometheus_b200.utils import flops
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            print(f"--gpus {args.gpus} needs torchrun with that many ranks", file=sys.stderr)
-            return 2
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-
+    seq_len, seqs, micro = args.seq_len, args.seqs_per_gpu, args.micro_batch
     model_name = MODEL_NAME
     trainer_kw = {}
-    if args.config == "latent":
-        args.seq_len = 1024 + 8 + 512
-        if args.seqs_per_gpu == SEQS_PER_GPU:
-            args.seqs_per_gpu = 8
+    sweeps = 1
+    fsdp = world > 1 and args.parallelism in ("auto", "fsdp") and args.grad_sync != "nccl"
+    if config == "latent":
+        seq_len = 1024 + 8 + 512
+        seqs = 8 if seqs == SEQS_PER_GPU else seqs
+        sweeps = 4
         model_name += " + latent slots (prefix 1024 | K=8 | answer 512, 4 Jacobi sweeps)"
-    if args.config == "longctx":
+    if config == "longctx":
         # one sequence split over the ranks (context parallel), 16384 tokens per rank:
         # 8 ranks hold the 131072-token sequence of the long-context configuration
-        args.seq_len = 16384 * world
-        args.seqs_per_gpu = 1
-        args.micro_batch = 1
+        seq_len, seqs, micro = 16384 * world, 1, 1
         trainer_kw = dict(context_parallel=world > 1)
-        model_name += f" at sequence length {args.seq_len} (context parallel over {world} rank(s))"
-    cfg = model.config_dense_1p3b(max_context=args.seq_len)
-    if args.config == "moe16b":
-        cfg = model.with_overrides(model.config_moe_16b(), max_context=args.seq_len)
-        if args.seqs_per_gpu == SEQS_PER_GPU:
-            args.seqs_per_gpu = 8
-        if args.micro_batch == 8:
-            # top-6 routing keeps six expert-side copies of every token's activations per MoE
-            # layer: 16384 tokens per micro-batch keep the 27 MoE layers' saved activations near 55 GB
-            args.micro_batch = 4
+        fsdp = False
+        model_name += f" at sequence length {seq_len} (context parallel over {world} rank(s))"
+    cfg = model.config_dense_1p3b(max_context=seq_len)
+    if config == "moe16b":
+        cfg = model.with_overrides(model.config_moe_16b(), max_context=seq_len)
+        seqs = 8 if seqs == SEQS_PER_GPU else seqs
+        # top-6 routing keeps six expert-side copies of every token's activations per MoE
+        # layer: 16384 tokens per micro-batch keep the 27 MoE layers' saved activations near 55 GB
+        micro = 4 if micro == 8 else micro
         trainer_kw = dict(fp8=True, expert_parallel=world > 1)
+        fsdp = fsdp and args.parallelism == "fsdp"
         model_name = "moe-16B (28L d2048, 64 routed top-6 + 2 shared experts h1408, FP8 e4m3 block-scaled linears)"
     if args.layers:
-        n_dense = 1 if args.config == "moe16b" else args.layers
+        n_dense = 1 if config == "moe16b" else args.layers
         cfg = model.with_overrides(cfg, n_layers=args.layers, n_dense=n_dense, n_moe=args.layers - n_dense,
                                    n_linear_attn=args.layers * 3 // 4, n_mla=args.layers // 4,
                                    core_block_layers=args.layers)
+    need = estimate_rank_bytes(cfg, world, config == "moe16b" and world > 1, micro * seq_len)
+    free_b, total_b = torch.cuda.mem_get_info(dev)
+    if need > 0.92 * total_b:
+        return {"skipped": f"needs about {need / 2**30:.0f} GiB per rank at {world} GPU(s), "
+                           f"the device has {total_b / 2**30:.0f} GiB", "bytes_needed_per_rank": int(need)}
     tcfg = train.train_config_for(cfg, warmup_steps=100, stable_steps=10_000, decay_steps=1000)
     torch.manual_seed(1234)
-    tr = engine.Trainer(cfg, tcfg, seed=0, device=dev, micro_batch=args.micro_batch,
-                        grad_sync=args.grad_sync, **trainer_kw)
+    tr = engine.Trainer(cfg, tcfg, seed=0, device=dev, micro_batch=micro, grad_sync=args.grad_sync,
+                        fsdp=fsdp, **trainer_kw)
     step_kw = {}
-    if args.config == "latent":
+    if config == "latent":
         tr.set_latent_slots(1024, 8, 4)
-        mask = torch.ones(args.seqs_per_gpu, args.seq_len, device=dev)
+        mask = torch.ones(seqs, seq_len, device=dev)
         mask[:, 1024:1032] = 0
         step_kw = dict(loss_mask=mask)
 
-    B, S = args.seqs_per_gpu, args.seq_len
-    cp = args.config == "longctx"
+    B, S = seqs, seq_len
+    cp = config == "longctx"
     gen = torch.Generator().manual_seed(1000 + (0 if cp else rank))     # CP ranks slice the same sequence
-    n_batches = args.steps + args.warmup
     host_tokens = [torch.randint(0, cfg.vocab_size, (B, S), generator=gen, dtype=torch.int64)
-                   for _ in range(min(n_batches, 4))]
+                   for _ in range(min(steps + warmup, 4))]
     host_masks = None
     if cp and world > 1:
         sliced = [tr.cp_slice(t, torch.ones(B, S)) for t in host_tokens]
@@ -224,74 +244,167 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
+    def timed(n, fn):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = None
+        for i in range(n):
+            out = fn(i)
+        e1.record()
+        sync_all()
+        return e0.elapsed_time(e1), out
+
+    for i in range(warmup):
         tr.step(dev_tokens[i % len(dev_tokens)], **kw_for(i))
     sync_all()
 
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and with_clocks:
         sampler.start()
     launches0 = _lib.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    e0.record()
-    for i in range(args.steps):
-        out = tr.step(dev_tokens[i % len(dev_tokens)], **kw_for(i))
-    e1.record()
-    sync_all()
-    ms = e0.elapsed_time(e1)
+    ms, out = timed(steps, lambda i: tr.step(dev_tokens[i % len(dev_tokens)], **kw_for(i)))
     launches = _lib.launch_count - launches0
     last_loss = float(out["loss"].item())
+    tr.raise_on_status(int(out["status"].item()))
 
     # end to end through the public API: pinned host tokens in, loss value out, every step
-    sync_all()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    e2e_loss = 0.0
-    for i in range(args.steps):
+    def host_step(i):
         hkw = kw_for(i, host=True)
-        res = tr.step_from_host(host_tokens[i % len(host_tokens)],
-                                *([hkw["loss_mask"] if hkw["loss_mask"].device.type == "cpu"
-                                   else hkw["loss_mask"].cpu().pin_memory()] if hkw else []))
-        e2e_loss = res["loss"]
-    f1.record()
-    sync_all()
-    ms_e2e = f0.elapsed_time(f1)
-    clocks = sampler.stop() if rank == 0 else {}
+        extra = []
+        if hkw:
+            m = hkw["loss_mask"]
+            extra = [m if m.device.type == "cpu" else m.cpu().pin_memory()]
+        return tr.step_from_host(host_tokens[i % len(host_tokens)], *extra)
 
-    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    ms_e2e, res = timed(steps, host_step)
+    e2e_loss = res["loss"]
+    clocks = sampler.stop() if (rank == 0 and with_clocks) else {}
+    ms_noop = None
+    if with_exposed and world > 1 and tr.sym is not None:
+        # the same steps with the peer traffic of the gradient fold, the weight refresh and the
+        # parameter gathers left out (the kernels' arithmetic and local memory traffic stay)
+        tr.comm_noop = True
+        tr.step(dev_tokens[0], **kw_for(0))
+        ms_noop, _ = timed(steps, lambda i: tr.step(dev_tokens[i % len(dev_tokens)], **kw_for(i)))
+        tr.comm_noop = False
+
+    t = torch.tensor([ms, ms_e2e, ms_noop if ms_noop is not None else 0.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = float(t[0]), float(t[1])
+    ms, ms_e2e, ms_noop_max = float(t[0]), float(t[1]), float(t[2])
     tokens_per_step = B * S * (1 if cp else world)
-    value = tokens_per_step * args.steps / (ms / 1e3)
-    e2e_value = tokens_per_step * args.steps / (ms_e2e / 1e3)
+    value = tokens_per_step * steps / (ms / 1e3)
+    e2e_value = tokens_per_step * steps / (ms_e2e / 1e3)
+    peaks = flops.measured_peaks()
+    mem = tr.memory_report()
+    par = "single"
+    if world > 1:
+        par = f"cp{world}" if cp else (f"fsdp{world}" if tr.fsdp else f"dp{world}")
+        if config == "moe16b":
+            par += f"+ep{world}"
+    result = {
+        "value": value, "ms_per_step": ms / steps,
+        "mfu": flops.mfu(value, cfg, S, world, sweeps=sweeps),
+        "mfu_of": f"{peaks['source']} cuBLAS bf16 burst {peaks['bf16_tflops']:.0f} TFLOP/s per GPU",
+        "exposed_comm_ms": (max(0.0, (ms - ms_noop_max) / steps) if ms_noop is not None else 0.0),
+        "config": {
+            "model": model_name if not args.layers else f"DEBUG {args.layers} layers",
+            "global_batch": B * (1 if cp else world), "seq_len": S, "parallelism": par,
+            "micro_batch": micro, "grad_sync": args.grad_sync,
+            "l2": f"per-step working set ({mem['weights_bf16_bytes'] / 2**30:.1f} GiB bf16 weights on "
+                  f"this rank + activations) exceeds the 126 MB L2; no flush needed",
+            "weights_plus_optimizer_bytes_per_rank": mem["weights_plus_state_bytes"],
+        },
+        "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"),
+                   "reasons": clocks.get("reasons", [])},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / steps,
+                "h2d_bytes_per_step": int(host_tokens[0].numel() * 8 + (host_masks[0].numel() * 4 if host_masks else 0)),
+                "d2h_bytes_per_step": 12},
+        "gpu_launches": launches, "loss": last_loss, "e2e_loss": e2e_loss,
+    }
+    tr.close()
+    del tr, dev_tokens, dev_masks
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    return result
+
+
+def main() -> int:
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(f"--gpus {args.gpus} needs torchrun with that many ranks", file=sys.stderr)
+            return 2
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    main_res = measure(args, args.config, world, rank, local_rank, dev, args.steps, args.warmup,
+                       with_clocks=True, with_exposed=not args.no_exposed)
+    if "skipped" in main_res:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": None, "n_gpus": world, "impl": "ours",
+                              "unavailable": main_res["skipped"]}), flush=True)
+        return 0
+    secondary = {}
+    if args.config == "dense" and not args.no_secondary and not args.layers:
+        # the 16B FP8 mixture-of-experts configuration, expert parallel over the same ranks, in
+        # the same run wherever it fits
+        sec = measure(args, "moe16b", world, rank, local_rank, dev, max(2, min(args.steps, 3)), 3,
+                      with_clocks=False, with_exposed=False)
+        if "skipped" in sec:
+            secondary["moe16b"] = {"value": None, "skipped": sec["skipped"],
+                                   "bytes_needed_per_rank": sec["bytes_needed_per_rank"]}
+        else:
+            secondary["moe16b"] = {k: sec[k] for k in ("value", "ms_per_step", "mfu", "config",
+                                                       "gpu_launches", "loss")}
+            secondary["moe16b"]["unit"] = "tokens/s"
     if rank == 0:
+        value = main_res["value"]
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (seeded uniform tokens, random-init weights)",
-            "config": {
-                "model": model_name if not args.layers else f"DEBUG {args.layers} layers",
-                "global_batch": B * (1 if cp else world), "seq_len": S,
-                "parallelism": (f"cp{world}" if cp else f"dp{world}" + ("+ep" + str(world) if args.config == "moe16b" else ""))
-                if world > 1 else "single",
-                "micro_batch": args.micro_batch, "grad_sync": args.grad_sync,
-                "l2": "per-step working set (3.5 GB bf16 weights + activations) exceeds the 126 MB L2",
-            },
-            "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"),
-                       "reasons": clocks.get("reasons", [])},
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": int(host_tokens[0].numel() * 8 + (host_masks[0].numel() * 4 if host_masks else 0)),
-                    "d2h_bytes_per_step": 8},
-            "gpu_launches": launches,
-            "loss": last_loss, "e2e_loss": e2e_loss, "impl": "ours",
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_res["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": vs_baseline(value, world, args),
+            "dtype": "bf16", "data": "synthetic (seeded uniform tokens, random-init weights)",
+            "config": main_res["config"], "clocks": main_res["clocks"], "e2e": main_res["e2e"],
+            "gpu_launches": main_res["gpu_launches"], "mfu": main_res["mfu"], "mfu_of": main_res["mfu_of"],
+            "exposed_comm_ms": main_res["exposed_comm_ms"],
+            "loss": main_res["loss"], "e2e_loss": main_res["e2e_loss"], "impl": "ours",
         }
+        if secondary:
+            line["secondary"] = secondary
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def vs_baseline(value: float, world: int, args):
+    """value / the baseline number recorded for this GPU count. The reference publishes no
+    throughput; the recorded baseline is this repository's own NCCL-only gradient path
+    (``--grad-sync nccl``) on the same configuration, kept in ``baseline/nccl_only.json``."""
+    if args.config != "dense" or args.layers:
+        return None
+    try:
+        table = json.loads((ROOT / "baseline" / "nccl_only.json").read_text())
+        base = table.get(str(world), {}).get("tokens_per_s")
+        return value / base if base else None
+    except Exception:
+        return None
 
 
 if __name__ == "__main__":

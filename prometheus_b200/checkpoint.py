@@ -50,6 +50,8 @@ def _bytes(t: torch.Tensor) -> bytes:
 
 def _full_state(tr) -> dict[str, torch.Tensor]:
     """All flat fp32 state buffers, complete on every rank."""
+    if hasattr(tr, "full_state"):          # the trainer knows its own (possibly sharded) layout
+        return tr.full_state()
     bufs = {"muon.master": tr.muon_master, "muon.mom": tr.muon_mom,
             "adam.master": tr.adam_master, "adam.m": tr.adam_m, "adam.v": tr.adam_v,
             "vec.master": tr.vec_master, "vec.m": tr.vec_m, "vec.v": tr.vec_v}
@@ -177,6 +179,39 @@ def apply(tr, ckpt, *, strict_config: bool = True) -> dict[str, Any] | None:
         src = torch.frombuffer(bytearray(raw), dtype=torch.float32)
         dst.copy_(src.to(dev))
 
+    def blob_f32(raw: bytes, numel: int, what: str):
+        if len(raw) != numel * 4:
+            raise ValueError(f"{what}: {len(raw)} bytes for {numel} fp32 values")
+        return torch.frombuffer(bytearray(raw), dtype=torch.float32)
+
+    if hasattr(tr, "_store_state"):
+        # sharded-state trainer: every rank reads the full tensors and keeps what it stores
+        with torch.no_grad():
+            for w in tr.weights.values():
+                n = int(math.prod(w.shape))
+                parts = [("master", wb[w.name], w.name)]
+                if w.group == "muon":
+                    parts.append(("mom", ob[w.name + ".mom"], w.name + ".mom"))
+                else:
+                    parts += [("m", ob[w.name + ".m"], w.name + ".m"), ("v", ob[w.name + ".v"], w.name + ".v")]
+                for which, raw, what in parts:
+                    full = blob_f32(raw, n, what).to(dev).view(w.shape)
+                    tr._store_state(w, which, full)
+                    if which == "master":
+                        tr._store_lp(w, full)
+            for i, b in getattr(tr, "router_bias", {}).items():
+                name = f"layers.{i}.router_bias"
+                if name in wb:
+                    put(b, wb[name], name)
+        if getattr(tr, "fsdp", False):
+            tr._fsdp_invalidate()
+        tr.step_count = int(m.step)
+        if getattr(tr, "sym", None) is not None:
+            torch.cuda.synchronize()
+            torch.distributed.barrier(tr.pg)
+        raw = getattr(m, "loader_state_json", "")
+        return json.loads(raw) if raw and raw != "{}" else None
+
     with torch.no_grad():
         for w in tr.weights.values():
             n = int(math.prod(w.shape))
@@ -202,6 +237,53 @@ def apply(tr, ckpt, *, strict_config: bool = True) -> dict[str, Any] | None:
         torch.distributed.barrier(tr.pg)
     raw = getattr(m, "loader_state_json", "")
     return json.loads(raw) if raw and raw != "{}" else None
+
+
+def broadcast_checkpoint(ckpt, error: str | None, tr):
+    """Rank 0's checkpoint (or its error) to every rank of the trainer's group. Returns an
+    object with the ``manifest`` / ``weights`` / ``optimizer`` fields :func:`apply` reads.
+    Blobs travel as byte tensors through the group's backend (NCCL: via the GPU)."""
+    import types
+
+    import torch.distributed as dist
+
+    group = getattr(tr, "pg", None)
+    backend = dist.get_backend(group)
+    dev = tr.device if backend == "nccl" else torch.device("cpu")
+    # ranks inside `group` address rank 0 of the group
+    src = dist.get_global_rank(group, 0) if group is not None else 0
+    head = [None]
+    if tr.rank == 0:
+        if error is not None:
+            head[0] = {"error": error}
+        else:
+            m = ckpt.manifest
+            head[0] = {"error": None, "step": int(m.step), "model_config_hash": m.model_config_hash,
+                       "loader_state_json": getattr(m, "loader_state_json", ""),
+                       "weights": [(b.name, int(b.shard_rank), len(b.bytes)) for b in ckpt.weights],
+                       "optimizer": [(b.name, int(b.shard_rank), len(b.bytes)) for b in ckpt.optimizer]}
+    dist.broadcast_object_list(head, src=src, group=group)
+    info = head[0]
+    if info["error"] is not None:
+        raise RuntimeError(f"checkpoint restore failed on rank 0: {info['error']}")
+    if tr.rank == 0:
+        blobs = {"weights": list(ckpt.weights), "optimizer": list(ckpt.optimizer)}
+    out = {"weights": [], "optimizer": []}
+    me = int(tr.rank)
+    for kind in ("weights", "optimizer"):
+        for j, (name, shard_rank, nbytes) in enumerate(info[kind]):
+            if tr.rank == 0:
+                t = torch.frombuffer(bytearray(blobs[kind][j].bytes), dtype=torch.uint8).to(dev)
+            else:
+                t = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+            dist.broadcast(t, src=src, group=group)
+            # a rank keeps shard 0 and its own shard of every name (what apply() looks at)
+            if shard_rank in (0, me):
+                out[kind].append(types.SimpleNamespace(name=name, shard_rank=shard_rank,
+                                                       bytes=t.cpu().numpy().tobytes()))
+    manifest = types.SimpleNamespace(step=info["step"], model_config_hash=info["model_config_hash"],
+                                     loader_state_json=info["loader_state_json"])
+    return types.SimpleNamespace(manifest=manifest, weights=out["weights"], optimizer=out["optimizer"])
 
 
 class TrainerCheckpointer:
@@ -242,6 +324,18 @@ class TrainerCheckpointer:
             self.pending = None
 
     def restore(self, tr, checkpoint_id: str | None = None):
+        """Load a checkpoint (by id, else the newest in-memory replica) into the trainer.
+        Collective when the trainer spans several ranks: only rank 0 holds the replicas and
+        reads the store, so it loads the checkpoint and broadcasts it; every rank then applies
+        it. A failure on rank 0 (unknown id, hash mismatch) is raised on every rank."""
         self.wait()
-        ck = self.cp.restore(checkpoint_id) if checkpoint_id else self.cp.restore_latest_memory()
-        return apply(tr, ck)
+        if getattr(tr, "world", 1) <= 1:
+            ck = self.cp.restore(checkpoint_id) if checkpoint_id else self.cp.restore_latest_memory()
+            return apply(tr, ck)
+        ck, err = None, None
+        if tr.rank == 0:
+            try:
+                ck = self.cp.restore(checkpoint_id) if checkpoint_id else self.cp.restore_latest_memory()
+            except Exception as e:          # noqa: BLE001 - re-raised on every rank below
+                err = f"{type(e).__name__}: {e}"
+        return apply(tr, broadcast_checkpoint(ck, err, tr))

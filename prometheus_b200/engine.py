@@ -85,6 +85,21 @@ class _EmbedFn(torch.autograd.Function):
         return None, None
 
 
+class _FsdpLayerHook(torch.autograd.Function):
+    """Identity on a layer's output whose backward runs before any backward node of that layer:
+    it makes the layer's gathered weights resident again and starts the previous layer's pull."""
+
+    @staticmethod
+    def forward(ctx, x, trainer, layer):
+        ctx.trainer, ctx.layer = trainer, layer
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.trainer._fsdp_enter(ctx.layer, backward=True)
+        return g, None, None
+
+
 class DeviceWaitTimeout(RuntimeError):
     """A bounded device-side wait (peer flag, barrier, mbarrier) ran out during a step: the
     gradients or weights of that step may be partial. Carries the latched code."""
@@ -104,7 +119,7 @@ class Trainer:
                  grad_sync: str = "auto", expert_parallel: bool = False,
                  ep_capacity_factor: float = 2.0, fp8: bool = False, context_parallel: bool = False,
                  z_loss_mode: str = "layers_logits", router_bias_rule: str = "count",
-                 allow_fallback: bool = False, recurrence: int = 1,
+                 allow_fallback: bool = False, fsdp: bool = False, recurrence: int = 1,
                  truncated_recurrence: int = M.TRUNCATED_RECURRENCE, check_status_every: int = 1):
         M.validate_config(model_config)
         T.validate_train_config(train_config)
@@ -120,6 +135,11 @@ class Trainer:
             self.world = torch.distributed.get_world_size(process_group)
             self.rank = torch.distributed.get_rank(process_group)
         self.grad_sync = grad_sync
+        # ZeRO-3: bf16 working weights kept as 1/world shards in symmetric memory and gathered
+        # layer by layer into two rotating landing buffers, one layer ahead of the compute;
+        # fp32 masters and optimizer moments only for the matrices this rank owns
+        self.fsdp = bool(fsdp) and self.world > 1
+        self.comm_noop = False      # timing only: skip the peer traffic (see exposed-comm measurement)
         self.ep = bool(expert_parallel) and self.world > 1 and model_config.n_moe > 0
         self.ep_capacity_factor = float(ep_capacity_factor)
         # block-scaled FP8 forward for the FFN / expert products (1 x 128 activations,
@@ -257,7 +277,9 @@ class Trainer:
                 mat(p + "k", (kvh * dh, d), [src(p + "W_k", 0, kvh * dh)])
                 mat(p + "v", (kvh * dh, d), [src(p + "W_v", 0, kvh * dh)])
                 if kind is M.AttentionKind.LINEAR and cfg.delta_beta == "sigmoid":
-                    mat(p + "beta", (nh, d), [src(p + "W_beta", 0, nh)])
+                    # rows padded to a multiple of 8 (16-byte rows for the GEMM's operands);
+                    # the padding rows are zero, see no gradient and are not exported
+                    mat(p + "beta", ((nh + 7) // 8 * 8, d), [src(p + "W_beta", 0, nh)])
                 mat(p + "o", (d, nh * dh), [(p + "W_o", 0, d, "o", None)])
             if M.ffn_kind(i, cfg) is M.FfnKind.DENSE:
                 hid = cfg.dense_hidden if cfg.dense_hidden is not None else cfg.expert_hidden
@@ -304,6 +326,8 @@ class Trainer:
                 key = (u.rows, u.cols, 1) if w.local else (u.rows, u.cols)
                 classes.setdefault(key, []).append(u)
         self.unit_classes = classes
+        self.unit_index = {(u.weight, u.r0): (key, j) for key, us in classes.items()
+                           for j, u in enumerate(us)}
         off = 0
         for key in sorted(classes):
             for u in classes[key]:
@@ -331,44 +355,45 @@ class Trainer:
         f32 = dict(dtype=torch.float32, device=dev)
         self.sym = None
         n_m, n_a, n_v = self.n_muon, self.n_adam, self.n_vec
+        if self.fsdp and self.grad_sync == "nccl":
+            raise ValueError("fsdp=True needs the peer-memory gradient path (grad_sync auto / p2p)")
         if self.world > 1 and self.grad_sync in ("auto", "p2p"):
             # Gradients and bf16 working weights live in symmetric memory: peers read the
-            # former (reduce to owner) and write the latter (update + broadcast).
+            # former (reduce to owner) and write the latter (update + broadcast / shard store).
             from .parallel.symm import SymmetricBuffer, SymmetricGroup
 
             ok, err = 1, None
             try:
                 self.sym = SymmetricGroup(self.pg)
                 self.sym_grad = SymmetricBuffer(4 * (n_m + n_a + n_v), self.pg)
-                self.sym_lp = SymmetricBuffer(2 * (n_m + n_a), self.pg)
+                if self.fsdp:
+                    self._plan_fsdp()
+                    self.sym_lp = SymmetricBuffer(2 * self.n_sym_w, self.pg)
+                else:
+                    self.sym_lp = SymmetricBuffer(2 * (n_m + n_a), self.pg)
             except RuntimeError as e:      # peer mapping refused on this machine
                 ok, err = 0, e
             flag = torch.tensor([ok], dtype=torch.int32, device=dev)
             torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN, group=self.pg)
             if int(flag.item()) == 0:
-                if self.grad_sync == "p2p":
+                if self.grad_sync == "p2p" or self.fsdp:
                     raise RuntimeError(f"symmetric memory unavailable: {err}")
                 self.sym = None
+        if self.sym is None:
+            self.fsdp = False
         if self.sym is not None:
             self.muon_grad = self.sym_grad.view(torch.float32, n_m, 0)
             self.adam_grad = self.sym_grad.view(torch.float32, n_a, 4 * n_m)
             self.vec_grad = self.sym_grad.view(torch.float32, n_v, 4 * (n_m + n_a))
-            self.muon_lp = self.sym_lp.view(BF16, n_m, 0)
-            self.adam_lp = self.sym_lp.view(BF16, n_a, 2 * n_m)
+            if not self.fsdp:
+                self.muon_lp = self.sym_lp.view(BF16, n_m, 0)
+                self.adam_lp = self.sym_lp.view(BF16, n_a, 2 * n_m)
         else:
             self.muon_grad = torch.zeros(n_m, **f32)
             self.adam_grad = torch.zeros(n_a, **f32)
             self.vec_grad = torch.zeros(n_v, **f32)
             self.muon_lp = torch.zeros(n_m, dtype=BF16, device=dev)
             self.adam_lp = torch.zeros(n_a, dtype=BF16, device=dev)
-        self.muon_master = torch.zeros(n_m, **f32)
-        self.muon_mom = torch.zeros(n_m, **f32)
-        self.adam_master = torch.zeros(n_a, **f32)
-        self.adam_m = torch.zeros(n_a, **f32)
-        self.adam_v = torch.zeros(n_a, **f32)
-        self.vec_master = torch.zeros(n_v, **f32)
-        self.vec_m = torch.zeros(n_v, **f32)
-        self.vec_v = torch.zeros(n_v, **f32)
         # ownership: rank r updates units [lo, hi) of every Muon shape class and one
         # contiguous slice of the AdamW slab; fp32 vectors are updated by every rank.
         from .parallel.fsdp import split_bounds
@@ -378,6 +403,33 @@ class Trainer:
                           for key, us in self.unit_classes.items()}
         a_lo, a_hi = split_bounds(n_a // 8, w_, r_)
         self.own_adam = (a_lo * 8, a_hi * 8)
+        # State storage. Replicated mode keeps full-size master / moment buffers addressed by
+        # the global flat offsets (only the owned ranges are ever current). ZeRO mode allocates
+        # the owned ranges only: class_lbase[key] / adam_shift translate a global offset of an
+        # owned element into the compact buffers.
+        self.compact = self.fsdp
+        self.class_range: dict[tuple, tuple] = {}
+        self.class_lbase: dict[tuple, int] = {}
+        lb = 0
+        for key in sorted(self.unit_classes):
+            units = self.unit_classes[key]
+            n = key[0] * key[1]
+            lo_u, hi_u = self.own_units[key]
+            glo, ghi = units[0].off + lo_u * n, units[0].off + hi_u * n
+            self.class_range[key] = (glo, ghi)
+            self.class_lbase[key] = lb if self.compact else glo
+            lb += ghi - glo
+        self.adam_shift = self.own_adam[0] if self.compact else 0
+        n_m_state = max(lb, 8) if self.compact else n_m
+        n_a_state = max(self.own_adam[1] - self.own_adam[0], 8) if self.compact else n_a
+        self.muon_master = torch.zeros(n_m_state, **f32)
+        self.muon_mom = torch.zeros(n_m_state, **f32)
+        self.adam_master = torch.zeros(n_a_state, **f32)
+        self.adam_m = torch.zeros(n_a_state, **f32)
+        self.adam_v = torch.zeros(n_a_state, **f32)
+        self.vec_master = torch.zeros(n_v, **f32)
+        self.vec_m = torch.zeros(n_v, **f32)
+        self.vec_v = torch.zeros(n_v, **f32)
         max_unit = max((k_[0] * k_[1] * (self.own_units[k_][1] - self.own_units[k_][0])
                         for k_ in self.unit_classes), default=1)
         self.ns_x = [torch.empty(max(max_unit, 1), dtype=BF16, device=dev) for _ in range(2)]
@@ -394,18 +446,197 @@ class Trainer:
         self.gnorm_sq = torch.zeros(1, **f32)
         self.local_sq = torch.zeros(1, **f32)
         self.vec_sq = torch.zeros(1, **f32)
-        bufs = {"muon": (self.muon_master, self.muon_grad, self.muon_lp),
-                "adam": (self.adam_master, self.adam_grad, self.adam_lp),
-                "vec": (self.vec_master, self.vec_grad, None)}
+        grads = {"muon": self.muon_grad, "adam": self.adam_grad, "vec": self.vec_grad}
+        if self.fsdp:
+            self._allocate_fsdp()
         self.p: dict[str, Tensor] = {}
         for w in self.weights.values():
             n = int(math.prod(w.shape))
-            master, grad, lpbuf = bufs[w.group]
-            t = (lpbuf if w.lp else master)[w.off:w.off + n].view(w.shape)
+            if not w.lp:
+                t = self.vec_master[w.off:w.off + n].view(w.shape)
+            elif self.fsdp:
+                t = self._fsdp_view(w)
+            else:
+                lpbuf = self.muon_lp if w.group == "muon" else self.adam_lp
+                t = lpbuf[w.off:w.off + n].view(w.shape)
             t.requires_grad_(True)
-            t.main_grad = grad[w.off:w.off + n].view(w.shape)
-            t.master = master[w.off:w.off + n].view(w.shape)
+            t.main_grad = grads[w.group][w.off:w.off + n].view(w.shape)
             self.p[w.name] = t
+
+    # ------------------------------------------------------------ ZeRO-3 layout
+    def _plan_fsdp(self) -> None:
+        """Group the bf16 working weights into blobs (one per layer, one per vocabulary-sized
+        table), cut every blob into ``world`` equal chunks, and lay the symmetric weight buffer
+        out as [this rank's chunk of every blob | replicated small weights | this rank's experts]."""
+        W = self.world
+        blobs: dict[tuple, dict] = {}
+        rep = 0
+        for w in self.weights.values():
+            if not w.lp:
+                continue
+            n = (int(math.prod(w.shape)) + 7) // 8 * 8
+            if w.local:
+                w.mode, w.blob = "local", None
+            elif w.name.startswith("layers."):
+                w.mode, w.blob = "shard", ("layer", int(w.name.split(".")[1]))
+            elif w.name in ("embed", "unembed") or w.name.endswith(".unembed"):
+                w.mode, w.blob = "shard", (w.name,)
+            else:
+                w.mode, w.blob = "bcast", None          # adapter, MTP projections: small
+            if w.mode == "shard":
+                b = blobs.setdefault(w.blob, {"key": w.blob, "weights": [], "L": 0})
+                w.pos = b["L"]
+                b["weights"].append(w.name)
+                b["L"] += n
+            else:
+                w.pos = rep
+                rep += n
+        off = 0
+        for b in blobs.values():
+            b["L"] = (b["L"] + 8 * W - 1) // (8 * W) * (8 * W)
+            b["chunk"] = b["L"] // W
+            b["shard_off"] = off
+            b["slot"] = f"layer{b['key'][1] % 2}" if b["key"][0] == "layer" else "big"
+            off += b["chunk"]
+        self.blobs = blobs
+        self.n_shard = off
+        self.rep_off = off
+        self.n_sym_w = off + rep
+
+    def _allocate_fsdp(self) -> None:
+        dev = self.device
+        sizes = {"layer0": 8, "layer1": 8, "big": 8}
+        for b in self.blobs.values():
+            sizes[b["slot"]] = max(sizes[b["slot"]], b["L"])
+        self.landing = {k: torch.empty(v, dtype=BF16, device=dev) for k, v in sizes.items()}
+        self.slot_state = {k: {"blob": None, "ready": None, "waited": True} for k in sizes}
+        self.fetch_stream = torch.cuda.Stream(dev)
+        self.sym_w_local = self.sym_lp.view(BF16, self.n_sym_w, 0)
+        # destination tables of the update kernels: per Muon unit (pos, chunk, base)
+        self.dest_tables: dict[tuple, Tensor] = {}
+        for key, units in self.unit_classes.items():
+            rows = []
+            for u in units:
+                w = self.weights[u.weight]
+                rows.append(self._dest_of(w, u.r0 * u.cols))
+            self.dest_tables[key] = torch.tensor(rows, dtype=torch.int64, device=dev).reshape(-1, 3)
+        # AdamW slab: the pieces of bf16-backed weights inside this rank's slab range
+        a_lo, a_hi = self.own_adam
+        self.adam_segments = []
+        for w in self.weights.values():
+            if w.group != "adam":
+                continue
+            n = int(math.prod(w.shape))
+            lo, hi = max(w.off, a_lo), min(w.off + n, a_hi)
+            if hi > lo:
+                self.adam_segments.append((lo, hi - lo, self._dest_of(w, lo - w.off)))
+
+    def _dest_of(self, w: "Weight", elem: int) -> tuple:
+        """(pos, chunk, base) of element ``elem`` of a weight's bf16 copy (see csrc/comm/fsdp.cu)."""
+        if w.mode == "shard":
+            b = self.blobs[w.blob]
+            return (w.pos + elem, b["chunk"], b["shard_off"])
+        return (0, 0 if w.mode == "bcast" else -1, self.rep_off + w.pos + elem)
+
+    def _fsdp_view(self, w: "Weight") -> Tensor:
+        n = int(math.prod(w.shape))
+        if w.mode == "shard":
+            b = self.blobs[w.blob]
+            return self.landing[b["slot"]][w.pos:w.pos + n].view(w.shape)
+        o = self.rep_off + w.pos
+        return self.sym_w_local[o:o + n].view(w.shape)
+
+    def _fsdp_fetch(self, key: tuple) -> None:
+        """Enqueue the all-gather of a blob into its landing slot on the fetch stream (no-op
+        when the slot already holds it). The slot's previous occupant may still be in use by
+        kernels already enqueued on the compute stream: the copy waits for them."""
+        b = self.blobs[key]
+        st = self.slot_state[b["slot"]]
+        if st["blob"] == key:
+            return
+        main = torch.cuda.current_stream(self.device)
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self.fetch_stream.wait_event(ev)
+        with torch.cuda.stream(self.fetch_stream):
+            if not self.comm_noop:
+                call("pb_shard_gather", self.sym_lp.ptrs, b["shard_off"], b["chunk"],
+                     ptr(self.landing[b["slot"]]), self.world, self.rank, 64, stream_ptr())
+            ready = torch.cuda.Event()
+            ready.record(self.fetch_stream)
+        st.update(blob=key, ready=ready, waited=False)
+
+    def _fsdp_ensure(self, key: tuple) -> None:
+        """The compute stream may read the blob's landing slot after this call."""
+        self._fsdp_fetch(key)
+        st = self.slot_state[self.blobs[key]["slot"]]
+        if not st["waited"]:
+            torch.cuda.current_stream(self.device).wait_event(st["ready"])
+            st["waited"] = True
+
+    def _fsdp_enter(self, layer: int, backward: bool = False) -> None:
+        """Layer ``layer`` is about to run (forward or backward): make its weights resident and
+        start pulling the next layer's into the other slot."""
+        self._fsdp_ensure(("layer", layer))
+        nxt = layer - 1 if backward else layer + 1
+        if 0 <= nxt < self.cfg.n_layers and ("layer", nxt) in self.blobs:
+            self._fsdp_fetch(("layer", nxt))
+
+    def _fsdp_invalidate(self) -> None:
+        for st in self.slot_state.values():
+            st.update(blob=None, ready=None, waited=True)
+
+    def weight(self, name: str) -> Tensor:
+        """The bf16 working tensor of a weight, resident (gathers its blob first under ZeRO-3)."""
+        if self.fsdp:
+            w = self.weights[name]
+            if w.lp and w.mode == "shard":
+                self._fsdp_ensure(w.blob)
+        return self.p[name]
+
+    def memory_report(self) -> dict:
+        """Bytes this rank holds for weights and optimizer state (gradients and activations not
+        counted): what ZeRO sharding is meant to shrink."""
+        state = sum(t.numel() * 4 for t in (self.muon_master, self.muon_mom, self.adam_master,
+                                            self.adam_m, self.adam_v, self.vec_master, self.vec_m,
+                                            self.vec_v))
+        if self.fsdp:
+            lp = 2 * self.n_sym_w
+            landing = sum(2 * t.numel() for t in self.landing.values())
+        else:
+            lp = 2 * (self.n_muon + self.n_adam)
+            landing = 0
+        return {"weights_bf16_bytes": lp, "landing_bytes": landing, "optimizer_state_bytes": state,
+                "gradient_bytes": 4 * (self.n_muon + self.n_adam + self.n_vec),
+                "weights_plus_state_bytes": lp + landing + state}
+
+    def close(self) -> None:
+        """Release the symmetric-memory mappings (collective: every rank calls it)."""
+        if self.sym is None:
+            return
+        torch.cuda.synchronize(self.device)
+        torch.distributed.barrier(self.pg)
+        self.p = {}
+        for name in ("muon_grad", "adam_grad", "vec_grad", "muon_lp", "adam_lp", "sym_w_local"):
+            if hasattr(self, name):
+                delattr(self, name)
+        bufs = [self.sym_grad, self.sym_lp]
+        for ctx in (self.ep_ctx, self.cp_ctx):
+            for attr in ("counts", "xbuf", "ybuf", "dotbuf", "buf"):
+                b = getattr(ctx, attr, None) if ctx is not None else None
+                if b is not None and hasattr(b, "close"):
+                    bufs.append(b)
+        if self.cp_ctx is not None:
+            bufs.append(self.cp_ctx.sym.ctrl)
+        bufs.append(self.sym.ctrl)
+        for b in bufs:
+            b.close_peers()
+        torch.cuda.synchronize(self.device)
+        torch.distributed.barrier(self.pg)     # nobody maps a peer's memory any more
+        for b in bufs:
+            b.free_local()
+        self.sym = self.ep_ctx = self.cp_ctx = None
+        torch.distributed.barrier(self.pg)
 
     # ------------------------------------------------------------ tree <-> flat
     @staticmethod
@@ -418,12 +649,64 @@ class Trainer:
             return t.reshape(-1, t.shape[-1]).t().contiguous()
         return t
 
+    def _owned_pieces(self, group: str, g0: int, g1: int):
+        """Intersections of the global flat range [g0, g1) of a state group with what this
+        rank stores: ``[(global_start, global_end, local_start)]``."""
+        out = []
+        if not self.compact:            # full-size buffers addressed by the global offsets
+            return [(g0, g1, g0)]
+        if group == "muon":
+            for key, (glo, ghi) in self.class_range.items():
+                lo, hi = max(g0, glo), min(g1, ghi)
+                if hi > lo:
+                    out.append((lo, hi, self.class_lbase[key] + lo - glo))
+        elif group == "adam":
+            lo, hi = max(g0, self.own_adam[0]), min(g1, self.own_adam[1])
+            if hi > lo:
+                out.append((lo, hi, lo - self.adam_shift))
+        else:
+            out.append((g0, g1, g0))
+        return out
+
+    def _state_buffers(self, group: str) -> dict:
+        if group == "muon":
+            return {"master": self.muon_master, "mom": self.muon_mom}
+        if group == "adam":
+            return {"master": self.adam_master, "m": self.adam_m, "v": self.adam_v}
+        return {"master": self.vec_master, "m": self.vec_m, "v": self.vec_v}
+
+    def _store_state(self, w: Weight, which: str, full: Tensor) -> None:
+        """Write one state tensor of a weight (fp32, the weight's shape) into what this rank
+        stores of it; ``which`` in master / mom / m / v."""
+        n = int(math.prod(w.shape))
+        flat = full.reshape(-1)
+        buf = self._state_buffers(w.group)[which]
+        for lo, hi, l0 in self._owned_pieces(w.group, w.off, w.off + n):
+            buf[l0:l0 + hi - lo].copy_(flat[lo - w.off:hi - w.off])
+
+    def _store_lp(self, w: Weight, full: Tensor) -> None:
+        """Refresh the bf16 working copy of a weight from its full fp32 value (this rank's part
+        of it under ZeRO-3)."""
+        if not w.lp:
+            return
+        n = int(math.prod(w.shape))
+        flat = full.reshape(-1).to(BF16)
+        if not self.fsdp or w.mode != "shard":
+            self.p[w.name].detach().reshape(-1).copy_(flat)
+            return
+        b = self.blobs[w.blob]
+        c0 = self.rank * b["chunk"]                # blob positions of my chunk: [c0, c0 + chunk)
+        lo, hi = max(w.pos, c0), min(w.pos + n, c0 + b["chunk"])
+        if hi > lo:
+            dst0 = b["shard_off"] + lo - c0
+            self.sym_w_local[dst0:dst0 + hi - lo].copy_(flat[lo - w.pos:hi - w.pos])
+
     def load_tree(self, params: dict) -> None:
         """Copy a parameter tree (reference layout) into the flat buffers."""
         flat = M.flatten_params(params)
         with torch.no_grad():
             for w in self.weights.values():
-                dst = self.p[w.name].master
+                full = torch.zeros(w.shape, dtype=torch.float32, device=self.device)
                 for tree_name, r0, rows, how, _ in w.sources:
                     leaf = flat[tree_name]
                     if not leaf.is_meta:
@@ -434,9 +717,10 @@ class Trainer:
                     else:
                         src = self._to_engine(M.init_leaf(self.cfg, tree_name, leaf.shape, self.seed,
                                                           self.device), how)
-                    dst[r0:r0 + rows].copy_(src.to(self.device))
-            self.muon_lp.copy_(self.muon_master)
-            self.adam_lp.copy_(self.adam_master)
+                    full[r0:r0 + rows].copy_(src.to(self.device))
+                self._store_state(w, "master", full)
+                self._store_lp(w, full)
+                del full
             self.router_bias = {}
             for i in self.moe_layers:
                 name = f"layers.{i}.router_bias"
@@ -444,37 +728,69 @@ class Trainer:
                     b = flat.get(name)
                     self.router_bias[i] = (torch.zeros(self.cfg.n_routed_experts)
                                            if b is None or b.is_meta else b.detach().float().clone()).to(self.device)
+        if self.fsdp:
+            self._fsdp_invalidate()
+        if self.sym is not None:
+            torch.cuda.synchronize()
+            torch.distributed.barrier(self.pg)
+
+    def full_state(self) -> dict:
+        """Every flat fp32 state buffer at its full (global) size, complete on every rank:
+        ``muon.master / muon.mom / adam.master / adam.m / adam.v / vec.master / vec.m / vec.v``.
+        With ownership sharding each rank contributes the ranges it owns and the rest comes from
+        a sum over the ranks (collective); expert-parallel ranges stay this rank's own."""
+        out = {"vec.master": self.vec_master, "vec.m": self.vec_m, "vec.v": self.vec_v}
+        if self.sym is None:
+            out.update({"muon.master": self.muon_master, "muon.mom": self.muon_mom,
+                        "adam.master": self.adam_master, "adam.m": self.adam_m, "adam.v": self.adam_v})
+            return out
+        import torch.distributed as dist
+
+        f32 = dict(dtype=torch.float32, device=self.device)
+        for which, buf in (("master", self.muon_master), ("mom", self.muon_mom)):
+            full = torch.zeros(self.n_muon, **f32)
+            local = []
+            for key, (glo, ghi) in self.class_range.items():
+                if ghi <= glo:
+                    continue
+                l0 = self.class_lbase[key]
+                if len(key) > 2:
+                    local.append((glo, ghi, l0))      # this rank's experts: not summed
+                else:
+                    full[glo:ghi] = buf[l0:l0 + ghi - glo]
+            dist.all_reduce(full, group=self.pg)
+            for glo, ghi, l0 in local:
+                full[glo:ghi] = buf[l0:l0 + ghi - glo]
+            out["muon." + which] = full
+        a_lo, a_hi = self.own_adam
+        for which, buf in (("master", self.adam_master), ("m", self.adam_m), ("v", self.adam_v)):
+            full = torch.zeros(self.n_adam, **f32)
+            full[a_lo:a_hi] = buf[a_lo - self.adam_shift:a_hi - self.adam_shift]
+            dist.all_reduce(full, group=self.pg)
+            out["adam." + which] = full
+        return out
+
+    def load_full_state(self, state: dict) -> None:
+        """Inverse of :meth:`full_state`: every rank is given the full buffers and keeps what it
+        stores; the bf16 working copies are rebuilt from the masters."""
+        with torch.no_grad():
+            for w in self.weights.values():
+                n = int(math.prod(w.shape))
+                for which in self._state_buffers(w.group):
+                    full = state[f"{w.group}.{which}"][w.off:w.off + n].to(self.device)
+                    self._store_state(w, which, full)
+                    if which == "master":
+                        self._store_lp(w, full)
+        if self.fsdp:
+            self._fsdp_invalidate()
         if self.sym is not None:
             torch.cuda.synchronize()
             torch.distributed.barrier(self.pg)
 
     def gather_masters(self) -> dict:
-        """Full fp32 master buffers per group on every rank. With ownership sharding each
-        rank only keeps the masters of the matrices it owns up to date, so the owned ranges
-        are summed across ranks (everything else contributes zeros)."""
-        if self.sym is None:
-            return {"muon": self.muon_master, "adam": self.adam_master, "vec": self.vec_master}
-        import torch.distributed as dist
-
-        muon = torch.zeros_like(self.muon_master)
-        local_ranges = []
-        for key, units in self.unit_classes.items():
-            rows, cols = key[:2]
-            lo_u, hi_u = self.own_units[key]
-            lo = units[0].off + lo_u * rows * cols
-            hi = units[0].off + hi_u * rows * cols
-            if len(key) > 2:
-                local_ranges.append((lo, hi))      # this rank's experts: not summed
-            else:
-                muon[lo:hi] = self.muon_master[lo:hi]
-        adam = torch.zeros_like(self.adam_master)
-        a_lo, a_hi = self.own_adam
-        adam[a_lo:a_hi] = self.adam_master[a_lo:a_hi]
-        dist.all_reduce(muon, group=self.pg)
-        dist.all_reduce(adam, group=self.pg)
-        for lo, hi in local_ranges:
-            muon[lo:hi] = self.muon_master[lo:hi]
-        return {"muon": muon, "adam": adam, "vec": self.vec_master}
+        """Full fp32 master buffers per group on every rank (see :meth:`full_state`)."""
+        st = self.full_state()
+        return {"muon": st["muon.master"], "adam": st["adam.master"], "vec": st["vec.master"]}
 
     def export_tree(self) -> dict:
         """Parameter tree (reference layout, fp32, on CPU) from the master buffers."""
@@ -532,7 +848,7 @@ class Trainer:
             # input on the same kernel; its input gradient folds into the shared dx epilogue
             q, k, v, bl = ops.linear_multi(n, (self.p[pre + "q"], self.p[pre + "k"], self.p[pre + "v"],
                                                self.p[pre + "beta"]))
-            beta = torch.sigmoid(bl).view(B, S, nh)
+            beta = torch.sigmoid(bl[:, :nh]).view(B, S, nh)
         else:
             q, k, v = ops.linear_multi(n, (self.p[pre + "q"], self.p[pre + "k"], self.p[pre + "v"]))
             beta = torch.ones((B, S, nh), dtype=BF16, device=n.device)
@@ -673,6 +989,8 @@ class Trainer:
         cfg = self.cfg
         for i in range(start, start + count):
             pre = f"layers.{i}."
+            if self.fsdp:
+                self._fsdp_enter(i)
             if res is None:
                 n, h = ops.rmsnorm(x, self.p[pre + "pre_attn_norm"]), x
             else:
@@ -689,6 +1007,9 @@ class Trainer:
                 f = self._ffn_linear(ops.swiglu(gu), self.p[pre + "down"])
             else:
                 f = self._moe_layer(n2, i)
+            if self.fsdp and torch.is_grad_enabled():
+                # the backward of this layer starts here: its weights must be resident again
+                f = _FsdpLayerHook.apply(f, self, i)
             x, res = f, h
         return x, res
 
@@ -715,7 +1036,7 @@ class Trainer:
         cfg = self.cfg
         B, S = tokens.shape
         if inputs_embeds is None:
-            h = _EmbedFn.apply(tokens, self.p["embed"]).reshape(B, S, cfg.d_model)
+            h = _EmbedFn.apply(tokens, self.weight("embed")).reshape(B, S, cfg.d_model)
         else:
             h = inputs_embeds.reshape(B, S, cfg.d_model)
         n_th = 0
@@ -781,7 +1102,7 @@ class Trainer:
         start, k, sweeps, trunc = self.latent_slots
         B, S = tokens.shape
         d = self.cfg.d_model
-        embeds = _EmbedFn.apply(tokens, self.p["embed"]).reshape(B, S, d)
+        embeds = _EmbedFn.apply(tokens, self.weight("embed")).reshape(B, S, d)
         cur, hidden = embeds, None
         for i in range(sweeps):
             if sweeps - trunc > 0 and i == sweeps - trunc:
@@ -814,7 +1135,7 @@ class Trainer:
             wt = loss_mask.float().clone()
             wt[:, 0] = 0.0                          # mask[:, 1:] aligned to the predicting position
             wt = torch.roll(wt, -1, dims=1).reshape(-1) / denom
-        ce = ops.softcap_cross_entropy(hid, self.p["unembed"], targets, wt.contiguous(),
+        ce = ops.softcap_cross_entropy(hid, self.weight("unembed"), targets, wt.contiguous(),
                                        float(self.tcfg.softcap), self.ce_chunk_rows)
         n_mtp = self.cfg.mtp_heads
         for j in range(n_mtp):
@@ -827,7 +1148,7 @@ class Trainer:
             dj = mtp_denoms[j] if mtp_denoms is not None else wj.sum().clamp(min=1.0)
             tj = torch.roll(tokens, -off, dims=1).reshape(-1).to(torch.int32)
             mh = ops.linear(ops.rmsnorm(hid, self.p[f"mtp.{j}.norm"]), self.p[f"mtp.{j}.proj"]) + hid
-            ce = ce + ops.softcap_cross_entropy(mh, self.p[f"mtp.{j}.unembed"], tj,
+            ce = ce + ops.softcap_cross_entropy(mh, self.weight(f"mtp.{j}.unembed"), tj,
                                                 (wj.reshape(-1) / (dj * n_mtp)).contiguous(),
                                                 float(self.tcfg.softcap), self.ce_chunk_rows)
         if self.moe_layers and self.tcfg.z_loss_weight and self.router_records:
@@ -868,8 +1189,23 @@ class Trainer:
                  ptr(self.gnorm_sq), 1, st)
             return
         sym = self.sym
-        sym.barrier(0)                      # every rank's backward is complete
+        noop = self.comm_noop               # timing only: same kernels minus the peer traffic
+        if self.fsdp:                       # no pull of a working weight may still be in flight
+            torch.cuda.current_stream(self.device).wait_stream(self.fetch_stream)
+        if not noop:
+            sym.barrier(0)                  # every rank's backward is complete
         first = True
+
+        def fold(byte_off, lo, n, out):
+            nonlocal first
+            if noop:
+                call("pb_sumsq_f32", ptr(out[lo:]), n, ptr(self.opt_scratch), ptr(self.local_sq),
+                     0 if first else 1, st)
+            else:
+                sym.reduce_to_owner(self.sym_grad, byte_off, lo, n, out, self.opt_scratch,
+                                    self.local_sq, not first)
+            first = False
+
         for key, units in sorted(self.unit_classes.items()):
             rows, cols = key[:2]
             lo_u, hi_u = self.own_units[key]
@@ -878,23 +1214,26 @@ class Trainer:
                 if len(key) > 2:       # this rank's experts: the local gradient is the gradient
                     call("pb_sumsq_f32", ptr(self.muon_grad[lo:]), (hi_u - lo_u) * rows * cols,
                          ptr(self.opt_scratch), ptr(self.local_sq), 0 if first else 1, st)
+                    first = False
                 else:
-                    sym.reduce_to_owner(self.sym_grad, 0, lo, (hi_u - lo_u) * rows * cols,
-                                        self.muon_grad, self.opt_scratch, self.local_sq, not first)
-                first = False
+                    fold(0, lo, (hi_u - lo_u) * rows * cols, self.muon_grad)
         a_lo, a_hi = self.own_adam
         if a_hi > a_lo:
-            sym.reduce_to_owner(self.sym_grad, 4 * self.n_muon, a_lo, a_hi - a_lo, self.adam_grad,
-                                self.opt_scratch, self.local_sq, not first)
-            first = False
+            fold(4 * self.n_muon, a_lo, a_hi - a_lo, self.adam_grad)
         if first:
             self.local_sq.zero_()
         # vectors: every rank folds all peers (same order, same bits) into a private copy
         if not hasattr(self, "vec_sum"):
             self.vec_sum = torch.zeros_like(self.vec_master)
-        sym.reduce_to_owner(self.sym_grad, 4 * (self.n_muon + self.n_adam), 0, self.n_vec,
-                            self.vec_sum, self.opt_scratch, self.vec_sq, False)
-        sym.allreduce_scalar(self.local_sq, self.gnorm_sq)   # also: all reads of grads done
+        if noop:
+            self.vec_sum.copy_(self.vec_grad)
+            call("pb_sumsq_f32", ptr(self.vec_sum), self.n_vec, ptr(self.opt_scratch),
+                 ptr(self.vec_sq), 0, st)
+            self.gnorm_sq.copy_(self.local_sq)
+        else:
+            sym.reduce_to_owner(self.sym_grad, 4 * (self.n_muon + self.n_adam), 0, self.n_vec,
+                                self.vec_sum, self.opt_scratch, self.vec_sq, False)
+            sym.allreduce_scalar(self.local_sq, self.gnorm_sq)   # also: all reads of grads done
         self.gnorm_sq.add_(self.vec_sq)
 
     def _newton_schulz_class(self, rows: int, cols: int, nb: int, steps: int) -> Tensor:
@@ -922,7 +1261,7 @@ class Trainer:
 
     def optimizer_step(self, lr_mult: float, gscale: float = 1.0) -> None:
         """Clip, AdamW slabs, batched Muon on the owned matrices; refreshes the bf16 working
-        copies (on every rank when the weights live in symmetric memory)."""
+        copies: locally, into every peer's replica, or into the shard holders (ZeRO-3)."""
         tc = self.tcfg
         st = stream_ptr()
         clip = float(tc.grad_clip)
@@ -933,14 +1272,32 @@ class Trainer:
         call("pb_adamw", ptr(self.vec_master), ptr(vec_grad), ptr(self.vec_m), ptr(self.vec_v),
              None, self.n_vec, *hp, step, ptr(self.gnorm_sq), clip, gscale, st)
         a_lo, a_hi = self.own_adam
-        if self.sym is None:
+        sh = self.adam_shift
+        peers_on = self.sym is not None and not self.comm_noop
+        if self.fsdp:
+            for lo, n, (pos, chunk, base) in self.adam_segments:
+                if not peers_on:       # timing only: same arithmetic, bf16 result to a scratch buffer
+                    call("pb_adamw", ptr(self.adam_master[lo - sh:]), ptr(self.adam_grad[lo:]),
+                         ptr(self.adam_m[lo - sh:]), ptr(self.adam_v[lo - sh:]),
+                         ptr(self._noop_scratch(n)), n, *hp, step, ptr(self.gnorm_sq), clip, gscale, st)
+                    continue
+                call("pb_adamw_table", ptr(self.adam_master[lo - sh:]), ptr(self.adam_grad[lo:]),
+                     ptr(self.adam_m[lo - sh:]), ptr(self.adam_v[lo - sh:]), n, *hp, step,
+                     ptr(self.gnorm_sq), clip, gscale, pos, chunk, base, self.sym_lp.ptrs,
+                     self.world, self.rank, st)
+        elif self.sym is None:
             call("pb_adamw", ptr(self.adam_master), ptr(self.adam_grad), ptr(self.adam_m),
                  ptr(self.adam_v), ptr(self.adam_lp), self.n_adam, *hp, step, ptr(self.gnorm_sq),
                  clip, gscale, st)
         elif a_hi > a_lo:
-            call("pb_adamw_bcast", ptr(self.adam_master), ptr(self.adam_grad), ptr(self.adam_m),
-                 ptr(self.adam_v), self.sym_lp.peer_ptrs(2 * self.n_muon), self.world, a_lo,
-                 a_hi - a_lo, *hp, step, ptr(self.gnorm_sq), clip, gscale, st)
+            if peers_on:
+                call("pb_adamw_bcast", ptr(self.adam_master), ptr(self.adam_grad), ptr(self.adam_m),
+                     ptr(self.adam_v), self.sym_lp.peer_ptrs(2 * self.n_muon), self.world, a_lo,
+                     a_hi - a_lo, *hp, step, ptr(self.gnorm_sq), clip, gscale, st)
+            else:
+                call("pb_adamw", ptr(self.adam_master[a_lo:]), ptr(self.adam_grad[a_lo:]),
+                     ptr(self.adam_m[a_lo:]), ptr(self.adam_v[a_lo:]), ptr(self.adam_lp[a_lo:]),
+                     a_hi - a_lo, *hp, step, ptr(self.gnorm_sq), clip, gscale, st)
         lr = float(tc.muon_lr) * lr_mult
         beta = float(tc.muon_momentum)
         for key, units in sorted(self.unit_classes.items()):
@@ -950,23 +1307,42 @@ class Trainer:
             if nb == 0:
                 continue
             n = rows * cols
-            base = units[0].off + lo_u * n
+            base = units[0].off + lo_u * n           # gradients: global flat offsets
+            lb = self.class_lbase[key]               # masters / momenta: where this rank keeps them
             # momentum, Nesterov and Frobenius normalisation of the whole shape class: three
             # launches whatever the number of matrices
-            call("pb_muon_prepare_batched", ptr(self.muon_grad[base:]), ptr(self.muon_mom[base:]),
+            call("pb_muon_prepare_batched", ptr(self.muon_grad[base:]), ptr(self.muon_mom[lb:]),
                  ptr(self.ns_x[0]), n, nb, beta, ptr(self.gnorm_sq), clip, gscale,
                  ptr(self.opt_scratch), st)
             xo = self._newton_schulz_class(rows, cols, nb, int(tc.muon_ns_steps))
             scale = T.muon_rms_scale(rows, cols)
-            if self.sym is None or len(key) > 2:
-                call("pb_muon_apply", ptr(self.muon_master[base:]), ptr(xo),
+            if self.fsdp and peers_on:
+                call("pb_muon_apply_table", ptr(self.muon_master[lb:]), ptr(xo), n, nb, lr, scale,
+                     self.muon_wd, ptr(self.dest_tables[key][lo_u:]), self.sym_lp.ptrs, self.world,
+                     self.rank, st)
+            elif self.fsdp:            # timing only: bf16 result to a scratch buffer
+                call("pb_muon_apply", ptr(self.muon_master[lb:]), ptr(xo),
+                     ptr(self._noop_scratch(n * nb)), n * nb, lr, scale, self.muon_wd, st)
+            elif self.sym is None or len(key) > 2 or not peers_on:
+                call("pb_muon_apply", ptr(self.muon_master[lb:]), ptr(xo),
                      ptr(self.muon_lp[base:]), n * nb, lr, scale, self.muon_wd, st)
             else:
                 call("pb_muon_apply_bcast", ptr(self.muon_master), ptr(xo),
                      self.sym_lp.peer_ptrs(0), self.world, base, n * nb, lr, scale,
                      self.muon_wd, st)
-        if self.sym is not None:
+        if self.fsdp:
+            self._fsdp_invalidate()         # every landing slot is stale now
+        if self.sym is not None and not self.comm_noop:
             self.sym.barrier(3)             # every peer's stores into my weights have landed
+
+    def _noop_scratch(self, n: int) -> Tensor:
+        """bf16 scratch the no-traffic timing mode writes refreshed weights to (so that the
+        real shards keep valid contents)."""
+        t = getattr(self, "_noop_lp", None)
+        if t is None or t.numel() < n:
+            t = torch.empty(n, dtype=BF16, device=self.device)
+            self._noop_lp = t
+        return t
 
     def zero_grad(self) -> None:
         self.muon_grad.zero_()
@@ -1062,15 +1438,29 @@ class Trainer:
         for row, i in enumerate(layers):
             pre = f"layers.{i}."
             for name, is_k, heads in ((pre + "q", 0, nh), (pre + "k", 1, nkv)):
-                w = self.p[name]
+                w = self.weights[name]
+                n = heads * dh * cfg.d_model
                 args = (heads * dh, cfg.d_model, dh, nh // nkv, nh, is_k, 0, ptr(m[row]), tau, st)
+                pieces = self._owned_pieces("muon", w.off, w.off + n)
+                owned = bool(pieces) and pieces[0][1] - pieces[0][0] == n
+                master = self.muon_master[pieces[0][2]:] if owned else None
                 if self.sym is None:
-                    call("pb_qk_clip_rescale", ptr(w.master), ptr(w), *args)
-                else:
+                    call("pb_qk_clip_rescale", ptr(master), ptr(self.p[name]), *args)
+                elif not self.fsdp:
                     # replicas must stay bit-identical: every rank rescales its bf16 copy from
                     # the copy itself; the fp32 master is rescaled where it lives
-                    call("pb_qk_clip_rescale", ptr(w.master), None, *args)
-                    call("pb_qk_clip_rescale", None, ptr(w), *args)
+                    call("pb_qk_clip_rescale", ptr(master), None, *args)
+                    call("pb_qk_clip_rescale", None, ptr(self.p[name]), *args)
+                elif owned:
+                    # the owner rescales the master and re-stores its bf16 value to the shard
+                    # holders (the update kernel with a zero step)
+                    key, idx = self.unit_index[(name, 0)]
+                    call("pb_qk_clip_rescale", ptr(master), None, *args)
+                    call("pb_muon_apply_table", ptr(master), ptr(self.ns_x[0]), n, 1, 0.0, 0.0, 0.0,
+                         ptr(self.dest_tables[key][idx:]), self.sym_lp.ptrs, self.world, self.rank, st)
+        if self.fsdp:
+            self._fsdp_invalidate()
+            self.sym.barrier(3)
         self.last_max_logits = m
 
     def status_tensor(self) -> Tensor:

@@ -26,7 +26,40 @@ import os
 import torch
 import torch.distributed as dist
 
-LINK_GBS = 770.0          # measured peer copy per direction per GPU on this pool
+NOMINAL_LINK_GBS = 900.0  # NVLink 5 per direction per GPU
+_link_gbs: float | None = None
+
+
+def link_gbs(dev=None) -> float:
+    """Peer bandwidth per direction per GPU, measured once per process: every rank pulls 256 MiB
+    from its next rank's symmetric buffer with 16-byte loads (the gather kernel of the ZeRO-3
+    path), CUDA events, minimum over the ranks. It is the denominator of every link-bound
+    roofline below; the nominal figure is only the fallback when the measurement cannot run."""
+    global _link_gbs
+    if _link_gbs is not None:
+        return _link_gbs
+    try:
+        import ctypes
+
+        from ..ops import _lib
+        from ..ops._lib import call, ptr, stream_ptr
+        from .symm import SymmetricBuffer
+
+        _lib.register("pb_shard_gather", [ctypes.POINTER(ctypes.c_void_p), ctypes.c_long, ctypes.c_long,
+                                          ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                          ctypes.c_void_p])
+        world, rank = dist.get_world_size(), dist.get_rank()
+        n = 128 * 1024 * 1024                                   # bf16 elements = 256 MiB
+        buf = SymmetricBuffer(2 * n)
+        dst = torch.empty(n, dtype=torch.bfloat16, device=buf.bytes.device)
+        nxt = (ctypes.c_void_p * 8)(buf.addrs[(rank + 1) % world], *([None] * 7))
+        run = lambda: call("pb_shard_gather", nxt, 0, n, ptr(dst), 1, 0, 0, stream_ptr())  # noqa: E731
+        ms = timed(run, buf.bytes.device, iters=5, warmup=2)
+        _link_gbs = 2.0 * n / (ms * 1e-3) / 1e9
+        buf.close()
+    except Exception:       # no peer mapping on this machine
+        _link_gbs = NOMINAL_LINK_GBS
+    return _link_gbs
 
 
 def _peaks() -> dict:
@@ -54,7 +87,7 @@ def timed(fn, dev, iters: int = 10, warmup: int = 3) -> float:
 
 def roofline(ms: float, flops: float, link_bytes: float) -> dict:
     t_compute = flops / (_peaks()["bf16_tflops"] * 1e12) * 1e3
-    t_link = link_bytes / (LINK_GBS * 1e9) * 1e3
+    t_link = link_bytes / (link_gbs() * 1e9) * 1e3
     bound = max(t_compute, t_link)
     return {"ms": ms, "roofline_ms": bound, "bound_by": "compute" if t_compute >= t_link else "link",
             "fraction_of_roofline": bound / ms if ms > 0 else 0.0}

@@ -33,6 +33,10 @@ _lib.register("pb_publish_scalar", [PP, I, I, P, P])
 _lib.register("pb_sum_slots", [P, I, P, P])
 _lib.register("pb_adamw_bcast", [P, P, P, P, PP, I, L, L, F, F, F, F, F, I, P, F, F, P])
 _lib.register("pb_muon_apply_bcast", [P, P, PP, I, L, L, F, F, F, P])
+# ZeRO-3 parameter sharding (csrc/comm/fsdp.cu)
+_lib.register("pb_shard_gather", [PP, L, L, P, I, I, I, P])
+_lib.register("pb_muon_apply_table", [P, P, L, I, F, F, F, P, PP, I, I, P])
+_lib.register("pb_adamw_table", [P, P, P, P, L, F, F, F, F, F, I, P, F, F, L, L, L, PP, I, I, P])
 
 MAX_RANKS = 8
 _DT = {torch.float32: "<f4", torch.bfloat16: None, torch.uint8: "|u1", torch.int32: "<i4"}
@@ -87,13 +91,26 @@ class SymmetricBuffer:
         vals = [a + byte_offset for a in self.addrs] + [None] * (MAX_RANKS - self.world)
         return (ctypes.c_void_p * MAX_RANKS)(*vals)
 
-    def close(self):
+    def close_peers(self):
+        """Unmap the peers' allocations (first phase of a collective release)."""
         for a in self._opened:
             call("pb_ipc_close_handle", a)
         self._opened = []
+
+    def free_local(self):
+        """Free this rank's allocation. Only after every peer has unmapped it: freeing an
+        exported allocation that an importer still has open is undefined."""
+        self.bytes = None
         if self.local_ptr:
             call("pb_symm_free", self.local_ptr)
             self.local_ptr = None
+
+    def close(self):
+        """Collective release: unmap peers, meet, free."""
+        self.close_peers()
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        self.free_local()
 
 
 class SymmetricGroup:

@@ -66,3 +66,61 @@ def test_apply_rejects_other_model_and_bad_sizes():
     short.adam_master = torch.zeros(36)
     with pytest.raises(ValueError):
         checkpoint.apply(short, ck)
+
+
+def _free_port():
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _two_rank_restore_worker(rank, world, port, root, out):
+    import os
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        a = _fake_trainer(0)                   # every rank holds the same (already complete) state
+        a.world, a.rank, a.pg = world, rank, None
+        saver = checkpoint.TrainerCheckpointer(root if rank == 0 else None)   # only rank 0 has the store
+        mem_id = saver.save_memory(a)
+        b = _fake_trainer(5 + rank)
+        b.world, b.rank, b.pg = world, rank, None
+        saver.restore(b)                       # newest in-memory replica lives on rank 0 only
+        same_mem = all(torch.equal(getattr(a, n), getattr(b, n))
+                       for n in ("muon_master", "muon_mom", "adam_m", "adam_v", "vec_master"))
+        cid = saver.save_persistent(a, wait=True, loader_state={"cursor": 3})
+        c = _fake_trainer(9 + rank)
+        c.world, c.rank, c.pg = world, rank, None
+        loader = saver.restore(c, cid)         # rank 1's own store is empty: it must still succeed
+        same_disk = torch.equal(a.adam_master, c.adam_master) and c.step_count == a.step_count
+        try:
+            saver.restore(c, "f" * 64)
+            raised = False
+        except RuntimeError:
+            raised = True                      # rank 0's error reaches every rank; nobody hangs
+        out.put((rank, mem_id == cid, same_mem, same_disk, loader, raised))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_restore_reaches_every_rank(tmp_path):
+    """Only rank 0 keeps replicas and reads the store; a rollback or a resume must still restore
+    every rank, and a failed restore must fail everywhere instead of leaving ranks in a barrier."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_two_rank_restore_worker, args=(r, 2, port, str(tmp_path / "s"), out))
+             for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(60)
+    assert got == [(r, True, True, True, {"cursor": 3}, True) for r in range(2)]

@@ -59,3 +59,8 @@ def test_two_rank_all_gather_gemm():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_context_parallel_trainer():
     _run_ranks(2, 29527, "CP_ENGINE_OK", "cp_engine")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_zero3_trainer():
+    _run_ranks(2, 29529, "FSDP_ENGINE_OK", "fsdp_engine")
