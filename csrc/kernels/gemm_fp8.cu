@@ -263,6 +263,31 @@ __global__ void quant_rows_kernel(const bf16* __restrict__ x, long ld, int M, in
   if (lane == 0) scales[static_cast<size_t>(kb) * M + row] = scale;
 }
 
+// y[row, :] = bf16(e4m3(q[row, :]) * scale of its 1 x 128 block); one warp per (row, block)
+__global__ void dequant_rows_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales,
+                                    long ld_s, int M, int K, bf16* __restrict__ y) {
+  const long w = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nkb = K / 128;
+  if (w >= static_cast<long>(M) * nkb) return;
+  const int row = static_cast<int>(w / nkb), kb = static_cast<int>(w % nkb);
+  const float s = scales[static_cast<size_t>(kb) * ld_s + row];
+  const uint32_t raw = *reinterpret_cast<const uint32_t*>(q + static_cast<size_t>(row) * K + kb * 128 + lane * 4);
+  float f[4];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((raw >> (16 * j)) & 0xffffu),
+                                                     __NV_E4M3);
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h));
+    f[2 * j] = v.x; f[2 * j + 1] = v.y;
+  }
+  __nv_bfloat162 o0 = __floats2bfloat162_rn(f[0] * s, f[1] * s), o1 = __floats2bfloat162_rn(f[2] * s, f[3] * s);
+  uint2 pk;
+  pk.x = *reinterpret_cast<uint32_t*>(&o0);
+  pk.y = *reinterpret_cast<uint32_t*>(&o1);
+  *reinterpret_cast<uint2*>(y + static_cast<size_t>(row) * K + kb * 128 + lane * 4) = pk;
+}
+
 // One CTA (256 threads) per 128 x 128 block of a [N, K] matrix (edges clipped).
 __global__ void quant_blocks_kernel(const bf16* __restrict__ w, long ld, int N, int K,
                                     uint8_t* __restrict__ q, float* __restrict__ scales) {
@@ -309,6 +334,18 @@ PB_API int pb_fp8_quant_rows(const void* x, long ld, int M, int K, void* q, floa
   const long blocks = (warps * 32 + 255) / 256;
   f8::quant_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
       static_cast<const bf16*>(x), ld, M, K, static_cast<uint8_t*>(q), scales);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// q [M, K] e4m3 with scales [K / 128, ld_s] (ld_s >= M: the row stride of the scale table)
+// -> y [M, K] bf16. The straight-through backward of an FP8 product uses these values.
+PB_API int pb_fp8_dequant_rows(const void* q, const float* scales, long ld_s, int M, int K, void* y,
+                               cudaStream_t st) {
+  if (M <= 0 || K <= 0 || K % 128 != 0 || ld_s < M) return PB_BAD_ARG;
+  const long warps = static_cast<long>(M) * (K / 128);
+  const long blocks = (warps * 32 + 255) / 256;
+  f8::dequant_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+      static_cast<const uint8_t*>(q), scales, ld_s, M, K, static_cast<bf16*>(y));
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -161,6 +161,7 @@ class Trainer:
         self.latent_slots: tuple | None = None      # see set_latent_slots
         self.max_logits: dict[int, Tensor] = {}
         self.ep_ctx = None
+        self.side_stream = None
         if self.ep and model_config.n_routed_experts % self.world:
             raise ValueError("expert parallelism needs n_routed_experts divisible by the world size")
         self.ce_chunk_rows = int(ce_chunk_rows)
@@ -622,7 +623,7 @@ class Trainer:
                 delattr(self, name)
         bufs = [self.sym_grad, self.sym_lp]
         for ctx in (self.ep_ctx, self.cp_ctx):
-            for attr in ("counts", "xbuf", "ybuf", "dotbuf", "buf"):
+            for attr in ("counts", "xbuf", "ybuf", "dotbuf", "xqbuf", "xsbuf", "buf"):
                 b = getattr(ctx, attr, None) if ctx is not None else None
                 if b is not None and hasattr(b, "close"):
                     bufs.append(b)
@@ -917,12 +918,29 @@ class Trainer:
             if self.ep_ctx is None:
                 rows = int(self.ep_capacity_factor * T_ * cfg.top_k) + 128 * el
                 self.ep_ctx = EpContext(self.sym, cfg.d_model, cfg.n_routed_experts, rows)
+            # the shared experts (dense, always on) run on a side stream, so their GEMMs fill
+            # the SMs while the routed path is in its barriers, pushes and pulls
+            shared = None
+            main = torch.cuda.current_stream(self.device)
+            if cfg.n_shared_experts:
+                if self.side_stream is None:
+                    self.side_stream = torch.cuda.Stream(self.device)
+                side = self.side_stream
+                side.wait_stream(main)
+                n2.record_stream(side)
+                with torch.cuda.stream(side):
+                    for j in range(cfg.n_shared_experts):
+                        gu = self._ffn_linear(n2, self.p[pre + f"shared{j}_gate_up"])
+                        sj = self._ffn_linear(ops.swiglu(gu), self.p[pre + f"shared{j}_down"])
+                        shared = sj if shared is None else shared + sj
             out, probs, ids, logits = ep_moe_ffn(
                 n2, self.p[pre + "router"], self.router_bias.get(i), w_gu, w_dn, cfg.top_k, self.ep_ctx,
-                shapes=((el, 2 * hid, cfg.d_model), (el, cfg.d_model, hid)), return_logits=True)
-            for j in range(cfg.n_shared_experts):
-                gu = ops.linear(n2, self.p[pre + f"shared{j}_gate_up"])
-                out = out + ops.linear(ops.swiglu(gu), self.p[pre + f"shared{j}_down"])
+                shapes=((el, 2 * hid, cfg.d_model), (el, cfg.d_model, hid)), return_logits=True,
+                fp8=self.fp8)
+            if shared is not None:
+                main.wait_stream(self.side_stream)
+                shared.record_stream(main)
+                out = out + shared
             self._record_router(i, probs, ids, logits)
             return out
         n_e = cfg.n_routed_experts + cfg.n_shared_experts

@@ -72,6 +72,7 @@ _SIGS = {
     "pb_moe_combine_bwd": [P, P, P, I, I, I, P, P],
     "pb_fp8_quant_rows": [P, L, I, I, P, P, P],
     "pb_fp8_quant_blocks": [P, L, I, I, P, P, P],
+    "pb_fp8_dequant_rows": [P, P, L, I, I, P, P],
     "pb_gemm_fp8_blockscaled": [P, P, P, P, P, I, I, I, I, L, P, P, I, P],
     "pb_gemm_set_debug": [I],
     "pb_gemm_bf16": [P, P, P, P, I, I, I, I, L, L, L, L, L, L, L, L, I, I, I, I, F, F, P, I, P],

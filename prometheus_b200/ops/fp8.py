@@ -53,17 +53,32 @@ def dequantize_blocks(q: Tensor, s: Tensor) -> Tensor:
     return q.view(torch.float8_e4m3fn).float() * full
 
 
+def dequantize_rows_bf16(q: Tensor, s: Tensor) -> Tensor:
+    """(q [M, K] e4m3 bytes, s [K / 128, >= M] fp32) -> bf16 [M, K] on the GPU: the values an FP8
+    product really multiplied, which its straight-through backward differentiates against."""
+    M, K = q.shape
+    assert q.dtype == torch.uint8 and q.is_contiguous() and s.stride(1) == 1 and s.shape[1] >= M
+    y = torch.empty((M, K), dtype=BF16, device=q.device)
+    call("pb_fp8_dequant_rows", ptr(q), ptr(s), s.stride(0), M, K, ptr(y), stream_ptr())
+    return y
+
+
 def gemm_fp8(aq: Tensor, sa: Tensor, bq: Tensor, sb: Tensor, *, mblk_group: Tensor | None = None,
-             max_ctas: int = 0) -> Tensor:
+             max_ctas: int = 0, out: Tensor | None = None) -> Tensor:
     """C [M, N] bf16 = (aq, sa) @ (bq, sb)^T. bq [N, K], or [E, N, K] with ``mblk_group`` (one
-    int32 per 128-row block of aq naming its expert, negative = skip that block)."""
+    int32 per 128-row block of aq naming its expert, negative = skip that block). ``out``: a
+    contiguous bf16 [M, N] destination (e.g. a symmetric-memory buffer peers read)."""
     from .functional import status_word
 
     M, K = aq.shape
     groups = bq.shape[0] if bq.ndim == 3 else 1
     N = bq.shape[-2]
     assert bq.shape[-1] == K and (groups == 1 or mblk_group is not None)
-    out = torch.empty((M, N), dtype=BF16, device=aq.device)
+    assert sa.shape[1] == M and sa.is_contiguous()
+    if out is None:
+        out = torch.empty((M, N), dtype=BF16, device=aq.device)
+    else:
+        assert out.shape == (M, N) and out.dtype == BF16 and out.is_contiguous()
     call("pb_gemm_fp8_blockscaled", ptr(aq), ptr(sa), ptr(bq), ptr(sb), ptr(out), M, N, K, groups, N,
          ptr(mblk_group), ptr(status_word(aq.device)), int(max_ctas), stream_ptr())
     return out

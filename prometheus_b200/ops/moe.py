@@ -85,15 +85,19 @@ def combine(y: Tensor, pl: Placement, gates: Tensor | None, T: int, add: Tensor 
     return out
 
 
-def grouped_gemm(a: Tensor, w: Tensor, pl: Placement, *, b_mn: bool = False) -> Tensor:
+def grouped_gemm(a: Tensor, w: Tensor, pl: Placement, *, b_mn: bool = False,
+                 out: Tensor | None = None) -> Tensor:
     """C[rows of expert e] = A[rows] @ W[e]^T (``b_mn``: @ W[e]); a [rows, K], w [E, N, K]
-    (``b_mn``: [E, K, N])."""
+    (``b_mn``: [E, K, N]). ``out``: a contiguous bf16 [rows, N] destination."""
     from .functional import status_word
 
     R, K = a.shape
     E = w.shape[0]
     N = w.shape[2] if b_mn else w.shape[1]
-    out = torch.empty((R, N), dtype=BF16, device=a.device)
+    if out is None:
+        out = torch.empty((R, N), dtype=BF16, device=a.device)
+    else:
+        assert out.shape == (R, N) and out.dtype == BF16 and out.is_contiguous()
     rc_w = w.stride(1)
     call("pb_gemm_bf16_grouped", ptr(a), ptr(w), ptr(out), R, N, K, E, a.stride(0), rc_w, N,
          w.stride(0), 1 if b_mn else 0, ptr(pl.mblk_group), ptr(status_word(a.device)), 0,

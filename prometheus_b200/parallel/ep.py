@@ -4,8 +4,11 @@ Rank r owns routed experts ``[r * El, (r + 1) * El)``. Tokens reach their expert
 back through symmetric memory (``csrc/comm/ep.cu``): the sender stores its rows straight into
 the owner's receive buffer over NVLink (push), the owner runs the grouped tcgen05 GEMMs on
 what arrived, and the sender reads its results back out of the owner's buffer (pull) while
-applying the gates. The only synchronisation is the bounded device barrier between phases;
-there is no host round trip and no library collective in the layer.
+applying the gates. With ``fp8=True`` the rows cross NVLink as e4m3 bytes plus 1 x 128 scales
+(half the bytes), quantised by the sending kernel, and the grouped FP8 GEMM reads the receive
+buffers as they are. The only synchronisation is three bounded device barriers per direction
+(counts visible, rows landed, results ready); the GEMMs write their results straight into the
+buffer the peers pull from. There is no host round trip and no library collective in the layer.
 
 Reference behaviour: ``kernels/__init__.py`` ``ep_dispatch`` / ``ep_combine`` of the reference
 (stable token order per expert, capacity overflow reported rather than silently reordered) and
@@ -25,6 +28,8 @@ from .symm import PP, SymmetricBuffer, SymmetricGroup
 P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
 _lib.register("pb_ep_layout", [PP, I, I, I, I, P, P, P, P, P, P, P])
 _lib.register("pb_ep_dispatch", [P, L, P, P, P, P, P, I, I, I, I, I, PP, I, P, P, P])
+_lib.register("pb_ep_dispatch_fp8", [P, L, P, P, P, P, I, I, I, I, I, PP, PP, I, P, P, P])
+_lib.register("pb_ep_zero_pad_fp8", [P, P, I, I, P, P, I, P])
 _lib.register("pb_ep_combine", [PP, I, P, P, P, P, I, I, I, P, P])
 _lib.register("pb_ep_rowdot", [P, P, P, I, I, P, P])
 _lib.register("pb_ep_pull_scalar", [PP, I, P, P, P, I, P, P])
@@ -50,6 +55,13 @@ class EpContext:
         self.max_rows = (int(max_rows) + 127) // 128 * 128
         g = sym.group
         self.counts = SymmetricBuffer(4 * n_experts, g)
+        self.fp8_ok = d_model % 128 == 0
+        if self.fp8_ok:        # FP8 receive buffers: e4m3 rows and their [d / 128, max_rows] scales
+            self.xqbuf = SymmetricBuffer(self.max_rows * d_model, g)
+            self.xsbuf = SymmetricBuffer(4 * (d_model // 128) * self.max_rows, g)
+            self.xq_local = self.xqbuf.view(torch.uint8, self.max_rows * d_model).view(self.max_rows, d_model)
+            self.xs_local = self.xsbuf.view(torch.float32, (d_model // 128) * self.max_rows).view(
+                d_model // 128, self.max_rows)
         self.xbuf = SymmetricBuffer(2 * self.max_rows * d_model, g)
         self.ybuf = SymmetricBuffer(2 * self.max_rows * d_model, g)
         self.dotbuf = SymmetricBuffer(4 * self.max_rows, g)
@@ -82,6 +94,21 @@ class EpContext:
              self.world, ptr(dest_rank), ptr(dest_row), stream_ptr())
         return dest_rank, dest_row
 
+    def dispatch_fp8(self, x: Tensor, ids: Tensor, local: M.Placement, send_base: Tensor):
+        """Quantise and push: e4m3 rows + 1 x 128 scales into the owners' FP8 receive buffers."""
+        T, k = ids.shape
+        dev = x.device
+        dest_rank = torch.empty(T * k, dtype=torch.int32, device=dev)
+        dest_row = torch.empty(T * k, dtype=torch.int32, device=dev)
+        call("pb_ep_dispatch_fp8", ptr(x), x.stride(0), ptr(ids), ptr(local.row_of), ptr(local.expert_off),
+             ptr(send_base), T * k, k, self.d, self.El, self.max_rows, self.xqbuf.ptrs, self.xsbuf.ptrs,
+             self.world, ptr(dest_rank), ptr(dest_row), stream_ptr())
+        return dest_rank, dest_row
+
+    def zero_pad_fp8(self, pl: M.Placement) -> None:
+        call("pb_ep_zero_pad_fp8", ptr(self.xq_local), ptr(self.xs_local), self.d, self.max_rows,
+             ptr(pl.expert_off), ptr(pl.totals), self.El, stream_ptr())
+
     def combine(self, dest_rank, dest_row, gates, T: int, k: int, add: Tensor | None = None) -> Tensor:
         out = torch.empty((T, self.d), dtype=BF16, device=dest_rank.device)
         call("pb_ep_combine", self.ybuf.ptrs, self.world, ptr(dest_rank), ptr(dest_row), ptr(gates),
@@ -94,8 +121,16 @@ class EpContext:
 
 
 class _EpMoeFn(torch.autograd.Function):
+    """Barrier slots: 4 = every rank's per-expert counts are written (forward only), 5 = every
+    pushed row has landed, 6 = every owner's results are in its pull buffer. No barrier
+    separates layers or directions: a rank overwrites a peer's receive buffer only after passing
+    slot 6 of the previous layer, which the peer reached after its last read of that buffer, and
+    its own pull buffers only after slot 4 (forward) or 5 (backward) of the layer, which every
+    puller of the previous contents reached after its pulls."""
+
     @staticmethod
-    def forward(ctx, x, router_w, router_bias, w_gu_p, w_down_p, top_k, ep, shapes):
+    def forward(ctx, x, router_w, router_bias, w_gu_p, w_down_p, top_k, ep, shapes, fp8=False):
+        from ..ops import fp8 as F8
         from ..ops.functional import gemm
 
         w_gu = w_gu_p.view(shapes[0]) if shapes is not None else w_gu_p      # [El, 2h, d]
@@ -103,36 +138,53 @@ class _EpMoeFn(torch.autograd.Function):
         T, d = x.shape
         h = w_gu.shape[1] // 2
         sym = ep.sym
+        use_fp8 = bool(fp8) and ep.fp8_ok and h % 128 == 0
         logits = gemm(x, router_w, out_dtype=torch.float32)
         probs, ids, gates = M.route(logits, router_bias, top_k)
         local = M.place(ids, ep.E)
-        sym.barrier(7)                          # the previous layer's pulls are over everywhere
         ep.counts_local.copy_(local.totals)
         sym.barrier(4)
         pl, send_base = ep.layout()
-        dest_rank, dest_row = ep.dispatch(x, ids, local, send_base, None)
-        sym.barrier(5)                          # every row has landed
-        ep.zero_pad(pl)
-        xp = ep.x_local.clone()
-        gu = M.grouped_gemm(xp, w_gu, pl)
+        if use_fp8:
+            dest_rank, dest_row = ep.dispatch_fp8(x, ids, local, send_base)
+            sym.barrier(5)                      # every row has landed
+            ep.zero_pad_fp8(pl)
+            wq, sw = F8.quantize_blocks(w_gu.contiguous())
+            gu = F8.gemm_fp8(ep.xq_local, ep.xs_local, wq, sw, mblk_group=pl.mblk_group)
+            # what the backward differentiates against: the quantised rows (half the bytes of a
+            # bf16 copy); the receive buffer itself is overwritten by the next layer's senders
+            saved_x = (ep.xq_local.clone(), ep.xs_local.clone())
+        else:
+            dest_rank, dest_row = ep.dispatch(x, ids, local, send_base, None)
+            sym.barrier(5)
+            ep.zero_pad(pl)
+            xp = ep.x_local.clone()
+            gu = M.grouped_gemm(xp, w_gu, pl)
+            saved_x = (xp, xp.new_empty(0))
         hs = torch.empty((pl.rows, h), dtype=BF16, device=x.device)
         call("pb_swiglu_fwd", ptr(gu), ptr(hs), pl.rows, h, stream_ptr())
-        y = M.grouped_gemm(hs, w_down, pl)
-        ep.y_local.copy_(y)
+        if use_fp8:
+            hq, sh = F8.quantize_rows(hs)
+            wq, sw = F8.quantize_blocks(w_down.contiguous())
+            F8.gemm_fp8(hq, sh, wq, sw, mblk_group=pl.mblk_group, out=ep.y_local)
+        else:
+            M.grouped_gemm(hs, w_down, pl, out=ep.y_local)
+        y = ep.y_local.clone()                  # the gate gradient needs <y_row, dy_row> later
         sym.barrier(6)                          # results are ready to be pulled
         out = ep.combine(dest_rank, dest_row, gates, T, top_k)
-        ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids, gates, xp, gu, hs, y,
-                              dest_rank, dest_row, send_base)
-        ctx.pl, ctx.local, ctx.ep = pl, local, ep
+        ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids, gates, saved_x[0], saved_x[1], gu,
+                              hs, y, dest_rank, dest_row, send_base)
+        ctx.pl, ctx.local, ctx.ep, ctx.use_fp8 = pl, local, ep, use_fp8
         ctx.refs = (router_w, w_gu_p, w_down_p)
         ctx.mark_non_differentiable(ids)
         return out, probs, ids, logits
 
     @staticmethod
     def backward(ctx, d_out, d_probs, _di, d_logits=None):
+        from ..ops import fp8 as F8
         from ..ops.functional import gemm
 
-        (x, router_w, w_gu, w_down, probs, ids, gates, xp, gu, hs, y, dest_rank, dest_row,
+        (x, router_w, w_gu, w_down, probs, ids, gates, xs0, xs1, gu, hs, y, dest_rank, dest_row,
          send_base) = ctx.saved_tensors
         router_ref, gu_ref, down_ref = ctx.refs
         pl, local, ep = ctx.pl, ctx.local, ctx.ep
@@ -143,21 +195,21 @@ class _EpMoeFn(torch.autograd.Function):
         h = w_gu.shape[1] // 2
         d_out = d_out.contiguous()
         gflat = gates.reshape(-1)
-        sym.barrier(7)
-        ep.dispatch(d_out, ids, local, send_base, gflat)       # dY rows = gate * dOut[t]
-        sym.barrier(4)
+        ep.dispatch(d_out, ids, local, send_base, gflat)       # dY rows = gate * dOut[t], bf16
+        sym.barrier(5)
         ep.zero_pad(pl)
-        dyp = ep.x_local.clone()
+        dyp = ep.x_local            # read in place: nobody overwrites it before slot 6 below
         call("pb_ep_rowdot", ptr(y), ptr(dyp), ptr(pl.expert_off[ep.El:]), pl.rows, d,
              ptr(ep.dot_local), stream_ptr())
         dh = M.grouped_gemm(dyp, w_down, pl, b_mn=True)
         g_down = M._acc_grad(down_ref, w_down.shape, lambda o, acc: M.grouped_wgrad(dyp, hs, pl, o, acc))
         dgu = torch.empty_like(gu)
         call("pb_swiglu_bwd", ptr(dh), ptr(gu), ptr(dgu), pl.rows, h, stream_ptr())
+        xp = F8.dequantize_rows_bf16(xs0, xs1) if ctx.use_fp8 else xs0
         g_gu = M._acc_grad(gu_ref, w_gu.shape, lambda o, acc: M.grouped_wgrad(dgu, xp, pl, o, acc))
-        dxp = M.grouped_gemm(dgu, w_gu, pl, b_mn=True)
-        ep.y_local.copy_(dxp)
-        sym.barrier(5)
+        del xp
+        M.grouped_gemm(dgu, w_gu, pl, b_mn=True, out=ep.y_local)
+        sym.barrier(6)
         dgates = torch.empty((T, k), dtype=torch.float32, device=x.device)
         call("pb_ep_pull_scalar", ep.dotbuf.ptrs, ep.world, ptr(dest_rank), ptr(dest_row), ptr(gflat),
              T * k, ptr(dgates), stream_ptr())
@@ -171,7 +223,6 @@ class _EpMoeFn(torch.autograd.Function):
         dl = dlogits.to(BF16)
         dx_r = gemm(dl, router_w, b_mn=True)
         dx = ep.combine(dest_rank, dest_row, None, T, k, add=dx_r)
-        sym.barrier(6)
         mg = getattr(router_ref, "main_grad", None)
         g_router = None
         if mg is not None:
@@ -179,16 +230,19 @@ class _EpMoeFn(torch.autograd.Function):
                  beta=1.0)
         else:
             g_router = gemm(dl, x, a_mn=True, b_mn=True)
-        return dx, g_router, None, g_gu, g_down, None, None, None
+        return dx, g_router, None, g_gu, g_down, None, None, None, None
 
 
 def ep_moe_ffn(x: Tensor, router_w: Tensor, router_bias: Tensor | None, w_gu_local: Tensor,
                w_down_local: Tensor, top_k: int, ep: EpContext, shapes=None,
-               return_logits: bool = False):
+               return_logits: bool = False, fp8: bool = False):
     """Routed-expert FFN with the experts sharded over ``ep``'s ranks. x [T, d] are this rank's
     tokens; router_w [E, d] is replicated; w_gu_local [El, 2h, d] and w_down_local [El, d, h]
     are this rank's experts. Returns (out [T, d], probs [T, E], ids [T, k]). Collective: every
     rank of the group must call it (same layer order), forward and backward. ``return_logits``
-    appends the router logits [T, E] fp32 (differentiable)."""
-    res = _EpMoeFn.apply(x, router_w, router_bias, w_gu_local, w_down_local, int(top_k), ep, shapes)
+    appends the router logits [T, E] fp32 (differentiable). ``fp8``: tokens cross NVLink as e4m3
+    rows + 1 x 128 scales and both expert products run on the block-scaled FP8 GEMM
+    (straight-through bf16 backward against the quantised rows)."""
+    res = _EpMoeFn.apply(x, router_w, router_bias, w_gu_local, w_down_local, int(top_k), ep, shapes,
+                         bool(fp8))
     return res if return_logits else res[:3]

@@ -183,24 +183,31 @@ def bench_ep(dev, rank, world, a):
     grp = SymmetricGroup(wait_budget_s=10.0)
     ep = EpContext(grp, d, E, max_rows=int(2.0 * T * k) + El * 128)
 
-    def fwd():
-        with torch.no_grad():
-            ep_moe_ffn(x, rw, None, wgu, wd, k, ep)
-
-    def both():
-        for t_ in (x, rw, wgu, wd):
-            t_.grad = None
-        out, _, _ = ep_moe_ffn(x, rw, None, wgu, wd, k, ep)
-        out.backward(go)
-
-    ms_f, ms_b = timed(fwd, dev, a.iters), timed(both, dev, a.iters)
-    grp.check()
+    res = {"path": "ep_moe_ffn", "world": world, "tokens_per_rank": T, "experts": E, "top_k": k}
     flops = 2.0 * T * k * 3 * d * h                # per rank (balanced routing)
     remote = (world - 1) / world
-    link_f = T * k * d * 2.0 * remote * 2          # dispatch out + combine back, bf16
-    return {"path": "ep_moe_ffn", "world": world, "tokens_per_rank": T, "experts": E, "top_k": k,
-            "fwd": {"tflops": flops / ms_f / 1e9, **roofline(ms_f, flops, link_f)},
-            "fwd_bwd": {"tflops": 3 * flops / ms_b / 1e9, **roofline(ms_b, 3 * flops, 2 * link_f)}}
+    for fp8 in (False, True):
+        def fwd():
+            with torch.no_grad():
+                ep_moe_ffn(x, rw, None, wgu, wd, k, ep, fp8=fp8)
+
+        def both():
+            for t_ in (x, rw, wgu, wd):
+                t_.grad = None
+            out, _, _ = ep_moe_ffn(x, rw, None, wgu, wd, k, ep, fp8=fp8)
+            out.backward(go)
+
+        ms_f, ms_b = timed(fwd, dev, a.iters), timed(both, dev, a.iters)
+        grp.check()
+        # bytes crossing NVLink per rank: dispatch out (bf16, or e4m3 + one fp32 scale per 128)
+        # + combine back (bf16); the backward moves bf16 both ways
+        out_b = T * k * d * ((1.0 + 4.0 / 128) if fp8 else 2.0) * remote
+        back_b = T * k * d * 2.0 * remote
+        tag = "fp8_wire" if fp8 else "bf16_wire"
+        res[tag] = {"fwd": {"tflops": flops / ms_f / 1e9, **roofline(ms_f, flops, out_b + back_b)},
+                    "fwd_bwd": {"tflops": 3 * flops / ms_b / 1e9,
+                                **roofline(ms_b, 3 * flops, out_b + 3 * back_b)}}
+    return res
 
 
 def bench_cp(dev, rank, world, a):

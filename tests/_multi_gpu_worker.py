@@ -66,6 +66,36 @@ def ep_main():
     dist.all_reduce(full_d)
     close(wgu_l.grad, full_gu[rank * El:(rank + 1) * El], 2e-2, "d_gate_up")
     close(wd_l.grad, full_d[rank * El:(rank + 1) * El], 2e-2, "d_down")
+    # FP8 on the wire: e4m3 rows + 1 x 128 scales cross NVLink, both products on the FP8 GEMM;
+    # equals the single-rank FP8 layer (same quantisation rule on both sides)
+    h8 = 256
+    wgu8, wd8 = r(E, 2 * h8, d, scale=0.08), r(E, d, h8, scale=0.08)
+    wgu8_l = wgu8[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    wd8_l = wd8[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    x8 = x.detach().clone().requires_grad_(True)
+    rw8 = rw.clone().requires_grad_(True)
+    for it in range(2):
+        for t in (x8, rw8, wgu8_l, wd8_l):
+            t.grad = None
+        out8, _, ids8 = ep_moe_ffn(x8, rw8, bias, wgu8_l, wd8_l, k, ep, fp8=True)
+        (out8.float() * go.float()).sum().backward()
+    torch.cuda.synchronize()
+    grp.check()
+    ops.check_status(dev)
+    lv = [t.detach().clone().requires_grad_(True) for t in (x, rw, wgu8, wd8)]
+    o8_ref, _, i8_ref = moe.moe_ffn(lv[0], lv[1], bias, lv[2], lv[3], k, fp8=True)
+    (o8_ref.float() * go.float()).sum().backward()
+    o16_ref, _, _ = moe.moe_ffn(lv[0].detach(), lv[1].detach(), bias, lv[2].detach(), lv[3].detach(), k)
+    torch.cuda.synchronize()
+    assert torch.equal(ids8, i8_ref)
+    close(out8, o8_ref, 1e-2, "fp8 out vs single-rank fp8")
+    close(out8, o16_ref, 8e-2, "fp8 out vs bf16")
+    close(x8.grad, lv[0].grad, 5e-2, "fp8 dx")
+    g8, gd8 = lv[2].grad.float().clone(), lv[3].grad.float().clone()
+    dist.all_reduce(g8)
+    dist.all_reduce(gd8)
+    close(wgu8_l.grad, g8[rank * El:(rank + 1) * El], 5e-2, "fp8 d_gate_up")
+    close(wd8_l.grad, gd8[rank * El:(rank + 1) * El], 5e-2, "fp8 d_down")
     # overflow is reported, not silent
     small = EpContext(grp, d, E, max_rows=128)
     ep_moe_ffn(x.detach(), rw, bias, wgu[rank * El:(rank + 1) * El], wd[rank * El:(rank + 1) * El], k, small)
