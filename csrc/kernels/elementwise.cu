@@ -352,8 +352,11 @@ __global__ void rope_kernel(bf16* __restrict__ x, const int* __restrict__ pos, l
 // ---------------------------------------------------------------------------
 // SwiGLU on a fused [rows, 2H] projection: out = silu(gu[:, :H]) * gu[:, H:]
 // ---------------------------------------------------------------------------
+// rows_dev (may be null): device-side row count; rows beyond it are left untouched. Buffers
+// sized for a worst case (expert-parallel receive buffers) then cost only what is in use.
 __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long rows,
-                                  int H) {
+                                  int H, const int* __restrict__ rows_dev) {
+  if (rows_dev != nullptr) rows = min(rows, static_cast<long>(*rows_dev));
   const int vph = H >> 3;
   const long total = rows * vph;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
@@ -369,7 +372,9 @@ __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict_
   }
 }
 __global__ void swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ gu,
-                                  bf16* __restrict__ dgu, long rows, int H) {
+                                  bf16* __restrict__ dgu, long rows, int H,
+                                  const int* __restrict__ rows_dev) {
+  if (rows_dev != nullptr) rows = min(rows, static_cast<long>(*rows_dev));
   const int vph = H >> 3;
   const long total = rows * vph;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
@@ -727,7 +732,49 @@ PB_API int pb_rope(void* x, const void* pos, long tokens, int heads, int D, int 
 PB_API int pb_swiglu_fwd(const void* gu, void* out, long rows, int H, cudaStream_t st) {
   if (H % 8 != 0) return PB_BAD_ARG;
   swiglu_fwd_kernel<<<grid_for(rows * (H / 8), 256), 256, 0, st>>>(
-      static_cast<const bf16*>(gu), static_cast<bf16*>(out), rows, H);
+      static_cast<const bf16*>(gu), static_cast<bf16*>(out), rows, H, nullptr);
+  return cudaGetLastError();
+}
+// The same over the first min(rows, *rows_dev) rows (rows_dev: a device int).
+PB_API int pb_swiglu_fwd_dyn(const void* gu, void* out, long rows, int H, const int* rows_dev,
+                             cudaStream_t st) {
+  if (H % 8 != 0) return PB_BAD_ARG;
+  swiglu_fwd_kernel<<<grid_for(rows * (H / 8), 256), 256, 0, st>>>(
+      static_cast<const bf16*>(gu), static_cast<bf16*>(out), rows, H, rows_dev);
+  return cudaGetLastError();
+}
+PB_API int pb_swiglu_bwd_dyn(const void* dout, const void* gu, void* dgu, long rows, int H,
+                             const int* rows_dev, cudaStream_t st) {
+  if (H % 8 != 0) return PB_BAD_ARG;
+  swiglu_bwd_kernel<<<grid_for(rows * (H / 8), 256), 256, 0, st>>>(
+      static_cast<const bf16*>(dout), static_cast<const bf16*>(gu), static_cast<bf16*>(dgu), rows,
+      H, rows_dev);
+  return cudaGetLastError();
+}
+
+// dst[0 : n) = src[0 : n) rows of row_bytes each, n = min(max_rows, *rows_dev): a copy of the
+// part of a worst-case-sized buffer that is in use (16-byte vectors; row_bytes % 16 == 0).
+__global__ void __launch_bounds__(256) copy_rows_dyn_kernel(const uint4* __restrict__ src,
+                                                            uint4* __restrict__ dst, long vec_per_row,
+                                                            long max_rows,
+                                                            const int* __restrict__ rows_dev) {
+  const long rows = min(max_rows, static_cast<long>(*rows_dev));
+  const long total = rows * vec_per_row;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  for (; i + 3 * stride < total; i += 4 * stride) {
+    const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+    dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+  }
+  for (; i < total; i += stride) dst[i] = src[i];
+}
+PB_API int pb_copy_rows_dyn(const void* src, void* dst, long row_bytes, long max_rows,
+                            const int* rows_dev, cudaStream_t st) {
+  if (row_bytes <= 0 || row_bytes % 16 != 0 || max_rows <= 0 || rows_dev == nullptr ||
+      ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) != 0)
+    return PB_BAD_ARG;
+  copy_rows_dyn_kernel<<<grid_for(max_rows * (row_bytes / 16), 256 * 4), 256, 0, st>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), row_bytes / 16, max_rows, rows_dev);
   return cudaGetLastError();
 }
 PB_API int pb_swiglu_bwd(const void* dout, const void* gu, void* dgu, long rows, int H,
@@ -735,7 +782,7 @@ PB_API int pb_swiglu_bwd(const void* dout, const void* gu, void* dgu, long rows,
   if (H % 8 != 0) return PB_BAD_ARG;
   swiglu_bwd_kernel<<<grid_for(rows * (H / 8), 256), 256, 0, st>>>(
       static_cast<const bf16*>(dout), static_cast<const bf16*>(gu), static_cast<bf16*>(dgu), rows,
-      H);
+      H, nullptr);
   return cudaGetLastError();
 }
 

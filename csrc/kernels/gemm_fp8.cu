@@ -243,12 +243,16 @@ __device__ __forceinline__ uint32_t to_e4m3x4(float a, float b, float c, float d
 }
 
 // One warp per (row, 128-element block); K a multiple of 128.
+// rows_dev (may be null): device-side count of the rows in use; the scale table keeps its row
+// stride M whatever that count.
 __global__ void quant_rows_kernel(const bf16* __restrict__ x, long ld, int M, int K,
-                                  uint8_t* __restrict__ q, float* __restrict__ scales) {
+                                  uint8_t* __restrict__ q, float* __restrict__ scales,
+                                  const int* __restrict__ rows_dev) {
   const long w = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int nkb = K / 128;
-  if (w >= static_cast<long>(M) * nkb) return;
+  const int m_eff = rows_dev != nullptr ? min(M, *rows_dev) : M;
+  if (w >= static_cast<long>(m_eff) * nkb) return;
   const int row = static_cast<int>(w / nkb), kb = static_cast<int>(w % nkb);
   const bf16* src = x + static_cast<size_t>(row) * ld + kb * 128 + lane * 4;
   const uint2 raw = *reinterpret_cast<const uint2*>(src);
@@ -265,11 +269,13 @@ __global__ void quant_rows_kernel(const bf16* __restrict__ x, long ld, int M, in
 
 // y[row, :] = bf16(e4m3(q[row, :]) * scale of its 1 x 128 block); one warp per (row, block)
 __global__ void dequant_rows_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales,
-                                    long ld_s, int M, int K, bf16* __restrict__ y) {
+                                    long ld_s, int M, int K, bf16* __restrict__ y,
+                                    const int* __restrict__ rows_dev) {
   const long w = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int nkb = K / 128;
-  if (w >= static_cast<long>(M) * nkb) return;
+  const int m_eff = rows_dev != nullptr ? min(M, *rows_dev) : M;
+  if (w >= static_cast<long>(m_eff) * nkb) return;
   const int row = static_cast<int>(w / nkb), kb = static_cast<int>(w % nkb);
   const float s = scales[static_cast<size_t>(kb) * ld_s + row];
   const uint32_t raw = *reinterpret_cast<const uint32_t*>(q + static_cast<size_t>(row) * K + kb * 128 + lane * 4);
@@ -333,19 +339,29 @@ PB_API int pb_fp8_quant_rows(const void* x, long ld, int M, int K, void* q, floa
   const long warps = static_cast<long>(M) * (K / 128);
   const long blocks = (warps * 32 + 255) / 256;
   f8::quant_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
-      static_cast<const bf16*>(x), ld, M, K, static_cast<uint8_t*>(q), scales);
+      static_cast<const bf16*>(x), ld, M, K, static_cast<uint8_t*>(q), scales, nullptr);
+  return static_cast<int>(cudaGetLastError());
+}
+// The same over the first min(M, *rows_dev) rows (rows_dev: a device int).
+PB_API int pb_fp8_quant_rows_dyn(const void* x, long ld, int M, int K, void* q, float* scales,
+                                 const int* rows_dev, cudaStream_t st) {
+  if (M <= 0 || K <= 0 || K % 128 != 0 || ld % 4 != 0) return PB_BAD_ARG;
+  const long warps = static_cast<long>(M) * (K / 128);
+  const long blocks = (warps * 32 + 255) / 256;
+  f8::quant_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+      static_cast<const bf16*>(x), ld, M, K, static_cast<uint8_t*>(q), scales, rows_dev);
   return static_cast<int>(cudaGetLastError());
 }
 
 // q [M, K] e4m3 with scales [K / 128, ld_s] (ld_s >= M: the row stride of the scale table)
 // -> y [M, K] bf16. The straight-through backward of an FP8 product uses these values.
 PB_API int pb_fp8_dequant_rows(const void* q, const float* scales, long ld_s, int M, int K, void* y,
-                               cudaStream_t st) {
+                               const int* rows_dev, cudaStream_t st) {
   if (M <= 0 || K <= 0 || K % 128 != 0 || ld_s < M) return PB_BAD_ARG;
   const long warps = static_cast<long>(M) * (K / 128);
   const long blocks = (warps * 32 + 255) / 256;
   f8::dequant_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
-      static_cast<const uint8_t*>(q), scales, ld_s, M, K, static_cast<bf16*>(y));
+      static_cast<const uint8_t*>(q), scales, ld_s, M, K, static_cast<bf16*>(y), rows_dev);
   return static_cast<int>(cudaGetLastError());
 }
 

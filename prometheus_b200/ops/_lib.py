@@ -72,7 +72,11 @@ _SIGS = {
     "pb_moe_combine_bwd": [P, P, P, I, I, I, P, P],
     "pb_fp8_quant_rows": [P, L, I, I, P, P, P],
     "pb_fp8_quant_blocks": [P, L, I, I, P, P, P],
-    "pb_fp8_dequant_rows": [P, P, L, I, I, P, P],
+    "pb_fp8_dequant_rows": [P, P, L, I, I, P, P, P],
+    "pb_fp8_quant_rows_dyn": [P, L, I, I, P, P, P, P],
+    "pb_swiglu_fwd_dyn": [P, P, L, I, P, P],
+    "pb_swiglu_bwd_dyn": [P, P, P, L, I, P, P],
+    "pb_copy_rows_dyn": [P, P, L, L, P, P],
     "pb_gemm_fp8_blockscaled": [P, P, P, P, P, I, I, I, I, L, P, P, I, P],
     "pb_gemm_set_debug": [I],
     "pb_gemm_bf16": [P, P, P, P, I, I, I, I, L, L, L, L, L, L, L, L, I, I, I, I, F, F, P, I, P],

@@ -17,13 +17,18 @@ Tensor = torch.Tensor
 BF16 = torch.bfloat16
 
 
-def quantize_rows(x: Tensor):
-    """x [M, K] bf16 (K % 128 == 0) -> (q [M, K] uint8 holding e4m3, scales [K / 128, M] fp32)."""
+def quantize_rows(x: Tensor, rows_used: Tensor | None = None):
+    """x [M, K] bf16 (K % 128 == 0) -> (q [M, K] uint8 holding e4m3, scales [K / 128, M] fp32).
+    ``rows_used`` (a device int32): only the first that many rows are touched."""
     M, K = x.shape
     assert x.dtype == BF16 and K % 128 == 0 and x.stride(1) == 1
     q = torch.empty((M, K), dtype=torch.uint8, device=x.device)
     s = torch.empty((K // 128, M), dtype=torch.float32, device=x.device)
-    call("pb_fp8_quant_rows", ptr(x), x.stride(0), M, K, ptr(q), ptr(s), stream_ptr())
+    if rows_used is None:
+        call("pb_fp8_quant_rows", ptr(x), x.stride(0), M, K, ptr(q), ptr(s), stream_ptr())
+    else:
+        call("pb_fp8_quant_rows_dyn", ptr(x), x.stride(0), M, K, ptr(q), ptr(s), ptr(rows_used),
+             stream_ptr())
     return q, s
 
 
@@ -53,13 +58,14 @@ def dequantize_blocks(q: Tensor, s: Tensor) -> Tensor:
     return q.view(torch.float8_e4m3fn).float() * full
 
 
-def dequantize_rows_bf16(q: Tensor, s: Tensor) -> Tensor:
+def dequantize_rows_bf16(q: Tensor, s: Tensor, rows_used: Tensor | None = None) -> Tensor:
     """(q [M, K] e4m3 bytes, s [K / 128, >= M] fp32) -> bf16 [M, K] on the GPU: the values an FP8
-    product really multiplied, which its straight-through backward differentiates against."""
+    product really multiplied, which its straight-through backward differentiates against.
+    ``rows_used`` (a device int32): only the first that many rows are written."""
     M, K = q.shape
     assert q.dtype == torch.uint8 and q.is_contiguous() and s.stride(1) == 1 and s.shape[1] >= M
     y = torch.empty((M, K), dtype=BF16, device=q.device)
-    call("pb_fp8_dequant_rows", ptr(q), ptr(s), s.stride(0), M, K, ptr(y), stream_ptr())
+    call("pb_fp8_dequant_rows", ptr(q), ptr(s), s.stride(0), M, K, ptr(y), ptr(rows_used), stream_ptr())
     return y
 
 

@@ -120,6 +120,15 @@ class EpContext:
              self.El, stream_ptr())
 
 
+def _copy_used(src: Tensor, used: Tensor) -> Tensor:
+    """A copy of the rows of a worst-case-sized 2-D buffer that are in use (``used``: device int32
+    count); the rest of the result is uninitialised and never read."""
+    dst = torch.empty_like(src)
+    call("pb_copy_rows_dyn", ptr(src), ptr(dst), src.shape[1] * src.element_size(), src.shape[0],
+         ptr(used), stream_ptr())
+    return dst
+
+
 class _EpMoeFn(torch.autograd.Function):
     """Barrier slots: 4 = every rank's per-expert counts are written (forward only), 5 = every
     pushed row has landed, 6 = every owner's results are in its pull buffer. No barrier
@@ -145,6 +154,7 @@ class _EpMoeFn(torch.autograd.Function):
         ep.counts_local.copy_(local.totals)
         sym.barrier(4)
         pl, send_base = ep.layout()
+        used = pl.expert_off[ep.El:]            # device int: rows of the receive buffer in use
         if use_fp8:
             dest_rank, dest_row = ep.dispatch_fp8(x, ids, local, send_base)
             sym.barrier(5)                      # every row has landed
@@ -153,23 +163,23 @@ class _EpMoeFn(torch.autograd.Function):
             gu = F8.gemm_fp8(ep.xq_local, ep.xs_local, wq, sw, mblk_group=pl.mblk_group)
             # what the backward differentiates against: the quantised rows (half the bytes of a
             # bf16 copy); the receive buffer itself is overwritten by the next layer's senders
-            saved_x = (ep.xq_local.clone(), ep.xs_local.clone())
+            saved_x = (_copy_used(ep.xq_local, used), ep.xs_local.clone())
         else:
             dest_rank, dest_row = ep.dispatch(x, ids, local, send_base, None)
             sym.barrier(5)
             ep.zero_pad(pl)
-            xp = ep.x_local.clone()
+            xp = _copy_used(ep.x_local, used)
             gu = M.grouped_gemm(xp, w_gu, pl)
             saved_x = (xp, xp.new_empty(0))
         hs = torch.empty((pl.rows, h), dtype=BF16, device=x.device)
-        call("pb_swiglu_fwd", ptr(gu), ptr(hs), pl.rows, h, stream_ptr())
+        call("pb_swiglu_fwd_dyn", ptr(gu), ptr(hs), pl.rows, h, ptr(used), stream_ptr())
         if use_fp8:
-            hq, sh = F8.quantize_rows(hs)
+            hq, sh = F8.quantize_rows(hs, used)
             wq, sw = F8.quantize_blocks(w_down.contiguous())
             F8.gemm_fp8(hq, sh, wq, sw, mblk_group=pl.mblk_group, out=ep.y_local)
         else:
             M.grouped_gemm(hs, w_down, pl, out=ep.y_local)
-        y = ep.y_local.clone()                  # the gate gradient needs <y_row, dy_row> later
+        y = _copy_used(ep.y_local, used)        # the gate gradient needs <y_row, dy_row> later
         sym.barrier(6)                          # results are ready to be pulled
         out = ep.combine(dest_rank, dest_row, gates, T, top_k)
         ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids, gates, saved_x[0], saved_x[1], gu,
@@ -199,13 +209,13 @@ class _EpMoeFn(torch.autograd.Function):
         sym.barrier(5)
         ep.zero_pad(pl)
         dyp = ep.x_local            # read in place: nobody overwrites it before slot 6 below
-        call("pb_ep_rowdot", ptr(y), ptr(dyp), ptr(pl.expert_off[ep.El:]), pl.rows, d,
-             ptr(ep.dot_local), stream_ptr())
+        used = pl.expert_off[ep.El:]
+        call("pb_ep_rowdot", ptr(y), ptr(dyp), ptr(used), pl.rows, d, ptr(ep.dot_local), stream_ptr())
         dh = M.grouped_gemm(dyp, w_down, pl, b_mn=True)
         g_down = M._acc_grad(down_ref, w_down.shape, lambda o, acc: M.grouped_wgrad(dyp, hs, pl, o, acc))
         dgu = torch.empty_like(gu)
-        call("pb_swiglu_bwd", ptr(dh), ptr(gu), ptr(dgu), pl.rows, h, stream_ptr())
-        xp = F8.dequantize_rows_bf16(xs0, xs1) if ctx.use_fp8 else xs0
+        call("pb_swiglu_bwd_dyn", ptr(dh), ptr(gu), ptr(dgu), pl.rows, h, ptr(used), stream_ptr())
+        xp = F8.dequantize_rows_bf16(xs0, xs1, used) if ctx.use_fp8 else xs0
         g_gu = M._acc_grad(gu_ref, w_gu.shape, lambda o, acc: M.grouped_wgrad(dgu, xp, pl, o, acc))
         del xp
         M.grouped_gemm(dgu, w_gu, pl, b_mn=True, out=ep.y_local)

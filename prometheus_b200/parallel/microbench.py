@@ -199,6 +199,20 @@ def bench_ep(dev, rank, world, a):
 
         ms_f, ms_b = timed(fwd, dev, a.iters), timed(both, dev, a.iters)
         grp.check()
+        if a.profile and rank == 0:
+            # kernel shares of one forward + backward (diagnosis only: timings taken under the
+            # profiler are not reported as results)
+            from torch.profiler import ProfilerActivity, profile
+
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                both()
+                torch.cuda.synchronize()
+            print(("fp8_wire" if fp8 else "bf16_wire") + " kernel shares\n"
+                  + prof.key_averages().table(sort_by="cuda_time_total", row_limit=24, max_name_column_width=60),
+                  flush=True)
+        if a.profile and rank != 0:
+            both()          # the other ranks run the same collective layer while rank 0 is profiled
+            torch.cuda.synchronize()
         # bytes crossing NVLink per rank: dispatch out (bf16, or e4m3 + one fp32 scale per 128)
         # + combine back (bf16); the backward moves bf16 both ways
         out_b = T * k * d * ((1.0 + 4.0 / 128) if fp8 else 2.0) * remote
@@ -236,6 +250,7 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--states", type=int, default=16)
+    ap.add_argument("--profile", action="store_true", help="print kernel shares of the EP layer (rank 0)")
     a = ap.parse_args(argv)
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", 0))
