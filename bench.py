@@ -196,7 +196,9 @@ def measure(args, config: str, world: int, rank: int, local_rank: int, dev, step
         # top-6 routing keeps six expert-side copies of every token's activations per MoE
         # layer: 16384 tokens per micro-batch keep the 27 MoE layers' saved activations near 55 GB
         micro = 4 if micro == 8 else micro
-        trainer_kw = dict(fp8=True, expert_parallel=world > 1)
+        # receive buffers sized for 1.5 x the balanced load (a layer that needs more latches an
+        # overflow code, which the step reports)
+        trainer_kw = dict(fp8=True, expert_parallel=world > 1, ep_capacity_factor=1.5)
         fsdp = fsdp and args.parallelism == "fsdp"
         model_name = "moe-16B (28L d2048, 64 routed top-6 + 2 shared experts h1408, FP8 e4m3 block-scaled linears)"
     if args.layers:

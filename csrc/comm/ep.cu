@@ -42,6 +42,7 @@ __global__ void ep_layout_kernel(EpPeers counts, int rank, int world, int E, int
                                  int* __restrict__ k_len,        // [El]
                                  int* __restrict__ mblk_group,   // [max_rows / 128]
                                  int* __restrict__ send_base,    // [E]
+                                 int* __restrict__ blk_expect,   // [max_rows / 128] or null
                                  int* status) {
   __shared__ int tot[EP_MAX_E];      // pairs per expert over all sources
   __shared__ int before[EP_MAX_E];   // pairs of sources < rank
@@ -93,6 +94,16 @@ __global__ void ep_layout_kernel(EpPeers counts, int rank, int world, int E, int
       g = lo;
     }
     mblk_group[m] = g;
+    if (blk_expect != nullptr) {
+      // rows of this block that senders will store (the rest is padding the owner zeroes)
+      int want = 0;
+      if (g >= 0) {
+        const int start = seg[mine + g];
+        const int valid_end = min(start + tot[mine + g], used);
+        want = max(0, min(row + 128, valid_end) - row);
+      }
+      blk_expect[m] = want;
+    }
   }
 }
 
@@ -148,7 +159,7 @@ __global__ void ep_dispatch_fp8_kernel(const bf16* __restrict__ src, long ld_src
                                        const int* __restrict__ ids, const int* __restrict__ row_of_local,
                                        const int* __restrict__ local_off, const int* __restrict__ send_base,
                                        int n_pairs, int k, int d, int El, int max_rows, EpPeers xq,
-                                       EpPeers xs, int* __restrict__ dest_rank,
+                                       EpPeers xs, EpPeers arrived, int* __restrict__ dest_rank,
                                        int* __restrict__ dest_row) {
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= n_pairs) return;
@@ -182,6 +193,13 @@ __global__ void ep_dispatch_fp8_kernel(const bf16* __restrict__ src, long ld_src
     pk.w = ep_e4m3x4(__fdiv_rn(f[12], scale), __fdiv_rn(f[13], scale), __fdiv_rn(f[14], scale), __fdiv_rn(f[15], scale));
     *reinterpret_cast<uint4*>(oq + c) = pk;
     if ((lane & 7) == 0) os[static_cast<size_t>(c >> 7) * max_rows + row] = scale;
+  }
+  if (arrived.p[q] != nullptr) {
+    // fused mode: tell the owner's GEMM that one more row of this 128-row block has landed.
+    // Every lane's stores are ordered before the count (fence, warp barrier, then the add).
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0) atomicAdd_system(static_cast<unsigned int*>(arrived.p[q]) + (row >> 7), 1u);
   }
 }
 
@@ -273,14 +291,16 @@ static EpPeers make_peers(void* const* ptrs, int world) {
   return p;
 }
 
+// blk_expect (may be null): rows each 128-row block of this rank's receive buffer will get.
 PB_API int pb_ep_layout(void* const* count_ptrs, int rank, int world, int E, int max_rows,
                         int* expert_off, int* totals, int* k_len, int* mblk_group, int* send_base,
-                        int* status, cudaStream_t st) {
+                        int* blk_expect, int* status, cudaStream_t st) {
   if (world <= 0 || world > EP_MAX_RANKS || E <= 0 || E > EP_MAX_E || E % world != 0 ||
       max_rows % 128 != 0)
     return PB_BAD_ARG;
   ep_layout_kernel<<<1, 512, 0, st>>>(make_peers(count_ptrs, world), rank, world, E, max_rows,
-                                      expert_off, totals, k_len, mblk_group, send_base, status);
+                                      expert_off, totals, k_len, mblk_group, send_base, blk_expect,
+                                      status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -297,17 +317,23 @@ PB_API int pb_ep_dispatch(const void* src, long ld_src, const int* ids, const in
 }
 
 // The FP8-on-the-wire dispatch: xq_ptrs / xs_ptrs are every rank's receive buffers (e4m3 bytes
-// [max_rows, d]; fp32 scales [d / 128, max_rows]). d a multiple of 128.
+// [max_rows, d]; fp32 scales [d / 128, max_rows]). d a multiple of 128. arrived_ptrs (may be
+// null): every rank's per-128-row-block arrival counters for the fused grouped GEMM
+// (pb_gemm_fp8_grouped_arrive); with it no barrier is needed between dispatch and GEMM.
 PB_API int pb_ep_dispatch_fp8(const void* src, long ld_src, const int* ids, const int* row_of_local,
                               const int* local_off, const int* send_base, int n_pairs, int k, int d,
                               int El, int max_rows, void* const* xq_ptrs, void* const* xs_ptrs,
-                              int world, int* dest_rank, int* dest_row, cudaStream_t st) {
+                              void* const* arrived_ptrs, int world, int* dest_rank, int* dest_row,
+                              cudaStream_t st) {
   if (n_pairs <= 0 || d % 128 != 0 || El <= 0 || (ld_src % 8) != 0) return PB_BAD_ARG;
   const int grid = static_cast<int>((static_cast<long>(n_pairs) * 32 + 255) / 256);
+  EpPeers arr;
+  for (int i = 0; i < EP_MAX_RANKS; ++i)
+    arr.p[i] = (arrived_ptrs != nullptr && i < world) ? arrived_ptrs[i] : nullptr;
   ep_dispatch_fp8_kernel<<<grid, 256, 0, st>>>(static_cast<const bf16*>(src), ld_src, ids, row_of_local,
                                                local_off, send_base, n_pairs, k, d, El, max_rows,
                                                make_peers(xq_ptrs, world), make_peers(xs_ptrs, world),
-                                               dest_rank, dest_row);
+                                               arr, dest_rank, dest_row);
   return static_cast<int>(cudaGetLastError());
 }
 

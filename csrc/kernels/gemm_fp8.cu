@@ -52,6 +52,14 @@ struct Params {
   const float* sb;     // [groups, ceil(N / 128), K / 128]
   const int* mblk_group;
   int* status;
+  // Fused expert-parallel dispatch (null otherwise): the rows of A and their scales are being
+  // stored into this GPU's memory by the other ranks' dispatch kernels while this kernel runs.
+  // blk_arrived[m] counts the rows of 128-row block m that have landed (the senders add to it
+  // with release semantics after each row), blk_expect[m] is how many will; the TMA producer
+  // takes a block only once it is complete. TMA reads this GPU's own memory only.
+  const uint32_t* blk_arrived;
+  const int* blk_expect;
+  uint64_t wait_budget_ns;
 };
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -118,6 +126,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         coords(t, m_blk, n_blk);
         const int g = group_of(m_blk);
         if (g < 0) continue;
+        if (p.blk_arrived != nullptr) {
+          const int want = p.blk_expect[m_blk];
+          if (want > 0) {
+            if (!wait_flag_ge(p.blk_arrived + m_blk, static_cast<uint32_t>(want), p.wait_budget_ns,
+                              p.status)) { ok = false; break; }
+            // the rows were written by peers' ordinary stores; the bulk loads below read
+            // through the asynchronous proxy
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+          }
+        }
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, p.status)) { ok = false; break; }
           mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
@@ -177,9 +195,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int a = it & 1;
-        const float scale = p.sa[static_cast<size_t>(kb) * p.M + srow] * sb[kb];
         if (!mbar_wait(&tfull[a], (it >> 1) & 1, p.status)) { ok = false; break; }
         tc_fence_after();
+        // read after the wait and past L1: in the fused-dispatch mode a peer wrote this scale
+        // during the kernel, and the accumulator being full implies it has landed
+        const float scale = __ldcg(p.sa + static_cast<size_t>(kb) * p.M + srow) * sb[kb];
         const uint32_t t_addr =
             tmem_base + a * BN + half * HALF + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
@@ -379,14 +399,47 @@ PB_API int pb_fp8_quant_blocks(const void* w, long ld, int rows, int K, void* q,
 // C [M, N] bf16 = block-scaled Aq [M, K] x Bq [groups, N, K]^T. K % 128 == 0, N % 8 == 0.
 // sa [K / 128, M]; sb [groups, ceil(N / 128), K / 128]; mblk_group null (groups == 1) or one
 // int per 128-row block of A / C.
+static int gemm_fp8_launch(const void* Aq, const float* sa, const void* Bq, const float* sb,
+                           void* C, int M, int N, int K, int groups, long ldc,
+                           const int* mblk_group, int* status, int max_ctas,
+                           const uint32_t* blk_arrived, const int* blk_expect, long budget_ns,
+                           cudaStream_t st);
+
 PB_API int pb_gemm_fp8_blockscaled(const void* Aq, const float* sa, const void* Bq, const float* sb,
                                    void* C, int M, int N, int K, int groups, long ldc,
                                    const int* mblk_group, int* status, int max_ctas,
                                    cudaStream_t st) {
+  return gemm_fp8_launch(Aq, sa, Bq, sb, C, M, N, K, groups, ldc, mblk_group, status, max_ctas,
+                         nullptr, nullptr, 0, st);
+}
+
+// The grouped product fused with the arrival of its rows: Aq / sa are a receive buffer that the
+// other ranks' dispatch kernels are still filling. blk_arrived (uint32 per 128-row block, in
+// memory the senders can reach, zero before the senders start) is incremented once per landed
+// row; blk_expect (int per block) is the number of rows each block will receive. A row block is
+// loaded only when complete; a block that does not complete within budget_ns latches
+// PB_TIMEOUT_FLAG in *status and the kernel drains.
+PB_API int pb_gemm_fp8_grouped_arrive(const void* Aq, const float* sa, const void* Bq, const float* sb,
+                                      void* C, int M, int N, int K, int groups, long ldc,
+                                      const int* mblk_group, const void* blk_arrived,
+                                      const int* blk_expect, long budget_ns, int* status,
+                                      cudaStream_t st) {
+  if (blk_arrived == nullptr || blk_expect == nullptr || budget_ns <= 0 || mblk_group == nullptr)
+    return PB_BAD_ARG;
+  return gemm_fp8_launch(Aq, sa, Bq, sb, C, M, N, K, groups, ldc, mblk_group, status, 0,
+                         static_cast<const uint32_t*>(blk_arrived), blk_expect, budget_ns, st);
+}
+
+static int gemm_fp8_launch(const void* Aq, const float* sa, const void* Bq, const float* sb,
+                           void* C, int M, int N, int K, int groups, long ldc,
+                           const int* mblk_group, int* status, int max_ctas,
+                           const uint32_t* blk_arrived, const int* blk_expect, long budget_ns,
+                           cudaStream_t st) {
   using namespace f8;
   if (M <= 0 || N <= 0 || K <= 0 || K % BK != 0 || groups <= 0 || (ldc * 2) % 16 != 0)
     return PB_BAD_ARG;
   if (groups > 1 && (mblk_group == nullptr || N % HALF != 0)) return PB_BAD_ARG;
+  if (groups == 1 && blk_arrived != nullptr && N % HALF != 0) return PB_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(Aq) & 15) || (reinterpret_cast<uintptr_t>(Bq) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
     return PB_BAD_ARG;
@@ -407,6 +460,8 @@ PB_API int pb_gemm_fp8_blockscaled(const void* Aq, const float* sa, const void* 
   Params p;
   p.M = M; p.N = N; p.K = K;
   p.sa = sa; p.sb = sb; p.mblk_group = mblk_group; p.status = status;
+  p.blk_arrived = blk_arrived; p.blk_expect = blk_expect;
+  p.wait_budget_ns = static_cast<uint64_t>(budget_ns);
   const long tiles = static_cast<long>((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;

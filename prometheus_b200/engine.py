@@ -623,7 +623,7 @@ class Trainer:
                 delattr(self, name)
         bufs = [self.sym_grad, self.sym_lp]
         for ctx in (self.ep_ctx, self.cp_ctx):
-            for attr in ("counts", "xbuf", "ybuf", "dotbuf", "xqbuf", "xsbuf", "buf"):
+            for attr in ("counts", "xbuf", "ybuf", "dotbuf", "xqbuf", "xsbuf", "arrbuf", "buf"):
                 b = getattr(ctx, attr, None) if ctx is not None else None
                 if b is not None and hasattr(b, "close"):
                     bufs.append(b)

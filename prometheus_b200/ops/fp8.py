@@ -70,10 +70,14 @@ def dequantize_rows_bf16(q: Tensor, s: Tensor, rows_used: Tensor | None = None) 
 
 
 def gemm_fp8(aq: Tensor, sa: Tensor, bq: Tensor, sb: Tensor, *, mblk_group: Tensor | None = None,
-             max_ctas: int = 0, out: Tensor | None = None) -> Tensor:
+             max_ctas: int = 0, out: Tensor | None = None, arrived: Tensor | None = None,
+             expect: Tensor | None = None, budget_ns: int = 0) -> Tensor:
     """C [M, N] bf16 = (aq, sa) @ (bq, sb)^T. bq [N, K], or [E, N, K] with ``mblk_group`` (one
     int32 per 128-row block of aq naming its expert, negative = skip that block). ``out``: a
-    contiguous bf16 [M, N] destination (e.g. a symmetric-memory buffer peers read)."""
+    contiguous bf16 [M, N] destination (e.g. a symmetric-memory buffer peers read).
+    ``arrived`` / ``expect`` (int32 per 128-row block): fused expert-parallel dispatch, aq / sa are
+    a receive buffer peers are still filling and a block is consumed once ``arrived >= expect``
+    (waits bounded by ``budget_ns``)."""
     from .functional import status_word
 
     M, K = aq.shape
@@ -85,6 +89,11 @@ def gemm_fp8(aq: Tensor, sa: Tensor, bq: Tensor, sb: Tensor, *, mblk_group: Tens
         out = torch.empty((M, N), dtype=BF16, device=aq.device)
     else:
         assert out.shape == (M, N) and out.dtype == BF16 and out.is_contiguous()
+    if arrived is not None:
+        call("pb_gemm_fp8_grouped_arrive", ptr(aq), ptr(sa), ptr(bq), ptr(sb), ptr(out), M, N, K, groups,
+             N, ptr(mblk_group), ptr(arrived), ptr(expect), int(budget_ns), ptr(status_word(aq.device)),
+             stream_ptr())
+        return out
     call("pb_gemm_fp8_blockscaled", ptr(aq), ptr(sa), ptr(bq), ptr(sb), ptr(out), M, N, K, groups, N,
          ptr(mblk_group), ptr(status_word(aq.device)), int(max_ctas), stream_ptr())
     return out

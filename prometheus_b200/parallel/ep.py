@@ -26,9 +26,9 @@ from ..ops._lib import call, ptr, stream_ptr
 from .symm import PP, SymmetricBuffer, SymmetricGroup
 
 P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
-_lib.register("pb_ep_layout", [PP, I, I, I, I, P, P, P, P, P, P, P])
+_lib.register("pb_ep_layout", [PP, I, I, I, I, P, P, P, P, P, P, P, P])
 _lib.register("pb_ep_dispatch", [P, L, P, P, P, P, P, I, I, I, I, I, PP, I, P, P, P])
-_lib.register("pb_ep_dispatch_fp8", [P, L, P, P, P, P, I, I, I, I, I, PP, PP, I, P, P, P])
+_lib.register("pb_ep_dispatch_fp8", [P, L, P, P, P, P, I, I, I, I, I, PP, PP, PP, I, P, P, P])
 _lib.register("pb_ep_zero_pad_fp8", [P, P, I, I, P, P, I, P])
 _lib.register("pb_ep_combine", [PP, I, P, P, P, P, I, I, I, P, P])
 _lib.register("pb_ep_rowdot", [P, P, P, I, I, P, P])
@@ -62,6 +62,12 @@ class EpContext:
             self.xq_local = self.xqbuf.view(torch.uint8, self.max_rows * d_model).view(self.max_rows, d_model)
             self.xs_local = self.xsbuf.view(torch.float32, (d_model // 128) * self.max_rows).view(
                 d_model // 128, self.max_rows)
+            # fused dispatch: rows landed per 128-row block of this rank's FP8 receive buffer
+            # (peers add to it), and how many each block expects (from the layout)
+            self.arrbuf = SymmetricBuffer(4 * (self.max_rows // 128), g)
+            self.arrived_local = self.arrbuf.view(torch.int32, self.max_rows // 128)
+            self.blk_expect = torch.zeros(self.max_rows // 128, dtype=torch.int32,
+                                          device=self.arrived_local.device)
         self.xbuf = SymmetricBuffer(2 * self.max_rows * d_model, g)
         self.ybuf = SymmetricBuffer(2 * self.max_rows * d_model, g)
         self.dotbuf = SymmetricBuffer(4 * self.max_rows, g)
@@ -80,7 +86,7 @@ class EpContext:
         send_base = torch.empty(self.E, **i32)
         call("pb_ep_layout", self.counts.ptrs, self.rank, self.world, self.E, self.max_rows,
              ptr(pl.expert_off), ptr(pl.totals), ptr(pl.k_len), ptr(pl.mblk_group), ptr(send_base),
-             ptr(self.sym.status), stream_ptr())
+             ptr(self.blk_expect) if self.fp8_ok else None, ptr(self.sym.status), stream_ptr())
         return pl, send_base
 
     def dispatch(self, x: Tensor, ids: Tensor, local: M.Placement, send_base: Tensor,
@@ -94,15 +100,19 @@ class EpContext:
              self.world, ptr(dest_rank), ptr(dest_row), stream_ptr())
         return dest_rank, dest_row
 
-    def dispatch_fp8(self, x: Tensor, ids: Tensor, local: M.Placement, send_base: Tensor):
-        """Quantise and push: e4m3 rows + 1 x 128 scales into the owners' FP8 receive buffers."""
+    def dispatch_fp8(self, x: Tensor, ids: Tensor, local: M.Placement, send_base: Tensor,
+                     count_arrivals: bool = True):
+        """Quantise and push: e4m3 rows + 1 x 128 scales into the owners' FP8 receive buffers,
+        and (``count_arrivals``) one count per landed row into the owner's per-block arrival
+        counters, which its grouped GEMM waits on block by block."""
         T, k = ids.shape
         dev = x.device
         dest_rank = torch.empty(T * k, dtype=torch.int32, device=dev)
         dest_row = torch.empty(T * k, dtype=torch.int32, device=dev)
         call("pb_ep_dispatch_fp8", ptr(x), x.stride(0), ptr(ids), ptr(local.row_of), ptr(local.expert_off),
              ptr(send_base), T * k, k, self.d, self.El, self.max_rows, self.xqbuf.ptrs, self.xsbuf.ptrs,
-             self.world, ptr(dest_rank), ptr(dest_row), stream_ptr())
+             self.arrbuf.ptrs if count_arrivals else None, self.world, ptr(dest_rank), ptr(dest_row),
+             stream_ptr())
         return dest_rank, dest_row
 
     def zero_pad_fp8(self, pl: M.Placement) -> None:
@@ -156,11 +166,15 @@ class _EpMoeFn(torch.autograd.Function):
         pl, send_base = ep.layout()
         used = pl.expert_off[ep.El:]            # device int: rows of the receive buffer in use
         if use_fp8:
-            dest_rank, dest_row = ep.dispatch_fp8(x, ids, local, send_base)
-            sym.barrier(5)                      # every row has landed
-            ep.zero_pad_fp8(pl)
+            # Fused dispatch + first grouped GEMM: no barrier between them. The senders count
+            # every landed row into the owner's per-block counters and the GEMM's TMA producer
+            # takes a 128-row block as soon as that block is complete (bounded wait).
+            ep.zero_pad_fp8(pl)                 # padding rows only: disjoint from what peers store
             wq, sw = F8.quantize_blocks(w_gu.contiguous())
-            gu = F8.gemm_fp8(ep.xq_local, ep.xs_local, wq, sw, mblk_group=pl.mblk_group)
+            dest_rank, dest_row = ep.dispatch_fp8(x, ids, local, send_base)
+            gu = F8.gemm_fp8(ep.xq_local, ep.xs_local, wq, sw, mblk_group=pl.mblk_group,
+                             arrived=ep.arrived_local, expect=ep.blk_expect, budget_ns=sym.budget_ns)
+            ep.arrived_local.zero_()            # before this rank's next slot-4 arrival
             # what the backward differentiates against: the quantised rows (half the bytes of a
             # bf16 copy); the receive buffer itself is overwritten by the next layer's senders
             saved_x = (_copy_used(ep.xq_local, used), ep.xs_local.clone())
