@@ -175,16 +175,27 @@ __global__ void ep_dispatch_fp8_kernel(const bf16* __restrict__ src, long ld_src
   const bf16* s = src + static_cast<size_t>(w / k) * ld_src;
   uint8_t* oq = static_cast<uint8_t*>(xq.p[q]) + static_cast<size_t>(row) * d;
   float* os = static_cast<float*>(xs.p[q]);
-  for (int c = lane * 16; c < d; c += 512) {       // d is a multiple of 128: a block never splits
+  // Every lane runs every iteration (the shuffles below name the whole warp); lanes past the
+  // end of a row narrower than 512 elements only take part in the shuffles. d is a multiple
+  // of 128, so the eight lanes of a block are active or idle together.
+  for (int c0 = 0; c0 < d; c0 += 512) {
+    const int c = c0 + lane * 16;
+    const bool active = c < d;
     float f[16];
-    unpack8(*reinterpret_cast<const bf16x8*>(s + c), f);
-    unpack8(*reinterpret_cast<const bf16x8*>(s + c + 8), f + 8);
+    if (active) {
+      unpack8(*reinterpret_cast<const bf16x8*>(s + c), f);
+      unpack8(*reinterpret_cast<const bf16x8*>(s + c + 8), f + 8);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) f[j] = 0.f;
+    }
     float amax = 0.f;
 #pragma unroll
     for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    if (!active) continue;
     const float scale = amax > 0.f ? amax / 448.f : 1.f;
     uint4 pk;
     pk.x = ep_e4m3x4(__fdiv_rn(f[0], scale), __fdiv_rn(f[1], scale), __fdiv_rn(f[2], scale), __fdiv_rn(f[3], scale));
