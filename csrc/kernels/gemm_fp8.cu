@@ -193,13 +193,27 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       float acc[HALF];
 #pragma unroll
       for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
+      // Scale of the K-block in hand, loaded one block ahead so its latency hides behind the
+      // previous block's promotion. In the fused-dispatch mode a peer may still be writing the
+      // scales when the tile starts: the first one is then read only after the first accumulator
+      // is full, which implies that the whole row block (payload and scales) has landed.
+      const float* sa_row = p.sa + srow;
+      float scale_cur = 0.f;
+      bool have = false;
+      if (p.blk_arrived == nullptr) {
+        scale_cur = __ldcg(sa_row) * sb[0];
+        have = true;
+      }
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int a = it & 1;
         if (!mbar_wait(&tfull[a], (it >> 1) & 1, p.status)) { ok = false; break; }
         tc_fence_after();
-        // read after the wait and past L1: in the fused-dispatch mode a peer wrote this scale
-        // during the kernel, and the accumulator being full implies it has landed
-        const float scale = __ldcg(p.sa + static_cast<size_t>(kb) * p.M + srow) * sb[kb];
+        if (!have) scale_cur = __ldcg(sa_row + static_cast<size_t>(kb) * p.M) * sb[kb];
+        const float scale = scale_cur;
+        if (kb + 1 < nkb) {
+          scale_cur = __ldcg(sa_row + static_cast<size_t>(kb + 1) * p.M) * sb[kb + 1];
+          have = true;
+        }
         const uint32_t t_addr =
             tmem_base + a * BN + half * HALF + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll

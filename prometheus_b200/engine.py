@@ -119,7 +119,8 @@ class Trainer:
                  grad_sync: str = "auto", expert_parallel: bool = False,
                  ep_capacity_factor: float = 2.0, fp8: bool = False, context_parallel: bool = False,
                  z_loss_mode: str = "layers_logits", router_bias_rule: str = "count",
-                 allow_fallback: bool = False, fsdp: bool = False, recurrence: int = 1,
+                 allow_fallback: bool = False, fsdp: bool = False, nvls: bool | str = "auto",
+                 recurrence: int = 1,
                  truncated_recurrence: int = M.TRUNCATED_RECURRENCE, check_status_every: int = 1):
         M.validate_config(model_config)
         T.validate_train_config(train_config)
@@ -140,6 +141,11 @@ class Trainer:
         # fp32 masters and optimizer moments only for the matrices this rank owns
         self.fsdp = bool(fsdp) and self.world > 1
         self.comm_noop = False      # timing only: skip the peer traffic (see exposed-comm measurement)
+        # replicated mode: broadcast the refreshed weights with one multimem.st through an NVLS
+        # multicast object when the machine offers one ("auto": use it if it can be set up on
+        # every rank, else the peer-to-peer stores; False: never)
+        self.nvls_mode = nvls
+        self.nvls_lp = None
         self.ep = bool(expert_parallel) and self.world > 1 and model_config.n_moe > 0
         self.ep_capacity_factor = float(ep_capacity_factor)
         # block-scaled FP8 forward for the FFN / expert products (1 x 128 activations,
@@ -355,6 +361,7 @@ class Trainer:
         dev = self.device
         f32 = dict(dtype=torch.float32, device=dev)
         self.sym = None
+        self.sym_lp = None
         n_m, n_a, n_v = self.n_muon, self.n_adam, self.n_vec
         if self.fsdp and self.grad_sync == "nccl":
             raise ValueError("fsdp=True needs the peer-memory gradient path (grad_sync auto / p2p)")
@@ -371,7 +378,14 @@ class Trainer:
                     self._plan_fsdp()
                     self.sym_lp = SymmetricBuffer(2 * self.n_sym_w, self.pg)
                 else:
-                    self.sym_lp = SymmetricBuffer(2 * (n_m + n_a), self.pg)
+                    if self.nvls_mode in ("auto", True):
+                        from .parallel.nvls import NvlsBuffer
+
+                        self.nvls_lp = NvlsBuffer.create(2 * (n_m + n_a), self.pg)
+                        if self.nvls_lp is None and self.nvls_mode is True:
+                            raise RuntimeError("nvls=True but no multicast object could be set up")
+                    if self.nvls_lp is None:
+                        self.sym_lp = SymmetricBuffer(2 * (n_m + n_a), self.pg)
             except RuntimeError as e:      # peer mapping refused on this machine
                 ok, err = 0, e
             flag = torch.tensor([ok], dtype=torch.int32, device=dev)
@@ -387,8 +401,9 @@ class Trainer:
             self.adam_grad = self.sym_grad.view(torch.float32, n_a, 4 * n_m)
             self.vec_grad = self.sym_grad.view(torch.float32, n_v, 4 * (n_m + n_a))
             if not self.fsdp:
-                self.muon_lp = self.sym_lp.view(BF16, n_m, 0)
-                self.adam_lp = self.sym_lp.view(BF16, n_a, 2 * n_m)
+                lp_buf = self.nvls_lp if self.nvls_lp is not None else self.sym_lp
+                self.muon_lp = lp_buf.view(BF16, n_m, 0)
+                self.adam_lp = lp_buf.view(BF16, n_a, 2 * n_m)
         else:
             self.muon_grad = torch.zeros(n_m, **f32)
             self.adam_grad = torch.zeros(n_a, **f32)
@@ -621,7 +636,10 @@ class Trainer:
         for name in ("muon_grad", "adam_grad", "vec_grad", "muon_lp", "adam_lp", "sym_w_local"):
             if hasattr(self, name):
                 delattr(self, name)
-        bufs = [self.sym_grad, self.sym_lp]
+        if self.nvls_lp is not None:
+            self.nvls_lp.close()
+            self.nvls_lp = None
+        bufs = [self.sym_grad] + ([self.sym_lp] if getattr(self, "sym_lp", None) is not None else [])
         for ctx in (self.ep_ctx, self.cp_ctx):
             for attr in ("counts", "xbuf", "ybuf", "dotbuf", "xqbuf", "xsbuf", "arrbuf", "buf"):
                 b = getattr(ctx, attr, None) if ctx is not None else None
@@ -1308,7 +1326,13 @@ class Trainer:
                  ptr(self.adam_v), ptr(self.adam_lp), self.n_adam, *hp, step, ptr(self.gnorm_sq),
                  clip, gscale, st)
         elif a_hi > a_lo:
-            if peers_on:
+            if peers_on and self.nvls_lp is not None:
+                # one multimem.st per 16 bytes: the switch replicates it into every rank's copy
+                call("pb_mm_adamw", ptr(self.adam_master[a_lo:]), ptr(self.adam_grad[a_lo:]),
+                     ptr(self.adam_m[a_lo:]), ptr(self.adam_v[a_lo:]),
+                     self.nvls_lp.mc_at(2 * (self.n_muon + a_lo)), a_hi - a_lo, *hp, step,
+                     ptr(self.gnorm_sq), clip, gscale, st)
+            elif peers_on:
                 call("pb_adamw_bcast", ptr(self.adam_master), ptr(self.adam_grad), ptr(self.adam_m),
                      ptr(self.adam_v), self.sym_lp.peer_ptrs(2 * self.n_muon), self.world, a_lo,
                      a_hi - a_lo, *hp, step, ptr(self.gnorm_sq), clip, gscale, st)
@@ -1344,6 +1368,9 @@ class Trainer:
             elif self.sym is None or len(key) > 2 or not peers_on:
                 call("pb_muon_apply", ptr(self.muon_master[lb:]), ptr(xo),
                      ptr(self.muon_lp[base:]), n * nb, lr, scale, self.muon_wd, st)
+            elif self.nvls_lp is not None:
+                call("pb_mm_muon_apply", ptr(self.muon_master[lb:]), ptr(xo),
+                     self.nvls_lp.mc_at(2 * base), n * nb, lr, scale, self.muon_wd, st)
             else:
                 call("pb_muon_apply_bcast", ptr(self.muon_master), ptr(xo),
                      self.sym_lp.peer_ptrs(0), self.world, base, n * nb, lr, scale,

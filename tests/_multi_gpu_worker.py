@@ -481,10 +481,95 @@ def fsdp_engine_main():
     dist.destroy_process_group()
 
 
+def nvls_main():
+    """NVLS multicast: one multimem.st lands in every rank's copy (bitwise equal to the
+    peer-to-peer broadcast), multimem.ld_reduce all-reduce equals the sum, and the replicated
+    trainer gives the same losses with either broadcast. Everything is released on every rank
+    before anything is asserted, so no rank leaves while its memory is bound."""
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    from datetime import timedelta
+
+    dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=90))
+    from prometheus_b200 import engine, model, train
+    from prometheus_b200.ops._lib import call, ptr, stream_ptr
+    from prometheus_b200.parallel import nvls
+    from prometheus_b200.parallel.fsdp import split_bounds
+    from prometheus_b200.parallel.symm import SymmetricBuffer, SymmetricGroup
+    from test_gpu_engine import small_hybrid
+
+    n = 1 << 20
+    buf = nvls.NvlsBuffer.create(4 * n)
+    if buf is None:
+        dist.barrier()
+        if rank == 0:
+            print("NVLS_OK (multicast objects unavailable on this machine: peer-to-peer paths only)")
+        dist.destroy_process_group()
+        return
+    facts = {}
+    grp = SymmetricGroup(wait_budget_s=10.0)
+    try:
+        # 1. broadcast: every rank updates its slice, result lands in every copy
+        lo, hi = split_bounds(n // 8, world, rank)
+        lo, hi = lo * 8, hi * 8
+        g = torch.Generator(device=dev).manual_seed(7)
+        master = torch.randn(n, device=dev, generator=g)
+        upd = torch.randn(n, device=dev, generator=g).bfloat16()
+        m_a, m_b = master.clone(), master.clone()
+        lp_mc = buf.view(torch.bfloat16, n)
+        p2p = SymmetricBuffer(2 * n)
+        call("pb_mm_muon_apply", ptr(m_a[lo:]), ptr(upd[lo:]), buf.mc_at(2 * lo), hi - lo, 0.1, 0.7, 0.01,
+             stream_ptr())
+        call("pb_muon_apply_bcast", ptr(m_b), ptr(upd[lo:]), p2p.peer_ptrs(0), world, lo, hi - lo, 0.1, 0.7,
+             0.01, stream_ptr())
+        grp.barrier(0)
+        torch.cuda.synchronize()
+        facts["bcast_equal"] = bool(torch.equal(lp_mc, p2p.view(torch.bfloat16, n)))
+        facts["bcast_nonzero"] = bool(lp_mc.float().abs().sum() > 0)
+        facts["master_equal"] = bool(torch.equal(m_a, m_b))
+        # 2. all-reduce in the switch
+        x = torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank))
+        want = x.clone()
+        dist.all_reduce(want)
+        f = buf.view(torch.float32, n)
+        f.copy_(x)
+        nvls.allreduce_f32(buf, n, grp)
+        torch.cuda.synchronize()
+        grp.check()
+        facts["allreduce_err"] = float((f - want).abs().max() / want.abs().max())
+        p2p.close()
+    finally:
+        buf.close()
+    # 3. trainer: multicast broadcast == peer-to-peer broadcast
+    cfg = small_hybrid()
+    tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=50, decay_steps=5)
+    params = model.init_params(cfg, 0)
+    tokens = torch.randint(0, cfg.vocab_size, (2 * world, 128), generator=torch.Generator().manual_seed(3)).to(dev)
+    mine = tokens[2 * rank:2 * rank + 2]
+    losses = {}
+    for mode in (True, False):
+        tr = engine.Trainer(cfg, tcfg, params=params, device=dev, micro_batch=2, grad_sync="p2p", nvls=mode)
+        try:
+            used = tr.nvls_lp is not None
+            losses[mode] = ([tr.step(mine)["loss"].item() for _ in range(3)], used)
+            torch.cuda.synchronize()
+        finally:
+            tr.close()
+    dist.barrier()
+    assert facts["bcast_equal"] and facts["bcast_nonzero"] and facts["master_equal"], facts
+    assert facts["allreduce_err"] < 1e-5, facts
+    assert losses[True][1] and not losses[False][1]
+    assert losses[True][0] == losses[False][0], losses
+    if rank == 0:
+        print("NVLS_OK", facts, losses[True][0])
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     try:
         {"ep": ep_main, "ep_engine": ep_engine_main, "cp_delta": cp_delta_main, "ag_gemm": ag_gemm_main, "cp_engine": cp_engine_main,
-         "fsdp_engine": fsdp_engine_main}.get((sys.argv[1:] or [""])[0], main)()
+         "fsdp_engine": fsdp_engine_main, "nvls": nvls_main}.get((sys.argv[1:] or [""])[0], main)()
     except BaseException:
         import traceback
 

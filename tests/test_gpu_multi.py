@@ -10,8 +10,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run_ranks(world, port, marker, *args):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+def _run_ranks(world, port, marker, *args, nvls="0"):
+    # the in-switch paths stay off except in the test that is about them
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PB200_NVLS=nvls, MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port),
            str(Path(__file__).parent / "_multi_gpu_worker.py"), *args]
@@ -64,3 +65,8 @@ def test_two_rank_context_parallel_trainer():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_zero3_trainer():
     _run_ranks(2, 29529, "FSDP_ENGINE_OK", "fsdp_engine")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_nvls_multicast_paths():
+    _run_ranks(2, 29531, "NVLS_OK", "nvls", nvls="1")
