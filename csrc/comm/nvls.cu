@@ -199,8 +199,18 @@ __global__ void __launch_bounds__(256) mm_adamw_kernel(
 // mc[lo : lo + n) (fp32) <- sum over the ranks' copies, written to every rank.
 __global__ void __launch_bounds__(256) mm_allreduce_f32_kernel(float* mc, long lo, long n) {
   const long n4 = n >> 2;
-  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n4;
-       i += static_cast<long>(gridDim.x) * blockDim.x) {
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  // four in-switch reductions in flight per thread before the first write-back
+  for (; i + 3 * stride < n4; i += 4 * stride) {
+    float4 s[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) s[u] = multimem_ld_reduce_add_v4(mc + lo + (i + u * stride) * 4);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      multimem_st_v4(mc + lo + (i + u * stride) * 4, *reinterpret_cast<const uint4*>(&s[u]));
+  }
+  for (; i < n4; i += stride) {
     float* a = mc + lo + i * 4;
     const float4 s = multimem_ld_reduce_add_v4(a);
     multimem_st_v4(a, *reinterpret_cast<const uint4*>(&s));

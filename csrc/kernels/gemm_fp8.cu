@@ -276,56 +276,144 @@ __device__ __forceinline__ uint32_t to_e4m3x4(float a, float b, float c, float d
   return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
 }
 
-// One warp per (row, 128-element block); K a multiple of 128.
+// One warp per row; a lane covers 16 consecutive elements (two 16-byte loads, one 16-byte
+// store), eight lanes one 128-element block, so a warp moves 512 elements per step. Every lane
+// runs every step (the shuffles name the whole warp); K is a multiple of 128, so the eight lanes
+// of a block are active or idle together.
 // rows_dev (may be null): device-side count of the rows in use; the scale table keeps its row
 // stride M whatever that count.
-__global__ void quant_rows_kernel(const bf16* __restrict__ x, long ld, int M, int K,
-                                  uint8_t* __restrict__ q, float* __restrict__ scales,
-                                  const int* __restrict__ rows_dev) {
-  const long w = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const int nkb = K / 128;
-  const int m_eff = rows_dev != nullptr ? min(M, *rows_dev) : M;
-  if (w >= static_cast<long>(m_eff) * nkb) return;
-  const int row = static_cast<int>(w / nkb), kb = static_cast<int>(w % nkb);
-  const bf16* src = x + static_cast<size_t>(row) * ld + kb * 128 + lane * 4;
-  const uint2 raw = *reinterpret_cast<const uint2*>(src);
-  const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-  const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-  const float f0 = __low2float(p0), f1 = __high2float(p0), f2 = __low2float(p1), f3 = __high2float(p1);
-  const float amax = warp_max(fmaxf(fmaxf(fabsf(f0), fabsf(f1)), fmaxf(fabsf(f2), fabsf(f3))));
+__device__ __forceinline__ uint4 quant16(const float (&f)[16], bool active, float* scale_out) {
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
   const float scale = amax > 0.f ? amax / 448.f : 1.f;
-  // true division (not a reciprocal multiply): ties must round as in x / scale
-  *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(row) * K + kb * 128 + lane * 4) =
-      to_e4m3x4(__fdiv_rn(f0, scale), __fdiv_rn(f1, scale), __fdiv_rn(f2, scale), __fdiv_rn(f3, scale));
-  if (lane == 0) scales[static_cast<size_t>(kb) * M + row] = scale;
+  *scale_out = scale;
+  uint4 pk = make_uint4(0u, 0u, 0u, 0u);
+  if (active) {
+    // true division (not a reciprocal multiply): ties must round as in x / scale
+    pk.x = to_e4m3x4(__fdiv_rn(f[0], scale), __fdiv_rn(f[1], scale), __fdiv_rn(f[2], scale), __fdiv_rn(f[3], scale));
+    pk.y = to_e4m3x4(__fdiv_rn(f[4], scale), __fdiv_rn(f[5], scale), __fdiv_rn(f[6], scale), __fdiv_rn(f[7], scale));
+    pk.z = to_e4m3x4(__fdiv_rn(f[8], scale), __fdiv_rn(f[9], scale), __fdiv_rn(f[10], scale), __fdiv_rn(f[11], scale));
+    pk.w = to_e4m3x4(__fdiv_rn(f[12], scale), __fdiv_rn(f[13], scale), __fdiv_rn(f[14], scale), __fdiv_rn(f[15], scale));
+  }
+  return pk;
 }
 
-// y[row, :] = bf16(e4m3(q[row, :]) * scale of its 1 x 128 block); one warp per (row, block)
-__global__ void dequant_rows_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales,
-                                    long ld_s, int M, int K, bf16* __restrict__ y,
-                                    const int* __restrict__ rows_dev) {
-  const long w = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+__global__ void __launch_bounds__(256) quant_rows_kernel(const bf16* __restrict__ x, long ld, int M,
+                                                         int K, uint8_t* __restrict__ q,
+                                                         float* __restrict__ scales,
+                                                         const int* __restrict__ rows_dev) {
   const int lane = threadIdx.x & 31;
-  const int nkb = K / 128;
   const int m_eff = rows_dev != nullptr ? min(M, *rows_dev) : M;
-  if (w >= static_cast<long>(m_eff) * nkb) return;
-  const int row = static_cast<int>(w / nkb), kb = static_cast<int>(w % nkb);
-  const float s = scales[static_cast<size_t>(kb) * ld_s + row];
-  const uint32_t raw = *reinterpret_cast<const uint32_t*>(q + static_cast<size_t>(row) * K + kb * 128 + lane * 4);
-  float f[4];
+  const long warps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  for (long row = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < m_eff;
+       row += warps) {
+    const bf16* src = x + static_cast<size_t>(row) * ld;
+    for (int c0 = 0; c0 < K; c0 += 512) {
+      const int c = c0 + lane * 16;
+      const bool active = c < K;
+      float f[16];
+      if (active) {
+        unpack8(*reinterpret_cast<const bf16x8*>(src + c), f);
+        unpack8(*reinterpret_cast<const bf16x8*>(src + c + 8), f + 8);
+      } else {
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((raw >> (16 * j)) & 0xffffu),
-                                                     __NV_E4M3);
-    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h));
-    f[2 * j] = v.x; f[2 * j + 1] = v.y;
+        for (int j = 0; j < 16; ++j) f[j] = 0.f;
+      }
+      float scale;
+      const uint4 pk = quant16(f, active, &scale);
+      if (active) {
+        *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + c) = pk;
+        if ((lane & 7) == 0) scales[static_cast<size_t>(c >> 7) * M + row] = scale;
+      }
+    }
   }
-  __nv_bfloat162 o0 = __floats2bfloat162_rn(f[0] * s, f[1] * s), o1 = __floats2bfloat162_rn(f[2] * s, f[3] * s);
-  uint2 pk;
-  pk.x = *reinterpret_cast<uint32_t*>(&o0);
-  pk.y = *reinterpret_cast<uint32_t*>(&o1);
-  *reinterpret_cast<uint2*>(y + static_cast<size_t>(row) * K + kb * 128 + lane * 4) = pk;
+}
+
+// SwiGLU fused with the row quantiser: h = silu(gate) * up is written as bf16 (the backward
+// and the weight gradient of the next product need it) and, from those bf16 values, as e4m3 +
+// 1 x 128 scales for the FP8 product that consumes it. One pass over gu instead of a SwiGLU
+// pass and a quantiser pass. gu [rows, 2H] (gate | up), H a multiple of 128.
+__global__ void __launch_bounds__(256) swiglu_quant_kernel(const bf16* __restrict__ gu,
+                                                           bf16* __restrict__ h, int M, int H,
+                                                           uint8_t* __restrict__ q,
+                                                           float* __restrict__ scales,
+                                                           const int* __restrict__ rows_dev) {
+  const int lane = threadIdx.x & 31;
+  const int m_eff = rows_dev != nullptr ? min(M, *rows_dev) : M;
+  const long warps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  for (long row = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < m_eff;
+       row += warps) {
+    const bf16* src = gu + static_cast<size_t>(row) * 2 * H;
+    for (int c0 = 0; c0 < H; c0 += 512) {
+      const int c = c0 + lane * 16;
+      const bool active = c < H;
+      float f[16];
+      if (active) {
+        float g[16], u[16];
+        unpack8(*reinterpret_cast<const bf16x8*>(src + c), g);
+        unpack8(*reinterpret_cast<const bf16x8*>(src + c + 8), g + 8);
+        unpack8(*reinterpret_cast<const bf16x8*>(src + H + c), u);
+        unpack8(*reinterpret_cast<const bf16x8*>(src + H + c + 8), u + 8);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float s = 1.f / (1.f + __expf(-g[j]));
+          // quantise what the bf16 copy holds, so both forms of h agree
+          f[j] = bf16_to_f32(f32_to_bf16(g[j] * s * u[j]));
+        }
+        bf16* dst = h + static_cast<size_t>(row) * H + c;
+        *reinterpret_cast<bf16x8*>(dst) = pack8(f);
+        *reinterpret_cast<bf16x8*>(dst + 8) = pack8(f + 8);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) f[j] = 0.f;
+      }
+      float scale;
+      const uint4 pk = quant16(f, active, &scale);
+      if (active) {
+        *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * H + c) = pk;
+        if ((lane & 7) == 0) scales[static_cast<size_t>(c >> 7) * M + row] = scale;
+      }
+    }
+  }
+}
+
+// y[row, :] = bf16(e4m3(q[row, :]) * scale of its 1 x 128 block); one warp per row, a lane
+// covers 16 consecutive elements (one 16-byte load, two 16-byte stores)
+__global__ void __launch_bounds__(256) dequant_rows_kernel(const uint8_t* __restrict__ q,
+                                                           const float* __restrict__ scales,
+                                                           long ld_s, int M, int K,
+                                                           bf16* __restrict__ y,
+                                                           const int* __restrict__ rows_dev) {
+  const int lane = threadIdx.x & 31;
+  const int m_eff = rows_dev != nullptr ? min(M, *rows_dev) : M;
+  const long warps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  for (long row = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < m_eff;
+       row += warps) {
+    for (int c = lane * 16; c < K; c += 512) {
+      const float s = scales[static_cast<size_t>(c >> 7) * ld_s + row];
+      const uint4 raw = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(row) * K + c);
+      const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+      float f[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(
+              static_cast<__nv_fp8x2_storage_t>((w4[j] >> (16 * hh)) & 0xffffu), __NV_E4M3);
+          const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+          f[4 * j + 2 * hh] = v.x * s;
+          f[4 * j + 2 * hh + 1] = v.y * s;
+        }
+      }
+      bf16* dst = y + static_cast<size_t>(row) * K + c;
+      *reinterpret_cast<bf16x8*>(dst) = pack8(f);
+      *reinterpret_cast<bf16x8*>(dst + 8) = pack8(f + 8);
+    }
+  }
 }
 
 // One CTA (256 threads) per 128 x 128 block of a [N, K] matrix (edges clipped).
@@ -369,9 +457,10 @@ using namespace pb;
 // x [M, K] bf16 (row stride ld, K % 128 == 0) -> q [M, K] e4m3, scales [K / 128, M] fp32.
 PB_API int pb_fp8_quant_rows(const void* x, long ld, int M, int K, void* q, float* scales,
                              cudaStream_t st) {
-  if (M <= 0 || K <= 0 || K % 128 != 0 || ld % 4 != 0) return PB_BAD_ARG;
-  const long warps = static_cast<long>(M) * (K / 128);
-  const long blocks = (warps * 32 + 255) / 256;
+  if (M <= 0 || K <= 0 || K % 128 != 0 || ld % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+    return PB_BAD_ARG;
+  long blocks = (static_cast<long>(M) * 32 + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
   f8::quant_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
       static_cast<const bf16*>(x), ld, M, K, static_cast<uint8_t*>(q), scales, nullptr);
   return static_cast<int>(cudaGetLastError());
@@ -379,11 +468,25 @@ PB_API int pb_fp8_quant_rows(const void* x, long ld, int M, int K, void* q, floa
 // The same over the first min(M, *rows_dev) rows (rows_dev: a device int).
 PB_API int pb_fp8_quant_rows_dyn(const void* x, long ld, int M, int K, void* q, float* scales,
                                  const int* rows_dev, cudaStream_t st) {
-  if (M <= 0 || K <= 0 || K % 128 != 0 || ld % 4 != 0) return PB_BAD_ARG;
-  const long warps = static_cast<long>(M) * (K / 128);
-  const long blocks = (warps * 32 + 255) / 256;
+  if (M <= 0 || K <= 0 || K % 128 != 0 || ld % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+    return PB_BAD_ARG;
+  long blocks = (static_cast<long>(M) * 32 + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
   f8::quant_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
       static_cast<const bf16*>(x), ld, M, K, static_cast<uint8_t*>(q), scales, rows_dev);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// h [M, H] bf16 = silu(gu[:, :H]) * gu[:, H:], and its e4m3 rows q [M, H] with scales
+// [H / 128, M], in one pass. H a multiple of 128; rows_dev (may be null): device row count.
+PB_API int pb_swiglu_quant(const void* gu, void* h, int M, int H, void* q, float* scales,
+                           const int* rows_dev, cudaStream_t st) {
+  if (M <= 0 || H <= 0 || H % 128 != 0) return PB_BAD_ARG;
+  long blocks = (static_cast<long>(M) * 32 + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  f8::swiglu_quant_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+      static_cast<const bf16*>(gu), static_cast<bf16*>(h), M, H, static_cast<uint8_t*>(q), scales,
+      rows_dev);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -392,8 +495,8 @@ PB_API int pb_fp8_quant_rows_dyn(const void* x, long ld, int M, int K, void* q, 
 PB_API int pb_fp8_dequant_rows(const void* q, const float* scales, long ld_s, int M, int K, void* y,
                                const int* rows_dev, cudaStream_t st) {
   if (M <= 0 || K <= 0 || K % 128 != 0 || ld_s < M) return PB_BAD_ARG;
-  const long warps = static_cast<long>(M) * (K / 128);
-  const long blocks = (warps * 32 + 255) / 256;
+  long blocks = (static_cast<long>(M) * 32 + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
   f8::dequant_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
       static_cast<const uint8_t*>(q), scales, ld_s, M, K, static_cast<bf16*>(y), rows_dev);
   return static_cast<int>(cudaGetLastError());

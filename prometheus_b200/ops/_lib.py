@@ -74,6 +74,7 @@ _SIGS = {
     "pb_fp8_quant_blocks": [P, L, I, I, P, P, P],
     "pb_fp8_dequant_rows": [P, P, L, I, I, P, P, P],
     "pb_fp8_quant_rows_dyn": [P, L, I, I, P, P, P, P],
+    "pb_swiglu_quant": [P, P, I, I, P, P, P, P],
     "pb_swiglu_fwd_dyn": [P, P, L, I, P, P],
     "pb_swiglu_bwd_dyn": [P, P, P, L, I, P, P],
     "pb_copy_rows_dyn": [P, P, L, L, P, P],

@@ -32,6 +32,21 @@ def quantize_rows(x: Tensor, rows_used: Tensor | None = None):
     return q, s
 
 
+def swiglu_quantize(gu: Tensor, rows_used: Tensor | None = None):
+    """gu [M, 2H] bf16 (gate | up, H % 128 == 0) -> (h [M, H] bf16, q [M, H] e4m3 bytes, scales
+    [H / 128, M] fp32) in one pass: ``h = silu(gate) * up`` and the 1 x 128 block quantisation
+    of those bf16 values, i.e. ``swiglu`` followed by ``quantize_rows`` without the second read.
+    ``rows_used`` (a device int32): only the first that many rows are touched."""
+    M, two_h = gu.shape
+    H = two_h // 2
+    assert gu.dtype == BF16 and gu.is_contiguous() and H % 128 == 0
+    h = torch.empty((M, H), dtype=BF16, device=gu.device)
+    q = torch.empty((M, H), dtype=torch.uint8, device=gu.device)
+    s = torch.empty((H // 128, M), dtype=torch.float32, device=gu.device)
+    call("pb_swiglu_quant", ptr(gu), ptr(h), M, H, ptr(q), ptr(s), ptr(rows_used), stream_ptr())
+    return h, q, s
+
+
 def quantize_blocks(w: Tensor):
     """w [N, K] or [E, N, K] bf16 -> (q same shape uint8, scales [(E,) ceil(N/128), K/128])."""
     assert w.dtype == BF16 and w.is_contiguous() and w.shape[-1] % 128 == 0

@@ -154,9 +154,17 @@ class _MoeFfnFn(torch.autograd.Function):
         pl = place(ids, E)
         xp = permute(x, pl)
         gu = _expert_gemm(xp, w_gu, pl, fp8)
-        hs = torch.empty((pl.rows, h), dtype=BF16, device=x.device)
-        call("pb_swiglu_fwd", ptr(gu), ptr(hs), pl.rows, h, stream_ptr())
-        y = _expert_gemm(hs, w_down, pl, fp8)
+        if fp8 and h % 128 == 0 and w_down.shape[1] % 128 == 0:
+            # SwiGLU and the e4m3 rows of its output in one pass
+            from . import fp8 as F8
+
+            hs, hq, sh = F8.swiglu_quantize(gu)
+            wq, sw = F8.quantize_blocks(w_down.contiguous())
+            y = F8.gemm_fp8(hq, sh, wq, sw, mblk_group=pl.mblk_group)
+        else:
+            hs = torch.empty((pl.rows, h), dtype=BF16, device=x.device)
+            call("pb_swiglu_fwd", ptr(gu), ptr(hs), pl.rows, h, stream_ptr())
+            y = _expert_gemm(hs, w_down, pl, fp8)
         out = combine(y, pl, gates, T)
         ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids_r, gates, xp, gu, hs, y)
         ctx.pl = pl

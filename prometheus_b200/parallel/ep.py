@@ -46,8 +46,16 @@ class EpContext:
     pairs; size it as ``capacity_factor * tokens_per_rank * top_k`` plus 127 rows per local expert.
     """
 
-    def __init__(self, sym: SymmetricGroup, d_model: int, n_experts: int, max_rows: int):
+    def __init__(self, sym: SymmetricGroup, d_model: int, n_experts: int, max_rows: int,
+                 fuse_dispatch: bool = False):
         self.sym = sym
+        # FP8 path only: True = no barrier between dispatch and the first grouped GEMM, the
+        # GEMM's TMA producer takes each 128-row block when the senders' per-row counts say it
+        # is complete; False = one bounded barrier, then the plain grouped GEMM. Measured on
+        # two B200s at 32768 tokens per rank the barrier form is the faster one (the senders
+        # push in token order, so blocks complete late, and the per-row system-scope counts
+        # cost the senders more than the barrier costs the owners).
+        self.fuse_dispatch = bool(fuse_dispatch)
         self.world, self.rank = sym.world, sym.rank
         if n_experts % self.world:
             raise ValueError("the expert count must be divisible by the expert-parallel size")
@@ -165,7 +173,7 @@ class _EpMoeFn(torch.autograd.Function):
         sym.barrier(4)
         pl, send_base = ep.layout()
         used = pl.expert_off[ep.El:]            # device int: rows of the receive buffer in use
-        if use_fp8:
+        if use_fp8 and ep.fuse_dispatch:
             # Fused dispatch + first grouped GEMM: no barrier between them. The senders count
             # every landed row into the owner's per-block counters and the GEMM's TMA producer
             # takes a 128-row block as soon as that block is complete (bounded wait).
@@ -175,6 +183,13 @@ class _EpMoeFn(torch.autograd.Function):
             gu = F8.gemm_fp8(ep.xq_local, ep.xs_local, wq, sw, mblk_group=pl.mblk_group,
                              arrived=ep.arrived_local, expect=ep.blk_expect, budget_ns=sym.budget_ns)
             ep.arrived_local.zero_()            # before this rank's next slot-4 arrival
+            saved_x = (_copy_used(ep.xq_local, used), ep.xs_local.clone())
+        elif use_fp8:
+            dest_rank, dest_row = ep.dispatch_fp8(x, ids, local, send_base, count_arrivals=False)
+            sym.barrier(5)                      # every row has landed
+            ep.zero_pad_fp8(pl)
+            wq, sw = F8.quantize_blocks(w_gu.contiguous())
+            gu = F8.gemm_fp8(ep.xq_local, ep.xs_local, wq, sw, mblk_group=pl.mblk_group)
             # what the backward differentiates against: the quantised rows (half the bytes of a
             # bf16 copy); the receive buffer itself is overwritten by the next layer's senders
             saved_x = (_copy_used(ep.xq_local, used), ep.xs_local.clone())
@@ -185,13 +200,13 @@ class _EpMoeFn(torch.autograd.Function):
             xp = _copy_used(ep.x_local, used)
             gu = M.grouped_gemm(xp, w_gu, pl)
             saved_x = (xp, xp.new_empty(0))
-        hs = torch.empty((pl.rows, h), dtype=BF16, device=x.device)
-        call("pb_swiglu_fwd_dyn", ptr(gu), ptr(hs), pl.rows, h, ptr(used), stream_ptr())
         if use_fp8:
-            hq, sh = F8.quantize_rows(hs, used)
+            hs, hq, sh = F8.swiglu_quantize(gu, used)      # SwiGLU and its e4m3 rows in one pass
             wq, sw = F8.quantize_blocks(w_down.contiguous())
             F8.gemm_fp8(hq, sh, wq, sw, mblk_group=pl.mblk_group, out=ep.y_local)
         else:
+            hs = torch.empty((pl.rows, h), dtype=BF16, device=x.device)
+            call("pb_swiglu_fwd_dyn", ptr(gu), ptr(hs), pl.rows, h, ptr(used), stream_ptr())
             M.grouped_gemm(hs, w_down, pl, out=ep.y_local)
         y = _copy_used(ep.y_local, used)        # the gate gradient needs <y_row, dy_row> later
         sym.barrier(6)                          # results are ready to be pulled

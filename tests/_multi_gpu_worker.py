@@ -74,11 +74,18 @@ def ep_main():
     wd8_l = wd8[rank * El:(rank + 1) * El].clone().requires_grad_(True)
     x8 = x.detach().clone().requires_grad_(True)
     rw8 = rw.clone().requires_grad_(True)
-    for it in range(2):
-        for t in (x8, rw8, wgu8_l, wd8_l):
-            t.grad = None
-        out8, _, ids8 = ep_moe_ffn(x8, rw8, bias, wgu8_l, wd8_l, k, ep, fp8=True)
-        (out8.float() * go.float()).sum().backward()
+    # both forms of the FP8 path: one barrier between dispatch and GEMM, and the fused form in
+    # which the GEMM consumes each 128-row block as its rows are counted in
+    ep_fused = EpContext(grp, d, E, max_rows=world * T * k + El * 128, fuse_dispatch=True)
+    outs8 = []
+    for ctx8 in (ep_fused, ep):
+        for it in range(2):
+            for t in (x8, rw8, wgu8_l, wd8_l):
+                t.grad = None
+            out8, _, ids8 = ep_moe_ffn(x8, rw8, bias, wgu8_l, wd8_l, k, ctx8, fp8=True)
+            (out8.float() * go.float()).sum().backward()
+        outs8.append(out8.detach().clone())
+    assert torch.equal(outs8[0], outs8[1]), "fused and barrier forms of the FP8 dispatch differ"
     torch.cuda.synchronize()
     grp.check()
     ops.check_status(dev)

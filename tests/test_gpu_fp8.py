@@ -90,3 +90,33 @@ def test_fp8_linear_and_grouped_gemm():
         seg = slice(off[e], off[e] + tot[e])
         ref = xd[seg] @ wd[e].t()
         assert (got[seg].float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
+
+
+def test_swiglu_quantize_and_dequantize_kernels():
+    """The fused SwiGLU + row quantiser equals SwiGLU followed by the row quantiser (bitwise:
+    it quantises the bf16 values it writes), rows beyond a device-side count stay untouched,
+    and the bf16 dequantiser returns exactly scale * e4m3 value."""
+    from prometheus_b200.ops import fp8
+    from prometheus_b200.ops import functional as ops
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for M, H in ((300, 128), (257, 1408), (64, 512)):
+        gu = (torch.randn(M, 2 * H, device="cuda", generator=g) * 2).bfloat16()
+        h_ref = ops.swiglu(gu)
+        q_ref, s_ref = fp8.quantize_rows(h_ref)
+        h, q, s = fp8.swiglu_quantize(gu)
+        assert torch.equal(h, h_ref) and torch.equal(q, q_ref) and torch.equal(s, s_ref), (M, H)
+        # against plain fp32 PyTorch
+        want = torch.nn.functional.silu(gu[:, :H].float()) * gu[:, H:].float()
+        assert (h.float() - want).abs().max() <= 1e-2 * want.abs().max()
+        deq = fp8.dequantize_rows_bf16(q, s)
+        ref = fp8.dequantize_rows(q, s)
+        assert torch.equal(deq.float(), ref.bfloat16().float())
+        assert (deq.float() - h.float()).abs().max() <= 0.07 * h.float().abs().max()
+        # device-side row count
+        used = torch.tensor([M // 2], dtype=torch.int32, device="cuda")
+        h2, q2, s2 = fp8.swiglu_quantize(gu, used)
+        assert torch.equal(h2[: M // 2], h_ref[: M // 2]) and torch.equal(q2[: M // 2], q_ref[: M // 2])
+        assert torch.equal(s2[:, : M // 2], s_ref[:, : M // 2])
+        d2 = fp8.dequantize_rows_bf16(q, s, used)
+        assert torch.equal(d2[: M // 2], deq[: M // 2])
