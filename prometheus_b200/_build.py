@@ -37,9 +37,32 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
 
 
-def native_lib_path() -> Path:
+SANITIZE_ENV = "PB200_NATIVE_SANITIZE"     # "", "address,undefined" or "thread": which build to load
+
+
+def _san_tag(sanitize: str | None) -> str:
+    return "" if not sanitize else "_" + sanitize.replace(",", "_")
+
+
+def native_lib_path(sanitize: str | None = None) -> Path:
+    """The pybind11 module; with ``sanitize`` (default: the ``PB200_NATIVE_SANITIZE``
+    environment variable) the instrumented build that lives beside it in ``_lib/san_*``."""
     suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    sanitize = os.environ.get(SANITIZE_ENV, "") if sanitize is None else sanitize
+    if sanitize:
+        return LIB_DIR / ("san" + _san_tag(sanitize)) / f"_pb200_native{suffix}"
     return LIB_DIR / f"_pb200_native{suffix}"
+
+
+def sanitizer_runtime(sanitize: str) -> str:
+    """Path of the sanitizer runtime to ``LD_PRELOAD`` when an instrumented module is loaded
+    into an uninstrumented interpreter."""
+    lib = "libtsan.so" if "thread" in sanitize else "libasan.so"
+    # libstdc++ rides along: the interpreter is not linked against it, and the runtime resolves
+    # its __cxa_throw interceptor when it starts
+    paths = [subprocess.run(["gcc", f"-print-file-name={name}"], capture_output=True, text=True).stdout.strip()
+             for name in (lib, "libstdc++.so")]
+    return " ".join(paths)
 
 
 def _nvcc() -> str:
@@ -91,31 +114,45 @@ def build_kernels(verbose: bool = False, force: bool = False) -> Path:
     return KERNEL_LIB
 
 
-def build_native(verbose: bool = False, force: bool = False) -> Path | None:
-    """Compile csrc/native/*.cpp into the pybind11 module (host only, no CUDA)."""
+def build_native(verbose: bool = False, force: bool = False, sanitize: str = "") -> Path | None:
+    """Compile csrc/native/*.cpp into the pybind11 module (host only, no CUDA).
+
+    ``sanitize`` = ``"address,undefined"`` or ``"thread"`` builds an instrumented copy
+    (``-fsanitize=...``, ``-O1 -g``, frame pointers kept) under ``_lib/san_*`` for the host-side
+    race / memory checks of the systems code (the asynchronous checkpoint writer, the loader):
+    load it with ``PB200_NATIVE_SANITIZE=<same string>`` and the matching runtime preloaded
+    (``sanitizer_runtime``)."""
     srcs = sorted((CSRC / "native").glob("*.cpp"))
     if not srcs:
         return None
     import pybind11
 
+    if sanitize not in ("", "address,undefined", "thread"):
+        raise ValueError("sanitize must be '', 'address,undefined' or 'thread'")
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     headers = list((CSRC / "native").glob("*.hpp")) + list((CSRC / "native").glob("*.h"))
     inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
            "-I", CSRC / "native"]
     flags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function"]
+    link_extra = []
+    if sanitize:
+        flags = ["-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={sanitize}", "-std=c++17", "-fPIC",
+                 "-fvisibility=hidden", "-Wall", "-Wno-unused-function"]
+        link_extra = [f"-fsanitize={sanitize}"]
     objs, jobs = [], []
     for src in srcs:
-        obj = OBJ_DIR / ("native_" + src.stem + ".o")
+        obj = OBJ_DIR / ("native" + _san_tag(sanitize) + "_" + src.stem + ".o")
         objs.append(obj)
         if force or _newer([src, *headers], obj):
             jobs.append(["g++", *flags, *inc, "-c", src, "-o", obj])
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(lambda c: _run(c, verbose), jobs))
-    out = native_lib_path()
+    out = native_lib_path(sanitize)
+    out.parent.mkdir(parents=True, exist_ok=True)
     if force or jobs or _newer(objs, out):
-        _run(["g++", "-shared", "-o", out, *objs, "-lpthread", "-lz"], verbose)
+        _run(["g++", "-shared", "-o", out, *objs, *link_extra, "-lpthread", "-lz"], verbose)
     return out
 
 
@@ -125,5 +162,9 @@ def build_all(verbose: bool = False, force: bool = False) -> None:
 
 
 if __name__ == "__main__":
-    build_all(verbose="-v" in sys.argv, force="--force" in sys.argv)
-    print("built:", KERNEL_LIB, native_lib_path())
+    san = [a.split("=", 1)[1] for a in sys.argv if a.startswith("--sanitize=")]
+    if san:
+        print("built:", build_native(verbose="-v" in sys.argv, force="--force" in sys.argv, sanitize=san[0]))
+    else:
+        build_all(verbose="-v" in sys.argv, force="--force" in sys.argv)
+        print("built:", KERNEL_LIB, native_lib_path(""))

@@ -197,6 +197,10 @@ class Trainer:
         # the kernels latch a status word when a bounded wait runs out; every
         # `check_status_every`-th step reads it back with the loss and raises (0: never)
         self.check_status_every = int(check_status_every)
+        self.time_phases = False           # record CUDA events round the phases of every step
+        self.phase_times: dict[str, float] = {}
+        self.collect_amax = False          # keep the largest |final hidden| of the step (FP8 range probe)
+        self.amax: dict[str, Tensor] = {}
         self.router_records: list = []
         self._router_load: dict[int, Tensor] = {}
         self.moe_load: Tensor | None = None          # (MoE layers, experts) load shares, last step
@@ -1171,6 +1175,11 @@ class Trainer:
             wt = loss_mask.float().clone()
             wt[:, 0] = 0.0                          # mask[:, 1:] aligned to the predicting position
             wt = torch.roll(wt, -1, dims=1).reshape(-1) / denom
+        if self.collect_amax:
+            with torch.no_grad():
+                a = hid.detach().abs().amax().float()
+                prev = self.amax.get("final_hidden")
+                self.amax["final_hidden"] = a if prev is None else torch.maximum(prev, a)
         ce = ops.softcap_cross_entropy(hid, self.weight("unembed"), targets, wt.contiguous(),
                                        float(self.tcfg.softcap), self.ce_chunk_rows)
         n_mtp = self.cfg.mtp_heads
@@ -1432,10 +1441,17 @@ class Trainer:
                 dist.all_reduce(dj, group=self.pg)
             mtp_denoms = list(dj.clamp(min=1.0))
         mb = self.micro_batch
+        ev = None
+        if self.time_phases:
+            self._harvest_phase_times()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record()
         for b0 in range(0, tokens.shape[0], mb):
             l = self.loss(tokens[b0:b0 + mb], loss_mask[b0:b0 + mb], denom, mtp_denoms)
             l.backward()
             total += l.detach()
+        if ev is not None:
+            ev[1].record()
         if self.router_bias and self._router_load:
             # aux-loss-free balancing, every MoE layer from its own load:
             # b_i <- b_i - u sign(load_i - mean(load_i))
@@ -1451,6 +1467,8 @@ class Trainer:
                 self.router_bias[i].sub_(delta[row])
             self.moe_load = load            # (MoE layers, experts) shares, for the metrics
         self._sync_grads()
+        if ev is not None:
+            ev[2].record()
         if self.world > 1:
             import torch.distributed as dist
 
@@ -1458,10 +1476,26 @@ class Trainer:
         self.optimizer_step(lr_mult)
         if clip_qk and self.max_logits:
             self._qk_clip()
+        if ev is not None:
+            ev[3].record()
+            self._phase_events = ev
         gnorm = self.gnorm_sq.sqrt()
         self.zero_grad()
         return {"loss": total, "grad_norm": gnorm, "lr": sched, "step": t,
                 "status": self.status_tensor()}
+
+    def _harvest_phase_times(self) -> None:
+        """Device times of the previous step's phases (its events have completed by the time the
+        next step starts, so reading them does not stall): forward + backward, the gradient
+        synchronisation (barrier wait + fold: what the compute stream spent inside
+        communication, i.e. an upper bound of the exposed communication), optimizer + weight
+        refresh."""
+        ev = getattr(self, "_phase_events", None)
+        if ev is None or not ev[3].query():
+            return
+        self.phase_times = {"fwd_bwd_ms": ev[0].elapsed_time(ev[1]), "sync_ms": ev[1].elapsed_time(ev[2]),
+                            "opt_ms": ev[2].elapsed_time(ev[3])}
+        self._phase_events = None
 
     def _qk_clip(self) -> None:
         """QK-clip on the logits the attention kernel saw this step: heads whose largest scaled

@@ -16,9 +16,11 @@ def _load():
     name = "_pb200_native"
     if name in sys.modules:
         return sys.modules[name]
-    path = _build.native_lib_path()
+    path = _build.native_lib_path()        # honours PB200_NATIVE_SANITIZE
     if not path.exists():
-        _build.build_native()
+        import os
+
+        _build.build_native(sanitize=os.environ.get(_build.SANITIZE_ENV, ""))
     spec = importlib.util.spec_from_file_location(name, path)
     mod = importlib.util.module_from_spec(spec)
     sys.modules[name] = mod

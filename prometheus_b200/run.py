@@ -15,7 +15,13 @@ the wiring of the pieces that exist on their own elsewhere in the package:
 * steps run on ``engine.Trainer`` (GPU) or, for ``--device cpu``, on the fp32 ``train.train_step``;
 * the loss goes to the native ``SpikeLog``: a spike rolls the trainer back to the last in-memory
   checkpoint and skips the offending batch, as the elastic controller prescribes;
-* ``Metrics`` / ``MetricLog`` record loss, gradient norm, learning rate, tokens per second;
+* a ``supervisor.RunSupervisor`` holds the native ``Controller``, ``Tracer`` and ``MetricLog``:
+  every phase of a step is a tracer span (and an NVTX range on a GPU); the step is bracketed as
+  a collective for the watchdog; the device status word comes back with the loss, and a latched
+  wait-timeout becomes a ``WatchdogTimeout`` health event before the loop stops; every
+  ``sdc_every`` steps the replicated state is checksummed on the device and voted on;
+  ``train.loss / grad_norm / lr / tokens_per_s / mfu``, ``comm.exposed_ms``, ``moe.load.*`` and
+  ``fp8.amax.*`` go to the metric log (``--set metric_log=path`` for a JSONL file);
 * checkpoints (in memory every ``ckpt_every`` steps, persistent at the end and every
   ``persist_every``) carry the loader cursor, so ``--resume`` continues bit-exactly.
 
@@ -61,6 +67,12 @@ class RunOptions:
     n_docs: int = 512                 # synthetic documents
     log_every: int = 1
     latent_slots: str = ""            # "start,k,sweeps[,truncated]"
+    fsdp: bool = True                 # ZeRO-3 weights + owned-only optimizer state at world > 1
+    allow_fallback: bool = False      # PyTorch / library forms for geometries without a kernel
+    recurrence: int = 1               # core-block iterations per forward
+    sdc_every: int = 0                # checksum vote over the replicated state every N steps
+    metric_log: str = ""              # JSONL sink of the metric log
+    straggler_ms: int = 600_000
 
 
 def _coerce(value: str, current):
@@ -172,7 +184,14 @@ def run(preset: str, sets=(), *, device: str | None = None, resume: str | None =
     # data-parallel ranks read different documents; context-parallel ranks slice the same ones
     docs = synthetic_documents(cfg.vocab_size, opts.n_docs, seq_len,
                                opts.seed + (0 if opts.context_parallel else 1000 * rank))
-    metrics, mlog = native.obs.Metrics(), native.obs.MetricLog()
+    from . import supervisor
+    from .utils import flops as flops_util
+
+    sup = supervisor.RunSupervisor(world=world, rank=rank, tokens_per_step=opts.batch * seq_len * world,
+                                   microbatch_tokens=max(1, min(opts.micro_batch, opts.batch)) * seq_len,
+                                   sdc_period_steps=opts.sdc_every, straggler_timeout_ms=opts.straggler_ms,
+                                   metric_sink=(opts.metric_log if rank == 0 and opts.metric_log else None))
+    metrics, mlog = sup.metrics, sup.log
     spikes = native.obs.SpikeLog(10000, float(opts.spike_threshold), 8, 0)
 
     gpu = dev.type == "cuda"
@@ -181,7 +200,11 @@ def run(preset: str, sets=(), *, device: str | None = None, resume: str | None =
         from . import checkpoint, engine
 
         tr = engine.Trainer(cfg, tcfg, seed=opts.seed, device=dev, micro_batch=opts.micro_batch, fp8=opts.fp8,
-                            expert_parallel=opts.expert_parallel, context_parallel=opts.context_parallel)
+                            expert_parallel=opts.expert_parallel, context_parallel=opts.context_parallel,
+                            fsdp=opts.fsdp and not opts.context_parallel, allow_fallback=opts.allow_fallback,
+                            recurrence=opts.recurrence)
+        tr.time_phases = True
+        tr.collect_amax = bool(opts.fp8)
         if opts.latent_slots:
             tr.set_latent_slots(*[int(x) for x in opts.latent_slots.split(",")])
         ck = checkpoint.TrainerCheckpointer(opts.ckpt_dir or None)
@@ -199,18 +222,41 @@ def run(preset: str, sets=(), *, device: str | None = None, resume: str | None =
     step = tr.step_count if gpu else 0
     last_saved_step = step
     while step < opts.steps:
-        tokens, mask, cursor = feed.next()
-        if gpu:
-            if tr.cp:
-                tokens, mask = tr.cp_slice(tokens, mask)
-            res = tr.step(tokens, mask)
-            loss, gnorm, lr = float(res["loss"]), float(res["grad_norm"]), float(res["lr"])
-        else:
-            b = train.Batch(tokens=tokens, loss_mask=mask, positions=torch.arange(tokens.shape[1]))
-            o = train.train_step(params, opt_state, b, cfg, tcfg, step=step + 1, muon_transfer=True,
-                                 muon_all_matrices=True)
-            loss, gnorm, lr = float(o.loss.ce), float(o.grad_norm), float(o.lr)
+        t_step0 = time.perf_counter()
+        with sup.phase("data"):
+            tokens, mask, cursor = feed.next()
+        status = 0
+        with sup.phase("step"), sup.collective("train_step"):
+            if gpu:
+                if tr.cp:
+                    tokens, mask = tr.cp_slice(tokens, mask)
+                with sup.phase("launch"):
+                    res = tr.step(tokens, mask)
+                with sup.phase("readback"):
+                    # loss, gradient norm and the device status word in one device-to-host copy
+                    host = torch.stack([res["loss"].float().reshape(()), res["grad_norm"].float().reshape(()),
+                                        res["status"].float().reshape(())]).cpu()
+                loss, gnorm, lr, status = float(host[0]), float(host[1]), float(res["lr"]), int(host[2])
+            else:
+                b = train.Batch(tokens=tokens, loss_mask=mask, positions=torch.arange(tokens.shape[1]))
+                o = train.train_step(params, opt_state, b, cfg, tcfg, step=step + 1, muon_transfer=True,
+                                     muon_all_matrices=True)
+                loss, gnorm, lr = float(o.loss.ce), float(o.grad_norm), float(o.lr)
         step += 1
+        health = sup.after_step(step, (time.perf_counter() - t_step0) * 1e3, status)
+        if status:
+            # a bounded device wait ran out: the step ran on partial data. The controller has the
+            # health event (the replica is drained there); this process stops instead of
+            # checkpointing a corrupt state.
+            metrics.inc("health.watchdog_timeouts", {"preset": preset}, 1)
+            if gpu:
+                tr.raise_on_status(status)
+        if gpu and sup.sdc_due(step):
+            with sup.phase("sdc_probe"):
+                gone = sup.sdc_probe(step, supervisor.replicated_state(tr), group=tr.pg)
+            if gone:
+                raise RuntimeError(f"silent data corruption: replicas {gone} disagree with the majority "
+                                   f"at step {step} ({sup.last_sdc_error})")
         actions = [str(a) for a in spikes.observe(step, loss, f"batch-{step}", preset)]
         rolled_back = any("Rollback" in a or "SkipShard" in a for a in actions) and step > 8
         if rolled_back:
@@ -227,13 +273,27 @@ def run(preset: str, sets=(), *, device: str | None = None, resume: str | None =
         tps = tokens.numel() * world / max(now - t_last, 1e-9)
         t_last = now
         labels = {"preset": preset}
+        values = {"train.loss": loss, "train.grad_norm": gnorm, "train.lr": lr, "train.tokens_per_s": tps,
+                  "train.grad_accumulation": float(health["grad_accumulation"])}
+        if gpu:
+            values["train.mfu"] = flops_util.mfu(tps, cfg, tokens.shape[1] * (world if tr.cp else 1), world,
+                                                 recurrence=tr.recurrence,
+                                                 sweeps=(tr.latent_slots[2] if tr.latent_slots else 1))
+            if tr.phase_times:
+                values["comm.exposed_ms"] = tr.phase_times["sync_ms"] if world > 1 else 0.0
+                values["train.fwd_bwd_ms"] = tr.phase_times["fwd_bwd_ms"]
+                values["train.opt_ms"] = tr.phase_times["opt_ms"]
+            values.update(supervisor.moe_load_stats(tr.moe_load))
+            for name, t in tr.amax.items():
+                values[f"fp8.amax.{name}"] = float(t)
+            tr.amax = {}
+        sup.record(step, values, labels)
         metrics.set("loss", labels, loss)
-        metrics.set("grad_norm", labels, gnorm)
-        metrics.set("lr", labels, lr)
         metrics.inc("steps", labels, 1)
         mlog.record("loss", labels, step, loss)
         history.append({"step": step, "loss": loss, "grad_norm": gnorm, "lr": lr, "tokens_per_s": tps,
-                        "rolled_back": rolled_back})
+                        "rolled_back": rolled_back, "mfu": values.get("train.mfu"),
+                        "exposed_comm_ms": values.get("comm.exposed_ms")})
         if rank == 0 and opts.log_every and step % opts.log_every == 0:
             print(json.dumps(history[-1]), file=out, flush=True)
         if opts.ckpt_every and step % opts.ckpt_every == 0 and not rolled_back:
@@ -247,7 +307,9 @@ def run(preset: str, sets=(), *, device: str | None = None, resume: str | None =
     final_id = None
     if gpu and opts.ckpt_dir:
         final_id = ck.save_persistent(tr, wait=True, loader_state=json.loads(loader.state().to_json()))
+    sup.close()
     summary = {"preset": preset, "steps": step, "final_loss": history[-1]["loss"] if history else None,
+               "phase_ms": {k: round(v, 3) for k, v in sup.phase_ms.items()}, "live_replicas": sup.live(),
                "skipped_batches": skipped, "sequences_packed": n_seq, "checkpoint_id": final_id,
                "last_memory_checkpoint_step": last_saved_step, "world": world, "device": str(dev)}
     if rank == 0:

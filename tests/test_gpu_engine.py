@@ -354,3 +354,37 @@ def test_latched_wait_timeout_reaches_the_host_step():
         tr.step_from_host(host)
     assert err.value.code == 2
     assert tr.step_from_host(host)["status"] == 0          # the word was cleared
+
+
+def test_run_loop_wires_controller_tracer_metrics_and_sdc_probe(tmp_path, monkeypatch):
+    """The run loop on a GPU: tracer spans for the phases, MFU / exposed-communication /
+    checksum-vote wiring, a JSONL metric log; and a latched device wait-timeout reaches the
+    controller as a watchdog event before the loop stops."""
+    import io
+    import json
+
+    from prometheus_b200 import engine, run, supervisor
+    from prometheus_b200.ops import functional as ops
+    from prometheus_b200.ops._lib import call, ptr, stream_ptr
+
+    monkeypatch.setitem(run.PRESETS, "small_hybrid", small_hybrid)
+    sink = tmp_path / "m.jsonl"
+    sets = ["steps=4", "batch=2", "micro_batch=2", "seq_len=128", "n_docs=64", "sdc_every=2",
+            f"metric_log={sink}", "ckpt_every=0"]
+    res = run.run("small_hybrid", sets, device="cuda", out=io.StringIO())
+    hist = res["history"]
+    assert len(hist) == 4 and all(h["mfu"] is not None and h["mfu"] > 0 for h in hist)
+    assert hist[-1]["exposed_comm_ms"] == 0.0                 # one GPU: nothing to expose
+    assert {"data", "step", "launch", "readback", "sdc_probe"} <= set(res["summary"]["phase_ms"])
+    assert res["summary"]["live_replicas"] == ["r0"]
+    names = {json.loads(line)["name"] for line in sink.read_text().splitlines() if line.strip()}
+    assert {"train.loss", "train.mfu", "train.tokens_per_s", "comm.exposed_ms", "train.fwd_bwd_ms"} <= names
+    # device and host forms of the shard checksum agree
+    t = torch.randn(4097, device="cuda")
+    assert supervisor.checksum64(t) == supervisor.checksum64(t.cpu())
+    # a wait that runs out during a run: latched status -> health event -> the loop raises
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    call("pb_wait_flag_probe", ptr(flag), 1, 2_000_000, ptr(ops.status_word("cuda")), stream_ptr())
+    with pytest.raises(engine.DeviceWaitTimeout):
+        run.run("small_hybrid", sets[:5] + ["ckpt_every=0"], device="cuda", out=io.StringIO())
+    ops.status_word("cuda").zero_()
