@@ -120,7 +120,8 @@ __global__ void ep_dispatch_kernel(const bf16* __restrict__ src, long ld_src,
   const int e = ids[w];
   const int q = e / El;
   const int row = send_base[e] + (row_of_local[w] - local_off[e]);
-  const bool ok = row < max_rows;
+  const bool ok = row < max_rows && PB_BOUNDS_OK(PB_K_EP_DISPATCH, q, EP_MAX_RANKS) &&
+                  PB_BOUNDS_OK(PB_K_EP_DISPATCH, row, max_rows);
   if (lane == 0) {
     dest_rank[w] = q;
     dest_row[w] = ok ? row : -1;
@@ -247,6 +248,7 @@ __global__ void ep_combine_kernel(EpPeers ybuf, const int* __restrict__ dest_ran
       const size_t i = static_cast<size_t>(t) * k + s;
       const int row = dest_row[i];
       if (row < 0) continue;
+      if (!PB_BOUNDS_OK(PB_K_EP_COMBINE, dest_rank[i], EP_MAX_RANKS)) continue;
       const float g = gates ? gates[i] : 1.f;
       const bf16* y = static_cast<const bf16*>(ybuf.p[dest_rank[i]]) + static_cast<size_t>(row) * d + c;
       const uint4 raw = __ldcv(reinterpret_cast<const uint4*>(y));
@@ -384,3 +386,5 @@ PB_API int pb_ep_pull_scalar(void* const* dot_ptrs, int world, const int* dest_r
                                                          dest_row, div, n, out);
   return static_cast<int>(cudaGetLastError());
 }
+
+PB_DEFINE_BOUNDS_READER(ep)

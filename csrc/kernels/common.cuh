@@ -52,6 +52,54 @@ enum : int {
 };
 
 // ---------------------------------------------------------------------------
+// Debug bounds checks (the -DPB_DEBUG_BOUNDS build of the library).
+//
+// Indices that come from data (a target token, a routed row, a peer rank, a sequence position)
+// are checked before the access they feed: the first violation of a launch records
+// (kernel id, index, limit) in a device-side record and the access is skipped, so the kernel
+// finishes and the context stays usable. The host reads and clears the record with
+// pb_debug_bounds_read. In the normal build PB_BOUNDS_OK() is the constant `true`.
+// ---------------------------------------------------------------------------
+enum : int {
+  PB_K_SOFTCAP_CE = 1, PB_K_MOE_PERMUTE = 2, PB_K_MOE_COMBINE = 3, PB_K_MOE_COMBINE_BWD = 4,
+  PB_K_EP_DISPATCH = 5, PB_K_EP_COMBINE = 6, PB_K_ROPE = 7, PB_K_LATENT = 8, PB_K_EP_PULL = 9,
+};
+#ifdef PB_DEBUG_BOUNDS
+struct BoundsRecord {
+  int kernel, hits;
+  long long index, limit;
+};
+// one record per translation unit (no relocatable device code in this build); every file that
+// checks exports a reader with PB_DEFINE_BOUNDS_READER and the host polls them all
+static __device__ BoundsRecord g_bounds_record = {0, 0, 0, 0};
+static inline int bounds_read_tu(long long* out4) {
+  BoundsRecord r;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemcpyFromSymbol(&r, g_bounds_record, sizeof(r));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  out4[0] = r.kernel; out4[1] = r.hits; out4[2] = r.index; out4[3] = r.limit;
+  const BoundsRecord z = {0, 0, 0, 0};
+  return static_cast<int>(cudaMemcpyToSymbol(g_bounds_record, &z, sizeof(z)));
+}
+#define PB_DEFINE_BOUNDS_READER(tu) \
+  PB_API int pb_debug_bounds_read_##tu(long long* out4) { return ::pb::bounds_read_tu(out4); }
+__device__ __forceinline__ bool bounds_ok(int kernel, long long index, long long limit) {
+  if (index >= 0 && index < limit) return true;
+  if (atomicAdd(&g_bounds_record.hits, 1) == 0) {
+    g_bounds_record.kernel = kernel;
+    g_bounds_record.index = index;
+    g_bounds_record.limit = limit;
+  }
+  return false;
+}
+#define PB_BOUNDS_OK(kernel, index, limit) (::pb::bounds_ok((kernel), (index), (limit)))
+#else
+#define PB_BOUNDS_OK(kernel, index, limit) (true)
+#define PB_DEFINE_BOUNDS_READER(tu)
+#endif
+
+// ---------------------------------------------------------------------------
 // small math / packing helpers
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float bf16_to_f32(bf16 x) { return __bfloat162float(x); }

@@ -604,7 +604,8 @@ __global__ void __launch_bounds__(512) softcap_ce_kernel(bf16* __restrict__ logi
     }
   }
   s = block_sum(s, scratch);
-  const float xt = bf16_to_f32(p[tgt]);
+  // a target outside the vocabulary would read (and below, write) outside the row
+  const float xt = PB_BOUNDS_OK(PB_K_SOFTCAP_CE, tgt, V) ? bf16_to_f32(p[tgt]) : 0.f;
   const float ct = cap > 0.f ? cap * tanh_fast(xt * inv_cap) : xt;
   const float lse = __logf(s) + shift;
   if (threadIdx.x == 0) {
@@ -648,6 +649,20 @@ static inline int grid_for(long total, int block, int cap = 148 * 16) {
 }  // namespace pb
 
 using namespace pb;
+
+// 1 when the library was built with -DPB_DEBUG_BOUNDS.
+PB_API int pb_debug_bounds_enabled() {
+#ifdef PB_DEBUG_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// Readers of the per-file violation records: pb_debug_bounds_read_<file>(out4), out4 (host, four
+// 64-bit values) = {kernel id, violations since the last read, index, limit} of the first recorded
+// violation of that file's kernels; the call clears the record and synchronises the device.
+PB_DEFINE_BOUNDS_READER(elementwise)
 
 PB_API int pb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out,
                           void* rstd, int rows, int d, float eps, cudaStream_t st) {

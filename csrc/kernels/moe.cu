@@ -198,10 +198,11 @@ __global__ void place_kernel(const int* __restrict__ ids, int n_pairs, int pairs
 // dst[row_of[t, s]] = scale * src[t]; one warp per pair. d % 8 == 0.
 __global__ void permute_kernel(const bf16* __restrict__ src, const int* __restrict__ row_of,
                                const float* __restrict__ scale, int n_pairs, int k, int d, long ld_src,
-                               bf16* __restrict__ dst) {
+                               bf16* __restrict__ dst, long dst_rows) {
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= n_pairs) return;
   const bf16* s = src + static_cast<size_t>(w / k) * ld_src;
+  if (!PB_BOUNDS_OK(PB_K_MOE_PERMUTE, row_of[w], dst_rows)) return;
   bf16* o = dst + static_cast<size_t>(row_of[w]) * d;
   const float g = scale ? scale[w] : 1.f;
   for (int c = lane * 8; c < d; c += 256) {
@@ -233,7 +234,7 @@ __global__ void zero_pad_kernel(bf16* __restrict__ buf, int d, const int* __rest
 // out[t] = sum_s gate[t, s] * y[row_of[t, s]] (+ add[t]); one warp per token, fp32 accumulate.
 __global__ void combine_kernel(const bf16* __restrict__ y, const int* __restrict__ row_of,
                                const float* __restrict__ gates, const bf16* __restrict__ add, int T,
-                               int k, int d, bf16* __restrict__ out) {
+                               int k, int d, bf16* __restrict__ out, long y_rows) {
   const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (t >= T) return;
   for (int c = lane * 8; c < d; c += 256) {
@@ -247,6 +248,7 @@ __global__ void combine_kernel(const bf16* __restrict__ y, const int* __restrict
       const size_t i = static_cast<size_t>(t) * k + s;
       const float g = gates ? gates[i] : 1.f;
       float f[8];
+      if (!PB_BOUNDS_OK(PB_K_MOE_COMBINE, row_of[i], y_rows)) continue;
       unpack8(*reinterpret_cast<const bf16x8*>(y + static_cast<size_t>(row_of[i]) * d + c), f);
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = fmaf(g, f[j], acc[j]);
@@ -323,8 +325,11 @@ PB_API int pb_moe_permute(const void* src, const int* row_of, const float* scale
                           int d, long ld_src, void* dst, const int* expert_off, const int* totals,
                           int E, cudaStream_t st) {
   if (n_pairs <= 0 || d % 8 != 0) return PB_BAD_ARG;
+  // rows of dst: the worst case the placement sizes its buffers for
+  const long dst_rows = (static_cast<long>(n_pairs) + static_cast<long>(E > 0 ? E : 1) * 127 + 127) / 128 * 128;
   moe::permute_kernel<<<warps_grid(n_pairs, 256), 256, 0, st>>>(
-      static_cast<const bf16*>(src), row_of, scale, n_pairs, k, d, ld_src, static_cast<bf16*>(dst));
+      static_cast<const bf16*>(src), row_of, scale, n_pairs, k, d, ld_src, static_cast<bf16*>(dst),
+      dst_rows);
   if (expert_off != nullptr)
     moe::zero_pad_kernel<<<E, 256, 0, st>>>(static_cast<bf16*>(dst), d, expert_off, totals);
   return static_cast<int>(cudaGetLastError());
@@ -337,12 +342,13 @@ PB_API int pb_moe_zero_pad(void* buf, int d, const int* expert_off, const int* t
   return static_cast<int>(cudaGetLastError());
 }
 
+// y_rows: rows of y (the bound the debug build checks row_of against; 0 = unknown).
 PB_API int pb_moe_combine(const void* y, const int* row_of, const float* gates, const void* add,
-                          int T, int k, int d, void* out, cudaStream_t st) {
+                          int T, int k, int d, void* out, long y_rows, cudaStream_t st) {
   if (T <= 0 || d % 8 != 0) return PB_BAD_ARG;
   moe::combine_kernel<<<warps_grid(T, 256), 256, 0, st>>>(
       static_cast<const bf16*>(y), row_of, gates, static_cast<const bf16*>(add), T, k, d,
-      static_cast<bf16*>(out));
+      static_cast<bf16*>(out), y_rows > 0 ? y_rows : (1L << 62));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -353,3 +359,5 @@ PB_API int pb_moe_combine_bwd(const void* y, const void* dout, const int* row_of
       static_cast<const bf16*>(y), static_cast<const bf16*>(dout), row_of, n_pairs, k, d, dgates);
   return static_cast<int>(cudaGetLastError());
 }
+
+PB_DEFINE_BOUNDS_READER(moe)

@@ -92,26 +92,32 @@ def kernel_sources() -> list[Path]:
     return sorted(list((CSRC / "kernels").glob("*.cu")) + list((CSRC / "comm").glob("*.cu")))
 
 
-def build_kernels(verbose: bool = False, force: bool = False) -> Path:
-    """Compile every .cu for sm_100a and link libpb200_kernels.so."""
+def build_kernels(verbose: bool = False, force: bool = False, debug_bounds: bool = False) -> Path:
+    """Compile every .cu for sm_100a and link libpb200_kernels.so. ``debug_bounds`` builds
+    ``libpb200_kernels_dbg.so`` with ``-DPB_DEBUG_BOUNDS`` instead: indices that come from data
+    are checked in the kernels and a violation is recorded and skipped rather than executed
+    (``PB200_DEBUG_BOUNDS=1`` makes the package load that library)."""
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     nvcc = _nvcc()
+    tag = "dbg_" if debug_bounds else ""
+    extra = ["-DPB_DEBUG_BOUNDS"] if debug_bounds else []
+    target = LIB_DIR / "libpb200_kernels_dbg.so" if debug_bounds else KERNEL_LIB
     headers = list((CSRC / "kernels").glob("*.cuh")) + list((CSRC / "comm").glob("*.cuh"))
     srcs = kernel_sources()
     objs, jobs = [], []
     for src in srcs:
-        obj = OBJ_DIR / (src.parent.name + "_" + src.stem + ".o")
+        obj = OBJ_DIR / (tag + src.parent.name + "_" + src.stem + ".o")
         objs.append(obj)
         if force or _newer([src, *headers], obj):
-            jobs.append([nvcc, *NVCC_ARCH, *NVCC_FLAGS, "-I", CSRC / "kernels", "-I", CSRC / "comm",
-                         "-c", src, "-o", obj])
+            jobs.append([nvcc, *NVCC_ARCH, *NVCC_FLAGS, *extra, "-rdc=false", "-I", CSRC / "kernels", "-I",
+                         CSRC / "comm", "-c", src, "-o", obj])
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(lambda c: _run(c, verbose), jobs))
-    if force or jobs or _newer(objs, KERNEL_LIB):
-        _run([nvcc, *NVCC_ARCH, "-shared", "-o", KERNEL_LIB, *objs], verbose)
-    return KERNEL_LIB
+    if force or jobs or _newer(objs, target):
+        _run([nvcc, *NVCC_ARCH, "-shared", "-o", target, *objs], verbose)
+    return target
 
 
 def build_native(verbose: bool = False, force: bool = False, sanitize: str = "") -> Path | None:
@@ -158,12 +164,15 @@ def build_native(verbose: bool = False, force: bool = False, sanitize: str = "")
 
 def build_all(verbose: bool = False, force: bool = False) -> None:
     build_kernels(verbose, force)
+    build_kernels(verbose, force, debug_bounds=True)     # the self-checking variant rides along
     build_native(verbose, force)
 
 
 if __name__ == "__main__":
     san = [a.split("=", 1)[1] for a in sys.argv if a.startswith("--sanitize=")]
-    if san:
+    if "--debug-bounds" in sys.argv:
+        print("built:", build_kernels(verbose="-v" in sys.argv, force="--force" in sys.argv, debug_bounds=True))
+    elif san:
         print("built:", build_native(verbose="-v" in sys.argv, force="--force" in sys.argv, sanitize=san[0]))
     else:
         build_all(verbose="-v" in sys.argv, force="--force" in sys.argv)

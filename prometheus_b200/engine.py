@@ -197,6 +197,7 @@ class Trainer:
         # the kernels latch a status word when a bounded wait runs out; every
         # `check_status_every`-th step reads it back with the loss and raises (0: never)
         self.check_status_every = int(check_status_every)
+        self.debug_canaries = False        # check the symmetric buffers' guard zones after every step
         self.time_phases = False           # record CUDA events round the phases of every step
         self.phase_times: dict[str, float] = {}
         self.collect_amax = False          # keep the largest |final hidden| of the step (FP8 range probe)
@@ -629,6 +630,27 @@ class Trainer:
         return {"weights_bf16_bytes": lp, "landing_bytes": landing, "optimizer_state_bytes": state,
                 "gradient_bytes": 4 * (self.n_muon + self.n_adam + self.n_vec),
                 "weights_plus_state_bytes": lp + landing + state}
+
+    def symmetric_buffers(self) -> list:
+        """Every symmetric allocation this trainer's kernels let peers write into."""
+        bufs = [b for b in (getattr(self, "sym_grad", None), self.sym_lp) if b is not None]
+        for ctx in (self.ep_ctx, self.cp_ctx):
+            for attr in ("counts", "xbuf", "ybuf", "dotbuf", "xqbuf", "xsbuf", "arrbuf", "buf"):
+                b = getattr(ctx, attr, None) if ctx is not None else None
+                if b is not None and hasattr(b, "canaries_intact"):
+                    bufs.append(b)
+        if self.sym is not None:
+            bufs.append(self.sym.ctrl)
+        return bufs
+
+    def check_canaries(self) -> None:
+        """Raise if a peer (or this rank) wrote outside the usable range of any symmetric
+        buffer: the guard zones on both sides of each allocation must still hold their pattern.
+        Synchronises; meant for debugging runs and tests (``debug_canaries`` runs it every step)."""
+        for i, b in enumerate(self.symmetric_buffers()):
+            if not b.canaries_intact():
+                raise RuntimeError(f"rank {self.rank}: a canary zone of symmetric buffer {i} "
+                                   f"({b.nbytes} bytes) was overwritten")
 
     def close(self) -> None:
         """Release the symmetric-memory mappings (collective: every rank calls it)."""
@@ -1481,6 +1503,8 @@ class Trainer:
             self._phase_events = ev
         gnorm = self.gnorm_sq.sqrt()
         self.zero_grad()
+        if self.debug_canaries and self.sym is not None:
+            self.check_canaries()
         return {"loss": total, "grad_norm": gnorm, "lr": sched, "step": t,
                 "status": self.status_tensor()}
 

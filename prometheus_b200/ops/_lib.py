@@ -13,7 +13,12 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libpb200_kernels.so"
+import os
+
+# PB200_DEBUG_BOUNDS=1 loads the -DPB_DEBUG_BOUNDS build (python -m prometheus_b200._build
+# --debug-bounds): data-dependent indices are checked and a violation is recorded, not executed
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / (
+    "libpb200_kernels_dbg.so" if os.environ.get("PB200_DEBUG_BOUNDS", "0") == "1" else "libpb200_kernels.so")
 _lib = None
 
 P, I, L, F = c_void_p, c_int, c_long, c_float
@@ -67,7 +72,8 @@ _SIGS = {
     "pb_moe_sort_nblocks": [I, I],
     "pb_moe_sort": [P, I, I, I, P, P, P, P, P, P, I, P],
     "pb_moe_permute": [P, P, P, I, I, I, L, P, P, P, I, P],
-    "pb_moe_combine": [P, P, P, P, I, I, I, P, P],
+    "pb_moe_combine": [P, P, P, P, I, I, I, P, L, P],
+    "pb_debug_bounds_enabled": [],
     "pb_moe_zero_pad": [P, I, P, P, I, P],
     "pb_moe_combine_bwd": [P, P, P, I, I, I, P, P],
     "pb_fp8_quant_rows": [P, L, I, I, P, P, P],
@@ -144,6 +150,26 @@ def call(name: str, *args) -> None:
     launch_count += _LAUNCHES.get(name, 1)
     if rc != 0:
         raise RuntimeError(f"{name} failed with code {rc}")
+
+
+def debug_bounds_read() -> dict | None:
+    """The first bounds violation recorded since the last call (debug-bounds build only):
+    ``{"kernel", "hits", "index", "limit"}``, or None when there was none. Synchronises."""
+    lib = load()
+    if not lib.pb_debug_bounds_enabled():
+        raise RuntimeError("the loaded kernel library was built without PB_DEBUG_BOUNDS")
+    first = None
+    for tu in ("elementwise", "moe", "ep"):            # one record per source file that checks
+        fn = getattr(lib, f"pb_debug_bounds_read_{tu}")
+        fn.argtypes, fn.restype = [c_void_p], c_int
+        buf = (ctypes.c_longlong * 4)()
+        rc = fn(ctypes.cast(buf, c_void_p))
+        if rc != 0:
+            raise RuntimeError(f"pb_debug_bounds_read_{tu} failed with code {rc}")
+        if buf[1] and first is None:
+            first = {"file": tu, "kernel": int(buf[0]), "hits": int(buf[1]), "index": int(buf[2]),
+                     "limit": int(buf[3])}
+    return first
 
 
 def query(name: str, *args) -> int:

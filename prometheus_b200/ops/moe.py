@@ -81,7 +81,7 @@ def combine(y: Tensor, pl: Placement, gates: Tensor | None, T: int, add: Tensor 
     d = y.shape[1]
     out = torch.empty((T, d), dtype=BF16, device=y.device)
     call("pb_moe_combine", ptr(y), ptr(pl.row_of), ptr(gates), ptr(add), T, pl.top_k, d, ptr(out),
-         stream_ptr())
+         y.shape[0], stream_ptr())
     return out
 
 

@@ -50,7 +50,17 @@ class _RawCuda:
                                          "version": 3, "strides": None}
 
 
+GUARD_BYTES = 256          # canary zone on each side of every symmetric allocation
+GUARD_BYTE = 0xA5
+
+
 class SymmetricBuffer:
+    """One allocation per rank, mapped by every peer. The usable range is fenced by two
+    256-byte canary zones filled with a fixed pattern: peers write into this memory with raw
+    pointers, so an off-by-one of a peer kernel lands in a canary instead of in a neighbouring
+    allocation, and ``canaries_intact()`` (checked by the trainer after each collective phase
+    when ``debug_canaries`` is on, and by the tests) sees it."""
+
     def __init__(self, nbytes: int, group=None):
         self.group = group
         self.world = dist.get_world_size(group)
@@ -59,10 +69,11 @@ class SymmetricBuffer:
             raise ValueError(f"at most {MAX_RANKS} ranks share symmetric memory")
         self.nbytes = (int(nbytes) + 255) // 256 * 256
         local = ctypes.c_void_p()
-        call("pb_symm_alloc", self.nbytes, ctypes.byref(local))
-        self.local_ptr = local.value
+        call("pb_symm_alloc", self.nbytes + 2 * GUARD_BYTES, ctypes.byref(local))
+        self._base_ptr = local.value
+        self.local_ptr = local.value + GUARD_BYTES
         handle = ctypes.create_string_buffer(64)
-        call("pb_ipc_get_handle", self.local_ptr, ctypes.cast(handle, P))
+        call("pb_ipc_get_handle", self._base_ptr, ctypes.cast(handle, P))
         handles = [None] * self.world
         dist.all_gather_object(handles, bytes(handle.raw), group=group)
         self._opened = []
@@ -75,11 +86,21 @@ class SymmetricBuffer:
             buf = ctypes.create_string_buffer(h, 64)
             call("pb_ipc_open_handle", ctypes.cast(buf, P), ctypes.byref(out))
             self._opened.append(out.value)
-            addrs.append(out.value)
+            addrs.append(out.value + GUARD_BYTES)
         self.addrs = addrs
         self.ptrs = (ctypes.c_void_p * MAX_RANKS)(*(addrs + [None] * (MAX_RANKS - self.world)))
-        self._raw = _RawCuda(self.local_ptr, self.nbytes)
-        self.bytes = torch.as_tensor(self._raw, device=torch.device("cuda", torch.cuda.current_device()))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self._raw_all = _RawCuda(self._base_ptr, self.nbytes + 2 * GUARD_BYTES)
+        whole = torch.as_tensor(self._raw_all, device=dev)
+        self._guards = (whole[:GUARD_BYTES], whole[GUARD_BYTES + self.nbytes:])
+        for g in self._guards:
+            g.fill_(GUARD_BYTE)
+        self.bytes = whole[GUARD_BYTES:GUARD_BYTES + self.nbytes]
+
+    def canaries_intact(self) -> bool:
+        """True while nothing has written outside the usable range of this rank's allocation
+        (synchronises: it reads the guard zones back)."""
+        return all(bool((g == GUARD_BYTE).all()) for g in self._guards)
 
     def view(self, dtype, numel: int, byte_offset: int = 0) -> torch.Tensor:
         """Typed view of the local allocation."""
@@ -101,8 +122,9 @@ class SymmetricBuffer:
         """Free this rank's allocation. Only after every peer has unmapped it: freeing an
         exported allocation that an importer still has open is undefined."""
         self.bytes = None
+        self._guards = ()
         if self.local_ptr:
-            call("pb_symm_free", self.local_ptr)
+            call("pb_symm_free", self._base_ptr)
             self.local_ptr = None
 
     def close(self):

@@ -449,6 +449,7 @@ def fsdp_engine_main():
             tr = engine.Trainer(cfg, tcfg, params=params, device=dev, micro_batch=2, grad_sync="p2p",
                                 fsdp=(mode == "fsdp"), **kw)
             assert tr.fsdp == (mode == "fsdp")
+            tr.debug_canaries = True       # nothing may write outside a symmetric buffer's range
             losses = [tr.step(mine)["loss"].item() for _ in range(3)]
             torch.cuda.synchronize()
             tr.sym.check()

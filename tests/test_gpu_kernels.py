@@ -383,3 +383,54 @@ def test_delta_prep_bwd_kernel_matches_fp32_oracle():
     _close(dk, rk, 3e-2)
     _close(dv, rv, 3e-2)
     _close(db, rb, 3e-2)
+
+
+def test_debug_bounds_build_records_and_skips_a_bad_index():
+    """The -DPB_DEBUG_BOUNDS library: an index that comes from data and leaves its range is
+    recorded as (kernel, index, limit) and the access is skipped; the kernel finishes and the
+    context stays usable. Both injected indices stay inside real allocations, so nothing could
+    fault even without the check. Runs in a child interpreter (the library is chosen at load)."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    code = r'''
+import torch
+from prometheus_b200.ops import _lib, functional as ops
+from prometheus_b200.ops._lib import call, ptr, stream_ptr
+assert _lib.load().pb_debug_bounds_enabled() == 1
+assert _lib.debug_bounds_read() is None
+# 1. soft-cap CE: a target outside the vocabulary (row 0 of 4: the element it names is in row 1)
+V, rows = 1024, 4
+logits = torch.randn(rows, V, device="cuda").bfloat16()
+targets = torch.tensor([V + 3, 5, 6, 7], dtype=torch.int32, device="cuda")
+wt = torch.ones(rows, device="cuda")
+loss = torch.empty(rows, device="cuda")
+call("pb_softcap_ce", ptr(logits), ptr(targets), ptr(wt), ptr(loss), None, rows, V, 30.0, 0, stream_ptr())
+rec = _lib.debug_bounds_read()
+assert rec == {"file": "elementwise", "kernel": 1, "hits": 1, "index": V + 3, "limit": V}, rec
+assert torch.isfinite(loss).all()
+assert _lib.debug_bounds_read() is None                      # reading clears the record
+# 2. MoE combine: a routed row beyond the stated row count (but inside the buffer)
+T, k, d = 8, 2, 64
+y = torch.randn(256, d, device="cuda").bfloat16()
+row_of = torch.arange(T * k, dtype=torch.int32, device="cuda")
+row_of[5] = 200
+gates = torch.ones(T, k, device="cuda")
+out = torch.empty(T, d, device="cuda", dtype=torch.bfloat16)
+call("pb_moe_combine", ptr(y), ptr(row_of), ptr(gates), None, T, k, d, ptr(out), 128, stream_ptr())
+rec = _lib.debug_bounds_read()
+assert rec["file"] == "moe" and rec["kernel"] == 3 and rec["index"] == 200 and rec["limit"] == 128, rec
+want = y[4].float()                                          # token 2 = rows 4 and (skipped) 200
+assert torch.allclose(out[2].float(), want, atol=1e-2)
+# the checked library computes the same results as the normal one on valid inputs
+x = torch.randn(64, 256, device="cuda").bfloat16(); w = torch.ones(256, device="cuda")
+assert torch.isfinite(ops.rmsnorm(x, w).float()).all()
+print("DEBUG_BOUNDS_OK")
+'''
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PB200_DEBUG_BOUNDS="1", PYTHONPATH=str(root))
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300,
+                         cwd=root)
+    assert res.returncode == 0 and "DEBUG_BOUNDS_OK" in res.stdout, (res.stdout + res.stderr)[-3000:]
