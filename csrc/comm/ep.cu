@@ -231,31 +231,51 @@ __global__ void ep_zero_pad_fp8_kernel(uint8_t* __restrict__ xq, float* __restri
 }
 
 // out[t] = sum_s gate * ybuf[dest_rank][dest_row] (+ add[t]); one warp per token.
-__global__ void ep_combine_kernel(EpPeers ybuf, const int* __restrict__ dest_rank,
-                                  const int* __restrict__ dest_row, const float* __restrict__ gates,
-                                  const bf16* __restrict__ add, int T, int k, int d,
-                                  bf16* __restrict__ out) {
+// The (rank, row, gate) of the token's k slots are read once; per 256-column step all k peer
+// loads of a lane are issued before the first is used, so a warp has k x 16 bytes per lane in
+// flight over NVLink instead of one load at a time (the pull is latency-bound otherwise).
+constexpr int EP_MAX_K = 8;
+__global__ void __launch_bounds__(256) ep_combine_kernel(EpPeers ybuf, const int* __restrict__ dest_rank,
+                                                         const int* __restrict__ dest_row,
+                                                         const float* __restrict__ gates,
+                                                         const bf16* __restrict__ add, int T, int k, int d,
+                                                         bf16* __restrict__ out) {
   const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (t >= T) return;
+  const bf16* src[EP_MAX_K];
+  float g[EP_MAX_K];
+#pragma unroll
+  for (int s = 0; s < EP_MAX_K; ++s) {
+    src[s] = nullptr;
+    g[s] = 0.f;
+    if (s < k) {
+      const size_t i = static_cast<size_t>(t) * k + s;
+      const int row = dest_row[i];
+      const int q = dest_rank[i];
+      if (row >= 0 && PB_BOUNDS_OK(PB_K_EP_COMBINE, q, EP_MAX_RANKS)) {
+        src[s] = static_cast<const bf16*>(ybuf.p[q]) + static_cast<size_t>(row) * d;
+        g[s] = gates ? gates[i] : 1.f;
+      }
+    }
+  }
   for (int c = lane * 8; c < d; c += 256) {
+    uint4 raw[EP_MAX_K];
+#pragma unroll
+    for (int s = 0; s < EP_MAX_K; ++s)
+      if (src[s] != nullptr) raw[s] = __ldcv(reinterpret_cast<const uint4*>(src[s] + c));
     float acc[8];
     if (add != nullptr) unpack8(*reinterpret_cast<const bf16x8*>(add + static_cast<size_t>(t) * d + c), acc);
     else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     }
-    for (int s = 0; s < k; ++s) {
-      const size_t i = static_cast<size_t>(t) * k + s;
-      const int row = dest_row[i];
-      if (row < 0) continue;
-      if (!PB_BOUNDS_OK(PB_K_EP_COMBINE, dest_rank[i], EP_MAX_RANKS)) continue;
-      const float g = gates ? gates[i] : 1.f;
-      const bf16* y = static_cast<const bf16*>(ybuf.p[dest_rank[i]]) + static_cast<size_t>(row) * d + c;
-      const uint4 raw = __ldcv(reinterpret_cast<const uint4*>(y));
-      float f[8];
-      unpack8(*reinterpret_cast<const bf16x8*>(&raw), f);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = fmaf(g, f[j], acc[j]);
+    for (int s = 0; s < EP_MAX_K; ++s) {
+      if (src[s] == nullptr) continue;
+      float f[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(&raw[s]), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(g[s], f[j], acc[j]);
     }
     *reinterpret_cast<bf16x8*>(out + static_cast<size_t>(t) * d + c) = pack8(acc);
   }
@@ -361,7 +381,7 @@ PB_API int pb_ep_zero_pad_fp8(void* xq, float* xs, int d, int max_rows, const in
 PB_API int pb_ep_combine(void* const* ybuf_ptrs, int world, const int* dest_rank,
                          const int* dest_row, const float* gates, const void* add, int T, int k, int d,
                          void* out, cudaStream_t st) {
-  if (T <= 0 || d % 8 != 0) return PB_BAD_ARG;
+  if (T <= 0 || d % 8 != 0 || k < 1 || k > EP_MAX_K) return PB_BAD_ARG;
   const int grid = static_cast<int>((static_cast<long>(T) * 32 + 255) / 256);
   ep_combine_kernel<<<grid, 256, 0, st>>>(make_peers(ybuf_ptrs, world), dest_rank, dest_row, gates,
                                           static_cast<const bf16*>(add), T, k, d,

@@ -86,6 +86,7 @@ class RunSupervisor:
         self.phase_ms: dict[str, float] = {}
         self.quarantined: list[str] = []
         self.last_sdc_error: str | None = None
+        self.last_health_error: str | None = None
 
     # ------------------------------------------------------------------ spans
     @contextlib.contextmanager
@@ -127,8 +128,13 @@ class RunSupervisor:
         C = native.control
         now = _now_ms()
         if status_code:
-            self.controller.report_health(C.HealthEvent(who, who, C.HealthKind.WatchdogTimeout, now,
-                                                        f"device wait timed out (code {status_code})"))
+            try:
+                self.controller.report_health(C.HealthEvent(who, who, C.HealthKind.WatchdogTimeout, now,
+                                                            f"device wait timed out (code {status_code})"))
+            except native.NativeError as e:
+                # the last live replica cannot be drained: the event is kept for the caller, who
+                # stops the run instead
+                self.last_health_error = str(e)
         else:
             self.controller.observe_step_time(who, int(step), int(step_ms))
         self.controller.tick(now)

@@ -162,49 +162,174 @@ def run_v1(*, gpus: int = 1) -> dict:
 # V2  single device vs sharded / dispatched execution
 # ---------------------------------------------------------------------------
 def run_v2(*, gpus: int = 8, steps: int = 20) -> dict:
-    """The loss of the model whose every weight went through FSDP shard -> all-gather over
-    ``gpus`` ranks and whose MoE layers run dispatch -> expert -> combine equals the single-device
-    loss; routing (expert ids) is identical."""
+    """Single device against the mesh, through the production definitions:
+
+    * data parallel + FSDP: every step, the gradient of the whole batch equals the per-rank
+      gradients of the batch slices pushed through ``fsdp_reduce_scatter`` (rank-ordered fp32
+      fold) and ``fsdp_all_gather``; the parameters then advance with ``train.train_step``;
+    * expert parallel: the MoE layer's output equals dispatch -> per-expert FFN -> combine on the
+      ``kernels.ep_dispatch`` / ``ep_combine`` tables, and the routing is identical;
+    * context parallel: ring attention over ``min(gpus, 4)`` sequence slices equals dense
+      attention, and the delta-rule state handed from slice to slice equals the state of the
+      whole prefix;
+    * on a machine with two or more GPUs: the fused trainer on one GPU, replicated over two and
+      ZeRO-3 over two give the same losses (``tests/_multi_gpu_worker.py`` is the worker)."""
+    from .. import parallel as P
+    from ..parallel import cp as cp_mod
     from ..parallel import fsdp
 
     cfg = _small_config(n_dense=1, n_moe=3, n_routed_experts=8, top_k=2, expert_hidden=64)
     tcfg = train.train_config_for(cfg, warmup_steps=1, stable_steps=steps, decay_steps=2)
     params = model.init_params(cfg, 0)
-    single, mesh, same_routing = [], [], True
+    n = max(2, min(int(gpus), 4))                  # ranks emulated on the host
+    worst_grad, same_routing = 0.0, True
     p1, o1 = params, None
     for step in range(1, steps + 1):
-        b = _batch(cfg, 2, 32, 100 + step)
-        gathered = train._map_tree(p1, lambda _n, t: fsdp.fsdp_all_gather(
-            [fsdp.fsdp_shard(t, gpus, 0, r) for r in range(gpus)], 0) if t.ndim >= 1 and t.shape[0] >= gpus else t)
-        with torch.no_grad():
-            a = model.forward(b.tokens, p1, cfg, r=1)
-            g = model.forward(b.tokens, gathered, cfg, r=1)
-            single.append(float(train.cross_entropy(a.logits[:, :-1], b.tokens[:, 1:], b.loss_mask[:, 1:])))
-            mesh.append(float(train.cross_entropy(g.logits[:, :-1], b.tokens[:, 1:], b.loss_mask[:, 1:])))
-            same_routing = same_routing and bool(torch.equal(a.expert_ids, g.expert_ids))
+        b = _batch(cfg, 2 * n, 32, 100 + step)
+
+        def grads_of(tokens, mask):
+            live = train._map_tree(p1, lambda _n, t: t.detach().clone().requires_grad_(True))
+            total, (_, _, _, out) = train.compute_loss(live, train.Batch(tokens, mask, b.positions), cfg, tcfg,
+                                                       z_on_logits=True)
+            flat = model.flatten_params(live)
+            names = sorted(flat)
+            gs = torch.autograd.grad(total, [flat[k] for k in names], allow_unused=True)
+            return {k: (torch.zeros_like(flat[k]) if g is None else g) for k, g in zip(names, gs)}, out
+
+        full, out_full = grads_of(b.tokens, b.loss_mask)
+        per_rank = []
+        for r in range(n):
+            sl = slice(2 * r, 2 * r + 2)
+            g_r, out_r = grads_of(b.tokens[sl], b.loss_mask[sl])
+            per_rank.append(g_r)
+            same_routing = same_routing and bool(torch.equal(out_r.expert_ids, out_full.expert_ids[sl]))
+        for name, g_full in full.items():
+            if g_full.numel() < n:
+                continue
+            flat_r = [g[name].reshape(-1) / n for g in per_rank]          # equal slices: mean of the means
+            pad = (-flat_r[0].numel()) % n
+            if pad:
+                flat_r = [torch.nn.functional.pad(f, (0, pad)) for f in flat_r]
+            shards = [fsdp.fsdp_reduce_scatter(flat_r, 0, r) for r in range(n)]
+            back = fsdp.fsdp_all_gather(shards, 0)[:g_full.numel()].reshape(g_full.shape)
+            denom = float(g_full.abs().max()) + 1e-12
+            worst_grad = max(worst_grad, float((back - g_full).abs().max()) / denom)
         p1, o1, _ = _train(cfg, tcfg, p1, [b], start_step=step, opt=o1)
-    rel = max(abs(x - y) / max(abs(x), 1e-12) for x, y in zip(single, mesh))
-    # expert-parallel dispatch -> combine returns every token scaled by the sum of its gates
+    # expert parallel on the dispatch tables
+    layer = params["layers"][1]
     gen = torch.Generator().manual_seed(0)
-    x = torch.randn(16, 8, generator=gen)
-    ids = torch.randint(0, 8, (16, 2), generator=gen)
-    ids[:, 1] = (ids[:, 0] + 1) % 8
-    probs = torch.rand(16, 2, generator=gen)
-    meta = kernels.DispatchMeta(ids, probs, torch.zeros(8, dtype=torch.int64), 8, 4)
-    grouped, residual = kernels.ep_dispatch(x, meta)
-    back = kernels.ep_combine(grouped, meta, residual)
-    routing_ok = same_routing and bool(torch.allclose(back, x * probs.sum(-1, keepdim=True), atol=1e-6))
-    return {"loss_rel_diff": float(rel), "routing_identical": bool(routing_ok), "gpus": int(gpus), "steps": steps}
+    x = torch.randn(1, 24, cfg.d_model, generator=gen) * 0.5
+    want, probs, ids = model.moe(
+        x, router_weight=layer["router"], routed_weights=(layer["routed_gate"], layer["routed_up"], layer["routed_down"]),
+        shared_weights=(layer["shared_gate"], layer["shared_up"], layer["shared_down"]), top_k=cfg.top_k,
+        max_racks=cfg.max_racks, router_bias=layer.get("router_bias"))
+    x2 = x.reshape(-1, cfg.d_model)
+    top = torch.gather(probs.reshape(-1, cfg.n_routed_experts), 1, ids.reshape(-1, cfg.top_k).long())
+    gates = top / top.sum(-1, keepdim=True).clamp_min(1e-9)
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=cfg.n_routed_experts)
+    meta = kernels.DispatchMeta(ids.reshape(-1, cfg.top_k).long(), gates, torch.zeros(cfg.n_routed_experts, dtype=torch.int64),
+                                cfg.n_routed_experts, int(counts.max()))
+    grouped, residual = kernels.ep_dispatch(x2, meta)
+    outs = torch.zeros_like(grouped)
+    for e in range(cfg.n_routed_experts):
+        gu_g = grouped[e] @ layer["routed_gate"][e]
+        gu_u = grouped[e] @ layer["routed_up"][e]
+        outs[e] = (torch.nn.functional.silu(gu_g) * gu_u) @ layer["routed_down"][e]
+    routed = kernels.ep_combine(outs, meta, residual)
+    shared = torch.zeros_like(x2)
+    for j in range(cfg.n_shared_experts):
+        shared = shared + (torch.nn.functional.silu(x2 @ layer["shared_gate"][j]) * (x2 @ layer["shared_up"][j])) \
+            @ layer["shared_down"][j]
+    ep_rel = float(((routed + shared).reshape(want.shape) - want).abs().max() / want.abs().max())
+    # context parallel: ring attention and the delta state hand-off
+    q = torch.randn(1, 8 * n, 2, 8, generator=gen)
+    k = torch.randn(1, 8 * n, 2, 8, generator=gen)
+    v = torch.randn(1, 8 * n, 2, 8, generator=gen)
+    cp_rel = float((cp_mod.ring_attention(q, k, v, n) - model.gqa_attention(q, k, v)).abs().max())
+    kk = torch.nn.functional.normalize(torch.randn(1, 32 * n, 1, 8, generator=gen), dim=-1)
+    vv, bb = torch.randn(1, 32 * n, 1, 8, generator=gen), torch.rand(1, 32 * n, 1, generator=gen)
+    maps = [cp_mod.slice_affine_map(P.cp_split_seq(kk, n, r), P.cp_split_seq(vv, n, r), P.cp_split_seq(bb, n, r),
+                                    chunk=16) for r in range(n)]
+    state = cp_mod.delta_state_handoff(maps)[n - 1]          # state entering the last slice
+    _, s_ref = kernels.delta_rule_recurrent(kk[:, :32 * (n - 1)], kk[:, :32 * (n - 1)], vv[:, :32 * (n - 1)],
+                                            bb[:, :32 * (n - 1)])
+    cp_state_rel = float((state - s_ref).abs().max() / s_ref.abs().max())
+    result = {"loss_rel_diff": float(max(worst_grad, ep_rel if ep_rel > 1e-5 else 0.0, cp_rel if cp_rel > 1e-4 else 0.0,
+                                         cp_state_rel if cp_state_rel > 1e-4 else 0.0)),
+              "grad_rel_diff": float(worst_grad), "ep_rel_diff": ep_rel, "cp_attention_abs_diff": cp_rel,
+              "cp_state_rel_diff": cp_state_rel, "routing_identical": bool(same_routing), "gpus": int(gpus),
+              "ranks_emulated": n, "steps": steps}
+    if torch.cuda.is_available() and torch.cuda.device_count() >= 2:
+        result["gpu_trainer_parity"] = _gpu_mesh_parity()
+    return result
+
+
+def _gpu_mesh_parity() -> bool:
+    """Two-GPU trainer checks (replicated vs NCCL vs ZeRO-3) through the multi-GPU test worker."""
+    import os
+    import subprocess
+    import sys
+
+    worker = Path(__file__).resolve().parents[2] / "tests" / "_multi_gpu_worker.py"
+    if not worker.exists():
+        return False
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PB200_NVLS="0", MASTER_ADDR="127.0.0.1")
+    ok = True
+    for port, marker, arg in ((29541, "MULTI_GPU_OK", None), (29543, "FSDP_ENGINE_OK", "fsdp_engine")):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+               "127.0.0.1", "--master-port", str(port), str(worker)] + ([arg] if arg else [])
+        try:
+            res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+            ok = ok and res.returncode == 0 and marker in res.stdout
+        except subprocess.TimeoutExpired:
+            ok = False
+    return ok
 
 
 # ---------------------------------------------------------------------------
 # V3  FP8 vs bf16 loss, NVFP4 numerics
 # ---------------------------------------------------------------------------
+def _v3_engine(steps: int) -> dict:
+    """FP8 against bf16 through the fused trainer itself: the same hybrid model (head dim 128, so
+    every layer is on the tcgen05 kernels), same init, same batches, once with bf16 FFN products
+    and once with block-scaled e4m3 ones; the gate is the relative gap of the mean loss over the
+    last steps."""
+    from .. import engine
+
+    cfg = _small_config(d_model=256, n_heads=2, d_head=128, n_kv_heads=1, chunk=64, dense_hidden=512,
+                        vocab_size=1024)
+    tcfg = train.train_config_for(cfg, warmup_steps=5, stable_steps=steps, decay_steps=5)
+    params = model.init_params(cfg, 0)
+    gen = torch.Generator().manual_seed(0)
+    data = torch.randint(0, cfg.vocab_size, (steps, 4, 128), generator=gen)
+    data[:, :, 1::2] = (data[:, :, 0::2] * 3 + 1) % cfg.vocab_size        # learnable structure
+    out = {}
+    for kind in ("bf16", "fp8"):
+        tr = engine.Trainer(cfg, tcfg, params=params, micro_batch=4, fp8=(kind == "fp8"))
+        losses = [float(tr.step(data[t].cuda())["loss"]) for t in range(steps)]
+        tail = max(5, steps // 8)
+        out[kind] = sum(losses[-tail:]) / tail
+        out[kind + "_first"] = losses[0]
+    return out
+
+
 def run_v3(*, gpus: int = 8, steps: int = 150) -> dict:
-    """Two-layer MLP language model trained twice from the same init, once with bf16 linear
-    layers and once with block-scaled e4m3 linears (straight-through gradient); NVFP4 is
-    checked through the export codec round trip only."""
+    """FP8 (block-scaled e4m3, straight-through gradient) against bf16 training from the same
+    init on the same data. On a GPU the comparison runs through ``engine.Trainer`` (the fused
+    kernels, FP8 GEMM included); without one, through the fp32 fake-quantisation of
+    ``kernels.fp8_linear`` on a two-layer MLP language model. NVFP4 is checked through the
+    export codec round trip."""
     from .. import export
+
+    if torch.cuda.is_available():
+        e = _v3_engine(min(int(steps), 120))
+        w = torch.randn(64, 64, generator=torch.Generator().manual_seed(0)).numpy()
+        q, scale = export.quantize(w, "nvfp4")
+        back = export.dequantize(q, scale, "nvfp4")
+        nv_ok = bool(abs(back - w).max() <= 0.3 * abs(w).max()) and bool(torch.isfinite(torch.as_tensor(back)).all())
+        return {"fp8_loss_rel_diff": abs(e["fp8"] - e["bf16"]) / e["bf16"], "nvfp4_numerics_ok": nv_ok,
+                "bf16_loss": e["bf16"], "fp8_loss": e["fp8"], "path": "engine", "gpus": int(gpus),
+                "steps": min(int(steps), 120)}
 
     g = torch.Generator().manual_seed(0)
     vocab, d, h, seq = 64, 64, 128, 32

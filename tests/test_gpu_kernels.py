@@ -409,7 +409,9 @@ wt = torch.ones(rows, device="cuda")
 loss = torch.empty(rows, device="cuda")
 call("pb_softcap_ce", ptr(logits), ptr(targets), ptr(wt), ptr(loss), None, rows, V, 30.0, 0, stream_ptr())
 rec = _lib.debug_bounds_read()
-assert rec == {"file": "elementwise", "kernel": 1, "hits": 1, "index": V + 3, "limit": V}, rec
+assert rec["hits"] >= 1                                      # every thread of the row's block saw it
+assert {k: rec[k] for k in ("file", "kernel", "index", "limit")} == \
+    {"file": "elementwise", "kernel": 1, "index": V + 3, "limit": V}, rec
 assert torch.isfinite(loss).all()
 assert _lib.debug_bounds_read() is None                      # reading clears the record
 # 2. MoE combine: a routed row beyond the stated row count (but inside the buffer)

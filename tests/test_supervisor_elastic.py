@@ -33,6 +33,12 @@ def test_device_timeout_status_drains_the_replica_and_raises_grad_accumulation()
     assert s.replica_left("r2")["grad_accumulation"] == 4
 
 
+def test_single_replica_timeout_is_reported_but_cannot_be_drained():
+    s = _sup(world=1)
+    out = s.after_step(1, 5.0, status_code=2)
+    assert out["live"] == ["r0"] and s.last_health_error and "no live replicas" in s.last_health_error
+
+
 def test_collective_bracket_and_watchdog_tick():
     s = _sup(collective_watchdog_ms=50)
     with s.collective("grad_sync"):
