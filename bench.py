@@ -58,6 +58,8 @@ def parse_args():
                          "state for owned matrices only; dp = replicated weights, ownership-sharded optimizer")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the 16B mixture-of-experts measurement that follows the dense one")
+    ap.add_argument("--secondary-layers", type=int, default=0,
+                    help="debug only: run the secondary measurement on a model cut to this many layers")
     ap.add_argument("--no-exposed", action="store_true",
                     help="skip the extra timed steps without peer traffic (exposed_comm_ms reads 0)")
     ap.add_argument("--config", default="dense", choices=["dense", "latent", "moe16b", "longctx"],
@@ -201,11 +203,11 @@ def measure(args, config: str, world: int, rank: int, local_rank: int, dev, step
         trainer_kw = dict(fp8=True, expert_parallel=world > 1, ep_capacity_factor=1.5)
         fsdp = fsdp and args.parallelism == "fsdp"
         model_name = "moe-16B (28L d2048, 64 routed top-6 + 2 shared experts h1408, FP8 e4m3 block-scaled linears)"
-    if args.layers:
-        n_dense = 1 if config == "moe16b" else args.layers
-        cfg = model.with_overrides(cfg, n_layers=args.layers, n_dense=n_dense, n_moe=args.layers - n_dense,
-                                   n_linear_attn=args.layers * 3 // 4, n_mla=args.layers // 4,
-                                   core_block_layers=args.layers)
+    cut = args.layers or (args.secondary_layers if config != args.config else 0)
+    if cut:
+        n_dense = 1 if config == "moe16b" else cut
+        cfg = model.with_overrides(cfg, n_layers=cut, n_dense=n_dense, n_moe=cut - n_dense,
+                                   n_linear_attn=cut * 3 // 4, n_mla=cut // 4, core_block_layers=cut)
     need = estimate_rank_bytes(cfg, world, config == "moe16b" and world > 1, micro * seq_len)
     free_b, total_b = torch.cuda.mem_get_info(dev)
     if need > 0.92 * total_b:
@@ -311,7 +313,7 @@ def measure(args, config: str, world: int, rank: int, local_rank: int, dev, step
         "mfu_of": f"{peaks['source']} cuBLAS bf16 burst {peaks['bf16_tflops']:.0f} TFLOP/s per GPU",
         "exposed_comm_ms": (max(0.0, (ms - ms_noop_max) / steps) if ms_noop is not None else 0.0),
         "config": {
-            "model": model_name if not args.layers else f"DEBUG {args.layers} layers",
+            "model": model_name if not cut else f"DEBUG {cut} layers",
             "global_batch": B * (1 if cp else world), "seq_len": S, "parallelism": par,
             "micro_batch": micro, "grad_sync": args.grad_sync,
             "l2": f"per-step working set ({mem['weights_bf16_bytes'] / 2**30:.1f} GiB bf16 weights on "
@@ -363,7 +365,7 @@ def main() -> int:
                               "unavailable": main_res["skipped"]}), flush=True)
         return 0
     secondary = {}
-    if args.config == "dense" and not args.no_secondary and not args.layers:
+    if args.config == "dense" and not args.no_secondary and (not args.layers or args.secondary_layers):
         # the 16B FP8 mixture-of-experts configuration, expert parallel over the same ranks, in
         # the same run wherever it fits
         sec = measure(args, "moe16b", world, rank, local_rank, dev, max(2, min(args.steps, 3)), 3,
