@@ -36,7 +36,6 @@ struct GemmParams {
   int a_mn, b_mn;
   int tma_store;  // epilogue stages tiles in shared memory and stores them with TMA
   int m_group;    // row blocks per rasterisation group (all column blocks of a group before the next)
-  int debug;  // bit 1: skip the epilogue's global stores (timing experiments only)
   int* status;
   // Grouped modes (both null for the plain GEMM):
   //  mblk_group[m_blk]: rows of A / C are grouped (128-aligned) and row block m_blk multiplies
@@ -161,10 +160,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const CUtenso
       if (halves == 2) chunk(rb, 1);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0 && x0 < p.N && y0 < p.M && !(p.debug & 2)) {
-        if (p.debug & 16) tma_store_3d(tmC, buf, x0, y0, b);
-        else tma_store_3d_hint(tmC, buf, x0, y0, b, evict_first);
-      }
+      if (lane == 0 && x0 < p.N && y0 < p.M) tma_store_3d_hint(tmC, buf, x0, y0, b, evict_first);
       if (lane == 0) tma_store_commit();
     }
   } else
@@ -174,7 +170,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const CUtenso
     tmem_ld_32x32b_x32(t_addr + c, r);
     tmem_ld_wait();
     const int col0 = n0 + c;
-    if (row_ok && col0 < p.N && !(p.debug & 2)) {
+    if (row_ok && col0 < p.N) {
       float v[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
@@ -806,13 +802,13 @@ int gemm2_pairs_resident() { return num_sms() / 2; }
 
 using namespace pb;
 
-static int g_gemm_debug = 0;
-// Timing experiments: bit 0 forces the 128-wide tile, bit 1 drops the epilogue stores,
-// bit 2 selects the direct-store epilogue, bit 3 keeps every product on the single-CTA kernel,
-// bit 4 stores the output tiles without the evict-first L2 hint, bit 5 fixes the rasterisation
-// group at 8 row blocks.
-PB_API int pb_gemm_set_debug(int flags) {
-  g_gemm_debug = flags;
+static int g_gemm_variant = 0;
+// Kernel-variant selection (the default, 0, picks by shape): bit 0 forces the 128-wide tile,
+// bit 2 the direct-store epilogue, bit 3 keeps every product on the single-CTA kernel. Every
+// variant computes the same product; the tests run them against each other.
+PB_API int pb_gemm_set_variant(int flags) {
+  if (flags & ~(1 | 4 | 8)) return PB_BAD_ARG;
+  g_gemm_variant = flags;
   return 0;
 }
 
@@ -917,7 +913,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
   const int batch_a = (k_len != nullptr) ? 1 : batch;
   const int batch_b = (k_len != nullptr) ? 1 : (mblk_group != nullptr ? b_batch : batch);
   if (mblk_group != nullptr && (strideB % 8) != 0) return PB_BAD_ARG;
-  const bool bn256 = N > 128 && !(g_gemm_debug & 1);
+  const bool bn256 = N > 128 && !(g_gemm_variant & 1);
   // CTA pairs (256 x 256 tiles) for plain and batched products; grouped and all-gather modes and
   // limited grids stay on one CTA. A pair tile covers two single-CTA tiles, so the waves fill
   // alike, except when the last row block is at most half a pair tile: then the pair kernel
@@ -925,7 +921,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
   const long pair_tiles = static_cast<long>((M + 255) / 256) * ((N + 255) / 256) * batch;
   const int m_tail = M % 256;
   const bool pair = bn256 && mblk_group == nullptr && k_len == nullptr && g_ag == nullptr &&
-                    !(g_gemm_debug & 8) && M > 128 && (max_ctas <= 0 || max_ctas >= num_sms()) &&
+                    !(g_gemm_variant & 8) && M > 128 && (max_ctas <= 0 || max_ctas >= num_sms()) &&
                     (m_tail == 0 || m_tail > 128 || pair_tiles >= 2 * gemm2_pairs_resident());
   const int BN = bn256 ? 256 : 128;
   CUtensorMap tmA, tmB;
@@ -948,7 +944,6 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
   p.out_f32 = out_f32; p.d_f32 = d_f32;
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.status = status;
-  p.debug = g_gemm_debug;
   {
     // Rasterisation: the A panels of a group of row blocks stay in L2 while the B panels stream
     // past them once per group, so B is read from DRAM (row blocks / group) times. The group is
@@ -960,7 +955,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
     if (g > 64) g = 64;
     // a B that fits in L2 next to the group is not re-read whatever the group: keep the wave square
     if (static_cast<long>(N) * K * 2 <= (32L << 20)) g = 8;
-    p.m_group = (g_gemm_debug & 32) ? 8 : static_cast<int>(g);
+    p.m_group = static_cast<int>(g);
   }
   p.mblk_group = mblk_group; p.k_off = k_off; p.k_len = k_len;
   p.ag_ready = nullptr;
@@ -975,7 +970,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* D, int M
   const int cbytes = out_f32 ? 4 : 2;
   CUtensorMap tmC = tmA;
   p.tma_store = 0;
-  if (!(g_gemm_debug & 4) && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+  if (!(g_gemm_variant & 4) && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
       (ldc * cbytes) % 16 == 0 && (batch == 1 || (strideC * cbytes) % 16 == 0)) {
     if (make_tmap_3d(&tmC, C, cbytes, N, M, batch, ldc, strideC, out_f32 ? 32 : 64, 32) == 0)
       p.tma_store = 1;

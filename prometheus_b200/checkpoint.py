@@ -139,9 +139,23 @@ def capture(tr, *, rung: int = 0, data_mix_hash: str = ZERO_HASH, tokenizer_id: 
     if loader_state is not None:
         m.loader_state_json = json.dumps(loader_state, sort_keys=True, separators=(",", ":"))
     rng = [("torch.cpu", torch.get_rng_state())]
-    if torch.cuda.is_available():
+    if torch.cuda.is_available() and getattr(tr.device, "type", "cpu") == "cuda":
         rng.append(("torch.cuda", torch.cuda.get_rng_state(tr.device)))
     m.rng = [C.RngState(scope, int(tr.rank), hashlib.sha256(_bytes(s)).hexdigest()) for scope, s in rng]
+    # the generator state itself travels as a shard (``rng.<scope>.<rank>``) next to its hash in
+    # the manifest, so a run with stochastic parts resumes bit for bit
+    mine = [(scope, _bytes(st)) for scope, st in rng]
+    every = [mine]
+    if getattr(tr, "world", 1) > 1 and torch.distributed.is_available() and torch.distributed.is_initialized():
+        every = [None] * tr.world          # every rank's generators, so all ranks build one manifest
+        torch.distributed.all_gather_object(every, mine, group=getattr(tr, "pg", None))
+    for r, states in enumerate(every):
+        r = r if len(every) > 1 else int(tr.rank)
+        for scope, blob in states:
+            name = f"rng.{scope}.{r}"
+            weights.append(C.ShardBlob(name, r, blob))
+            wmeta.append(C.WeightMeta(name, r, [len(blob)], "int8", C.sha256_hex(blob), []))
+    m.weights = wmeta
     m.created_at = created_at or _dt.datetime.now(_dt.timezone.utc).strftime("%Y-%m-%dT%H:%M:%SZ")
     m.parent_checkpoint_id = parent
     m.git_commit = git_commit
@@ -206,6 +220,7 @@ def apply(tr, ckpt, *, strict_config: bool = True) -> dict[str, Any] | None:
         if getattr(tr, "fsdp", False):
             tr._fsdp_invalidate()
         tr.step_count = int(m.step)
+        _restore_rng(tr, wb)
         if getattr(tr, "sym", None) is not None:
             torch.cuda.synchronize()
             torch.distributed.barrier(tr.pg)

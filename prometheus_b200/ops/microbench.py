@@ -56,7 +56,7 @@ def bench_gemm(a):
     if a.debug:
         from ._lib import call
 
-        call("pb_gemm_set_debug", a.debug)
+        call("pb_gemm_set_variant", a.debug)
     x = torch.randn((a.k, a.m) if a.a_mn else (a.m, a.k), device="cuda").to(BF16)
     w = torch.randn((a.k, a.n) if a.b_mn else (a.n, a.k), device="cuda").to(BF16)
     ms = timeit(lambda: ops.gemm(x, w, a_mn=a.a_mn, b_mn=a.b_mn), a.iters)
@@ -83,11 +83,11 @@ def bench_gemm(a):
         hdl = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
         xr = x.t() if a.a_mn else x
         wr = w if a.b_mn else w.t()
-        runs = [("library", None)] + [(f"debug={v}", int(v)) for v in (a.variants or "0").split(",")]
+        runs = [("library", None)] + [(f"variant={v}", int(v)) for v in (a.variants or "0").split(",")]
         out["sustained"] = {}
         for name, flag in runs:
             if flag is not None:
-                call("pb_gemm_set_debug", flag)
+                call("pb_gemm_set_variant", flag)
             fn = (lambda: xr @ wr) if flag is None else (lambda: ops.gemm(x, w, a_mn=a.a_mn, b_mn=a.b_mn))
             for _ in range(5):
                 fn()
@@ -120,20 +120,20 @@ def bench_gemm(a):
             out["sustained"][name] = {"tflops": round(2.0 * a.m * a.n * a.k / ms_s / 1e9, 1),
                                       "sm_mhz_median": clk[len(clk) // 2] if clk else None,
                                       "watts_median": round(pw[len(pw) // 2], 1) if pw else None}
-        call("pb_gemm_set_debug", a.debug)
+        call("pb_gemm_set_variant", a.debug)
         return out
     if a.variants:
-        # the same product under several pb_gemm_set_debug values, timed in this process one after
+        # the same product under several pb_gemm_set_variant values, timed in this process one after
         # the other (same GPU, same clocks): 0 = default dispatch, 8 = single-CTA kernel only
         from ._lib import call
 
         out["variants_tflops"] = {}
         for rep in range(2):
             for flag in [int(v) for v in a.variants.split(",")]:
-                call("pb_gemm_set_debug", flag)
+                call("pb_gemm_set_variant", flag)
                 ms_v = timeit(lambda: ops.gemm(x, w, a_mn=a.a_mn, b_mn=a.b_mn), a.iters)
                 out["variants_tflops"].setdefault(str(flag), []).append(round(2.0 * a.m * a.n * a.k / ms_v / 1e9, 1))
-        call("pb_gemm_set_debug", a.debug)
+        call("pb_gemm_set_variant", a.debug)
     return out
 
 
@@ -343,10 +343,10 @@ def main():
     g.add_argument("--a-mn", action="store_true")
     g.add_argument("--b-mn", action="store_true")
     g.add_argument("--compare", action="store_true")
-    g.add_argument("--debug", type=int, default=0, help="timing experiments, see pb_gemm_set_debug")
+    g.add_argument("--debug", type=int, default=0, help="kernel variant bits, see pb_gemm_set_variant")
     g.add_argument("--sustain", type=float, default=0.0,
                    help="seconds per variant of back-to-back launches with NVML clock / power polling")
-    g.add_argument("--variants", default="", help="comma-separated pb_gemm_set_debug values to time side by side")
+    g.add_argument("--variants", default="", help="comma-separated pb_gemm_set_variant values to time side by side")
     d = sub.add_parser("delta")
     f = sub.add_parser("fp8")
     f.add_argument("--m", type=int, default=8192)

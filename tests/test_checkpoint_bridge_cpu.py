@@ -31,7 +31,7 @@ def test_capture_apply_roundtrip_and_manifest(tmp_path):
     ck = checkpoint.capture(a, loader_state={"epoch": 1, "cursor": 5}, created_at="2026-01-01T00:00:00Z")
     m = ck.manifest
     assert m.step == 7 and len(m.checkpoint_id) == 64
-    assert [w.name for w in m.weights] == list(a.weights)
+    assert [w.name for w in m.weights] == list(a.weights) + ["rng.torch.cpu.0"]   # generator bytes ride along
     assert {o.name: o.kind for o in m.optimizer} == {
         "layers.0.q.mom": "muon", "layers.0.o.mom": "muon", "embed.m": "adamw", "embed.v": "adamw",
         "final_norm.m": "adamw", "final_norm.v": "adamw"}
@@ -47,6 +47,13 @@ def test_capture_apply_roundtrip_and_manifest(tmp_path):
         assert torch.equal(getattr(a, name), getattr(b, name)), name
     assert b.step_count == 7
     assert torch.equal(b.muon_lp, a.muon_master.to(torch.bfloat16))
+    # the generator state itself is restored, not only its hash: the next draws repeat
+    torch.manual_seed(1234)
+    ck2 = checkpoint.capture(a)
+    first = torch.rand(4)
+    torch.manual_seed(99)
+    checkpoint.apply(b, ck2)
+    assert torch.equal(torch.rand(4), first)
     # in-memory path
     c = _fake_trainer(2)
     saver.save_memory(a)

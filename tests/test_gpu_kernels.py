@@ -89,10 +89,10 @@ def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn):
     ops.check_status("cuda")
     _close(c, ref)
     try:
-        call("pb_gemm_set_debug", 8)       # every product on the single-CTA kernel
+        call("pb_gemm_set_variant", 8)       # every product on the single-CTA kernel
         c1 = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
     finally:
-        call("pb_gemm_set_debug", 0)
+        call("pb_gemm_set_variant", 0)
     _close(c, c1, 2e-3)
 
 
