@@ -247,11 +247,23 @@ def apply(tr, ckpt, *, strict_config: bool = True) -> dict[str, Any] | None:
             if name in wb:
                 put(b, wb[name], name)
     tr.step_count = int(m.step)
+    _restore_rng(tr, wb)
     if getattr(tr, "sym", None) is not None:
         torch.cuda.synchronize()
         torch.distributed.barrier(tr.pg)
     raw = getattr(m, "loader_state_json", "")
     return json.loads(raw) if raw and raw != "{}" else None
+
+
+def _restore_rng(tr, blobs_by_name: dict) -> None:
+    """Put back the generator states saved as ``rng.<scope>.<rank>`` shards (this rank's own)."""
+    me = int(getattr(tr, "rank", 0))
+    raw = blobs_by_name.get(f"rng.torch.cpu.{me}")
+    if raw is not None:
+        torch.set_rng_state(torch.frombuffer(bytearray(raw), dtype=torch.uint8))
+    raw = blobs_by_name.get(f"rng.torch.cuda.{me}")
+    if raw is not None and torch.cuda.is_available() and getattr(tr.device, "type", "cpu") == "cuda":
+        torch.cuda.set_rng_state(torch.frombuffer(bytearray(raw), dtype=torch.uint8), tr.device)
 
 
 def broadcast_checkpoint(ckpt, error: str | None, tr):
