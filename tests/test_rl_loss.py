@@ -77,3 +77,40 @@ def test_tensor_logps_are_differentiable_and_pessimistic_min():
     plain = R.gspo_dapo_loss(g2, R.make_config(), 1).pg
     pess = R.gspo_dapo_loss(g2, R.make_config(pessimistic=True), 1).pg
     assert float(pess) < float(plain)      # negative advantage with a huge ratio is not clipped away
+
+
+def test_batched_loss_equals_the_sum_of_group_losses_and_drops_flat_groups():
+    """Many groups in one packed batch: per-group totals equal the one-group calls, a group with
+    equal rewards contributes exactly nothing, and the gradient flows to the trainer log-probs
+    of the kept samples only."""
+    g = torch.Generator().manual_seed(0)
+    cfg = R.make_config(loss_normalizer=3.0, overlong_cache=3, overlong_penalty=0.05, tis_clip=2.0)
+    groups, leaves = [], []
+    for gi in range(5):
+        samples = []
+        for si in range(4):
+            n = int(torch.randint(2, 7, (1,), generator=g))
+            new = (-torch.rand(n, generator=g)).requires_grad_(True)
+            old = new.detach() + 0.1 * torch.randn(n, generator=g)
+            lat_n = (-torch.rand(2, generator=g)).requires_grad_(True) if si % 2 else ()
+            lat_o = (lat_n.detach() + 0.05) if si % 2 else ()
+            reward = 1.0 if gi == 3 else float(torch.rand((), generator=g))      # group 3: all equal
+            samples.append(R.Sample(new, old, lat_n, lat_o, reward, n, 7 - (si % 3)))
+            leaves.append((gi, new))
+        groups.append(R.Group(f"p{gi}", tuple(samples)))
+    packed = R.pack_groups(groups, 7, cfg)
+    out = R.batched_loss(packed, cfg)
+    singles = [R.gspo_dapo_loss(grp, cfg, 7) for grp in groups]
+    for gi, s in enumerate(singles):
+        assert float(out["per_group"][gi]) == pytest.approx(float(s.total), rel=1e-5, abs=1e-7)
+    assert float(out["per_group"][3]) == 0.0 and int(out["n_kept"]) == 16
+    assert float(out["total"]) == pytest.approx(sum(float(s.total) for s in singles), rel=1e-5)
+    out["total"].backward()
+    for gi, leaf in leaves:
+        if gi == 3:
+            assert leaf.grad is None or float(leaf.grad.abs().sum()) == 0.0
+    assert any(float(leaf.grad.abs().sum()) > 0 for gi, leaf in leaves if gi != 3)
+    with pytest.raises(R.LossError):
+        R.pack_groups([], 7, cfg)
+    with pytest.raises(R.LossError):
+        R.pack_groups([R.Group("", groups[0].samples)], 7, cfg)
