@@ -4,10 +4,12 @@
 ``parallel/placement.py:86-226`` (``shard_map`` over a ``"pp"`` mesh axis, a scan over
 ticks, ``ppermute(i -> i+1)``, ``psum`` to replicate the outputs): every rank of the
 group is one stage, runs the same tick loop, receives its input activation from the
-previous stage and posts its output to the next with non-blocking ``isend``/``irecv`` so
-the transfer of tick ``t`` overlaps the compute of tick ``t+1``; the last stage's outputs
-are replicated with one broadcast per call. With no process group (or a group of one) it
-degenerates to the in-process runner.
+previous stage and posts its output to the next with non-blocking ``isend`` / ``irecv``: the
+receive of the next microbatch is posted before the current one is computed, so the transfer
+of tick ``t + 1`` overlaps the compute of tick ``t``. The last stage's outputs are replicated
+with a single broadcast of the stacked outputs; their shape travels once per call (it is the
+same for every microbatch), not once per microbatch. With no process group (or a group of
+one) it degenerates to the in-process runner.
 """
 from __future__ import annotations
 
@@ -50,15 +52,21 @@ def spmd_circular_pipeline(microbatches: Sequence[torch.Tensor], n_stages: int,
         pending = []
         nxt = dist.get_global_rank(group, stage + 1) if group is not None else stage + 1
         prv = dist.get_global_rank(group, stage - 1) if group is not None and stage > 0 else stage - 1
-        for tick in pipeline_forward_schedule(len(mbs), n_stages):
-            mb = tick[stage]
-            if mb is None:
-                continue
+        mine = [tick[stage] for tick in pipeline_forward_schedule(len(mbs), n_stages) if tick[stage] is not None]
+
+        def post_recv(mb):
+            buf = torch.empty_like(mbs[mb])
+            return dist.irecv(buf, src=prv, group=group), buf
+
+        inflight = post_recv(mine[0]) if stage > 0 and mine else None
+        for j, mb in enumerate(mine):
             if stage == 0:
                 x = mbs[mb]
             else:
-                x = torch.empty_like(mbs[mb])
-                dist.recv(x, src=prv, group=group)
+                req, x = inflight
+                # the next microbatch's receive is in flight while this one is computed
+                inflight = post_recv(mine[j + 1]) if j + 1 < len(mine) else None
+                req.wait()
             y = stage_fn(stage, x)
             if stage + 1 < n_stages:
                 pending.append((dist.isend(y.contiguous(), dst=nxt, group=group), y))
@@ -69,15 +77,15 @@ def spmd_circular_pipeline(microbatches: Sequence[torch.Tensor], n_stages: int,
     if not replicate:
         return tuple(outs)
     last = dist.get_global_rank(group, n_stages - 1) if group is not None else n_stages - 1
-    result = []
-    for m in range(len(mbs)):
-        meta = [None]
-        if rank == n_stages - 1:
-            meta = [(tuple(outs[m].shape), outs[m].dtype)]
-        dist.broadcast_object_list(meta, src=last, group=group)
-        shape, dtype = meta[0]
-        buf = outs[m] if rank == n_stages - 1 else torch.empty(shape, dtype=dtype,
-                                                                device=mbs[m].device)
-        dist.broadcast(buf, src=last, group=group)
-        result.append(buf)
-    return tuple(result)
+    # one shape message and one broadcast for all microbatches (they share shape and dtype)
+    meta = [None]
+    if rank == n_stages - 1:
+        meta = [(tuple(outs[0].shape), outs[0].dtype)]
+    dist.broadcast_object_list(meta, src=last, group=group)
+    shape, dtype = meta[0]
+    if rank == n_stages - 1:
+        stacked = torch.stack([o.contiguous() for o in outs])
+    else:
+        stacked = torch.empty((len(mbs), *shape), dtype=dtype, device=mbs[0].device)
+    dist.broadcast(stacked, src=last, group=group)
+    return tuple(stacked[m] for m in range(len(mbs)))

@@ -45,6 +45,8 @@ PACK_GOLDENS = [
     (1, [[10, 11, 12], [20, 21]], ("concat_eos", 4, False), [([10, 11, 12, 20], [1, 1, 1, 1], None), ([21, 0, 0, 0], [1, 0, 0, 0], None)]),
     (9, [[1, 2, 3, 4, 5, 6, 7]], ("concat_eos", 3, True), [([1, 2, 3], [1, 1, 1], None), ([4, 5, 6], [1, 1, 1], None), ([7, 0, 0], [1, 0, 0], None)]),
     (9, [[10, 11], [20]], ("document_mask", 4, True), [([10, 11, 9, 20], [1, 1, 1, 1], [0, 0, 0, 1])]),
+    # the last partial sequence of a document-mask packing is padded (mask 0, document id 0)
+    (9, [[10], [20, 21]], ("document_mask", 5, True), [([10, 9, 20, 21, 0], [1, 1, 1, 1, 0], [0, 0, 1, 1, 0])]),
 ]
 
 
@@ -53,6 +55,16 @@ def test_pack_goldens(eos, docs, cfg, expected):
     p = L.Packing("g", cfg[1], cfg[0], cfg[2], 0)
     got = L.pack(docs, p, eos)
     assert [(s.tokens, s.mask, s.document_ids) for s in got] == expected
+
+
+def test_pack_single_document_golden():
+    """One document per sequence: truncated to the length, documents shorter than
+    ``drop_short_below`` dropped, the rest padded; no document ids (single_document.json of the
+    reference's loader goldens)."""
+    p = L.Packing("golden-single-document", 4, "single_document", False, 0, drop_short_below=2)
+    got = L.pack([[1, 2], [3], [4, 5, 6, 7, 8]], p, 1)
+    assert [(s.tokens, s.mask, s.document_ids) for s in got] == \
+        [([1, 2, 0, 0], [1, 1, 0, 0], None), ([4, 5, 6, 7], [1, 1, 1, 1], None)]
 
 
 def test_pack_single_and_errors():
