@@ -50,6 +50,11 @@ _SIGS = {
     "pb_set_flag": [P, I, P],
     "pb_delta_scan_fwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
     "pb_delta_scan_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
+    "pb_delta_scan_fwd_seg": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
+    "pb_delta_scan_bwd_seg": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
+    "pb_delta_scan_summary_fwd": [P, P, P, P, P, I, I, I, I, I, P, P],
+    "pb_delta_scan_summary_bwd": [P, P, P, P, P, P, I, I, I, I, I, P, P],
+    "pb_delta_compose": [P, P, P, P, P, P, I, I, I, P],
     "pb_latent_gather": [P, P, I, I, I, I, I, P],
     "pb_latent_scatter": [P, P, I, I, I, I, I, P],
     "pb_latent_norm_scatter": [P, P, P, P, P, I, I, I, I, I, F, P],

@@ -162,20 +162,39 @@ def _from_chunks(x: Tensor, b: int, h: int, n: int) -> Tensor:
     return x.reshape(b, h, n, 64, d).permute(0, 2, 3, 1, 4).reshape(b, n * 64, h, d)
 
 
+def scan_segments(n_seq: int, n_chunks: int, ctas: int = 148) -> int:
+    """Segments per sequence for the state walk: one CTA walks one segment, so a batch with
+    fewer (batch, head) sequences than the GPU has SMs is cut until the CTAs fill it (powers of
+    two, at least four chunks per segment). 1 means the plain single-pass walk."""
+    seg = 1
+    while n_seq * seg * 2 <= ctas and n_chunks % (seg * 2) == 0 and n_chunks // (seg * 2) >= 4:
+        seg *= 2
+    return seg
+
+
 class _DeltaFusedFn(torch.autograd.Function):
     """Delta rule, head dim 128, chunk 64, sequence a multiple of 64, on three kernels: the
     chunk-local WY operands (``pb_delta_prep_fwd``), the forward state walk and the backward
     state walk. q, k, v are read in place from their ``[B, S, H, 128]`` layout and the output
-    is written in that layout. The chunk-local part of the backward is batched tcgen05 GEMMs."""
+    is written in that layout. The chunk-local part of the backward is batched tcgen05 GEMMs.
+
+    The walk is affine in the state, ``S_out = P S_in + R`` per run of chunks. When the batch
+    has too few sequences to fill the GPU (``scan_segments`` > 1), or when the sequence is
+    split over the ranks of a context-parallel group (``cp``), each segment's ``(P, R)`` comes
+    from a summary walk without outputs (two CTAs per segment), a small sequential kernel folds
+    them into the state entering every segment -- with the cross-rank hand-off in the middle
+    under ``cp`` -- and one segmented walk produces the outputs: two passes of 1 / n_seg the
+    length instead of one full-length pass. The backward does the same with ``P^T``."""
 
     @staticmethod
-    def forward(ctx, q, k, v, beta, s0):
+    def forward(ctx, q, k, v, beta, s0, cp=None, n_seg=None):
         from ._lib import call, ptr, stream_ptr
         from .functional import status_word
 
         b, s, h, d = q.shape
         n = s // 64
         g = b * h * n
+        bh = b * h
         dev = q.device
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         beta = beta.contiguous()
@@ -192,12 +211,35 @@ class _DeltaFusedFn(torch.autograd.Function):
         out = torch.empty_like(q)
         u = torch.empty_like(w)
         sb = torch.empty((g, 128, 128), dtype=bf, device=dev)
-        sfin = torch.empty((b * h, 128, 128), dtype=torch.float32, device=dev)
-        s0c = None if s0 is None else s0.reshape(b * h, d, d).float().contiguous()
-        call("pb_delta_scan_fwd", ptr(w), ptr(uhat), ptr(q), ptr(k), ptr(m), ptr(out), ptr(u),
-             ptr(sb), ptr(s0c), ptr(sfin), b * h, n, h, h * d, status, stream_ptr())
-        ctx.save_for_backward(q, k, v, beta, w, m, ap, t, u, sb)
+        sfin = torch.empty((bh, 128, 128), dtype=torch.float32, device=dev)
+        s0c = None if s0 is None else s0.reshape(bh, d, d).float().contiguous()
+        seg = int(n_seg) if n_seg else scan_segments(bh, n)
+        p_map = None
+        if seg == 1 and cp is None:
+            call("pb_delta_scan_fwd", ptr(w), ptr(uhat), ptr(q), ptr(k), ptr(m), ptr(out), ptr(u),
+                 ptr(sb), ptr(s0c), ptr(sfin), bh, n, h, h * d, status, stream_ptr())
+        else:
+            f32 = dict(dtype=torch.float32, device=dev)
+            r_map = torch.empty((bh * seg, 128, 128), **f32)
+            p_map = torch.empty_like(r_map)
+            call("pb_delta_scan_summary_fwd", ptr(w), ptr(uhat), ptr(k), ptr(r_map), ptr(p_map),
+                 bh, n, seg, h, h * d, status, stream_ptr())
+            if cp is not None:
+                # this rank's whole slice as one map, exchanged; what comes back is the state
+                # entering the slice
+                r_tot, p_tot = torch.empty((bh, 128, 128), **f32), torch.empty((bh, 128, 128), **f32)
+                call("pb_delta_compose", ptr(p_map), ptr(r_map), None, None, ptr(r_tot), ptr(p_tot),
+                     bh, seg, 0, stream_ptr())
+                s0c = cp.handoff(p_tot, r_tot).reshape(bh, d, d).contiguous()
+                ctx.p_tot = p_tot
+            s_in = torch.empty_like(r_map)
+            call("pb_delta_compose", ptr(p_map), ptr(r_map), ptr(s0c), ptr(s_in), ptr(sfin), None,
+                 bh, seg, 0, stream_ptr())
+            call("pb_delta_scan_fwd_seg", ptr(w), ptr(uhat), ptr(q), ptr(k), ptr(m), ptr(out), ptr(u),
+                 ptr(sb), ptr(s_in), None, bh, n, seg, h, h * d, status, stream_ptr())
+        ctx.save_for_backward(q, k, v, beta, w, m, ap, t, u, sb, p_map)
         ctx.has_s0 = s0 is not None
+        ctx.seg, ctx.cp = seg, cp
         return out, sfin.reshape(b, h, d, d)
 
     @staticmethod
@@ -205,18 +247,35 @@ class _DeltaFusedFn(torch.autograd.Function):
         from ._lib import call, ptr, stream_ptr
         from .functional import gemm, status_word
 
-        q, k, v, beta, w, m, ap, t, u, sb = ctx.saved_tensors
+        q, k, v, beta, w, m, ap, t, u, sb, p_map = ctx.saved_tensors
         b, s, h, d = q.shape
         n = s // 64
-        g = b * h * n
+        bh = b * h
         dev = q.device
+        seg, cp = ctx.seg, ctx.cp
         d_out = d_out.contiguous()
         ndu = torch.empty_like(u)          # the kernel writes -dU
         dsb = torch.empty_like(sb)
-        ds0 = torch.empty((b * h, 128, 128), dtype=torch.float32, device=dev)
-        dfin = None if d_sfin is None else d_sfin.reshape(b * h, d, d).float().contiguous()
-        call("pb_delta_scan_bwd", ptr(w), ptr(q), ptr(k), ptr(m), ptr(d_out), ptr(ndu), ptr(dsb),
-             ptr(dfin), ptr(ds0), b * h, n, h, h * d, ptr(status_word(dev)), stream_ptr())
+        ds0 = torch.empty((bh, 128, 128), dtype=torch.float32, device=dev)
+        dfin = None if d_sfin is None else d_sfin.reshape(bh, d, d).float().contiguous()
+        status = ptr(status_word(dev))
+        if p_map is None:
+            call("pb_delta_scan_bwd", ptr(w), ptr(q), ptr(k), ptr(m), ptr(d_out), ptr(ndu), ptr(dsb),
+                 ptr(dfin), ptr(ds0), bh, n, h, h * d, status, stream_ptr())
+        else:
+            g_map = torch.empty_like(p_map)
+            call("pb_delta_scan_summary_bwd", ptr(w), ptr(q), ptr(k), ptr(m), ptr(d_out), ptr(g_map),
+                 bh, n, seg, h, h * d, status, stream_ptr())
+            if cp is not None:
+                g_tot = torch.empty((bh, 128, 128), dtype=torch.float32, device=dev)
+                call("pb_delta_compose", ptr(p_map), ptr(g_map), None, None, ptr(g_tot), None,
+                     bh, seg, 1, stream_ptr())
+                dfin = cp.handoff(ctx.p_tot, g_tot, reverse=True).reshape(bh, d, d).contiguous()
+            g_in = torch.empty_like(p_map)
+            call("pb_delta_compose", ptr(p_map), ptr(g_map), ptr(dfin), ptr(g_in), ptr(ds0), None,
+                 bh, seg, 1, stream_ptr())
+            call("pb_delta_scan_bwd_seg", ptr(w), ptr(q), ptr(k), ptr(m), ptr(d_out), ptr(ndu),
+                 ptr(dsb), ptr(g_in), None, bh, n, seg, h, h * d, status, stream_ptr())
         doc = _to_chunks(d_out, n)
         d_w = gemm(ndu, sb)                                   # dW = -dU S^T
         d_m = gemm(doc, u)                                    # dM = dO U^T (masked in the kernel)
@@ -227,8 +286,8 @@ class _DeltaFusedFn(torch.autograd.Function):
         call("pb_delta_prep_bwd", ptr(q), ptr(k), ptr(v), ptr(beta),
              1 if beta.dtype == torch.float32 else 0, ptr(ap), ptr(t), ptr(d_w), ptr(ndu), ptr(d_m),
              ptr(d_qs), ptr(d_ks), ptr(d_q), ptr(d_k), ptr(d_v), ptr(d_beta), b, s, h, h * d,
-             ptr(status_word(dev)), 0, stream_ptr())
-        return d_q, d_k, d_v, d_beta, (ds0.reshape(b, h, d, d) if ctx.has_s0 else None)
+             status, 0, stream_ptr())
+        return (d_q, d_k, d_v, d_beta, (ds0.reshape(b, h, d, d) if ctx.has_s0 else None), None, None)
 
 
 def delta_prep_backward_ref(q, k, v, beta, ap, t, d_w, ndu, d_m, d_qs, d_ks):
@@ -256,9 +315,13 @@ def delta_prep_backward_ref(q, k, v, beta, ap, t, d_w, ndu, d_m, d_qs, d_ks):
             d_beta)
 
 
-def delta_rule_fused(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tensor | None):
+def delta_rule_fused(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tensor | None,
+                     cp=None, n_seg: int | None = None):
     """bf16, head dim 128, chunk 64 (sequences are zero-padded to a multiple of 64: padded
-    tokens have beta = 0 and k = 0, so they leave the state untouched)."""
+    tokens have beta = 0 and k = 0, so they leave the state untouched). ``cp``: a
+    ``parallel.cp.DeltaCpContext`` when the sequence is split over ranks (``state`` is then
+    ignored: the incoming state is what the earlier ranks hand over). ``n_seg`` overrides the
+    number of segments per sequence (default: ``scan_segments``)."""
     s = q.shape[1]
     pad = (-s) % 64
     if pad:
@@ -266,7 +329,7 @@ def delta_rule_fused(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, state: Tenso
         k = torch.nn.functional.pad(k, (0, 0, 0, 0, 0, pad))
         v = torch.nn.functional.pad(v, (0, 0, 0, 0, 0, pad))
         beta = torch.nn.functional.pad(beta, (0, 0, 0, pad))
-    out, sfin = _DeltaFusedFn.apply(q, k, v, beta, state)
+    out, sfin = _DeltaFusedFn.apply(q, k, v, beta, state, cp, n_seg)
     return (out[:, :s] if pad else out), sfin
 
 

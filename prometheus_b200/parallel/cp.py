@@ -262,57 +262,19 @@ class DeltaCpContext:
         self.buf.close()
 
 
-class _DeltaCpFn(torch.autograd.Function):
-    """Delta rule over a sequence split across the ranks of ``ctx_cp``.
-
-    forward   three local passes: (1) from the zero state -> R, (2) keys only, from the
-              identity -> P, (3) after the hand-off, from the true incoming state -> output.
-              Rank 0 keeps the output of pass (1).
-    backward  the local backward is affine in the gradient of the final state with the
-              transposed linear part P^T, so: (1) local backward with a zero final-state
-              gradient -> Q, (2) reverse hand-off of (P, Q), (3) local backward with the true
-              final-state gradient."""
-
-    @staticmethod
-    def forward(ctx, q, k, v, beta, cp):
-        from ..ops.delta import delta_rule_fused
-
-        b, s, h, d = q.shape
-        with torch.no_grad():
-            out0, r_map = delta_rule_fused(q, k, v, beta, None)
-            eye = torch.eye(d, device=q.device, dtype=torch.float32).expand(b, h, d, d).contiguous()
-            _, p_map = delta_rule_fused(q, k, torch.zeros_like(v), beta, eye)
-            s_in = cp.handoff(p_map, r_map).reshape(b, h, d, d)
-            if cp.rank == 0:
-                out = out0
-            else:
-                out, _ = delta_rule_fused(q, k, v, beta, s_in)
-        ctx.save_for_backward(q, k, v, beta, s_in, p_map)
-        ctx.cp = cp
-        return out
-
-    @staticmethod
-    def backward(ctx, d_out):
-        from ..ops.delta import delta_rule_fused
-
-        q, k, v, beta, s_in, p_map = ctx.saved_tensors
-        cp = ctx.cp
-        with torch.enable_grad():
-            leaves = [t.detach().requires_grad_() for t in (q, k, v, beta, s_in)]
-            out, s_fin = delta_rule_fused(*leaves)
-            (q_map,) = torch.autograd.grad(out, leaves[4], d_out, retain_graph=True)
-            g_fin = cp.handoff(p_map, q_map, reverse=True).reshape_as(s_fin)
-            dq, dk, dv, dbeta = torch.autograd.grad((out, s_fin), leaves[:4], (d_out, g_fin))
-        return dq, dk, dv, dbeta, None
-
-
 def delta_rule_cp(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, cp: DeltaCpContext) -> Tensor:
     """This rank's slice of the delta-rule output for a sequence split contiguously over the
     ranks of ``cp`` (rank order = sequence order). Shapes as ``ops.delta.delta_rule_fused``;
     head dim 128, slice length a multiple of 64."""
     if q.shape[0] * q.shape[2] != cp.bh:
         _err(f"context was built for batch*heads = {cp.bh}, got {q.shape[0] * q.shape[2]}")
-    return _DeltaCpFn.apply(q, k, v, beta, cp)
+    from ..ops.delta import delta_rule_fused
+
+    # two local passes: the slice's affine map (summary walk, no outputs), the hand-off of
+    # (P, R) between ranks, then the segmented walk from the true incoming state; backward the
+    # same with P^T (ops.delta._DeltaFusedFn)
+    out, _ = delta_rule_fused(q, k, v, beta, None, cp=cp)
+    return out
 
 
 # ---------------------------------------------------------------------------

@@ -340,6 +340,48 @@ def test_delta_rule_fused_matches_recurrence(B, S, H):
     ops.check_status("cuda")
 
 
+@pytest.mark.parametrize("B,S,H,seg", [(1, 1024, 2, 4), (1, 512, 1, 2), (2, 768, 1, 3)])
+def test_delta_rule_segmented_walk_equals_single_pass(B, S, H, seg):
+    """Sequences cut into segments (summary walk -> sequential fold -> segmented walk) against
+    the single-pass walk of the same kernels and against the fp32 per-token recurrence, forward,
+    final state and every gradient, with an initial state and a final-state gradient."""
+    from prometheus_b200 import kernels
+    from prometheus_b200.ops import functional as ops
+    from prometheus_b200.ops.delta import delta_rule_fused, scan_segments
+
+    assert scan_segments(16, 256) == 8 and scan_segments(128, 64) == 1 and scan_segments(1, 8) == 2
+    D = 128
+    q = torch.nn.functional.normalize(_r(B, S, H, D, seed=1).float(), dim=-1).to(BF16)
+    k = torch.nn.functional.normalize(_r(B, S, H, D, seed=2).float(), dim=-1).to(BF16)
+    v = _r(B, S, H, D, seed=3)
+    beta = torch.sigmoid(_r(B, S, H, seed=4).float()).to(BF16)
+    s0 = _r(B, H, D, D, seed=5, scale=0.05, dtype=torch.float32)
+    go = _r(B, S, H, D, seed=6)
+
+    def run(n_seg):
+        leaves = [t.clone().requires_grad_(True) for t in (q, k, v, beta)]
+        s0l = s0.clone().requires_grad_(True)
+        out, st = delta_rule_fused(*leaves, s0l, n_seg=n_seg)
+        (out.float() * go.float()).sum().add(st.sum() * 0.01).backward()
+        torch.cuda.synchronize()
+        ops.check_status("cuda")
+        return [out, st] + [t.grad for t in leaves] + [s0l.grad]
+
+    one, cut = run(1), run(seg)
+    for name, a, b in zip(("out", "state", "dq", "dk", "dv", "dbeta", "ds0"), cut, one):
+        err = (a.float() - b.float()).norm().item()
+        assert err <= 1.5e-2 * (b.float().norm().item() + 1e-6), (name, err)
+    ref_leaves = [t.float().clone().requires_grad_(True) for t in (q, k, v, beta)]
+    s0r = s0.clone().requires_grad_(True)
+    o_ref, s_ref = kernels.delta_rule_recurrent(*ref_leaves, s0r)
+    (o_ref * go.float()).sum().add(s_ref.sum() * 0.01).backward()
+    _close(cut[0], o_ref, 3e-2)
+    _close(cut[1], s_ref, 3e-2)
+    for a, b in zip(cut[2:6], ref_leaves):
+        _close(a, b.grad, 6e-2)
+    _close(cut[6], s0r.grad, 6e-2)
+
+
 def test_delta_prep_bwd_kernel_matches_fp32_oracle():
     """The fused chunk-local backward against the same algebra in batched fp32 PyTorch."""
     from prometheus_b200.ops import delta as dl
