@@ -118,6 +118,7 @@ class Trainer:
                  muon_weight_decay: float = 0.0, process_group=None, ce_chunk_rows: int = 4096,
                  grad_sync: str = "auto", expert_parallel: bool = False,
                  ep_capacity_factor: float = 2.0, fp8: bool = False, context_parallel: bool = False,
+                 cp_layout: str = "zigzag",
                  z_loss_mode: str = "layers_logits", router_bias_rule: str = "count",
                  allow_fallback: bool = False, fsdp: bool = False, nvls: bool | str = "auto",
                  recurrence: int = 1,
@@ -157,6 +158,13 @@ class Trainer:
         # weights and gradients are handled exactly as under data parallelism.
         self.cp = bool(context_parallel) and self.world > 1
         self.cp_ctx = None
+        # "zigzag": rank r holds half-slices r and 2 world - 1 - r of every sequence, so causal
+        # attention costs every rank the same and keys / values and their gradients move by this
+        # package's own peer-memory kernels; "contiguous": rank order = sequence order, softmax
+        # layers gather K / V through the collective library (the last rank does 1.9x the mean)
+        if cp_layout not in ("zigzag", "contiguous"):
+            raise ValueError("cp_layout must be 'zigzag' or 'contiguous'")
+        self.cp_zigzag = self.cp and cp_layout == "zigzag"
         has_mla = any(M.attention_kind(i, model_config) is M.AttentionKind.MLA for i in range(model_config.n_layers))
         if self.cp and (model_config.mtp_heads or has_mla or expert_parallel):
             raise ValueError("context parallelism supports the delta-rule + GQA hybrids without MTP heads, "
@@ -639,6 +647,8 @@ class Trainer:
                 b = getattr(ctx, attr, None) if ctx is not None else None
                 if b is not None and hasattr(b, "canaries_intact"):
                     bufs.append(b)
+        if self.cp_ctx is not None and hasattr(self.cp_ctx, "symmetric_buffers"):
+            bufs += self.cp_ctx.symmetric_buffers()
         if self.sym is not None:
             bufs.append(self.sym.ctrl)
         return bufs
@@ -672,7 +682,10 @@ class Trainer:
                 if b is not None and hasattr(b, "close"):
                     bufs.append(b)
         if self.cp_ctx is not None:
-            bufs.append(self.cp_ctx.sym.ctrl)
+            if hasattr(self.cp_ctx, "symmetric_buffers"):
+                bufs += self.cp_ctx.symmetric_buffers()
+            else:
+                bufs.append(self.cp_ctx.sym.ctrl)
         bufs.append(self.sym.ctrl)
         for b in bufs:
             b.close_peers()
@@ -900,7 +913,11 @@ class Trainer:
         q = ops.l2norm_(q, dh).view(B, S, nh, dh)
         k = ops.l2norm_(k, dh).view(B, S, nh, dh)
         v = v.view(B, S, nh, dh)
-        if self.cp:
+        if self.cp_zigzag:
+            from .parallel.cp import delta_rule_zigzag
+
+            o = delta_rule_zigzag(q, k, v, beta, self._zigzag_ctx(B * nh))
+        elif self.cp:
             from .parallel.cp import DeltaCpContext, delta_rule_cp
 
             if self.cp_ctx is None or self.cp_ctx.bh != B * nh:
@@ -1015,13 +1032,26 @@ class Trainer:
             acc = self._router_load.get(layer)
             self._router_load[layer] = stat if acc is None else acc + stat
 
+    def _zigzag_ctx(self, rows: int):
+        """The zig-zag context of this trainer (``rows`` = micro-batch x heads; the delta-rule
+        and the softmax layers of the hybrid share the head count)."""
+        from .parallel.cp import ZigzagCpContext
+
+        if self.cp_ctx is None or self.cp_ctx.rows != rows:
+            self.cp_ctx = ZigzagCpContext(rows, self.pg)
+        return self.cp_ctx
+
     def _gqa_layer(self, n: Tensor, i: int, B: int, S: int) -> Tensor:
         cfg = self.cfg
         nh, dh, nkv = M.head_geometry(cfg)
         pre = f"layers.{i}."
         q, k, v = ops.linear_multi(n, (self.p[pre + "q"], self.p[pre + "k"], self.p[pre + "v"]))
         pos = None
-        if self.cp:      # global positions of this rank's slice
+        if self.cp_zigzag:      # global positions of this rank's two half-slices
+            half = S // 2
+            ar = torch.arange(half, dtype=torch.int32, device=n.device)
+            pos = torch.cat([ar + self.rank * half, ar + (2 * self.world - 1 - self.rank) * half]).repeat(B)
+        elif self.cp:      # global positions of this rank's slice
             pos = (torch.arange(S, dtype=torch.int32, device=n.device) + self.rank * S).repeat(B)
         # rotary embedding over the projection outputs themselves (no copy)
         q = ops.rope2d_(q, nh, seq_len=S, pos=pos, base=cfg.rope_base).view(B, S, nh, dh)
@@ -1029,6 +1059,11 @@ class Trainer:
         v = v.view(B, S, nkv, dh)
         from .ops import attention
 
+        if self.cp_zigzag:
+            from .parallel.cp import zigzag_attention
+
+            o = zigzag_attention(q, k, v, self._zigzag_ctx(B * nh))
+            return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
         if self.cp:
             from .parallel.cp import cp_attention
 
@@ -1185,9 +1220,14 @@ class Trainer:
         if self.cp:
             # tokens / mask carry one extra column: the first token of the next rank's slice
             # (anything with mask 0 on the last rank), so every local position has its target
-            targets = tokens[:, 1:].reshape(-1).to(torch.int32)
-            wt = loss_mask.float()[:, 1:].reshape(-1) / denom
-            tokens, loss_mask = tokens[:, :-1].contiguous(), loss_mask[:, :-1].contiguous()
+            # (zig-zag: one such column after each of the two half-slices)
+            parts = 2 if self.cp_zigzag else 1
+            tk = tokens.reshape(tokens.shape[0], parts, -1)
+            mk = loss_mask.float().reshape(tokens.shape[0], parts, -1)
+            targets = tk[:, :, 1:].reshape(-1).to(torch.int32)
+            wt = mk[:, :, 1:].reshape(-1) / denom
+            tokens = tk[:, :, :-1].reshape(tokens.shape[0], -1).contiguous()
+            loss_mask = mk[:, :, :-1].reshape(tokens.shape[0], -1).contiguous()
             B, S = tokens.shape
             hid = self.forward_hidden(tokens)
         else:
@@ -1429,8 +1469,9 @@ class Trainer:
     def step(self, tokens: Tensor, loss_mask: Tensor | None = None) -> dict:
         """One optimizer step over a local batch (B_local, S) of token ids on the device.
         Returns device scalars: loss (mean CE over the global batch) and grad_norm.
-        Under context parallelism the batch is this rank's slice plus one column (see
-        ``cp_slice``): ``(B, S_local + 1)``."""
+        Under context parallelism the batch is what ``cp_slice`` returns: this rank's slice plus
+        one next-token column, ``(B, S_local + 1)``, or with the zig-zag split its two half-slices
+        each followed by that column, ``(B, S_local + 2)``."""
         self.step_count += 1
         t = self.step_count
         sched = T.wsd_lr(t, self.tcfg)
@@ -1444,7 +1485,10 @@ class Trainer:
         self.max_logits = {}
         if loss_mask is None:
             loss_mask = torch.ones_like(tokens, dtype=torch.float32)
-        denom = loss_mask[:, 1:].sum().float()
+        if self.cp_zigzag:     # two half-slices, each followed by its next-token column
+            denom = loss_mask.float().reshape(loss_mask.shape[0], 2, -1)[:, :, 1:].sum()
+        else:
+            denom = loss_mask[:, 1:].sum().float()
         if self.world > 1:
             import torch.distributed as dist
 
@@ -1586,16 +1630,21 @@ class Trainer:
 
     def cp_slice(self, tokens: Tensor, loss_mask: Tensor | None = None):
         """This rank's slice of full sequences ``(B, S)`` for a context-parallel step:
-        ``(tokens (B, S/world + 1), mask (B, S/world + 1))`` with the extra column holding the next
+        ``(tokens (B, S/world + 1), mask (B, S/world + 1))`` (zig-zag: two half-slices, each with
+        its extra column, ``S/world + 2`` in all) with the extra column holding the next
         slice's first token (mask 0 after the end of the sequence)."""
         B, S = tokens.shape
-        if S % self.world:
-            raise ValueError("sequence length must be divisible by the context-parallel size")
-        sl = S // self.world
-        lo = self.rank * sl
+        parts = 2 * self.world if self.cp_zigzag else self.world
+        if S % parts:
+            raise ValueError(f"sequence length must be divisible by {parts}")
+        sl = S // parts
         mask = torch.ones_like(tokens, dtype=torch.float32) if loss_mask is None else loss_mask.float()
-        tok = torch.cat([tokens, tokens[:, :1]], dim=1)[:, lo:lo + sl + 1]
-        m = torch.cat([mask, torch.zeros_like(mask[:, :1])], dim=1)[:, lo:lo + sl + 1]
+        tok_x = torch.cat([tokens, tokens[:, :1]], dim=1)
+        m_x = torch.cat([mask, torch.zeros_like(mask[:, :1])], dim=1)
+        # zig-zag: half-slices rank and 2 world - 1 - rank, each followed by its next token
+        starts = [self.rank * sl, (parts - 1 - self.rank) * sl] if self.cp_zigzag else [self.rank * sl]
+        tok = torch.cat([tok_x[:, lo:lo + sl + 1] for lo in starts], dim=1)
+        m = torch.cat([m_x[:, lo:lo + sl + 1] for lo in starts], dim=1)
         return tok.contiguous(), m.contiguous()
 
     def step_from_host(self, host_tokens: Tensor, host_mask: Tensor | None = None) -> dict:

@@ -64,6 +64,11 @@ _SIGS = {
     "pb_cp_buffer_bytes": [I],
     "pb_cp_push": [P, P, P, I, I, I, I, I, P],
     "pb_cp_compose": [P, P, P, I, I, I, I, I, L, P, P],
+    "pb_cp_chain_bytes": [I, I],
+    "pb_cp_push_chain": [P, P, P, I, I, I, I, I, I, P],
+    "pb_cp_wait_chain": [P, I, I, I, L, P, P],
+    "pb_cp_kv_gather": [P, P, P, I, L, P],
+    "pb_cp_kv_reduce": [P, P, P, I, I, L, L, P],
     "pb_attn_fwd": [P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P],
     "pb_attn_fwd_cp": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
     "pb_attn_bwd_cp": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],

@@ -267,8 +267,17 @@ def bench_elementwise(a):
     add("swiglu_bwd", 5 * rows * hid * 2, lambda: torch.autograd.grad(sy, gug, gs, retain_graph=True))
     S = 4096
     q = torch.randn(rows // S, S, 16, 128, device="cuda").to(BF16)
-    add("rope", 2 * rows * d * 2, lambda: ops.rope_(q, seq_len=S))
-    add("l2norm_fwd", 2 * rows * d * 2, lambda: ops.l2norm(q))
+    # the forms the trainer calls: written over the projection output, no copy
+    q2 = q.reshape(rows, d)
+    with torch.no_grad():
+        add("rope", 2 * rows * d * 2, lambda: ops.rope2d_(q2, 16, seq_len=S))
+        add("l2norm_fwd", 2 * rows * d * 2 + rows * 16 * 4, lambda: ops.l2norm_(q2, 128))
+        xn = torch.nn.functional.normalize(torch.randn(rows, d, device="cuda").view(rows, 16, 128), dim=-1)
+        xn = xn.reshape(rows, d).to(BF16)
+        inv = torch.ones(rows * 16, device="cuda")
+        gq = torch.randn(rows, d, device="cuda").to(BF16)
+        add("l2norm_bwd", 3 * rows * d * 2 + rows * 16 * 4,
+            lambda: call("pb_l2norm_bwd", ptr(gq), ptr(xn), ptr(inv), rows * 16, 128, stream_ptr()))
     add("fp8_quant_rows", rows * d * 3 + rows * d // 32, lambda: fp8.quantize_rows(x))
     wq = torch.randn(hid, d, device="cuda").to(BF16)
     add("fp8_quant_blocks", hid * d * 3, lambda: fp8.quantize_blocks(wq))

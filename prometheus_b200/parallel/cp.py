@@ -262,6 +262,265 @@ class DeltaCpContext:
         self.buf.close()
 
 
+# ---------------------------------------------------------------------------
+# zig-zag split: balanced causal attention, delta-rule chain over 2 x world half-slices
+# ---------------------------------------------------------------------------
+def zigzag_positions(world: int, rank: int) -> tuple[int, int]:
+    """Chain positions (half-slice indices) of rank ``rank``: ``rank`` and ``2 world - 1 - rank``.
+    Causal attention over half-slice ``p`` costs ``p + 1/2`` units, so every rank does
+    ``2 world`` units: no rank waits for the one that holds the end of the sequence."""
+    return rank, 2 * world - 1 - rank
+
+
+def zigzag_slice(x: Tensor, world: int, rank: int, *, axis: int = 1) -> Tensor:
+    """This rank's two half-slices of ``x`` along ``axis``, concatenated (near half first)."""
+    n = x.shape[axis]
+    if n % (2 * world):
+        _err(f"length {n} is not divisible by 2 x {world}")
+    half = n // (2 * world)
+    a, b = zigzag_positions(world, rank)
+    return torch.cat([x.narrow(axis, a * half, half), x.narrow(axis, b * half, half)], dim=axis)
+
+
+class ZigzagCpContext:
+    """Peer-memory state of one context-parallel group with the zig-zag split
+    (``csrc/comm/cp.cu``, chain mode): the delta-rule state chain over ``2 world`` half-slices,
+    the gather of keys / values and the return of their gradients. No collective-library call
+    on the layer path: peers' memory is read and written by this package's own kernels with
+    plain loads and stores, every wait is bounded and latches ``sym.status``.
+
+    ``rows`` = batch x delta heads of the model's delta-rule layers; the key / value buffers are
+    sized on first use. One sequence per micro-batch (``batch == 1``) for the attention part."""
+
+    SLOT_CHAIN = (2, 3)       # device-barrier slots: before a chain push, per direction
+    SLOT_KV, SLOT_DKV = 4, 5
+
+    def __init__(self, rows: int, group=None, wait_budget_s: float = 20.0):
+        from ..ops._lib import query
+        from .symm import SymmetricBuffer, SymmetricGroup
+
+        self.group = group
+        self.sym = SymmetricGroup(group, wait_budget_s)
+        self.world, self.rank = self.sym.world, self.sym.rank
+        self.rows = int(rows)
+        self.bh = 2 * self.rows                     # local maps: two half-slices per sequence
+        self.chain = SymmetricBuffer(query("pb_cp_chain_bytes", self.rows, self.world), group)
+        self.chain.bytes[:256].zero_()
+        self.chain_ptrs = self.chain.peer_ptrs(0)
+        self.epoch = [0, 0]
+        self.budget_ns = int(wait_budget_s * 1e9)
+        self._kv = None
+        self._parity = [0, 0]
+        torch.cuda.synchronize()
+        import torch.distributed as dist
+
+        dist.barrier(group)
+
+    # ------------------------------------------------------------- delta-rule chain
+    def _chain_view(self, direction: int, which: int) -> Tensor:
+        per = self.rows * 2 * self.world * 128 * 128
+        off = 256 + (direction * 2 + which) * per * 4
+        return self.chain.view(torch.float32, per, off)
+
+    def handoff(self, p: Tensor, r: Tensor, s0: Tensor | None = None, reverse: bool = False) -> Tensor:
+        """``p``, ``r``: fp32 ``(batch * 2 * heads, 128, 128)``, the maps of this rank's two
+        half-slices per sequence (local sequence index ``(b * 2 + half) * heads + h``). Returns,
+        in the same layout, the state entering each of them (forward) or the state gradient
+        leaving each of them (reverse)."""
+        from ..ops._lib import call, ptr, stream_ptr
+
+        d = 1 if reverse else 0
+        n = p.shape[0]
+        heads_batch = n // 2
+        if n != self.bh:
+            _err(f"context was built for {self.bh} local maps, got {n}")
+        p = p.reshape(n, 128, 128).float().contiguous()
+        r = r.reshape(n, 128, 128).float().contiguous()
+        self.sym.barrier(self.SLOT_CHAIN[d])        # peers have folded the previous maps
+        self.epoch[d] += 1
+        # batch and heads only fix the (b, half, h) -> (row, position) map; rows = batch * heads
+        call("pb_cp_push_chain", ptr(p), ptr(r), self.chain_ptrs, self.rank, self.world,
+             self._batch, heads_batch // self._batch, d, self.epoch[d], stream_ptr())
+        call("pb_cp_wait_chain", self.chain.local_ptr, self.world, d, self.epoch[d], self.budget_ns,
+             ptr(self.sym.status), stream_ptr())
+        w2 = 2 * self.world
+        p_all, r_all = self._chain_view(d, 0), self._chain_view(d, 1)
+        s_all = torch.empty((self.rows, w2, 128, 128), dtype=torch.float32, device=p.device)
+        call("pb_delta_compose", ptr(p_all), ptr(r_all), None, ptr(s_all), None, None, self.rows, w2,
+             d, stream_ptr())
+        a, b = zigzag_positions(self.world, self.rank)
+        heads = heads_batch // self._batch
+        mine = s_all[:, [a, b]].reshape(self._batch, heads, 2, 128, 128).permute(0, 2, 1, 3, 4)
+        return mine.reshape(n, 128, 128).contiguous()
+
+    _batch = 1
+
+    def set_batch(self, batch: int) -> None:
+        if self.rows % batch:
+            _err("rows must be batch x heads")
+        self._batch = int(batch)
+
+    # --------------------------------------------------------- keys / values
+    def _kv_buffers(self, half_elems: int, device):
+        from .symm import SymmetricBuffer
+
+        if self._kv is None or self._kv["half_elems"] != half_elems:
+            full = 2 * self.world * half_elems
+            stage = [SymmetricBuffer(4 * half_elems * 2, self.group) for _ in range(2)]
+            grads = [SymmetricBuffer(2 * full * 2, self.group) for _ in range(2)]
+            self._kv = {"half_elems": half_elems, "full": full, "stage": stage, "grads": grads}
+        return self._kv
+
+    def gather_kv(self, k: Tensor, v: Tensor):
+        """k, v: this rank's ``(1, 2 L, Hkv, D)`` bf16 (two half-slices). Returns natural-order
+        ``(1, 2 world L, Hkv, D)`` keys and values of the whole sequence, pulled from the peers."""
+        from ..ops._lib import call, ptr, stream_ptr
+
+        b, s2, hkv, d = k.shape
+        if b != 1:
+            _err("zig-zag attention takes one sequence per micro-batch")
+        half = s2 // 2
+        half_elems = half * hkv * d
+        kv = self._kv_buffers(half_elems, k.device)
+        par = self._parity[0]
+        self._parity[0] ^= 1
+        st = kv["stage"][par]
+        stage = st.view(torch.bfloat16, 4 * half_elems)
+        stage[:2 * half_elems].copy_(k.reshape(-1))
+        stage[2 * half_elems:].copy_(v.reshape(-1))
+        # one barrier per layer: the two staging buffers alternate, and a peer reaches the next
+        # barrier only after its pull of this buffer has finished on its stream
+        self.sym.barrier(self.SLOT_KV)
+        kf = torch.empty((1, 2 * self.world * half, hkv, d), dtype=k.dtype, device=k.device)
+        vf = torch.empty_like(kf)
+        call("pb_cp_kv_gather", st.peer_ptrs(0), ptr(kf), ptr(vf), self.world, half_elems * 2, stream_ptr())
+        return kf, vf
+
+    def grad_buffers(self, half_elems: int):
+        """This rank's ``[dK | dV]`` buffer of the current backward layer, as two bf16 views of
+        ``full`` elements each (written by the attention backward, read by the peers)."""
+        kv = self._kv
+        par = self._parity[1]
+        self._parity[1] ^= 1
+        g = kv["grads"][par]
+        full = kv["full"]
+        return g, g.view(torch.bfloat16, full), g.view(torch.bfloat16, full, full * 2)
+
+    def reduce_dkv(self, gbuf, half_elems: int, like: Tensor):
+        from ..ops._lib import call, ptr, stream_ptr
+
+        self.sym.barrier(self.SLOT_DKV)             # every rank's dK / dV are complete
+        dk = torch.empty_like(like)
+        dv = torch.empty_like(like)
+        call("pb_cp_kv_reduce", gbuf.peer_ptrs(0), ptr(dk), ptr(dv), self.rank, self.world, half_elems,
+             self._kv["full"], stream_ptr())
+        return dk, dv
+
+    def check(self) -> None:
+        self.sym.check()
+
+    def symmetric_buffers(self):
+        out = [self.chain, self.sym.ctrl]
+        if self._kv is not None:
+            out += self._kv["stage"] + self._kv["grads"]
+        return out
+
+    def close(self) -> None:
+        for b in self.symmetric_buffers()[:-1]:
+            b.close()
+
+
+class _ZigzagAttnFn(torch.autograd.Function):
+    """Causal GQA attention of a zig-zag split sequence. Forward: gather K / V (peer pulls), then
+    the offset kernel once per half-slice (queries at chain position ``p`` against keys
+    ``[0, (p + 1) L)``). Backward: the two backward calls leave dK / dV of the prefixes they saw
+    in this rank's symmetric buffer; every owner sums its rows over the ranks in rank order."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, zz):
+        from ..ops._lib import call, ptr, stream_ptr
+        from ..ops.functional import status_word
+
+        b, s2, hq, d = q.shape
+        hkv = k.shape[2]
+        L = s2 // 2
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        kf, vf = zz.gather_kv(k, v)
+        out = torch.empty_like(q)
+        lse2 = torch.empty((2, b, hq, L), dtype=torch.float32, device=q.device)
+        scale = 1.0 / math.sqrt(d)
+        status = ptr(status_word(q.device))
+        row_q, es = hq * d, q.element_size()
+        for half, pos in enumerate(zigzag_positions(zz.world, zz.rank)):
+            off = half * L * row_q * es
+            call("pb_attn_fwd_cp", q.data_ptr() + off, ptr(kf), ptr(vf), out.data_ptr() + off,
+                 ptr(lse2[half]), None, b, L, (pos + 1) * L, pos * L, hq, hkv, row_q, hkv * d, row_q,
+                 float(scale), status, stream_ptr())
+        ctx.save_for_backward(q, kf, vf, out, lse2)
+        ctx.zz, ctx.kshape = zz, tuple(k.shape)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        from ..ops._lib import call, ptr, stream_ptr
+        from ..ops.functional import status_word
+
+        q, kf, vf, out, lse2 = ctx.saved_tensors
+        zz = ctx.zz
+        b, s2, hq, d = q.shape
+        _, _, hkv, _ = ctx.kshape
+        L = s2 // 2
+        half_elems = L * hkv * d
+        d_out = d_out.contiguous()
+        dq = torch.empty_like(q)
+        delta = torch.empty_like(lse2)
+        scale = 1.0 / math.sqrt(d)
+        status = ptr(status_word(q.device))
+        row_q, es = hq * d, q.element_size()
+        gbuf, dk_full, dv_full = zz.grad_buffers(half_elems)
+        near, far = zigzag_positions(zz.world, zz.rank)
+        # far half first: it sees the longer prefix and writes every row the near half will add to
+        tmp_k = torch.empty((near + 1) * half_elems, dtype=q.dtype, device=q.device)
+        tmp_v = torch.empty_like(tmp_k)
+        for half, pos, dk, dv in ((1, far, dk_full, dv_full), (0, near, tmp_k, tmp_v)):
+            off = half * L * row_q * es
+            call("pb_attn_bwd_cp", q.data_ptr() + off, ptr(kf), ptr(vf), out.data_ptr() + off,
+                 d_out.data_ptr() + off, ptr(lse2[half]), ptr(delta[half]), dq.data_ptr() + off, ptr(dk),
+                 ptr(dv), b, L, (pos + 1) * L, pos * L, hq, hkv, row_q, hkv * d, row_q, float(scale),
+                 status, stream_ptr())
+        dk_full[:tmp_k.numel()] += tmp_k
+        dv_full[:tmp_v.numel()] += tmp_v
+        like = torch.empty(ctx.kshape, dtype=q.dtype, device=q.device)
+        dk, dv = zz.reduce_dkv(gbuf, half_elems, like)
+        return dq, dk, dv, None
+
+
+def zigzag_attention(q: Tensor, k: Tensor, v: Tensor, zz: ZigzagCpContext) -> Tensor:
+    """Causal GQA attention for sequences split zig-zag over ``zz``'s ranks. q ``(B, 2 L, Hq, 128)``,
+    k / v ``(B, 2 L, Hkv, 128)`` bf16: this rank's two half-slices, near one first; ``L`` a
+    multiple of 256."""
+    if q.shape[1] % 512:
+        _err("zig-zag attention needs half-slices that are multiples of 256 tokens")
+    if q.shape[0] == 1:
+        return _ZigzagAttnFn.apply(q, k, v, zz)
+    # the peer buffers hold one sequence: a micro-batch of several goes through one at a time
+    return torch.cat([_ZigzagAttnFn.apply(q[b:b + 1], k[b:b + 1], v[b:b + 1], zz)
+                      for b in range(q.shape[0])], dim=0)
+
+
+def delta_rule_zigzag(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, zz: ZigzagCpContext) -> Tensor:
+    """Delta rule over a zig-zag split sequence: the two half-slices of every sequence are run
+    as separate batch entries whose incoming states come from the fold over the ``2 world``
+    chain positions. Shapes as ``delta_rule_cp`` (local length = two half-slices)."""
+    from ..ops.delta import delta_rule_fused
+
+    b, s2, h, d = q.shape
+    zz.set_batch(b)
+    halves = [t.reshape(b * 2, s2 // 2, *t.shape[2:]) for t in (q, k, v, beta)]
+    out, _ = delta_rule_fused(*halves, None, cp=zz)
+    return out.reshape(b, s2, h, d)
+
+
 def delta_rule_cp(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, cp: DeltaCpContext) -> Tensor:
     """This rank's slice of the delta-rule output for a sequence split contiguously over the
     ranks of ``cp`` (rank order = sequence order). Shapes as ``ops.delta.delta_rule_fused``;

@@ -315,6 +315,70 @@ def cp_delta_main():
         print("CP_DELTA_OK")
 
 
+
+def cp_zigzag_main():
+    """Zig-zag split (rank r holds half-slices r and 2 world - 1 - r): the delta rule over the
+    2 x world chain and causal GQA attention with peer-pulled keys / values, forward and all
+    gradients, against the same layers on the whole sequence on one GPU; twice (buffers alternate)."""
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    from datetime import timedelta
+
+    dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=90))
+    from prometheus_b200.ops import functional as ops
+    from prometheus_b200.ops.attention import causal_gqa
+    from prometheus_b200.ops.delta import delta_rule_fused
+    from prometheus_b200.parallel.cp import (ZigzagCpContext, delta_rule_zigzag, zigzag_attention,
+                                             zigzag_slice)
+
+    B, H, HKV, D = 2, 4, 2, 128
+    S = 512 * world
+    gen = torch.Generator(device=dev).manual_seed(11)
+    q = torch.nn.functional.normalize(torch.randn(B, S, H, D, device=dev, generator=gen), dim=-1).bfloat16()
+    k = torch.nn.functional.normalize(torch.randn(B, S, H, D, device=dev, generator=gen), dim=-1).bfloat16()
+    v = torch.randn(B, S, H, D, device=dev, generator=gen).bfloat16()
+    beta = torch.sigmoid(torch.randn(B, S, H, device=dev, generator=gen)).float()
+    go = torch.randn(B, S, H, D, device=dev, generator=gen).bfloat16()
+    ka = torch.randn(B, S, HKV, D, device=dev, generator=gen).bfloat16()
+    va = torch.randn(B, S, HKV, D, device=dev, generator=gen).bfloat16()
+    zz = ZigzagCpContext(B * H, wait_budget_s=10.0)
+
+    def close(a, b, tol, what):
+        err = (a.float() - b.float()).norm().item()
+        sc = b.float().norm().item() + 1e-6
+        assert err <= tol * sc, f"rank {rank} {what}: err {err:.4g} norm {sc:.4g}"
+
+    sl = lambda t: zigzag_slice(t, world, rank)          # noqa: E731
+    for it in range(2):
+        mine = [sl(t).clone().requires_grad_(True) for t in (q, k, v, beta)]
+        out = delta_rule_zigzag(*mine, zz)
+        (out.float() * sl(go).float()).sum().backward()
+        am = [sl(t).clone().requires_grad_(True) for t in (q, ka, va)]
+        ao = zigzag_attention(*am, zz)
+        (ao.float() * sl(go).float()).sum().backward()
+    torch.cuda.synchronize()
+    zz.check()
+    ops.check_status(dev)
+    full = [t.clone().requires_grad_(True) for t in (q, k, v, beta)]
+    ref, _ = delta_rule_fused(*full, None)
+    (ref.float() * go.float()).sum().backward()
+    close(out, sl(ref), 2e-2, "delta out")
+    for name, m, f in zip("qkvb", mine, full):
+        close(m.grad, sl(f.grad), 4e-2, "delta d" + name)
+    af = [t.clone().requires_grad_(True) for t in (q, ka, va)]
+    aref = causal_gqa(*af)
+    (aref.float() * go.float()).sum().backward()
+    close(ao, sl(aref), 2e-2, "attention out")
+    for name, m, f in zip("qkv", am, af):
+        close(m.grad, sl(f.grad), 3e-2, "attention d" + name)
+    for b in zz.symmetric_buffers():
+        assert b.canaries_intact()
+    dist.barrier()
+    if rank == 0:
+        print("CP_ZIGZAG_OK")
+
+
 def ag_gemm_main():
     """Row-sharded weight gathered inside the GEMM kernel == matmul with the full weight."""
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -397,25 +461,30 @@ def cp_engine_main():
     tokens = torch.randint(0, cfg.vocab_size, (2, S), generator=torch.Generator().manual_seed(3)).to(dev)
     mask = torch.ones(2, S, device=dev)
     mask[:, 5:9] = 0
-    ref = engine.Trainer(cfg, tcfg, params=params, device=dev, micro_batch=2, process_group=solo_groups[rank])
-    cp = engine.Trainer(cfg, tcfg, params=params, device=dev, micro_batch=2, context_parallel=True)
-    assert ref.world == 1 and cp.world == world and cp.cp
-    for step in range(2):
-        want = ref.step(tokens, mask)
-        got = cp.step(*cp.cp_slice(tokens, mask))
-        torch.cuda.synchronize()
-        ops.check_status(dev)
-        lw, lg = want["loss"].item(), got["loss"].item()
-        nw, ng = want["grad_norm"].item(), got["grad_norm"].item()
-        assert abs(lw - lg) < 2e-2 * abs(lw), f"rank {rank} step {step}: loss {lg} vs {lw}"
-        assert abs(nw - ng) < 6e-2 * nw, f"rank {rank} step {step}: grad norm {ng} vs {nw}"
-    a = model.flatten_params(ref.export_tree())
-    b = model.flatten_params(cp.export_tree())
-    start = model.flatten_params(params)
-    for name in ("layers.0.W_q", "layers.3.W_k", "layers.1.ffn_gate", "embed"):
-        da, db = (a[name] - start[name]).float().flatten(), (b[name] - start[name]).float().flatten()
-        cos = torch.nn.functional.cosine_similarity(da, db, dim=0).item()
-        assert cos > 0.9, f"{name}: update cosine {cos:.3f}"
+    for layout in ("zigzag", "contiguous"):
+        ref = engine.Trainer(cfg, tcfg, params=params, device=dev, micro_batch=2, process_group=solo_groups[rank])
+        cp = engine.Trainer(cfg, tcfg, params=params, device=dev, micro_batch=2, context_parallel=True,
+                            cp_layout=layout)
+        assert ref.world == 1 and cp.world == world and cp.cp and cp.cp_zigzag == (layout == "zigzag")
+        for step in range(2):
+            want = ref.step(tokens, mask)
+            got = cp.step(*cp.cp_slice(tokens, mask))
+            torch.cuda.synchronize()
+            ops.check_status(dev)
+            cp.cp_ctx.check()
+            lw, lg = want["loss"].item(), got["loss"].item()
+            nw, ng = want["grad_norm"].item(), got["grad_norm"].item()
+            assert abs(lw - lg) < 2e-2 * abs(lw), f"rank {rank} {layout} step {step}: loss {lg} vs {lw}"
+            assert abs(nw - ng) < 6e-2 * nw, f"rank {rank} {layout} step {step}: grad norm {ng} vs {nw}"
+        a = model.flatten_params(ref.export_tree())
+        b = model.flatten_params(cp.export_tree())
+        start = model.flatten_params(params)
+        for name in ("layers.0.W_q", "layers.3.W_k", "layers.1.ffn_gate", "embed"):
+            da, db = (a[name] - start[name]).float().flatten(), (b[name] - start[name]).float().flatten()
+            cos = torch.nn.functional.cosine_similarity(da, db, dim=0).item()
+            assert cos > 0.9, f"{layout} {name}: update cosine {cos:.3f}"
+        cp.check_canaries()
+        cp.close()
     dist.barrier()
     if rank == 0:
         print("CP_ENGINE_OK")
@@ -576,7 +645,7 @@ def nvls_main():
 
 if __name__ == "__main__":
     try:
-        {"ep": ep_main, "ep_engine": ep_engine_main, "cp_delta": cp_delta_main, "ag_gemm": ag_gemm_main, "cp_engine": cp_engine_main,
+        {"ep": ep_main, "ep_engine": ep_engine_main, "cp_delta": cp_delta_main, "cp_zigzag": cp_zigzag_main, "ag_gemm": ag_gemm_main, "cp_engine": cp_engine_main,
          "fsdp_engine": fsdp_engine_main, "nvls": nvls_main}.get((sys.argv[1:] or [""])[0], main)()
     except BaseException:
         import traceback

@@ -53,6 +53,11 @@ def test_two_rank_context_parallel_delta_rule():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_zigzag_context_parallel_layers():
+    _run_ranks(2, 29533, "CP_ZIGZAG_OK", "cp_zigzag")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_all_gather_gemm():
     _run_ranks(2, 29525, "AG_GEMM_OK", "ag_gemm")
 
