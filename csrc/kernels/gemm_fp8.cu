@@ -393,25 +393,41 @@ __global__ void __launch_bounds__(256) dequant_rows_kernel(const uint8_t* __rest
   const long warps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
   for (long row = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < m_eff;
        row += warps) {
-    for (int c = lane * 16; c < K; c += 512) {
-      const float s = scales[static_cast<size_t>(c >> 7) * ld_s + row];
-      const uint4 raw = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(row) * K + c);
-      const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
-      float f[16];
+    // four column groups (2048 elements of the row) per pass: their payload and scale loads are
+    // all issued before the first conversion, so a pass costs one memory latency, not four
+    for (int c0 = 0; c0 < K; c0 += 2048) {
+      uint4 raw[4];
+      float sc[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(
-              static_cast<__nv_fp8x2_storage_t>((w4[j] >> (16 * hh)) & 0xffffu), __NV_E4M3);
-          const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-          f[4 * j + 2 * hh] = v.x * s;
-          f[4 * j + 2 * hh + 1] = v.y * s;
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 512 + lane * 16;
+        if (c < K) {
+          raw[u] = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(row) * K + c);
+          sc[u] = scales[static_cast<size_t>(c >> 7) * ld_s + row];
         }
       }
-      bf16* dst = y + static_cast<size_t>(row) * K + c;
-      *reinterpret_cast<bf16x8*>(dst) = pack8(f);
-      *reinterpret_cast<bf16x8*>(dst + 8) = pack8(f + 8);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 512 + lane * 16;
+        if (c >= K) continue;
+        const float s = sc[u];
+        const uint32_t w4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+        float f[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(
+                static_cast<__nv_fp8x2_storage_t>((w4[j] >> (16 * hh)) & 0xffffu), __NV_E4M3);
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+            f[4 * j + 2 * hh] = v.x * s;
+            f[4 * j + 2 * hh + 1] = v.y * s;
+          }
+        }
+        bf16* dst = y + static_cast<size_t>(row) * K + c;
+        *reinterpret_cast<bf16x8*>(dst) = pack8(f);
+        *reinterpret_cast<bf16x8*>(dst + 8) = pack8(f + 8);
+      }
     }
   }
 }

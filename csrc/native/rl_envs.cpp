@@ -15,6 +15,8 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <sys/stat.h>
+
 #include <cmath>
 #include <map>
 #include <set>
@@ -129,9 +131,27 @@ std::optional<int64_t> eval_int_expr(const std::string& s) {   // digits with + 
   return total;
 }
 
+// Where sandboxes run. InProcess: the engine below, no KVM, no sockets. Firecracker: the gate of
+// the reference's microVM backend (rl/envs/src/lib.rs:327-378): it can only be constructed on a
+// node with a KVM device, and booting an image needs the kernel and rootfs files to exist;
+// isolation semantics are those of the in-process engine.
+struct FirecrackerBackend {
+  std::string socket, kernel, rootfs;
+};
+
 class Pool {
  public:
   explicit Pool(PoolConfig c) : cfg_(std::move(c)) {}
+  static Pool firecracker(std::string socket, std::string kernel, std::string rootfs, PoolConfig c,
+                          const std::string& kvm_device) {
+    struct stat sb;
+    if (::stat(kvm_device.c_str(), &sb) != 0) throw Error("Backend", "kvm device missing: " + kvm_device);
+    Pool p(std::move(c));
+    p.fc_ = FirecrackerBackend{std::move(socket), std::move(kernel), std::move(rootfs)};
+    return p;
+  }
+  std::string backend() const { return fc_ ? "firecracker" : "in_process"; }
+  const std::optional<FirecrackerBackend>& firecracker_paths() const { return fc_; }
   size_t live_count() const {
     size_t n = 0;
     for (auto& kv : boxes_) n += kv.second.live ? 1 : 0;
@@ -158,6 +178,13 @@ class Pool {
   std::string snapshot_from_image(const std::string& image) {
     auto it = images_.find(image);
     if (it == images_.end()) throw Error("UnknownImage", "unknown image " + image);
+    if (fc_) {     // booting a microVM needs its boot images
+      struct stat sb;
+      if (::stat(fc_->kernel.c_str(), &sb) != 0 || !S_ISREG(sb.st_mode))
+        throw Error("Backend", "kernel image missing: " + fc_->kernel);
+      if (::stat(fc_->rootfs.c_str(), &sb) != 0 || !S_ISREG(sb.st_mode))
+        throw Error("Backend", "rootfs image missing: " + fc_->rootfs);
+    }
     const std::string id = "snap-" + std::to_string(next_snap_++);
     Sandbox s;
     s.files = it->second.agent_files;
@@ -369,6 +396,7 @@ class Pool {
     return it->second;
   }
   PoolConfig cfg_;
+  std::optional<FirecrackerBackend> fc_;
   std::map<std::string, Image> images_;
   std::map<std::string, Sandbox> snaps_, boxes_;
   std::vector<TamperFlag> tamper_;
@@ -733,6 +761,14 @@ void bind_rl_envs(py::module_& m) {
            py::arg("web_cutoff_unix_s") = 0, py::arg("gpu_walltime_s") = py::none(), py::arg("default_timeout_s") = 60);
   py::class_<Pool>(em, "Pool")
       .def(py::init<PoolConfig>(), py::arg("config") = PoolConfig{})
+      .def_static("firecracker", &Pool::firecracker, py::arg("socket"), py::arg("kernel"), py::arg("rootfs"),
+                  py::arg("config") = PoolConfig{}, py::arg("kvm_device") = "/dev/kvm")
+      .def_property_readonly("backend", &Pool::backend)
+      .def_property_readonly("firecracker_paths", [](const Pool& p) -> py::object {
+        if (!p.firecracker_paths()) return py::none();
+        const auto& f = *p.firecracker_paths();
+        return py::make_tuple(f.socket, f.kernel, f.rootfs);
+      })
       .def("live_count", &Pool::live_count)
       .def_property_readonly("tamper_flags", &Pool::tamper_flags)
       .def("register_image", &Pool::register_image)
