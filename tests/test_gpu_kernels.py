@@ -15,10 +15,29 @@ def _r(*shape, seed=0, scale=1.0, dtype=BF16):
 
 
 def _close(got, ref, tol=2e-2):
+    """Three bounds, so that neither a wrong row of small magnitude nor a dropped tail tile can
+    hide behind the largest element: (1) max abs error against the largest reference element,
+    (2) every row (last axis) on its own: error norm <= 4 tol x that row's norm + tol x the norm
+    of a typical row, (3) cosine of the flattened tensors >= 1 - tol^2."""
     got, ref = got.float(), ref.float()
+    assert got.shape == ref.shape, f"shape {tuple(got.shape)} vs {tuple(ref.shape)}"
+    assert torch.isfinite(got).all(), "non-finite values"
     err = (got - ref).abs().max().item()
     scale = ref.abs().max().item() + 1e-6
     assert err <= tol * scale, f"max err {err:.4g} vs scale {scale:.4g}"
+    if ref.ndim >= 1 and ref.shape[-1] > 1:
+        g2, r2 = got.reshape(-1, ref.shape[-1]), ref.reshape(-1, ref.shape[-1])
+        row_err = (g2 - r2).norm(dim=1)
+        row_ref = r2.norm(dim=1)
+        typical = ref.pow(2).mean().sqrt().item() * math.sqrt(ref.shape[-1]) + 1e-6
+        over = row_err - (4 * tol * row_ref + tol * typical)
+        worst = int(over.argmax())
+        assert over[worst].item() <= 0, (f"row {worst}: err {row_err[worst].item():.4g}, row norm "
+                                         f"{row_ref[worst].item():.4g}, typical row {typical:.4g}")
+    denom = got.norm().item() * ref.norm().item()
+    if denom > 0:
+        cos = (got * ref).sum().item() / denom
+        assert cos >= 1 - tol * tol, f"cosine {cos:.6f}"
 
 
 def test_kernel_library_is_loaded_in_tree():
