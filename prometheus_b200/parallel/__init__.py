@@ -180,6 +180,6 @@ def ep_combine(expert_out: Any, meta: Any, residual: Any):
 
 from .fsdp import fsdp_all_gather, fsdp_reduce_scatter, fsdp_shard, zero3_views  # noqa: E402
 from .schedule import circular_pipeline, pipeline_forward_schedule  # noqa: E402
-from .pp import spmd_circular_pipeline  # noqa: E402
+from .pp import spmd_circular_pipeline, spmd_pipeline_train  # noqa: E402
 from .cp import (cp_ring_schedule, cp_split_seq, ring_attention, ring_attention_rank,  # noqa: E402
                  delta_state_handoff, compose_affine)

@@ -164,3 +164,57 @@ def test_two_process_gloo_pipeline_ring_and_handoff():
     for p in procs:
         p.join(60)
     assert got == [(0, True, True, True), (1, True, True, True)]
+
+
+def _pp_train_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        layers = [torch.nn.Linear(6, 6) for _ in range(world)]         # same weights on every rank
+        mbs = [torch.randn(5, 6, generator=torch.Generator().manual_seed(10 + i)) for i in range(3)]
+        tgt = [torch.randn(5, 6, generator=torch.Generator().manual_seed(20 + i)) for i in range(3)]
+        loss_fn = lambda y, m: ((y - tgt[m]) ** 2).mean()               # noqa: E731
+        mine = layers[rank]
+        total = P.spmd_pipeline_train(mbs, world, lambda s, x: torch.tanh(mine(x)), loss_fn)
+        # the unsplit model on one process
+        ref = [torch.nn.Linear(6, 6) for _ in range(world)]
+        for a, b in zip(ref, layers):
+            a.load_state_dict(b.state_dict())
+        want = 0.0
+        for m, x in enumerate(mbs):
+            h = x
+            for l in ref:
+                h = torch.tanh(l(h))
+            loss = loss_fn(h, m)
+            loss.backward()
+            want = want + loss.item()
+        ok_grad = torch.allclose(mine.weight.grad, ref[rank].weight.grad, rtol=1e-5, atol=1e-6) and \
+            torch.allclose(mine.bias.grad, ref[rank].bias.grad, rtol=1e-5, atol=1e-6)
+        ok_loss = total is None if rank < world - 1 else abs(float(total) - want) < 1e-5
+        out.put((rank, ok_grad, ok_loss))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_gloo_pipeline_backward_matches_the_unsplit_model(world):
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pp_train_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted(out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(60)
+    assert got == [(r, True, True) for r in range(world)]
+
+
+def test_pipeline_train_single_stage_and_errors():
+    lin = torch.nn.Linear(3, 3)
+    xs = [torch.randn(2, 3) for _ in range(2)]
+    total = P.spmd_pipeline_train(xs, 1, lambda s, x: lin(x), lambda y, m: y.sum())
+    assert lin.weight.grad is not None and torch.isfinite(total)
+    with pytest.raises(P.MeshError):
+        P.spmd_pipeline_train(xs, 2, lambda s, x: x, lambda y, m: y.sum())
