@@ -6,6 +6,8 @@
 // _apply_rope interleaved pairs (model/__init__.py:337-359), _swiglu
 // (model/__init__.py:547-549), _l2_normalize (model/__init__.py:201-203),
 // soft_cap + cross_entropy (train/__init__.py:561-604).
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace pb {
@@ -62,10 +64,21 @@ __global__ void __launch_bounds__(128) rmsnorm_fwd_kernel(const bf16* __restrict
 
 // d = 256 NV (NV <= 8): the row lives in registers between the two passes and every load of the
 // row is issued before the first use. Same arithmetic as rmsnorm_fwd_kernel.
-template <int NV>
+// q_out / s_out (may be null): the normalised row also leaves as e4m3 with one fp32 scale per
+// 128 columns, q [rows, d] bytes and s [d / 128, rows] floats, the operand layout of the
+// block-scaled FP8 GEMM. The bf16-rounded values are what is quantised (scale = amax / 448, 1 for
+// an all-zero block, true division), so the bytes equal those of the stand-alone row quantiser
+// run over y. A 128-column block is the 8 elements of 16 consecutive lanes.
+__device__ __forceinline__ uint32_t rms_e4m3x4(float a, float b, float c, float d) {
+  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+template <int NV, bool Q>
 __global__ void __launch_bounds__(128) rmsnorm_fwd_reg_kernel(
     const bf16* __restrict__ x, const bf16* __restrict__ res, const float* __restrict__ w,
-    bf16* __restrict__ y, bf16* h_out, float* __restrict__ rstd_out, int rows, float eps) {
+    bf16* __restrict__ y, bf16* h_out, float* __restrict__ rstd_out, int rows, float eps,
+    uint8_t* __restrict__ q_out, float* __restrict__ s_out) {
   constexpr int d = NV * 256;
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -106,7 +119,22 @@ __global__ void __launch_bounds__(128) rmsnorm_fwd_reg_kernel(
     const float4 w1 = *reinterpret_cast<const float4*>(w + col + 4);
     f[0] *= rstd * w0.x; f[1] *= rstd * w0.y; f[2] *= rstd * w0.z; f[3] *= rstd * w0.w;
     f[4] *= rstd * w1.x; f[5] *= rstd * w1.y; f[6] *= rstd * w1.z; f[7] *= rstd * w1.w;
-    *reinterpret_cast<bf16x8*>(y + base + col) = pack8(f);
+    const bf16x8 out = pack8(f);
+    *reinterpret_cast<bf16x8*>(y + base + col) = out;
+    if (Q) {
+      unpack8(out, f);                      // quantise what was stored
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const float scale = amax > 0.f ? amax / 448.f : 1.f;
+      uint2 pk;
+      pk.x = rms_e4m3x4(__fdiv_rn(f[0], scale), __fdiv_rn(f[1], scale), __fdiv_rn(f[2], scale), __fdiv_rn(f[3], scale));
+      pk.y = rms_e4m3x4(__fdiv_rn(f[4], scale), __fdiv_rn(f[5], scale), __fdiv_rn(f[6], scale), __fdiv_rn(f[7], scale));
+      *reinterpret_cast<uint2*>(q_out + base + col) = pk;
+      if ((lane & 15) == 0) s_out[static_cast<size_t>(col >> 7) * rows + row] = scale;
+    }
   }
 }
 
@@ -664,11 +692,32 @@ PB_API int pb_debug_bounds_enabled() {
 // violation of that file's kernels; the call clears the record and synchronises the device.
 PB_DEFINE_BOUNDS_READER(elementwise)
 
+static int rmsnorm_fwd_impl(const void* x, const void* res, const void* w, void* y, void* h_out,
+                            void* rstd, void* q, void* scales, int rows, int d, float eps,
+                            cudaStream_t st);
+
 PB_API int pb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out,
                           void* rstd, int rows, int d, float eps, cudaStream_t st) {
+  return rmsnorm_fwd_impl(x, res, w, y, h_out, rstd, nullptr, nullptr, rows, d, eps, st);
+}
+
+// The same with the FP8 image of y for the GEMM that follows: q [rows, d] e4m3 bytes, scales
+// [d / 128, rows] fp32. d a multiple of 256, at most 2048 (the register-resident kernel).
+PB_API int pb_rmsnorm_fwd_fp8(const void* x, const void* res, const void* w, void* y, void* h_out,
+                              void* rstd, void* q, void* scales, int rows, int d, float eps,
+                              cudaStream_t st) {
+  if (q == nullptr || scales == nullptr || d % 256 != 0 || d > 2048) return PB_BAD_ARG;
+  return rmsnorm_fwd_impl(x, res, w, y, h_out, rstd, q, scales, rows, d, eps, st);
+}
+
+static int rmsnorm_fwd_impl(const void* x, const void* res, const void* w, void* y, void* h_out,
+                            void* rstd, void* q, void* scales, int rows, int d, float eps,
+                            cudaStream_t st) {
   if (d % 8 != 0 || rows <= 0) return PB_BAD_ARG;
   const int wpb = 4;
   if (d % 256 == 0 && d <= 2048) {
+    uint8_t* q_ = static_cast<uint8_t*>(q);
+    float* sc_ = static_cast<float*>(scales);
     const bf16* x_ = static_cast<const bf16*>(x);
     const bf16* r_ = static_cast<const bf16*>(res);
     const float* w_ = static_cast<const float*>(w);
@@ -679,7 +728,12 @@ PB_API int pb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y
     switch (d / 256) {
 #define PB_CASE(NV)                                                                              \
   case NV:                                                                                       \
-    rmsnorm_fwd_reg_kernel<NV><<<grid, wpb * 32, 0, st>>>(x_, r_, w_, y_, h_, s_, rows, eps);    \
+    if (q_ != nullptr)                                                                           \
+      rmsnorm_fwd_reg_kernel<NV, true><<<grid, wpb * 32, 0, st>>>(x_, r_, w_, y_, h_, s_, rows,  \
+                                                                  eps, q_, sc_);                 \
+    else                                                                                         \
+      rmsnorm_fwd_reg_kernel<NV, false><<<grid, wpb * 32, 0, st>>>(x_, r_, w_, y_, h_, s_, rows, \
+                                                                   eps, nullptr, nullptr);       \
     break;
       PB_CASE(1) PB_CASE(2) PB_CASE(3) PB_CASE(4) PB_CASE(5) PB_CASE(6) PB_CASE(7) PB_CASE(8)
 #undef PB_CASE

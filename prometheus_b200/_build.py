@@ -116,7 +116,11 @@ def build_kernels(verbose: bool = False, force: bool = False, debug_bounds: bool
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(lambda c: _run(c, verbose), jobs))
     if force or jobs or _newer(objs, target):
-        _run([nvcc, *NVCC_ARCH, "-shared", "-o", target, *objs], verbose)
+        # link beside the target and rename: a process (or a snapshot of the tree) never sees a
+        # half-written library
+        tmp = target.with_name(target.name + ".tmp")
+        _run([nvcc, *NVCC_ARCH, "-shared", "-o", tmp, *objs], verbose)
+        os.replace(tmp, target)
     return target
 
 
@@ -158,7 +162,9 @@ def build_native(verbose: bool = False, force: bool = False, sanitize: str = "")
     out = native_lib_path(sanitize)
     out.parent.mkdir(parents=True, exist_ok=True)
     if force or jobs or _newer(objs, out):
-        _run(["g++", "-shared", "-o", out, *objs, *link_extra, "-lpthread", "-lz"], verbose)
+        tmp = out.with_name(out.name + ".tmp")
+        _run(["g++", "-shared", "-o", tmp, *objs, *link_extra, "-lpthread", "-lz"], verbose)
+        os.replace(tmp, out)
     return out
 
 

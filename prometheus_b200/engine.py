@@ -929,11 +929,13 @@ class Trainer:
                                               allow_fallback=self.allow_fallback)
         return ops.linear(o.reshape(B * S, nh * dh), self.p[pre + "o"])
 
-    def _ffn_linear(self, x: Tensor, w: Tensor) -> Tensor:
+    def _ffn_linear(self, x: Tensor, w: Tensor, xq=None) -> Tensor:
+        """``xq``: the e4m3 rows + scales of ``x`` when the norm kernel that produced it wrote
+        them too (one quantisation shared by every FP8 consumer of the normalised stream)."""
         if self.fp8 and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
             from .ops import fp8
 
-            return fp8.fp8_linear(x, w)
+            return fp8.fp8_linear(x, w, xq)
         return ops.linear(x, w)
 
     def _mla_layer(self, n: Tensor, i: int, B: int, S: int) -> Tensor:
@@ -963,7 +965,7 @@ class Trainer:
         o = o.transpose(1, 2).reshape(B * S, nh * dn)
         return ops.linear(o, self.p[pre + "o"])
 
-    def _moe_layer(self, n2: Tensor, i: int) -> Tensor:
+    def _moe_layer(self, n2: Tensor, i: int, n2q=None) -> Tensor:
         from .ops import moe
 
         cfg = self.cfg
@@ -989,9 +991,11 @@ class Trainer:
                 side = self.side_stream
                 side.wait_stream(main)
                 n2.record_stream(side)
+                for t_ in (n2q or ()):
+                    t_.record_stream(side)
                 with torch.cuda.stream(side):
                     for j in range(cfg.n_shared_experts):
-                        gu = self._ffn_linear(n2, self.p[pre + f"shared{j}_gate_up"])
+                        gu = self._ffn_linear(n2, self.p[pre + f"shared{j}_gate_up"], n2q)
                         sj = self._ffn_linear(ops.swiglu(gu), self.p[pre + f"shared{j}_down"])
                         shared = sj if shared is None else shared + sj
             out, probs, ids, logits = ep_moe_ffn(
@@ -1098,12 +1102,17 @@ class Trainer:
                 a = self._mla_layer(n, i, B, S)
             else:
                 a = self._gqa_layer(n, i, B, S)
-            n2, h = ops.add_rmsnorm(a, h, self.p[pre + "pre_ffn_norm"])
+            # FP8 linears: the norm kernel also writes the e4m3 rows + scales its consumers read
+            want_q = self.fp8 and (pre + "gate_up" in self.p or (self.ep and cfg.n_shared_experts > 0))
+            if want_q:
+                n2, h, n2q = ops.add_rmsnorm(a, h, self.p[pre + "pre_ffn_norm"], emit_fp8=True)
+            else:
+                (n2, h), n2q = ops.add_rmsnorm(a, h, self.p[pre + "pre_ffn_norm"]), None
             if pre + "gate_up" in self.p:
-                gu = self._ffn_linear(n2, self.p[pre + "gate_up"])
+                gu = self._ffn_linear(n2, self.p[pre + "gate_up"], n2q)
                 f = self._ffn_linear(ops.swiglu(gu), self.p[pre + "down"])
             else:
-                f = self._moe_layer(n2, i)
+                f = self._moe_layer(n2, i, n2q)
             if self.fsdp and torch.is_grad_enabled():
                 # the backward of this layer starts here: its weights must be resident again
                 f = _FsdpLayerHook.apply(f, self, i)

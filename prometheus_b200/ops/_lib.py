@@ -25,6 +25,7 @@ P, I, L, F = c_void_p, c_int, c_long, c_float
 
 _SIGS = {
     "pb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "pb_rmsnorm_fwd_fp8": [P, P, P, P, P, P, P, P, I, I, F, P],
     "pb_rmsnorm_bwd_nparts": [I, I],
     "pb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
     "pb_rope": [P, P, L, I, I, I, I, F, I, P],

@@ -116,11 +116,14 @@ def gemm_fp8(aq: Tensor, sa: Tensor, bq: Tensor, sb: Tensor, *, mblk_group: Tens
 
 class _Fp8LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w):
+    def forward(ctx, x, w, pre=None):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        xq, sx = quantize_rows(x2)
+        if pre is not None and pre[0].shape == x2.shape and pre[1].shape == (x2.shape[1] // 128, x2.shape[0]):
+            xq, sx = pre             # quantised by the producer of x (fused into its kernel)
+        else:
+            xq, sx = quantize_rows(x2)
         wq, sw = quantize_blocks(w)
         ctx.save_for_backward(x2, w)
         ctx.w_ref = w
@@ -143,10 +146,12 @@ class _Fp8LinearFn(torch.autograd.Function):
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, d=mg, beta=1.0)
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True)
-        return dx, dw
+        return dx, dw, None
 
 
-def fp8_linear(x: Tensor, w: Tensor) -> Tensor:
+def fp8_linear(x: Tensor, w: Tensor, xq=None) -> Tensor:
     """y = q(x) @ q(w)^T with 1 x 128 activation blocks and 128 x 128 weight blocks (w stored
-    (out, in)); straight-through bf16 gradients, fp32 ``main_grad`` accumulation as ``linear``."""
-    return _Fp8LinearFn.apply(x, w)
+    (out, in)); straight-through bf16 gradients, fp32 ``main_grad`` accumulation as ``linear``.
+    ``xq``: ``(q, scales)`` of ``x`` when its producer already wrote them
+    (``functional.add_rmsnorm(..., emit_fp8=True)``); the row quantiser is then skipped."""
+    return _Fp8LinearFn.apply(x, w, xq)

@@ -202,22 +202,26 @@ def _accumulate_param_grad(p: Tensor, g: Tensor):
 
 class _RmsNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, res, w, eps):
+    def forward(ctx, x, res, w, eps, fp8_out=None):
+        """``fp8_out``: a list that receives ``(q, scales)``, the e4m3 image of ``y`` in the operand
+        layout of the block-scaled GEMM, written by the same kernel (d a multiple of 256, <= 2048)."""
         shape = x.shape
         d = shape[-1]
         x2 = x.reshape(-1, d).contiguous()
         rows = x2.shape[0]
         y = torch.empty_like(x2)
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
-        if res is not None:
-            r2 = res.reshape(-1, d).contiguous()
-            h = torch.empty_like(x2)
-            call("pb_rmsnorm_fwd", ptr(x2), ptr(r2), ptr(w), ptr(y), ptr(h), ptr(rstd), rows, d,
-                 float(eps), stream_ptr())
+        r2 = res.reshape(-1, d).contiguous() if res is not None else None
+        h = torch.empty_like(x2) if res is not None else x2
+        if fp8_out is not None and d % 256 == 0 and d <= 2048:
+            q = torch.empty((rows, d), dtype=torch.uint8, device=x.device)
+            sc = torch.empty((d // 128, rows), dtype=torch.float32, device=x.device)
+            call("pb_rmsnorm_fwd_fp8", ptr(x2), ptr(r2), ptr(w), ptr(y), ptr(h) if res is not None else None,
+                 ptr(rstd), ptr(q), ptr(sc), rows, d, float(eps), stream_ptr())
+            fp8_out.append((q, sc))
         else:
-            h = x2
-            call("pb_rmsnorm_fwd", ptr(x2), None, ptr(w), ptr(y), None, ptr(rstd), rows, d,
-                 float(eps), stream_ptr())
+            call("pb_rmsnorm_fwd", ptr(x2), ptr(r2), ptr(w), ptr(y), ptr(h) if res is not None else None,
+                 ptr(rstd), rows, d, float(eps), stream_ptr())
         ctx.save_for_backward(h, w, rstd)
         ctx.w_ref = w
         ctx.has_res = res is not None
@@ -240,7 +244,7 @@ class _RmsNormFn(torch.autograd.Function):
              ptr(part), 0, rows, d, stream_ptr())
         dx = dx.reshape(ctx.shape)
         gw = _accumulate_param_grad(ctx.w_ref, dw) if ctx.needs_input_grad[2] else None
-        return dx, (dx if ctx.has_res else None), gw, None
+        return dx, (dx if ctx.has_res else None), gw, None, None
 
 
 def rmsnorm(x: Tensor, w: Tensor, eps: float = 1e-6) -> Tensor:
@@ -248,9 +252,16 @@ def rmsnorm(x: Tensor, w: Tensor, eps: float = 1e-6) -> Tensor:
     return _RmsNormFn.apply(x, None, w, eps)[0]
 
 
-def add_rmsnorm(x: Tensor, res: Tensor, w: Tensor, eps: float = 1e-6):
-    """h = x + res; y = rmsnorm(h). Returns (y, h) from one kernel."""
-    return _RmsNormFn.apply(x, res, w, eps)
+def add_rmsnorm(x: Tensor, res: Tensor, w: Tensor, eps: float = 1e-6, emit_fp8: bool = False):
+    """h = x + res; y = rmsnorm(h). Returns (y, h) from one kernel. With ``emit_fp8`` the kernel
+    also writes the e4m3 rows and 1 x 128 scales of ``y`` (what ``fp8.quantize_rows(y)`` would
+    produce, without the extra pass over ``y``) and ``(y, h, (q, scales))`` comes back;
+    the third element is ``None`` where the fused kernel does not cover the width."""
+    if not emit_fp8:
+        return _RmsNormFn.apply(x, res, w, eps)
+    got: list = []
+    y, h = _RmsNormFn.apply(x, res, w, eps, got)
+    return y, h, (got[0] if got else None)
 
 
 def rmsnorm_ref(x, w, eps=1e-6, res=None):

@@ -120,3 +120,34 @@ def test_swiglu_quantize_and_dequantize_kernels():
         assert torch.equal(s2[:, : M // 2], s_ref[:, : M // 2])
         d2 = fp8.dequantize_rows_bf16(q, s, used)
         assert torch.equal(d2[: M // 2], deq[: M // 2])
+
+
+@pytest.mark.parametrize("rows,d", [(300, 2048), (64, 1024), (1000, 256)])
+def test_rmsnorm_emits_the_fp8_rows_the_gemm_reads(rows, d):
+    """add + RMSNorm with the fused e4m3 output: y and h as without it, q and scales bitwise equal
+    to the stand-alone row quantiser run over y, and the FP8 linear that takes them equal to the
+    one that quantises for itself (forward and both gradients)."""
+    from prometheus_b200.ops import fp8
+    from prometheus_b200.ops import functional as ops
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(rows, d, device="cuda", generator=g).bfloat16()
+    r = torch.randn(rows, d, device="cuda", generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(d, device="cuda", generator=g)).float()
+    x[3] = 0
+    r[3] = 0                                              # an all-zero row: scale 1, bytes 0
+    y0, h0 = ops.add_rmsnorm(x, r, w)
+    y1, h1, qs = ops.add_rmsnorm(x, r, w, emit_fp8=True)
+    assert qs is not None and torch.equal(y0, y1) and torch.equal(h0, h1)
+    q_ref, s_ref = fp8.quantize_rows(y0)
+    assert torch.equal(qs[0], q_ref) and torch.equal(qs[1], s_ref)
+    wl = (torch.randn(256, d, device="cuda", generator=g) * 0.05).bfloat16()
+    outs = []
+    for pre in (None, qs):
+        yl = y0.clone().requires_grad_(True)
+        wp = wl.clone().requires_grad_(True)
+        o = fp8.fp8_linear(yl, wp, pre)
+        o.float().square().sum().backward()
+        outs.append((o, yl.grad, wp.grad))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
