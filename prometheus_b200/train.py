@@ -537,13 +537,23 @@ def _clip_qk_weights(params: Any, max_logit: float) -> Any:
     return params
 
 
-def _update_router_bias(params: Any, expert_ids: Tensor, n_experts: int, u: float = 1e-3) -> Any:
+def _update_router_bias(params: Any, expert_ids: Tensor, n_experts: int, u: float = 1e-3,
+                        router_probs: Tensor | None = None, rule: str = "probs") -> Any:
     """Aux-loss-free balancing: ``b <- b - u * sign(load - mean)`` on every ``router_bias``
-    leaf, with load = fraction of assignments per expert in the last MoE layer."""
-    if expert_ids is None or expert_ids.numel() == 0:
+    leaf. ``rule="probs"`` (the reference's, train/__init__.py:810-816): load = mean router
+    probability per expert over the tokens of the last MoE layer. ``rule="count"``: load =
+    fraction of the top-k assignments per expert in that layer, i.e. what the experts actually
+    received (the fused trainer's default; the two can differ in sign for an expert that is often
+    probable but rarely in the top k)."""
+    if rule not in ("probs", "count"):
+        raise ValueError("router_bias_rule must be 'probs' or 'count'")
+    if rule == "probs" and router_probs is not None and router_probs.numel() > 0:
+        load = _f32(router_probs).reshape(-1, router_probs.shape[-1]).mean(dim=0)
+    elif expert_ids is None or expert_ids.numel() == 0:
         return params
-    load = torch.bincount(expert_ids.reshape(-1).long(), minlength=n_experts).float()
-    load = load / load.sum().clamp(min=1.0)
+    else:
+        load = torch.bincount(expert_ids.reshape(-1).long(), minlength=n_experts).float()
+        load = load / load.sum().clamp(min=1.0)
     delta = torch.sign(load - load.mean()) * float(u)
 
     def walk(obj):
@@ -584,9 +594,10 @@ def compute_loss(params: dict, batch: Batch, model_config: ModelConfig,
 def train_step(params: dict, opt_state: dict, batch: Batch, model_config: ModelConfig,
                train_config: TrainConfig, *, step: int, muon_transfer: bool = False,
                muon_weight_decay: float = 0.0, muon_all_matrices: bool = False, r: int = 1,
-               z_on_logits: bool = False) -> StepOutput:
+               z_on_logits: bool = False, router_bias_rule: str = "probs") -> StepOutput:
     """One FP32-master step: forward, loss, global-norm clip, Muon / AdamW, QK-clip,
-    router-bias nudge. ``step`` is 1-based."""
+    router-bias nudge (``router_bias_rule``: "probs" = the reference's mean router probability,
+    "count" = share of the top-k assignments). ``step`` is 1-based."""
     validate_train_config(train_config)
     t = int(step)
     if t < 1:
@@ -652,7 +663,8 @@ def train_step(params: dict, opt_state: dict, batch: Batch, model_config: ModelC
         if float(train_config.qk_clip) > 0:
             new_params = _clip_qk_weights(new_params, float(train_config.qk_clip))
         new_params = _update_router_bias(new_params, out.expert_ids,
-                                         int(model_config.n_routed_experts))
+                                         int(model_config.n_routed_experts),
+                                         router_probs=out.router_probs, rule=router_bias_rule)
     return StepOutput(
         params=new_params, opt_state=new_opt,
         loss=LossBreakdown(ce=ce.detach(), mtp=mtp.detach(), z=z.detach(), total=total.detach()),

@@ -146,3 +146,23 @@ def test_train_step_reference_flags():
     assert out.step == 1 and out.lr == pytest.approx(tcfg.peak_lr * 0.5)
     assert "momentum" in out.opt_state["layers"][0]["ffn_gate"]
     assert "m" in out.opt_state["layers"][0]["W_q"]
+
+
+def test_router_bias_rules_probs_and_count():
+    """The reference rule (mean router probability of the last MoE layer) and the assignment-count
+    rule move ``router_bias`` by the same step size and can disagree in sign per expert."""
+    import torch
+
+    from prometheus_b200 import train as T
+
+    params = {"layers": [{"router_bias": torch.zeros(4)}]}
+    probs = torch.tensor([[[0.4, 0.3, 0.2, 0.1], [0.4, 0.3, 0.2, 0.1]]])       # expert 1 above the mean 0.25
+    ids = torch.tensor([[[0, 2], [0, 3]]])                                   # ... but never assigned
+    by_probs = T._update_router_bias(params, ids, 4, u=0.5, router_probs=probs, rule="probs")
+    by_count = T._update_router_bias(params, ids, 4, u=0.5, router_probs=probs, rule="count")
+    assert by_probs["layers"][0]["router_bias"].tolist() == [-0.5, -0.5, 0.5, 0.5]
+    assert by_count["layers"][0]["router_bias"].tolist() == [-0.5, 0.5, 0.0, 0.0]
+    assert params["layers"][0]["router_bias"].tolist() == [0.0] * 4              # input untouched
+    import pytest
+    with pytest.raises(ValueError):
+        T._update_router_bias(params, ids, 4, rule="other")
