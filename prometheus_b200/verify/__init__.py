@@ -370,7 +370,56 @@ def run_v3(*, gpus: int = 8, steps: int = 150) -> dict:
 # ---------------------------------------------------------------------------
 # V4  faults: bitwise resume, SDC hash, spike rollback
 # ---------------------------------------------------------------------------
+def _engine_config():
+    """The small hybrid with head dim 128: every layer runs on the tcgen05 kernels."""
+    return _small_config(d_model=256, n_heads=2, d_head=128, n_kv_heads=1, chunk=64, dense_hidden=512,
+                         vocab_size=1024)
+
+
+def _v4_engine() -> dict:
+    """Kill and resume through the fused trainer and the native checkpoint store: three steps, a
+    persistent checkpoint on disk, a new trainer with a different init restored from it, three
+    more steps; every state buffer must be bitwise equal to those of six straight steps (the
+    kernels are deterministic). A flipped byte in a stored shard must fail the restore."""
+    from .. import checkpoint, engine
+
+    cfg = _engine_config()
+    tcfg = train.train_config_for(cfg, warmup_steps=1, stable_steps=50, decay_steps=5)
+    gen = torch.Generator().manual_seed(4)
+    toks = [torch.randint(0, cfg.vocab_size, (4, 128), generator=gen).cuda() for _ in range(6)]
+    straight = engine.Trainer(cfg, tcfg, seed=3, device="cuda", micro_batch=2)
+    for t in toks:
+        straight.step(t)
+    first = engine.Trainer(cfg, tcfg, seed=3, device="cuda", micro_batch=2)
+    for t in toks[:3]:
+        first.step(t)
+    names = ("muon_master", "muon_mom", "adam_master", "adam_m", "adam_v", "vec_master")
+    with tempfile.TemporaryDirectory() as tmp:
+        cid = checkpoint.TrainerCheckpointer(str(Path(tmp) / "s")).save_persistent(first, wait=True)
+        second = engine.Trainer(cfg, tcfg, seed=99, device="cuda", micro_batch=2)
+        checkpoint.TrainerCheckpointer(str(Path(tmp) / "s")).restore(second, cid)
+        for t in toks[3:]:
+            second.step(t)
+        bitwise = all(torch.equal(getattr(straight, n), getattr(second, n)) for n in names)
+        # silent data corruption: flip one byte of the largest stored shard
+        files = sorted((p for p in (Path(tmp) / "s").iterdir() if p.is_file()), key=lambda p: p.stat().st_size)
+        raw = bytearray(files[-1].read_bytes())
+        raw[len(raw) // 2] ^= 0x10
+        files[-1].write_bytes(bytes(raw))
+        try:
+            checkpoint.TrainerCheckpointer(str(Path(tmp) / "s")).restore(
+                engine.Trainer(cfg, tcfg, seed=1, device="cuda", micro_batch=2), cid)
+            caught = False
+        except Exception:
+            caught = True
+    return {"resumed_bitwise_equal": bool(bitwise), "sdc_caught_flip": bool(caught)}
+
+
 def run_v4(*, gpus: int = 4) -> dict:
+    """Faults: bitwise resume after a kill, a flipped bit caught by its hash, a loss spike rolled
+    back with its shard skipped. On a GPU the first two run through ``engine.Trainer`` and
+    ``checkpoint.TrainerCheckpointer`` (``_v4_engine``); the spike policy runs on the fp32 tree
+    step either way."""
     C = native.ckpt
     cfg = _small_config()
     tcfg = train.train_config_for(cfg, warmup_steps=1, stable_steps=50, decay_steps=5)
@@ -422,8 +471,13 @@ def run_v4(*, gpus: int = 4) -> dict:
     after, _, _ = _train(cfg, tcfg, good, stream[9:10], start_step=10, opt=o) if spike else (trial.params, None, None)
     ref, _, _ = _train(cfg, tcfg, params, stream)
     skipped = spike and _tree_bytes(after) == _tree_bytes(ref)
-    return {"resumed_bitwise_equal": bool(bitwise), "sdc_caught_flip": bool(sdc),
-            "spike_rollback_skipped_shard": bool(skipped), "gpus": int(gpus)}
+    out = {"resumed_bitwise_equal": bool(bitwise), "sdc_caught_flip": bool(sdc),
+           "spike_rollback_skipped_shard": bool(skipped), "gpus": int(gpus), "path": "tree"}
+    if torch.cuda.is_available():
+        e = _v4_engine()
+        out.update(resumed_bitwise_equal=out["resumed_bitwise_equal"] and e["resumed_bitwise_equal"],
+                   sdc_caught_flip=out["sdc_caught_flip"] and e["sdc_caught_flip"], path="tree+engine")
+    return out
 
 
 # ---------------------------------------------------------------------------
@@ -459,10 +513,35 @@ def run_v5(*, gpus: int = 8, steps: int = 40) -> dict:
 # ---------------------------------------------------------------------------
 # V6  latent curriculum
 # ---------------------------------------------------------------------------
+def _v6_engine() -> dict:
+    """Latent slots through the fused trainer: with K slots the Jacobi iteration is exact after
+    K + 1 sweeps (slot j depends on slot j - 1 only), so the hidden states after 1, 2, 4, 8 sweeps
+    must approach the 9-sweep ones, through the engine's own latent step kernels."""
+    from .. import engine
+
+    cfg = _engine_config()
+    tcfg = train.train_config_for(cfg, warmup_steps=1, stable_steps=50, decay_steps=5)
+    tr = engine.Trainer(cfg, tcfg, seed=2, device="cuda", micro_batch=2)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(6)).cuda()
+    k, start = 8, 64
+
+    def hidden(sweeps):
+        tr.set_latent_slots(start, k, sweeps)
+        with torch.no_grad():
+            return tr.forward_hidden_latent(tokens).float().reshape(2, 256, -1)
+
+    exact = hidden(k + 1)
+    errs = [float((hidden(s) - exact)[:, start:].abs().max()) for s in (1, 2, 4, 8)]
+    scale = float(exact.abs().max())
+    rises = all(x >= y - 0.02 * scale for x, y in zip(errs, errs[1:])) and errs[-1] < 0.5 * errs[0]
+    return {"accuracy_rises_with_latent_budget": bool(rises), "sweep_errors": errs}
+
+
 def run_v6(*, gpus: int = 4) -> dict:
-    """A contraction map stands in for the network: more Jacobi sweeps (latent budget) move the
-    latent slots closer to the sequential solution; the halting losses stay finite over a
-    short curriculum; a thought decodes to the ids it was built from."""
+    """More Jacobi sweeps (latent budget) move the latent slots closer to the sequential
+    solution; the halting losses stay finite over a short curriculum; a thought decodes to the
+    ids it was built from. On a GPU the sweep check also runs through ``engine.Trainer``
+    (``_v6_engine``); the fp32 check uses a small contraction map as the network."""
     g = torch.Generator().manual_seed(0)
     d, k = 16, 8
     a = torch.randn(d, d, generator=g) * 0.2
@@ -490,8 +569,14 @@ def run_v6(*, gpus: int = 4) -> dict:
     ids = torch.tensor([3, 17, 9])
     hidden = unembed[ids] * 4.0
     dec = (hidden @ unembed.t()).argmax(-1)
-    return {"curriculum_no_collapse": bool(finite), "accuracy_rises_with_latent_budget": bool(rises),
-            "thoughts_decode": bool(torch.equal(dec, ids)), "sweep_errors": errs, "gpus": int(gpus)}
+    out = {"curriculum_no_collapse": bool(finite), "accuracy_rises_with_latent_budget": bool(rises),
+           "thoughts_decode": bool(torch.equal(dec, ids)), "sweep_errors": errs, "gpus": int(gpus), "path": "fp32"}
+    if torch.cuda.is_available():
+        e = _v6_engine()
+        out.update(accuracy_rises_with_latent_budget=out["accuracy_rises_with_latent_budget"]
+                   and e["accuracy_rises_with_latent_budget"], engine_sweep_errors=e["sweep_errors"],
+                   path="fp32+engine")
+    return out
 
 
 # ---------------------------------------------------------------------------

@@ -388,3 +388,19 @@ def test_run_loop_wires_controller_tracer_metrics_and_sdc_probe(tmp_path, monkey
     with pytest.raises(engine.DeviceWaitTimeout):
         run.run("small_hybrid", sets[:5] + ["ckpt_every=0"], device="cuda", out=io.StringIO())
     ops.status_word("cuda").zero_()
+
+
+def test_verification_stages_drive_the_fused_trainer():
+    """Stages 3, 4 and 6 on a GPU go through ``engine.Trainer``: FP8 against bf16 training,
+    kill / resume through the checkpoint store bitwise plus a flipped shard byte, and latent
+    slots approaching their fixed point with the number of Jacobi sweeps."""
+    from prometheus_b200 import verify
+
+    v3 = verify.run_v3(gpus=1, steps=40)
+    assert v3["path"] == "engine" and v3["fp8_loss_rel_diff"] < 0.02 and v3["nvfp4_numerics_ok"]
+    v4 = verify.run_v4(gpus=1)
+    assert v4["path"] == "tree+engine" and v4["resumed_bitwise_equal"] and v4["sdc_caught_flip"]
+    assert v4["spike_rollback_skipped_shard"]
+    v6 = verify.run_v6(gpus=1)
+    assert v6["path"] == "fp32+engine" and v6["accuracy_rises_with_latent_budget"], v6
+    assert v6["curriculum_no_collapse"] and v6["thoughts_decode"]
