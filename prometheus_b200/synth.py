@@ -5,6 +5,8 @@ sampling against verifiers, procedural ARC families with dihedral x colour augme
 agentic trajectories; reference ``synth/__init__.py`` :161-1331 and the ``synth`` crate) and adds
 the two adapters that connect it to the rest of this package: a generator backed by the batch
 generation engine and a grid tokenizer backed by ``tokenizer.Tokenizer.encode_grid``.
+``synth_twin`` states the same rules a second time in Python / NumPy; the two are checked
+against each other on generated inputs.
 """
 from __future__ import annotations
 
