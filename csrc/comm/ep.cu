@@ -130,16 +130,25 @@ __global__ void ep_dispatch_kernel(const bf16* __restrict__ src, long ld_src,
   const bf16* s = src + static_cast<size_t>(w / k) * ld_src;
   bf16* o = static_cast<bf16*>(xbuf.p[q]) + static_cast<size_t>(row) * d;
   const float g = scale ? scale[w] : 1.f;
-  for (int c = lane * 8; c < d; c += 256) {
-    bf16x8 v = *reinterpret_cast<const bf16x8*>(s + c);
-    if (scale) {
-      float f[8];
-      unpack8(v, f);
+  // eight 16-byte loads of the row in flight per lane before the first (possibly remote) store:
+  // a 2048-wide row costs one memory latency instead of eight
+  for (int c0 = lane * 8; c0 < d; c0 += 2048) {
+    bf16x8 v[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] *= g;
-      v = pack8(f);
+    for (int u = 0; u < 8; ++u)
+      if (c0 + u * 256 < d) v[u] = *reinterpret_cast<const bf16x8*>(s + c0 + u * 256);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (c0 + u * 256 >= d) continue;
+      if (scale) {
+        float f[8];
+        unpack8(v[u], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] *= g;
+        v[u] = pack8(f);
+      }
+      *reinterpret_cast<bf16x8*>(o + c0 + u * 256) = v[u];
     }
-    *reinterpret_cast<bf16x8*>(o + c) = v;
   }
 }
 
@@ -179,13 +188,28 @@ __global__ void ep_dispatch_fp8_kernel(const bf16* __restrict__ src, long ld_src
   // Every lane runs every iteration (the shuffles below name the whole warp); lanes past the
   // end of a row narrower than 512 elements only take part in the shuffles. d is a multiple
   // of 128, so the eight lanes of a block are active or idle together.
-  for (int c0 = 0; c0 < d; c0 += 512) {
+  // The loads of up to 2048 elements of the row (four steps) are issued before the first step is
+  // quantised, so the row costs one memory latency.
+  for (int c00 = 0; c00 < d; c00 += 2048) {
+  bf16x8 raw[4][2];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int c = c00 + u * 512 + lane * 16;
+    if (c < d) {
+      raw[u][0] = *reinterpret_cast<const bf16x8*>(s + c);
+      raw[u][1] = *reinterpret_cast<const bf16x8*>(s + c + 8);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int c0 = c00 + u * 512;
+    if (c0 >= d) continue;                     // uniform over the warp: no lane shuffles alone
     const int c = c0 + lane * 16;
     const bool active = c < d;
     float f[16];
     if (active) {
-      unpack8(*reinterpret_cast<const bf16x8*>(s + c), f);
-      unpack8(*reinterpret_cast<const bf16x8*>(s + c + 8), f + 8);
+      unpack8(raw[u][0], f);
+      unpack8(raw[u][1], f + 8);
     } else {
 #pragma unroll
       for (int j = 0; j < 16; ++j) f[j] = 0.f;
@@ -205,6 +229,7 @@ __global__ void ep_dispatch_fp8_kernel(const bf16* __restrict__ src, long ld_src
     pk.w = ep_e4m3x4(__fdiv_rn(f[12], scale), __fdiv_rn(f[13], scale), __fdiv_rn(f[14], scale), __fdiv_rn(f[15], scale));
     *reinterpret_cast<uint4*>(oq + c) = pk;
     if ((lane & 7) == 0) os[static_cast<size_t>(c >> 7) * max_rows + row] = scale;
+  }
   }
   if (arrived.p[q] != nullptr) {
     // fused mode: tell the owner's GEMM that one more row of this 128-row block has landed.
