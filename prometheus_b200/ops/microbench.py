@@ -190,18 +190,26 @@ def bench_delta(a):
     leaves = [t.requires_grad_(True) for t in (q, k, v, beta)]
     go = torch.randn(B, S, H, D, device="cuda").to(BF16)
 
+    from .delta import delta_rule_fused, scan_segments
+
+    seg = a.segments if a.segments else scan_segments(B * H, S // 64)
+
     def fwd():
         with torch.no_grad():
-            kernels.chunked_delta_rule(q, k, v, beta)
+            delta_rule_fused(q, k, v, beta, None, n_seg=seg)
 
     def fwdbwd():
-        o, _ = kernels.chunked_delta_rule(*leaves)
+        o, _ = delta_rule_fused(*leaves, None, n_seg=seg)
         o.backward(go)
 
+    if a.once:                       # one call of each, for a profiler capture of a small case
+        fwdbwd()
+        torch.cuda.synchronize()
+        return {"kernel": "delta_rule", "seqs": B, "seq_len": S, "segments": seg, "once": True}
     ms_f, ms_fb = timeit(fwd, a.iters), timeit(fwdbwd, a.iters)
     chunks = B * H * S // 64
     flops_scan = chunks * 2.0 * (3 * 64 * 128 * 128 + 64 * 64 * 128)
-    return {"kernel": "delta_rule", "seqs": B, "seq_len": S, "heads": H, "fwd_ms": ms_f,
+    return {"kernel": "delta_rule", "seqs": B, "seq_len": S, "heads": H, "segments": seg, "fwd_ms": ms_f,
             "fwd_bwd_ms": ms_fb, "scan_fwd_tflops_if_all_scan": flops_scan / ms_f / 1e9}
 
 
@@ -369,6 +377,8 @@ def main():
     mo.add_argument("--hidden", type=int, default=1408)
     d.add_argument("--seqs", type=int, default=4)
     d.add_argument("--seq-len", type=int, default=4096)
+    d.add_argument("--segments", type=int, default=0, help="segments per sequence of the state walk (0: automatic)")
+    d.add_argument("--once", action="store_true")
     r = sub.add_parser("rmsnorm")
     r.add_argument("--rows", type=int, default=131072)
     r.add_argument("--d", type=int, default=2048)
