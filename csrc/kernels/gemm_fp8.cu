@@ -364,9 +364,11 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const bf16* __restric
           // quantise what the bf16 copy holds, so both forms of h agree
           f[j] = bf16_to_f32(f32_to_bf16(g[j] * s * u[j]));
         }
-        bf16* dst = h + static_cast<size_t>(row) * H + c;
-        *reinterpret_cast<bf16x8*>(dst) = pack8(f);
-        *reinterpret_cast<bf16x8*>(dst + 8) = pack8(f + 8);
+        if (h != nullptr) {                  // callers that keep only the e4m3 rows pass null
+          bf16* dst = h + static_cast<size_t>(row) * H + c;
+          *reinterpret_cast<bf16x8*>(dst) = pack8(f);
+          *reinterpret_cast<bf16x8*>(dst + 8) = pack8(f + 8);
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) f[j] = 0.f;
@@ -433,8 +435,12 @@ __global__ void __launch_bounds__(256) dequant_rows_kernel(const uint8_t* __rest
 }
 
 // One CTA (256 threads) per 128 x 128 block of a [N, K] matrix (edges clipped).
+// q / scales may be null when only `deq` is wanted. deq (may be null): bf16 [N, K] image of the
+// quantised block, e4m3(w / scale) * scale: the operand the FP8 GEMM really multiplied, which is
+// what the backward of an FP8 linear differentiates against.
 __global__ void quant_blocks_kernel(const bf16* __restrict__ w, long ld, int N, int K,
-                                    uint8_t* __restrict__ q, float* __restrict__ scales) {
+                                    uint8_t* __restrict__ q, float* __restrict__ scales,
+                                    bf16* __restrict__ deq) {
   __shared__ float red[33];
   const int nb = blockIdx.y, kb = blockIdx.x;
   const int r0 = nb * 128, c0 = kb * 128;
@@ -457,12 +463,28 @@ __global__ void quant_blocks_kernel(const bf16* __restrict__ w, long ld, int N, 
       const uint2 raw = *reinterpret_cast<const uint2*>(w + static_cast<size_t>(r) * ld + c);
       const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
       const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-      *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(r) * K + c) =
+      const uint32_t packed =
           to_e4m3x4(__fdiv_rn(__low2float(p0), scale), __fdiv_rn(__high2float(p0), scale),
                     __fdiv_rn(__low2float(p1), scale), __fdiv_rn(__high2float(p1), scale));
+      if (q != nullptr) *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(r) * K + c) = packed;
+      if (deq != nullptr) {
+        float f[4];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(
+              static_cast<__nv_fp8x2_storage_t>((packed >> (16 * hh)) & 0xffffu), __NV_E4M3);
+          const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+          f[2 * hh] = v.x * scale;
+          f[2 * hh + 1] = v.y * scale;
+        }
+        uint2 o;
+        *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(f[0], f[1]);
+        *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(f[2], f[3]);
+        *reinterpret_cast<uint2*>(deq + static_cast<size_t>(r) * K + c) = o;
+      }
     }
   }
-  if (threadIdx.x == 0) scales[static_cast<size_t>(nb) * gridDim.x + kb] = scale;
+  if (threadIdx.x == 0 && scales != nullptr) scales[static_cast<size_t>(nb) * gridDim.x + kb] = scale;
 }
 
 }  // namespace f8
@@ -525,7 +547,19 @@ PB_API int pb_fp8_quant_blocks(const void* w, long ld, int rows, int K, void* q,
   if (rows <= 0 || K <= 0 || K % 128 != 0 || ld % 4 != 0) return PB_BAD_ARG;
   dim3 grid(K / 128, (rows + 127) / 128);
   f8::quant_blocks_kernel<<<grid, 256, 0, st>>>(static_cast<const bf16*>(w), ld, rows, K,
-                                                static_cast<uint8_t*>(q), scales);
+                                                static_cast<uint8_t*>(q), scales, nullptr);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out [rows, K] bf16 = the 128 x 128 block quantisation of w applied and undone (e4m3 rounding at
+// the block's scale): the weight an FP8 linear really used. Same shape rules as
+// pb_fp8_quant_blocks.
+PB_API int pb_fp8_fakequant_blocks(const void* w, long ld, int rows, int K, void* out,
+                                   cudaStream_t st) {
+  if (rows <= 0 || K <= 0 || K % 128 != 0 || ld % 4 != 0 || out == nullptr) return PB_BAD_ARG;
+  dim3 grid(K / 128, (rows + 127) / 128);
+  f8::quant_blocks_kernel<<<grid, 256, 0, st>>>(static_cast<const bf16*>(w), ld, rows, K, nullptr,
+                                                nullptr, static_cast<bf16*>(out));
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -89,6 +89,7 @@ _SIGS = {
     "pb_moe_combine_bwd": [P, P, P, I, I, I, P, P],
     "pb_fp8_quant_rows": [P, L, I, I, P, P, P],
     "pb_fp8_quant_blocks": [P, L, I, I, P, P, P],
+    "pb_fp8_fakequant_blocks": [P, L, I, I, P, P],
     "pb_fp8_dequant_rows": [P, P, L, I, I, P, P, P],
     "pb_fp8_quant_rows_dyn": [P, L, I, I, P, P, P, P],
     "pb_swiglu_quant": [P, P, I, I, P, P, P, P],

@@ -32,15 +32,16 @@ def quantize_rows(x: Tensor, rows_used: Tensor | None = None):
     return q, s
 
 
-def swiglu_quantize(gu: Tensor, rows_used: Tensor | None = None):
+def swiglu_quantize(gu: Tensor, rows_used: Tensor | None = None, keep_bf16: bool = True):
     """gu [M, 2H] bf16 (gate | up, H % 128 == 0) -> (h [M, H] bf16, q [M, H] e4m3 bytes, scales
     [H / 128, M] fp32) in one pass: ``h = silu(gate) * up`` and the 1 x 128 block quantisation
     of those bf16 values, i.e. ``swiglu`` followed by ``quantize_rows`` without the second read.
-    ``rows_used`` (a device int32): only the first that many rows are touched."""
+    ``rows_used`` (a device int32): only the first that many rows are touched. ``keep_bf16=False``
+    skips the bf16 copy (``h`` comes back as ``None``)."""
     M, two_h = gu.shape
     H = two_h // 2
     assert gu.dtype == BF16 and gu.is_contiguous() and H % 128 == 0
-    h = torch.empty((M, H), dtype=BF16, device=gu.device)
+    h = torch.empty((M, H), dtype=BF16, device=gu.device) if keep_bf16 else None
     q = torch.empty((M, H), dtype=torch.uint8, device=gu.device)
     s = torch.empty((H // 128, M), dtype=torch.float32, device=gu.device)
     call("pb_swiglu_quant", ptr(gu), ptr(h), M, H, ptr(q), ptr(s), ptr(rows_used), stream_ptr())
@@ -61,6 +62,19 @@ def quantize_blocks(w: Tensor):
     if w.ndim == 3:
         s = s.view(w.shape[0], w.shape[1] // 128, K // 128)
     return q, s
+
+
+def fakequant_blocks(w: Tensor) -> Tensor:
+    """bf16 image of ``w`` after 128 x 128 block quantisation to e4m3 and back: the weight the FP8
+    GEMM really multiplied by. The backward of an FP8 linear differentiates against it."""
+    assert w.dtype == BF16 and w.is_contiguous() and w.shape[-1] % 128 == 0
+    K = w.shape[-1]
+    rows = w.numel() // K
+    if w.ndim == 3:
+        assert w.shape[1] % 128 == 0, "grouped weights need 128-aligned rows per expert"
+    out = torch.empty_like(w)
+    call("pb_fp8_fakequant_blocks", ptr(w), K, rows, K, ptr(out), stream_ptr())
+    return out
 
 
 def dequantize_rows(q: Tensor, s: Tensor) -> Tensor:
@@ -125,7 +139,10 @@ class _Fp8LinearFn(torch.autograd.Function):
         else:
             xq, sx = quantize_rows(x2)
         wq, sw = quantize_blocks(w)
-        ctx.save_for_backward(x2, w)
+        # the backward differentiates y = x^ w^^T, the product that was computed: it needs the
+        # quantised activations (kept as e4m3 + scales: half the bytes of x) and the quantised
+        # weight (re-made from w when the backward runs)
+        ctx.save_for_backward(xq, sx, w)
         ctx.w_ref = w
         ctx.xshape = x.shape
         return gemm_fp8(xq, sx, wq, sw).reshape(*x.shape[:-1], w.shape[0])
@@ -134,24 +151,29 @@ class _Fp8LinearFn(torch.autograd.Function):
     def backward(ctx, dy):
         from .functional import gemm
 
-        x2, w = ctx.saved_tensors
+        xq, sx, w = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        dx = gemm(dy2, w, b_mn=True).reshape(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, fakequant_blocks(w.contiguous()), b_mn=True).reshape(ctx.xshape)     # g w^
         dw = None
         if ctx.needs_input_grad[1]:
+            xh = dequantize_rows_bf16(xq, sx)                                                   # x^
             mg = getattr(ctx.w_ref, "main_grad", None)
             if mg is not None:
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, d=mg, beta=1.0)
+                gemm(dy2, xh, a_mn=True, b_mn=True, out=mg, d=mg, beta=1.0)
             else:
-                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+                dw = gemm(dy2, xh, a_mn=True, b_mn=True)
         return dx, dw, None
 
 
 def fp8_linear(x: Tensor, w: Tensor, xq=None) -> Tensor:
     """y = q(x) @ q(w)^T with 1 x 128 activation blocks and 128 x 128 weight blocks (w stored
-    (out, in)); straight-through bf16 gradients, fp32 ``main_grad`` accumulation as ``linear``.
+    (out, in)). Straight-through gradients on the quantised operands, ``gx = g w^``,
+    ``gw = g^T x^`` (reference kernels/__init__.py:849-944), as bf16 products; fp32
+    ``main_grad`` accumulation as ``linear``.
     ``xq``: ``(q, scales)`` of ``x`` when its producer already wrote them
     (``functional.add_rmsnorm(..., emit_fp8=True)``); the row quantiser is then skipped."""
     return _Fp8LinearFn.apply(x, w, xq)

@@ -153,20 +153,38 @@ class _MoeFfnFn(torch.autograd.Function):
             ids, gates = ids_r, gates_r
         pl = place(ids, E)
         xp = permute(x, pl)
-        gu = _expert_gemm(xp, w_gu, pl, fp8)
-        if fp8 and h % 128 == 0 and w_down.shape[1] % 128 == 0:
+        empty = x.new_empty(0)
+        # FP8 products keep their quantised inputs (e4m3 + scales) for the backward, which
+        # differentiates the product that was really computed: g w^ and g^T x^
+        q_gu = bool(fp8) and d % 128 == 0 and w_gu.shape[1] % 128 == 0
+        q_dn = bool(fp8) and h % 128 == 0 and w_down.shape[1] % 128 == 0
+        if q_gu:
+            from . import fp8 as F8
+
+            xq, sx = F8.quantize_rows(xp)
+            wq, sw = F8.quantize_blocks(w_gu.contiguous())
+            gu = F8.gemm_fp8(xq, sx, wq, sw, mblk_group=pl.mblk_group)
+            x_saved = (xq, sx)
+        else:
+            gu = grouped_gemm(xp, w_gu, pl)
+            x_saved = (xp, empty)
+        if q_dn:
             # SwiGLU and the e4m3 rows of its output in one pass
             from . import fp8 as F8
 
-            hs, hq, sh = F8.swiglu_quantize(gu)
+            _none, hq, sh = F8.swiglu_quantize(gu, keep_bf16=False)
             wq, sw = F8.quantize_blocks(w_down.contiguous())
             y = F8.gemm_fp8(hq, sh, wq, sw, mblk_group=pl.mblk_group)
+            h_saved = (hq, sh)
         else:
             hs = torch.empty((pl.rows, h), dtype=BF16, device=x.device)
             call("pb_swiglu_fwd", ptr(gu), ptr(hs), pl.rows, h, stream_ptr())
-            y = _expert_gemm(hs, w_down, pl, fp8)
+            y = grouped_gemm(hs, w_down, pl)
+            h_saved = (hs, empty)
         out = combine(y, pl, gates, T)
-        ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids_r, gates, xp, gu, hs, y)
+        ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids_r, gates, x_saved[0], x_saved[1], gu,
+                              h_saved[0], h_saved[1], y)
+        ctx.q_gu, ctx.q_dn = q_gu, q_dn
         ctx.pl = pl
         ctx.refs = (router_w, w_gu_p, w_down_p)
         ctx.top_k = top_k
@@ -177,8 +195,15 @@ class _MoeFfnFn(torch.autograd.Function):
     def backward(ctx, d_out, d_probs, _di, d_logits=None):
         from .functional import gemm
 
-        x, router_w, w_gu, w_down, probs, ids, gates, xp, gu, hs, y = ctx.saved_tensors
+        x, router_w, w_gu, w_down, probs, ids, gates, xs0, xs1, gu, hs0, hs1, y = ctx.saved_tensors
         router_ref, gu_ref, down_ref = ctx.refs
+        if ctx.q_gu or ctx.q_dn:
+            from . import fp8 as F8
+        # operands of the straight-through backward: the quantised ones where the forward was FP8
+        xp = F8.dequantize_rows_bf16(xs0, xs1) if ctx.q_gu else xs0
+        hs = F8.dequantize_rows_bf16(hs0, hs1) if ctx.q_dn else hs0
+        wd_b = F8.fakequant_blocks(w_down.contiguous()) if ctx.q_dn else w_down
+        wg_b = F8.fakequant_blocks(w_gu.contiguous()) if ctx.q_gu else w_gu
         pl = ctx.pl
         T, d = x.shape
         E_all, two_h, _ = w_gu.shape
@@ -191,12 +216,14 @@ class _MoeFfnFn(torch.autograd.Function):
         call("pb_moe_combine_bwd", ptr(y), ptr(d_out), ptr(pl.row_of), T * k, k, d, ptr(dgates),
              stream_ptr())
         dyp = permute(d_out, pl, scale=gates.reshape(-1))
-        dh = grouped_gemm(dyp, w_down, pl, b_mn=True)
+        dh = grouped_gemm(dyp, wd_b, pl, b_mn=True)
         g_down = _acc_grad(down_ref, w_down.shape, lambda o, acc: grouped_wgrad(dyp, hs, pl, o, acc))
+        del hs, wd_b
         dgu = torch.empty_like(gu)
         call("pb_swiglu_bwd", ptr(dh), ptr(gu), ptr(dgu), pl.rows, h, stream_ptr())
         g_gu = _acc_grad(gu_ref, w_gu.shape, lambda o, acc: grouped_wgrad(dgu, xp, pl, o, acc))
-        dxp = grouped_gemm(dgu, w_gu, pl, b_mn=True)
+        dxp = grouped_gemm(dgu, wg_b, pl, b_mn=True)
+        del xp, wg_b
         dlogits = torch.empty((T, E), dtype=torch.float32, device=x.device)
         dg_r = dgates if k_r == k else dgates[:, :k_r].contiguous()
         g_r = gates if k_r == k else gates[:, :k_r].contiguous()
@@ -220,24 +247,13 @@ class _MoeFfnFn(torch.autograd.Function):
         return dx, g_router, None, g_gu, g_down, None, None, None, None
 
 
-def _expert_gemm(a: Tensor, w: Tensor, pl: Placement, use_fp8: bool) -> Tensor:
-    """Forward expert product: bf16 grouped GEMM, or 1 x 128 / 128 x 128 block-scaled FP8 when
-    the shapes allow (contraction and output width multiples of 128)."""
-    if use_fp8 and a.shape[1] % 128 == 0 and w.shape[1] % 128 == 0:
-        from . import fp8
-
-        aq, sa = fp8.quantize_rows(a)
-        wq, sw = fp8.quantize_blocks(w.contiguous())
-        return fp8.gemm_fp8(aq, sa, wq, sw, mblk_group=pl.mblk_group)
-    return grouped_gemm(a, w, pl)
-
-
 def moe_ffn(x: Tensor, router_w: Tensor, router_bias: Tensor | None, w_gu: Tensor, w_down: Tensor,
             top_k: int, n_shared: int = 0, shapes=None, fp8: bool = False, return_logits: bool = False):
     """Routed (+ shared) expert FFN. x [T, d] bf16; router_w [E, d]; w_gu [E + n_shared, 2h, d]
     (gate rows then up rows per expert; the shared experts last); w_down [E + n_shared, d, h].
     ``shapes`` gives those two 3-D shapes when the weights are passed as flat 2-D parameters.
-    ``fp8``: forward expert products in block-scaled FP8 (straight-through bf16 backward).
+    ``fp8``: forward expert products in block-scaled FP8; the backward is straight-through on the
+    quantised operands (``g w^``, ``g^T x^``) as bf16 products.
     Returns (out [T, d], probs [T, E] fp32, ids [T, k] int32); out and probs are differentiable.
     ``return_logits`` appends the router logits [T, E] fp32 (differentiable: the router z-loss)."""
     res = _MoeFfnFn.apply(x, router_w, router_bias, w_gu, w_down, int(top_k), int(n_shared), shapes,

@@ -201,18 +201,20 @@ class _EpMoeFn(torch.autograd.Function):
             gu = M.grouped_gemm(xp, w_gu, pl)
             saved_x = (xp, xp.new_empty(0))
         if use_fp8:
-            hs, hq, sh = F8.swiglu_quantize(gu, used)      # SwiGLU and its e4m3 rows in one pass
+            _none, hq, sh = F8.swiglu_quantize(gu, used, keep_bf16=False)   # SwiGLU -> e4m3 rows in one pass
             wq, sw = F8.quantize_blocks(w_down.contiguous())
             F8.gemm_fp8(hq, sh, wq, sw, mblk_group=pl.mblk_group, out=ep.y_local)
+            saved_h = (hq, sh)         # the backward differentiates against the quantised rows
         else:
             hs = torch.empty((pl.rows, h), dtype=BF16, device=x.device)
             call("pb_swiglu_fwd_dyn", ptr(gu), ptr(hs), pl.rows, h, ptr(used), stream_ptr())
             M.grouped_gemm(hs, w_down, pl, out=ep.y_local)
+            saved_h = (hs, hs.new_empty(0))
         y = _copy_used(ep.y_local, used)        # the gate gradient needs <y_row, dy_row> later
         sym.barrier(6)                          # results are ready to be pulled
         out = ep.combine(dest_rank, dest_row, gates, T, top_k)
         ctx.save_for_backward(x, router_w, w_gu, w_down, probs, ids, gates, saved_x[0], saved_x[1], gu,
-                              hs, y, dest_rank, dest_row, send_base)
+                              saved_h[0], saved_h[1], y, dest_rank, dest_row, send_base)
         ctx.pl, ctx.local, ctx.ep, ctx.use_fp8 = pl, local, ep, use_fp8
         ctx.refs = (router_w, w_gu_p, w_down_p)
         ctx.mark_non_differentiable(ids)
@@ -223,7 +225,7 @@ class _EpMoeFn(torch.autograd.Function):
         from ..ops import fp8 as F8
         from ..ops.functional import gemm
 
-        (x, router_w, w_gu, w_down, probs, ids, gates, xs0, xs1, gu, hs, y, dest_rank, dest_row,
+        (x, router_w, w_gu, w_down, probs, ids, gates, xs0, xs1, gu, hs0, hs1, y, dest_rank, dest_row,
          send_base) = ctx.saved_tensors
         router_ref, gu_ref, down_ref = ctx.refs
         pl, local, ep = ctx.pl, ctx.local, ctx.ep
@@ -240,14 +242,20 @@ class _EpMoeFn(torch.autograd.Function):
         dyp = ep.x_local            # read in place: nobody overwrites it before slot 6 below
         used = pl.expert_off[ep.El:]
         call("pb_ep_rowdot", ptr(y), ptr(dyp), ptr(used), pl.rows, d, ptr(ep.dot_local), stream_ptr())
-        dh = M.grouped_gemm(dyp, w_down, pl, b_mn=True)
+        # straight-through on what the FP8 products multiplied: quantised weights and rows
+        wd_b = F8.fakequant_blocks(w_down.contiguous()) if ctx.use_fp8 else w_down
+        dh = M.grouped_gemm(dyp, wd_b, pl, b_mn=True)
+        hs = F8.dequantize_rows_bf16(hs0, hs1, used) if ctx.use_fp8 else hs0
         g_down = M._acc_grad(down_ref, w_down.shape, lambda o, acc: M.grouped_wgrad(dyp, hs, pl, o, acc))
+        del hs, wd_b
         dgu = torch.empty_like(gu)
         call("pb_swiglu_bwd_dyn", ptr(dh), ptr(gu), ptr(dgu), pl.rows, h, ptr(used), stream_ptr())
         xp = F8.dequantize_rows_bf16(xs0, xs1, used) if ctx.use_fp8 else xs0
         g_gu = M._acc_grad(gu_ref, w_gu.shape, lambda o, acc: M.grouped_wgrad(dgu, xp, pl, o, acc))
         del xp
-        M.grouped_gemm(dgu, w_gu, pl, b_mn=True, out=ep.y_local)
+        wg_b = F8.fakequant_blocks(w_gu.contiguous()) if ctx.use_fp8 else w_gu
+        M.grouped_gemm(dgu, wg_b, pl, b_mn=True, out=ep.y_local)
+        del wg_b
         sym.barrier(6)
         dgates = torch.empty((T, k), dtype=torch.float32, device=x.device)
         call("pb_ep_pull_scalar", ep.dotbuf.ptrs, ep.world, ptr(dest_rank), ptr(dest_row), ptr(gflat),
@@ -281,7 +289,7 @@ def ep_moe_ffn(x: Tensor, router_w: Tensor, router_bias: Tensor | None, w_gu_loc
     rank of the group must call it (same layer order), forward and backward. ``return_logits``
     appends the router logits [T, E] fp32 (differentiable). ``fp8``: tokens cross NVLink as e4m3
     rows + 1 x 128 scales and both expert products run on the block-scaled FP8 GEMM
-    (straight-through bf16 backward against the quantised rows)."""
+    (straight-through backward on the quantised rows and weights, as bf16 products)."""
     res = _EpMoeFn.apply(x, router_w, router_bias, w_gu_local, w_down_local, int(top_k), ep, shapes,
                          bool(fp8))
     return res if return_logits else res[:3]
