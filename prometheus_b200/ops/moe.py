@@ -200,10 +200,9 @@ class _MoeFfnFn(torch.autograd.Function):
         if ctx.q_gu or ctx.q_dn:
             from . import fp8 as F8
         # operands of the straight-through backward: the quantised ones where the forward was FP8
-        xp = F8.dequantize_rows_bf16(xs0, xs1) if ctx.q_gu else xs0
+        # (each made just before its use, so that only one pair is alive at a time)
         hs = F8.dequantize_rows_bf16(hs0, hs1) if ctx.q_dn else hs0
         wd_b = F8.fakequant_blocks(w_down.contiguous()) if ctx.q_dn else w_down
-        wg_b = F8.fakequant_blocks(w_gu.contiguous()) if ctx.q_gu else w_gu
         pl = ctx.pl
         T, d = x.shape
         E_all, two_h, _ = w_gu.shape
@@ -221,6 +220,8 @@ class _MoeFfnFn(torch.autograd.Function):
         del hs, wd_b
         dgu = torch.empty_like(gu)
         call("pb_swiglu_bwd", ptr(dh), ptr(gu), ptr(dgu), pl.rows, h, stream_ptr())
+        xp = F8.dequantize_rows_bf16(xs0, xs1) if ctx.q_gu else xs0
+        wg_b = F8.fakequant_blocks(w_gu.contiguous()) if ctx.q_gu else w_gu
         g_gu = _acc_grad(gu_ref, w_gu.shape, lambda o, acc: grouped_wgrad(dgu, xp, pl, o, acc))
         dxp = grouped_gemm(dgu, wg_b, pl, b_mn=True)
         del xp, wg_b
