@@ -368,9 +368,16 @@ def main() -> int:
     if args.config == "dense" and not args.no_secondary and (not args.layers or args.secondary_layers):
         # the 16B FP8 mixture-of-experts configuration, expert parallel over the same ranks, in
         # the same run wherever it fits
-        sec = measure(args, "moe16b", world, rank, local_rank, dev, max(2, min(args.steps, 3)), 3,
-                      with_clocks=False, with_exposed=False)
-        if "skipped" in sec:
+        # a failure here (out of memory, a latched device status) must not cost the primary
+        # measurement its line: it is reported under secondary.moe16b.error instead
+        try:
+            sec = measure(args, "moe16b", world, rank, local_rank, dev, max(2, min(args.steps, 3)), 3,
+                          with_clocks=False, with_exposed=False)
+        except Exception as e:          # noqa: BLE001
+            sec = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+        if "error" in sec:
+            secondary["moe16b"] = {"value": None, "error": sec["error"]}
+        elif "skipped" in sec:
             secondary["moe16b"] = {"value": None, "skipped": sec["skipped"],
                                    "bytes_needed_per_rank": sec["bytes_needed_per_rank"]}
         else:
