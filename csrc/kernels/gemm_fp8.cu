@@ -312,22 +312,39 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const bf16* __restrict_
   for (long row = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < m_eff;
        row += warps) {
     const bf16* src = x + static_cast<size_t>(row) * ld;
-    for (int c0 = 0; c0 < K; c0 += 512) {
-      const int c = c0 + lane * 16;
-      const bool active = c < K;
-      float f[16];
-      if (active) {
-        unpack8(*reinterpret_cast<const bf16x8*>(src + c), f);
-        unpack8(*reinterpret_cast<const bf16x8*>(src + c + 8), f + 8);
-      } else {
+    // up to four 512-element steps of the row are loaded before the first one is quantised
+    // (one memory latency per 2048 elements); every lane runs every step (the shuffles in
+    // quant16 name the whole warp)
+    for (int c00 = 0; c00 < K; c00 += 2048) {
+      bf16x8 raw[4][2];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) f[j] = 0.f;
+      for (int u = 0; u < 4; ++u) {
+        const int c = c00 + u * 512 + lane * 16;
+        if (c < K) {
+          raw[u][0] = *reinterpret_cast<const bf16x8*>(src + c);
+          raw[u][1] = *reinterpret_cast<const bf16x8*>(src + c + 8);
+        }
       }
-      float scale;
-      const uint4 pk = quant16(f, active, &scale);
-      if (active) {
-        *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + c) = pk;
-        if ((lane & 7) == 0) scales[static_cast<size_t>(c >> 7) * M + row] = scale;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c0 = c00 + u * 512;
+        if (c0 >= K) continue;               // uniform over the warp
+        const int c = c0 + lane * 16;
+        const bool active = c < K;
+        float f[16];
+        if (active) {
+          unpack8(raw[u][0], f);
+          unpack8(raw[u][1], f + 8);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) f[j] = 0.f;
+        }
+        float scale;
+        const uint4 pk = quant16(f, active, &scale);
+        if (active) {
+          *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + c) = pk;
+          if ((lane & 7) == 0) scales[static_cast<size_t>(c >> 7) * M + row] = scale;
+        }
       }
     }
   }
@@ -438,50 +455,61 @@ __global__ void __launch_bounds__(256) dequant_rows_kernel(const uint8_t* __rest
 // q / scales may be null when only `deq` is wanted. deq (may be null): bf16 [N, K] image of the
 // quantised block, e4m3(w / scale) * scale: the operand the FP8 GEMM really multiplied, which is
 // what the backward of an FP8 linear differentiates against.
-__global__ void quant_blocks_kernel(const bf16* __restrict__ w, long ld, int N, int K,
-                                    uint8_t* __restrict__ q, float* __restrict__ scales,
-                                    bf16* __restrict__ deq) {
+__global__ void __launch_bounds__(256)
+quant_blocks_kernel(const bf16* __restrict__ w, long ld, int N, int K, uint8_t* __restrict__ q,
+                    float* __restrict__ scales, bf16* __restrict__ deq) {
+  // The 128 x 128 block is read once: thread t keeps 16 consecutive elements of four rows
+  // (rows t / 8 + 32 i, columns 16 (t % 8) ..) in registers across the block-wide maximum.
   __shared__ float red[33];
   const int nb = blockIdx.y, kb = blockIdx.x;
-  const int r0 = nb * 128, c0 = kb * 128;
+  const int r0 = nb * 128 + (threadIdx.x >> 3), c = kb * 128 + (threadIdx.x & 7) * 16;
+  const bool vec_ok = (ld % 8) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+  float v[4][16];
   float amax = 0.f;
-  for (int i = threadIdx.x; i < 128 * 32; i += blockDim.x) {
-    const int r = r0 + i / 32, c = c0 + (i % 32) * 4;
-    if (r < N && c < K) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(w + static_cast<size_t>(r) * ld + c);
-      const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-      const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-      amax = fmaxf(amax, fmaxf(fmaxf(fabsf(__low2float(p0)), fabsf(__high2float(p0))),
-                               fmaxf(fabsf(__low2float(p1)), fabsf(__high2float(p1)))));
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + 32 * i;
+    if (r < N && c < K) {                      // K is a multiple of 128: the 16 columns are in range
+      const bf16* src = w + static_cast<size_t>(r) * ld + c;
+      if (vec_ok) {
+        unpack8(*reinterpret_cast<const bf16x8*>(src), v[i]);
+        unpack8(*reinterpret_cast<const bf16x8*>(src + 8), v[i] + 8);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[i][j] = __bfloat162float(src[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
     }
   }
   amax = block_max(amax, red);
   const float scale = amax > 0.f ? amax / 448.f : 1.f;
-  for (int i = threadIdx.x; i < 128 * 32; i += blockDim.x) {
-    const int r = r0 + i / 32, c = c0 + (i % 32) * 4;
-    if (r < N && c < K) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(w + static_cast<size_t>(r) * ld + c);
-      const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-      const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-      const uint32_t packed =
-          to_e4m3x4(__fdiv_rn(__low2float(p0), scale), __fdiv_rn(__high2float(p0), scale),
-                    __fdiv_rn(__low2float(p1), scale), __fdiv_rn(__high2float(p1), scale));
-      if (q != nullptr) *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(r) * K + c) = packed;
-      if (deq != nullptr) {
-        float f[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + 32 * i;
+    if (r >= N || c >= K) continue;
+    uint32_t pk[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      pk[g] = to_e4m3x4(__fdiv_rn(v[i][4 * g], scale), __fdiv_rn(v[i][4 * g + 1], scale),
+                        __fdiv_rn(v[i][4 * g + 2], scale), __fdiv_rn(v[i][4 * g + 3], scale));
+    if (q != nullptr)
+      *reinterpret_cast<uint4*>(q + static_cast<size_t>(r) * K + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    if (deq != nullptr) {
+      float f[16];
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(
-              static_cast<__nv_fp8x2_storage_t>((packed >> (16 * hh)) & 0xffffu), __NV_E4M3);
-          const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-          f[2 * hh] = v.x * scale;
-          f[2 * hh + 1] = v.y * scale;
+              static_cast<__nv_fp8x2_storage_t>((pk[g] >> (16 * hh)) & 0xffffu), __NV_E4M3);
+          const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+          f[4 * g + 2 * hh] = t.x * scale;
+          f[4 * g + 2 * hh + 1] = t.y * scale;
         }
-        uint2 o;
-        *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(f[0], f[1]);
-        *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(f[2], f[3]);
-        *reinterpret_cast<uint2*>(deq + static_cast<size_t>(r) * K + c) = o;
-      }
+      bf16* dst = deq + static_cast<size_t>(r) * K + c;
+      *reinterpret_cast<bf16x8*>(dst) = pack8(f);
+      *reinterpret_cast<bf16x8*>(dst + 8) = pack8(f + 8);
     }
   }
   if (threadIdx.x == 0 && scales != nullptr) scales[static_cast<size_t>(nb) * gridDim.x + kb] = scale;
