@@ -25,16 +25,19 @@ constexpr int MAX_E = 512;
 constexpr int MAX_K = 32;
 
 // One warp per token. logits: [T, E] fp32. bias: [E] or null (selection only).
+// PER = experts per lane the instantiation is unrolled for (2 covers 64 experts: a quarter of
+// the compare / select work of the 512-expert form for the same result).
+template <int PER>
 __global__ void route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                              int T, int E, int k, float* __restrict__ probs, int* __restrict__ ids,
                              float* __restrict__ gates) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= T) return;
   const float* row = logits + static_cast<size_t>(warp) * E;
-  float p[MAX_E / 32], s[MAX_E / 32];
+  float p[PER], s[PER];
   const int per = (E + 31) / 32;
 #pragma unroll
-  for (int i = 0; i < MAX_E / 32; ++i) {
+  for (int i = 0; i < PER; ++i) {
     const int e = i * 32 + lane;
     if (i < per && e < E) {
       p[i] = 1.f / (1.f + expf(-row[e]));
@@ -52,7 +55,7 @@ __global__ void route_kernel(const float* __restrict__ logits, const float* __re
     float bv = -INFINITY;
     int be = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < MAX_E / 32; ++i) {
+    for (int i = 0; i < PER; ++i) {
       const int e = i * 32 + lane;
       if (i < per && s[i] > bv) { bv = s[i]; be = e; }
     }
@@ -65,7 +68,7 @@ __global__ void route_kernel(const float* __restrict__ logits, const float* __re
     // owner lane retires the winner and reports its probability
     float pv = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_E / 32; ++i)
+    for (int i = 0; i < PER; ++i)
       if (i * 32 + lane == be) { pv = p[i]; s[i] = -INFINITY; }
     pv = __shfl_sync(0xffffffffu, pv, be & 31);
     if (lane == j) mine = pv;
@@ -289,7 +292,12 @@ static inline int warps_grid(long warps, int threads) {
 PB_API int pb_moe_route(const float* logits, const float* bias, int T, int E, int k, float* probs,
                         int* ids, float* gates, cudaStream_t st) {
   if (T <= 0 || E <= 0 || E > moe::MAX_E || k <= 0 || k > moe::MAX_K || k > E) return PB_BAD_ARG;
-  moe::route_kernel<<<warps_grid(T, 256), 256, 0, st>>>(logits, bias, T, E, k, probs, ids, gates);
+  const int per = (E + 31) / 32;
+  const int grid = warps_grid(T, 256);
+  if (per <= 2) moe::route_kernel<2><<<grid, 256, 0, st>>>(logits, bias, T, E, k, probs, ids, gates);
+  else if (per <= 4) moe::route_kernel<4><<<grid, 256, 0, st>>>(logits, bias, T, E, k, probs, ids, gates);
+  else if (per <= 8) moe::route_kernel<8><<<grid, 256, 0, st>>>(logits, bias, T, E, k, probs, ids, gates);
+  else moe::route_kernel<moe::MAX_E / 32><<<grid, 256, 0, st>>>(logits, bias, T, E, k, probs, ids, gates);
   return static_cast<int>(cudaGetLastError());
 }
 
