@@ -188,28 +188,13 @@ __global__ void ep_dispatch_fp8_kernel(const bf16* __restrict__ src, long ld_src
   // Every lane runs every iteration (the shuffles below name the whole warp); lanes past the
   // end of a row narrower than 512 elements only take part in the shuffles. d is a multiple
   // of 128, so the eight lanes of a block are active or idle together.
-  // The loads of up to 2048 elements of the row (four steps) are issued before the first step is
-  // quantised, so the row costs one memory latency.
-  for (int c00 = 0; c00 < d; c00 += 2048) {
-  bf16x8 raw[4][2];
-#pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    const int c = c00 + u * 512 + lane * 16;
-    if (c < d) {
-      raw[u][0] = *reinterpret_cast<const bf16x8*>(s + c);
-      raw[u][1] = *reinterpret_cast<const bf16x8*>(s + c + 8);
-    }
-  }
-#pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    const int c0 = c00 + u * 512;
-    if (c0 >= d) continue;                     // uniform over the warp: no lane shuffles alone
+  for (int c0 = 0; c0 < d; c0 += 512) {
     const int c = c0 + lane * 16;
     const bool active = c < d;
     float f[16];
     if (active) {
-      unpack8(raw[u][0], f);
-      unpack8(raw[u][1], f + 8);
+      unpack8(*reinterpret_cast<const bf16x8*>(s + c), f);
+      unpack8(*reinterpret_cast<const bf16x8*>(s + c + 8), f + 8);
     } else {
 #pragma unroll
       for (int j = 0; j < 16; ++j) f[j] = 0.f;
@@ -229,7 +214,6 @@ __global__ void ep_dispatch_fp8_kernel(const bf16* __restrict__ src, long ld_src
     pk.w = ep_e4m3x4(__fdiv_rn(f[12], scale), __fdiv_rn(f[13], scale), __fdiv_rn(f[14], scale), __fdiv_rn(f[15], scale));
     *reinterpret_cast<uint4*>(oq + c) = pk;
     if ((lane & 7) == 0) os[static_cast<size_t>(c >> 7) * max_rows + row] = scale;
-  }
   }
   if (arrived.p[q] != nullptr) {
     // fused mode: tell the owner's GEMM that one more row of this 128-row block has landed.

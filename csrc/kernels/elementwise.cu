@@ -582,11 +582,6 @@ __device__ __forceinline__ float tanh_fast(float x) {
   return y;
 }
 
-// At most two rows per SM (the launcher asks for 100 KB of dynamic shared memory that the kernel
-// does not touch, only to cap the residency): the rows in flight (296 x 256 KB at a vocabulary
-// of 131072) then fit in the L2 cache, so the second pass over a row does not go back to HBM.
-// Both passes keep four 16-byte loads per thread in flight.
-constexpr int CE_RESIDENCY_SMEM = 100 * 1024;
 __global__ void __launch_bounds__(512) softcap_ce_kernel(bf16* __restrict__ logits,
                                                          const int* __restrict__ targets,
                                                          const float* __restrict__ wt,
@@ -627,23 +622,13 @@ __global__ void __launch_bounds__(512) softcap_ce_kernel(bf16* __restrict__ logi
     shift = block_max(m, scratch);
   }
   float s = 0.f;
-  for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * blockDim.x) {
-    bf16x8 raw[4];
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(p)[v], f);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int v = v0 + u * blockDim.x;
-      if (v < nvec) raw[u] = reinterpret_cast<const bf16x8*>(p)[v];
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      if (v0 + u * blockDim.x >= nvec) continue;
-      float f[8];
-      unpack8(raw[u], f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float c = cap > 0.f ? cap * tanh_fast(f[i] * inv_cap) : f[i];
-        s += __expf(c - shift);
-      }
+    for (int i = 0; i < 8; ++i) {
+      const float c = cap > 0.f ? cap * tanh_fast(f[i] * inv_cap) : f[i];
+      s += __expf(c - shift);
     }
   }
   s = block_sum(s, scratch);
@@ -658,31 +643,20 @@ __global__ void __launch_bounds__(512) softcap_ce_kernel(bf16* __restrict__ logi
   if (!write_grad) return;
   const float inv_s = 1.f / s;
   __syncthreads();  // the target element is read above before anyone overwrites it
-  for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * blockDim.x) {
-    bf16x8 raw[4];
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(p)[v], f);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int v = v0 + u * blockDim.x;
-      if (v < nvec) raw[u] = reinterpret_cast<const bf16x8*>(p)[v];
+    for (int i = 0; i < 8; ++i) {
+      const float t = cap > 0.f ? tanh_fast(f[i] * inv_cap) : 0.f;
+      const float c = cap > 0.f ? cap * t : f[i];
+      float g = __expf(c - shift) * inv_s;
+      if (v * 8 + i == tgt) g -= 1.f;
+      g *= w;
+      if (cap > 0.f) g *= (1.f - t * t);
+      f[i] = g;
     }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int v = v0 + u * blockDim.x;
-      if (v >= nvec) continue;
-      float f[8];
-      unpack8(raw[u], f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float t = cap > 0.f ? tanh_fast(f[i] * inv_cap) : 0.f;
-        const float c = cap > 0.f ? cap * t : f[i];
-        float g = __expf(c - shift) * inv_s;
-        if (v * 8 + i == tgt) g -= 1.f;
-        g *= w;
-        if (cap > 0.f) g *= (1.f - t * t);
-        f[i] = g;
-      }
-      reinterpret_cast<bf16x8*>(p)[v] = pack8(f);
-    }
+    reinterpret_cast<bf16x8*>(p)[v] = pack8(f);
   }
 }
 
@@ -915,14 +889,7 @@ PB_API int pb_softcap_ce(void* logits, const void* targets, const void* wt, void
                          void* lse_rows, long rows, int V, float cap, int write_grad,
                          cudaStream_t st) {
   if (V % 8 != 0 || rows <= 0) return PB_BAD_ARG;
-  static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
-  if (attr_once.need()) {
-    cudaError_t e = cudaFuncSetAttribute(softcap_ce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         CE_RESIDENCY_SMEM);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_once.done();
-  }
-  softcap_ce_kernel<<<static_cast<unsigned>(rows), 512, CE_RESIDENCY_SMEM, st>>>(
+  softcap_ce_kernel<<<static_cast<unsigned>(rows), 512, 0, st>>>(
       static_cast<bf16*>(logits), static_cast<const int*>(targets),
       static_cast<const float*>(wt), static_cast<float*>(loss_rows),
       static_cast<float*>(lse_rows), V, cap, write_grad);

@@ -312,39 +312,22 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const bf16* __restrict_
   for (long row = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < m_eff;
        row += warps) {
     const bf16* src = x + static_cast<size_t>(row) * ld;
-    // up to four 512-element steps of the row are loaded before the first one is quantised
-    // (one memory latency per 2048 elements); every lane runs every step (the shuffles in
-    // quant16 name the whole warp)
-    for (int c00 = 0; c00 < K; c00 += 2048) {
-      bf16x8 raw[4][2];
+    for (int c0 = 0; c0 < K; c0 += 512) {
+      const int c = c0 + lane * 16;
+      const bool active = c < K;
+      float f[16];
+      if (active) {
+        unpack8(*reinterpret_cast<const bf16x8*>(src + c), f);
+        unpack8(*reinterpret_cast<const bf16x8*>(src + c + 8), f + 8);
+      } else {
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = c00 + u * 512 + lane * 16;
-        if (c < K) {
-          raw[u][0] = *reinterpret_cast<const bf16x8*>(src + c);
-          raw[u][1] = *reinterpret_cast<const bf16x8*>(src + c + 8);
-        }
+        for (int j = 0; j < 16; ++j) f[j] = 0.f;
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c0 = c00 + u * 512;
-        if (c0 >= K) continue;               // uniform over the warp
-        const int c = c0 + lane * 16;
-        const bool active = c < K;
-        float f[16];
-        if (active) {
-          unpack8(raw[u][0], f);
-          unpack8(raw[u][1], f + 8);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) f[j] = 0.f;
-        }
-        float scale;
-        const uint4 pk = quant16(f, active, &scale);
-        if (active) {
-          *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + c) = pk;
-          if ((lane & 7) == 0) scales[static_cast<size_t>(c >> 7) * M + row] = scale;
-        }
+      float scale;
+      const uint4 pk = quant16(f, active, &scale);
+      if (active) {
+        *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + c) = pk;
+        if ((lane & 7) == 0) scales[static_cast<size_t>(c >> 7) * M + row] = scale;
       }
     }
   }
