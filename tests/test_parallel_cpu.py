@@ -218,3 +218,49 @@ def test_pipeline_train_single_stage_and_errors():
     assert lin.weight.grad is not None and torch.isfinite(total)
     with pytest.raises(P.MeshError):
         P.spmd_pipeline_train(xs, 2, lambda s, x: x, lambda y, m: y.sum())
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_zigzag_split_chain_and_balance(world):
+    """The zig-zag layout on the CPU definitions: rank r holds half-slices r and 2 world - 1 - r;
+    the delta-rule states entering every half-slice, folded in chain order from the half-slice
+    maps, reproduce the serial scan when the per-rank outputs are put back in sequence order; and
+    the causal-attention work per rank is the same for every rank."""
+    from prometheus_b200.parallel.cp import zigzag_positions, zigzag_slice
+
+    b, h, d = 1, 2, 16
+    half = 32
+    s = 2 * world * half
+    g = torch.Generator().manual_seed(world)
+    k = torch.nn.functional.normalize(torch.randn(b, s, h, d, generator=g), dim=-1)
+    q = torch.nn.functional.normalize(torch.randn(b, s, h, d, generator=g), dim=-1)
+    v = torch.randn(b, s, h, d, generator=g)
+    beta = torch.rand(b, s, h, generator=g)
+    o_ref, _ = kernels.delta_rule_recurrent(q, k, v, beta)
+    # every chain position's map, as the owning rank would build it from its local tensors
+    maps = [None] * (2 * world)
+    local = {}
+    for r in range(world):
+        lq, lk, lv, lb = (zigzag_slice(t, world, r) for t in (q, k, v, beta))
+        assert lq.shape[1] == 2 * half
+        local[r] = (lq, lk, lv, lb)
+        for which, pos in enumerate(zigzag_positions(world, r)):
+            sl = slice(which * half, (which + 1) * half)
+            maps[pos] = cp.slice_affine_map(lk[:, sl], lv[:, sl], lb[:, sl], chunk=16)
+            torch.testing.assert_close(lq[:, sl], q[:, pos * half:(pos + 1) * half])
+    incoming = P.delta_state_handoff(maps)                       # fold over the 2 x world positions
+    out = torch.empty_like(o_ref)
+    for r in range(world):
+        lq, lk, lv, lb = local[r]
+        for which, pos in enumerate(zigzag_positions(world, r)):
+            sl = slice(which * half, (which + 1) * half)
+            o, _ = kernels.chunked_delta_rule(lq[:, sl], lk[:, sl], lv[:, sl], lb[:, sl], incoming[pos],
+                                              kernels.LinearAttnConfig(chunk=16))
+            out[:, pos * half:(pos + 1) * half] = o
+    torch.testing.assert_close(out, o_ref, rtol=1e-4, atol=1e-4)
+    # causal work in units of half-slice blocks: position p attends p + 1/2 blocks
+    work = [sum(p + 0.5 for p in zigzag_positions(world, r)) for r in range(world)]
+    assert len(set(work)) == 1 and work[0] == world
+    assert sorted(p for r in range(world) for p in zigzag_positions(world, r)) == list(range(2 * world))
+    with pytest.raises(P.MeshError):
+        zigzag_slice(q[:, :s - 1], world, 0)
