@@ -260,7 +260,7 @@ def test_zigzag_split_chain_and_balance(world):
     torch.testing.assert_close(out, o_ref, rtol=1e-4, atol=1e-4)
     # causal work in units of half-slice blocks: position p attends p + 1/2 blocks
     work = [sum(p + 0.5 for p in zigzag_positions(world, r)) for r in range(world)]
-    assert len(set(work)) == 1 and work[0] == world
+    assert len(set(work)) == 1 and work[0] == 2 * world
     assert sorted(p for r in range(world) for p in zigzag_positions(world, r)) == list(range(2 * world))
     with pytest.raises(P.MeshError):
         zigzag_slice(q[:, :s - 1], world, 0)
