@@ -163,13 +163,29 @@ def _from_chunks(x: Tensor, b: int, h: int, n: int) -> Tensor:
 
 
 def scan_segments(n_seq: int, n_chunks: int, ctas: int = 148) -> int:
-    """Segments per sequence for the state walk: one CTA walks one segment, so a batch with
-    fewer (batch, head) sequences than the GPU has SMs is cut until the CTAs fill it (powers of
-    two, at least four chunks per segment). 1 means the plain single-pass walk."""
-    seg = 1
-    while n_seq * seg * 2 <= ctas and n_chunks % (seg * 2) == 0 and n_chunks // (seg * 2) >= 4:
+    """Segments per sequence for the state walk, chosen by a cost model in units of one chunk
+    step of one CTA wave. The single-pass walk costs ``waves(n_seq) * n_chunks``. With ``seg``
+    segments the summary launch has two CTAs per segment and does about 0.6 of a chunk step
+    per chunk (three of the six products, no stores), the segmented walk one step per chunk,
+    and the two extra launches plus the fold about 24 steps of start-up (tensor-memory
+    allocation, first loads, state load / store: measured at about ten chunk steps per launch):
+
+        waves(2 n_seq seg) * 0.6 n_chunks / seg  +  waves(n_seq seg) * n_chunks / seg  +  24
+
+    The smallest power of two (at least four chunks per segment) that beats the single pass
+    by a fifth is taken; 1 means the plain single-pass walk."""
+    def waves(c):
+        return -(-c // ctas)
+
+    best, best_cost = 1, float(waves(n_seq) * n_chunks)
+    seg = 2
+    while n_chunks % seg == 0 and n_chunks // seg >= 4:
+        per = n_chunks / seg
+        cost = waves(2 * n_seq * seg) * 0.6 * per + waves(n_seq * seg) * per + 24.0
+        if cost < 0.8 * best_cost and cost < best_cost:
+            best, best_cost = seg, cost
         seg *= 2
-    return seg
+    return best
 
 
 class _DeltaFusedFn(torch.autograd.Function):

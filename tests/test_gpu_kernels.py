@@ -368,7 +368,8 @@ def test_delta_rule_segmented_walk_equals_single_pass(B, S, H, seg):
     from prometheus_b200.ops import functional as ops
     from prometheus_b200.ops.delta import delta_rule_fused, scan_segments
 
-    assert scan_segments(16, 256) == 8 and scan_segments(128, 64) == 1 and scan_segments(1, 8) == 2
+    assert scan_segments(16, 256) == 8 and scan_segments(128, 64) == 1 and scan_segments(1, 8) == 1
+    assert scan_segments(64, 64) == 1 and scan_segments(32, 128) == 4
     D = 128
     q = torch.nn.functional.normalize(_r(B, S, H, D, seed=1).float(), dim=-1).to(BF16)
     k = torch.nn.functional.normalize(_r(B, S, H, D, seed=2).float(), dim=-1).to(BF16)
