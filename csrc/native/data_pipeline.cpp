@@ -16,6 +16,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 #include <zlib.h>
+#include <sys/stat.h>
 
 #include <map>
 #include <set>
@@ -759,6 +760,8 @@ class Orchestrator {
       if (::mkdir(dir.c_str(), 0777) != 0) throw Error("Other", dir + ": " + std::strerror(errno));
       return;
     }
+    struct stat sb;
+    if (::stat(dir.c_str(), &sb) != 0 || !S_ISDIR(sb.st_mode)) throw Error("Other", dir + ": not a directory");
     const std::string path = dir + "/events.jsonl";
     if (!file_exists(path)) return;
     const std::string text = read_file(path);
