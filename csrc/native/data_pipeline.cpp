@@ -66,9 +66,27 @@ void push_break(std::string& out) {
   if (!out.empty() && out.back() != '\n') out.push_back('\n');
 }
 
+void append_utf8(unsigned long cp, std::string& out) {
+  if (cp < 0x80) out.push_back(static_cast<char>(cp));
+  else if (cp < 0x800) {
+    out.push_back(static_cast<char>(0xC0 | (cp >> 6)));
+    out.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
+  } else if (cp < 0x10000) {
+    out.push_back(static_cast<char>(0xE0 | (cp >> 12)));
+    out.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F)));
+    out.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
+  } else {
+    out.push_back(static_cast<char>(0xF0 | (cp >> 18)));
+    out.push_back(static_cast<char>(0x80 | ((cp >> 12) & 0x3F)));
+    out.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F)));
+    out.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
+  }
+}
+
 std::string decode_entities(const std::string& s) {
-  static const std::map<std::string, std::string> named = {{"amp", "&"}, {"lt", "<"}, {"gt", ">"}, {"quot", "\""},
-                                                           {"apos", "'"}, {"nbsp", "\xC2\xA0"}};
+  static const std::map<std::string, unsigned long> named = {
+#include "html_entities.inc"
+      {"apos", 0x27}};
   std::string out;
   for (size_t i = 0; i < s.size();) {
     if (s[i] == '&') {
@@ -77,7 +95,7 @@ std::string decode_entities(const std::string& s) {
         const std::string name = s.substr(i + 1, semi - i - 1);
         auto it = named.find(name);
         if (it != named.end()) {
-          out += it->second;
+          append_utf8(it->second, out);
           i = semi + 1;
           continue;
         }
@@ -86,20 +104,7 @@ std::string decode_entities(const std::string& s) {
           char* end = nullptr;
           const unsigned long cp = std::strtoul(name.c_str() + (hex ? 2 : 1), &end, hex ? 16 : 10);
           if (*end == 0 && cp > 0 && cp < 0x110000) {
-            if (cp < 0x80) out.push_back(static_cast<char>(cp));
-            else if (cp < 0x800) {
-              out.push_back(static_cast<char>(0xC0 | (cp >> 6)));
-              out.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
-            } else if (cp < 0x10000) {
-              out.push_back(static_cast<char>(0xE0 | (cp >> 12)));
-              out.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F)));
-              out.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
-            } else {
-              out.push_back(static_cast<char>(0xF0 | (cp >> 18)));
-              out.push_back(static_cast<char>(0x80 | ((cp >> 12) & 0x3F)));
-              out.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F)));
-              out.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
-            }
+            append_utf8(cp, out);
             i = semi + 1;
             continue;
           }

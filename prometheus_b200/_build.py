@@ -141,7 +141,7 @@ def build_native(verbose: bool = False, force: bool = False, sanitize: str = "")
         raise ValueError("sanitize must be '', 'address,undefined' or 'thread'")
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
-    headers = list((CSRC / "native").glob("*.hpp")) + list((CSRC / "native").glob("*.h"))
+    headers = [h for pat in ("*.hpp", "*.h", "*.inc") for h in (CSRC / "native").glob(pat)]
     inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
            "-I", CSRC / "native"]
     flags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function"]
