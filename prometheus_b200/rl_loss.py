@@ -179,6 +179,8 @@ def pack_groups(groups: Sequence[Group], trainer_version: int, config: LossConfi
                 raise LossError("trainer and rollout token log-probs must be non-empty and equally long")
             if len(s.latent_logp_trainer) != len(s.latent_logp_rollout):
                 raise LossError("trainer and rollout latent log-probs must be equally long")
+            if not _is_t(s.reward) and not math.isfinite(s.reward):
+                raise LossError("a reward is not finite")
             gap = staleness(trainer_version, s.policy_version)
             if gap > config.max_staleness:
                 raise LossError(f"rollout is {gap} versions stale (limit {config.max_staleness})")
