@@ -122,6 +122,8 @@ def _validate_delta(q, k, v, beta, state):
         raise KernelError(f"v shape {tuple(v.shape)} incompatible with q {tuple(q.shape)}")
     if tuple(beta.shape) != tuple(q.shape[:3]):
         raise KernelError(f"beta shape {tuple(beta.shape)} != {tuple(q.shape[:3])}")
+    if beta.device.type == "cpu" and not beta.requires_grad and bool((beta < 0).any()):
+        raise KernelError("beta must be in (0, 1]")            # host tensors only: no device sync
     b, _, h, dk = q.shape
     dv = v.shape[-1]
     if state is None:
@@ -328,7 +330,7 @@ class _Fp8LinearFn(torch.autograd.Function):
 def fp8_linear(x, weight, block: int = DEFAULT_FP8_BLOCK, *, weight_2d: bool = False) -> Tensor:
     """FP8 block-scaled linear: x (..., K), weight (N, K) -> (..., N), fp32 accumulate."""
     x, weight = _f32(x), _f32(weight)
-    if weight.ndim != 2 or x.shape[-1] != weight.shape[-1]:
+    if weight.ndim != 2 or x.ndim < 1 or x.shape[-1] != weight.shape[-1]:
         raise KernelError(f"fp8_linear shapes {tuple(x.shape)} x {tuple(weight.shape)}")
     return _Fp8LinearFn.apply(x, weight, int(block), bool(weight_2d))
 
