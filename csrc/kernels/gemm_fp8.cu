@@ -15,7 +15,8 @@
 //   warps 2-9  promotion + epilogue, two groups of four warps, one per 128-column half (one B
 //            scale each): every thread owns one output row of its half; per K-block it reads
 //            the 128 partial sums from tensor memory (two 64-column batches per wait), scales
-//            them by sa * sb and adds them to 128 fp32 registers; after the last K-block the
+//            them by sa * sb and adds them to 128 fp32 registers with packed two-wide FMAs
+//            (fma.rn.f32x2: the promotion is bound by FMA issue slots); after the last K-block the
 //            row goes out as bf16 through a swizzled staging slab and TMA stores
 // Grouped mode (mixture-of-experts): row block m multiplies expert mblk_group[m] of a
 // [groups, N, K] weight tensor with scales [groups, N / 128, K / 128]; negative = skip.
@@ -62,6 +63,25 @@ struct Params {
   uint64_t wait_budget_ns;
 };
 
+// Two fp32 FMAs in one instruction (fma.rn.f32x2): a0 += s * x0, a1 += s * x1, each rounded
+// like fmaf. The promotion is bound by FMA issue slots, and this halves them.
+__device__ __forceinline__ void fma2(float& a0, float& a1, float s, uint32_t x0, uint32_t x1) {
+  asm("{\n\t.reg .b64 pa, pb, pc;\n\t"
+      "mov.b64 pa, {%0, %1};\n\t"
+      "mov.b64 pb, {%3, %4};\n\t"
+      "mov.b64 pc, {%2, %2};\n\t"
+      "fma.rn.f32x2 pa, pc, pb, pa;\n\t"
+      "mov.b64 {%0, %1}, pa;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "f"(s), "r"(x0), "r"(x1));
+}
+
+// PROBE 0 is the product. The others exist only in the debug build of the library and time
+// parts of the kernel (their output is not the product's): 1 = no promotion (loads, MMAs and
+// the per-K-block accumulator hand-over only), 2 = accumulation in place with one hand-over
+// per tile (the ceiling of this tile shape and operand feed), 3 = promotion FMAs without the
+// tensor-memory loads, 4 = tensor-memory loads without the FMAs.
+template <int PROBE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, const Params p) {
@@ -156,9 +176,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         int m_blk, n_blk;
         coords(t, m_blk, n_blk);
         if (group_of(m_blk) < 0) continue;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        for (int kb = 0; kb < nkb; it += (PROBE == 2 ? (kb == nkb - 1) : 1), ++kb) {
           const int acc = it & 1;
-          if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
+          if ((PROBE != 2 || kb == 0) && !mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
           if (!mbar_wait(&full[s], ph, p.status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smA + s * A_BYTES);
@@ -166,9 +186,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < BK / 32; ++j)
             umma_f8(tmem_base + acc * BN, make_sdesc_sw128(a_addr + j * 32, 16, 1024),
-                    make_sdesc_sw128(b_addr + j * 32, 16, 1024), idesc, j > 0 ? 1u : 0u);
+                    make_sdesc_sw128(b_addr + j * 32, 16, 1024), idesc,
+                    (j > 0 || (PROBE == 2 && kb > 0)) ? 1u : 0u);
           umma_commit(&empty[s]);
-          umma_commit(&tfull[acc]);
+          if (PROBE != 2 || kb == nkb - 1) umma_commit(&tfull[acc]);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
@@ -204,7 +225,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         scale_cur = __ldcg(sa_row) * sb[0];
         have = true;
       }
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
+      for (int kb = 0; kb < (PROBE == 2 ? 1 : nkb); ++kb, ++it) {
         const int a = it & 1;
         if (!mbar_wait(&tfull[a], (it >> 1) & 1, p.status)) { ok = false; break; }
         tc_fence_after();
@@ -216,17 +237,34 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         const uint32_t t_addr =
             tmem_base + a * BN + half * HALF + (static_cast<uint32_t>(q * 32) << 16);
+        if constexpr (PROBE == 0) {
 #pragma unroll
-        for (int c = 0; c < HALF; c += 64) {
-          uint32_t r0[32], r1[32];
-          tmem_ld_32x32b_x32(t_addr + c, r0);
-          tmem_ld_32x32b_x32(t_addr + c + 32, r1);
-          tmem_ld_wait();
+          for (int c = 0; c < HALF; c += 64) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(t_addr + c, r0);
+            tmem_ld_32x32b_x32(t_addr + c + 32, r1);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            acc[c + i] = fmaf(scale, __uint_as_float(r0[i]), acc[c + i]);
-            acc[c + 32 + i] = fmaf(scale, __uint_as_float(r1[i]), acc[c + 32 + i]);
+            for (int i = 0; i < 32; i += 2) {
+              fma2(acc[c + i], acc[c + i + 1], scale, r0[i], r0[i + 1]);
+              fma2(acc[c + 32 + i], acc[c + 32 + i + 1], scale, r1[i], r1[i + 1]);
+            }
           }
+        } else if constexpr (PROBE == 3) {
+          const float v = __uint_as_float(0x3f800000u + (kb & 3));
+#pragma unroll
+          for (int i = 0; i < HALF; ++i) acc[i] = fmaf(scale, v + i, acc[i]);
+        } else if constexpr (PROBE == 4) {
+#pragma unroll
+          for (int c = 0; c < HALF; c += 64) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(t_addr + c, r0);
+            tmem_ld_32x32b_x32(t_addr + c + 32, r1);
+            tmem_ld_wait();
+            acc[c] = fmaf(scale, __uint_as_float(r0[0]) + __uint_as_float(r1[31]), acc[c]);
+          }
+        } else {
+          acc[0] += scale + __uint_as_float(t_addr & 1u);
         }
         tc_fence_before();
         mbar_arrive(&tempty[a]);
@@ -575,6 +613,7 @@ PB_API int pb_fp8_fakequant_blocks(const void* w, long ld, int rows, int K, void
 // C [M, N] bf16 = block-scaled Aq [M, K] x Bq [groups, N, K]^T. K % 128 == 0, N % 8 == 0.
 // sa [K / 128, M]; sb [groups, ceil(N / 128), K / 128]; mblk_group null (groups == 1) or one
 // int per 128-row block of A / C.
+template <int PROBE = 0>
 static int gemm_fp8_launch(const void* Aq, const float* sa, const void* Bq, const float* sb,
                            void* C, int M, int N, int K, int groups, long ldc,
                            const int* mblk_group, int* status, int max_ctas,
@@ -606,6 +645,23 @@ PB_API int pb_gemm_fp8_grouped_arrive(const void* Aq, const float* sa, const voi
                          static_cast<const uint32_t*>(blk_arrived), blk_expect, budget_ns, st);
 }
 
+#ifdef PB_DEBUG_BOUNDS
+// Debug build only: the timing probes of gemm_fp8_kernel (1 no promotion, 2 accumulation in
+// place, 3 FMAs only, 4 tensor-memory loads only). C receives values that are not the product.
+PB_API int pb_gemm_fp8_probe(const void* Aq, const float* sa, const void* Bq, const float* sb,
+                             void* C, int M, int N, int K, long ldc, int probe, int* status,
+                             cudaStream_t st) {
+  switch (probe) {
+    case 1: return gemm_fp8_launch<1>(Aq, sa, Bq, sb, C, M, N, K, 1, ldc, nullptr, status, 0, nullptr, nullptr, 0, st);
+    case 2: return gemm_fp8_launch<2>(Aq, sa, Bq, sb, C, M, N, K, 1, ldc, nullptr, status, 0, nullptr, nullptr, 0, st);
+    case 3: return gemm_fp8_launch<3>(Aq, sa, Bq, sb, C, M, N, K, 1, ldc, nullptr, status, 0, nullptr, nullptr, 0, st);
+    case 4: return gemm_fp8_launch<4>(Aq, sa, Bq, sb, C, M, N, K, 1, ldc, nullptr, status, 0, nullptr, nullptr, 0, st);
+    default: return PB_BAD_ARG;
+  }
+}
+#endif
+
+template <int PROBE>
 static int gemm_fp8_launch(const void* Aq, const float* sa, const void* Bq, const float* sb,
                            void* C, int M, int N, int K, int groups, long ldc,
                            const int* mblk_group, int* status, int max_ctas,
@@ -621,7 +677,7 @@ static int gemm_fp8_launch(const void* Aq, const float* sa, const void* Bq, cons
     return PB_BAD_ARG;
   static pb::DeviceOnce attr_once;   // per device: the attribute belongs to the current GPU
   if (attr_once.need()) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel<PROBE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_once.done();
@@ -642,6 +698,6 @@ static int gemm_fp8_launch(const void* Aq, const float* sa, const void* Bq, cons
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = static_cast<int>(tiles);
-  gemm_fp8_kernel<<<grid, THREADS, SMEM_TOTAL, st>>>(tmA, tmB, tmC, p);
+  gemm_fp8_kernel<PROBE><<<grid, THREADS, SMEM_TOTAL, st>>>(tmA, tmB, tmC, p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -98,6 +98,7 @@ _SIGS = {
     "pb_copy_rows_dyn": [P, P, L, L, P, P],
     "pb_gemm_fp8_blockscaled": [P, P, P, P, P, I, I, I, I, L, P, P, I, P],
     "pb_gemm_fp8_grouped_arrive": [P, P, P, P, P, I, I, I, I, L, P, P, P, L, P, P],
+    "pb_gemm_fp8_probe": [P, P, P, P, P, I, I, I, L, I, P, P],       # debug build only
     "pb_gemm_set_variant": [I],
     "pb_gemm_bf16": [P, P, P, P, I, I, I, I, L, L, L, L, L, L, L, L, I, I, I, I, F, F, P, I, P],
 }

@@ -147,9 +147,23 @@ def bench_fp8(a):
     ms = timeit(lambda: fp8.gemm_fp8(xq, sx, wq, sw), a.iters)
     ms_q = timeit(lambda: fp8.quantize_rows(x), a.iters)
     tf = 2.0 * a.m * a.n * a.k / ms / 1e9
-    return {"kernel": "gemm_fp8_blockscaled", "m": a.m, "n": a.n, "k": a.k, "ms": ms, "tflops": tf,
-            "vs_bf16_peak": tf / peaks()["bf16_tflops"], "quant_rows_ms": ms_q,
-            "quant_rows_gbs": (a.m * a.k * 3 + a.m * a.k // 32) / ms_q / 1e6}
+    out = {"kernel": "gemm_fp8_blockscaled", "m": a.m, "n": a.n, "k": a.k, "ms": ms, "tflops": tf,
+           "vs_bf16_peak": tf / peaks()["bf16_tflops"], "quant_rows_ms": ms_q,
+           "quant_rows_gbs": (a.m * a.k * 3 + a.m * a.k // 32) / ms_q / 1e6}
+    if a.probes:
+        # Parts of the kernel timed alone (debug build of the library: PB200_DEBUG_BOUNDS=1).
+        # Their outputs are not products; only the times mean something.
+        from ._lib import call, ptr, stream_ptr
+        from .functional import status_word
+
+        c = torch.empty((a.m, a.n), dtype=BF16, device="cuda")
+        names = {1: "no_promotion", 2: "accumulate_in_place", 3: "fma_only", 4: "tmem_loads_only"}
+        for probe, name in names.items():
+            t = timeit(lambda: call("pb_gemm_fp8_probe", ptr(xq), ptr(sx), ptr(wq), ptr(sw), ptr(c), a.m, a.n, a.k, a.n,
+                                    probe, ptr(status_word(x.device)), stream_ptr()), a.iters)
+            out[f"probe_{name}_ms"] = t
+            out[f"probe_{name}_tflops"] = 2.0 * a.m * a.n * a.k / t / 1e9
+    return out
 
 
 def bench_moe(a):
@@ -369,6 +383,8 @@ def main():
     f.add_argument("--m", type=int, default=8192)
     f.add_argument("--n", type=int, default=8192)
     f.add_argument("--k", type=int, default=8192)
+    f.add_argument("--probes", action="store_true",
+                   help="also time the kernel's parts alone (needs PB200_DEBUG_BOUNDS=1: the debug build)")
     mo = sub.add_parser("moe")
     mo.add_argument("--tokens", type=int, default=32768)
     mo.add_argument("--experts", type=int, default=8)
