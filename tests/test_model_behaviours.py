@@ -128,7 +128,7 @@ def test_rope_two_dimensional():
 # ------------------------------------------------------------------------------ linear attention
 def np_delta(q, k, v, s0=None):
     q, k, v = (np.asarray(x, dtype=np.float64) for x in (q, k, v))
-    norm = lambda x: x / np.sqrt((x ** 2).sum(-1, keepdims=True) + 1e-6 ** 2) if False else x / np.maximum(np.linalg.norm(x, axis=-1, keepdims=True), 1e-6)
+    norm = lambda x: x / np.maximum(np.linalg.norm(x, axis=-1, keepdims=True), 1e-6)
     q, k = norm(q), norm(k)
     b, s, h, d = q.shape
     S = np.zeros((b, h, d, d)) if s0 is None else np.asarray(s0, dtype=np.float64).copy()
