@@ -409,6 +409,11 @@ class Tokenizer {
       t.merges.emplace_back(static_cast<uint32_t>(o.at("left").as_u64()),
                             static_cast<uint32_t>(o.at("right").as_u64()));
     }
+    // the contract names the hash of the vocabulary file it was written with: a file that was
+    // edited or swapped afterwards does not load
+    if (const Json* h = c.find("vocab_hash"))
+      if (h->is_string() && h->as_string() != sha256_hex(blob))
+        throw Error("Message", "vocab.jsonl does not match the vocab_hash in tokenizer.json");
     return t;
   }
 

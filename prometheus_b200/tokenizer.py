@@ -46,6 +46,13 @@ def _wrap(fn, *args):
         raise TokenizerError(str(e)) from None
 
 
+def _ids(values, what: str) -> list:
+    out = [int(v) for v in values]
+    if any(v < 0 for v in out):
+        raise TokenizerError(f"negative {what} {min(out)}")
+    return out
+
+
 class Tokenizer:
     def __init__(self, impl) -> None:
         self._t = impl
@@ -70,17 +77,17 @@ class Tokenizer:
         return _wrap(self._t.encode, text)
 
     def decode(self, ids: Sequence[int]) -> str:
-        return _wrap(self._t.decode, [int(i) for i in ids])
+        return _wrap(self._t.decode, _ids(ids, "token id"))
 
     def encode_bytes(self, data: bytes) -> list:
         return _wrap(self._t.encode_bytes, data)
 
     def decode_bytes(self, ids: Sequence[int]) -> bytes:
-        return bytes(_wrap(self._t.decode_bytes, [int(i) for i in ids]))
+        return bytes(_wrap(self._t.decode_bytes, _ids(ids, "token id")))
 
     def encode_grid(self, cells: Sequence[int]) -> list:
         """One token per cell (``FIRST_ARC + colour``) for the row-major flattening of a grid."""
-        return _wrap(self._t.encode_grid, [int(c) for c in cells])
+        return _wrap(self._t.encode_grid, _ids(cells, "grid color"))
 
     def tokens_per_word(self, text: str) -> float:
         return _wrap(self._t.tokens_per_word, text)
