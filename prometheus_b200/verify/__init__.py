@@ -592,9 +592,22 @@ def run_v6(*, gpus: int = 4) -> dict:
 # ---------------------------------------------------------------------------
 # V7  RL loop controls
 # ---------------------------------------------------------------------------
-def run_v7(*, gpus: int = 8, steps: int = 60) -> dict:
+V7_PARITY_THRESHOLD = 0.05        # mean |trainer log-prob - rollout log-prob| that halts the run
+V7_INJECTED_DRIFT = 0.4
+
+
+def run_v7(*, gpus: int = 8, steps: int = 60, update: bool = True, inject_drift: bool = True,
+           plant_write: str | None = "grader") -> dict:
     """A 4-armed verifiable bandit trained with the sequence-level clipped objective; the
-    parity monitor halts on an injected log-prob drift; a write to the grader's files is flagged."""
+    parity monitor halts on an injected log-prob drift; a write to the grader's files is flagged.
+
+    The three keyword switches are the stage's negative controls: without the policy update the
+    reward must not rise, without the injected drift the monitor must not halt, and a write to
+    an agent path (or no write) must not be flagged."""
+    if isinstance(gpus, bool) or not isinstance(gpus, int) or gpus < 1:
+        raise VerifyError("gpus must be a positive integer")
+    if plant_write not in ("grader", "agent", None):
+        raise VerifyError("plant_write must be 'grader', 'agent' or None")
     R = rl_loss
     g = torch.Generator().manual_seed(0)
     logits = torch.zeros(4, requires_grad=True)
@@ -613,16 +626,19 @@ def run_v7(*, gpus: int = 8, steps: int = 60) -> dict:
         clipped = torch.minimum(ratio * torch.tensor(adv), torch.clamp(ratio, 1 - cfg.clip_eps_low, 1 + cfg.clip_eps_high) * torch.tensor(adv))
         (-(clipped.mean())).backward()
         with torch.no_grad():
-            logits -= 0.5 * logits.grad
+            if update:
+                logits -= 0.5 * logits.grad
             logits.grad = None
     rises = sum(rewards_seen[-10:]) / 10 > sum(rewards_seen[:10]) / 10 + 0.2
     # parity halt: the trainer / rollout log-prob gap of a drifted policy is past the tolerance and
     # the kill switch freezes the lab; a second kill is refused because it is already frozen
-    drift = [abs(a - b) for a, b in zip([-1.0, -2.0, -0.5], [-1.4, -2.6, -0.9])]
+    trainer_lp = [-1.0, -2.0, -0.5]
+    rollout_lp = [x - (V7_INJECTED_DRIFT if inject_drift else 0.0) for x in trainer_lp]
+    drift = [abs(a - b) for a, b in zip(trainer_lp, rollout_lp)]
     halted = False
     with tempfile.TemporaryDirectory() as tmp:
         m = native.monitors.Monitors(str(Path(tmp) / "freeze.json"))
-        if sum(drift) / len(drift) > 0.05:
+        if sum(drift) / len(drift) > V7_PARITY_THRESHOLD:
             m.kill("log-prob parity drift", 1)
         halted = bool(m.frozen())
     # reward hacking: a write under the grader root is refused and recorded as a tamper flag
@@ -631,10 +647,13 @@ def run_v7(*, gpus: int = 8, steps: int = 60) -> dict:
     pool.register_image(E.Image("v7", {"/work/a.txt": b"x"}, {"/grader/test.py": b"assert 1"}, {}))
     sb = pool.fork_group(pool.snapshot_from_image("v7"), 1)[0]
     flagged = False
-    try:
-        pool.call(sb, "evil", "shell", json.dumps({"command": "echo pass > /grader/test.py"}), None, 5)
-    except native.NativeError as e:
-        flagged = e.kind == "TestFileWrite" and len(pool.tamper_flags) == 1
+    if plant_write is not None:
+        target = "/grader/test.py" if plant_write == "grader" else "/work/notes.txt"
+        try:
+            pool.call(sb, "evil", "shell", json.dumps({"command": f"echo pass > {target}"}), None, 5)
+        except native.NativeError as e:
+            flagged = e.kind == "TestFileWrite"
+    flagged = flagged and len(pool.tamper_flags) == 1
     return {"reward_rises": bool(rises), "logprob_drift_halted": bool(halted), "planted_write_flagged": bool(flagged),
             "gpus": int(gpus), "mean_reward_first10": sum(rewards_seen[:10]) / 10, "mean_reward_last10": sum(rewards_seen[-10:]) / 10}
 
@@ -642,10 +661,11 @@ def run_v7(*, gpus: int = 8, steps: int = 60) -> dict:
 # ---------------------------------------------------------------------------
 # V8  serving parity
 # ---------------------------------------------------------------------------
-def run_v8(*, gpus: int = 1) -> dict:
+def run_v8(*, gpus: int = 1, perturb: float = 0.0) -> dict:
     """Weights exported through the weight-export contract and loaded back give the same
     log-probs as the training-side forward; a session whose KV tier was swapped out and
-    restored decodes the same tokens."""
+    restored decodes the same tokens. ``perturb`` (negative control) adds that much to every
+    served weight: the log-prob check must then fail."""
     from .. import export, fork
 
     cfg = _small_config()
@@ -662,7 +682,7 @@ def run_v8(*, gpus: int = 1) -> dict:
         loaded = {}
         for sh in exp.shards:
             arr = export.dequantize(np.load(Path(tmp) / sh.path), None, "bf16")
-            loaded[sh.name] = torch.from_numpy(np.asarray(arr, dtype=np.float32)).reshape(flat[sh.name].shape)
+            loaded[sh.name] = torch.from_numpy(np.asarray(arr, dtype=np.float32)).reshape(flat[sh.name].shape) + float(perturb)
         served = train._map_tree(params, lambda n, _t: loaded[n])
     with torch.no_grad():
         lp = torch.log_softmax(model.forward(tok, params, cfg, r=1).logits, -1)
@@ -681,9 +701,11 @@ def run_v8(*, gpus: int = 1) -> dict:
 # ---------------------------------------------------------------------------
 # V9  one research cycle
 # ---------------------------------------------------------------------------
-def run_v9(*, gpus: int = 1) -> dict:
+def run_v9(*, gpus: int = 1, planted_effect: float = 0.2) -> dict:
     """Two planted ideas go through propose -> run -> replicate -> record on the ledger: the
-    known positive replicates (effect in both seeds), the known negative is recorded as negative."""
+    known positive replicates (effect in both seeds), the known negative is recorded as negative.
+    ``planted_effect`` is the loss the planted positive removes (negative control: with 0 it is
+    not found, and both ideas are recorded as negatives)."""
     L = native.ledger
     with tempfile.TemporaryDirectory() as tmp:
         led = L.Ledger(str(Path(tmp) / "ledger.jsonl"))
@@ -691,7 +713,7 @@ def run_v9(*, gpus: int = 1) -> dict:
         def measure(idea, seed):
             g = torch.Generator().manual_seed(seed)
             base = 1.0 + 0.01 * float(torch.randn((), generator=g))
-            return base - (0.2 if idea == "planted-positive" else 0.0)
+            return base - (float(planted_effect) if idea == "planted-positive" else 0.0)
 
         found, replicated, negative = False, False, False
         for idea in ("planted-positive", "planted-negative"):
@@ -715,18 +737,31 @@ def run_v9(*, gpus: int = 1) -> dict:
 # ---------------------------------------------------------------------------
 # V10  chaos soak
 # ---------------------------------------------------------------------------
-def run_v10(*, hours: float = 72.0, seed: int = 0) -> dict:
+def run_v10(*, hours: float = 72.0, seed: int = 0, drop_task: bool = False, duplicate_output: bool = False) -> dict:
     """The native chaos world advanced through ``hours`` of injected time with the soak fault
-    mix; the invariants give the three counters."""
-    if not (hours > 0 and math.isfinite(hours)):
+    mix; the invariants give the three counters. ``drop_task`` and ``duplicate_output`` are the
+    stage's negative controls: a task enqueued and never completed, and one attempt completed
+    twice, after the soak; the counters must then show them."""
+    if isinstance(hours, bool) or not isinstance(hours, (int, float)) or not (hours > 0 and math.isfinite(hours)):
         raise VerifyError("hours must be a positive finite number")
     CH = native.chaos
     with tempfile.TemporaryDirectory() as tmp:
         world = CH.World.create(str(Path(tmp) / "soak"), 3, 4, int(seed))
         rep = CH.run_soak(world, int(hours * 3600 * 1000), int(seed))
         inv = rep.invariants
+        dead = 0 if inv.hold() else 1      # a dead token breaks the soak's invariants as a whole
+        if drop_task or duplicate_output:
+            if rep.recovered is False:
+                world.recover()
+            now = int(world.now())
+            if drop_task:
+                world.enqueue_task("control-dropped", now)
+            if duplicate_output:
+                world.enqueue_task("control-twice", now)
+                world.complete_task("control-twice", 1, b"out", now)
+                world.complete_task("control-twice", 1, b"out", now)
+            inv = world.invariants()
         lost, dup = int(inv.lost_tasks), int(inv.duplicated_outputs)
-        dead = 0 if inv.hold() else 1      # a dead token breaks the invariants as a whole
     return {"hours": float(hours), "lost_tasks": lost, "duplicated_outputs": dup, "dead_tokens": dead,
             "faults_applied": int(rep.faults_applied)}
 
