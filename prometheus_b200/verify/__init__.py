@@ -423,11 +423,18 @@ def _v4_engine() -> dict:
     return {"resumed_bitwise_equal": bool(bitwise), "sdc_caught_flip": bool(caught)}
 
 
-def run_v4(*, gpus: int = 4) -> dict:
+def run_v4(*, gpus: int = 4, corrupt_restore: bool = False, check_hash: bool = True,
+           skip_bad_shard: bool = True) -> dict:
     """Faults: bitwise resume after a kill, a flipped bit caught by its hash, a loss spike rolled
     back with its shard skipped. On a GPU the first two run through ``engine.Trainer`` and
     ``checkpoint.TrainerCheckpointer`` (``_v4_engine``); the spike policy runs on the fp32 tree
-    step either way."""
+    step either way.
+
+    Negative controls: ``corrupt_restore`` flips one bit of the restored parameters (the resume
+    is then not bitwise equal), ``check_hash=False`` leaves the flipped shard unhashed (the flip
+    goes unreported), ``skip_bad_shard=False`` keeps the step taken on the bad shard."""
+    if isinstance(gpus, bool) or not isinstance(gpus, int) or gpus < 1:
+        raise VerifyError("gpus must be a positive integer")
     C = native.ckpt
     cfg = _small_config()
     tcfg = train.train_config_for(cfg, warmup_steps=1, stable_steps=50, decay_steps=5)
@@ -447,6 +454,10 @@ def run_v4(*, gpus: int = 4) -> dict:
             keys[name] = C.sha256_hex(data)
             store.put(keys[name], data)
         restored = {name: store.get(key) for name, key in keys.items()}
+        if corrupt_restore:
+            hit = bytearray(restored["params"])
+            hit[len(hit) // 3] ^= 0x01
+            restored["params"] = bytes(hit)
         same_blob = all(restored[n] == blobs[n] for n in blobs)
         flat_half = model.flatten_params(half)
         off, rebuilt = 0, {}
@@ -463,7 +474,7 @@ def run_v4(*, gpus: int = 4) -> dict:
         key = keys["params"]
         raw = bytearray(store.get(key))
         raw[len(raw) // 2] ^= 0x10
-        sdc = C.sha256_hex(bytes(raw)) != key
+        sdc = check_hash and C.sha256_hex(bytes(raw)) != key
         try:
             C.DirStore(str(Path(tmp) / "s")).put(key, bytes(raw))     # content-addressed: a wrong body is refused or ...
             sdc = sdc and C.sha256_hex(store.get(key)) in (key, C.sha256_hex(bytes(raw)))
@@ -476,12 +487,13 @@ def run_v4(*, gpus: int = 4) -> dict:
     bad = _batch(cfg, 2, 32, 999)
     trial = train.train_step(good, o, bad, cfg, tcfg, step=10, muon_transfer=True, muon_all_matrices=True)
     spike = float(trial.loss.ce) > 1.05 * max(losses[-2:])
-    after, _, _ = _train(cfg, tcfg, good, stream[9:10], start_step=10, opt=o) if spike else (trial.params, None, None)
+    rolled_back = spike and skip_bad_shard
+    after, _, _ = _train(cfg, tcfg, good, stream[9:10], start_step=10, opt=o) if rolled_back else (trial.params, None, None)
     ref, _, _ = _train(cfg, tcfg, params, stream)
     skipped = spike and _tree_bytes(after) == _tree_bytes(ref)
     out = {"resumed_bitwise_equal": bool(bitwise), "sdc_caught_flip": bool(sdc),
            "spike_rollback_skipped_shard": bool(skipped), "gpus": int(gpus), "path": "tree"}
-    if torch.cuda.is_available():
+    if torch.cuda.is_available() and not corrupt_restore and check_hash and skip_bad_shard:
         e = _v4_engine()
         out.update(resumed_bitwise_equal=out["resumed_bitwise_equal"] and e["resumed_bitwise_equal"],
                    sdc_caught_flip=out["sdc_caught_flip"] and e["sdc_caught_flip"], path="tree+engine")
@@ -547,11 +559,18 @@ def _v6_engine() -> dict:
     return {"accuracy_rises_with_latent_budget": bool(rises), "sweep_errors": errs}
 
 
-def run_v6(*, gpus: int = 4) -> dict:
+def run_v6(*, gpus: int = 4, freeze_budget: bool = False, pin_halt: bool = False, scramble_decode: bool = False) -> dict:
     """More Jacobi sweeps (latent budget) move the latent slots closer to the sequential
     solution; the halting losses stay finite over a short curriculum; a thought decodes to the
     ids it was built from. On a GPU the sweep check also runs through ``engine.Trainer``
-    (``_v6_engine``); the fp32 check uses a small contraction map as the network."""
+    (``_v6_engine``); the fp32 check uses a small contraction map as the network.
+
+    Negative controls: ``freeze_budget`` gives every arm one sweep (nothing can improve),
+    ``pin_halt`` feeds a halting head saturated at "stop at once" whose teacher wants the last
+    step (the halting loss leaves the finite range the gate allows), ``scramble_decode`` decodes
+    through a permuted unembedding (the thought no longer reads as its ids)."""
+    if isinstance(gpus, bool) or not isinstance(gpus, int) or gpus < 1:
+        raise VerifyError("gpus must be a positive integer")
     g = torch.Generator().manual_seed(0)
     d, k = 16, 8
     a = torch.randn(d, d, generator=g) * 0.2
@@ -565,23 +584,28 @@ def run_v6(*, gpus: int = 4) -> dict:
     exact, _ = latent.latent_slot_forward(embeds, forward_hidden, adapter, 8, k, n_sweeps=k + 1)
     errs = []
     for sweeps in (1, 2, 4, 8):
-        got, _ = latent.latent_slot_forward(embeds, forward_hidden, adapter, 8, k, n_sweeps=sweeps)
+        got, _ = latent.latent_slot_forward(embeds, forward_hidden, adapter, 8, k, n_sweeps=1 if freeze_budget else sweeps)
         errs.append(float((got - exact).abs().max()))
     rises = all(x >= y - 1e-9 for x, y in zip(errs, errs[1:])) and errs[-1] < errs[0]
     cfg = latent.LatentConfig()
     finite = True
     for stage in range(6):                      # curriculum: teacher steps shrink as compression grows
         logits = torch.randn(6, generator=g)
+        if pin_halt:
+            logits = torch.full((6,), 80.0)
         halt = latent.halt_from_logits(logits)
-        finite = finite and math.isfinite(float(latent.halt_loss(halt.p, max(1, 6 - stage)))) \
+        hl = float(latent.halt_loss(halt.p, 5 if pin_halt else max(1, 6 - stage)))
+        # a collapsed halting head puts (almost) no mass where the teacher stops: -log(eps) = 13.8
+        finite = finite and math.isfinite(hl) and hl < 10.0 \
             and math.isfinite(float(latent.halt_kl(halt.p, cfg.lambda_prior)))
     unembed = torch.randn(32, d, generator=g)
     ids = torch.tensor([3, 17, 9])
     hidden = unembed[ids] * 4.0
-    dec = (hidden @ unembed.t()).argmax(-1)
+    table = unembed[torch.randperm(32, generator=g)] if scramble_decode else unembed
+    dec = (hidden @ table.t()).argmax(-1)
     out = {"curriculum_no_collapse": bool(finite), "accuracy_rises_with_latent_budget": bool(rises),
            "thoughts_decode": bool(torch.equal(dec, ids)), "sweep_errors": errs, "gpus": int(gpus), "path": "fp32"}
-    if torch.cuda.is_available():
+    if torch.cuda.is_available() and not (freeze_budget or pin_halt or scramble_decode):
         e = _v6_engine()
         out.update(accuracy_rises_with_latent_budget=out["accuracy_rises_with_latent_budget"]
                    and e["accuracy_rises_with_latent_budget"], engine_sweep_errors=e["sweep_errors"],

@@ -71,3 +71,30 @@ def test_exit_checks_refuse_the_control_results(tmp_path):
         with pytest.raises(native.NativeError) as e:
             V.check_exit(stage, d)
         assert e.value.kind == "ExitFailed"
+
+
+def test_v4_each_fault_gate_can_fail():
+    good = V.run_v4()
+    assert all(good[k] for k in ("resumed_bitwise_equal", "sdc_caught_flip", "spike_rollback_skipped_shard"))
+    json.dumps(good)
+    assert V.run_v4(corrupt_restore=True)["resumed_bitwise_equal"] is False             # one flipped bit in the restored state
+    assert V.run_v4(check_hash=False)["sdc_caught_flip"] is False                        # a flip nobody hashes goes unreported
+    kept = V.run_v4(skip_bad_shard=False)
+    assert kept["spike_rollback_skipped_shard"] is False and kept["resumed_bitwise_equal"] is True     # the other gates are untouched
+    for bad in (0, -2, True):
+        with pytest.raises(V.VerifyError):
+            V.run_v4(gpus=bad)
+
+
+def test_v6_each_latent_gate_can_fail():
+    good = V.run_v6()
+    assert all(good[k] for k in ("curriculum_no_collapse", "accuracy_rises_with_latent_budget", "thoughts_decode"))
+    assert good["sweep_errors"] == sorted(good["sweep_errors"], reverse=True) and good["sweep_errors"][-1] < good["sweep_errors"][0]
+    frozen = V.run_v6(freeze_budget=True)
+    assert frozen["accuracy_rises_with_latent_budget"] is False and len(set(frozen["sweep_errors"])) == 1
+    assert V.run_v6(pin_halt=True)["curriculum_no_collapse"] is False
+    assert V.run_v6(scramble_decode=True)["thoughts_decode"] is False
+    assert V.run_v6(gpus=1)["gpus"] == 1
+    for bad in (0, -1, True):
+        with pytest.raises(V.VerifyError):
+            V.run_v6(gpus=bad)
