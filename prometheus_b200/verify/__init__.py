@@ -503,7 +503,14 @@ def run_v4(*, gpus: int = 4, corrupt_restore: bool = False, check_hash: bool = T
 # ---------------------------------------------------------------------------
 # V5  small-scale ladder fit and resume across job boundaries
 # ---------------------------------------------------------------------------
-def run_v5(*, gpus: int = 8, steps: int = 40) -> dict:
+def run_v5(*, gpus: int = 8, steps: int = 40, reverse_curve: bool = False, fresh_optimizer_on_resume: bool = False) -> dict:
+    """A short ladder run: the loss curve is close to a power law in the step count, and a run
+    split over two jobs ends bitwise where the unsplit run ends. Negative controls:
+    ``reverse_curve`` fits the curve backwards (a rising loss must not pass), and
+    ``fresh_optimizer_on_resume`` drops the optimizer state at the job boundary (the second job
+    then cannot reproduce the unsplit run)."""
+    if isinstance(gpus, bool) or not isinstance(gpus, int) or gpus < 1:
+        raise VerifyError("gpus must be a positive integer")
     cfg = _small_config(n_dense=1, n_moe=3, n_routed_experts=4, top_k=2, expert_hidden=64)
     tcfg = train.train_config_for(cfg, warmup_steps=2, stable_steps=steps, decay_steps=4)
     params = model.init_params(cfg, 0)
@@ -512,6 +519,8 @@ def run_v5(*, gpus: int = 8, steps: int = 40) -> dict:
     batches = [train.Batch(tokens=base[(i % 4) * 2:(i % 4) * 2 + 2], loss_mask=torch.ones(2, 32),
                            positions=torch.arange(32)) for i in range(steps)]
     _, _, losses = _train(cfg, tcfg, params, batches)
+    if reverse_curve:
+        losses = losses[::-1]
     # ladder fit: log-loss against log-step is close to a line with negative slope
     xs = [math.log(i + 1) for i in range(4, steps)]
     ys = [math.log(max(l, 1e-6)) for l in losses[4:]]
@@ -523,7 +532,8 @@ def run_v5(*, gpus: int = 8, steps: int = 40) -> dict:
     # two "jobs": the second starts from the first one's saved state
     a, oa, _ = _train(cfg, tcfg, params, batches[:steps // 2])
     saved = (_tree_bytes(a), _tree_bytes(oa))
-    b2, _, _ = _train(cfg, tcfg, a, batches[steps // 2:], start_step=steps // 2 + 1, opt=oa)
+    b2, _, _ = _train(cfg, tcfg, a, batches[steps // 2:], start_step=steps // 2 + 1,
+                      opt=None if fresh_optimizer_on_resume else oa)
     full, _, _ = _train(cfg, tcfg, params, batches)
     resume_ok = saved[0] == _tree_bytes(a) and _tree_bytes(b2) == _tree_bytes(full)
     return {"loss_curve_matches_ladder": bool(fit_ok), "checkpoint_resume_ok": bool(resume_ok), "slope": slope,

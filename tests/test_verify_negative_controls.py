@@ -98,3 +98,14 @@ def test_v6_each_latent_gate_can_fail():
     for bad in (0, -1, True):
         with pytest.raises(V.VerifyError):
             V.run_v6(gpus=bad)
+
+
+def test_v5_curve_and_resume_gates_can_fail():
+    good = V.run_v5(steps=16)
+    assert good["loss_curve_matches_ladder"] and good["checkpoint_resume_ok"] and good["slope"] < 0
+    assert V.run_v5(steps=16, reverse_curve=True)["loss_curve_matches_ladder"] is False
+    lost = V.run_v5(steps=16, fresh_optimizer_on_resume=True)
+    assert lost["checkpoint_resume_ok"] is False and lost["loss_curve_matches_ladder"] is True
+    for bad in (0, -1, True):
+        with pytest.raises(V.VerifyError):
+            V.run_v5(gpus=bad)
