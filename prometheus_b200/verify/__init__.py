@@ -161,7 +161,7 @@ def run_v1(*, gpus: int = 1) -> dict:
 # ---------------------------------------------------------------------------
 # V2  single device vs sharded / dispatched execution
 # ---------------------------------------------------------------------------
-def run_v2(*, gpus: int = 8, steps: int = 20) -> dict:
+def run_v2(*, gpus: int = 8, steps: int = 20, drop_rank: bool = False) -> dict:
     """Single device against the mesh, through the production definitions:
 
     * data parallel + FSDP: every step, the gradient of the whole batch equals the per-rank
@@ -173,7 +173,12 @@ def run_v2(*, gpus: int = 8, steps: int = 20) -> dict:
       attention, and the delta-rule state handed from slice to slice equals the state of the
       whole prefix;
     * on a machine with two or more GPUs: the fused trainer on one GPU, replicated over two and
-      ZeRO-3 over two give the same losses (``tests/_multi_gpu_worker.py`` is the worker)."""
+      ZeRO-3 over two give the same losses (``tests/_multi_gpu_worker.py`` is the worker).
+
+    ``drop_rank`` (negative control) loses the last rank's gradient before the reduction: the
+    reduced gradient then differs from the whole-batch one and the stage must fail."""
+    if isinstance(gpus, bool) or not isinstance(gpus, int) or gpus < 1:
+        raise VerifyError("gpus must be a positive integer")
     from .. import parallel as P
     from ..parallel import cp as cp_mod
     from ..parallel import fsdp
@@ -207,6 +212,8 @@ def run_v2(*, gpus: int = 8, steps: int = 20) -> dict:
             if g_full.numel() < n:
                 continue
             flat_r = [g[name].reshape(-1) / n for g in per_rank]          # equal slices: mean of the means
+            if drop_rank:
+                flat_r[-1] = torch.zeros_like(flat_r[-1])
             pad = (-flat_r[0].numel()) % n
             if pad:
                 flat_r = [torch.nn.functional.pad(f, (0, pad)) for f in flat_r]
@@ -259,7 +266,7 @@ def run_v2(*, gpus: int = 8, steps: int = 20) -> dict:
               "grad_rel_diff": float(worst_grad), "ep_rel_diff": ep_rel, "cp_attention_abs_diff": cp_rel,
               "cp_state_rel_diff": cp_state_rel, "routing_identical": bool(same_routing), "gpus": int(gpus),
               "ranks_emulated": n, "steps": steps}
-    if torch.cuda.is_available() and torch.cuda.device_count() >= 2:
+    if torch.cuda.is_available() and torch.cuda.device_count() >= 2 and not drop_rank:
         result["gpu_trainer_parity"] = _gpu_mesh_parity()
     return result
 
@@ -313,7 +320,7 @@ def _v3_engine(steps: int) -> dict:
     return out
 
 
-def run_v3(*, gpus: int = 8, steps: int | None = None) -> dict:
+def run_v3(*, gpus: int = 8, steps: int | None = None, crush_precision: bool = False) -> dict:
     """FP8 (block-scaled e4m3, straight-through gradient) against bf16 training from the same
     init on the same data. On a GPU the comparison runs through ``engine.Trainer`` (the fused
     kernels, FP8 GEMM included); without one, through the fp32 fake-quantisation of
@@ -323,10 +330,15 @@ def run_v3(*, gpus: int = 8, steps: int | None = None) -> dict:
     ``steps`` defaults to 480 on the engine path and 150 on the CPU path. The engine default
     runs until the loss curve flattens: while the loss is still falling fast the FP8 run trails
     the bf16 one by a few steps, which reads as a 1.5 - 2.3 % gap at 120 - 240 steps and as
-    0.2 % at 480 (measured on a B200); the gate of the stage is 0.5 %."""
+    0.2 % at 480 (measured on a B200); the gate of the stage is 0.5 %.
+
+    ``crush_precision`` (negative control, fp32 path) replaces the FP8 operands by their signs
+    times the mean magnitude: one bit is not enough, and the loss gap must exceed the gate."""
     from .. import export
 
-    if torch.cuda.is_available():
+    if isinstance(gpus, bool) or not isinstance(gpus, int) or gpus < 1:
+        raise VerifyError("gpus must be a positive integer")
+    if torch.cuda.is_available() and not crush_precision:
         steps = 480 if steps is None else int(steps)
         e = _v3_engine(steps)
         w = torch.randn(64, 64, generator=torch.Generator().manual_seed(0)).numpy()
@@ -346,7 +358,13 @@ def run_v3(*, gpus: int = 8, steps: int | None = None) -> dict:
     data = torch.randint(0, vocab, (steps, 16, seq), generator=g)
     data[:, :, 1::2] = (data[:, :, 0::2] * 3 + 1) % vocab      # learnable structure
 
+    def one_bit(t):
+        q = torch.sign(t) * t.abs().mean()
+        return t + (q - t).detach()                       # straight-through, like the FP8 path
+
     def lin(x, w, kind):
+        if kind == "fp8" and crush_precision:
+            return one_bit(x) @ one_bit(w).t()
         if kind == "fp8":
             return kernels.fp8_linear(x, w, 32)
         return (x.to(torch.bfloat16) @ w.to(torch.bfloat16).t()).float()

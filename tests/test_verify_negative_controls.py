@@ -109,3 +109,20 @@ def test_v5_curve_and_resume_gates_can_fail():
     for bad in (0, -1, True):
         with pytest.raises(V.VerifyError):
             V.run_v5(gpus=bad)
+
+
+def test_v2_fails_when_a_rank_is_lost_before_the_reduction():
+    good, bad = V.run_v2(steps=2), V.run_v2(steps=2, drop_rank=True)
+    assert good["loss_rel_diff"] < 1e-4 and good["routing_identical"] is True and good["ranks_emulated"] == 4
+    assert bad["grad_rel_diff"] > 0.1 and bad["loss_rel_diff"] > 0.1
+    for bad_gpus in (0, -1, True):
+        with pytest.raises(V.VerifyError):
+            V.run_v2(gpus=bad_gpus)
+
+
+def test_v3_fails_at_one_bit_of_precision():
+    good, bad = V.run_v3(steps=60), V.run_v3(steps=60, crush_precision=True)
+    assert good["fp8_loss_rel_diff"] <= 0.005 and good["nvfp4_numerics_ok"] is True
+    assert bad["fp8_loss_rel_diff"] > 0.005
+    with pytest.raises(V.VerifyError):
+        V.run_v3(gpus=0)
