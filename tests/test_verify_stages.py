@@ -128,7 +128,10 @@ def test_exit_checkers(tmp_path):
 
 @pytest.mark.parametrize("stage", ["v2", "v3", "v6", "v7", "v9", "v10"])
 def test_runners_meet_their_own_exit_criteria(stage, tmp_path):
-    kw = {"steps": 60} if stage == "v3" else ({"steps": 6} if stage == "v2" else {})
+    import torch
+
+    # with a GPU present v3 runs the fused trainer, which needs its default step count
+    kw = {"steps": 6} if stage == "v2" else ({"steps": 60} if stage == "v3" and not torch.cuda.is_available() else {})
     result = verify.run_stage(stage, **kw)
     verify.write_result(stage, result, tmp_path)
     verify.check_exit(stage, tmp_path)
