@@ -113,6 +113,8 @@ def ring_attention_rank(q, ks: Sequence, vs: Sequence, rank: int, *, causal: boo
 
 def ring_attention(q, k, v, n: int, *, causal: bool = True, scale: float | None = None) -> Tensor:
     """All ranks in one call: split, run every rank's fold, concatenate along the sequence."""
+    if _int(n, "n") < 1:
+        _err(f"n must be >= 1, got {n}")
     qs = [cp_split_seq(q, n, r) for r in range(n)]
     ks = [cp_split_seq(k, n, r) for r in range(n)]
     vs = [cp_split_seq(v, n, r) for r in range(n)]
