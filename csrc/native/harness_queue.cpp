@@ -297,7 +297,9 @@ std::pair<std::string, Json> work_payload(const std::string& module, const std::
   extra["module"] = module;
   extra["role"] = role;
   uint64_t round = 0;
-  if (const Json* r = extra.find("round"); r && r->is_integer()) round = r->as_u64();
+  // only a non-negative JSON integer names a round; a negative, fractional or textual one reads as round 0
+  if (const Json* r = extra.find("round"); r && (r->kind == Json::UInt || (r->kind == Json::Int && r->i >= 0)))
+    round = r->as_u64();
   std::string id = role + "/" + module + "/" + std::to_string(round);
   if (const Json* op = extra.find("op"); op && op->is_string()) id += "/" + op->as_string();
   if (const Json* c = extra.find("candidate"); c && c->is_string()) id += "/" + c->as_string();
