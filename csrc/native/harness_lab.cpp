@@ -754,6 +754,20 @@ class EvalGate {
 
 // ------------------------------------------------------------------------------- monitors
 const char* const kBoundaries[] = {"kernel", "graders", "held_out", "monitors"};
+// The freeze file names a boundary "Kernel" / "Graders" / "HeldOut" / "Monitors" (the format of
+// reference harness/monitors/src/lib.rs, so either implementation reads the other's file); the API
+// and the snapshot use the lower-case names above.
+const char* const kBoundariesOnDisk[] = {"Kernel", "Graders", "HeldOut", "Monitors"};
+std::string boundary_to_disk(const std::string& b) {
+  for (int i = 0; i < 4; ++i)
+    if (b == kBoundaries[i]) return kBoundariesOnDisk[i];
+  return b;
+}
+std::string boundary_from_disk(const std::string& s) {
+  for (int i = 0; i < 4; ++i)
+    if (s == kBoundariesOnDisk[i] || s == kBoundaries[i]) return kBoundaries[i];
+  throw Error("Message", "unknown boundary in freeze file: " + s);
+}
 
 struct Violation {
   std::string boundary, detail;
@@ -770,10 +784,12 @@ class Monitors {
       try {
         v = Json::parse(read_file(path_));
         frozen_ = v.at("frozen").as_bool();
-        if (!v.at("frozen_at").is_null()) frozen_at_ = v.at("frozen_at").as_u64();
-        if (!v.at("reason").is_null()) reason_ = v.at("reason").as_string();
+        // an absent or null time or reason reads as "none"; the list of violations must be there
+        if (const Json* a = v.find("frozen_at"); a && !a->is_null()) frozen_at_ = a->as_u64();
+        if (const Json* r = v.find("reason"); r && !r->is_null()) reason_ = r->as_string();
         for (const Json& x : v.at("violations").arr())
-          violations_.push_back({x.at("boundary").as_string(), x.at("detail").as_string(), x.at("at_ms").as_u64()});
+          violations_.push_back({boundary_from_disk(x.at("boundary").as_string()), x.at("detail").as_string(),
+                                 x.at("at_ms").as_u64()});
       } catch (const Error& e) {
         throw Error("Message", e.what());
       }
@@ -842,7 +858,7 @@ class Monitors {
     Json vs = Json::array();
     for (const auto& x : violations_) {
       Json o = Json::object();
-      o["boundary"] = x.boundary;
+      o["boundary"] = boundary_to_disk(x.boundary);
       o["at_ms"] = x.at_ms;
       o["detail"] = x.detail;
       vs.arr().push_back(o);
