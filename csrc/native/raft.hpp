@@ -71,7 +71,7 @@ struct TokenRecord {
 struct ControlState {
   std::vector<NodeInfo> membership;
   std::optional<RoleLease> coordinator, token_broker;
-  std::string kernel_version;
+  std::string kernel_version = "0";   // a fresh group runs kernel "0" until a release is committed
   std::optional<TokenRecord> token;
 };
 
